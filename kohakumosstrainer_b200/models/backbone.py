@@ -1,0 +1,169 @@
+"""MossBackbone: (packed latents, packed text, sigma, SeqInfo) -> packed velocity.
+
+Module names equal the official state-dict keys (`src/kohakumoss/model/backbone.py:27-222`):
+`video_embedder`, `text_embedder.{proj,blocks.i.*}`, `rope.bands`, `time_embedding.{0,2}`,
+`shared_block_modulation`, `layers.i.{norm1,norm2,q_norm,k_norm,proj.{q,k,v,o,ffn_up_gate,
+ffn_down}}`, `final_norm_video`, `video_head_modulation`, `final_linear_video`.
+
+The backbone is a pure function of its inputs; which blocks run is a plan resolved once
+(`bind_forward`), including the per-sample "segment skip" packed CFG uses.
+"""
+
+from __future__ import annotations
+
+from collections.abc import Callable
+
+import torch
+from torch import Tensor, nn
+
+from ..ops import OpSet, eager, resolve_ops
+from ..types.arch import MossArchConfig
+from ..types.seqinfo import SeqInfo
+from .block import HEAD_SCALE, HEAD_SHIFT, BlockCtx, JointBlock, TextEmbedder
+from .components import RMSNorm, RopeBands, TimeEmbedding
+from .linear import MossLinear
+from .runners import PlainRunner
+
+KEEP_FP32 = ("time_embedding", "shared_block_modulation", "video_head_modulation")
+
+
+class MossBackbone(nn.Module):
+    def __init__(self, cfg: MossArchConfig, device=None, dtype=None):
+        super().__init__()
+        cfg.validate()
+        kw = dict(device=device, dtype=dtype)
+        self.cfg = cfg
+        self.video_embedder = MossLinear(cfg.latent_channels, cfg.dim, **kw)
+        self.text_embedder = TextEmbedder(cfg, **kw)
+        self.rope = RopeBands(cfg.rope_bands, cfg.rope_base, device=device)
+        self.time_embedding = TimeEmbedding(cfg.freq_dim, cfg.dim, **kw)
+        self.shared_block_modulation = MossLinear(cfg.dim, 6 * cfg.dim, **kw)
+        self.layers = nn.ModuleList(JointBlock(cfg, i, **kw) for i in range(cfg.depth))
+        self.final_norm_video = RMSNorm(cfg.dim, cfg.eps, **kw)
+        self.final_linear_video = MossLinear(cfg.dim, cfg.latent_channels, bias=False, **kw)
+        self.video_head_modulation = MossLinear(cfg.dim, 2 * cfg.dim, **kw)
+        self.residual_scale: tuple[float, ...] = (1.0,) * cfg.depth
+        self.runner = PlainRunner()
+        self.ops: OpSet | None = None
+        self._default = self._plan_forward()
+
+    # -- construction -------------------------------------------------------------------
+    def init_weights(self, std: float = 0.02, generator: torch.Generator | None = None) -> None:
+        for module in self.modules():
+            if isinstance(module, MossLinear):
+                if module._parameters.get("weight") is not None:
+                    nn.init.normal_(module.weight, std=std, generator=generator)
+                if module.bias is not None:
+                    nn.init.zeros_(module.bias)
+            elif isinstance(module, RMSNorm):
+                module.init_weights()
+
+    def bind_ops(self, ops: OpSet | None = None) -> "MossBackbone":
+        """Resolve (or re-bind after a structural change) the op set for this model's
+        device and hand it to every block."""
+        if ops is None:
+            ops = resolve_ops(self.video_embedder.weight_like.device)
+        self.ops = ops
+        self.text_embedder.bind(ops)
+        for block in self.layers:
+            block.bind(ops)
+        return self
+
+    def set_runner(self, runner) -> None:
+        self.runner = runner
+
+    def set_residual_scale(self, scales) -> None:
+        self.residual_scale = tuple(scales)
+        self._default = self._plan_forward()
+
+    def conditioning_linears(self) -> tuple[MossLinear, ...]:
+        te = self.time_embedding
+        return (te[0], te[2], self.shared_block_modulation, self.video_head_modulation)
+
+    def block_linears(self):
+        """(path, MossLinear) of every joint-block projection, in execution order."""
+        for i, block in enumerate(self.layers):
+            for name, lin in block.proj.items():
+                yield f"layers.{i}.proj.{name}", lin
+
+    # -- pieces -------------------------------------------------------------------------
+    def conditioning(self, sigma: Tensor) -> tuple[Tensor, Tensor]:
+        """fp32 block modulation [B, 6, D] and head modulation [B, 2, D]."""
+        te = self.time_embedding
+        emb = eager.timestep_embedding(sigma.float() * self.cfg.time_scale, self.cfg.freq_dim)
+        hidden = te[1](te[0](emb.to(te[0].weight.dtype)))
+        time = te[2](hidden.to(te[2].weight.dtype)).float()
+        mod = self.shared_block_modulation(time.to(self.shared_block_modulation.weight.dtype)).float()
+        head = self.video_head_modulation(time.to(self.video_head_modulation.weight.dtype)).float()
+        return mod.unflatten(-1, (6, -1)), head.unflatten(-1, (2, -1))
+
+    def compute_dtype(self) -> torch.dtype:
+        return self.layers[0].proj["q"].weight_like.dtype
+
+    def embed(self, img: Tensor, text: Tensor, seq: SeqInfo) -> Tensor:
+        video = self.video_embedder(img.to(self.video_embedder.weight_like.dtype))
+        words = self.text_embedder(text, seq, self.rope.bands)
+        x = video.new_empty(seq.n_joint, video.shape[-1])
+        x = x.index_copy(0, seq.img_in_joint, video)
+        return x.index_copy(0, seq.txt_in_joint, words.to(x.dtype))
+
+    def head(self, x: Tensor, head: Tensor, seq: SeqInfo) -> Tensor:
+        xi = x.index_select(0, seq.img_in_joint)
+        norm = self.final_norm_video
+        y = self.ops.rms_norm_mod(xi, norm.weight, head[:, HEAD_SHIFT], head[:, HEAD_SCALE], seq.seg_img, norm.eps)
+        return self.final_linear_video(y)
+
+    # -- plans --------------------------------------------------------------------------
+    def _plan(self, skip: frozenset, segment_skip: frozenset = frozenset()):
+        steps = []
+        for i in range(len(self.layers)):
+            r = self.residual_scale[i]
+            if i in skip:
+                if r != 1.0:
+                    steps.append(("scale", i, r))
+            elif i in segment_skip:
+                steps.append(("select", i, r))
+            else:
+                steps.append(("run", i, r))
+        return tuple(steps)
+
+    def _plan_forward(self, skip_layers=(), segment_skip_layers=()) -> Callable:
+        skip = frozenset(skip_layers)
+        segment = frozenset(segment_skip_layers) - skip
+        plan = self._plan(skip, segment)
+        masked = bool(segment_skip_layers)
+
+        def run(model, img, text, sigma, seq, mask=None):
+            return model._run_plan(plan, img, text, sigma, seq, mask if masked else None)
+
+        return run
+
+    def bind_forward(self, skip_layers=(), segment_skip_layers=()) -> Callable[..., Tensor]:
+        """A forward with its block plan resolved once. `skip_layers` skips blocks for
+        every sample; `segment_skip_layers` skips them only for samples flagged by the
+        bool [B] `mask` passed as the fifth argument (packed CFG)."""
+        fn = self._plan_forward(skip_layers, segment_skip_layers)
+        return lambda *args: fn(self, *args)
+
+    def _run_plan(self, plan, img, text, sigma, seq, mask) -> Tensor:
+        if self.ops is None:
+            self.bind_ops()
+        mod, head = self.conditioning(sigma)
+        x = self.embed(img, text, seq)
+        ctx = BlockCtx(seq, mod, self.rope.bands, self.residual_scale)
+        keep = None
+        if mask is not None:
+            keep = (~mask).index_select(0, seq.seg_joint.long()).unsqueeze(-1)
+        for kind, i, r in plan:
+            if kind == "scale":
+                x = x * r
+            elif kind == "run":
+                x = self.runner.run(i, self.layers[i], x, ctx)
+            else:
+                out = self.runner.run(i, self.layers[i], x, ctx)
+                x = torch.where(keep, out, x if r == 1.0 else x * r)
+        return self.head(x, head, seq)
+
+    def forward(self, img: Tensor, text: Tensor, sigma: Tensor, seq: SeqInfo) -> Tensor:
+        """img [N_img, C], text [N_txt, text_dim], sigma fp32 [B] in [0, 1] -> v [N_img, C]."""
+        return self._default(self, img, text, sigma, seq)

@@ -1,0 +1,136 @@
+"""Joint image+text block and the text-refiner block.
+
+Data flow per joint block (reference: `src/kohakumoss/model/block.py:77-121`):
+`y = norm_mod(x)`, `q,k = qk_norm_rope(q(y), k(y))`, `v = v(y)`, `o = attn(q,k,v)`,
+`x = x*r + o_proj(o)*gate_a[seg]`, `y = norm_mod(x)`,
+`x = x + ffn_down(situ(ffn_up_gate(y)))*gate_f[seg]`.
+All 42 blocks share one `[B, 6, D]` modulation. The block only talks to an op set, so
+the same module runs the eager reference on CPU and the fused sm_100a kernels on CUDA.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+from torch import Tensor, nn
+
+from ..types.arch import MossArchConfig
+from ..types.seqinfo import SeqInfo
+from .components import RMSNorm
+from .linear import MossLinear
+
+SHIFT_ATTN, SCALE_ATTN, GATE_ATTN, SHIFT_FFN, SCALE_FFN, GATE_FFN = range(6)
+HEAD_SHIFT, HEAD_SCALE = range(2)
+PROJ = ("q", "k", "v", "o")
+
+
+@dataclass
+class BlockCtx:
+    """What every block reads besides its input."""
+
+    seq: SeqInfo
+    mod: Tensor
+    bands: Tensor
+    residual_scale: tuple[float, ...]
+    slots: tuple[Tensor, ...] = field(init=False, repr=False)
+
+    def __post_init__(self) -> None:
+        self.slots = self.mod.unbind(1)
+
+
+class JointBlock(nn.Module):
+    def __init__(self, cfg: MossArchConfig, index: int, device=None, dtype=None):
+        super().__init__()
+        dim, ffn = cfg.dim, cfg.ffn_dim
+        kw = dict(device=device, dtype=dtype)
+        self.index = index
+        self.heads = cfg.heads
+        self.norm1 = RMSNorm(dim, cfg.eps, **kw)
+        self.norm2 = RMSNorm(dim, cfg.eps, **kw)
+        self.q_norm = RMSNorm(cfg.head_dim, cfg.eps, **kw)
+        self.k_norm = RMSNorm(cfg.head_dim, cfg.eps, **kw)
+        proj = {name: MossLinear(dim, dim, bias=False, **kw) for name in PROJ}
+        proj["ffn_up_gate"] = MossLinear(dim, 2 * ffn, bias=False, **kw)
+        proj["ffn_down"] = MossLinear(ffn, dim, bias=False, **kw)
+        self.proj = nn.ModuleDict(proj)
+        self.ops = None
+
+    def bind(self, ops) -> None:
+        self.ops = ops
+
+    def sub_blocks(self):
+        return self.attn_part, self.ffn_part
+
+    def forward(self, x: Tensor, ctx: BlockCtx) -> Tensor:
+        return self.ffn_part(self.attn_part(x, ctx), ctx)
+
+    def attn_part(self, x: Tensor, ctx: BlockCtx) -> Tensor:
+        ops, seq, mod, p = self.ops, ctx.seq, ctx.slots, self.proj
+        seg = seq.seg_joint
+        y = ops.rms_norm_mod(x, self.norm1.weight, mod[SHIFT_ATTN], mod[SCALE_ATTN], seg, self.norm1.eps)
+        q, k, v = ops.qkv_rope(
+            y, p["q"], p["k"], p["v"], self.heads, self.q_norm.weight, self.k_norm.weight,
+            seq.pos_joint, ctx.bands, self.q_norm.eps,
+        )
+        o = ops.attention(q, k, v, seq.attn_joint).flatten(1)
+        r = ctx.residual_scale[self.index]
+        return ops.linear_gated_residual(o, p["o"], x, mod[GATE_ATTN], seg, r)
+
+    def ffn_part(self, x: Tensor, ctx: BlockCtx) -> Tensor:
+        ops, mod, seg, p = self.ops, ctx.slots, ctx.seq.seg_joint, self.proj
+        y = ops.rms_norm_mod(x, self.norm2.weight, mod[SHIFT_FFN], mod[SCALE_FFN], seg, self.norm2.eps)
+        a = ops.linear_situ(y, p["ffn_up_gate"])
+        return ops.linear_gated_residual(a, p["ffn_down"], x, mod[GATE_FFN], seg, 1.0)
+
+
+class TextBlock(nn.Module):
+    """Pre-norm self-attention (biased fused qkv, qk-norm, RoPE on text positions) and a
+    SiTU FFN with separate gate / up linears; no modulation, no gates
+    (`src/kohakumoss/model/text_block.py:17-61`)."""
+
+    def __init__(self, cfg: MossArchConfig, device=None, dtype=None):
+        super().__init__()
+        dim, ffn = cfg.dim, cfg.ffn_dim
+        kw = dict(device=device, dtype=dtype)
+        self.heads = cfg.heads
+        self.norm1 = RMSNorm(dim, cfg.eps, **kw)
+        self.norm2 = RMSNorm(dim, cfg.eps, **kw)
+        self.q_norm = RMSNorm(cfg.head_dim, cfg.eps, **kw)
+        self.k_norm = RMSNorm(cfg.head_dim, cfg.eps, **kw)
+        self.qkv = MossLinear(dim, 3 * dim, **kw)
+        self.proj = MossLinear(dim, dim, **kw)
+        self.ffn_gate = MossLinear(dim, ffn, **kw)
+        self.ffn_up = MossLinear(dim, ffn, **kw)
+        self.ffn_down = MossLinear(ffn, dim, **kw)
+        self.ops = None
+
+    def bind(self, ops) -> None:
+        self.ops = ops
+
+    def forward(self, x: Tensor, seq: SeqInfo, bands: Tensor) -> Tensor:
+        ops = self.ops
+        y = ops.rms_norm(x, self.norm1.weight, self.norm1.eps)
+        q, k, v = (t.unflatten(-1, (self.heads, -1)) for t in self.qkv(y).chunk(3, -1))
+        q, k = ops.qk_norm_rope(q, k, self.q_norm.weight, self.k_norm.weight, seq.pos_txt, bands, self.q_norm.eps)
+        o = ops.attention(q, k, v.contiguous(), seq.attn_text).flatten(1)
+        x = ops.linear_gated_residual(o, self.proj, x, None, None, 1.0)
+        y = ops.rms_norm(x, self.norm2.weight, self.norm2.eps)
+        a = ops.situ_pair(self.ffn_up(y), self.ffn_gate(y))
+        return ops.linear_gated_residual(a, self.ffn_down, x, None, None, 1.0)
+
+
+class TextEmbedder(nn.Module):
+    def __init__(self, cfg: MossArchConfig, device=None, dtype=None):
+        super().__init__()
+        self.proj = MossLinear(cfg.text_dim, cfg.dim, device=device, dtype=dtype)
+        self.blocks = nn.ModuleList(TextBlock(cfg, device=device, dtype=dtype) for _ in range(cfg.text_blocks))
+
+    def bind(self, ops) -> None:
+        for block in self.blocks:
+            block.bind(ops)
+
+    def forward(self, text: Tensor, seq: SeqInfo, bands: Tensor) -> Tensor:
+        x = self.proj(text.to(self.proj.weight_like.dtype))
+        for block in self.blocks:
+            x = block(x, seq, bands)
+        return x

@@ -1,0 +1,69 @@
+"""Shape of a MOSS-Image transformer.
+
+Field names, defaults and presets follow the reference config
+(`src/kohakumoss/types/arch.py:6-50`) so `ARCH_OVERRIDES` dictionaries carry over.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, replace
+
+
+@dataclass(frozen=True)
+class MossArchConfig:
+    dim: int = 3072
+    depth: int = 42
+    heads: int = 24
+    ffn_dim: int = 8192
+    text_dim: int = 4096
+    text_blocks: int = 2
+    latent_channels: int = 128
+    freq_dim: int = 256
+    rope_base: float = 10000.0
+    rope_axes: int = 4
+    eps: float = 1e-6
+    time_scale: float = 1000.0
+    negative_skip_layers: tuple[int, ...] = (22,)
+
+    @property
+    def head_dim(self) -> int:
+        return self.dim // self.heads
+
+    @property
+    def rope_bands(self) -> int:
+        return self.head_dim // (2 * self.rope_axes)
+
+    def validate(self) -> None:
+        problems = []
+        if self.dim % self.heads:
+            problems.append("dim must divide by heads")
+        elif self.head_dim % (2 * self.rope_axes):
+            problems.append("head_dim must divide by 2 * rope_axes")
+        if self.freq_dim % 2:
+            problems.append("freq_dim must be even")
+        if problems:
+            raise ValueError("; ".join(problems))
+
+    def override(self, **kwargs) -> "MossArchConfig":
+        return replace(self, **kwargs)
+
+    def block_params(self) -> int:
+        """Parameters of one joint block (weights + norm vectors)."""
+        d, f = self.dim, self.ffn_dim
+        return 4 * d * d + 3 * d * f + 2 * d + 2 * self.head_dim
+
+    def n_params(self) -> int:
+        d, f = self.dim, self.ffn_dim
+        text_block = 3 * d * d + 3 * d + d * d + d + 2 * (d * f + f) + f * d + d + 2 * d + 2 * self.head_dim
+        cond = self.freq_dim * d + d + d * d + d + d * 6 * d + 6 * d + d * 2 * d + 2 * d
+        embed = self.latent_channels * d + d + self.text_dim * d + d
+        head = d + d * self.latent_channels
+        return self.depth * self.block_params() + self.text_blocks * text_block + cond + embed + head
+
+
+PRESETS: dict[str, MossArchConfig] = {
+    "base": MossArchConfig(),
+    "sft": MossArchConfig(),
+    # Small shapes for tests and smoke runs (not in the reference presets).
+    "tiny": MossArchConfig(dim=256, depth=4, heads=4, ffn_dim=512, text_dim=256, text_blocks=1),
+}

@@ -1,0 +1,52 @@
+"""Test configuration: markers, reference-oracle import path, per-test seeds."""
+
+import os
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")
+    config.addinivalue_line("markers", "multi_gpu: needs at least two CUDA devices")
+    config.addinivalue_line("markers", "slow: takes more than a few seconds")
+
+
+def pytest_collection_modifyitems(config, items):
+    have = torch.cuda.is_available()
+    count = torch.cuda.device_count() if have else 0
+    for item in items:
+        if "gpu" in item.keywords and not have:
+            item.add_marker(pytest.mark.skip(reason="no CUDA device"))
+        if "multi_gpu" in item.keywords and count < 2:
+            item.add_marker(pytest.mark.skip(reason="needs >= 2 CUDA devices"))
+
+
+@pytest.fixture(autouse=True)
+def _seed():
+    torch.manual_seed(0)
+
+
+def reference_src() -> Path | None:
+    """Source tree of the upstream implementation when it is mounted (used as a CPU
+    oracle only; tests that need it skip when it is absent)."""
+    for cand in (os.environ.get("KMOSS_REFERENCE_SRC"), "/root/reference/src"):
+        if cand and Path(cand, "kohakumoss").is_dir():
+            return Path(cand)
+    return None
+
+
+@pytest.fixture(scope="session")
+def reference():
+    src = reference_src()
+    if src is None:
+        pytest.skip("upstream reference source not mounted")
+    if str(src) not in sys.path:
+        sys.path.append(str(src))
+    return src
