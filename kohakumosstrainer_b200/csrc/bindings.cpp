@@ -1,0 +1,375 @@
+// torch.ops.kmoss_b200.*: thin argument marshalling from ATen tensors to the raw-pointer
+// kernel launchers. No kernel here; every op enqueues on the current CUDA stream.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include <optional>
+
+#include "blockops.cuh"
+#include "gemm_sm100.cuh"
+
+namespace {
+
+using at::Tensor;
+using std::optional;
+
+#define KM_CHECK_CUDA(expr)                                                              \
+  do {                                                                                   \
+    cudaError_t _e = (expr);                                                             \
+    TORCH_CHECK(_e == cudaSuccess, #expr " failed: ", cudaGetErrorString(_e));            \
+  } while (0)
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+template <class T>
+const T* cptr(const optional<Tensor>& t) {
+  return t.has_value() && t->defined() ? reinterpret_cast<const T*>(t->data_ptr()) : nullptr;
+}
+template <class T>
+T* mptr(const optional<Tensor>& t) {
+  return t.has_value() && t->defined() ? reinterpret_cast<T*>(t->data_ptr()) : nullptr;
+}
+
+int gemm_dtype_of(const Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kBFloat16: return kmoss::GEMM_BF16;
+    case at::kFloat8_e4m3fn: return kmoss::GEMM_E4M3;
+    case at::kFloat8_e5m2: return kmoss::GEMM_E5M2;
+    default: TORCH_CHECK(false, "gemm operand must be bf16, float8_e4m3fn or float8_e5m2, got ", t.scalar_type());
+  }
+}
+
+Tensor& status_tensor() {
+  static Tensor status;
+  if (!status.defined())
+    status = at::zeros({4}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, at::cuda::current_device()));
+  return status;
+}
+
+Tensor kernel_status() { return status_tensor(); }
+
+// D = epilogue(A . B^T). `a` is [M, K] (K-major) or [K, M] (MN-major); `b` is [N, K] or [K, N].
+void gemm(const Tensor& a, const Tensor& b, int64_t M, int64_t N, int64_t K, bool a_mn, bool b_mn, Tensor out,
+          double alpha, const optional<Tensor>& scale_a, const optional<Tensor>& scale_b,
+          const optional<Tensor>& row_scale, const optional<Tensor>& col_scale, const optional<Tensor>& bias,
+          const optional<Tensor>& res, double beta, const optional<Tensor>& gate, const optional<Tensor>& seg,
+          const optional<Tensor>& t, const optional<Tensor>& u, int64_t epilogue, const optional<Tensor>& aux,
+          const optional<Tensor>& q_norm_w, const optional<Tensor>& k_norm_w, const optional<Tensor>& rope,
+          int64_t rope_cols, double eps, const optional<Tensor>& head_rstd, int64_t splits,
+          const optional<Tensor>& workspace) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "gemm: CUDA tensors required");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "gemm: operands must be 2-D with unit inner stride");
+  TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1, "gemm: out must be 2-D with unit inner stride");
+  c10::cuda::CUDAGuard guard(a.device());
+  kmoss::GemmProblem g{};
+  g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.A = a.data_ptr(); g.B = b.data_ptr();
+  g.lda = a.stride(0); g.ldb = b.stride(0);
+  g.a_dtype = gemm_dtype_of(a); g.b_dtype = gemm_dtype_of(b);
+  g.a_mn = a_mn; g.b_mn = b_mn;
+  if (a_mn) { TORCH_CHECK(a.size(0) >= K && a.size(1) >= M, "gemm: MN-major A must be [K, M]"); }
+  else { TORCH_CHECK(a.size(0) >= M && a.size(1) >= K, "gemm: K-major A must be [M, K]"); }
+  const int64_t b_rows = epilogue == kmoss::EPI_SITU ? 2 * N : N;
+  if (b_mn) { TORCH_CHECK(b.size(0) >= K && b.size(1) >= N, "gemm: MN-major B must be [K, N]"); }
+  else { TORCH_CHECK(b.size(0) >= b_rows && b.size(1) >= K, "gemm: K-major B must be [N, K]"); }
+  if (t.has_value() && t->defined()) {
+    TORCH_CHECK(u.has_value() && u->defined(), "gemm: bypass needs both T and U");
+    TORCH_CHECK(t->scalar_type() == at::kBFloat16 && u->scalar_type() == at::kBFloat16, "gemm: bypass operands must be bf16");
+    TORCH_CHECK(t->size(0) >= M && u->size(0) >= b_rows && t->size(1) == u->size(1), "gemm: bypass shapes");
+    g.T = t->data_ptr(); g.U = u->data_ptr(); g.ldt = t->stride(0); g.ldu = u->stride(0); g.R = (int)t->size(1);
+  }
+  g.epilogue = (int)epilogue;
+  g.out = out.data_ptr(); g.ldo = out.stride(0);
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kFloat, "gemm: out must be bf16 or fp32");
+  g.out_dtype = out.scalar_type() == at::kBFloat16 ? kmoss::OUT_BF16 : kmoss::OUT_F32;
+  TORCH_CHECK(out.size(0) >= M && out.size(1) >= N, "gemm: out too small");
+  g.alpha = (float)alpha;
+  g.scale_a = cptr<float>(scale_a); g.scale_b = cptr<float>(scale_b);
+  g.row_scale = cptr<float>(row_scale); g.col_scale = cptr<float>(col_scale);
+  if (bias.has_value() && bias->defined()) {
+    g.bias = bias->data_ptr();
+    g.bias_dtype = bias->scalar_type() == at::kFloat ? 1 : 0;
+    TORCH_CHECK(bias->scalar_type() == at::kFloat || bias->scalar_type() == at::kBFloat16, "gemm: bias dtype");
+  }
+  if (res.has_value() && res->defined()) {
+    TORCH_CHECK(res->scalar_type() == at::kBFloat16 && res->stride(1) == 1, "gemm: residual must be bf16 rows");
+    g.res = res->data_ptr(); g.ldr = res->stride(0);
+  }
+  g.beta = (float)beta;
+  if (gate.has_value() && gate->defined()) {
+    TORCH_CHECK(seg.has_value() && seg->defined() && seg->scalar_type() == at::kInt, "gemm: gate needs int32 seg");
+    TORCH_CHECK(gate->scalar_type() == at::kFloat && gate->dim() == 2 && gate->stride(1) == 1, "gemm: gate must be fp32 [B, N] view");
+    g.gate = gate->data_ptr<float>(); g.gate_stride = gate->stride(0); g.seg = seg->data_ptr<int>();
+  }
+  if (aux.has_value() && aux->defined()) { g.aux = aux->data_ptr(); g.ldaux = aux->stride(0); }
+  g.q_norm_w = cptr<void>(q_norm_w); g.k_norm_w = cptr<void>(k_norm_w);
+  g.pos = cptr<float>(rope);
+  g.rope_cols = (int)rope_cols; g.eps = (float)eps;
+  g.head_rstd = mptr<float>(head_rstd);
+  g.splits = (int)splits;
+  if (splits > 1) {
+    TORCH_CHECK(workspace.has_value() && workspace->defined(), "gemm: split-K needs a workspace");
+    TORCH_CHECK((size_t)workspace->numel() * workspace->element_size() >= kmoss::gemm_workspace_bytes((int)M, (int)N, (int)splits),
+                "gemm: workspace too small");
+    g.workspace = reinterpret_cast<float*>(workspace->data_ptr());
+  }
+  g.status = status_tensor().data_ptr<int>();
+  KM_CHECK_CUDA(kmoss::gemm_launch(g, cur_stream()));
+}
+
+int64_t gemm_pick_splits(int64_t M, int64_t N, int64_t K, int64_t elem_bytes) {
+  return kmoss::gemm_pick_splits((int)M, (int)N, (int)K, (int)elem_bytes);
+}
+
+void rms_norm_mod_fwd(const Tensor& x, const optional<Tensor>& w, const optional<Tensor>& shift,
+                      const optional<Tensor>& scale, const optional<Tensor>& seg, double eps, Tensor y,
+                      const optional<Tensor>& rstd, const optional<Tensor>& yq, const optional<Tensor>& q_scale,
+                      const optional<Tensor>& amax) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "rms_norm_mod: x must be bf16 [N, D]");
+  kmoss::NormModArgs a{};
+  a.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()); a.ldx = x.stride(0);
+  if (w.has_value() && w->defined()) { a.w = w->data_ptr(); a.w_f32 = w->scalar_type() == at::kFloat; }
+  if (shift.has_value() && shift->defined()) { a.shift = shift->data_ptr<float>(); a.mod_stride = shift->stride(0); }
+  if (scale.has_value() && scale->defined()) { a.scale = scale->data_ptr<float>(); a.mod_stride = scale->stride(0); }
+  if (a.shift && a.scale) { TORCH_CHECK(shift->stride(0) == scale->stride(0), "rms_norm_mod: shift / scale strides differ"); }
+  a.seg = cptr<int>(seg);
+  TORCH_CHECK(!(a.shift || a.scale) || a.seg, "rms_norm_mod: modulation needs seg");
+  a.eps = (float)eps;
+  a.y = reinterpret_cast<__nv_bfloat16*>(y.data_ptr()); a.ldy = y.stride(0);
+  a.rstd = mptr<float>(rstd);
+  if (yq.has_value() && yq->defined()) { a.yq = reinterpret_cast<uint8_t*>(yq->data_ptr()); a.ldq = yq->stride(0); }
+  a.q_scale = cptr<float>(q_scale);
+  a.amax = mptr<float>(amax);
+  a.rows = (int)x.size(0); a.dim = (int)x.size(1);
+  KM_CHECK_CUDA(kmoss::rms_norm_mod_fwd(a, cur_stream()));
+}
+
+kmoss::NormModBwdArgs norm_bwd_args(const Tensor& dy, const Tensor& x, const optional<Tensor>& w,
+                                    const optional<Tensor>& scale, const optional<Tensor>& seg, const Tensor& rstd) {
+  kmoss::NormModBwdArgs a{};
+  a.dy = reinterpret_cast<const __nv_bfloat16*>(dy.data_ptr()); a.lddy = dy.stride(0);
+  a.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()); a.ldx = x.stride(0);
+  if (w.has_value() && w->defined()) { a.w = w->data_ptr(); a.w_f32 = w->scalar_type() == at::kFloat; }
+  if (scale.has_value() && scale->defined()) { a.scale = scale->data_ptr<float>(); a.mod_stride = scale->stride(0); }
+  a.seg = cptr<int>(seg);
+  a.rstd = rstd.data_ptr<float>();
+  a.rows = (int)x.size(0); a.dim = (int)x.size(1);
+  return a;
+}
+
+void rms_norm_mod_bwd(const Tensor& dy, const Tensor& x, const optional<Tensor>& w, const optional<Tensor>& scale,
+                      const optional<Tensor>& seg, const Tensor& rstd, Tensor dx, const optional<Tensor>& dres,
+                      double dres_scale) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(dy.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16, "rms_norm_mod_bwd: bf16 only");
+  auto a = norm_bwd_args(dy, x, w, scale, seg, rstd);
+  a.dx = reinterpret_cast<__nv_bfloat16*>(dx.data_ptr()); a.lddx = dx.stride(0);
+  if (dres.has_value() && dres->defined()) {
+    a.dres = reinterpret_cast<const __nv_bfloat16*>(dres->data_ptr()); a.lddres = dres->stride(0);
+    a.dres_scale = (float)dres_scale;
+  }
+  KM_CHECK_CUDA(kmoss::rms_norm_mod_bwd(a, cur_stream()));
+}
+
+Tensor norm_weight_grad(const Tensor& dy, const Tensor& x, const optional<Tensor>& scale, const optional<Tensor>& seg,
+                        const Tensor& rstd) {
+  c10::cuda::CUDAGuard guard(x.device());
+  auto a = norm_bwd_args(dy, x, std::nullopt, scale, seg, rstd);
+  const int chunks = std::max(1, std::min(64, a.rows / 256));
+  Tensor partial = at::empty({chunks, a.dim}, x.options().dtype(at::kFloat));
+  KM_CHECK_CUDA(kmoss::norm_weight_grad(a, partial.data_ptr<float>(), chunks, cur_stream()));
+  return partial.sum(0);
+}
+
+// mode 0: sum a; 1: sum a * b * rstd * w; 2: sum a * b  -- per segment, rows sorted by segment
+Tensor seg_sum(const Tensor& a_, const optional<Tensor>& b_, const optional<Tensor>& w, const optional<Tensor>& rstd,
+               const Tensor& cu, int64_t mode) {
+  c10::cuda::CUDAGuard guard(a_.device());
+  kmoss::SegSumArgs a{};
+  a.a = reinterpret_cast<const __nv_bfloat16*>(a_.data_ptr()); a.lda = a_.stride(0);
+  if (b_.has_value() && b_->defined()) { a.b = reinterpret_cast<const __nv_bfloat16*>(b_->data_ptr()); a.ldb = b_->stride(0); }
+  if (w.has_value() && w->defined()) { a.w = w->data_ptr(); a.w_f32 = w->scalar_type() == at::kFloat; }
+  a.rstd = cptr<float>(rstd);
+  a.cu = cu.data_ptr<int>();
+  a.batch = (int)cu.numel() - 1; a.dim = (int)a_.size(1); a.mode = (int)mode;
+  Tensor out = at::empty({a.batch, a.dim}, a_.options().dtype(at::kFloat));
+  a.out = out.data_ptr<float>(); a.ldo = a.dim;
+  KM_CHECK_CUDA(kmoss::seg_sum(a, cur_stream()));
+  return out;
+}
+
+Tensor rope_table(const Tensor& pos, const Tensor& bands) {
+  c10::cuda::CUDAGuard guard(pos.device());
+  TORCH_CHECK(pos.scalar_type() == at::kFloat && bands.scalar_type() == at::kFloat && pos.is_contiguous() && bands.is_contiguous());
+  const int rows = (int)pos.size(0), axes = (int)pos.size(1), nb = (int)bands.numel();
+  Tensor table = at::empty({rows, 2 * axes * nb}, pos.options());
+  KM_CHECK_CUDA(kmoss::rope_table(pos.data_ptr<float>(), bands.data_ptr<float>(), table.data_ptr<float>(), rows, axes, nb, cur_stream()));
+  return table;
+}
+
+void qk_norm_rope_fwd(const Tensor& x, const Tensor& w, const Tensor& rope, double eps, Tensor y,
+                      const optional<Tensor>& rstd, int64_t heads) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.stride(-1) == 1 && x.dim() == 2, "qk_norm_rope: x must be bf16 [N, H*128] rows");
+  kmoss::QkRopeArgs a{};
+  a.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()); a.ldx = x.stride(0);
+  a.w = w.data_ptr(); a.w_f32 = w.scalar_type() == at::kFloat;
+  a.rope = rope.data_ptr<float>(); a.eps = (float)eps;
+  a.y = reinterpret_cast<__nv_bfloat16*>(y.data_ptr()); a.ldy = y.stride(0);
+  a.rstd = mptr<float>(rstd);
+  a.rows = (int)x.size(0); a.heads = (int)heads;
+  KM_CHECK_CUDA(kmoss::qk_norm_rope_fwd(a, cur_stream()));
+}
+
+void qk_norm_rope_bwd(const Tensor& y, const Tensor& dy, const Tensor& w, const Tensor& rope, const Tensor& rstd,
+                      Tensor dx, const optional<Tensor>& dw_rows, int64_t heads) {
+  c10::cuda::CUDAGuard guard(y.device());
+  kmoss::QkRopeBwdArgs a{};
+  a.y = reinterpret_cast<const __nv_bfloat16*>(y.data_ptr()); a.ldy = y.stride(0);
+  a.dy = reinterpret_cast<const __nv_bfloat16*>(dy.data_ptr()); a.lddy = dy.stride(0);
+  a.w = w.data_ptr(); a.w_f32 = w.scalar_type() == at::kFloat;
+  a.rope = rope.data_ptr<float>(); a.rstd = rstd.data_ptr<float>();
+  a.dx = reinterpret_cast<__nv_bfloat16*>(dx.data_ptr()); a.lddx = dx.stride(0);
+  a.dw_rows = mptr<float>(dw_rows);
+  a.rows = (int)y.size(0); a.heads = (int)heads;
+  KM_CHECK_CUDA(kmoss::qk_norm_rope_bwd(a, cur_stream()));
+}
+
+void situ_fwd(const Tensor& up, const Tensor& gate, Tensor out) {
+  c10::cuda::CUDAGuard guard(up.device());
+  TORCH_CHECK(up.stride(0) == gate.stride(0) && up.stride(1) == 1 && gate.stride(1) == 1, "situ: strides");
+  KM_CHECK_CUDA(kmoss::situ_fwd(up.data_ptr(), gate.data_ptr(), up.stride(0), out.data_ptr(), out.stride(0),
+                                (int)up.size(0), (int)up.size(1), cur_stream()));
+}
+
+void situ_bwd(const Tensor& da, const Tensor& up, const Tensor& gate, Tensor dup, Tensor dgate) {
+  c10::cuda::CUDAGuard guard(up.device());
+  TORCH_CHECK(up.stride(0) == gate.stride(0) && dup.stride(0) == dgate.stride(0), "situ_bwd: strides");
+  KM_CHECK_CUDA(kmoss::situ_bwd(da.data_ptr(), da.stride(0), up.data_ptr(), gate.data_ptr(), up.stride(0), dup.data_ptr(),
+                                dgate.data_ptr(), dup.stride(0), (int)up.size(0), (int)up.size(1), cur_stream()));
+}
+
+void gated_residual(const Tensor& x, const Tensor& o, const optional<Tensor>& gate, const optional<Tensor>& seg,
+                    double r, Tensor out) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && o.is_contiguous() && out.is_contiguous(), "gated_residual: contiguous tensors");
+  const float* g = nullptr; long gs = 0;
+  if (gate.has_value() && gate->defined()) { g = gate->data_ptr<float>(); gs = gate->stride(0); }
+  KM_CHECK_CUDA(kmoss::gated_residual(x.data_ptr(), o.data_ptr(), g, gs, cptr<int>(seg), (float)r, out.data_ptr(),
+                                      (int)x.size(0), (int)x.size(1), cur_stream()));
+}
+
+void seg_scale(const Tensor& x, const Tensor& vec, const Tensor& seg, Tensor out) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && out.is_contiguous() && vec.stride(1) == 1, "seg_scale: layout");
+  KM_CHECK_CUDA(kmoss::seg_scale(x.data_ptr(), vec.data_ptr<float>(), vec.stride(0), seg.data_ptr<int>(), out.data_ptr(),
+                                 (int)x.size(0), (int)x.size(1), cur_stream()));
+}
+
+kmoss::TokenMseArgs mse_args(const Tensor& pred, const Tensor& target, const Tensor& seg, const optional<Tensor>& weight,
+                             const optional<Tensor>& mask) {
+  TORCH_CHECK(pred.is_contiguous() && target.is_contiguous() && target.scalar_type() == at::kFloat, "token_mse: layout");
+  kmoss::TokenMseArgs a{};
+  a.pred = pred.data_ptr(); a.pred_f32 = pred.scalar_type() == at::kFloat;
+  a.target = target.data_ptr<float>();
+  a.seg = seg.data_ptr<int>();
+  a.weight = cptr<float>(weight); a.mask = cptr<float>(mask);
+  a.rows = (int)pred.size(0); a.dim = (int)pred.size(1);
+  return a;
+}
+
+Tensor token_mse_fwd(const Tensor& pred, const Tensor& target, const Tensor& seg, const optional<Tensor>& weight,
+                     const optional<Tensor>& mask) {
+  c10::cuda::CUDAGuard guard(pred.device());
+  auto a = mse_args(pred, target, seg, weight, mask);
+  Tensor partial = at::empty({kmoss::token_mse_blocks(a.rows)}, target.options());
+  Tensor loss = at::empty({}, target.options());
+  KM_CHECK_CUDA(kmoss::token_mse_fwd(a, partial.data_ptr<float>(), loss.data_ptr<float>(), cur_stream()));
+  return loss;
+}
+
+Tensor token_mse_bwd(const Tensor& dloss, const Tensor& pred, const Tensor& target, const Tensor& seg,
+                     const optional<Tensor>& weight, const optional<Tensor>& mask) {
+  c10::cuda::CUDAGuard guard(pred.device());
+  auto a = mse_args(pred, target, seg, weight, mask);
+  Tensor dpred = at::empty_like(pred);
+  Tensor dl = dloss.to(at::kFloat).contiguous();
+  KM_CHECK_CUDA(kmoss::token_mse_bwd(a, dl.data_ptr<float>(), dpred.data_ptr(), cur_stream()));
+  return dpred;
+}
+
+// Per-tensor fp8 quantisation of a bf16 tensor: returns (q, scale[2] = {dequant, quant}).
+std::tuple<Tensor, Tensor> quantize_fp8_tensor(const Tensor& x, bool e5m2) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous(), "quantize_fp8_tensor: contiguous bf16");
+  Tensor amax = at::zeros({1}, x.options().dtype(at::kFloat));
+  Tensor scale = at::empty({2}, x.options().dtype(at::kFloat));
+  Tensor q = at::empty(x.sizes(), x.options().dtype(e5m2 ? at::kFloat8_e5m2 : at::kFloat8_e4m3fn));
+  auto s = cur_stream();
+  KM_CHECK_CUDA(kmoss::fp8_amax(x.data_ptr(), x.numel(), amax.data_ptr<float>(), s));
+  KM_CHECK_CUDA(kmoss::fp8_scale_from_amax(amax.data_ptr<float>(), e5m2 ? 57344.f : 448.f, scale.data_ptr<float>(), s));
+  KM_CHECK_CUDA(kmoss::fp8_cast(x.data_ptr(), x.numel(), scale.data_ptr<float>() + 1, q.data_ptr(), e5m2, s));
+  return {q, scale};
+}
+
+// Cast with a known quant scale (delayed scaling / pre-computed amax).
+void cast_fp8(const Tensor& x, const Tensor& qscale, Tensor q) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.is_contiguous() && q.is_contiguous(), "cast_fp8: layout");
+  KM_CHECK_CUDA(kmoss::fp8_cast(x.data_ptr(), x.numel(), qscale.data_ptr<float>(), q.data_ptr(),
+                                q.scalar_type() == at::kFloat8_e5m2, cur_stream()));
+}
+
+std::tuple<Tensor, Tensor> quantize_fp8_rows(const Tensor& x) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "quantize_fp8_rows: bf16 rows");
+  Tensor q = at::empty({x.size(0), x.size(1)}, x.options().dtype(at::kFloat8_e4m3fn));
+  Tensor rs = at::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  KM_CHECK_CUDA(kmoss::fp8_cast_rows(x.data_ptr(), x.stride(0), (int)x.size(0), (int)x.size(1), q.data_ptr(), q.stride(0),
+                                     rs.data_ptr<float>(), cur_stream()));
+  return {q, rs};
+}
+
+}  // namespace
+
+TORCH_LIBRARY(kmoss_b200, m) {
+  m.def("kernel_status() -> Tensor", &kernel_status);
+  m.def("gemm_pick_splits(int M, int N, int K, int elem_bytes) -> int", &gemm_pick_splits);
+  m.def(
+      "gemm(Tensor a, Tensor b, int M, int N, int K, bool a_mn, bool b_mn, Tensor(a!) out, float alpha, "
+      "Tensor? scale_a, Tensor? scale_b, Tensor? row_scale, Tensor? col_scale, Tensor? bias, Tensor? res, float beta, "
+      "Tensor? gate, Tensor? seg, Tensor? t, Tensor? u, int epilogue, Tensor(b!)? aux, Tensor? q_norm_w, "
+      "Tensor? k_norm_w, Tensor? rope, int rope_cols, float eps, Tensor(c!)? head_rstd, int splits, "
+      "Tensor(d!)? workspace) -> ()",
+      &gemm);
+  m.def(
+      "rms_norm_mod_fwd(Tensor x, Tensor? w, Tensor? shift, Tensor? scale, Tensor? seg, float eps, Tensor(a!) y, "
+      "Tensor(b!)? rstd, Tensor(c!)? yq, Tensor? q_scale, Tensor(d!)? amax) -> ()",
+      &rms_norm_mod_fwd);
+  m.def(
+      "rms_norm_mod_bwd(Tensor dy, Tensor x, Tensor? w, Tensor? scale, Tensor? seg, Tensor rstd, Tensor(a!) dx, "
+      "Tensor? dres, float dres_scale) -> ()",
+      &rms_norm_mod_bwd);
+  m.def("norm_weight_grad(Tensor dy, Tensor x, Tensor? scale, Tensor? seg, Tensor rstd) -> Tensor", &norm_weight_grad);
+  m.def("seg_sum(Tensor a, Tensor? b, Tensor? w, Tensor? rstd, Tensor cu, int mode) -> Tensor", &seg_sum);
+  m.def("rope_table(Tensor pos, Tensor bands) -> Tensor", &rope_table);
+  m.def("qk_norm_rope_fwd(Tensor x, Tensor w, Tensor rope, float eps, Tensor(a!) y, Tensor(b!)? rstd, int heads) -> ()",
+        &qk_norm_rope_fwd);
+  m.def(
+      "qk_norm_rope_bwd(Tensor y, Tensor dy, Tensor w, Tensor rope, Tensor rstd, Tensor(a!) dx, Tensor(b!)? dw_rows, "
+      "int heads) -> ()",
+      &qk_norm_rope_bwd);
+  m.def("situ_fwd(Tensor up, Tensor gate, Tensor(a!) out) -> ()", &situ_fwd);
+  m.def("situ_bwd(Tensor da, Tensor up, Tensor gate, Tensor(a!) dup, Tensor(b!) dgate) -> ()", &situ_bwd);
+  m.def("gated_residual(Tensor x, Tensor o, Tensor? gate, Tensor? seg, float r, Tensor(a!) out) -> ()", &gated_residual);
+  m.def("seg_scale(Tensor x, Tensor vec, Tensor seg, Tensor(a!) out) -> ()", &seg_scale);
+  m.def("token_mse_fwd(Tensor pred, Tensor target, Tensor seg, Tensor? weight, Tensor? mask) -> Tensor", &token_mse_fwd);
+  m.def("token_mse_bwd(Tensor dloss, Tensor pred, Tensor target, Tensor seg, Tensor? weight, Tensor? mask) -> Tensor",
+        &token_mse_bwd);
+  m.def("quantize_fp8_tensor(Tensor x, bool e5m2) -> (Tensor, Tensor)", &quantize_fp8_tensor);
+  m.def("cast_fp8(Tensor x, Tensor qscale, Tensor(a!) q) -> ()", &cast_fp8);
+  m.def("quantize_fp8_rows(Tensor x) -> (Tensor, Tensor)", &quantize_fp8_rows);
+}

@@ -1,0 +1,655 @@
+// Memory-bound block ops for sm_100a: adaLN-modulated RMSNorm, per-head qk RMSNorm + RoPE,
+// SiTU-GLU, gated residual, token MSE, RoPE table, fp8 quantisers.
+//
+// Every kernel moves 16-byte vectors, keeps its math in fp32 and rounds once at the store
+// (the precision contract of the reference kernels: `src/kohakumoss_kernels/backends/triton/
+// blocks/{norm,rope,ffn,residual,loss}.py`, eager forms in `backends/eager/*.py`). Forward
+// forms of rope / situ / gated residual normally run inside the GEMM epilogues
+// (gemm_sm100.cu); the standalone kernels here serve backward, the text refiner and the
+// unfused comparison path. Reductions over tokens are deterministic (fixed partials).
+
+#include "blockops.cuh"
+
+#include "common.cuh"
+
+namespace kmoss {
+
+namespace {
+
+constexpr int ROWS_PER_BLOCK = 4;  // one warp per row
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  uint4 w = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16(w.x), b = unpack_bf16(w.y), c = unpack_bf16(w.z), d = unpack_bf16(w.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 w;
+  w.x = pack_bf16(v[0], v[1]); w.y = pack_bf16(v[2], v[3]);
+  w.z = pack_bf16(v[4], v[5]); w.w = pack_bf16(v[6], v[7]);
+  *reinterpret_cast<uint4*>(p) = w;
+}
+__device__ __forceinline__ void load8f(const float* p, float (&v)[8]) {
+  float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+// weight vectors may be bf16 or fp32 (fp32 masters)
+__device__ __forceinline__ void load8w(const void* p, int is_f32, int idx, float (&v)[8]) {
+  if (is_f32) load8f(reinterpret_cast<const float*>(p) + idx, v);
+  else load8(reinterpret_cast<const __nv_bfloat16*>(p) + idx, v);
+}
+
+__device__ __forceinline__ void atomic_max_nonneg(float* addr, float v) {
+  atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));  // valid for v >= 0
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm (+ per-sample modulation): y = x * rstd * w * (1 + scale[seg]) + shift[seg]
+// Optionally also emits the e4m3 copy of y (per-tensor scale given) and accumulates amax(y).
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(32 * ROWS_PER_BLOCK)
+rms_norm_mod_fwd_kernel(NormModArgs a) {
+  const int row = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= a.rows) return;
+  const __nv_bfloat16* x = a.x + (size_t)row * a.ldx;
+  float ss = 0.f;
+  for (int i = lane * 8; i < a.dim; i += 256) {
+    float v[8];
+    load8(x + i, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / (float)a.dim + a.eps);
+  if (lane == 0 && a.rstd != nullptr) a.rstd[row] = rstd;
+  const int s = a.seg != nullptr ? a.seg[row] : 0;
+  const float* shift = a.shift != nullptr ? a.shift + (size_t)s * a.mod_stride : nullptr;
+  const float* scale = a.scale != nullptr ? a.scale + (size_t)s * a.mod_stride : nullptr;
+  __nv_bfloat16* y = a.y + (size_t)row * a.ldy;
+  float amax = 0.f;
+  const float qs = a.q_scale != nullptr ? *a.q_scale : 1.f;
+  for (int i = lane * 8; i < a.dim; i += 256) {
+    float v[8], w[8];
+    load8(x + i, v);
+    if (a.w != nullptr) load8w(a.w, a.w_f32, i, w);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float t = v[j] * rstd;
+      if (a.w != nullptr) t *= w[j];
+      if (scale != nullptr) t *= 1.f + scale[i + j];
+      if (shift != nullptr) t += shift[i + j];
+      v[j] = t;
+    }
+    store8(y + i, v);
+    if (a.amax != nullptr || a.yq != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // statistics and the fp8 copy are taken from the rounded bf16 value
+        v[j] = __bfloat162float(__float2bfloat16(v[j]));
+        amax = fmaxf(amax, fabsf(v[j]));
+      }
+      if (a.yq != nullptr) {
+        uint2 q;
+        __nv_fp8x4_e4m3 lo(make_float4(v[0] * qs, v[1] * qs, v[2] * qs, v[3] * qs));
+        __nv_fp8x4_e4m3 hi(make_float4(v[4] * qs, v[5] * qs, v[6] * qs, v[7] * qs));
+        q.x = *reinterpret_cast<uint32_t*>(&lo);
+        q.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(a.yq + (size_t)row * a.ldq + i) = q;
+      }
+    }
+  }
+  if (a.amax != nullptr) {
+    amax = warp_max(amax);
+    if (lane == 0) atomic_max_nonneg(a.amax, amax);
+  }
+}
+
+// dx = rstd * (g - xhat * mean(g * xhat)), g = dy * w * (1 + scale[seg]); optional "+= dres".
+__global__ void __launch_bounds__(32 * ROWS_PER_BLOCK)
+rms_norm_mod_bwd_kernel(NormModBwdArgs a) {
+  const int row = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= a.rows) return;
+  const __nv_bfloat16* x = a.x + (size_t)row * a.ldx;
+  const __nv_bfloat16* dy = a.dy + (size_t)row * a.lddy;
+  const float rstd = a.rstd[row];
+  const int s = a.seg != nullptr ? a.seg[row] : 0;
+  const float* scale = a.scale != nullptr ? a.scale + (size_t)s * a.mod_stride : nullptr;
+  float dot = 0.f;
+  for (int i = lane * 8; i < a.dim; i += 256) {
+    float v[8], g[8], w[8];
+    load8(x + i, v);
+    load8(dy + i, g);
+    if (a.w != nullptr) load8w(a.w, a.w_f32, i, w);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float t = g[j];
+      if (a.w != nullptr) t *= w[j];
+      if (scale != nullptr) t *= 1.f + scale[i + j];
+      dot += t * v[j] * rstd;
+    }
+  }
+  dot = warp_sum(dot) / (float)a.dim;
+  __nv_bfloat16* dx = a.dx + (size_t)row * a.lddx;
+  const __nv_bfloat16* dres = a.dres != nullptr ? a.dres + (size_t)row * a.lddres : nullptr;
+  for (int i = lane * 8; i < a.dim; i += 256) {
+    float v[8], g[8], w[8], r[8];
+    load8(x + i, v);
+    load8(dy + i, g);
+    if (a.w != nullptr) load8w(a.w, a.w_f32, i, w);
+    if (dres != nullptr) load8(dres + i, r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float t = g[j];
+      if (a.w != nullptr) t *= w[j];
+      if (scale != nullptr) t *= 1.f + scale[i + j];
+      float o = rstd * (t - v[j] * rstd * dot);
+      if (dres != nullptr) o += a.dres_scale * r[j];
+      v[j] = o;
+    }
+    store8(dx + i, v);
+  }
+}
+
+// Parameter / modulation gradients of the modulated norm, one block per (column tile,
+// row chunk): partial[chunk, 3, dim] = sum over the chunk's rows of
+//   [0] dy * (1 + scale) * xhat          (-> d weight, summed over chunks)
+//   per-segment sums go through `seg_sum_kernel` on dy * xhat * w and dy.
+__global__ void norm_weight_grad_kernel(NormModBwdArgs a, float* partial, int rows_per_chunk) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  const int chunk = blockIdx.y;
+  if (col >= a.dim) return;
+  const int r0 = chunk * rows_per_chunk;
+  const int r1 = min(a.rows, r0 + rows_per_chunk);
+  float acc = 0.f;
+  for (int r = r0; r < r1; ++r) {
+    const int s = a.seg != nullptr ? a.seg[r] : 0;
+    float g = __bfloat162float(a.dy[(size_t)r * a.lddy + col]);
+    if (a.scale != nullptr) g *= 1.f + a.scale[(size_t)s * a.mod_stride + col];
+    acc += g * __bfloat162float(a.x[(size_t)r * a.ldx + col]) * a.rstd[r];
+  }
+  partial[(size_t)chunk * a.dim + col] = acc;
+}
+
+// out[b, col] = sum over rows r of segment b (rows are segment-sorted: cu[b] .. cu[b+1])
+// of f(r, col); mode 0: dy ; mode 1: dy * xhat * w   (d shift / d scale of the norm);
+// mode 2: a[r, col] * b[r, col] (d gate of the gated residual).
+__global__ void seg_sum_kernel(SegSumArgs a) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  if (col >= a.dim) return;
+  const int r0 = a.cu[b], r1 = a.cu[b + 1];
+  float acc = 0.f;
+  for (int r = r0; r < r1; ++r) {
+    float v = __bfloat162float(a.a[(size_t)r * a.lda + col]);
+    if (a.mode == 1) {
+      float w = a.w != nullptr ? (a.w_f32 ? reinterpret_cast<const float*>(a.w)[col]
+                                          : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.w)[col]))
+                               : 1.f;
+      v *= __bfloat162float(a.b[(size_t)r * a.ldb + col]) * a.rstd[r] * w;
+    } else if (a.mode == 2) {
+      v *= __bfloat162float(a.b[(size_t)r * a.ldb + col]);
+    }
+    acc += v;
+  }
+  a.out[(size_t)b * a.ldo + col] = acc;
+}
+
+// ---------------------------------------------------------------------------------------
+// RoPE table: [N, 128] fp32 = cos[64] | sin[64]; half-dim j uses axis j / 16, band j % 16.
+// ---------------------------------------------------------------------------------------
+__global__ void rope_table_kernel(const float* pos, const float* bands, float* table, int rows,
+                                  int axes, int n_bands) {
+  const int half = axes * n_bands;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * half) return;
+  const int r = idx / half, j = idx - r * half;
+  const float phase = pos[(size_t)r * axes + j / n_bands] * bands[j % n_bands];
+  float s, c;
+  sincosf(phase, &s, &c);
+  table[(size_t)r * 2 * half + j] = c;
+  table[(size_t)r * 2 * half + half + j] = s;
+}
+
+// Per-head RMSNorm + split-half rotation on [N, H, 128]; one warp per (token, head).
+// Lane l holds pairs (4l .. 4l+3, 64 + 4l .. 64 + 4l + 3).
+__global__ void __launch_bounds__(128) qk_norm_rope_fwd_kernel(QkRopeArgs a) {
+  const long wid = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long)a.rows * a.heads) return;
+  const int row = (int)(wid / a.heads), head = (int)(wid - (long)row * a.heads);
+  const __nv_bfloat16* x = a.x + (size_t)row * a.ldx + head * 128;
+  uint2 wa = *reinterpret_cast<const uint2*>(x + 4 * lane);
+  uint2 wb = *reinterpret_cast<const uint2*>(x + 64 + 4 * lane);
+  float va[4], vb[4];
+  { float2 t = unpack_bf16(wa.x), u = unpack_bf16(wa.y); va[0] = t.x; va[1] = t.y; va[2] = u.x; va[3] = u.y; }
+  { float2 t = unpack_bf16(wb.x), u = unpack_bf16(wb.y); vb[0] = t.x; vb[1] = t.y; vb[2] = u.x; vb[3] = u.y; }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) ss += va[j] * va[j] + vb[j] * vb[j];
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss * (1.f / 128.f) + a.eps);
+  if (lane == 0 && a.rstd != nullptr) a.rstd[(size_t)row * a.heads + head] = rstd;
+  const float* cs = a.rope + (size_t)row * 128;
+  float oa[4], ob[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int ia = 4 * lane + j, ib = 64 + ia;
+    const float w_a = a.w_f32 ? reinterpret_cast<const float*>(a.w)[ia] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.w)[ia]);
+    const float w_b = a.w_f32 ? reinterpret_cast<const float*>(a.w)[ib] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.w)[ib]);
+    const float p = va[j] * rstd * w_a, q = vb[j] * rstd * w_b;
+    const float c = cs[ia], s = cs[64 + ia];
+    oa[j] = p * c - q * s;
+    ob[j] = q * c + p * s;
+  }
+  __nv_bfloat16* y = a.y + (size_t)row * a.ldy + head * 128;
+  uint2 o;
+  o.x = pack_bf16(oa[0], oa[1]); o.y = pack_bf16(oa[2], oa[3]);
+  *reinterpret_cast<uint2*>(y + 4 * lane) = o;
+  o.x = pack_bf16(ob[0], ob[1]); o.y = pack_bf16(ob[2], ob[3]);
+  *reinterpret_cast<uint2*>(y + 64 + 4 * lane) = o;
+}
+
+// Backward of the above from the OUTPUT y (the fused forward never stores the
+// pre-norm projection): z = R^-1 y = xhat * w, so xhat = z / w; with g = R^-1 dy:
+//   dx = rstd * (g * w - xhat * mean(g * w * xhat));  dw partial = g * xhat (per row).
+__global__ void __launch_bounds__(128) qk_norm_rope_bwd_kernel(QkRopeBwdArgs a) {
+  const long wid = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long)a.rows * a.heads) return;
+  const int row = (int)(wid / a.heads), head = (int)(wid - (long)row * a.heads);
+  const __nv_bfloat16* y = a.y + (size_t)row * a.ldy + head * 128;
+  const __nv_bfloat16* dy = a.dy + (size_t)row * a.lddy + head * 128;
+  const float* cs = a.rope + (size_t)row * 128;
+  const float rstd = a.rstd[(size_t)row * a.heads + head];
+  uint2 ya = *reinterpret_cast<const uint2*>(y + 4 * lane), yb = *reinterpret_cast<const uint2*>(y + 64 + 4 * lane);
+  uint2 ga = *reinterpret_cast<const uint2*>(dy + 4 * lane), gb = *reinterpret_cast<const uint2*>(dy + 64 + 4 * lane);
+  float y_a[4], y_b[4], g_a[4], g_b[4];
+  { float2 t = unpack_bf16(ya.x), u = unpack_bf16(ya.y); y_a[0] = t.x; y_a[1] = t.y; y_a[2] = u.x; y_a[3] = u.y; }
+  { float2 t = unpack_bf16(yb.x), u = unpack_bf16(yb.y); y_b[0] = t.x; y_b[1] = t.y; y_b[2] = u.x; y_b[3] = u.y; }
+  { float2 t = unpack_bf16(ga.x), u = unpack_bf16(ga.y); g_a[0] = t.x; g_a[1] = t.y; g_a[2] = u.x; g_a[3] = u.y; }
+  { float2 t = unpack_bf16(gb.x), u = unpack_bf16(gb.y); g_b[0] = t.x; g_b[1] = t.y; g_b[2] = u.x; g_b[3] = u.y; }
+  float xh_a[4], xh_b[4], gw_a[4], gw_b[4], gz_a[4], gz_b[4];
+  float dot = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int ia = 4 * lane + j, ib = 64 + ia;
+    const float c = cs[ia], s = cs[64 + ia];
+    // inverse rotation (transpose of the forward rotation)
+    const float za = y_a[j] * c + y_b[j] * s, zb = y_b[j] * c - y_a[j] * s;
+    gz_a[j] = g_a[j] * c + g_b[j] * s;
+    gz_b[j] = g_b[j] * c - g_a[j] * s;
+    const float w_a = a.w_f32 ? reinterpret_cast<const float*>(a.w)[ia] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.w)[ia]);
+    const float w_b = a.w_f32 ? reinterpret_cast<const float*>(a.w)[ib] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.w)[ib]);
+    xh_a[j] = fabsf(w_a) > 1e-12f ? za / w_a : 0.f;
+    xh_b[j] = fabsf(w_b) > 1e-12f ? zb / w_b : 0.f;
+    gw_a[j] = gz_a[j] * w_a;
+    gw_b[j] = gz_b[j] * w_b;
+    dot += gw_a[j] * xh_a[j] + gw_b[j] * xh_b[j];
+  }
+  dot = warp_sum(dot) * (1.f / 128.f);
+  float da[4], db[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    da[j] = rstd * (gw_a[j] - xh_a[j] * dot);
+    db[j] = rstd * (gw_b[j] - xh_b[j] * dot);
+  }
+  __nv_bfloat16* dx = a.dx + (size_t)row * a.lddx + head * 128;
+  uint2 o;
+  o.x = pack_bf16(da[0], da[1]); o.y = pack_bf16(da[2], da[3]);
+  *reinterpret_cast<uint2*>(dx + 4 * lane) = o;
+  o.x = pack_bf16(db[0], db[1]); o.y = pack_bf16(db[2], db[3]);
+  *reinterpret_cast<uint2*>(dx + 64 + 4 * lane) = o;
+  if (a.dw_rows != nullptr) {
+    // per-(row, head) contribution to d weight, reduced over rows and heads by the caller
+    float* dw = a.dw_rows + ((size_t)row * a.heads + head) * 128;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      dw[4 * lane + j] = gz_a[j] * xh_a[j];
+      dw[64 + 4 * lane + j] = gz_b[j] * xh_b[j];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// SiTU-GLU: a = (4 tanh(g/4) sigmoid(g)) * (25 tanh(u/25)), x = [up | gate]
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float situ_gate(float g) { return 4.f * tanhf(0.25f * g) / (1.f + __expf(-g)); }
+__device__ __forceinline__ float situ_up(float u) { return 25.f * tanhf(0.04f * u); }
+
+__global__ void situ_fwd_kernel(const __nv_bfloat16* up, const __nv_bfloat16* gate, long ld_in,
+                                __nv_bfloat16* out, long ld_out, int rows, int f) {
+  const long n8 = (long)rows * (f / 8);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / (f / 8)), c = (int)(i - (long)r * (f / 8)) * 8;
+    float u[8], g[8];
+    load8(up + (size_t)r * ld_in + c, u);
+    load8(gate + (size_t)r * ld_in + c, g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) u[j] = situ_gate(g[j]) * situ_up(u[j]);
+    store8(out + (size_t)r * ld_out + c, u);
+  }
+}
+
+// d up = da * G(g) * (1 - tanh^2(u/25));  d gate = da * U(u) * G'(g),
+// G'(g) = (1 - tanh^2(g/4)) sig(g) + 4 tanh(g/4) sig(g) (1 - sig(g))
+__global__ void situ_bwd_kernel(const __nv_bfloat16* da, long ld_da, const __nv_bfloat16* up,
+                                const __nv_bfloat16* gate, long ld_in, __nv_bfloat16* dup,
+                                __nv_bfloat16* dgate, long ld_out, int rows, int f) {
+  const long n8 = (long)rows * (f / 8);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / (f / 8)), c = (int)(i - (long)r * (f / 8)) * 8;
+    float u[8], g[8], d[8], ou[8], og[8];
+    load8(up + (size_t)r * ld_in + c, u);
+    load8(gate + (size_t)r * ld_in + c, g);
+    load8(da + (size_t)r * ld_da + c, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float tu = tanhf(0.04f * u[j]);
+      const float tg = tanhf(0.25f * g[j]);
+      const float sg = 1.f / (1.f + __expf(-g[j]));
+      const float G = 4.f * tg * sg;
+      const float U = 25.f * tu;
+      ou[j] = d[j] * G * (1.f - tu * tu);
+      og[j] = d[j] * U * ((1.f - tg * tg) * sg + G * (1.f - sg));
+    }
+    store8(dup + (size_t)r * ld_out + c, ou);
+    store8(dgate + (size_t)r * ld_out + c, og);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Gated residual and its backward pieces
+// ---------------------------------------------------------------------------------------
+// out = x * r + o * gate[seg]   (gate nullable)
+__global__ void gated_residual_kernel(const __nv_bfloat16* x, const __nv_bfloat16* o, const float* gate,
+                                      long gate_stride, const int* seg, float r, __nv_bfloat16* out,
+                                      int rows, int dim) {
+  const long n8 = (long)rows * (dim / 8);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / (dim / 8)), c = (int)(i - (long)row * (dim / 8)) * 8;
+    float a[8], b[8];
+    load8(x + (size_t)row * dim + c, a);
+    load8(o + (size_t)row * dim + c, b);
+    const float* gp = gate != nullptr ? gate + (size_t)seg[row] * gate_stride + c : nullptr;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = a[j] * r + b[j] * (gp != nullptr ? gp[j] : 1.f);
+    store8(out + (size_t)row * dim + c, a);
+  }
+}
+
+// y = x * v[seg]   (row-wise scaling by a per-sample vector; d_o = dout * gate[seg])
+__global__ void seg_scale_kernel(const __nv_bfloat16* x, const float* vec, long vec_stride,
+                                 const int* seg, __nv_bfloat16* out, int rows, int dim) {
+  const long n8 = (long)rows * (dim / 8);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / (dim / 8)), c = (int)(i - (long)row * (dim / 8)) * 8;
+    float a[8];
+    load8(x + (size_t)row * dim + c, a);
+    const float* gp = vec + (size_t)seg[row] * vec_stride + c;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] *= gp[j];
+    store8(out + (size_t)row * dim + c, a);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Token MSE: loss = sum_r weight[seg[r]] * mask[r] * mean_c (pred - target)^2, fp32,
+// deterministic: per-block partials then a single-block ordered sum.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) token_mse_partial_kernel(TokenMseArgs a, float* partial) {
+  __shared__ float red[8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float acc = 0.f;
+  for (int row = blockIdx.x * 8 + warp; row < a.rows; row += gridDim.x * 8) {
+    float e = 0.f;
+    for (int c = lane; c < a.dim; c += 32) {
+      const float p = a.pred_f32 ? reinterpret_cast<const float*>(a.pred)[(size_t)row * a.dim + c]
+                                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.pred)[(size_t)row * a.dim + c]);
+      const float d = p - a.target[(size_t)row * a.dim + c];
+      e += d * d;
+    }
+    e = warp_sum(e) / (float)a.dim;
+    float w = a.weight != nullptr ? a.weight[a.seg[row]] : 1.f;
+    if (a.mask != nullptr) w *= a.mask[row];
+    acc += e * w;
+  }
+  if (lane == 0) red[warp] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int i = 0; i < 8; ++i) s += red[i];
+    partial[blockIdx.x] = s;
+  }
+}
+__global__ void sum_partials_kernel(const float* partial, int n, float* out) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    float s = 0.f;
+    for (int i = 0; i < n; ++i) s += partial[i];
+    *out = s;
+  }
+}
+// d pred = dloss * weight[seg] * mask * 2 (pred - target) / dim
+__global__ void token_mse_bwd_kernel(TokenMseArgs a, const float* dloss, void* dpred) {
+  const long n = (long)a.rows * a.dim;
+  const float g = *dloss * 2.f / (float)a.dim;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / a.dim);
+    float w = a.weight != nullptr ? a.weight[a.seg[row]] : 1.f;
+    if (a.mask != nullptr) w *= a.mask[row];
+    const float p = a.pred_f32 ? reinterpret_cast<const float*>(a.pred)[i]
+                               : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.pred)[i]);
+    const float d = g * w * (p - a.target[i]);
+    if (a.pred_f32) reinterpret_cast<float*>(dpred)[i] = d;
+    else reinterpret_cast<__nv_bfloat16*>(dpred)[i] = __float2bfloat16(d);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// fp8 quantisers (e4m3 / e5m2), per-tensor and per-row
+// ---------------------------------------------------------------------------------------
+__global__ void amax_kernel(const __nv_bfloat16* x, long n, float* amax) {
+  float m = 0.f;
+  const long n8 = n / 8;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    float v[8];
+    load8(x + i * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[j]));
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (long i = n8 * 8; i < n; ++i) m = fmaxf(m, fabsf(__bfloat162float(x[i])));
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) atomic_max_nonneg(amax, m);
+}
+
+// scale_out[0] = dequant scale (amax / fmax), scale_out[1] = quant scale (fmax / amax)
+__global__ void fp8_scale_kernel(const float* amax, float fmax, float* scale_out) {
+  const float a = fmaxf(*amax, 1e-12f);
+  scale_out[0] = a / fmax;
+  scale_out[1] = fmax / a;
+}
+
+template <bool E5M2>
+__global__ void cast_fp8_kernel(const __nv_bfloat16* x, long n, const float* qscale, uint8_t* q) {
+  const float s = *qscale;
+  const long n8 = n / 8;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    float v[8];
+    load8(x + i * 8, v);
+    uint2 o;
+    if (E5M2) {
+      __nv_fp8x4_e5m2 lo(make_float4(v[0] * s, v[1] * s, v[2] * s, v[3] * s));
+      __nv_fp8x4_e5m2 hi(make_float4(v[4] * s, v[5] * s, v[6] * s, v[7] * s));
+      o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+    } else {
+      __nv_fp8x4_e4m3 lo(make_float4(v[0] * s, v[1] * s, v[2] * s, v[3] * s));
+      __nv_fp8x4_e4m3 hi(make_float4(v[4] * s, v[5] * s, v[6] * s, v[7] * s));
+      o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+    }
+    *reinterpret_cast<uint2*>(q + i * 8) = o;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    for (long i = n8 * 8; i < n; ++i) {
+      const float t = __bfloat162float(x[i]) * s;
+      q[i] = E5M2 ? __nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E5M2) : __nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3);
+    }
+  }
+}
+
+// One warp per row: row amax -> scale -> e4m3 row; row_scale[r] = amax / 448.
+__global__ void __launch_bounds__(32 * ROWS_PER_BLOCK)
+cast_fp8_rows_kernel(const __nv_bfloat16* x, long ldx, int rows, int dim, uint8_t* q, long ldq, float* row_scale) {
+  const int row = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + (size_t)row * ldx;
+  float m = 0.f;
+  for (int i = lane * 8; i < dim; i += 256) {
+    float v[8];
+    load8(xr + i, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[j]));
+  }
+  m = fmaxf(warp_max(m), 1e-12f);
+  const float s = 448.f / m;
+  if (lane == 0) row_scale[row] = m / 448.f;
+  for (int i = lane * 8; i < dim; i += 256) {
+    float v[8];
+    load8(xr + i, v);
+    __nv_fp8x4_e4m3 lo(make_float4(v[0] * s, v[1] * s, v[2] * s, v[3] * s));
+    __nv_fp8x4_e4m3 hi(make_float4(v[4] * s, v[5] * s, v[6] * s, v[7] * s));
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(q + (size_t)row * ldq + i) = o;
+  }
+}
+
+inline int grid_for(long work, int threads, int cap_mult = 8) {
+  long b = (work + threads - 1) / threads;
+  long cap = 148L * cap_mult;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------------------
+cudaError_t rms_norm_mod_fwd(const NormModArgs& a, cudaStream_t s) {
+  if (a.rows <= 0) return cudaSuccess;
+  if (a.dim % 8) return cudaErrorInvalidValue;
+  rms_norm_mod_fwd_kernel<<<(a.rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK, 32 * ROWS_PER_BLOCK, 0, s>>>(a);
+  return cudaGetLastError();
+}
+cudaError_t rms_norm_mod_bwd(const NormModBwdArgs& a, cudaStream_t s) {
+  if (a.rows <= 0) return cudaSuccess;
+  if (a.dim % 8) return cudaErrorInvalidValue;
+  rms_norm_mod_bwd_kernel<<<(a.rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK, 32 * ROWS_PER_BLOCK, 0, s>>>(a);
+  return cudaGetLastError();
+}
+cudaError_t norm_weight_grad(const NormModBwdArgs& a, float* partial, int chunks, cudaStream_t s) {
+  if (a.rows <= 0) return cudaSuccess;
+  const int rows_per_chunk = (a.rows + chunks - 1) / chunks;
+  dim3 grid((a.dim + 127) / 128, chunks);
+  norm_weight_grad_kernel<<<grid, 128, 0, s>>>(a, partial, rows_per_chunk);
+  return cudaGetLastError();
+}
+cudaError_t seg_sum(const SegSumArgs& a, cudaStream_t s) {
+  if (a.batch <= 0) return cudaSuccess;
+  dim3 grid((a.dim + 127) / 128, a.batch);
+  seg_sum_kernel<<<grid, 128, 0, s>>>(a);
+  return cudaGetLastError();
+}
+cudaError_t rope_table(const float* pos, const float* bands, float* table, int rows, int axes, int n_bands, cudaStream_t s) {
+  const long n = (long)rows * axes * n_bands;
+  if (n <= 0) return cudaSuccess;
+  rope_table_kernel<<<(int)((n + 255) / 256), 256, 0, s>>>(pos, bands, table, rows, axes, n_bands);
+  return cudaGetLastError();
+}
+cudaError_t qk_norm_rope_fwd(const QkRopeArgs& a, cudaStream_t s) {
+  const long warps = (long)a.rows * a.heads;
+  if (warps <= 0) return cudaSuccess;
+  qk_norm_rope_fwd_kernel<<<(int)((warps + 3) / 4), 128, 0, s>>>(a);
+  return cudaGetLastError();
+}
+cudaError_t qk_norm_rope_bwd(const QkRopeBwdArgs& a, cudaStream_t s) {
+  const long warps = (long)a.rows * a.heads;
+  if (warps <= 0) return cudaSuccess;
+  qk_norm_rope_bwd_kernel<<<(int)((warps + 3) / 4), 128, 0, s>>>(a);
+  return cudaGetLastError();
+}
+cudaError_t situ_fwd(const void* up, const void* gate, long ld_in, void* out, long ld_out, int rows, int f, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if (f % 8) return cudaErrorInvalidValue;
+  situ_fwd_kernel<<<grid_for((long)rows * (f / 8), 256), 256, 0, s>>>(
+      (const __nv_bfloat16*)up, (const __nv_bfloat16*)gate, ld_in, (__nv_bfloat16*)out, ld_out, rows, f);
+  return cudaGetLastError();
+}
+cudaError_t situ_bwd(const void* da, long ld_da, const void* up, const void* gate, long ld_in, void* dup, void* dgate,
+                     long ld_out, int rows, int f, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if (f % 8) return cudaErrorInvalidValue;
+  situ_bwd_kernel<<<grid_for((long)rows * (f / 8), 256), 256, 0, s>>>(
+      (const __nv_bfloat16*)da, ld_da, (const __nv_bfloat16*)up, (const __nv_bfloat16*)gate, ld_in,
+      (__nv_bfloat16*)dup, (__nv_bfloat16*)dgate, ld_out, rows, f);
+  return cudaGetLastError();
+}
+cudaError_t gated_residual(const void* x, const void* o, const float* gate, long gate_stride, const int* seg, float r,
+                           void* out, int rows, int dim, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if (dim % 8) return cudaErrorInvalidValue;
+  gated_residual_kernel<<<grid_for((long)rows * (dim / 8), 256), 256, 0, s>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)o, gate, gate_stride, seg, r, (__nv_bfloat16*)out, rows, dim);
+  return cudaGetLastError();
+}
+cudaError_t seg_scale(const void* x, const float* vec, long vec_stride, const int* seg, void* out, int rows, int dim,
+                      cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if (dim % 8) return cudaErrorInvalidValue;
+  seg_scale_kernel<<<grid_for((long)rows * (dim / 8), 256), 256, 0, s>>>(
+      (const __nv_bfloat16*)x, vec, vec_stride, seg, (__nv_bfloat16*)out, rows, dim);
+  return cudaGetLastError();
+}
+int token_mse_blocks(int rows) {
+  int b = (rows + 7) / 8;
+  return b < 1 ? 1 : (b > 296 ? 296 : b);
+}
+cudaError_t token_mse_fwd(const TokenMseArgs& a, float* partial, float* loss, cudaStream_t s) {
+  const int blocks = token_mse_blocks(a.rows);
+  token_mse_partial_kernel<<<blocks, 256, 0, s>>>(a, partial);
+  sum_partials_kernel<<<1, 32, 0, s>>>(partial, blocks, loss);
+  return cudaGetLastError();
+}
+cudaError_t token_mse_bwd(const TokenMseArgs& a, const float* dloss, void* dpred, cudaStream_t s) {
+  const long n = (long)a.rows * a.dim;
+  if (n <= 0) return cudaSuccess;
+  token_mse_bwd_kernel<<<grid_for(n, 256), 256, 0, s>>>(a, dloss, dpred);
+  return cudaGetLastError();
+}
+cudaError_t fp8_amax(const void* x, long n, float* amax, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  amax_kernel<<<grid_for(n / 8 + 1, 256, 4), 256, 0, s>>>((const __nv_bfloat16*)x, n, amax);
+  return cudaGetLastError();
+}
+cudaError_t fp8_scale_from_amax(const float* amax, float fmax, float* scale_out, cudaStream_t s) {
+  fp8_scale_kernel<<<1, 1, 0, s>>>(amax, fmax, scale_out);
+  return cudaGetLastError();
+}
+cudaError_t fp8_cast(const void* x, long n, const float* qscale, void* q, int e5m2, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  const int g = grid_for(n / 8 + 1, 256, 8);
+  if (e5m2) cast_fp8_kernel<true><<<g, 256, 0, s>>>((const __nv_bfloat16*)x, n, qscale, (uint8_t*)q);
+  else cast_fp8_kernel<false><<<g, 256, 0, s>>>((const __nv_bfloat16*)x, n, qscale, (uint8_t*)q);
+  return cudaGetLastError();
+}
+cudaError_t fp8_cast_rows(const void* x, long ldx, int rows, int dim, void* q, long ldq, float* row_scale, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if (dim % 8) return cudaErrorInvalidValue;
+  cast_fp8_rows_kernel<<<(rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK, 32 * ROWS_PER_BLOCK, 0, s>>>(
+      (const __nv_bfloat16*)x, ldx, rows, dim, (uint8_t*)q, ldq, row_scale);
+  return cudaGetLastError();
+}
+
+}  // namespace kmoss

@@ -1,0 +1,141 @@
+"""In-tree build of the CUDA extension: `python -m kohakumosstrainer_b200.csrc.build`.
+
+Each `.cu` is compiled by nvcc for sm_100a only (`-gencode arch=compute_100a,code=sm_100a`)
+without any torch header (seconds per file); `bindings.cpp` is the only translation unit that
+sees ATen. Objects and the shared library live next to the sources so they travel with the
+tree; a content hash of the sources decides staleness, never file times.
+"""
+
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+PKG = HERE.parent
+LIB = PKG / "_C.so"
+OBJ = HERE / "build"
+STAMP = OBJ / "stamp.json"
+
+CUDA_SOURCES = ("gemm_sm100.cu", "blockops.cu", "attention_sm100.cu", "optim.cu", "comm.cu", "no_alloc.cu")
+CPP_SOURCES = ("bindings.cpp",)
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--use_fast_math", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _sources() -> tuple[list[Path], list[Path]]:
+    cu = [HERE / s for s in CUDA_SOURCES if (HERE / s).exists()]
+    cpp = [HERE / s for s in CPP_SOURCES if (HERE / s).exists()]
+    return cu, cpp
+
+
+def _digest(path: Path, headers: list[Path], flags: list[str]) -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(flags).encode())
+    for p in [path, *headers]:
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    return h.hexdigest()
+
+
+def source_digest() -> str:
+    """Hash of every source and header; stored beside the library."""
+    cu, cpp = _sources()
+    headers = sorted(HERE.glob("*.cuh")) + sorted(HERE.glob("*.h"))
+    h = hashlib.sha256()
+    for p in [*cu, *cpp, *headers]:
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def is_fresh() -> bool:
+    if not LIB.exists() or not STAMP.exists():
+        return False
+    try:
+        return json.loads(STAMP.read_text()).get("library") == source_digest()
+    except (OSError, ValueError):
+        return False
+
+
+def _run(cmd: list[str]) -> None:
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"build step failed: {' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
+
+
+def build(verbose: bool = False, force: bool = False) -> Path:
+    """Compile what changed and link `_C.so`. Returns the library path."""
+    if not force and is_fresh():
+        return LIB
+    import torch
+    from torch.utils import cpp_extension
+
+    OBJ.mkdir(exist_ok=True)
+    stamp = {}
+    if STAMP.exists():
+        try:
+            stamp = json.loads(STAMP.read_text())
+        except ValueError:
+            stamp = {}
+    objects = stamp.get("objects", {})
+    cu, cpp = _sources()
+    headers = sorted(HERE.glob("*.cuh")) + sorted(HERE.glob("*.h"))
+    nvcc = _nvcc()
+    cuda_home = Path(nvcc).resolve().parent.parent
+    jobs = []
+    for src in cu:
+        obj = OBJ / (src.stem + ".o")
+        digest = _digest(src, headers, NVCC_FLAGS)
+        if force or objects.get(src.name) != digest or not obj.exists():
+            jobs.append((src, digest, [nvcc, *NVCC_FLAGS, "-I", str(HERE), "-c", str(src), "-o", str(obj)]))
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    cxx_flags = ["-O2", "-std=c++17", "-fPIC", f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-DTORCH_API_INCLUDE_EXTENSION_H"]
+    includes = [f"-I{p}" for p in cpp_extension.include_paths()] + [f"-I{cuda_home / 'include'}", f"-I{HERE}"]
+    for src in cpp:
+        obj = OBJ / (src.stem + ".o")
+        digest = _digest(src, headers, cxx_flags + [torch.__version__])
+        if force or objects.get(src.name) != digest or not obj.exists():
+            jobs.append((src, digest, ["g++", *cxx_flags, *includes, "-c", str(src), "-o", str(obj)]))
+
+    def compile_one(job):
+        src, digest, cmd = job
+        if verbose:
+            print("[build]", src.name, flush=True)
+        _run(cmd)
+        return src.name, digest
+
+    with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:
+        for name, digest in pool.map(compile_one, jobs):
+            objects[name] = digest
+    torch_lib = Path(torch.__file__).parent / "lib"
+    objs = [str(OBJ / (s.stem + ".o")) for s in [*cu, *cpp]]
+    link = [
+        "g++", "-shared", "-o", str(LIB), *objs, f"-L{torch_lib}", f"-L{cuda_home / 'lib64'}",
+        "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-lcudart",
+        f"-Wl,-rpath,{torch_lib}", f"-Wl,-rpath,{cuda_home / 'lib64'}",
+    ]
+    _run(link)
+    STAMP.write_text(json.dumps({"objects": objects, "library": source_digest()}, indent=1))
+    return LIB
+
+
+if __name__ == "__main__":
+    path = build(verbose=True, force="--force" in sys.argv)
+    print(path)

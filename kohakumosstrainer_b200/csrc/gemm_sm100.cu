@@ -1,0 +1,778 @@
+// tcgen05 / TMEM GEMM family for sm_100a.
+//
+// One persistent kernel template covers every dense product of the trainer:
+//   * bf16 x bf16 and fp8 (e4m3 / e5m2) x fp8, fp32 accumulation in tensor memory;
+//   * each operand either K-major or MN-major, so forward (x W^T), dgrad (dy W) and wgrad
+//     (dy^T x) all read the row-major tensors the framework already holds, with no transposes;
+//   * an optional low-rank bypass product (LoRA / LoKr factors) issued into the SAME TMEM
+//     accumulator ahead of the main loop, so an adapter costs no extra pass over the output;
+//   * epilogues on the fp32 accumulator: scale / bias / per-sample gate / residual add
+//     (gated residual), SiTU-GLU on paired up / gate tiles, per-head RMSNorm + RoPE for q / k;
+//   * split-K with a deterministic fp32 reduction for skinny problems (adapter gradients).
+//
+// Structure per CTA (192 threads, one CTA per SM, static persistent tile loop):
+//   warp 0   : TMA producer   - cp.async.bulk.tensor (128-byte swizzle) into a 4..8 stage ring
+//   warp 1   : MMA issuer     - one elected thread issues tcgen05.mma, commits to mbarriers
+//   warps 2-5: epilogue       - tcgen05.ld of the finished accumulator (double-buffered in
+//                               TMEM, so the epilogue of tile i overlaps the mainloop of i+1)
+// What the reference does for these ops: Triton `tl.dot` kernels with GROUP_M swizzle plus
+// cuBLAS for backward (`src/kohakumoss_kernels/backends/triton/blocks/_gemm_kernels.py:14-214`,
+// `backends/_fused_linear.py:357-410`).
+
+#include "gemm_sm100.cuh"
+
+#include "common.cuh"
+
+namespace kmoss {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int GROUP_M = 8;
+constexpr int NUM_THREADS = 192;
+constexpr int NUM_EPI_THREADS = 128;
+
+struct DeviceParams {
+  int M, N, K;
+  int num_m_blocks, num_n_blocks, num_k_blocks;
+  int splits, k_blocks_per_split;
+  int total_tiles;
+  int has_bypass;  // 1 when T / U maps are valid
+  int R;
+  int a_e5m2, b_e5m2;
+  int epilogue;
+  void* out;
+  long ldo;
+  int out_dtype;
+  float alpha;
+  const float* scale_a;
+  const float* scale_b;
+  const float* row_scale;
+  const float* col_scale;
+  const void* bias;
+  int bias_dtype;
+  const __nv_bfloat16* res;
+  long ldr;
+  float beta;
+  const float* gate;
+  long gate_stride;
+  const int* seg;
+  __nv_bfloat16* aux;
+  long ldaux;
+  int situ_f;  // F: row offset of the gate half inside B for EPI_SITU
+  const __nv_bfloat16* q_norm_w;
+  const __nv_bfloat16* k_norm_w;
+  const float* rope;  // [M, 128] fp32 = cos[64] | sin[64] per row
+  int rope_cols;
+  float eps;
+  float* head_rstd;
+  float* workspace;
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, const DeviceParams& p, int& m_blk, int& n_blk,
+                                            int& split) {
+  split = tile % p.splits;
+  int t = tile / p.splits;
+  int per_group = GROUP_M * p.num_n_blocks;
+  int group = t / per_group;
+  int first_m = group * GROUP_M;
+  int rows = min(GROUP_M, p.num_m_blocks - first_m);
+  int within = t - group * per_group;
+  m_blk = first_m + within % rows;
+  n_blk = within / rows;
+}
+
+__device__ __forceinline__ float situ_f(float u, float g) {
+  // (4 tanh(g/4) sigmoid(g)) * (25 tanh(u/25))
+  float sg = 1.0f / (1.0f + __expf(-g));
+  return (4.0f * tanhf(0.25f * g) * sg) * (25.0f * tanhf(0.04f * u));
+}
+
+template <int BN, bool A_MN, bool B_MN, bool FP8>
+struct Cfg {
+  static constexpr int BK = FP8 ? 128 : 64;       // elements per k-block (128 bytes)
+  static constexpr int UMMA_K = FP8 ? 32 : 16;    // elements per instruction
+  static constexpr int K_STEPS = BK / UMMA_K;     // 4
+  static constexpr int CHUNK = FP8 ? 128 : 64;    // MN elements per 128-byte swizzle row
+  static constexpr int A_STAGE = BM * 128;
+  // An MN-major B tile is stored as whole 128-byte-wide chunks of BK rows each.
+  static constexpr int B_CHUNKS = (BN + CHUNK - 1) / CHUNK;
+  static constexpr int B_STAGE = B_MN ? B_CHUNKS * BK * 128 : BN * 128;
+  static constexpr int STAGE = A_STAGE + B_STAGE;
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  // Bytes one k-block / one bypass block deposits on a full barrier.
+  static constexpr uint32_t MAIN_TX = A_STAGE + B_STAGE;
+  static constexpr uint32_t BYPASS_TX = A_STAGE + BN * 128;  // T 128 x 64 and U BN x 64, bf16 K-major
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/;
+  // Advance of the descriptor start address per UMMA_K step, in bytes.
+  static constexpr uint32_t A_KSTEP = A_MN ? (UMMA_K / 8) * 1024 : 32;
+  static constexpr uint32_t B_KSTEP = B_MN ? (UMMA_K / 8) * 1024 : 32;
+  static constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16;
+  static constexpr uint32_t B_LBO = B_MN ? BK * 128 : 16;
+};
+
+// ---------------------------------------------------------------------------------------
+// Epilogue math on one 32-column chunk of one row
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void store_row_chunk(const DeviceParams& p, int m, int n0,
+                                                const float (&v)[32]) {
+  // n0 is a multiple of 32; full vector path when the chunk is inside N and rows are
+  // 16-byte aligned, scalar path otherwise.
+  if (p.out_dtype == OUT_BF16) {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + n0;
+    if (n0 + 32 <= p.N && (p.ldo & 7) == 0) {
+      uint4* o4 = reinterpret_cast<uint4*>(o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 w;
+        w.x = pack_bf16(v[8 * i + 0], v[8 * i + 1]);
+        w.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
+        w.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]);
+        w.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
+        o4[i] = w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (n0 + j < p.N) o[j] = __float2bfloat16(v[j]);
+    }
+  } else {
+    float* o = reinterpret_cast<float*>(p.out) + (size_t)m * p.ldo + n0;
+    if (n0 + 32 <= p.N && (p.ldo & 3) == 0) {
+      float4* o4 = reinterpret_cast<float4*>(o);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (n0 + j < p.N) o[j] = v[j];
+    }
+  }
+}
+
+// out = (acc * s + bias) * gate[seg[m], n] + beta * res[m, n]
+__device__ __forceinline__ void linear_epilogue_chunk(const DeviceParams& p, int m, int n0,
+                                                      float row_s, int seg_m, float (&v)[32]) {
+  const bool full = (n0 + 32 <= p.N);
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    int n = n0 + j;
+    bool ok = full || n < p.N;
+    float s = row_s;
+    if (p.col_scale != nullptr && ok) s *= __ldg(p.col_scale + n);
+    float x = v[j] * s;
+    if (p.bias != nullptr && ok) {
+      x += p.bias_dtype == 0 ? __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(p.bias) + n))
+                             : __ldg(reinterpret_cast<const float*>(p.bias) + n);
+    }
+    if (p.gate != nullptr && ok) x *= __ldg(p.gate + (size_t)seg_m * p.gate_stride + n);
+    v[j] = x;
+  }
+  if (p.res != nullptr) {
+    const __nv_bfloat16* r = p.res + (size_t)m * p.ldr + n0;
+    if (full && (p.ldr & 7) == 0) {
+      const uint4* r4 = reinterpret_cast<const uint4*>(r);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 w = r4[i];
+        float2 a = unpack_bf16(w.x), b = unpack_bf16(w.y), c = unpack_bf16(w.z), d = unpack_bf16(w.w);
+        v[8 * i + 0] += p.beta * a.x; v[8 * i + 1] += p.beta * a.y;
+        v[8 * i + 2] += p.beta * b.x; v[8 * i + 3] += p.beta * b.y;
+        v[8 * i + 4] += p.beta * c.x; v[8 * i + 5] += p.beta * c.y;
+        v[8 * i + 6] += p.beta * d.x; v[8 * i + 7] += p.beta * d.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (n0 + j < p.N) v[j] += p.beta * __bfloat162float(r[j]);
+    }
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, bool FP8>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const __grid_constant__ CUtensorMap map_t, const __grid_constant__ CUtensorMap map_u,
+            const DeviceParams p) {
+  using C = Cfg<BN, A_MN, B_MN, FP8>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)C::STAGES * C::STAGE);
+  // barrier layout: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * C::STAGES + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), NUM_EPI_THREADS / 32);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int bypass_steps = p.has_bypass ? (p.R + 15) / 16 : 0;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------------
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+        int m_blk, n_blk, split;
+        tile_coords(tile, p, m_blk, n_blk, split);
+        const int m0 = m_blk * BM;
+        const int n0 = n_blk * BN;
+        const int kb_begin = split * p.k_blocks_per_split;
+        const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
+        bool ok = true;
+        if (bypass_steps > 0 && split == 0) {
+          // Bypass tiles travel through the ring like a k-block (bf16, K-major, <= 64 wide).
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 100 + stage)) break;
+          mbar_expect_tx(full_bar(stage), C::BYPASS_TX);
+          const uint32_t a_dst = smem_base + stage * C::STAGE;
+          const uint32_t b_dst = a_dst + C::A_STAGE;
+          tma_load_2d(a_dst, &map_t, full_bar(stage), 0, m0);
+          if (p.epilogue == EPI_SITU) {
+            tma_load_2d(b_dst, &map_u, full_bar(stage), 0, n0 / 2);
+            tma_load_2d(b_dst + (BN / 2) * 128, &map_u, full_bar(stage), 0, p.situ_f + n0 / 2);
+          } else {
+            tma_load_2d(b_dst, &map_u, full_bar(stage), 0, n0);
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 100 + stage)) { ok = false; break; }
+          mbar_expect_tx(full_bar(stage), C::MAIN_TX);
+          const uint32_t a_dst = smem_base + stage * C::STAGE;
+          const uint32_t b_dst = a_dst + C::A_STAGE;
+          const int k0 = kb * C::BK;
+          if constexpr (!A_MN) {
+            tma_load_2d(a_dst, &map_a, full_bar(stage), k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / C::CHUNK; ++c)
+              tma_load_2d(a_dst + c * (C::BK * 128), &map_a, full_bar(stage), m0 + c * C::CHUNK, k0);
+          }
+          if constexpr (!B_MN) {
+            if (p.epilogue == EPI_SITU) {
+              // up rows [n0/2, n0/2 + BN/2) and gate rows [F + n0/2, ...)
+              tma_load_2d(b_dst, &map_b, full_bar(stage), k0, n0 / 2);
+              tma_load_2d(b_dst + (BN / 2) * 128, &map_b, full_bar(stage), k0, p.situ_f + n0 / 2);
+            } else {
+              tma_load_2d(b_dst, &map_b, full_bar(stage), k0, n0);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < C::B_CHUNKS; ++c)
+              tma_load_2d(b_dst + c * (C::BK * 128), &map_b, full_bar(stage), n0 + c * C::CHUNK, k0);
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ---------------------------------------
+    if (elect_one()) {
+      constexpr uint32_t idesc_main = umma_idesc(0, 0, A_MN ? 1u : 0u, B_MN ? 1u : 0u, BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      // Operand formats: bf16 = 1 for kind::f16; e4m3 = 0 / e5m2 = 1 for kind::f8f6f4.
+      const uint32_t fmt_a = FP8 ? (uint32_t)p.a_e5m2 : 1u;
+      const uint32_t fmt_b = FP8 ? (uint32_t)p.b_e5m2 : 1u;
+      const uint32_t idesc = idesc_main | (fmt_a << 7) | (fmt_b << 10);
+      const uint32_t idesc_bypass = umma_idesc(1, 1, 0, 0, BM, BN);
+      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+        int m_blk, n_blk, split;
+        tile_coords(tile, p, m_blk, n_blk, split);
+        const int kb_begin = split * p.k_blocks_per_split;
+        const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
+        if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 300 + acc)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        uint32_t accumulate = 0;
+        bool ok = true;
+        if (bypass_steps > 0 && split == 0) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 200 + stage)) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * C::STAGE;
+          const uint32_t b_addr = a_addr + C::A_STAGE;
+          const uint64_t a_desc = umma_smem_desc(a_addr, 16, 1024);
+          const uint64_t b_desc = umma_smem_desc(b_addr, 16, 1024);
+          for (int k = 0; k < bypass_steps; ++k) {
+            mma_f16_ss(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc_bypass, accumulate);
+            accumulate = 1;
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 200 + stage)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * C::STAGE;
+          const uint32_t b_addr = a_addr + C::A_STAGE;
+          const uint64_t a_desc = umma_smem_desc(a_addr, C::A_LBO, 1024);
+          const uint64_t b_desc = umma_smem_desc(b_addr, C::B_LBO, 1024);
+#pragma unroll
+          for (int k = 0; k < C::K_STEPS; ++k) {
+            const uint64_t ad = a_desc + (uint64_t)((k * C::A_KSTEP) >> 4);
+            const uint64_t bd = b_desc + (uint64_t)((k * C::B_KSTEP) >> 4);
+            if constexpr (FP8) mma_f8_ss(d_tmem, ad, bd, idesc, accumulate);
+            else mma_f16_ss(d_tmem, ad, bd, idesc, accumulate);
+            accumulate = 1;
+          }
+          tc_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(acc_full_bar(acc));  // accumulator complete -> epilogue may read
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue warps ------------------------------------
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const int row_in_tile = quarter * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    float scalar = p.alpha;
+    if (p.scale_a != nullptr) scalar *= __ldg(p.scale_a);
+    if (p.scale_b != nullptr) scalar *= __ldg(p.scale_b);
+    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+      int m_blk, n_blk, split;
+      tile_coords(tile, p, m_blk, n_blk, split);
+      const int m = m_blk * BM + row_in_tile;
+      const int n_tile = n_blk * BN;
+      if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, 400 + acc)) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      const bool row_ok = m < p.M;
+
+      if (p.splits > 1) {
+        float* ws = p.workspace + ((size_t)split * p.M + (row_ok ? m : 0)) * p.N;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          if (row_ok) {
+            const int n0 = n_tile + c * 32;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) ws[n0 + j] = __uint_as_float(r[j]);
+          }
+        }
+      } else if (p.epilogue == EPI_LINEAR) {
+        float row_s = scalar;
+        int seg_m = 0;
+        if (row_ok) {
+          if (p.row_scale != nullptr) row_s *= __ldg(p.row_scale + m);
+          if (p.gate != nullptr) seg_m = __ldg(p.seg + m);
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          const int n0 = n_tile + c * 32;
+          if (row_ok && n0 < p.N) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            linear_epilogue_chunk(p, m, n0, row_s, seg_m, v);
+            store_row_chunk(p, m, n0, v);
+          }
+        }
+      } else if (p.epilogue == EPI_SITU) {
+        // accumulator columns [0, BN/2) = up, [BN/2, BN) = gate, for output columns
+        // [n_tile/2, n_tile/2 + BN/2)
+        float row_s = scalar;
+        if (row_ok && p.row_scale != nullptr) row_s *= __ldg(p.row_scale + m);
+        const int out0 = n_tile / 2;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t ru[32], rg[32];
+          tmem_ld_32x32(t_row + c * 32, ru);
+          tmem_ld_32x32(t_row + BN / 2 + c * 32, rg);
+          tmem_ld_wait();
+          const int n0 = out0 + c * 32;
+          if (row_ok && n0 < p.N) {
+            float u[32], g[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float su = row_s, sg = row_s;
+              if (p.col_scale != nullptr && n0 + j < p.N) {
+                su *= __ldg(p.col_scale + n0 + j);
+                sg *= __ldg(p.col_scale + p.situ_f + n0 + j);
+              }
+              u[j] = __uint_as_float(ru[j]) * su;
+              g[j] = __uint_as_float(rg[j]) * sg;
+            }
+            if (p.aux != nullptr) {
+              // pre-activations, rounded to bf16 exactly as the unfused path stores them
+              __nv_bfloat16* au = p.aux + (size_t)m * p.ldaux + n0;
+              __nv_bfloat16* ag = au + p.situ_f;
+              if (n0 + 32 <= p.N && (p.ldaux & 7) == 0 && (p.situ_f & 7) == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  uint4 w;
+                  w.x = pack_bf16(u[8 * i], u[8 * i + 1]); w.y = pack_bf16(u[8 * i + 2], u[8 * i + 3]);
+                  w.z = pack_bf16(u[8 * i + 4], u[8 * i + 5]); w.w = pack_bf16(u[8 * i + 6], u[8 * i + 7]);
+                  reinterpret_cast<uint4*>(au)[i] = w;
+                  w.x = pack_bf16(g[8 * i], g[8 * i + 1]); w.y = pack_bf16(g[8 * i + 2], g[8 * i + 3]);
+                  w.z = pack_bf16(g[8 * i + 4], g[8 * i + 5]); w.w = pack_bf16(g[8 * i + 6], g[8 * i + 7]);
+                  reinterpret_cast<uint4*>(ag)[i] = w;
+                }
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (n0 + j < p.N) { au[j] = __float2bfloat16(u[j]); ag[j] = __float2bfloat16(g[j]); }
+              }
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                u[j] = __bfloat162float(__float2bfloat16(u[j]));
+                g[j] = __bfloat162float(__float2bfloat16(g[j]));
+              }
+            }
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = situ_f(u[j], g[j]);
+            store_row_chunk(p, m, n0, v);
+          }
+        }
+      } else {  // EPI_QK_ROPE: heads of 128 columns; BN is 128 or 256
+        float row_s = scalar;
+        if (row_ok && p.row_scale != nullptr) row_s *= __ldg(p.row_scale + m);
+#pragma unroll 1
+        for (int h = 0; h < BN / 128; ++h) {
+          const int n_head = n_tile + h * 128;
+          const uint32_t t_head = t_row + h * 128;
+          if (n_head >= p.N) break;
+          if (n_head < p.rope_cols) {
+            const __nv_bfloat16* w = (n_head < p.rope_cols / 2) ? p.q_norm_w : p.k_norm_w;
+            float ss = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32(t_head + c * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                float s = row_s;
+                if (p.col_scale != nullptr) s *= __ldg(p.col_scale + n_head + c * 32 + j);
+                float x = __uint_as_float(r[j]) * s;
+                ss += x * x;
+              }
+            }
+            const float inv = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
+            if (row_ok && p.head_rstd != nullptr)
+              p.head_rstd[(size_t)m * (p.rope_cols / 128) + n_head / 128] = inv;
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+              uint32_t ra[32], rb[32];
+              tmem_ld_32x32(t_head + c * 32, ra);
+              tmem_ld_32x32(t_head + 64 + c * 32, rb);
+              tmem_ld_wait();
+              if (row_ok) {
+                float va[32], vb[32];
+                const float* cs = p.rope + (size_t)m * 128 + c * 32;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const int ja = c * 32 + j, jb = 64 + c * 32 + j;
+                  float sa = row_s, sb = row_s;
+                  if (p.col_scale != nullptr) {
+                    sa *= __ldg(p.col_scale + n_head + ja);
+                    sb *= __ldg(p.col_scale + n_head + jb);
+                  }
+                  float a = __uint_as_float(ra[j]) * sa * inv * __bfloat162float(__ldg(w + ja));
+                  float b = __uint_as_float(rb[j]) * sb * inv * __bfloat162float(__ldg(w + jb));
+                  float co = cs[j], si = cs[64 + j];
+                  va[j] = a * co - b * si;
+                  vb[j] = b * co + a * si;
+                }
+                store_row_chunk(p, m, n_head + c * 32, va);
+                store_row_chunk(p, m, n_head + 64 + c * 32, vb);
+              }
+            }
+          } else {
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32(t_head + c * 32, r);
+              tmem_ld_wait();
+              const int n0 = n_head + c * 32;
+              if (row_ok && n0 < p.N) {
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                linear_epilogue_chunk(p, m, n0, row_s, 0, v);
+                store_row_chunk(p, m, n0, v);
+              }
+            }
+          }
+        }
+      }
+      // hand the accumulator back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------------------------- teardown -----------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // Bounded grace period for copies still in flight before shared memory is released.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// split-K reduction: sums the fp32 partials and applies the linear epilogue
+// ---------------------------------------------------------------------------------------
+__global__ void splitk_reduce_kernel(DeviceParams p) {
+  const size_t total = (size_t)p.M * p.N;
+  float scalar = p.alpha;
+  if (p.scale_a != nullptr) scalar *= __ldg(p.scale_a);
+  if (p.scale_b != nullptr) scalar *= __ldg(p.scale_b);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int m = (int)(i / p.N);
+    const int n = (int)(i - (size_t)m * p.N);
+    float acc = 0.f;
+    for (int s = 0; s < p.splits; ++s) acc += p.workspace[(size_t)s * total + i];
+    float s = scalar;
+    if (p.row_scale != nullptr) s *= p.row_scale[m];
+    if (p.col_scale != nullptr) s *= p.col_scale[n];
+    float x = acc * s;
+    if (p.bias != nullptr)
+      x += p.bias_dtype == 0 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n])
+                             : reinterpret_cast<const float*>(p.bias)[n];
+    if (p.gate != nullptr) x *= p.gate[(size_t)p.seg[m] * p.gate_stride + n];
+    if (p.res != nullptr) x += p.beta * __bfloat162float(p.res[(size_t)m * p.ldr + n]);
+    if (p.out_dtype == OUT_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16(x);
+    else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = x;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+    if (q != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// 2-D row-major matrix [rows, cols] with row stride `ld` elements; box = [box_rows, box_cols],
+// box_cols * elem_bytes == 128 (one swizzle row).
+bool make_map(CUtensorMap* map, const void* base, int elem_bytes, bool fp8, uint64_t rows, uint64_t cols,
+              uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+int sm_count() {
+  static int n = []() {
+    int dev = 0, v = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v;
+  }();
+  return n;
+}
+
+template <int BN, bool A_MN, bool B_MN, bool FP8>
+cudaError_t launch_cfg(const GemmProblem& g, DeviceParams& p, cudaStream_t stream) {
+  using C = Cfg<BN, A_MN, B_MN, FP8>;
+  const int eb = FP8 ? 1 : 2;
+  CUtensorMap map_a, map_b, map_t, map_u;
+  bool ok = true;
+  if (!A_MN) ok &= make_map(&map_a, g.A, eb, FP8, g.M, g.K, g.lda, BM, C::BK);
+  else ok &= make_map(&map_a, g.A, eb, FP8, g.K, g.M, g.lda, C::BK, C::CHUNK);
+  const uint64_t b_rows = g.epilogue == EPI_SITU ? 2 * (uint64_t)p.situ_f : (uint64_t)g.N;
+  const uint32_t b_box_rows = g.epilogue == EPI_SITU ? BN / 2 : BN;
+  if (!B_MN) ok &= make_map(&map_b, g.B, eb, FP8, b_rows, g.K, g.ldb, b_box_rows, C::BK);
+  else ok &= make_map(&map_b, g.B, eb, FP8, g.K, g.N, g.ldb, C::BK, C::CHUNK);
+  if (p.has_bypass) {
+    ok &= make_map(&map_t, g.T, 2, false, g.M, g.R, g.ldt, BM, 64);
+    ok &= make_map(&map_u, g.U, 2, false, b_rows, g.R, g.ldu, b_box_rows, 64);
+  } else {
+    map_t = map_a;
+    map_u = map_b;
+  }
+  if (!ok) return cudaErrorInvalidValue;
+
+  p.num_m_blocks = (g.M + BM - 1) / BM;
+  const int n_extent = g.epilogue == EPI_SITU ? 2 * g.N : g.N;
+  p.num_n_blocks = (n_extent + BN - 1) / BN;
+  p.num_k_blocks = (g.K + C::BK - 1) / C::BK;
+  p.splits = g.splits > 1 ? g.splits : 1;
+  if (p.splits > p.num_k_blocks) p.splits = p.num_k_blocks > 0 ? p.num_k_blocks : 1;
+  p.k_blocks_per_split = (p.num_k_blocks + p.splits - 1) / p.splits;
+  p.splits = (p.num_k_blocks + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+  if (p.splits < 1) p.splits = 1;
+  p.total_tiles = p.num_m_blocks * p.num_n_blocks * p.splits;
+
+  auto kern = gemm_kernel<BN, A_MN, B_MN, FP8>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+  if (grid <= 0) return cudaSuccess;
+  kern<<<grid, NUM_THREADS, C::SMEM, stream>>>(map_a, map_b, map_t, map_u, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  if (p.splits > 1) {
+    const size_t total = (size_t)g.M * g.N;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p);
+    e = cudaGetLastError();
+  }
+  return e;
+}
+
+template <int BN>
+cudaError_t launch_bn(const GemmProblem& g, DeviceParams& p, cudaStream_t s) {
+  const bool fp8 = g.a_dtype != GEMM_BF16;
+  if (!fp8) {
+    if (!g.a_mn && !g.b_mn) return launch_cfg<BN, false, false, false>(g, p, s);
+    if (!g.a_mn && g.b_mn) return launch_cfg<BN, false, true, false>(g, p, s);
+    if (g.a_mn && g.b_mn) return launch_cfg<BN, true, true, false>(g, p, s);
+    return launch_cfg<BN, true, false, false>(g, p, s);
+  }
+  if (!g.a_mn && !g.b_mn) return launch_cfg<BN, false, false, true>(g, p, s);
+  if (!g.a_mn && g.b_mn) return launch_cfg<BN, false, true, true>(g, p, s);
+  if (g.a_mn && g.b_mn) return launch_cfg<BN, true, true, true>(g, p, s);
+  return launch_cfg<BN, true, false, true>(g, p, s);
+}
+
+}  // namespace
+
+size_t gemm_workspace_bytes(int M, int N, int splits) {
+  return splits > 1 ? (size_t)splits * M * N * sizeof(float) : 0;
+}
+
+int gemm_pick_splits(int M, int N, int K, int elem_bytes) {
+  const int bk = 128 / elem_bytes;
+  const int bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+  const int kblocks = (K + bk - 1) / bk;
+  if (tiles >= 74 || kblocks < 8) return 1;
+  int s = 148 / tiles;
+  if (s > kblocks / 4) s = kblocks / 4;
+  if (s > 32) s = 32;
+  return s < 1 ? 1 : s;
+}
+
+cudaError_t gemm_launch(const GemmProblem& g, cudaStream_t stream) {
+  if (g.M <= 0 || g.N <= 0) return cudaSuccess;
+  const bool fp8 = g.a_dtype != GEMM_BF16;
+  if (fp8 != (g.b_dtype != GEMM_BF16)) return cudaErrorInvalidValue;
+  const int eb = fp8 ? 1 : 2;
+  // TMA needs 16-byte aligned bases and row strides.
+  if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.B) & 15)) return cudaErrorMisalignedAddress;
+  if ((g.lda * eb) % 16 || (g.ldb * eb) % 16) return cudaErrorMisalignedAddress;
+  if (g.K <= 0) return cudaErrorInvalidValue;
+
+  DeviceParams p{};
+  p.M = g.M; p.N = g.N; p.K = g.K;
+  p.has_bypass = (g.T != nullptr && g.U != nullptr && g.R > 0) ? 1 : 0;
+  if (p.has_bypass) {
+    if (g.R > 64 || (g.ldt * 2) % 16 || (g.ldu * 2) % 16) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(g.T) & 15) || (reinterpret_cast<uintptr_t>(g.U) & 15)) return cudaErrorMisalignedAddress;
+  }
+  p.R = g.R;
+  p.a_e5m2 = g.a_dtype == GEMM_E5M2 ? 1 : 0;
+  p.b_e5m2 = g.b_dtype == GEMM_E5M2 ? 1 : 0;
+  p.epilogue = g.epilogue;
+  p.out = g.out; p.ldo = g.ldo; p.out_dtype = g.out_dtype;
+  p.alpha = g.alpha;
+  p.scale_a = g.scale_a; p.scale_b = g.scale_b;
+  p.row_scale = g.row_scale; p.col_scale = g.col_scale;
+  p.bias = g.bias; p.bias_dtype = g.bias_dtype;
+  p.res = reinterpret_cast<const __nv_bfloat16*>(g.res); p.ldr = g.ldr; p.beta = g.beta;
+  p.gate = g.gate; p.gate_stride = g.gate_stride; p.seg = g.seg;
+  p.aux = reinterpret_cast<__nv_bfloat16*>(g.aux); p.ldaux = g.ldaux;
+  p.situ_f = g.N;
+  p.q_norm_w = reinterpret_cast<const __nv_bfloat16*>(g.q_norm_w);
+  p.k_norm_w = reinterpret_cast<const __nv_bfloat16*>(g.k_norm_w);
+  p.rope = g.pos;  // precomputed [M, 128] cos|sin table
+  p.rope_cols = g.rope_cols; p.eps = g.eps;
+  p.head_rstd = g.head_rstd;
+  p.workspace = g.workspace; p.status = g.status;
+
+  if (g.epilogue == EPI_SITU) {
+    if (g.b_mn || g.splits > 1 || (g.N % 128) != 0) return cudaErrorInvalidValue;
+    return launch_bn<256>(g, p, stream);
+  }
+  if (g.epilogue == EPI_QK_ROPE) {
+    if (g.splits > 1 || (g.N % 128) != 0 || (g.rope_cols % 256) != 0) return cudaErrorInvalidValue;
+    return launch_bn<256>(g, p, stream);
+  }
+  if (g.splits > 1 && g.workspace == nullptr) return cudaErrorInvalidValue;
+  if (g.N > 128) return launch_bn<256>(g, p, stream);
+  // An MN-major fp8 B tile is 128 elements wide at least (one 128-byte swizzle row).
+  if (g.N > 64 || (fp8 && g.b_mn)) return launch_bn<128>(g, p, stream);
+  return launch_bn<64>(g, p, stream);
+}
+
+}  // namespace kmoss

@@ -1,0 +1,87 @@
+// Host-visible interface of the tcgen05 GEMM family (see gemm_sm100.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace kmoss {
+
+enum GemmDtype : int { GEMM_BF16 = 0, GEMM_E4M3 = 1, GEMM_E5M2 = 2 };
+enum GemmOut : int { OUT_BF16 = 0, OUT_F32 = 1 };
+enum GemmEpilogue : int {
+  EPI_LINEAR = 0,   // out = (acc*s + bias) * gate[seg[m], n] + beta * res[m, n]
+  EPI_SITU = 1,     // B rows [n, n+64) are `up`, [F+n, F+n+64) are `gate`: out[m, n] = situ(up, gate)
+  EPI_QK_ROPE = 2,  // per-head RMSNorm + 4-axis split-half RoPE on the q / k column ranges
+};
+
+// D[M, N] = epilogue(A[M, K] . B[N, K]^T). An operand is "K-major" when its K index is
+// contiguous in memory (A stored [M, K], B stored [N, K]) and "MN-major" when its M / N
+// index is contiguous (A stored [K, M], B stored [K, N]); `lda` / `ldb` are the row strides
+// of the stored matrices in elements.
+struct GemmProblem {
+  int M, N, K;
+  const void* A;
+  const void* B;
+  long lda, ldb;
+  int a_dtype, b_dtype;  // GemmDtype; bf16 with bf16, fp8 with fp8 (e4m3 / e5m2 may mix)
+  int a_mn, b_mn;        // 0 = K-major, 1 = MN-major
+
+  // Optional second (low-rank bypass) product accumulated into the same TMEM tile before
+  // the main loop: acc = T[M, R] . U[N, R]^T (bf16, K-major, R multiple of 16, <= 64), then
+  // acc += A . B^T. With fp8 main operands the caller pre-divides T by the fp8 scales.
+  const void* T;
+  const void* U;
+  long ldt, ldu;
+  int R;
+
+  // epilogue
+  int epilogue;          // GemmEpilogue
+  void* out;
+  long ldo;
+  int out_dtype;         // GemmOut
+  float alpha;           // host scalar
+  const float* scale_a;  // device scalars (nullable): acc *= *scale_a * *scale_b
+  const float* scale_b;
+  const float* row_scale;  // [M] nullable
+  const float* col_scale;  // [N] nullable
+  const void* bias;        // [N] nullable
+  int bias_dtype;          // 0 bf16, 1 fp32
+  const void* res;         // [M, N] bf16 nullable (residual stream)
+  long ldr;
+  float beta;
+  const float* gate;       // [B, N] fp32 view with row stride gate_stride, nullable
+  long gate_stride;
+  const int* seg;          // [M] int32 sample index per row (with gate)
+
+  // EPI_SITU: N counts output columns F; B holds 2F rows (up | gate). aux (nullable)
+  // receives the pre-activation [M, 2F] bf16 for the backward pass.
+  void* aux;
+  long ldaux;
+
+  // EPI_QK_ROPE: columns [0, rope_cols) are heads of 128 that get norm_w (q for
+  // n < rope_cols / 2, else k) and rotation by the per-row table pos[M, 128] = cos[64] | sin[64];
+  // other columns take the linear epilogue.
+  const void* q_norm_w;
+  const void* k_norm_w;
+  const float* pos;
+  int rope_cols;
+  float eps;
+  float* head_rstd;  // [M, rope_cols / 128] fp32 nullable: 1 / rms of each normalised head (for backward)
+
+  // split-K: partial sums [splits, M, N] fp32 in `workspace` (bytes >= splits*M*N*4)
+  int splits;
+  float* workspace;
+
+  int* status;  // int[4] device status word (nullable)
+};
+
+// Launch on `stream`. Returns cudaSuccess or the launch / argument error. No allocation.
+cudaError_t gemm_launch(const GemmProblem& p, cudaStream_t stream);
+
+// Bytes of workspace `gemm_launch` needs for this problem (0 when splits <= 1).
+size_t gemm_workspace_bytes(int M, int N, int splits);
+
+// Heuristic number of K splits so a skinny problem fills the 148 SMs.
+int gemm_pick_splits(int M, int N, int K, int elem_bytes);
+
+}  // namespace kmoss
