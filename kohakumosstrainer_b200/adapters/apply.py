@@ -1,0 +1,216 @@
+"""Targeting presets, adapter configuration and the AdapterSet attached to a backbone.
+
+Preset expressions (`attn`, `attn-mlp`, `full-block`, `all`, plus `+text-refiner`,
+`+modulation`, `+embed`) are regexes over backbone module paths, identical to the
+reference's (`src/kohakumoss/adapters/build/presets.py:9-36`). Keys in saved files are
+`lora_unet_<path with . -> _>.<tensor>` (`build/network.py:26-28`).
+"""
+
+from __future__ import annotations
+
+import re
+from dataclasses import dataclass, field
+
+import torch
+from torch import Tensor, nn
+
+from ..models.linear import MossLinear
+from .modules import MODULES, AdapterModule
+
+JOINT_ATTN = r"layers\.\d+\.proj\.(q|k|v|o)$"
+JOINT_MLP = r"layers\.\d+\.proj\.(ffn_up_gate|ffn_down)$"
+TEXT_BLOCK = r"text_embedder\.blocks\.\d+\.(qkv|proj|ffn_gate|ffn_up|ffn_down)$"
+TEXT_PROJ = r"text_embedder\.proj$"
+MODULATION = r"(shared_block_modulation|video_head_modulation|time_embedding\.\d+)$"
+EMBED_HEAD = r"(video_embedder|final_linear_video)$"
+JOINT_NORMS = r"layers\.\d+\.(norm1|norm2|q_norm|k_norm)$"
+TEXT_NORMS = r"text_embedder\.blocks\.\d+\.(norm1|norm2|q_norm|k_norm)$"
+FINAL_NORM = r"final_norm_video$"
+
+BASES = {
+    "attn": ([JOINT_ATTN], [JOINT_NORMS]),
+    "attn-mlp": ([JOINT_ATTN, JOINT_MLP], [JOINT_NORMS]),
+    "full-block": ([JOINT_ATTN, JOINT_MLP, TEXT_BLOCK], [JOINT_NORMS, TEXT_NORMS]),
+    "all": ([JOINT_ATTN, JOINT_MLP, TEXT_BLOCK, TEXT_PROJ, MODULATION, EMBED_HEAD], [JOINT_NORMS, TEXT_NORMS, FINAL_NORM]),
+}
+MODIFIERS = {
+    "text-refiner": ([TEXT_BLOCK, TEXT_PROJ], [TEXT_NORMS]),
+    "modulation": ([MODULATION], []),
+    "embed": ([EMBED_HEAD], [FINAL_NORM]),
+}
+ALGOS = ("lora", "locon", "loha", "lokr", "oft", "ia3", "full", "diff", "dora")
+
+
+def resolve_preset(preset: str | dict) -> tuple[list[str], list[str]]:
+    """(target-name regexes, norm regexes) of a `base[+modifier...]` expression or a dict
+    `{"target_name": [...], "norm_name": [...]}`."""
+    if isinstance(preset, dict):
+        return list(preset.get("target_name", [])), list(preset.get("norm_name", []))
+    base, *mods = preset.split("+")
+    if base not in BASES:
+        raise KeyError(f"unknown MOSS preset {base!r}; known: {sorted(BASES)}")
+    names, norms = (list(v) for v in BASES[base])
+    for mod in mods:
+        if mod not in MODIFIERS:
+            raise KeyError(f"unknown preset modifier {mod!r}; known: {sorted(MODIFIERS)}")
+        en, eo = MODIFIERS[mod]
+        names += [n for n in en if n not in names]
+        norms += [n for n in eo if n not in norms]
+    return names, norms
+
+
+@dataclass(frozen=True)
+class AdapterConfig:
+    algo: str = "lora"
+    preset: str | dict = "attn-mlp"
+    dim: int = 32
+    alpha: float = 32.0
+    algo_kwargs: dict = field(default_factory=dict)
+    dora: bool = False
+    dora_on_output: bool = True
+    dropout: float = 0.0
+    rank_dropout: float = 0.0
+    module_dropout: float = 0.0
+    mode: str = "bypass"
+    train_norms: bool = False
+    multiplier: float = 1.0
+    prefix: str = "lora_unet"
+    lr_ratio_up: float = 1.0
+    seed: int = 0
+    dtype: torch.dtype = torch.float32
+
+    def problems(self) -> list[str]:
+        out = []
+        if self.algo not in ALGOS:
+            out.append(f"ALGO {self.algo!r} unknown (have {', '.join(ALGOS)})")
+        if self.mode not in ("bypass", "merge"):
+            out.append("ADAPTER_MODE must be bypass|merge")
+        if self.dim < 1:
+            out.append("DIM must be >= 1")
+        return out
+
+
+def lora_name_of(prefix: str, path: str) -> str:
+    return f"{prefix}_{path}".replace(".", "_")
+
+
+class AdapterSet(nn.Module):
+    """The adapters of one backbone: an `nn.ModuleDict` keyed by LyCORIS name, the target
+    paths, and (with `train_norms`) the norm weights made trainable."""
+
+    def __init__(self, cfg: AdapterConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.modules_by_name = nn.ModuleDict()
+        self.paths: dict[str, str] = {}
+        self.norm_params: dict[str, nn.Parameter] = {}
+
+    def __len__(self) -> int:
+        return len(self.modules_by_name)
+
+    def items(self):
+        for name, module in self.modules_by_name.items():
+            yield name, self.paths[name], module
+
+    def trainable_parameters(self) -> list[nn.Parameter]:
+        params = [p for p in self.modules_by_name.parameters() if p.requires_grad]
+        return params + list(self.norm_params.values())
+
+    def param_groups(self, lr: float) -> list[dict]:
+        """LoRA+ : factors that start at zero (`lora_up`, `hada_w2_a`, `lokr_w2*`) learn at
+        `lr * lr_ratio_up`."""
+        ratio = self.cfg.lr_ratio_up
+        fast, slow = [], []
+        zero_init = ("lora_up", "hada_w2_a", "lokr_w2", "oft_blocks")
+        for name, p in self.modules_by_name.named_parameters():
+            (fast if ratio != 1.0 and any(z in name for z in zero_init) else slow).append(p)
+        groups = [{"params": slow + list(self.norm_params.values()), "lr": lr}]
+        if fast:
+            groups.append({"params": fast, "lr": lr * ratio})
+        return groups
+
+    def set_multiplier(self, m: float) -> None:
+        for mod in self.modules_by_name.values():
+            mod.multiplier = float(m)
+
+    def adapter_state(self) -> dict[str, Tensor]:
+        """Flat LyCORIS-named state: `<lora_name>.<tensor>`."""
+        out = {}
+        for name, mod in self.modules_by_name.items():
+            for key, value in mod.state_dict().items():
+                if key == "on_input":
+                    out[f"{name}.on_input"] = value.detach()
+                    continue
+                out[f"{name}.{key}"] = value.detach()
+        for path, p in self.norm_params.items():
+            out[f"{lora_name_of(self.cfg.prefix, path)}.w_norm"] = p.detach()
+        return out
+
+    def load_adapter_state(self, state: dict[str, Tensor], strict: bool = True) -> None:
+        own = self.adapter_state()
+        missing = [k for k in own if k not in state]
+        unexpected = [k for k in state if k not in own]
+        if strict and (missing or unexpected):
+            raise KeyError(f"adapter state mismatch: missing {missing[:5]}, unexpected {unexpected[:5]}")
+        with torch.no_grad():
+            for k, v in state.items():
+                if k in own:
+                    own[k].copy_(v)
+
+    def detach_from(self, model: nn.Module) -> None:
+        for lin in model.modules():
+            if isinstance(lin, MossLinear):
+                lin.set_adapter(None)
+
+
+def targets_of(model: nn.Module, patterns: list[str]) -> list[tuple[str, MossLinear]]:
+    regs = [re.compile(p) for p in patterns]
+    out = []
+    for path, module in model.named_modules():
+        if isinstance(module, MossLinear) and any(r.search(path) for r in regs):
+            out.append((path, module))
+    return out
+
+
+def apply(model: nn.Module, cfg: AdapterConfig, freeze_base: bool = True) -> AdapterSet:
+    """Build one adapter per targeted linear, attach it, freeze everything else."""
+    problems = cfg.problems()
+    if problems:
+        raise ValueError("; ".join(problems))
+    names, norms = resolve_preset(cfg.preset)
+    aset = AdapterSet(cfg)
+    if freeze_base:
+        for p in model.parameters():
+            p.requires_grad_(False)
+    algo = "lora" if cfg.algo == "dora" else cfg.algo
+    cls = MODULES[algo]
+    gen_state = torch.random.get_rng_state()
+    torch.manual_seed(cfg.seed)
+    try:
+        for path, lin in targets_of(model, names):
+            dev = lin.weight_like.device
+            kwargs = dict(cfg.algo_kwargs)
+            mod: AdapterModule = cls(
+                lin.in_features, lin.out_features, cfg.dim, cfg.alpha, multiplier=cfg.multiplier,
+                dropout=cfg.dropout, rank_dropout=cfg.rank_dropout, module_dropout=cfg.module_dropout, **kwargs,
+            )
+            mod.to(device=dev, dtype=cfg.dtype)
+            if cfg.dora or cfg.algo == "dora":
+                mod.enable_dora(lin.base_weight(torch.float32), cfg.dora_on_output)
+            name = lora_name_of(cfg.prefix, path)
+            aset.modules_by_name[name] = mod
+            aset.paths[name] = path
+            lin.set_adapter(mod, cfg.mode)
+    finally:
+        torch.random.set_rng_state(gen_state)
+    if cfg.train_norms:
+        regs = [re.compile(p) for p in norms]
+        for path, module in model.named_modules():
+            if hasattr(module, "weight") and any(r.search(path) for r in regs):
+                module.weight.requires_grad_(True)
+                aset.norm_params[path] = module.weight
+    if hasattr(model, "ops") and model.ops is not None and model.ops.name == "native":
+        from ..ops import native_ops
+
+        native_ops.invalidate_packs(model)
+    return aset

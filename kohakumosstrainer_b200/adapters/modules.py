@@ -1,0 +1,347 @@
+"""Adapter modules with LyCORIS tensor names and math, written against plain torch.
+
+Each module owns the trainable tensors of one target linear and exposes
+
+* `delta(base)`      - the dense weight change dW `[out, in]` (fp32 math),
+* `merged(W)`        - the effective weight (W + m dW, or the DoRA / OFT transform of W),
+* `bypass(x, y, lin)`- y + adapter(x) without forming dW where the algebra allows it,
+* `state()`          - tensors under their LyCORIS names (`lora_down.weight`, `hada_w1_a`, ...).
+
+Names, shapes, scales and initialisation follow public LyCORIS conventions as the reference
+records them (`src/kohakumoss/adapters/infer/formats.py:8-51`, `kinds/lowrank.py`,
+`kinds/rotation.py`, `tests/_util/oft_ref.py:12-21`). Plain LoRA sets `fusable = True`: the
+CUDA op set runs it as a low-rank bypass inside the base GEMM's TMEM accumulator.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor, nn
+
+
+def _factorization(dim: int, factor: int = -1) -> tuple[int, int]:
+    """Split `dim = m * n`, m <= n, m as close to `factor` (or sqrt(dim) for -1) as divides."""
+    if factor > 0 and dim % factor == 0:
+        m, n = factor, dim // factor
+        return (m, n) if m <= n else (n, m)
+    if factor < 0:
+        factor = dim
+    m, n = 1, dim
+    length = m + n
+    while m < n:
+        new_m = m + 1
+        while dim % new_m:
+            new_m += 1
+        new_n = dim // new_m
+        if new_m + new_n > length or new_m > factor:
+            break
+        m, n = new_m, new_n
+        length = m + n
+    return (m, n) if m <= n else (n, m)
+
+
+class AdapterModule(nn.Module):
+    """Common state: alpha (buffer, saved), multiplier, dropout rates, DoRA magnitude."""
+
+    algo = "base"
+    fusable = False
+
+    def __init__(self, in_features: int, out_features: int, rank: int, alpha: float, multiplier: float = 1.0,
+                 dropout: float = 0.0, rank_dropout: float = 0.0, module_dropout: float = 0.0):
+        super().__init__()
+        self.in_features, self.out_features, self.rank = in_features, out_features, rank
+        self.register_buffer("alpha", torch.tensor(float(alpha)))
+        self.multiplier = float(multiplier)
+        self.dropout, self.rank_dropout, self.module_dropout = dropout, rank_dropout, module_dropout
+        self._alpha = float(alpha)
+        self.dora_scale: nn.Parameter | None = None
+        self.dora_on_output = True
+
+    # ---- scale -----------------------------------------------------------------------
+    @property
+    def base_scale(self) -> float:
+        return self._alpha / self.rank if self.rank else 1.0
+
+    @property
+    def scale(self) -> float:
+        return self.base_scale * self.multiplier
+
+    # ---- DoRA ------------------------------------------------------------------------
+    def enable_dora(self, base_weight: Tensor, on_output: bool = True) -> None:
+        """Weight-decomposed adaptation: magnitude initialised to the norm of the base
+        weight (per output row when `on_output`, per input column otherwise)."""
+        self.dora_on_output = on_output
+        w = base_weight.detach().float()
+        norm = w.norm(dim=1, keepdim=True) if on_output else w.norm(dim=0, keepdim=True)
+        self.dora_scale = nn.Parameter(norm.to(base_weight.device))
+        self.fusable = False
+
+    def _decompose(self, w: Tensor) -> Tensor:
+        dim = 1 if self.dora_on_output else 0
+        norm = w.norm(dim=dim, keepdim=True) + torch.finfo(w.dtype).eps
+        return w * (self.dora_scale.to(w.dtype) / norm)
+
+    # ---- interface -------------------------------------------------------------------
+    def delta(self, base: Tensor | None = None) -> Tensor:
+        raise NotImplementedError
+
+    def merged(self, w: Tensor) -> Tensor:
+        wf = w.float()
+        new = wf + self.delta(wf) * self.scale
+        if self.dora_scale is not None:
+            new = wf + self.multiplier * (self._decompose(wf + self.delta(wf) * self.base_scale) - wf)
+        return new.to(w.dtype)
+
+    def _skip(self) -> bool:
+        return self.training and self.module_dropout > 0 and torch.rand(()) < self.module_dropout
+
+    def bypass(self, x: Tensor, y: Tensor, lin) -> Tensor:
+        """Generic bypass through the dense delta (kinds with structure override this)."""
+        if self._skip():
+            return y
+        if self.dora_scale is not None:
+            w = lin.base_weight(torch.float32)
+            bias = None if lin.bias is None else lin.bias.to(x.dtype)
+            return F.linear(x, self.merged(w).to(x.dtype), bias)
+        return y + F.linear(x, (self.delta(None) * self.scale).to(x.dtype))
+
+    def state(self) -> dict[str, Tensor]:
+        out = {k: v for k, v in self.state_dict().items()}
+        return out
+
+
+class LoRAModule(AdapterModule):
+    """LoRA / LoCon on a linear: dW = up @ down * alpha / r."""
+
+    algo = "lora"
+
+    def __init__(self, in_features, out_features, rank, alpha, **kw):
+        super().__init__(in_features, out_features, rank, alpha, **kw)
+        self.lora_down = nn.Linear(in_features, rank, bias=False)
+        self.lora_up = nn.Linear(rank, out_features, bias=False)
+        nn.init.kaiming_uniform_(self.lora_down.weight, a=math.sqrt(5))
+        nn.init.zeros_(self.lora_up.weight)
+        self.fusable = self.dropout == 0 and self.rank_dropout == 0 and self.module_dropout == 0
+
+    def down_weight(self) -> Tensor:
+        return self.lora_down.weight
+
+    def up_weight(self) -> Tensor:
+        return self.lora_up.weight
+
+    def delta(self, base=None) -> Tensor:
+        return self.lora_up.weight.float() @ self.lora_down.weight.float()
+
+    def bypass(self, x, y, lin):
+        if self.dora_scale is not None:
+            return super().bypass(x, y, lin)
+        if self._skip():
+            return y
+        h = x
+        if self.training and self.dropout > 0:
+            h = F.dropout(h, self.dropout)
+        t = F.linear(h, self.lora_down.weight.to(x.dtype))
+        scale = self.scale
+        if self.training and self.rank_dropout > 0:
+            keep = (torch.rand(self.rank, device=x.device) > self.rank_dropout).to(t.dtype)
+            t = t * keep
+            scale = scale / max(1e-6, 1.0 - self.rank_dropout)
+        return y + F.linear(t, self.lora_up.weight.to(x.dtype)) * scale
+
+
+class LoHaModule(AdapterModule):
+    """LoHa: dW = (w1_a @ w1_b) * (w2_a @ w2_b) * alpha / r (Hadamard product)."""
+
+    algo = "loha"
+
+    def __init__(self, in_features, out_features, rank, alpha, **kw):
+        super().__init__(in_features, out_features, rank, alpha, **kw)
+        self.hada_w1_a = nn.Parameter(torch.empty(out_features, rank))
+        self.hada_w1_b = nn.Parameter(torch.empty(rank, in_features))
+        self.hada_w2_a = nn.Parameter(torch.empty(out_features, rank))
+        self.hada_w2_b = nn.Parameter(torch.empty(rank, in_features))
+        nn.init.normal_(self.hada_w1_b, std=1.0)
+        nn.init.normal_(self.hada_w1_a, std=0.1)
+        nn.init.normal_(self.hada_w2_b, std=1.0)
+        nn.init.zeros_(self.hada_w2_a)
+
+    def delta(self, base=None) -> Tensor:
+        return (self.hada_w1_a.float() @ self.hada_w1_b.float()) * (self.hada_w2_a.float() @ self.hada_w2_b.float())
+
+
+class LoKrModule(AdapterModule):
+    """LoKr: dW = kron(w1, w2) * scale with w1 [out_l, in_m], w2 [out_k, in_n];
+    each factor full or low-rank (`*_a @ *_b`)."""
+
+    algo = "lokr"
+
+    def __init__(self, in_features, out_features, rank, alpha, factor: int = -1, decompose_both: bool = False,
+                 full_matrix: bool = False, **kw):
+        super().__init__(in_features, out_features, rank, alpha, **kw)
+        in_m, in_n = _factorization(in_features, factor)
+        out_l, out_k = _factorization(out_features, factor)
+        self.shape = ((out_l, out_k), (in_m, in_n))
+        self.use_w1 = not (decompose_both and rank < max(out_l, in_m) / 2 and not full_matrix)
+        self.use_w2 = full_matrix or not (rank < max(out_k, in_n) / 2)
+        if self.use_w1:
+            self.lokr_w1 = nn.Parameter(torch.empty(out_l, in_m))
+            nn.init.kaiming_uniform_(self.lokr_w1, a=math.sqrt(5))
+        else:
+            self.lokr_w1_a = nn.Parameter(torch.empty(out_l, rank))
+            self.lokr_w1_b = nn.Parameter(torch.empty(rank, in_m))
+            nn.init.kaiming_uniform_(self.lokr_w1_a, a=math.sqrt(5))
+            nn.init.kaiming_uniform_(self.lokr_w1_b, a=math.sqrt(5))
+        if self.use_w2:
+            self.lokr_w2 = nn.Parameter(torch.zeros(out_k, in_n))
+        else:
+            self.lokr_w2_a = nn.Parameter(torch.empty(out_k, rank))
+            self.lokr_w2_b = nn.Parameter(torch.zeros(rank, in_n))
+            nn.init.kaiming_uniform_(self.lokr_w2_a, a=math.sqrt(5))
+        if self.use_w1 and self.use_w2:
+            # both factors dense: LyCORIS stores alpha = rank so the scale is 1
+            self._alpha = float(rank)
+            self.alpha.fill_(float(rank))
+
+    def w1(self) -> Tensor:
+        return self.lokr_w1.float() if self.use_w1 else self.lokr_w1_a.float() @ self.lokr_w1_b.float()
+
+    def w2(self) -> Tensor:
+        return self.lokr_w2.float() if self.use_w2 else self.lokr_w2_a.float() @ self.lokr_w2_b.float()
+
+    def delta(self, base=None) -> Tensor:
+        return torch.kron(self.w1(), self.w2())
+
+    def bypass(self, x, y, lin):
+        """kron(w1, w2) x = w1 X w2^T on x reshaped [.., in_m, in_n]: two small products
+        instead of a dense [out, in] delta."""
+        if self.dora_scale is not None or self._skip():
+            return super().bypass(x, y, lin)
+        (out_l, out_k), (in_m, in_n) = self.shape
+        xr = x.reshape(*x.shape[:-1], in_m, in_n)
+        h = torch.matmul(xr, self.w2().to(x.dtype).t())  # [.., in_m, out_k]
+        h = torch.matmul(self.w1().to(x.dtype), h)  # [.., out_l, out_k]
+        return y + h.reshape(*x.shape[:-1], out_l * out_k) * self.scale
+
+
+class OFTModule(AdapterModule):
+    """Orthogonal finetuning: W' = blockdiag(R_i) W with R = (I + Q)(I - Q)^-1, Q = B - B^T;
+    `constraint` (saved as alpha) bounds ||Q||; `rescale` is an optional learned per-row gain."""
+
+    algo = "oft"
+
+    def __init__(self, in_features, out_features, rank, alpha=0.0, rescaled: bool = False, **kw):
+        block = rank
+        while out_features % block:
+            block -= 1
+        n = out_features // block
+        super().__init__(in_features, out_features, block, alpha, **kw)
+        self.block_size, self.n_blocks = block, n
+        self.constraint = float(alpha) * out_features
+        self.oft_blocks = nn.Parameter(torch.zeros(n, block, block))
+        self.rescale = nn.Parameter(torch.ones(out_features, 1)) if rescaled else None
+
+    @property
+    def scale(self) -> float:
+        return self.multiplier
+
+    def rotation(self, multiplier: float = 1.0) -> Tensor:
+        b = self.oft_blocks.float()
+        q = b - b.transpose(1, 2)
+        if self.constraint > 0:
+            norm = q.norm() + 1e-8
+            if norm > self.constraint:
+                q = q * (self.constraint / norm)
+        eye = torch.eye(self.block_size, device=q.device).expand_as(q)
+        r = (eye + q) @ torch.linalg.inv(eye - q)
+        if multiplier != 1.0:
+            r = r * multiplier + eye * (1.0 - multiplier)
+        return r
+
+    def merged(self, w: Tensor) -> Tensor:
+        wf = w.float()
+        r = self.rotation(self.multiplier)
+        new = torch.einsum("nij,njk->nik", r, wf.reshape(self.n_blocks, self.block_size, -1)).reshape_as(wf)
+        if self.rescale is not None:
+            new = new * self.rescale.float()
+        return new.to(w.dtype)
+
+    def delta(self, base=None) -> Tensor:
+        if base is None:
+            raise ValueError("OFT needs the base weight to express itself as a delta")
+        return self.merged(base).float() - base.float()
+
+    def bypass(self, x, y, lin):
+        """Rotate the base OUTPUT: (R W) x = R (W x); bias is added after the rotation."""
+        if self._skip():
+            return y
+        bias = None if lin.bias is None else lin.bias.to(y.dtype)
+        core = y if bias is None else y - bias
+        r = self.rotation(self.multiplier).to(y.dtype)
+        out = torch.einsum("nij,...nj->...ni", r, core.reshape(*core.shape[:-1], self.n_blocks, self.block_size))
+        out = out.reshape_as(core)
+        if self.rescale is not None:
+            out = out * self.rescale.to(y.dtype).squeeze(-1)
+        return out if bias is None else out + bias
+
+
+class IA3Module(AdapterModule):
+    """(IA)^3: a learned per-channel gain on the input (`on_input`) or the output."""
+
+    algo = "ia3"
+
+    def __init__(self, in_features, out_features, rank=1, alpha=1.0, on_input: bool = False, **kw):
+        super().__init__(in_features, out_features, 1, 1.0, **kw)
+        self.register_buffer("on_input", torch.tensor(bool(on_input)))
+        self._on_input = bool(on_input)
+        self.weight = nn.Parameter(torch.zeros(in_features if on_input else out_features))
+
+    def delta(self, base=None) -> Tensor:
+        if base is None:
+            raise ValueError("IA3 needs the base weight to express itself as a delta")
+        g = self.weight.float()
+        return base.float() * (g[None, :] if self._on_input else g[:, None])
+
+    def merged(self, w):
+        return (w.float() + self.multiplier * self.delta(w.float())).to(w.dtype)
+
+    def bypass(self, x, y, lin):
+        if self._on_input:
+            return y + self.multiplier * F.linear(x * self.weight.to(x.dtype), lin.base_weight(x.dtype))
+        bias = None if lin.bias is None else lin.bias.to(y.dtype)
+        core = y if bias is None else y - bias
+        return y + self.multiplier * core * self.weight.to(y.dtype)
+
+
+class DiffModule(AdapterModule):
+    """Dense difference ("full" algo on a single layer): stores `diff` (and `diff_b`)."""
+
+    algo = "full"
+
+    def __init__(self, in_features, out_features, rank=1, alpha=1.0, bias: bool = False, **kw):
+        super().__init__(in_features, out_features, 1, 1.0, **kw)
+        self.diff = nn.Parameter(torch.zeros(out_features, in_features))
+        self.diff_b = nn.Parameter(torch.zeros(out_features)) if bias else None
+
+    def delta(self, base=None):
+        return self.diff.float()
+
+    def bypass(self, x, y, lin):
+        out = y + F.linear(x, self.diff.to(x.dtype)) * self.multiplier
+        if self.diff_b is not None:
+            out = out + self.diff_b.to(x.dtype) * self.multiplier
+        return out
+
+
+MODULES: dict[str, type[AdapterModule]] = {
+    "lora": LoRAModule,
+    "locon": LoRAModule,
+    "loha": LoHaModule,
+    "lokr": LoKrModule,
+    "oft": OFTModule,
+    "ia3": IA3Module,
+    "full": DiffModule,
+    "diff": DiffModule,
+}

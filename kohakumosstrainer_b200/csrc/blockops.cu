@@ -213,42 +213,37 @@ __global__ void rope_table_kernel(const float* pos, const float* bands, float* t
 }
 
 // Per-head RMSNorm + split-half rotation on [N, H, 128]; one warp per (token, head).
-// Lane l holds pairs (4l .. 4l+3, 64 + 4l .. 64 + 4l + 3).
+// Lane l holds the pairs (2l, 64 + 2l) and (2l + 1, 64 + 2l + 1).
+__device__ __forceinline__ float load_w(const void* w, int is_f32, int i) {
+  return is_f32 ? reinterpret_cast<const float*>(w)[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[i]);
+}
+
 __global__ void __launch_bounds__(128) qk_norm_rope_fwd_kernel(QkRopeArgs a) {
   const long wid = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (wid >= (long)a.rows * a.heads) return;
   const int row = (int)(wid / a.heads), head = (int)(wid - (long)row * a.heads);
   const __nv_bfloat16* x = a.x + (size_t)row * a.ldx + head * 128;
-  uint2 wa = *reinterpret_cast<const uint2*>(x + 4 * lane);
-  uint2 wb = *reinterpret_cast<const uint2*>(x + 64 + 4 * lane);
-  float va[4], vb[4];
-  { float2 t = unpack_bf16(wa.x), u = unpack_bf16(wa.y); va[0] = t.x; va[1] = t.y; va[2] = u.x; va[3] = u.y; }
-  { float2 t = unpack_bf16(wb.x), u = unpack_bf16(wb.y); vb[0] = t.x; vb[1] = t.y; vb[2] = u.x; vb[3] = u.y; }
-  float ss = 0.f;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) ss += va[j] * va[j] + vb[j] * vb[j];
+  const float2 va = unpack_bf16(*reinterpret_cast<const uint32_t*>(x + 2 * lane));
+  const float2 vb = unpack_bf16(*reinterpret_cast<const uint32_t*>(x + 64 + 2 * lane));
+  float ss = va.x * va.x + va.y * va.y + vb.x * vb.x + vb.y * vb.y;
   ss = warp_sum(ss);
   const float rstd = rsqrtf(ss * (1.f / 128.f) + a.eps);
   if (lane == 0 && a.rstd != nullptr) a.rstd[(size_t)row * a.heads + head] = rstd;
   const float* cs = a.rope + (size_t)row * 128;
-  float oa[4], ob[4];
+  const float xa[2] = {va.x, va.y}, xb[2] = {vb.x, vb.y};
+  float oa[2], ob[2];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int ia = 4 * lane + j, ib = 64 + ia;
-    const float w_a = a.w_f32 ? reinterpret_cast<const float*>(a.w)[ia] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.w)[ia]);
-    const float w_b = a.w_f32 ? reinterpret_cast<const float*>(a.w)[ib] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.w)[ib]);
-    const float p = va[j] * rstd * w_a, q = vb[j] * rstd * w_b;
+  for (int j = 0; j < 2; ++j) {
+    const int ia = 2 * lane + j, ib = 64 + ia;
+    const float p = xa[j] * rstd * load_w(a.w, a.w_f32, ia), q = xb[j] * rstd * load_w(a.w, a.w_f32, ib);
     const float c = cs[ia], s = cs[64 + ia];
     oa[j] = p * c - q * s;
     ob[j] = q * c + p * s;
   }
   __nv_bfloat16* y = a.y + (size_t)row * a.ldy + head * 128;
-  uint2 o;
-  o.x = pack_bf16(oa[0], oa[1]); o.y = pack_bf16(oa[2], oa[3]);
-  *reinterpret_cast<uint2*>(y + 4 * lane) = o;
-  o.x = pack_bf16(ob[0], ob[1]); o.y = pack_bf16(ob[2], ob[3]);
-  *reinterpret_cast<uint2*>(y + 64 + 4 * lane) = o;
+  *reinterpret_cast<uint32_t*>(y + 2 * lane) = pack_bf16(oa[0], oa[1]);
+  *reinterpret_cast<uint32_t*>(y + 64 + 2 * lane) = pack_bf16(ob[0], ob[1]);
 }
 
 // Backward of the above from the OUTPUT y (the fused forward never stores the
@@ -263,25 +258,22 @@ __global__ void __launch_bounds__(128) qk_norm_rope_bwd_kernel(QkRopeBwdArgs a) 
   const __nv_bfloat16* dy = a.dy + (size_t)row * a.lddy + head * 128;
   const float* cs = a.rope + (size_t)row * 128;
   const float rstd = a.rstd[(size_t)row * a.heads + head];
-  uint2 ya = *reinterpret_cast<const uint2*>(y + 4 * lane), yb = *reinterpret_cast<const uint2*>(y + 64 + 4 * lane);
-  uint2 ga = *reinterpret_cast<const uint2*>(dy + 4 * lane), gb = *reinterpret_cast<const uint2*>(dy + 64 + 4 * lane);
-  float y_a[4], y_b[4], g_a[4], g_b[4];
-  { float2 t = unpack_bf16(ya.x), u = unpack_bf16(ya.y); y_a[0] = t.x; y_a[1] = t.y; y_a[2] = u.x; y_a[3] = u.y; }
-  { float2 t = unpack_bf16(yb.x), u = unpack_bf16(yb.y); y_b[0] = t.x; y_b[1] = t.y; y_b[2] = u.x; y_b[3] = u.y; }
-  { float2 t = unpack_bf16(ga.x), u = unpack_bf16(ga.y); g_a[0] = t.x; g_a[1] = t.y; g_a[2] = u.x; g_a[3] = u.y; }
-  { float2 t = unpack_bf16(gb.x), u = unpack_bf16(gb.y); g_b[0] = t.x; g_b[1] = t.y; g_b[2] = u.x; g_b[3] = u.y; }
-  float xh_a[4], xh_b[4], gw_a[4], gw_b[4], gz_a[4], gz_b[4];
+  const float2 ya = unpack_bf16(*reinterpret_cast<const uint32_t*>(y + 2 * lane));
+  const float2 yb = unpack_bf16(*reinterpret_cast<const uint32_t*>(y + 64 + 2 * lane));
+  const float2 ga = unpack_bf16(*reinterpret_cast<const uint32_t*>(dy + 2 * lane));
+  const float2 gb = unpack_bf16(*reinterpret_cast<const uint32_t*>(dy + 64 + 2 * lane));
+  const float y_a[2] = {ya.x, ya.y}, y_b[2] = {yb.x, yb.y}, g_a[2] = {ga.x, ga.y}, g_b[2] = {gb.x, gb.y};
+  float xh_a[2], xh_b[2], gw_a[2], gw_b[2], gz_a[2], gz_b[2];
   float dot = 0.f;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int ia = 4 * lane + j, ib = 64 + ia;
+  for (int j = 0; j < 2; ++j) {
+    const int ia = 2 * lane + j, ib = 64 + ia;
     const float c = cs[ia], s = cs[64 + ia];
     // inverse rotation (transpose of the forward rotation)
     const float za = y_a[j] * c + y_b[j] * s, zb = y_b[j] * c - y_a[j] * s;
     gz_a[j] = g_a[j] * c + g_b[j] * s;
     gz_b[j] = g_b[j] * c - g_a[j] * s;
-    const float w_a = a.w_f32 ? reinterpret_cast<const float*>(a.w)[ia] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.w)[ia]);
-    const float w_b = a.w_f32 ? reinterpret_cast<const float*>(a.w)[ib] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.w)[ib]);
+    const float w_a = load_w(a.w, a.w_f32, ia), w_b = load_w(a.w, a.w_f32, ib);
     xh_a[j] = fabsf(w_a) > 1e-12f ? za / w_a : 0.f;
     xh_b[j] = fabsf(w_b) > 1e-12f ? zb / w_b : 0.f;
     gw_a[j] = gz_a[j] * w_a;
@@ -289,25 +281,22 @@ __global__ void __launch_bounds__(128) qk_norm_rope_bwd_kernel(QkRopeBwdArgs a) 
     dot += gw_a[j] * xh_a[j] + gw_b[j] * xh_b[j];
   }
   dot = warp_sum(dot) * (1.f / 128.f);
-  float da[4], db[4];
+  float da[2], db[2];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+  for (int j = 0; j < 2; ++j) {
     da[j] = rstd * (gw_a[j] - xh_a[j] * dot);
     db[j] = rstd * (gw_b[j] - xh_b[j] * dot);
   }
   __nv_bfloat16* dx = a.dx + (size_t)row * a.lddx + head * 128;
-  uint2 o;
-  o.x = pack_bf16(da[0], da[1]); o.y = pack_bf16(da[2], da[3]);
-  *reinterpret_cast<uint2*>(dx + 4 * lane) = o;
-  o.x = pack_bf16(db[0], db[1]); o.y = pack_bf16(db[2], db[3]);
-  *reinterpret_cast<uint2*>(dx + 64 + 4 * lane) = o;
+  *reinterpret_cast<uint32_t*>(dx + 2 * lane) = pack_bf16(da[0], da[1]);
+  *reinterpret_cast<uint32_t*>(dx + 64 + 2 * lane) = pack_bf16(db[0], db[1]);
   if (a.dw_rows != nullptr) {
     // per-(row, head) contribution to d weight, reduced over rows and heads by the caller
     float* dw = a.dw_rows + ((size_t)row * a.heads + head) * 128;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      dw[4 * lane + j] = gz_a[j] * xh_a[j];
-      dw[64 + 4 * lane + j] = gz_b[j] * xh_b[j];
+    for (int j = 0; j < 2; ++j) {
+      dw[2 * lane + j] = gz_a[j] * xh_a[j];
+      dw[64 + 2 * lane + j] = gz_b[j] * xh_b[j];
     }
   }
 }

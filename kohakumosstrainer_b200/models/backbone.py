@@ -64,6 +64,9 @@ class MossBackbone(nn.Module):
         if ops is None:
             ops = resolve_ops(self.video_embedder.weight_like.device)
         self.ops = ops
+        for module in self.modules():
+            if isinstance(module, MossLinear):
+                module.__dict__["native"] = ops.name == "native"
         self.text_embedder.bind(ops)
         for block in self.layers:
             block.bind(ops)

@@ -28,6 +28,7 @@ class MossLinear(nn.Linear):
         self.__dict__["compute"] = None
         self.__dict__["adapter"] = None
         self.__dict__["adapter_mode"] = "bypass"
+        self.__dict__["native"] = True
 
     def reset_parameters(self) -> None:  # weights come from the builder or a checkpoint
         pass
@@ -91,10 +92,10 @@ class MossLinear(nn.Linear):
         return w
 
     def forward(self, x: Tensor) -> Tensor:
-        if x.is_cuda:
-            from ..ops import native
+        if x.is_cuda and self.native:
+            from ..ops import native_ops
 
-            return native.fused_linear(self, x)
+            return native_ops.fused_linear(self, x)
         return self.forward_eager(x)
 
     def forward_eager(self, x: Tensor) -> Tensor:

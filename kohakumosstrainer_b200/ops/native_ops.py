@@ -1,0 +1,670 @@
+"""The sm_100a op set: autograd-aware layer ops built on the tcgen05 GEMM and block kernels.
+
+A joint block runs as a short chain of fused launches:
+
+    norm+modulation (+amax)  ->  [fp8 cast]  ->  qkv GEMM (+LoRA bypass, qk-norm+RoPE epilogue)
+    ->  varlen attention  ->  o GEMM (+bypass, gate * . + r * x epilogue)
+    ->  norm+modulation  ->  up|gate GEMM (+bypass, SiTU epilogue)  ->  down GEMM (+bypass, gated residual)
+
+Forward, dgrad and wgrad all go through the same GEMM family: the stored `[out, in]` weight is
+the K-major B operand of the forward product and the MN-major B operand of dgrad, so no
+transposed weight copy exists. Adapter (LoRA) factors ride as a low-rank bypass inside the
+base GEMM's accumulator. The reference composes these ops from Triton kernels plus cuBLAS
+(`src/kohakumoss/model/opset.py:94-124`, `src/kohakumoss_kernels/backends/_fused_linear.py`).
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from . import eager, native
+from .native import EPI_LINEAR, EPI_QK_ROPE, EPI_SITU
+from .opset import OpSet
+
+BF16 = torch.bfloat16
+E4M3 = torch.float8_e4m3fn
+E5M2 = torch.float8_e5m2
+MIN_ROWS = 1  # products with fewer rows than this go through the library (conditioning MLPs)
+
+
+# ----------------------------------------------------------------------------------------
+# helpers
+# ----------------------------------------------------------------------------------------
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+class WeightPack:
+    """How a layer's base weight enters the GEMM: the stored tensor plus its scales.
+
+    kind "bf16": `w` bf16 [out, in]. kind "fp8": `w` e4m3 [out, in], `scale` (tensor [2] =
+    {dequant, quant}) for a per-tensor recipe, `col_scale` fp32 [out] always (constant for a
+    per-tensor recipe, per-row for the row recipe, piecewise for fused q|k|v)."""
+
+    __slots__ = ("kind", "w", "scale", "col_scale", "per_tensor", "trainable", "params")
+
+    def __init__(self, kind, w, scale=None, col_scale=None, per_tensor=True, trainable=False, params=()):
+        self.kind, self.w, self.scale, self.col_scale = kind, w, scale, col_scale
+        self.per_tensor, self.trainable, self.params = per_tensor, trainable, tuple(params)
+
+    @property
+    def out_features(self) -> int:
+        return self.w.shape[0]
+
+
+class LoraPack:
+    """Concatenated low-rank factors of the adapters riding one GEMM.
+
+    `down` [R, in] (rows of every adapter stacked), `up` [out, R] (block layout: adapter j
+    fills its output range x its rank columns). `plain_scale` fp32 [R] holds each adapter's
+    scale alpha/r * multiplier; `t_scale` is the same divided by the weight's dequant scale
+    when the base is fp8 (the bypass shares the accumulator the epilogue rescales)."""
+
+    def __init__(self, down, up, plain_scale, t_scale, parts):
+        self.down, self.up, self.plain_scale, self.t_scale, self.parts = down, up, plain_scale, t_scale, parts
+        self.ratio = plain_scale / t_scale  # = weight dequant scale per column under fp8, else 1
+        self.R = down.shape[0]
+
+
+def _main_gemm(x, xq, xs, wp: WeightPack, **kw) -> Tensor:
+    if wp.kind == "fp8":
+        return native.gemm(xq, wp.w, scale_a=xs[:1], col_scale=wp.col_scale, **kw)
+    return native.gemm(x, wp.w, **kw)
+
+
+class _LinearCore:
+    """Forward / backward of `out = epilogue(x W^T + bias + sum_j s_j (x down_j^T) up_j^T)`.
+
+    With T = (x down^T) * s the adapter term is T up^T: one skinny GEMM for T, then T and `up`
+    enter the base GEMM as its bypass operands. Under an fp8 base the accumulator holds
+    quantised units that the epilogue multiplies by s_x * s_w, so T is pre-divided by the same
+    two (device) scalars in the epilogue of the skinny GEMM; nothing extra is launched."""
+
+    @staticmethod
+    def forward(x, wp: WeightPack, bias, lp: LoraPack | None, **epi):
+        xq = xs = None
+        if wp.kind == "fp8":
+            xq, xs = native.quantize_fp8(x, E4M3)
+        t = None
+        if lp is not None:
+            t = native.gemm(x, lp.down, col_scale=lp.t_scale, scale_a=None if xs is None else xs[1:2])
+        out = _main_gemm(x, xq, xs, wp, bias=bias, t=t, u=None if lp is None else lp.up, **epi)
+        return out, t, xs
+
+    @staticmethod
+    def backward(d, x, wp: WeightPack, lp: LoraPack | None, t, xs, need_dx=True, need_bias=False):
+        """`d`: gradient w.r.t. the pre-epilogue linear output, bf16 [M, out].
+        Returns (dx, d_down [R, in], d_up [out, R], dW, dbias)."""
+        dx = d_down = d_up = dW = dbias = None
+        fp8 = wp.kind == "fp8"
+        dq = ds = None
+        if fp8 and need_dx:
+            if not wp.per_tensor:
+                d_main = (d.float() * wp.col_scale).to(BF16)  # row recipe: scale varies along K
+                dq, ds = native.quantize_fp8(d_main, E5M2)
+            else:
+                dq, ds = native.quantize_fp8(d, E5M2)
+        if lp is not None:
+            # t2 = (d up) * s: gradient w.r.t. the rank activations, [M, R]
+            t2 = native.gemm(d, lp.up, b_mn=True, col_scale=lp.plain_scale)
+            # d up = d^T T_plain, where T_plain = t * (s_x * s_w) under fp8
+            if fp8:
+                d_up = native.gemm(d, t, a_mn=True, b_mn=True, out_dtype=torch.float32, splits=None,
+                                   scale_a=xs[:1], col_scale=lp.ratio)
+            else:
+                d_up = native.gemm(d, t, a_mn=True, b_mn=True, out_dtype=torch.float32, splits=None)
+            # d down^T [in, R] = x^T t2
+            d_down = native.gemm(x, t2, a_mn=True, b_mn=True, out_dtype=torch.float32, splits=None).t()
+        if need_dx:
+            tb = ub = None
+            if lp is not None:
+                ub = lp.down.t().contiguous()  # [in, R]: the bypass B operand of dgrad
+                tb = t2
+            if fp8:
+                sb = wp.scale[:1] if wp.per_tensor else None
+                if lp is not None:
+                    # keep the bypass out of the fp8 rescale: divide it by s_d (* s_w)
+                    tb = native.gemm(d, lp.up, b_mn=True, col_scale=lp.plain_scale, scale_a=ds[1:2],
+                                     scale_b=None if sb is None else wp.scale[1:2])
+                dx = native.gemm(dq, wp.w, b_mn=True, scale_a=ds[:1], scale_b=sb, t=tb, u=ub)
+            else:
+                dx = native.gemm(d, wp.w, b_mn=True, t=tb, u=ub)
+        if wp.trainable:
+            dW = native.gemm(d, x, a_mn=True, b_mn=True, out_dtype=torch.float32)
+        if need_bias:
+            dbias = d.float().sum(0)
+        return dx, d_down, d_up, dW, dbias
+
+
+# ----------------------------------------------------------------------------------------
+# block ops with autograd
+# ----------------------------------------------------------------------------------------
+class RmsNormModFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, shift, scale, seg, eps, cu):
+        ops = native.load()
+        y = torch.empty_like(x)
+        rstd = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
+        ops.rms_norm_mod_fwd(x, w, shift, scale, seg, eps, y, rstd, None, None, None)
+        ctx.save_for_backward(x, w, shift, scale, seg, rstd, cu)
+        ctx.eps = eps
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        ops = native.load()
+        x, w, shift, scale, seg, rstd, cu = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = dw = dshift = dscale = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            ops.rms_norm_mod_bwd(dy, x, w, scale, seg, rstd, dx, None, 0.0)
+        if w is not None and ctx.needs_input_grad[1]:
+            dw = ops.norm_weight_grad(dy, x, scale, seg, rstd).to(w.dtype)
+        if shift is not None and ctx.needs_input_grad[2]:
+            dshift = ops.seg_sum(dy, None, None, None, cu, 0)
+        if scale is not None and ctx.needs_input_grad[3]:
+            dscale = ops.seg_sum(dy, x, w, rstd, cu, 1)
+        return dx, dw, dshift, dscale, None, None, None
+
+
+def _cu_of(seg: Tensor | None, n_segments: int | None = None) -> Tensor | None:
+    """Row offsets of sorted segments, cached on the seg tensor."""
+    if seg is None:
+        return None
+    cached = getattr(seg, "_kmoss_cu", None)
+    if cached is None:
+        counts = torch.bincount(seg.long(), minlength=n_segments or 0)
+        cached = torch.zeros(counts.numel() + 1, dtype=torch.int32, device=seg.device)
+        cached[1:] = counts.cumsum(0)
+        try:
+            seg._kmoss_cu = cached
+        except AttributeError:
+            pass
+    return cached
+
+
+def rms_norm_mod(x, weight, shift, scale, seg, eps):
+    if x.dtype != BF16:
+        return eager.rms_norm_mod(x, weight, shift, scale, seg, eps)
+    needs_cu = (shift is not None and shift.requires_grad) or (scale is not None and scale.requires_grad)
+    cu = _cu_of(seg, None if shift is None else shift.shape[0]) if needs_cu else None
+    return RmsNormModFn.apply(x.contiguous(), weight, shift, scale, seg, eps, cu)
+
+
+def rms_norm(x, weight, eps):
+    if x.dtype != BF16:
+        return eager.rms_norm(x, weight, eps)
+    return RmsNormModFn.apply(x.contiguous(), weight, None, None, None, eps, None)
+
+
+class QkNormRopeFn(torch.autograd.Function):
+    """Standalone per-head RMSNorm + RoPE on one of q / k, [N, H*128] rows (text refiner)."""
+
+    @staticmethod
+    def forward(ctx, x, w, table, eps, heads):
+        ops = native.load()
+        y = torch.empty(x.shape[0], heads * 128, dtype=x.dtype, device=x.device)
+        rstd = torch.empty(x.shape[0], heads, dtype=torch.float32, device=x.device)
+        ops.qk_norm_rope_fwd(x, w, table, eps, y, rstd, heads)
+        ctx.save_for_backward(y, w, table, rstd)
+        ctx.heads = heads
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        ops = native.load()
+        y, w, table, rstd = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = torch.empty_like(y)
+        dw_rows = None
+        if ctx.needs_input_grad[1]:
+            dw_rows = torch.empty(y.shape[0], ctx.heads, 128, dtype=torch.float32, device=y.device)
+        ops.qk_norm_rope_bwd(y, dy, w, table, rstd, dx, dw_rows, ctx.heads)
+        dw = None if dw_rows is None else dw_rows.sum((0, 1)).to(w.dtype)
+        return dx, dw, None, None, None
+
+
+def _table(pos: Tensor, bands: Tensor) -> Tensor:
+    cached = getattr(pos, "_kmoss_rope", None)
+    if cached is None:
+        cached = native.rope_table(pos, bands)
+        try:
+            pos._kmoss_rope = cached
+        except AttributeError:
+            pass
+    return cached
+
+
+def qk_norm_rope(q, k, q_weight, k_weight, pos, bands, eps):
+    if q.dtype != BF16 or q.shape[-1] != 128:
+        return eager.qk_norm_rope(q, k, q_weight, k_weight, pos, bands, eps)
+    heads = q.shape[1]
+    table = _table(pos, bands)
+
+    def one(x, w):
+        x2 = x.flatten(1)
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        return QkNormRopeFn.apply(x2, w, table, eps, heads).unflatten(1, (heads, 128))
+
+    return one(q, q_weight), one(k, k_weight)
+
+
+class SituFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, up, gate):
+        out = torch.empty(up.shape, dtype=up.dtype, device=up.device)
+        native.load().situ_fwd(up, gate, out)
+        ctx.save_for_backward(up, gate)
+        return out
+
+    @staticmethod
+    def backward(ctx, da):
+        up, gate = ctx.saved_tensors
+        d = torch.empty(up.shape[0], 2 * up.shape[1], dtype=up.dtype, device=up.device)
+        f = up.shape[1]
+        native.load().situ_bwd(da.contiguous(), up, gate, d[:, :f], d[:, f:])
+        return d[:, :f], d[:, f:]
+
+
+def situ_glu(x):
+    if x.dtype != BF16 or x.shape[-1] % 16:
+        return eager.situ_glu(x)
+    f = x.shape[-1] // 2
+    return SituFn.apply(x[:, :f], x[:, f:])
+
+
+def situ_pair(u, g):
+    if u.dtype != BF16 or u.shape[-1] % 8:
+        return eager.situ_pair(u, g)
+    if u.stride(0) != g.stride(0):
+        u, g = u.contiguous(), g.contiguous()
+    return SituFn.apply(u, g)
+
+
+class GatedResidualFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, o, gate, seg, r, cu):
+        out = torch.empty_like(x)
+        native.load().gated_residual(x, o, gate, seg, r, out)
+        ctx.save_for_backward(o, gate, seg, cu)
+        ctx.r = r
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        ops = native.load()
+        o, gate, seg, cu = ctx.saved_tensors
+        dout = dout.contiguous()
+        dx = dout if ctx.r == 1.0 else dout * ctx.r
+        if gate is None:
+            return dx, dout, None, None, None, None
+        do = torch.empty_like(o)
+        ops.seg_scale(dout, gate, seg, do)
+        dgate = None
+        if ctx.needs_input_grad[2]:
+            dgate = ops.seg_sum(dout, o, None, None, cu, 2)
+        return dx, do, dgate, None, None, None
+
+
+def gated_residual(x, o, gate, seg, r=1.0):
+    if x.dtype != BF16 or x.shape[-1] % 8:
+        return eager.gated_residual(x, o, gate, seg, r)
+    cu = _cu_of(seg, gate.shape[0]) if gate is not None and gate.requires_grad else None
+    return GatedResidualFn.apply(x.contiguous(), o.contiguous(), gate, seg, r, cu)
+
+
+class TokenMseFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, pred, target, seg, weight, mask):
+        ctx.save_for_backward(pred, target, seg, weight, mask)
+        return native.load().token_mse_fwd(pred, target, seg, weight, mask)
+
+    @staticmethod
+    def backward(ctx, dloss):
+        pred, target, seg, weight, mask = ctx.saved_tensors
+        return native.load().token_mse_bwd(dloss, pred, target, seg, weight, mask), None, None, None, None
+
+
+def token_mse(pred, target, seg, weight, mask=None):
+    if pred.dtype not in (BF16, torch.float32):
+        return eager.token_mse(pred, target, seg, weight, mask)
+    return TokenMseFn.apply(pred.contiguous(), target.float().contiguous(), seg, weight.float(), None if mask is None else mask.float())
+
+
+# ----------------------------------------------------------------------------------------
+# layer packs: how a MossLinear (or a fused group of them) enters the GEMM
+# ----------------------------------------------------------------------------------------
+def weight_pack(lins) -> WeightPack:
+    """WeightPack of one linear or of several linears fused along the output dim. Cached on
+    the first module; cleared by `invalidate_packs` after a structural change."""
+    first = lins[0]
+    cached = first.__dict__.get("_kmoss_wpack")
+    if cached is not None and cached[0] == len(lins):
+        return cached[1]
+    bases = [lin.base for lin in lins]
+    if all(b is not None and getattr(b, "kind", "") == "fp8" for b in bases):
+        if len(lins) == 1:
+            b0 = bases[0]
+            pack = WeightPack("fp8", b0.q, b0.scale, b0.col_scale, b0.per_tensor)
+        else:
+            # a fused group exists only when the weights were quantised together into one
+            # buffer with one scale (`quant.weights.quantize_group`)
+            group = getattr(bases[0], "group", None)
+            if group is None or any(getattr(b, "group", None) is not group for b in bases):
+                return None
+            pack = WeightPack("fp8", group.q, group.scale, group.col_scale, group.per_tensor)
+    elif all(b is None for b in bases) and all(lin.compute is None for lin in lins):
+        ws = [lin.weight for lin in lins]
+        trainable = any(p.requires_grad for p in ws)
+        if len(ws) == 1:
+            w = ws[0] if ws[0].dtype == BF16 else None
+        else:
+            w = _fused_storage(ws)
+        if w is None:
+            return None
+        pack = WeightPack("bf16", w.detach() if not trainable else w, trainable=trainable, params=ws)
+    else:
+        return None
+    first.__dict__["_kmoss_wpack"] = (len(lins), pack)
+    return pack
+
+
+def _fused_storage(ws) -> Tensor | None:
+    """Concatenate weights along dim 0 once and re-point each parameter at its slice, so the
+    fused GEMM and the per-parameter state dict share one buffer."""
+    if any(w.dtype != BF16 for w in ws):
+        return None
+    first = ws[0]
+    rows = [w.shape[0] for w in ws]
+    contiguous = all(
+        ws[i + 1].data_ptr() == ws[i].data_ptr() + ws[i].numel() * 2 for i in range(len(ws) - 1)
+    )
+    if contiguous and getattr(first, "_kmoss_fused", None) is not None:
+        return first._kmoss_fused
+    fused = torch.cat([w.detach() for w in ws], 0)
+    start = 0
+    for w, n in zip(ws, rows):
+        w.data = fused[start : start + n]
+        start += n
+    first._kmoss_fused = fused
+    return fused
+
+
+def invalidate_packs(model) -> None:
+    for m in model.modules():
+        m.__dict__.pop("_kmoss_wpack", None)
+        m.__dict__.pop("_kmoss_lpack", None)
+
+
+class NotFusable(Exception):
+    pass
+
+
+def _build_lora_pack(lins, adapters, wp: WeightPack) -> LoraPack:
+    parts, plain, tdiv = [], [], []
+    col = row = 0
+    out_total = sum(lin.out_features for lin in lins)
+    for lin, ad in zip(lins, adapters):
+        if ad is not None:
+            if not getattr(ad, "fusable", False) or lin.adapter_mode != "bypass":
+                raise NotFusable
+            if wp.kind == "fp8" and not wp.per_tensor:
+                raise NotFusable
+            r = ad.rank
+            parts.append((ad, row, lin.out_features, col, r))
+            col += _pad8(r)
+        row += lin.out_features
+    R = col
+    if R == 0 or R > 64:
+        raise NotFusable
+    dev = lins[0].weight_like.device
+    down = torch.zeros(R, lins[0].in_features, dtype=BF16, device=dev)
+    up = torch.zeros(out_total, R, dtype=BF16, device=dev)
+    plain_scale = torch.ones(R, dtype=torch.float32, device=dev)
+    for ad, row0, nout, col0, r in parts:
+        plain_scale[col0 : col0 + r] = float(ad.scale)
+    t_scale = plain_scale * wp.scale[1] if wp.kind == "fp8" else plain_scale
+    return LoraPack(down, up, plain_scale, t_scale, parts)
+
+
+class _GatherLora(torch.autograd.Function):
+    """Copy the adapters' factors into the packed operands (forward) and hand the packed
+    gradients back as slices (backward). The packed buffers persist across steps; only their
+    contents refresh, so the GEMM operands keep stable addresses."""
+
+    @staticmethod
+    def forward(ctx, pack_id, *factors):
+        pack = _PACKS[pack_id]
+        for i, (ad, row0, nout, col0, r) in enumerate(pack.parts):
+            pack.down[col0 : col0 + r].copy_(factors[2 * i])
+            pack.up[row0 : row0 + nout, col0 : col0 + r].copy_(factors[2 * i + 1])
+        ctx.pack_id = pack_id
+        return pack.down[:], pack.up[:]
+
+    @staticmethod
+    def backward(ctx, d_down, d_up):
+        pack = _PACKS[ctx.pack_id]
+        grads = []
+        for i, (ad, row0, nout, col0, r) in enumerate(pack.parts):
+            gd = None if d_down is None else d_down[col0 : col0 + r]
+            gu = None if d_up is None else d_up[row0 : row0 + nout, col0 : col0 + r]
+            grads += [gd, gu]
+        return (None, *grads)
+
+
+_PACKS: dict[int, LoraPack] = {}
+
+
+# ----------------------------------------------------------------------------------------
+# fused layer functions
+# ----------------------------------------------------------------------------------------
+class FusedLinearFn(torch.autograd.Function):
+    """out = epilogue(x W^T + b + LoRA(x)); epilogue in {linear, gated residual, situ, qk-rope}.
+
+    Inputs after the config object: x, residual (or None), gate (or None), bias, W (dense
+    parameters, possibly several for a fused group), then `down`, `up` of the packed LoRA.
+    """
+
+    @staticmethod
+    def forward(ctx, cfg, x, res, gate, bias, down, up, *weights):
+        wp: WeightPack = cfg["wp"]
+        lp: LoraPack | None = cfg["lp"]
+        mode = cfg["mode"]
+        epi = {}
+        aux = head_rstd = None
+        if mode == "gated":
+            epi = dict(res=res, beta=cfg["r"], gate=gate, seg=cfg["seg"])
+        elif mode == "situ":
+            f = wp.out_features // 2
+            if cfg["save_aux"]:
+                aux = torch.empty(x.shape[0], 2 * f, dtype=BF16, device=x.device)
+            epi = dict(epilogue=EPI_SITU, aux=aux)
+        elif mode == "qkrope":
+            head_rstd = torch.empty(x.shape[0], cfg["rope_cols"] // 128, dtype=torch.float32, device=x.device)
+            epi = dict(epilogue=EPI_QK_ROPE, q_norm_w=cfg["q_norm_w"], k_norm_w=cfg["k_norm_w"], rope=cfg["table"],
+                       rope_cols=cfg["rope_cols"], eps=cfg["eps"], head_rstd=head_rstd)
+        out, t, xs = _LinearCore.forward(x, wp, bias, lp, **epi)
+        ctx.cfg = cfg
+        ctx.save_for_backward(x, t, xs, gate, aux, head_rstd, out if mode == "qkrope" else None)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        cfg = ctx.cfg
+        x, t, xs, gate, aux, head_rstd, out = ctx.saved_tensors
+        wp, lp, mode = cfg["wp"], cfg["lp"], cfg["mode"]
+        ops = native.load()
+        dout = dout.contiguous()
+        dres = dgate = None
+        if mode == "gated":
+            if ctx.needs_input_grad[2]:
+                dres = dout if cfg["r"] == 1.0 else dout * cfg["r"]
+            if gate is not None:
+                d = torch.empty_like(dout)
+                ops.seg_scale(dout, gate, cfg["seg"], d)
+            else:
+                d = dout
+        elif mode == "situ":
+            f = aux.shape[1] // 2
+            d = torch.empty_like(aux)
+            ops.situ_bwd(dout, aux[:, :f], aux[:, f:], d[:, :f], d[:, f:])
+        elif mode == "qkrope":
+            rc = cfg["rope_cols"]
+            heads = rc // 256
+            d = torch.empty_like(dout)
+            for i, w in enumerate((cfg["q_norm_w"], cfg["k_norm_w"])):
+                sl = slice(i * rc // 2, (i + 1) * rc // 2)
+                ops.qk_norm_rope_bwd(out[:, sl], dout[:, sl], w, cfg["table"], head_rstd[:, i * heads : (i + 1) * heads],
+                                     d[:, sl], None, heads)
+            if dout.shape[1] > rc:
+                d[:, rc:] = dout[:, rc:]
+        else:
+            d = dout
+        dx, d_down, d_up, dW, dbias = _LinearCore.backward(
+            d, x, wp, lp, t, xs, need_dx=ctx.needs_input_grad[1], need_bias=ctx.needs_input_grad[4]
+        )
+        if d_down is not None:
+            d_down, d_up = d_down.to(lp.down.dtype), d_up.to(lp.up.dtype)
+        dws = []
+        if dW is not None:
+            start = 0
+            for p in wp.params:
+                dws.append(dW[start : start + p.shape[0]].to(p.dtype) if p.requires_grad else None)
+                start += p.shape[0]
+        else:
+            dws = [None] * len(wp.params)
+        if dbias is not None and cfg.get("bias_dtype") is not None:
+            dbias = dbias.to(cfg["bias_dtype"])
+        return (None, dx, dres, dgate, dbias, d_down, d_up, *dws)
+
+
+def _prepare(lins):
+    """(wp, lp, down, up) for a group of linears, or None when the group must be composed."""
+    if not all(lin.weight_like.is_cuda for lin in lins):
+        return None
+    wp = weight_pack(lins)
+    if wp is None:
+        return None
+    first = lins[0]
+    adapters = [lin.adapter for lin in lins]
+    lp = None
+    down = up = None
+    if any(a is not None for a in adapters):
+        cached = first.__dict__.get("_kmoss_lpack")
+        if cached is None:
+            try:
+                lp = _build_lora_pack(lins, adapters, wp)
+            except NotFusable:
+                first.__dict__["_kmoss_lpack"] = "no"
+                return None
+            _PACKS[id(lp)] = lp
+            first.__dict__["_kmoss_lpack"] = lp
+        elif cached == "no":
+            return None
+        else:
+            lp = cached
+        factors = []
+        for ad, *_ in lp.parts:
+            factors += [ad.down_weight(), ad.up_weight()]
+        down, up = _GatherLora.apply(id(lp), *factors)
+    return wp, lp, down, up
+
+
+def _bias_of(lins):
+    biases = [lin.bias for lin in lins]
+    if all(b is None for b in biases):
+        return None
+    if len(lins) == 1:
+        return biases[0]
+    return torch.cat([b if b is not None else torch.zeros(l.out_features, device=l.weight_like.device, dtype=BF16)
+                      for b, l in zip(biases, lins)])
+
+
+def _fusable_input(x: Tensor) -> bool:
+    return x.is_cuda and x.dtype == BF16 and x.dim() == 2 and x.shape[1] % 8 == 0
+
+
+def fused_linear(lin, x: Tensor) -> Tensor:
+    """`MossLinear.forward` on CUDA: tcgen05 GEMM with fused adapter bypass when the layer is
+    bf16 / fp8 and the rows are wide enough; the library product otherwise (tiny conditioning
+    MLPs in fp32)."""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    if not _fusable_input(x2) or x2.shape[0] < MIN_ROWS or lin.out_features % 8:
+        return lin.forward_eager(x)
+    prep = _prepare([lin])
+    if prep is None:
+        return lin.forward_eager(x)
+    wp, lp, down, up = prep
+    cfg = dict(wp=wp, lp=lp, mode="linear", bias_dtype=None if lin.bias is None else lin.bias.dtype)
+    weights = wp.params if wp.trainable else ()
+    out = FusedLinearFn.apply(cfg, x2.contiguous(), None, None, lin.bias, down, up, *weights)
+    return out.reshape(*shape[:-1], lin.out_features)
+
+
+class NativeOps(OpSet):
+    name = "native"
+
+    rms_norm = staticmethod(rms_norm)
+    rms_norm_mod = staticmethod(rms_norm_mod)
+    qk_norm_rope = staticmethod(qk_norm_rope)
+    situ_glu = staticmethod(situ_glu)
+    situ_pair = staticmethod(situ_pair)
+    gated_residual = staticmethod(gated_residual)
+    token_mse = staticmethod(token_mse)
+
+    def __init__(self, pins: dict | None = None):
+        self.pins = dict(pins or {})
+        from . import attention
+
+        self.attention_varlen = attention.attention_varlen
+        if self.pins.get("attention_varlen") == "eager":
+            self.attention_varlen = eager.attention_varlen
+
+    # -- layer-level fused ops -----------------------------------------------------------
+    def qkv_rope(self, y, lin_q, lin_k, lin_v, heads, q_weight, k_weight, pos, bands, eps):
+        lins = [lin_q, lin_k, lin_v]
+        dim = lin_q.out_features
+        prep = None
+        if (_fusable_input(y) and dim == heads * 128 and self.pins.get("linear_qk_rope") != "eager"
+                and all(l.bias is None for l in lins)):
+            prep = _prepare(lins)
+        if prep is None:
+            return OpSet.qkv_rope(self, y, lin_q, lin_k, lin_v, heads, q_weight, k_weight, pos, bands, eps)
+        wp, lp, down, up = prep
+        cfg = dict(wp=wp, lp=lp, mode="qkrope", q_norm_w=q_weight.detach(), k_norm_w=k_weight.detach(),
+                   table=_table(pos, bands), rope_cols=2 * dim, eps=eps)
+        if q_weight.requires_grad or k_weight.requires_grad or q_weight.dtype != BF16:
+            return OpSet.qkv_rope(self, y, lin_q, lin_k, lin_v, heads, q_weight, k_weight, pos, bands, eps)
+        weights = wp.params if wp.trainable else ()
+        out = FusedLinearFn.apply(cfg, y.contiguous(), None, None, None, down, up, *weights)
+        q, k, v = out.unflatten(1, (3, heads, 128)).unbind(1)
+        return q, k, v
+
+    def linear_situ(self, y, lin):
+        prep = None
+        if _fusable_input(y) and lin.bias is None and (lin.out_features // 2) % 128 == 0 \
+                and self.pins.get("linear_situ") != "eager":
+            prep = _prepare([lin])
+        if prep is None:
+            return OpSet.linear_situ(self, y, lin)
+        wp, lp, down, up = prep
+        cfg = dict(wp=wp, lp=lp, mode="situ", save_aux=torch.is_grad_enabled())
+        weights = wp.params if wp.trainable else ()
+        return FusedLinearFn.apply(cfg, y.contiguous(), None, None, None, down, up, *weights)
+
+    def linear_gated_residual(self, a, lin, x, gate, seg, r):
+        prep = None
+        if (_fusable_input(a) and x.dtype == BF16 and self.pins.get("linear_gated_residual") != "eager"
+                and (gate is None or not gate.requires_grad)):
+            prep = _prepare([lin])
+        if prep is None:
+            return OpSet.linear_gated_residual(self, a, lin, x, gate, seg, r)
+        wp, lp, down, up = prep
+        cfg = dict(wp=wp, lp=lp, mode="gated", r=float(r), seg=seg,
+                   bias_dtype=None if lin.bias is None else lin.bias.dtype)
+        weights = wp.params if wp.trainable else ()
+        return FusedLinearFn.apply(cfg, a.contiguous(), x.contiguous(), gate, lin.bias, down, up, *weights)

@@ -1,0 +1,118 @@
+"""Frozen base weights stored in fp8.
+
+`BASE_PRECISION="fp8_compute"` in the reference keeps each linear's weight as e4m3 with a
+per-tensor or per-row scale and runs the product in fp8 (`src/kohakumoss/quant/compute.py:45-164`,
+recipes in `src/kohakumoss_kernels/fp8/formats.py:70-136`). Here the stored tensor is fed to
+the tcgen05 `kind::f8f6f4` GEMM as is: K-major for the forward product, MN-major for dgrad,
+so no transposed copy is kept. Linears that one GEMM consumes together (q | k | v of a joint
+block) are quantised as ONE buffer with ONE scale (`quantize_group`), which is what lets the
+fused projection stay a per-tensor-scaled product.
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+E4M3 = torch.float8_e4m3fn
+E4M3_MAX = 448.0
+
+
+def _quantize(w: Tensor, recipe: str) -> tuple[Tensor, Tensor, Tensor]:
+    """(q e4m3 [out, in], scale[2] = {dequant, quant} (per tensor), col_scale fp32 [out])."""
+    wf = w.detach().float()
+    if recipe == "tensor":
+        amax = wf.abs().max().clamp_min(1e-12)
+        dq = amax / E4M3_MAX
+        q = (wf / dq).clamp(-E4M3_MAX, E4M3_MAX).to(E4M3)
+        scale = torch.stack((dq, 1.0 / dq)).float()
+        return q, scale, dq.expand(w.shape[0]).contiguous().float()
+    if recipe == "row":
+        amax = wf.abs().amax(1).clamp_min(1e-12)
+        dq = amax / E4M3_MAX
+        q = (wf / dq[:, None]).clamp(-E4M3_MAX, E4M3_MAX).to(E4M3)
+        return q, torch.ones(2, device=w.device), dq.float().contiguous()
+    raise ValueError(f"unknown fp8 recipe {recipe!r} (tensor|row)")
+
+
+class QuantGroup:
+    """One fp8 buffer + scale shared by several linears fused along the output dim."""
+
+    def __init__(self, q: Tensor, scale: Tensor, col_scale: Tensor, per_tensor: bool):
+        self.q, self.scale, self.col_scale, self.per_tensor = q, scale, col_scale, per_tensor
+
+
+class Fp8Weight:
+    """Stored fp8 weight of one linear (`MossLinear.set_base`)."""
+
+    kind = "fp8"
+
+    def __init__(self, q: Tensor, scale: Tensor, col_scale: Tensor, per_tensor: bool, group: QuantGroup | None = None):
+        self.q, self.scale, self.col_scale, self.per_tensor, self.group = q, scale, col_scale, per_tensor, group
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+    def weight(self, dtype: torch.dtype = torch.bfloat16) -> Tensor:
+        return (self.q.float() * self.col_scale[:, None]).to(dtype)
+
+    def linear(self, x: Tensor, bias: Tensor | None) -> Tensor:
+        """Reference-precision emulation (dequantise, then a dense product); the CUDA op set
+        never calls this, it feeds `q` to the fp8 GEMM."""
+        return torch.nn.functional.linear(x, self.weight(x.dtype), bias)
+
+    def _apply(self, fn) -> None:
+        moved_q = fn(self.q)
+        if moved_q.dtype != self.q.dtype:  # a dtype cast of the module must not touch fp8 bytes
+            moved_q = moved_q.to(self.q.dtype) if moved_q.device == self.q.device else fn(self.q.view(torch.uint8)).view(E4M3)
+        self.q = moved_q
+        self.scale = fn(self.scale).float()
+        self.col_scale = fn(self.col_scale).float()
+
+    def state(self, prefix: str) -> dict[str, Tensor]:
+        return {prefix + "weight": self.q, prefix + "weight_scale": self.col_scale if not self.per_tensor else self.scale[:1]}
+
+
+def quantize_linear(lin, recipe: str = "tensor", drop_dense: bool = True) -> Fp8Weight:
+    q, scale, col = _quantize(lin.weight, recipe)
+    base = Fp8Weight(q, scale, col, recipe == "tensor")
+    lin.set_base(base)
+    if drop_dense:
+        lin.drop_weight()
+    return base
+
+
+def quantize_group(lins, recipe: str = "tensor", drop_dense: bool = True) -> QuantGroup:
+    """Quantise several linears (same input width) into one buffer with a joint scale."""
+    w = torch.cat([lin.weight.detach() for lin in lins], 0)
+    q, scale, col = _quantize(w, recipe)
+    group = QuantGroup(q, scale, col, recipe == "tensor")
+    start = 0
+    for lin in lins:
+        n = lin.out_features
+        lin.set_base(Fp8Weight(q[start : start + n], scale, col[start : start + n], recipe == "tensor", group))
+        if drop_dense:
+            lin.drop_weight()
+        start += n
+    return group
+
+
+def apply_base_precision(model, base_precision: str = "fp8_compute", recipe: str = "tensor", drop_dense: bool = True) -> int:
+    """Quantise the joint-block projections of a backbone in place; returns how many linears
+    changed. `bf16` / `compute` / `auto` leave the dense weights alone."""
+    if base_precision in ("auto", "compute", "bf16", "none", ""):
+        return 0
+    if base_precision not in ("fp8_compute", "fp8"):
+        raise ValueError(f"BASE_PRECISION {base_precision!r} is not handled here")
+    count = 0
+    for block in model.layers:
+        p = block.proj
+        quantize_group([p["q"], p["k"], p["v"]], recipe, drop_dense)
+        for name in ("o", "ffn_up_gate", "ffn_down"):
+            quantize_linear(p[name], recipe, drop_dense)
+        count += 6
+    from ..ops import native_ops
+
+    native_ops.invalidate_packs(model)
+    return count

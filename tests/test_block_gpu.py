@@ -1,0 +1,173 @@
+"""Block ops and the fused layer path on CUDA against the eager fp32 reference."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from kohakumosstrainer_b200.types import MossArchConfig, build_seqinfo  # noqa: E402
+
+
+def _rel(x, y):
+    return ((x.float() - y.float()).norm() / y.float().norm().clamp_min(1e-12)).item()
+
+
+def _seq(dev):
+    hw = torch.tensor([[16, 16], [12, 20], [8, 8]])
+    tl = torch.tensor([32, 17, 50])
+    return build_seqinfo(hw, tl).to(dev)
+
+
+def test_rms_norm_mod_forward_backward():
+    from kohakumosstrainer_b200.ops import eager, native_ops
+
+    seq = _seq("cuda")
+    n, d = seq.n_joint, 256
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(n, d, device="cuda", generator=g).bfloat16().requires_grad_()
+    w = (torch.rand(d, device="cuda", generator=g) + 0.5).bfloat16().requires_grad_()
+    mod = torch.randn(3, 6, d, device="cuda", generator=g).requires_grad_()
+    y = native_ops.rms_norm_mod(x, w, mod[:, 0], mod[:, 1], seq.seg_joint, 1e-6)
+    xr, wr, mr = (t.detach().float().requires_grad_() for t in (x, w, mod))
+    yr = eager.rms_norm_mod(xr, wr, mr[:, 0], mr[:, 1], seq.seg_joint, 1e-6)
+    assert _rel(y, yr) < 5e-3
+    dy = torch.randn(n, d, device="cuda", generator=g)
+    y.backward(dy.bfloat16())
+    yr.backward(dy.bfloat16().float())
+    assert _rel(x.grad, xr.grad) < 1e-2
+    assert _rel(w.grad, wr.grad) < 1e-2
+    assert _rel(mod.grad, mr.grad) < 1e-2
+
+
+def test_qk_norm_rope_standalone_forward_backward():
+    from kohakumosstrainer_b200.ops import eager, native_ops
+
+    seq = _seq("cuda")
+    n, h = seq.n_joint, 4
+    g = torch.Generator(device="cuda").manual_seed(1)
+    q = torch.randn(n, h, 128, device="cuda", generator=g).bfloat16().requires_grad_()
+    k = torch.randn(n, h, 128, device="cuda", generator=g).bfloat16().requires_grad_()
+    qw = (torch.rand(128, device="cuda", generator=g) + 0.5).bfloat16().requires_grad_()
+    kw = (torch.rand(128, device="cuda", generator=g) + 0.5).bfloat16().requires_grad_()
+    bands = 1.0 / (10000 ** (torch.arange(16, device="cuda", dtype=torch.float32) / 16))
+    oq, ok = native_ops.qk_norm_rope(q, k, qw, kw, seq.pos_joint, bands, 1e-6)
+    ref = [t.detach().float().requires_grad_() for t in (q, k, qw, kw)]
+    rq, rk = eager.qk_norm_rope(ref[0], ref[1], ref[2], ref[3], seq.pos_joint, bands, 1e-6)
+    assert _rel(oq, rq) < 6e-3 and _rel(ok, rk) < 6e-3
+    dq = torch.randn_like(rq).bfloat16()
+    dk = torch.randn_like(rk).bfloat16()
+    torch.autograd.backward([oq, ok], [dq, dk])
+    torch.autograd.backward([rq, rk], [dq.float(), dk.float()])
+    assert _rel(q.grad, ref[0].grad) < 2e-2
+    assert _rel(k.grad, ref[1].grad) < 2e-2
+    assert _rel(qw.grad, ref[2].grad) < 2e-2
+
+
+def test_situ_and_gated_residual_and_loss():
+    from kohakumosstrainer_b200.ops import eager, native_ops
+
+    seq = _seq("cuda")
+    n, f = seq.n_joint, 512
+    g = torch.Generator(device="cuda").manual_seed(2)
+    h = (torch.randn(n, 2 * f, device="cuda", generator=g) * 3).bfloat16().requires_grad_()
+    a = native_ops.situ_glu(h)
+    hr = h.detach().float().requires_grad_()
+    ar = eager.situ_glu(hr)
+    assert _rel(a, ar) < 5e-3
+    da = torch.randn(n, f, device="cuda", generator=g).bfloat16()
+    a.backward(da)
+    ar.backward(da.float())
+    assert _rel(h.grad, hr.grad) < 1e-2
+
+    x = torch.randn(n, f, device="cuda", generator=g).bfloat16().requires_grad_()
+    o = torch.randn(n, f, device="cuda", generator=g).bfloat16().requires_grad_()
+    mod = torch.randn(3, 6, f, device="cuda", generator=g).requires_grad_()
+    out = native_ops.gated_residual(x, o, mod[:, 2], seq.seg_joint, 0.9)
+    xr, orr, mr = (t.detach().float().requires_grad_() for t in (x, o, mod))
+    outr = eager.gated_residual(xr, orr, mr[:, 2], seq.seg_joint, 0.9)
+    assert _rel(out, outr) < 5e-3
+    d = torch.randn(n, f, device="cuda", generator=g).bfloat16()
+    out.backward(d)
+    outr.backward(d.float())
+    assert _rel(x.grad, xr.grad) < 1e-2 and _rel(o.grad, orr.grad) < 1e-2 and _rel(mod.grad, mr.grad) < 1e-2
+
+    pred = torch.randn(seq.n_img, 128, device="cuda", generator=g).bfloat16().requires_grad_()
+    target = torch.randn(seq.n_img, 128, device="cuda", generator=g)
+    wt = torch.rand(3, device="cuda", generator=g)
+    loss = native_ops.token_mse(pred, target, seq.seg_img, wt)
+    pr = pred.detach().float().requires_grad_()
+    lr = eager.token_mse(pr, target, seq.seg_img, wt)
+    torch.testing.assert_close(loss, lr, rtol=1e-4, atol=1e-4)
+    loss.backward()
+    lr.backward()
+    assert _rel(pred.grad, pr.grad) < 1e-2
+
+
+def _pair(base: str, seed=0):
+    """(bf16 model on the native op set, fp32 twin on the eager op set) with identical
+    bf16-representable weights, the same fp8 bytes and the same LoRA factors."""
+    import copy
+
+    from kohakumosstrainer_b200 import adapters
+    from kohakumosstrainer_b200.models import build_backbone
+    from kohakumosstrainer_b200.models.build import apply_param_dtypes
+    from kohakumosstrainer_b200.ops import EagerOps
+    from kohakumosstrainer_b200.quant import apply_base_precision
+
+    cfg = MossArchConfig(dim=256, depth=2, heads=2, ffn_dim=512, text_dim=256, text_blocks=1)
+    ref = build_backbone(cfg, device="cuda", dtype=torch.float32, seed=seed)
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.copy_(p.bfloat16().float())
+    model = copy.deepcopy(ref)
+    apply_param_dtypes(model, torch.bfloat16)
+    model.bind_ops()
+    ref.bind_ops(EagerOps())
+    if base == "fp8":
+        apply_base_precision(model, "fp8_compute", "tensor")
+        apply_base_precision(ref, "fp8_compute", "tensor")
+    acfg = adapters.AdapterConfig(dim=8, alpha=8, preset="attn-mlp")
+    aset = adapters.apply(model, adapters.AdapterConfig(dim=8, alpha=8, preset="attn-mlp", dtype=torch.bfloat16))
+    with torch.no_grad():
+        for _, _, mod in aset.items():
+            mod.lora_up.weight.normal_(std=0.05)
+    rset = adapters.apply(ref, acfg)
+    rset.load_adapter_state({k: v.float() for k, v in aset.adapter_state().items()})
+    return model, aset, ref, rset
+
+
+@pytest.mark.parametrize("base", ["bf16", "fp8"])
+def test_model_lora_step_matches_fp32_reference(base):
+    """Tiny DiT, LoRA r8 on attn+mlp: native bf16 / fp8 forward + backward against the fp32
+    eager twin (fp8: the twin multiplies by the dequantised weights)."""
+    from kohakumosstrainer_b200.ops import native
+
+    seq = _seq("cuda")
+    g = torch.Generator(device="cuda").manual_seed(3)
+    model, aset, ref, rset = _pair(base)
+    assert model.ops.name == "native"
+    z = torch.randn(seq.n_img, 128, device="cuda", generator=g).bfloat16()
+    text = torch.randn(seq.n_txt, 256, device="cuda", generator=g).bfloat16()
+    sigma = torch.rand(3, device="cuda", generator=g)
+    target = torch.randn(seq.n_img, 128, device="cuda", generator=g)
+    ones = torch.ones(3, device="cuda")
+
+    v = model(z, text, sigma, seq)
+    loss = model.ops.token_mse(v, target, seq.seg_img, ones) / seq.n_img
+    loss.backward()
+    native.check_status()
+    rv = ref(z.float(), text.float(), sigma, seq)
+    rloss = ref.ops.token_mse(rv, target, seq.seg_img, ones) / seq.n_img
+    rloss.backward()
+
+    tol = 0.03 if base == "bf16" else 0.08
+    assert _rel(v, rv) < tol, (loss.item(), rloss.item())
+    assert abs(loss.item() - rloss.item()) / abs(rloss.item()) < tol
+    rg = dict(rset.named_parameters())
+    bad = []
+    for n, p in aset.named_parameters():
+        assert p.grad is not None, n
+        err = _rel(p.grad, rg[n].grad)
+        if err > (0.1 if base == "bf16" else 0.3):
+            bad.append((n, err))
+    assert not bad, bad[:6]
