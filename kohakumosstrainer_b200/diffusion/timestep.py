@@ -1,0 +1,107 @@
+"""Timestep (sigma) samplers, drawn on a CPU generator so a run replays exactly.
+
+`moss`: discrete 1000-step grid with a truncated logit-normal pmf, a uniform mix and mass
+moved to sigma = 1, optionally staged by training step; `uniform`; `logit_normal`
+(`src/kohakumoss/diffusion/timestep/{moss,simple,shift}.py` in the reference).
+"""
+
+from __future__ import annotations
+
+import bisect
+import math
+
+import torch
+from torch import Tensor
+
+from ..utils.registry import Registry
+
+TIMESTEPS = Registry("timestep sampler")
+
+TECH_REPORT_STAGES = (
+    (0, {"mu": 0.0, "s": 1.0, "shift": 3.0, "cutoff": None, "p_full": 0.01}),
+    (140_000, {"mu": -1.45, "s": 1.05, "shift": 1.0, "cutoff": None, "p_full": 0.01}),
+    (207_000, {"mu": -1.45, "s": 1.05, "shift": 1.0, "cutoff": 0.95, "p_full": 0.0}),
+    (274_000, {"mu": -1.09, "s": 0.95, "shift": 1.0, "cutoff": 0.95, "p_full": 0.0}),
+)
+
+
+def shift_sigma(sigma: Tensor, shift: float) -> Tensor:
+    """`s t / (1 + (s - 1) t)`: pushes sigma towards noise for shift > 1."""
+    if shift == 1.0:
+        return sigma
+    return shift * sigma / (1.0 + (shift - 1.0) * sigma)
+
+
+def _cdf_sf(x: Tensor, mu: float, s: float) -> tuple[Tensor, Tensor]:
+    """(P(S <= x), P(S > x)) of S = 1 - sigmoid(mu + s Z); the upper tail has its own erfc."""
+    x = x.clamp(0.0, 1.0)
+    u = (torch.log1p(-x) - torch.log(x) - mu) / (s * math.sqrt(2.0))
+    cdf, sf = 0.5 * torch.erfc(u), 0.5 * torch.erfc(-u)
+    low, high = x <= 0, x >= 1
+    cdf = torch.where(low, 0.0, torch.where(high, 1.0, cdf))
+    sf = torch.where(low, 1.0, torch.where(high, 0.0, sf))
+    return cdf, sf
+
+
+def moss_pmf(steps: int, mu: float, s: float, cutoff: float | None, uniform_mix: float, p_full: float) -> Tensor:
+    """pmf over sigma_j = j / steps, j = 1..steps (fp32, sums to 1)."""
+    a = 1.0 if cutoff is None else float(cutoff)
+    j = torch.arange(steps + 1, dtype=torch.float32)
+    cdf, sf = _cdf_sf(a * j / steps, mu, s)
+    lower = cdf[1:] <= 0.5
+    mass = torch.where(lower, cdf[1:] - cdf[:-1], sf[:-1] - sf[1:])
+    mass = mass / cdf[-1].clamp_min(torch.finfo(torch.float32).tiny)
+    pmf = (1.0 - uniform_mix) * mass + uniform_mix / steps
+    pmf = pmf * (1.0 - p_full)
+    pmf[-1] += p_full
+    return pmf / pmf.sum()
+
+
+class _Stage:
+    def __init__(self, steps, uniform_mix, mu=0.0, s=1.0, shift=1.0, cutoff=None, p_full=0.0, **extra):
+        pmf = moss_pmf(steps, mu, s, cutoff, extra.get("uniform_mix", uniform_mix), p_full)
+        grid = torch.arange(1, steps + 1, dtype=torch.float32) / steps
+        self.sigma = shift_sigma(grid, shift)
+        self.cdf = pmf.cumsum(0)
+        self.cdf[-1] = 1.0
+
+    def draw(self, batch: int, generator: torch.Generator) -> Tensor:
+        u = torch.rand(batch, generator=generator)
+        return self.sigma[torch.searchsorted(self.cdf, u).clamp_max(self.cdf.numel() - 1)]
+
+
+@TIMESTEPS.register("moss")
+class MossTimestep:
+    def __init__(self, mu=-1.09, s=0.95, shift=1.0, cutoff=0.95, uniform_mix=0.01, p_full=0.0, steps=1000, schedule=None):
+        if schedule is None:
+            table = ((0, dict(mu=mu, s=s, shift=shift, cutoff=cutoff, p_full=p_full)),)
+        elif schedule == "tech_report":
+            table = TECH_REPORT_STAGES
+        else:
+            table = tuple((int(st), dict(kw)) for st, kw in schedule)
+        self.starts = [st for st, _ in table]
+        self.stages = [_Stage(steps, uniform_mix, **kw) for _, kw in table]
+
+    def stage_at(self, step: int) -> _Stage:
+        return self.stages[bisect.bisect_right(self.starts, step) - 1]
+
+    def sample(self, batch: int, generator: torch.Generator, step: int = 0) -> Tensor:
+        return self.stage_at(step).draw(batch, generator)
+
+
+@TIMESTEPS.register("uniform")
+class UniformTimestep:
+    def __init__(self, shift=1.0, low=0.001, high=1.0):
+        self.shift, self.low, self.span = shift, low, high - low
+
+    def sample(self, batch, generator, step=0):
+        return shift_sigma(self.low + self.span * torch.rand(batch, generator=generator), self.shift)
+
+
+@TIMESTEPS.register("logit_normal")
+class LogitNormalTimestep:
+    def __init__(self, mu=0.0, s=1.0, shift=1.0):
+        self.mu, self.s, self.shift = mu, s, shift
+
+    def sample(self, batch, generator, step=0):
+        return shift_sigma(torch.sigmoid(self.mu + self.s * torch.randn(batch, generator=generator)), self.shift)
