@@ -1,0 +1,252 @@
+"""Headline benchmark: MOSS-Image-Base DiT LoRA training, latent (image) tokens per second.
+
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference]
+
+Config (the metric's definition): LoRA rank 8 on q/k/v/o/ffn of the full MOSS-Image-Base DiT
+(dim 3072, depth 42, 24 heads, ffn 8192; random-init weights), fp8 per-tensor-scaled base
+GEMMs with a bf16 adapter, DDP over N GPUs of one node, per GPU one packed batch of ~20k
+joint tokens per step from native-resolution buckets (512^2 .. 1024^2 areas, 64-px steps, one
+latent token per 16 x 16 px, patch dim 128, <= 256 text tokens of width 4096, N(0, 1) data).
+Weak scaling: per-GPU work is fixed. For N > 1 the script is launched by torchrun (one rank
+per GPU, NCCL); rank 0 prints ONE JSON line.
+
+Two timed regions, each W warm-up + K steps, bracketed by barrier + synchronize, CUDA events,
+max over ranks:
+  * `value`: step inputs already on the device (forward, backward, gradient all-reduce,
+    norm / clip, optimiser step);
+  * `e2e`: the public `Trainer.train_step(host_batch)` call: H2D copy of the step's inputs from
+    pinned host memory every step and the loss read back to the host every step.
+Every step touches several GB of activations and 5 GB of weights, far beyond the 126 MB L2,
+so no explicit L2 flush is needed between iterations.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+BASELINE_JOINT_TOK_S = 26830.0  # reference: LoKr f8, 1x B300 SXM6 (docs/performance/training-b300.md:10)
+MODEL = "MOSS-Image-Base DiT 5.1B (dim 3072, depth 42), LoRA r8 attn+mlp, fp8 per-tensor base, bf16 adapter"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--variant", default="base", help="architecture preset (tests use 'tiny')")
+    ap.add_argument("--max-tokens", type=int, default=20480)
+    ap.add_argument("--depth", type=int, default=0, help="override depth (debug only; marks the run invalid)")
+    ap.add_argument("--base", default="fp8_compute")
+    ap.add_argument("--ddp-backend", default="kohakumoss", choices=("kohakumoss", "torch", "nccl"))
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, reasons, smax, power = [], set(), None, []
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                smax = float(r[2])
+                power.append(float(r[3]))
+            except ValueError:
+                continue
+            for name, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "power_w_max": max(power) if power else None, "samples": len(sm)}
+
+
+def reference_arm(args) -> None:
+    """The upstream package installs offline only with --no-deps; its trainer and adapter
+    packages import lycoris-lora, kohaku-engine and kohakuvault, which are absent, so a LoRA
+    training step cannot run through its own public API."""
+    reason = ("reference installs with --no-deps into baseline/_ref, but kohakumoss.training.entry and "
+              "kohakumoss.adapters need lycoris-lora / kohaku-engine / kohakuvault / anyschedule "
+              "(not installable offline; it also pins torch>=2.13), so its LoRA training step cannot run")
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref"))
+    try:
+        import kohakumoss.training.entry  # noqa: F401
+        import kohakumoss.adapters  # noqa: F401
+    except Exception as err:  # the expected outcome on this image
+        reason += f" ({type(err).__name__}: {err})"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": reason[:400]}))
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    import torch
+    import torch.distributed as dist
+
+    from kohakumosstrainer_b200.data import SyntheticConfig, SyntheticDataset
+    from kohakumosstrainer_b200.ops import native
+    from kohakumosstrainer_b200.training import Trainer, TrainerConfig
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        print(json.dumps({"metric": "dit_train_latent_tokens_per_s", "value": None, "error": "no CUDA device"}))
+        return
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    overrides = {"depth": args.depth} if args.depth else {}
+    text_dim = 4096 if args.variant in ("base", "sft") else 256
+    cfg = TrainerConfig(
+        variant=args.variant, arch_overrides=overrides, algo="lora", preset="attn-mlp", dim=8, alpha=8.0,
+        base_precision=args.base, fp8_recipe="tensor", precision="bf16", optimizer="adamw", lr=1e-4,
+        grad_clip=1.0, steps=10_000, parallel="ddp" if world > 1 else "none",
+        ddp_backend="kohakumoss" if args.ddp_backend == "kohakumoss" else "torch", timestep="moss",
+    )
+    trainer = Trainer(cfg, device=device, rank=rank, world=world)
+    data = SyntheticDataset(SyntheticConfig(max_tokens=args.max_tokens, text_dim=text_dim, seed=1234))
+    total = 2 * (args.warmup + args.steps)
+    host = [data.materialize(i, rank, world) for i in range(total)]
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(run_step, offset):
+        """W warm-up + K timed steps; returns (ms per step max over ranks, image tokens this rank)."""
+        for i in range(args.warmup):
+            run_step(offset + i)
+        sync()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        tokens = 0
+        launches0 = native.LAUNCHES["count"]
+        start.record()
+        for i in range(args.steps):
+            tokens += run_step(offset + args.warmup + i)
+        end.record()
+        sync()
+        ms = torch.tensor([start.elapsed_time(end)], device=device)
+        tok = torch.tensor([float(tokens)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            dist.all_reduce(tok, op=dist.ReduceOp.SUM)
+        return ms.item() / args.steps, tok.item(), native.LAUNCHES["count"] - launches0
+
+    # -- region 1: device-resident inputs -------------------------------------------------
+    staged = {}
+
+    def device_step(i):
+        hb, batch = host[i], staged[i]
+        denom = trainer.normalizer.denominator(hb.image_tokens, device)
+        if trainer.parallel is not None:
+            trainer.parallel.start(last=True)
+        loss = trainer.step_fn(batch, denom)
+        loss.backward()
+        trainer.bundle.observe(loss)
+        trainer.bundle.step()
+        trainer.step_fn.step_index += 1
+        return hb.image_tokens
+
+    # stage every input of region 1 before timing so no H2D copy falls inside it
+    for i in range(args.warmup + args.steps):
+        staged[i] = host[i].to_device(device, torch.float32, torch.bfloat16)
+    trainer.bundle.step_sync = "deferred"
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms_dev, tok_dev, launches = timed(device_step, 0)
+    clocks = sampler.stop()
+    trainer.bundle.settle()
+    staged.clear()
+
+    # -- region 2: end to end through Trainer.train_step -----------------------------------
+    trainer.bundle.step_sync = "step"
+    half = args.warmup + args.steps
+    losses = []
+
+    def e2e_step(i):
+        nxt = host[i + 1] if i + 1 < total else None
+        out = trainer.train_step(host[i], next_batch=nxt)
+        losses.append(out["loss"])
+        return host[i].image_tokens
+
+    ms_e2e, tok_e2e, _ = timed(e2e_step, half)
+    native.check_status()
+
+    value = tok_dev / (ms_dev * args.steps / 1e3)
+    e2e_value = tok_e2e / (ms_e2e * args.steps / 1e3)
+    joint = sum(h.joint_tokens for h in host[args.warmup : args.warmup + args.steps]) * world / (ms_dev * args.steps / 1e3)
+    h2d = sum(h.nbytes() for h in host[half + args.warmup : half + args.warmup + args.steps]) / args.steps
+    if rank == 0:
+        out = {
+            "metric": "dit_train_latent_tokens_per_s", "value": round(value, 1), "unit": "latent tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_dev, 2),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": round(joint / BASELINE_JOINT_TOK_S, 3),
+            "vs_baseline_note": "joint (image+text) tokens/s over the reference's published 26,830 joint tok/s on 1x B300 (LoKr f8)",
+            "dtype": "bf16 activations, fp8 e4m3 base GEMMs (per-tensor), bf16 LoRA", "data": "synthetic",
+            "impl": "ours",
+            "config": {
+                "model": MODEL if args.variant in ("base", "sft") and not args.depth else f"{args.variant} (debug, invalid as a headline)",
+                "global_batch": f"{world} x ~{args.max_tokens} joint tokens/step", "seq_len": args.max_tokens,
+                "parallelism": f"dp{world}", "optimizer": "adamw", "l2": "inputs larger than L2 (GBs of activations per step)",
+                "joint_tokens_per_s": round(joint, 1),
+            },
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_value, 1), "unit": "latent tokens/s", "ms_per_step": round(ms_e2e, 2),
+                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 12},
+            "gpu_launches": int(launches),
+            "final_loss": losses[-1] if losses else None,
+            "max_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 2),
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

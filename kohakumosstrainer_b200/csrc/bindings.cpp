@@ -5,10 +5,12 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
+#include <cmath>
 #include <optional>
 
 #include "blockops.cuh"
 #include "gemm_sm100.cuh"
+#include "optim.cuh"
 
 namespace {
 
@@ -333,9 +335,54 @@ std::tuple<Tensor, Tensor> quantize_fp8_rows(const Tensor& x) {
   return {q, rs};
 }
 
+
+// ---- optimiser ---------------------------------------------------------------------------
+// `table` is a uint8 CUDA tensor holding OptTensor records, `chunks` an int32 [n, 2] CUDA tensor.
+int64_t opt_record_bytes() { return (int64_t)sizeof(kmoss::OptTensor); }
+int64_t opt_chunk_elems() { return kmoss::opt_chunk_elems(); }
+
+void adamw_multi(const Tensor& table, const Tensor& chunks, double lr, double beta1, double beta2, double eps,
+                 int64_t step, double ema_decay, const optional<Tensor>& grad_scale, const optional<Tensor>& skip) {
+  c10::cuda::CUDAGuard guard(table.device());
+  kmoss::AdamWHyper h{};
+  h.lr = (float)lr; h.beta1 = (float)beta1; h.beta2 = (float)beta2; h.eps = (float)eps;
+  h.inv_bc1 = (float)(1.0 / (1.0 - std::pow(beta1, (double)step)));
+  h.inv_sqrt_bc2 = (float)(1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step)));
+  h.ema_decay = (float)ema_decay;
+  h.grad_scale = cptr<float>(grad_scale);
+  h.skip = cptr<int>(skip);
+  KM_CHECK_CUDA(kmoss::adamw_multi(reinterpret_cast<const kmoss::OptTensor*>(table.data_ptr()),
+                                   reinterpret_cast<const int2*>(chunks.data_ptr()), (int)chunks.size(0), h, cur_stream()));
+}
+
+// returns fp32 [3] = {norm, clip coefficient, sum of squares}
+Tensor grad_norm_multi(const Tensor& table, const Tensor& chunks, double max_norm, const optional<Tensor>& nonfinite) {
+  c10::cuda::CUDAGuard guard(table.device());
+  const int n = (int)chunks.size(0);
+  Tensor partial = at::empty({std::max(n, 1)}, table.options().dtype(at::kFloat));
+  Tensor out = at::empty({3}, table.options().dtype(at::kFloat));
+  KM_CHECK_CUDA(kmoss::grad_norm_multi(reinterpret_cast<const kmoss::OptTensor*>(table.data_ptr()),
+                                       reinterpret_cast<const int2*>(chunks.data_ptr()), n, partial.data_ptr<float>(),
+                                       mptr<int>(nonfinite), (float)max_norm, out.data_ptr<float>(), cur_stream()));
+  return out;
+}
+
+void ema_multi(const Tensor& table, const Tensor& chunks, double decay, const optional<Tensor>& skip) {
+  c10::cuda::CUDAGuard guard(table.device());
+  KM_CHECK_CUDA(kmoss::ema_multi(reinterpret_cast<const kmoss::OptTensor*>(table.data_ptr()),
+                                 reinterpret_cast<const int2*>(chunks.data_ptr()), (int)chunks.size(0), (float)decay,
+                                 cptr<int>(skip), cur_stream()));
+}
+
 }  // namespace
 
 TORCH_LIBRARY(kmoss_b200, m) {
+  m.def("opt_record_bytes() -> int", &opt_record_bytes);
+  m.def("opt_chunk_elems() -> int", &opt_chunk_elems);
+  m.def("adamw_multi(Tensor table, Tensor chunks, float lr, float beta1, float beta2, float eps, int step, "
+        "float ema_decay, Tensor? grad_scale, Tensor? skip) -> ()", &adamw_multi);
+  m.def("grad_norm_multi(Tensor table, Tensor chunks, float max_norm, Tensor(a!)? nonfinite) -> Tensor", &grad_norm_multi);
+  m.def("ema_multi(Tensor table, Tensor chunks, float decay, Tensor? skip) -> ()", &ema_multi);
   m.def("kernel_status() -> Tensor", &kernel_status);
   m.def("gemm_pick_splits(int M, int N, int K, int elem_bytes) -> int", &gemm_pick_splits);
   m.def(

@@ -1,0 +1,136 @@
+// Multi-tensor optimiser kernels for sm_100a: fused AdamW (+ decoupled weight decay, fp32
+// master weights, EMA) over an address table, and the global gradient sum of squares.
+//
+// One launch updates every tensor of a parameter group: the table of tensor descriptors and
+// the chunk -> (tensor, offset) map live in device memory and are built once, because
+// parameter, gradient and state addresses do not change between steps. The clip coefficient
+// and the skip flag are read from device memory, so the step needs no host synchronisation.
+// The reference splits this work over `torch._foreach_*` calls, a Triton address-table kernel
+// and a separate EMA lerp (`src/kohakumoss_kernels/backends/triton/optim/multi.py:34-132`,
+// `src/kohakumoss/training/ema/averagers.py:144-171`).
+
+#include "optim.cuh"
+
+#include "common.cuh"
+
+namespace kmoss {
+
+namespace {
+
+constexpr int OPT_THREADS = 256;
+constexpr int OPT_CHUNK = 8192;  // elements per block
+
+__device__ __forceinline__ float load_elem(const void* p, int dtype, long i) {
+  return dtype == 0 ? reinterpret_cast<const float*>(p)[i]
+                    : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ __forceinline__ void store_elem(void* p, int dtype, long i, float v) {
+  if (dtype == 0) reinterpret_cast<float*>(p)[i] = v;
+  else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16(v);
+}
+
+__global__ void __launch_bounds__(OPT_THREADS)
+adamw_multi_kernel(const OptTensor* __restrict__ tensors, const int2* __restrict__ chunks, AdamWHyper h) {
+  if (h.skip != nullptr && *h.skip != 0) return;
+  const int2 c = chunks[blockIdx.x];
+  const OptTensor t = tensors[c.x];
+  const long begin = (long)c.y * OPT_CHUNK;
+  const long end = min(t.n, begin + OPT_CHUNK);
+  const float gs = h.grad_scale != nullptr ? *h.grad_scale : 1.f;
+  const float lr = h.lr * t.lr_mul;
+  const float decay = 1.f - lr * t.weight_decay;
+  for (long i = begin + threadIdx.x; i < end; i += OPT_THREADS) {
+    const float g = load_elem(t.grad, t.grad_dtype, i) * gs;
+    float p = t.master != nullptr ? t.master[i] : load_elem(t.param, t.param_dtype, i);
+    float m = t.exp_avg[i], v = t.exp_avg_sq[i];
+    m = h.beta1 * m + (1.f - h.beta1) * g;
+    v = h.beta2 * v + (1.f - h.beta2) * g * g;
+    const float denom = sqrtf(v) * h.inv_sqrt_bc2 + h.eps;
+    if (t.decay_to_one) p = 1.f + (p - 1.f) * decay;  // norm weights decay towards 1
+    else p *= decay;
+    p -= lr * h.inv_bc1 * m / denom;
+    t.exp_avg[i] = m;
+    t.exp_avg_sq[i] = v;
+    if (t.master != nullptr) t.master[i] = p;
+    store_elem(t.param, t.param_dtype, i, p);
+    if (t.ema != nullptr) t.ema[i] += (1.f - h.ema_decay) * (p - t.ema[i]);
+  }
+}
+
+// partial[block] = sum of squares of the block's chunk of gradients (fp32, fixed order)
+__global__ void __launch_bounds__(OPT_THREADS)
+sumsq_multi_kernel(const OptTensor* __restrict__ tensors, const int2* __restrict__ chunks, float* partial,
+                   int* nonfinite) {
+  __shared__ float red[OPT_THREADS / 32];
+  const int2 c = chunks[blockIdx.x];
+  const OptTensor t = tensors[c.x];
+  const long begin = (long)c.y * OPT_CHUNK;
+  const long end = min(t.n, begin + OPT_CHUNK);
+  float acc = 0.f;
+  for (long i = begin + threadIdx.x; i < end; i += OPT_THREADS) {
+    const float g = load_elem(t.grad, t.grad_dtype, i);
+    acc += g * g;
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int i = 0; i < OPT_THREADS / 32; ++i) s += red[i];
+    partial[blockIdx.x] = s;
+    if (nonfinite != nullptr && !isfinite(s)) atomicAdd(nonfinite, 1);
+  }
+}
+
+// out[0] = sqrt(sum partial); out[1] = clip coefficient min(1, max_norm / (norm + 1e-6))
+__global__ void finish_norm_kernel(const float* partial, int n, float extra_sumsq_scale, const float* extra_sumsq,
+                                   float max_norm, float* out) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  float s = 0.f;
+  for (int i = 0; i < n; ++i) s += partial[i];
+  if (extra_sumsq != nullptr) s = s * extra_sumsq_scale + *extra_sumsq;
+  const float norm = sqrtf(s);
+  out[0] = norm;
+  out[1] = max_norm > 0.f ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f;
+  out[2] = s;
+}
+
+// EMA only (for parameters stepped by another optimiser): ema += (1 - d) * (p - ema)
+__global__ void __launch_bounds__(OPT_THREADS)
+ema_multi_kernel(const OptTensor* __restrict__ tensors, const int2* __restrict__ chunks, float decay, const int* skip) {
+  if (skip != nullptr && *skip != 0) return;
+  const int2 c = chunks[blockIdx.x];
+  const OptTensor t = tensors[c.x];
+  if (t.ema == nullptr) return;
+  const long begin = (long)c.y * OPT_CHUNK;
+  const long end = min(t.n, begin + OPT_CHUNK);
+  for (long i = begin + threadIdx.x; i < end; i += OPT_THREADS) {
+    const float p = t.master != nullptr ? t.master[i] : load_elem(t.param, t.param_dtype, i);
+    t.ema[i] += (1.f - decay) * (p - t.ema[i]);
+  }
+}
+
+}  // namespace
+
+int opt_chunk_elems() { return OPT_CHUNK; }
+
+cudaError_t adamw_multi(const OptTensor* tensors, const int2* chunks, int n_chunks, const AdamWHyper& h, cudaStream_t s) {
+  if (n_chunks <= 0) return cudaSuccess;
+  adamw_multi_kernel<<<n_chunks, OPT_THREADS, 0, s>>>(tensors, chunks, h);
+  return cudaGetLastError();
+}
+
+cudaError_t grad_norm_multi(const OptTensor* tensors, const int2* chunks, int n_chunks, float* partial, int* nonfinite,
+                            float max_norm, float* out, cudaStream_t s) {
+  if (n_chunks > 0) sumsq_multi_kernel<<<n_chunks, OPT_THREADS, 0, s>>>(tensors, chunks, partial, nonfinite);
+  finish_norm_kernel<<<1, 32, 0, s>>>(partial, n_chunks, 1.f, nullptr, max_norm, out);
+  return cudaGetLastError();
+}
+
+cudaError_t ema_multi(const OptTensor* tensors, const int2* chunks, int n_chunks, float decay, const int* skip, cudaStream_t s) {
+  if (n_chunks <= 0) return cudaSuccess;
+  ema_multi_kernel<<<n_chunks, OPT_THREADS, 0, s>>>(tensors, chunks, decay, skip);
+  return cudaGetLastError();
+}
+
+}  // namespace kmoss

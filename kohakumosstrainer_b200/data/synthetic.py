@@ -1,0 +1,87 @@
+"""Synthetic packed batches of the shapes real MOSS-Image training produces.
+
+Samples draw an area uniformly in `[min_area, max_area]` pixels and a log-uniform aspect
+ratio, snap both sides to `size_step` pixels (native-resolution buckets), get one latent token
+per 16 x 16 pixels with `channels` N(0, 1) values and up to `max_text` text tokens of width
+`text_dim` N(0, 1); samples are packed greedily until `max_tokens` joint tokens are reached
+(the `BATCHING="tokens"` rule of the reference, `src/kohakumoss_data/resolution/batching.py:23-72`).
+Batch i of rank r is a pure function of (seed, r, i), like the stateless loader.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from ..utils.seeds import seed_of
+from .types import HostBatch
+
+LATENT_FACTOR = 16
+
+
+@dataclass(frozen=True)
+class SyntheticConfig:
+    max_tokens: int = 20480          # joint (image + text) tokens per packed batch
+    min_area: int = 512 * 512
+    max_area: int = 1024 * 1024
+    size_step: int = 64
+    aspect_range: tuple[float, float] = (0.5, 2.0)
+    min_text: int = 32
+    max_text: int = 256
+    channels: int = 128
+    text_dim: int = 4096
+    fixed_size: tuple[int, int] | None = None    # (h, w) pixels: every sample this size
+    fixed_text: int | None = None
+    samples: int | None = None                   # exact sample count (with fixed_size)
+    dtype: torch.dtype = torch.bfloat16
+    seed: int = 0
+
+
+class SyntheticDataset:
+    def __init__(self, cfg: SyntheticConfig = SyntheticConfig()):
+        self.cfg = cfg
+
+    def _draw_size(self, g: torch.Generator) -> tuple[int, int]:
+        c = self.cfg
+        if c.fixed_size is not None:
+            return c.fixed_size
+        area = c.min_area + (c.max_area - c.min_area) * torch.rand((), generator=g).item()
+        lo, hi = (math.log(a) for a in c.aspect_range)
+        aspect = math.exp(lo + (hi - lo) * torch.rand((), generator=g).item())  # w / h
+        h = max(c.size_step, int(round(math.sqrt(area / aspect) / c.size_step)) * c.size_step)
+        w = max(c.size_step, int(round(math.sqrt(area * aspect) / c.size_step)) * c.size_step)
+        return h, w
+
+    def plan(self, index: int, rank: int = 0) -> tuple[list[tuple[int, int]], list[int]]:
+        """Latent grids and text lengths of batch `index` on `rank` (no tensors yet)."""
+        c = self.cfg
+        g = torch.Generator().manual_seed(seed_of("synthetic-plan", c.seed, rank, index))
+        grids, texts, total = [], [], 0
+        while True:
+            h, w = self._draw_size(g)
+            t = c.fixed_text if c.fixed_text is not None else int(torch.randint(c.min_text, c.max_text + 1, (), generator=g))
+            n = (h // LATENT_FACTOR) * (w // LATENT_FACTOR) + t
+            if c.samples is not None:
+                if len(grids) == c.samples:
+                    break
+            elif grids and total + n > c.max_tokens:
+                break
+            grids.append((h // LATENT_FACTOR, w // LATENT_FACTOR))
+            texts.append(t)
+            total += n
+            if c.samples is None and total >= c.max_tokens:
+                break
+        return grids, texts
+
+    def materialize(self, index: int, rank: int = 0, world: int = 1, pin: bool = True) -> HostBatch:
+        c = self.cfg
+        grids, texts = self.plan(index, rank)
+        g = torch.Generator().manual_seed(seed_of("synthetic-data", c.seed, rank, index))
+        n_img = sum(h * w for h, w in grids)
+        n_txt = sum(texts)
+        latents = torch.randn(n_img, c.channels, generator=g).to(c.dtype)
+        text = torch.randn(n_txt, c.text_dim, generator=g).to(c.dtype)
+        batch = HostBatch(latents, text, torch.tensor(grids), torch.tensor(texts), index=index)
+        return batch.pin_memory() if pin else batch

@@ -20,7 +20,7 @@ _STATE = {"native": None}
 def _native_ready() -> bool:
     if _STATE["native"] is None:
         try:
-            _STATE["native"] = hasattr(native.load(), "attention_fwd")
+            _STATE["native"] = hasattr(native.load()._ops, "attention_fwd")
         except Exception:
             _STATE["native"] = False
     return _STATE["native"]

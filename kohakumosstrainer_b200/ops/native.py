@@ -41,8 +41,46 @@ def load(build_if_missing: bool = True):
         if not path.exists():
             raise RuntimeError(f"native library {path} is missing; run python -m kohakumosstrainer_b200.csrc.build")
         torch.ops.load_library(str(path))
-        _OPS = torch.ops.kmoss_b200
+        _OPS = _CountingOps(torch.ops.kmoss_b200)
     return _OPS
+
+
+# Kernel launches behind each op (own kernels only), for the launch counter benchmarks report.
+_LAUNCHES_PER_OP = {
+    "gemm": 1, "rms_norm_mod_fwd": 1, "rms_norm_mod_bwd": 1, "norm_weight_grad": 1, "seg_sum": 1, "rope_table": 1,
+    "qk_norm_rope_fwd": 1, "qk_norm_rope_bwd": 1, "situ_fwd": 1, "situ_bwd": 1, "gated_residual": 1, "seg_scale": 1,
+    "token_mse_fwd": 2, "token_mse_bwd": 1, "quantize_fp8_tensor": 3, "cast_fp8": 1, "quantize_fp8_rows": 1,
+    "adamw_multi": 1, "grad_norm_multi": 2, "ema_multi": 1, "attention_fwd": 1, "attention_bwd": 3,
+    "allreduce": 1,
+}
+LAUNCHES = {"count": 0}
+
+
+class _CountingOps:
+    """`torch.ops.kmoss_b200` with a launch counter: `LAUNCHES["count"]` grows by the number
+    of this library's kernels each call enqueues (a split-K GEMM counts its reduction too)."""
+
+    def __init__(self, ops):
+        self._ops = ops
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._ops, name)
+            n = _LAUNCHES_PER_OP.get(name, 0)
+            if n == 0:
+                fn = raw
+            elif name == "gemm":
+                def fn(*args, _raw=raw):
+                    LAUNCHES["count"] += 2 if args[-2] > 1 else 1
+                    return _raw(*args)
+            else:
+                def fn(*args, _raw=raw, _n=n):
+                    LAUNCHES["count"] += _n
+                    return _raw(*args)
+            self._cache[name] = fn
+        return fn
 
 
 def available() -> bool:

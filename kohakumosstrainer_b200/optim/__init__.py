@@ -1,0 +1,13 @@
+"""Optimisers (fused AdamW, Muon hybrid), schedules, EMA and the step bundle."""
+
+from .adamw import FusedAdamW
+from .bundle import Bundle, build_optimizer
+from .ema import ConstantEMA, PowerEMA
+from .groups import param_groups, weight_decay_rule
+from .muon import MuonHybrid, newton_schulz
+from .schedule import build_schedule
+
+__all__ = [
+    "FusedAdamW", "Bundle", "build_optimizer", "ConstantEMA", "PowerEMA", "param_groups", "weight_decay_rule",
+    "MuonHybrid", "newton_schulz", "build_schedule",
+]

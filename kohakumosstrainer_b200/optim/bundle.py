@@ -1,0 +1,160 @@
+"""Bundle: optimiser + schedule + gradient norm / clip / non-finite guard for one step.
+
+Order of a step (the reference's `bundle.step()`, `src/kohakumoss/training/optim/bundle/
+base.py:254-283`): finish the gradient reduction, take the fp32 global norm, agree on
+[loss, bad-flag] across ranks, read them with ONE host sync (`STEP_SYNC="step"`) or none
+(`"deferred"`: the skip flag stays on the device and the optimiser kernel reads it), clip,
+step, schedule, EMA. On CUDA the norm, the clip coefficient and the flag are produced by one
+multi-tensor launch over the gradient table and consumed by the optimiser launch.
+"""
+
+from __future__ import annotations
+
+from collections.abc import Callable
+
+import torch
+from torch import Tensor
+
+from .adamw import FusedAdamW, ParamTable
+from .groups import is_muon_param, param_groups
+from .muon import MuonHybrid
+from .schedule import build_schedule
+
+OPTIMIZERS = ("adamw", "adamw16", "adamw8bit", "adamw8bit_kernel", "muon", "prodigy", "schedule_free")
+
+
+def build_optimizer(named_params, name: str = "adamw", lr: float = 1e-4, betas=(0.9, 0.95), eps: float = 1e-8,
+                    weight_decay: float = 0.01, wd_rules: str = "moss", kwargs: dict | None = None,
+                    decay_to_one: tuple[str, ...] = (), lr_mul: dict | None = None, splits: dict | None = None):
+    """`OPTIMIZER` knob -> optimiser. `adamw16` / `adamw8bit*` map onto the fused AdamW with
+    fp32 masters (B200 has the memory for fp32 states; the low-memory state formats of the
+    reference exist to fit 24 GB cards)."""
+    named = [(n, p) for n, p in named_params if p.requires_grad]
+    kwargs = dict(kwargs or {})
+    if name not in OPTIMIZERS:
+        raise ValueError(f"OPTIMIZER {name!r} unknown (have {', '.join(OPTIMIZERS)})")
+    if name == "muon":
+        muon = [(n, p) for n, p in named if is_muon_param(n, p)]
+        rest = [(n, p) for n, p in named if not is_muon_param(n, p)]
+        groups = param_groups(rest, weight_decay, wd_rules, decay_to_one, lr_mul)
+        if muon:
+            sp = []
+            for n, p in muon:
+                s = 1
+                for pat, k in (splits or {"qkv": 3, "ffn_up_gate": 2}).items():
+                    if pat in n:
+                        s = k
+                sp.append(s)
+            groups.append(dict(params=[p for _, p in muon], use_muon=True, splits=sp, weight_decay=weight_decay))
+        return MuonHybrid(groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, **kwargs)
+    if name in ("prodigy", "schedule_free"):
+        raise NotImplementedError(f"OPTIMIZER={name} is not available in this build")
+    groups = param_groups(named, weight_decay, wd_rules, decay_to_one, lr_mul)
+    master = name in ("adamw16",) or kwargs.pop("master_weights", False)
+    return FusedAdamW(groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, master_weights=master)
+
+
+class Bundle:
+    def __init__(self, optimizer, params: list[Tensor], total_steps: int = 1000, schedule: dict | None = None,
+                 grad_clip: float = 1.0, step_sync: str = "step", reduce_flags: Callable | None = None,
+                 reduce_norm_sq: Callable | None = None, ema=None, finish_grads: Callable | None = None):
+        self.optimizer = optimizer
+        self.params = [p for p in params if p.requires_grad]
+        self.base_lrs = [g["lr"] for g in optimizer.param_groups]
+        self.factor = build_schedule(schedule, total_steps)
+        self.grad_clip = float(grad_clip)
+        self.step_sync = step_sync
+        self.reduce_flags = reduce_flags        # in-place SUM all-reduce of a small fp32 tensor
+        self.reduce_norm_sq = reduce_norm_sq    # SUM all-reduce of the squared norm (sharded grads)
+        self.finish_grads = finish_grads        # waits for the gradient reduction
+        self.ema = ema
+        self.step_index = 0
+        self.skipped = 0
+        self.last_loss = float("nan")
+        self.last_norm = float("nan")
+        self.last_ok = True
+        self._table: ParamTable | None = None
+        self._loss: Tensor | None = None
+        if ema is not None:
+            ema.attach_to(optimizer)
+
+    @property
+    def lr(self) -> float:
+        return float(self.optimizer.param_groups[0]["lr"])
+
+    def observe(self, loss: Tensor) -> None:
+        """Accumulate the (detached) loss of a micro-batch for logging and the finite check."""
+        loss = loss.detach().float()
+        self._loss = loss if self._loss is None else self._loss + loss
+
+    def _norm(self) -> tuple[Tensor, Tensor]:
+        """(stats fp32[3] = {norm, clip coefficient, sumsq}, nonfinite int32[1]) on device."""
+        grads = [p.grad for p in self.params if p.grad is not None]
+        dev = self.params[0].device
+        bad = torch.zeros(1, dtype=torch.int32, device=dev)
+        if dev.type == "cuda" and all(g.dtype in (torch.float32, torch.bfloat16) for g in grads):
+            from ..ops import native
+
+            entries = [dict(param=p.data, grad=p.grad) for p in self.params if p.grad is not None]
+            keys = tuple((e["param"].data_ptr(), e["grad"].data_ptr()) for e in entries)
+            if self._table is None or self._table.keys != keys:
+                self._table = ParamTable(entries, dev)
+            stats = native.load().grad_norm_multi(self._table.table, self._table.chunks, self.grad_clip, bad)
+        else:
+            sumsq = sum((g.float().square().sum() for g in grads), torch.zeros((), device=dev))
+            norm = sumsq.sqrt()
+            clip = torch.clamp(self.grad_clip / (norm + 1e-6), max=1.0) if self.grad_clip > 0 else torch.ones_like(norm)
+            stats = torch.stack((norm, clip, sumsq))
+            bad += (~torch.isfinite(norm)).to(torch.int32)
+        if self.reduce_norm_sq is not None:
+            sumsq = self.reduce_norm_sq(stats[2:3].clone())
+            norm = sumsq.sqrt()
+            clip = torch.clamp(self.grad_clip / (norm + 1e-6), max=1.0) if self.grad_clip > 0 else torch.ones_like(norm)
+            stats = torch.cat((norm, clip, sumsq))
+        return stats, bad
+
+    def step(self) -> bool:
+        """One optimiser step; returns False when the step was skipped (non-finite)."""
+        if self.finish_grads is not None:
+            self.finish_grads()
+        for g, base in zip(self.optimizer.param_groups, self.base_lrs):
+            g["lr"] = base * self.factor(self.step_index)
+        stats, bad = self._norm()
+        loss = self._loss if self._loss is not None else torch.zeros((), device=stats.device)
+        flags = torch.stack((loss.reshape(()), (bad[0] > 0).float() + (~torch.isfinite(stats[0])).float()))
+        if self.reduce_flags is not None:
+            flags = self.reduce_flags(flags)
+        skip = ((flags[1] > 0) | ~torch.isfinite(flags[0])).to(torch.int32).reshape(1)
+        if self.ema is not None:
+            self.ema.before_step(self.step_index)
+        self.optimizer.step(grad_scale=stats[1:2] if self.grad_clip > 0 else None, skip=skip)
+        ok = True
+        if self.step_sync == "step":
+            loss_v, norm_v, skip_v = torch.cat((flags[:1], stats[:1], skip.float())).tolist()  # the one host sync
+            ok = skip_v == 0
+            self.last_loss, self.last_norm, self.last_ok = loss_v, norm_v, ok
+            self.skipped += int(not ok)
+        else:
+            self._deferred = (flags[:1], stats[:1], skip)
+        if self.ema is not None and ok:
+            self.ema.update(self.step_index)
+        self.optimizer.zero_grad(set_to_none=False)
+        self._loss = None
+        self.step_index += 1
+        return ok
+
+    def settle(self) -> None:
+        """Read back the deferred step's numbers (STEP_SYNC="deferred": called when logging)."""
+        d = getattr(self, "_deferred", None)
+        if d is not None:
+            loss_v, norm_v, skip_v = torch.cat((d[0], d[1], d[2].float())).tolist()
+            self.last_loss, self.last_norm, self.last_ok = loss_v, norm_v, skip_v == 0
+            self._deferred = None
+
+    def state_dict(self) -> dict:
+        return {"optimizer": self.optimizer.state_dict(), "schedule": {"step": self.step_index}, "skipped": self.skipped}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.optimizer.load_state_dict(sd["optimizer"])
+        self.step_index = sd["schedule"]["step"]
+        self.skipped = sd.get("skipped", 0)

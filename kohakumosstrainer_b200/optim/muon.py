@@ -1,0 +1,141 @@
+"""Muon + AdamW hybrid: Nesterov momentum then Newton-Schulz orthogonalisation on the 2-D
+hidden matrices, fused AdamW everywhere else.
+
+Semantics of the reference (`src/kohakumoss/training/optim/optimizers/muon.py:23-138`):
+momentum 0.95 (Nesterov), 5 NS steps with coefficients (3.4445, -4.7750, 2.0315) in bf16,
+update scaled by `0.2 * sqrt(max(rows, cols))`, fused qkv split in 3 and up|gate split in 2,
+decoupled weight decay. On CUDA every NS product (`X X^T`, `A A`, `B X`) is a tcgen05 GEMM
+from this package with the `a X + B X` combination in the GEMM epilogue (residual input);
+`shard_gather` lets an FSDP engine hand in a callable that all-gathers the sharded update.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import Tensor
+
+from .adamw import FusedAdamW
+
+NS_COEFFS = (3.4445, -4.7750, 2.0315)
+
+
+def _ns_torch(x: Tensor, steps: int) -> Tensor:
+    a, b, c = NS_COEFFS
+    for _ in range(steps):
+        aa = x @ x.T
+        bb = b * aa + c * aa @ aa
+        x = a * x + bb @ x
+    return x
+
+
+def _ns_native(x: Tensor, steps: int) -> Tensor:
+    """Same iteration on the tcgen05 GEMM: A = X X^T; B = b A + c A A (residual epilogue);
+    X = a X + B X (residual epilogue). X is [m, k] bf16 with m <= k."""
+    from ..ops import native
+
+    a, b, c = NS_COEFFS
+    for _ in range(steps):
+        aa = native.gemm(x, x)                                         # [m, m] = X X^T
+        bb = native.gemm(aa, aa, b_mn=True, alpha=c, res=aa, beta=b)  # c A A + b A  (A symmetric)
+        x = native.gemm(bb, x, b_mn=True, res=x, beta=a)              # B X + a X
+    return x
+
+
+def newton_schulz(g: Tensor, steps: int = 5, eps: float = 1e-7) -> Tensor:
+    """Approximate orthogonal factor of a 2-D `g`, iterated in bf16."""
+    x = g.to(torch.bfloat16)
+    transposed = x.shape[0] > x.shape[1]
+    if transposed:
+        x = x.T
+    x = (x / (x.norm() + eps)).contiguous()
+    if x.is_cuda and x.shape[0] % 8 == 0 and x.shape[1] % 8 == 0 and x.shape[0] >= 64:
+        x = _ns_native(x, steps)
+    else:
+        x = _ns_torch(x, steps)
+    if transposed:
+        x = x.T
+    return x.to(g.dtype)
+
+
+class MuonHybrid(torch.optim.Optimizer):
+    """`use_muon` groups: Muon; other groups: the fused multi-tensor AdamW."""
+
+    def __init__(self, params, lr=5e-5, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0, momentum=0.95,
+                 nesterov=True, ns_steps=5, rms_match=0.2):
+        defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, momentum=momentum, nesterov=nesterov,
+                        ns_steps=ns_steps, rms_match=rms_match, use_muon=False, splits=None, lr_mul=1.0,
+                        decay_to_one=False)
+        super().__init__(params, defaults)
+        adam_groups = [g for g in self.param_groups if not g["use_muon"]]
+        self._adamw = None
+        if adam_groups:
+            self._adamw = FusedAdamW([dict(g) for g in adam_groups], lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        self.ema_buffers: dict[int, Tensor] = {}
+        self.ema_decay = 1.0
+        self.shard_gather = None  # callable(param, local_update) -> full update, set by sharded engines
+
+    def attach_ema(self, buffers: dict[int, Tensor]) -> None:
+        self.ema_buffers = buffers
+        if self._adamw is not None:
+            self._adamw.attach_ema(buffers)
+
+    @torch.no_grad()
+    def step(self, closure=None, grad_scale: Tensor | None = None, skip: Tensor | None = None):
+        if self._adamw is not None:
+            adam = [g for g in self.param_groups if not g["use_muon"]]
+            for inner, outer in zip(self._adamw.param_groups, adam):
+                inner["lr"] = outer["lr"]
+            self._adamw.ema_decay = self.ema_decay
+            self._adamw.step(grad_scale=grad_scale, skip=skip)
+        for group in self.param_groups:
+            if group["use_muon"]:
+                self._muon(group, grad_scale, skip)
+
+    def _muon(self, group, grad_scale, skip) -> None:
+        lr, wd, mom = group["lr"] * group.get("lr_mul", 1.0), group["weight_decay"], group["momentum"]
+        splits = group["splits"] or [1] * len(group["params"])
+        keep = None if skip is None else (skip == 0).to(torch.float32)
+        for p, n in zip(group["params"], splits):
+            if p.grad is None:
+                continue
+            g = p.grad.float()
+            if grad_scale is not None:
+                g = g * grad_scale
+            state = self.state[p]
+            if "momentum_buffer" not in state:
+                state["momentum_buffer"] = torch.zeros_like(g)
+            buf = state["momentum_buffer"]
+            new_buf = buf * mom + g
+            upd = g + new_buf * mom if group["nesterov"] else new_buf
+            if self.shard_gather is not None:
+                upd = self.shard_gather(p, upd)
+            ortho = torch.cat([newton_schulz(c, group["ns_steps"]) for c in upd.chunk(n, 0)], 0)
+            if self.shard_gather is not None:
+                ortho = self.shard_gather(p, ortho, scatter=True)
+            rows = p.shape[0] // n if self.shard_gather is None else ortho.shape[0] // n
+            scale = group["rms_match"] * math.sqrt(max(rows, p.shape[1]))
+            new_p = p.float() * (1 - lr * wd) - ortho.float() * (lr * scale)
+            if keep is not None:  # non-finite step: leave parameter and momentum untouched
+                new_p = torch.where(keep.bool(), new_p, p.float())
+                new_buf = torch.where(keep.bool(), new_buf, buf)
+            buf.copy_(new_buf)
+            p.copy_(new_p.to(p.dtype))
+            ema = self.ema_buffers.get(id(p))
+            if ema is not None:
+                d = 1 - self.ema_decay
+                ema.add_((p.float() - ema) * (d if keep is None else d * keep))
+
+    def state_dict(self):
+        sd = super().state_dict()
+        if self._adamw is not None:
+            sd["kmoss_adamw"] = self._adamw.state_dict()
+        return sd
+
+    def load_state_dict(self, sd):
+        sd = dict(sd)
+        inner = sd.pop("kmoss_adamw", None)
+        super().load_state_dict(sd)
+        if inner is not None and self._adamw is not None:
+            self._adamw.load_state_dict(inner)

@@ -1,0 +1,93 @@
+"""One micro-batch of rectified-flow training on a packed batch.
+
+`DeviceBatcher` moves a pinned `HostBatch` to the device on a copy stream, one step ahead of
+compute; `TrainStep` draws sigma on a CPU generator seeded by (seed, rank) and noise on a
+device generator, noises the latents, runs the backbone and returns the token-loss SUM divided
+by the global image-token count of the optimiser step
+(`src/kohakumoss/training/step.py:123-383` in the reference).
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from ..data.types import DeviceBatch, HostBatch
+from ..diffusion import TIMESTEPS, WEIGHTINGS, noise_latents, token_loss
+from ..utils.seeds import seed_of
+
+
+class DeviceBatcher:
+    """Host -> device staging with one batch of lookahead on a side stream."""
+
+    def __init__(self, device, latent_dtype=torch.float32, text_dtype=torch.bfloat16):
+        self.device = torch.device(device)
+        self.latent_dtype, self.text_dtype = latent_dtype, text_dtype
+        self.stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+        self._pending: tuple[DeviceBatch, object] | None = None
+        self.h2d_bytes = 0
+
+    def _move(self, hb: HostBatch) -> tuple[DeviceBatch, object]:
+        if self.stream is None:
+            return hb.to_device(self.device, self.latent_dtype, self.text_dtype), None
+        with torch.cuda.stream(self.stream):
+            db = hb.to_device(self.device, self.latent_dtype, self.text_dtype)
+            ev = torch.cuda.Event()
+            ev.record(self.stream)
+        return db, ev
+
+    def prefetch(self, hb: HostBatch) -> None:
+        self._pending = self._move(hb)
+
+    def __call__(self, hb: HostBatch | None = None) -> DeviceBatch:
+        """The prefetched batch if there is one, else `hb` moved now."""
+        db, ev = self._pending if self._pending is not None else self._move(hb)
+        self._pending = None
+        if ev is not None:
+            torch.cuda.current_stream(self.device).wait_event(ev)
+            for t in (db.latents, db.text):
+                t.record_stream(torch.cuda.current_stream(self.device))
+        self.h2d_bytes += db.h2d_bytes
+        return db
+
+
+class TrainStep:
+    def __init__(self, model, device, timestep="moss", timestep_kwargs=None, loss="mse", loss_kwargs=None,
+                 weighting="none", seed: int = 0, rank: int = 0, compute_dtype=torch.bfloat16):
+        self.model = model
+        self.device = torch.device(device)
+        self.sampler = TIMESTEPS.get(timestep)(**(timestep_kwargs or {})) if isinstance(timestep, str) else timestep
+        self.loss, self.loss_kwargs = loss, dict(loss_kwargs or {})
+        self.weighting = WEIGHTINGS.get(weighting)
+        self.compute_dtype = compute_dtype
+        self.sigma_gen = torch.Generator().manual_seed(seed_of("sigma", seed, rank))
+        self.noise_gen = torch.Generator(self.device).manual_seed(seed_of("noise", seed, rank))
+        self.step_index = 0
+
+    def draw_sigma(self, batch: int) -> Tensor:
+        """fp32 [B] on the device; drawn on the host generator, copied through pinned memory."""
+        sigma = self.sampler.sample(batch, self.sigma_gen, self.step_index)
+        if self.device.type == "cuda":
+            return sigma.pin_memory().to(self.device, non_blocking=True)
+        return sigma
+
+    def __call__(self, batch: DeviceBatch, denom: Tensor | float, sigma: Tensor | None = None) -> Tensor:
+        """Loss of this micro-batch, already divided by the step's global token count."""
+        seq = batch.seq
+        if sigma is None:
+            sigma = self.draw_sigma(seq.batch)
+        z0 = batch.latents.float()
+        eps = torch.randn(z0.shape, generator=self.noise_gen, device=self.device, dtype=torch.float32)
+        z, target = noise_latents(z0, eps, sigma, seq.seg_img)
+        v = self.model(z.to(self.compute_dtype), batch.text.to(self.compute_dtype), sigma, seq)
+        weight = self.weighting(sigma)
+        total = token_loss(self.model.ops, v, target, seq.seg_img, weight, None, self.loss, **self.loss_kwargs)
+        return total / denom
+
+    def rng_state(self) -> dict:
+        return {"sigma": self.sigma_gen.get_state(), "noise": self.noise_gen.get_state(), "step": self.step_index}
+
+    def load_rng_state(self, state: dict) -> None:
+        self.sigma_gen.set_state(state["sigma"])
+        self.noise_gen.set_state(state["noise"].to("cpu") if hasattr(state["noise"], "to") else state["noise"])
+        self.step_index = state.get("step", 0)

@@ -1,0 +1,142 @@
+"""Trainer: the public training API (build model + adapters + optimiser, run steps).
+
+`Trainer(TrainerConfig(...))` is what `scripts/train/moss.py`, `bench.py` and the tests use;
+`train_step(host_batches)` performs one optimiser step over GRAD_ACC micro-batches: H2D copy
+from pinned memory, noise, forward, backward, gradient reduction (DDP), norm / clip / step /
+EMA, and returns the loss read back from the device. It mirrors the reference's native driver
+loop (`src/kohakumoss/training/drivers/native.py:53-99`, `drivers/common.py:59-99`).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from .. import adapters as adapters_pkg
+from ..data.types import HostBatch
+from ..diffusion import TokenNormalizer
+from ..models import build_backbone
+from ..models.build import resolve_arch
+from ..models.runners import build_runner
+from ..optim import Bundle, ConstantEMA, build_optimizer
+from ..quant import apply_base_precision
+from .step import DeviceBatcher, TrainStep
+
+
+@dataclass
+class TrainerConfig:
+    variant: str = "base"
+    arch_overrides: dict = field(default_factory=dict)
+    algo: str = "lora"                 # lora | loha | lokr | oft | ia3 | dora | full
+    preset: str = "attn-mlp"
+    dim: int = 8
+    alpha: float = 8.0
+    algo_kwargs: dict = field(default_factory=dict)
+    adapter_mode: str = "bypass"
+    base_precision: str = "fp8_compute"  # auto | compute | fp8_compute
+    fp8_recipe: str = "tensor"
+    precision: str = "bf16"
+    optimizer: str = "adamw"
+    optimizer_kwargs: dict = field(default_factory=dict)
+    lr: float = 1e-4
+    betas: tuple = (0.9, 0.95)
+    eps: float = 1e-8
+    weight_decay: float = 0.01
+    wd_rules: str = "moss"
+    schedule: dict = field(default_factory=lambda: {"mode": "cosine", "warmup": 100, "end": -1})
+    grad_clip: float = 1.0
+    step_sync: str = "step"
+    ema: float = 0.0
+    steps: int = 1000
+    grad_acc: int = 1
+    checkpoint: str = "none"           # activation checkpointing mode
+    timestep: str = "moss"
+    timestep_kwargs: dict = field(default_factory=dict)
+    loss: str = "mse"
+    weighting: str = "none"
+    seed: int = 0
+    kernels: dict = field(default_factory=dict)
+    parallel: str = "none"             # none | ddp | fsdp (engines attach through `hooks`)
+    ddp_bucket_mb: int = 25
+    ddp_reduce_dtype: str = "fp32"
+    ddp_backend: str = "kohakumoss"
+
+
+class Trainer:
+    def __init__(self, cfg: TrainerConfig, device="cuda", rank: int = 0, world: int = 1, model=None):
+        self.cfg, self.rank, self.world = cfg, rank, world
+        self.device = torch.device(device)
+        dtype = {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}[cfg.precision]
+        if self.device.type == "cpu" and dtype != torch.float32:
+            dtype = torch.float32
+        self.dtype = dtype
+        arch = resolve_arch(cfg.variant, cfg.arch_overrides)
+        self.model = model if model is not None else build_backbone(arch, device=self.device, dtype=dtype, seed=cfg.seed)
+        if cfg.kernels:
+            from ..ops import resolve_ops
+
+            self.model.bind_ops(resolve_ops(self.device, cfg.kernels))
+        self.model.set_runner(build_runner(cfg.checkpoint, arch.depth))
+        self.adapters = None
+        if cfg.algo == "full":
+            apply_base_precision(self.model, "auto")
+            for p in self.model.parameters():
+                p.requires_grad_(True)
+            named = list(self.model.named_parameters())
+        else:
+            apply_base_precision(self.model, cfg.base_precision, cfg.fp8_recipe)
+            acfg = adapters_pkg.AdapterConfig(
+                algo=cfg.algo, preset=cfg.preset, dim=cfg.dim, alpha=cfg.alpha, algo_kwargs=cfg.algo_kwargs,
+                mode=cfg.adapter_mode, seed=cfg.seed, dtype=dtype,
+            )
+            self.adapters = adapters_pkg.apply(self.model, acfg)
+            named = [(n, p) for n, p in self.adapters.named_parameters() if p.requires_grad]
+        self.named_trainable = named
+        self.params = [p for _, p in named]
+        self.parallel = None
+        reduce_flags = reduce_tokens = None
+        finish = None
+        if cfg.parallel == "ddp" and world > 1:
+            from ..parallel.ddp import GradReducer, all_reduce_sum, broadcast_params
+
+            broadcast_params(self.params)
+            self.parallel = GradReducer(self.params, bucket_mb=cfg.ddp_bucket_mb, reduce_dtype=cfg.ddp_reduce_dtype,
+                                        backend=cfg.ddp_backend, device=self.device)
+            reduce_flags = reduce_tokens = all_reduce_sum
+            finish = self.parallel.finish
+        opt = build_optimizer(named, cfg.optimizer, cfg.lr, cfg.betas, cfg.eps, cfg.weight_decay, cfg.wd_rules,
+                              cfg.optimizer_kwargs)
+        self.ema = ConstantEMA(named, (cfg.ema,)) if cfg.ema > 0 else None
+        self.bundle = Bundle(opt, self.params, cfg.steps, cfg.schedule, cfg.grad_clip, cfg.step_sync,
+                             reduce_flags=reduce_flags, ema=self.ema, finish_grads=finish)
+        self.normalizer = TokenNormalizer(reduce_tokens, 1)
+        self.step_fn = TrainStep(self.model, self.device, cfg.timestep, cfg.timestep_kwargs, cfg.loss, None,
+                                 cfg.weighting, cfg.seed, rank, dtype)
+        self.batcher = DeviceBatcher(self.device, torch.float32, dtype)
+        self.tokens_seen = 0
+        self.samples_seen = 0
+
+    def train_step(self, host_batches: list[HostBatch] | HostBatch, next_batch: HostBatch | None = None) -> dict:
+        """One optimiser step over the given micro-batches. Returns host-side numbers
+        (`loss`, `grad_norm`, `ok`, `image_tokens`); reading `loss` is the step's D2H sync."""
+        if isinstance(host_batches, HostBatch):
+            host_batches = [host_batches]
+        count = sum(hb.image_tokens for hb in host_batches)
+        denom = self.normalizer.denominator(count, self.device)
+        n = len(host_batches)
+        for i, hb in enumerate(host_batches):
+            batch = self.batcher(hb)
+            nxt = host_batches[i + 1] if i + 1 < n else next_batch
+            if nxt is not None:
+                self.batcher.prefetch(nxt)
+            if self.parallel is not None:
+                self.parallel.start(last=i == n - 1)
+            loss = self.step_fn(batch, denom)
+            loss.backward()
+            self.bundle.observe(loss)
+        ok = self.bundle.step()
+        self.step_fn.step_index += 1
+        self.tokens_seen += count
+        self.samples_seen += sum(hb.samples for hb in host_batches)
+        return {"loss": self.bundle.last_loss, "grad_norm": self.bundle.last_norm, "ok": ok, "image_tokens": count}
