@@ -8,6 +8,7 @@
 #include <cmath>
 #include <optional>
 
+#include "attention_sm100.cuh"
 #include "blockops.cuh"
 #include "gemm_sm100.cuh"
 #include "optim.cuh"
@@ -374,9 +375,33 @@ void ema_multi(const Tensor& table, const Tensor& chunks, double decay, const op
                                  cptr<int>(skip), cur_stream()));
 }
 
+
+// ---- attention ---------------------------------------------------------------------------
+void check_qkv(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 3 && t.size(2) == 128 && t.stride(2) == 1 &&
+                  t.stride(1) == 128 && t.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0,
+              "attention: ", name, " must be bf16 [N, H, 128] with contiguous heads and 16-byte aligned rows");
+}
+
+void attention_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& tiles, double scale, Tensor o,
+                   const optional<Tensor>& lse) {
+  c10::cuda::CUDAGuard guard(q.device());
+  check_qkv(q, "q"); check_qkv(k, "k"); check_qkv(v, "v"); check_qkv(o, "o");
+  TORCH_CHECK(tiles.scalar_type() == at::kInt && tiles.is_contiguous() && tiles.dim() == 2 && tiles.size(1) == 4, "attention: tiles int32 [T, 4]");
+  kmoss::AttnArgs a{};
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.o = o.data_ptr();
+  a.ldq = q.stride(0); a.ldk = k.stride(0); a.ldv = v.stride(0); a.ldo = o.stride(0);
+  a.lse = mptr<float>(lse);
+  a.tiles = tiles.data_ptr<int>(); a.n_tiles = (int)tiles.size(0);
+  a.n_rows = (int)q.size(0); a.heads = (int)q.size(1); a.scale = (float)scale;
+  a.status = status_tensor().data_ptr<int>();
+  KM_CHECK_CUDA(kmoss::attention_fwd(a, cur_stream()));
+}
+
 }  // namespace
 
 TORCH_LIBRARY(kmoss_b200, m) {
+  m.def("attention_fwd(Tensor q, Tensor k, Tensor v, Tensor tiles, float scale, Tensor(a!) o, Tensor(b!)? lse) -> ()", &attention_fwd);
   m.def("opt_record_bytes() -> int", &opt_record_bytes);
   m.def("opt_chunk_elems() -> int", &opt_chunk_elems);
   m.def("adamw_multi(Tensor table, Tensor chunks, float lr, float beta1, float beta2, float eps, int step, "
