@@ -18,6 +18,8 @@
 
 #include "attention_sm100.cuh"
 
+#include <stdio.h>
+
 #include "common.cuh"
 #include "tma_host.cuh"
 
@@ -255,6 +257,435 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
 }
 
+
+// =========================================================================================
+// Backward.  delta = rowsum(dO * O);  P = exp2(S * sc - lse);  dS = P * (dP - delta)
+//   dQ kernel   : CTA = 128 query rows, loops over 64-key tiles:  S = Q K^T, dP = dO V^T,
+//                 dQ += dS K            (dS: bf16 in shared memory, dQ: fp32 in TMEM)
+//   dK/dV kernel: CTA = 128 keys, loops over 64-query tiles:      S^T = K Q^T, dP^T = V dO^T,
+//                 dV += P^T dO, dK += dS^T Q
+// Two kernels instead of one with fp32 atomics on dQ: every output element has exactly one
+// writer, so gradients are bitwise reproducible.
+// =========================================================================================
+constexpr int BWD_THREADS = 192;
+
+__global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* o, long ldo, const __nv_bfloat16* dout,
+                                                         long lddo, float* delta, int n_rows, int heads) {
+  const long wid = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long)n_rows * heads) return;
+  const int row = (int)(wid / heads), head = (int)(wid - (long)row * heads);
+  const uint2 a = *reinterpret_cast<const uint2*>(o + (size_t)row * ldo + head * DH + 4 * lane);
+  const uint2 b = *reinterpret_cast<const uint2*>(dout + (size_t)row * lddo + head * DH + 4 * lane);
+  const float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), b0 = unpack_bf16(b.x), b1 = unpack_bf16(b.y);
+  float s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+  s = warp_sum(s);
+  if (lane == 0) delta[(size_t)head * n_rows + row] = s;
+}
+
+// ---- dQ ------------------------------------------------------------------------------------
+constexpr int DQ_SM_Q = 0;                      // 32 KB
+constexpr int DQ_SM_DO = 32768;                 // 32 KB
+constexpr int DQ_SM_KV = 65536;                 // 2 stages x (K 16 KB + V 16 KB)
+constexpr int DQ_SM_DS = DQ_SM_KV + 65536;      // 2 buffers x 16 KB
+constexpr int DQ_SM_BAR = DQ_SM_DS + 32768;
+constexpr int DQ_SMEM = DQ_SM_BAR + 256;
+constexpr uint32_t DQ_TM_S = 0, DQ_TM_DP = 128, DQ_TM_DQ = 256, DQ_TM_COLS = 512;
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                   const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                   const AttnBwdArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sbase = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DQ_SM_BAR);
+  const uint32_t bar0 = smem_u32(bars);
+  // 0 qdo_full | 1,2 k_full | 3,4 v_full | 5,6 kv_empty | 7,8 sdp_full | 9,10 ds_full | 11,12 ds_empty | 13 done
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int q0 = a.tiles[4 * tile + 0], seg_start = a.tiles[4 * tile + 1], seg_end = a.tiles[4 * tile + 2];
+  const int n_kv = (seg_end - seg_start + BN - 1) / BN;
+
+  if (threadIdx.x == 0) {
+    if ((sbase & 1023u) != 0) report_status(a.status, STATUS_BAD_ARGUMENT, 901, (int)(sbase & 1023u));
+    for (int i = 0; i < 14; ++i) mbar_init(bar(i), (i == 9 || i == 10) ? 4 : 1);
+    *abort_flag = (sbase & 1023u) != 0 ? 1 : 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), DQ_TM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one() && !*abort_flag) {
+      mbar_expect_tx(bar(0), 65536);
+      tma_load_2d(sbase + DQ_SM_Q, &map_q, bar(0), head * DH, q0);
+      tma_load_2d(sbase + DQ_SM_Q + 16384, &map_q, bar(0), head * DH + 64, q0);
+      tma_load_2d(sbase + DQ_SM_DO, &map_do, bar(0), head * DH, q0);
+      tma_load_2d(sbase + DQ_SM_DO + 16384, &map_do, bar(0), head * DH + 64, q0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(bar(5 + st), ((j >> 1) & 1) ^ 1, abort_flag, a.status, 800 + st)) break;
+        const uint32_t kdst = sbase + DQ_SM_KV + st * 32768, vdst = kdst + 16384;
+        const int row = seg_start + j * BN;
+        mbar_expect_tx(bar(1 + st), 16384);
+        tma_load_2d(kdst, &map_k, bar(1 + st), head * DH, row);
+        tma_load_2d(kdst + 8192, &map_k, bar(1 + st), head * DH + 64, row);
+        mbar_expect_tx(bar(3 + st), 16384);
+        tma_load_2d(vdst, &map_v, bar(3 + st), head * DH, row);
+        tma_load_2d(vdst + 8192, &map_v, bar(3 + st), head * DH + 64, row);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one() && !*abort_flag) {
+      constexpr uint32_t idesc_s = umma_idesc(1, 1, 0, 0, BM, BN);
+      constexpr uint32_t idesc_dq = umma_idesc(1, 1, 0, 1, BM, DH);
+      auto issue_sdp = [&](int j) {
+        const int st = j & 1;
+        const uint32_t kaddr = sbase + DQ_SM_KV + st * 32768, vaddr = kaddr + 16384;
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          const uint64_t qd = umma_smem_desc(sbase + DQ_SM_Q + kb * 16384, 16, 1024);
+          const uint64_t kd = umma_smem_desc(kaddr + kb * 8192, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + DQ_TM_S + st * BN, qd + 2 * k, kd + 2 * k, idesc_s, (kb | k) != 0);
+        }
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          const uint64_t dd = umma_smem_desc(sbase + DQ_SM_DO + kb * 16384, 16, 1024);
+          const uint64_t vd = umma_smem_desc(vaddr + kb * 8192, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + DQ_TM_DP + st * BN, dd + 2 * k, vd + 2 * k, idesc_s, (kb | k) != 0);
+        }
+        tc_commit(bar(7 + st));
+      };
+      bool ok = mbar_wait(bar(0), 0, abort_flag, a.status, 810) && mbar_wait(bar(1), 0, abort_flag, a.status, 811) &&
+                mbar_wait(bar(3), 0, abort_flag, a.status, 812);
+      if (ok) {
+        tc_fence_after();
+        issue_sdp(0);
+      }
+      int j = 0;
+      for (; ok && j < n_kv; ++j) {
+        const int st = j & 1;
+        if (j + 1 < n_kv) {
+          const int sn = (j + 1) & 1, pn = ((j + 1) >> 1) & 1;
+          if (!mbar_wait(bar(1 + sn), pn, abort_flag, a.status, 813) || !mbar_wait(bar(3 + sn), pn, abort_flag, a.status, 814)) break;
+          tc_fence_after();
+          issue_sdp(j + 1);
+        }
+        if (!mbar_wait(bar(9 + st), (j >> 1) & 1, abort_flag, a.status, 815)) break;
+        tc_fence_after();
+        const uint64_t sd = umma_smem_desc(sbase + DQ_SM_DS + st * 16384, 16, 1024);
+        const uint64_t kd = umma_smem_desc(sbase + DQ_SM_KV + st * 32768, 8192, 1024);  // K_j read MN-major
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + DQ_TM_DQ, sd + 2 * k, kd + 128 * k, idesc_dq, (j | k) != 0);
+        tc_commit(bar(5 + st));
+        tc_commit(bar(11 + st));
+      }
+      if (ok && j == n_kv) tc_commit(bar(13));
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int row = q0 + r;
+    const bool live = row < seg_end;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const float sc = a.scale * LOG2E;
+    const float lse = live ? a.lse[(size_t)head * a.n_rows + row] : INFINITY;
+    const float dl = live ? a.delta[(size_t)head * a.n_rows + row] : 0.f;
+    bool ok = !*abort_flag;
+    for (int j = 0; ok && j < n_kv; ++j) {
+      const int st = j & 1;
+      if (!mbar_wait(bar(7 + st), (j >> 1) & 1, abort_flag, a.status, 820 + st)) { ok = false; break; }
+      tc_fence_after();
+      const int valid = min(BN, seg_end - (seg_start + j * BN));
+      uint32_t pk[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s_[32], d_[32];
+        tmem_ld_32x32(tmem + lane_base + DQ_TM_S + st * BN + half * 32, s_);
+        tmem_ld_32x32(tmem + lane_base + DQ_TM_DP + st * BN + half * 32, d_);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float v0 = 0.f, v1 = 0.f;
+          const int c0 = half * 32 + 2 * i;
+          if (c0 < valid) v0 = exp2f(__uint_as_float(s_[2 * i]) * sc - lse) * (__uint_as_float(d_[2 * i]) - dl);
+          if (c0 + 1 < valid) v1 = exp2f(__uint_as_float(s_[2 * i + 1]) * sc - lse) * (__uint_as_float(d_[2 * i + 1]) - dl);
+          pk[half * 16 + i] = pack_bf16(v0, v1);
+        }
+      }
+      if (!mbar_wait(bar(11 + st), ((j >> 1) & 1) ^ 1, abort_flag, a.status, 830 + st)) { ok = false; break; }
+      uint8_t* prow = smem + DQ_SM_DS + st * 16384 + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(9 + st));
+    }
+    if (ok && mbar_wait(bar(13), 0, abort_flag, a.status, 840)) {
+      tc_fence_after();
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(a.dq) + (size_t)(live ? row : 0) * a.lddq + head * DH;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32(tmem + lane_base + DQ_TM_DQ + c * 32, o);
+        tmem_ld_wait();
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(o[8 * i]) * a.scale, __uint_as_float(o[8 * i + 1]) * a.scale);
+            w.y = pack_bf16(__uint_as_float(o[8 * i + 2]) * a.scale, __uint_as_float(o[8 * i + 3]) * a.scale);
+            w.z = pack_bf16(__uint_as_float(o[8 * i + 4]) * a.scale, __uint_as_float(o[8 * i + 5]) * a.scale);
+            w.w = pack_bf16(__uint_as_float(o[8 * i + 6]) * a.scale, __uint_as_float(o[8 * i + 7]) * a.scale);
+            *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = w;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, DQ_TM_COLS);
+  }
+}
+
+// ---- dK / dV -------------------------------------------------------------------------------
+constexpr int BQ = 64;                           // query rows per iteration
+constexpr int KV_SM_K = 0;                       // 32 KB: 2 k-blocks x [128 keys][128 B]
+constexpr int KV_SM_V = 32768;                   // 32 KB
+constexpr int KV_SM_QDO = 65536;                 // 2 stages x (Q 16 KB + dO 16 KB)
+constexpr int KV_SM_PDS = KV_SM_QDO + 65536;     // 2 buffers x (P^T 16 KB + dS^T 16 KB)
+constexpr int KV_SM_VEC = KV_SM_PDS + 65536;     // per warp: 2 x (lse[64] | delta[64]) fp32
+constexpr int KV_SM_BAR = KV_SM_VEC + 4096;
+constexpr int KV_SMEM = KV_SM_BAR + 256;
+constexpr uint32_t KV_TM_S = 0, KV_TM_DP = 128, KV_TM_DV = 256, KV_TM_DK = 384, KV_TM_COLS = 512;
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                     const AttnBwdArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sbase = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + KV_SM_BAR);
+  const uint32_t bar0 = smem_u32(bars);
+  // 0 kv_full | 1,2 qdo_full | 3,4 qdo_empty | 5,6 sdp_full | 7,8 pds_full | 9,10 pds_empty | 11 done
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* vec = reinterpret_cast<float*>(smem + KV_SM_VEC);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int k0 = a.tiles[4 * tile + 0], seg_start = a.tiles[4 * tile + 1], seg_end = a.tiles[4 * tile + 2];
+  const int n_q = (seg_end - seg_start + BQ - 1) / BQ;
+
+  if (threadIdx.x == 0) {
+    if ((sbase & 1023u) != 0) report_status(a.status, STATUS_BAD_ARGUMENT, 902, (int)(sbase & 1023u));
+    for (int i = 0; i < 12; ++i) mbar_init(bar(i), (i == 7 || i == 8) ? 4 : 1);
+    *abort_flag = (sbase & 1023u) != 0 ? 1 : 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), KV_TM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one() && !*abort_flag) {
+      mbar_expect_tx(bar(0), 65536);
+      tma_load_2d(sbase + KV_SM_K, &map_k, bar(0), head * DH, k0);
+      tma_load_2d(sbase + KV_SM_K + 16384, &map_k, bar(0), head * DH + 64, k0);
+      tma_load_2d(sbase + KV_SM_V, &map_v, bar(0), head * DH, k0);
+      tma_load_2d(sbase + KV_SM_V + 16384, &map_v, bar(0), head * DH + 64, k0);
+      for (int i = 0; i < n_q; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(bar(3 + st), ((i >> 1) & 1) ^ 1, abort_flag, a.status, 850 + st)) break;
+        const uint32_t qdst = sbase + KV_SM_QDO + st * 32768, ddst = qdst + 16384;
+        const int row = seg_start + i * BQ;
+        mbar_expect_tx(bar(1 + st), 32768);
+        tma_load_2d(qdst, &map_q, bar(1 + st), head * DH, row);
+        tma_load_2d(qdst + 8192, &map_q, bar(1 + st), head * DH + 64, row);
+        tma_load_2d(ddst, &map_do, bar(1 + st), head * DH, row);
+        tma_load_2d(ddst + 8192, &map_do, bar(1 + st), head * DH + 64, row);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one() && !*abort_flag) {
+      constexpr uint32_t idesc_s = umma_idesc(1, 1, 0, 0, BM, BQ);
+      constexpr uint32_t idesc_acc = umma_idesc(1, 1, 0, 1, BM, DH);
+      auto issue_sdp = [&](int i) {
+        const int st = i & 1;
+        const uint32_t qaddr = sbase + KV_SM_QDO + st * 32768, daddr = qaddr + 16384;
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          const uint64_t kd = umma_smem_desc(sbase + KV_SM_K + kb * 16384, 16, 1024);
+          const uint64_t qd = umma_smem_desc(qaddr + kb * 8192, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + KV_TM_S + st * BQ, kd + 2 * k, qd + 2 * k, idesc_s, (kb | k) != 0);
+        }
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          const uint64_t vd = umma_smem_desc(sbase + KV_SM_V + kb * 16384, 16, 1024);
+          const uint64_t dd = umma_smem_desc(daddr + kb * 8192, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + KV_TM_DP + st * BQ, vd + 2 * k, dd + 2 * k, idesc_s, (kb | k) != 0);
+        }
+        tc_commit(bar(5 + st));
+      };
+      bool ok = mbar_wait(bar(0), 0, abort_flag, a.status, 860) && mbar_wait(bar(1), 0, abort_flag, a.status, 861);
+      if (ok) {
+        tc_fence_after();
+        issue_sdp(0);
+      }
+      int i = 0;
+      for (; ok && i < n_q; ++i) {
+        const int st = i & 1;
+        if (i + 1 < n_q) {
+          if (!mbar_wait(bar(1 + ((i + 1) & 1)), ((i + 1) >> 1) & 1, abort_flag, a.status, 862)) break;
+          tc_fence_after();
+          issue_sdp(i + 1);
+        }
+        if (!mbar_wait(bar(7 + st), (i >> 1) & 1, abort_flag, a.status, 863)) break;
+        tc_fence_after();
+        const uint32_t qaddr = sbase + KV_SM_QDO + st * 32768, daddr = qaddr + 16384;
+        const uint64_t pd = umma_smem_desc(sbase + KV_SM_PDS + st * 32768, 16, 1024);
+        const uint64_t sd = umma_smem_desc(sbase + KV_SM_PDS + st * 32768 + 16384, 16, 1024);
+        const uint64_t dod = umma_smem_desc(daddr, 8192, 1024);  // dO_i read MN-major
+        const uint64_t qd = umma_smem_desc(qaddr, 8192, 1024);   // Q_i read MN-major
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + KV_TM_DV, pd + 2 * k, dod + 128 * k, idesc_acc, (i | k) != 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + KV_TM_DK, sd + 2 * k, qd + 128 * k, idesc_acc, (i | k) != 0);
+        tc_commit(bar(3 + st));
+        tc_commit(bar(9 + st));
+      }
+      if (ok && i == n_q) tc_commit(bar(11));
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // key row inside the tile
+    const int key = k0 + r;
+    const bool live = key < seg_end;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const float sc = a.scale * LOG2E;
+    bool ok = !*abort_flag;
+    for (int i = 0; ok && i < n_q; ++i) {
+      const int st = i & 1;
+      {  // each warp stages lse / delta of this query tile for its own 32 rows (no CTA-wide barrier)
+        float* mine = vec + (quarter * 2 + st) * 128;
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = lane * 4 + u;  // 0..63 lse, 64..127 delta
+          const int qrow = seg_start + i * BQ + (idx & 63);
+          float v;
+          if (idx < 64) v = qrow < seg_end ? a.lse[(size_t)head * a.n_rows + qrow] : INFINITY;
+          else v = qrow < seg_end ? a.delta[(size_t)head * a.n_rows + qrow] : 0.f;
+          mine[idx] = v;
+        }
+        __syncwarp();
+      }
+      const float* lse = vec + (quarter * 2 + st) * 128;
+      const float* dl = lse + 64;
+      if (!mbar_wait(bar(5 + st), (i >> 1) & 1, abort_flag, a.status, 870 + st)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t pkp[32], pkd[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s_[32], d_[32];
+        tmem_ld_32x32(tmem + lane_base + KV_TM_S + st * BQ + half * 32, s_);
+        tmem_ld_32x32(tmem + lane_base + KV_TM_DP + st * BQ + half * 32, d_);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const int c0 = half * 32 + 2 * c;
+          const float p0 = exp2f(__uint_as_float(s_[2 * c]) * sc - lse[c0]);
+          const float p1 = exp2f(__uint_as_float(s_[2 * c + 1]) * sc - lse[c0 + 1]);
+          const float g0 = p0 * (__uint_as_float(d_[2 * c]) - dl[c0]);
+          const float g1 = p1 * (__uint_as_float(d_[2 * c + 1]) - dl[c0 + 1]);
+          pkp[half * 16 + c] = pack_bf16(p0, p1);
+          pkd[half * 16 + c] = pack_bf16(g0, g1);
+        }
+      }
+      if (!mbar_wait(bar(9 + st), ((i >> 1) & 1) ^ 1, abort_flag, a.status, 880 + st)) { ok = false; break; }
+      uint8_t* prow = smem + KV_SM_PDS + st * 32768 + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const int off = (c ^ (r & 7)) << 4;
+        *reinterpret_cast<uint4*>(prow + off) = make_uint4(pkp[4 * c], pkp[4 * c + 1], pkp[4 * c + 2], pkp[4 * c + 3]);
+        *reinterpret_cast<uint4*>(prow + 16384 + off) = make_uint4(pkd[4 * c], pkd[4 * c + 1], pkd[4 * c + 2], pkd[4 * c + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(7 + st));
+    }
+    if (ok && mbar_wait(bar(11), 0, abort_flag, a.status, 890)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const float mul = which == 0 ? 1.f : a.scale;
+        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(which == 0 ? a.dv : a.dk);
+        const long ld = which == 0 ? a.lddv : a.lddk;
+        __nv_bfloat16* orow = base + (size_t)(live ? key : 0) * ld + head * DH;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem + lane_base + (which == 0 ? KV_TM_DV : KV_TM_DK) + c * 32, o);
+          tmem_ld_wait();
+          if (live) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(o[8 * j]) * mul, __uint_as_float(o[8 * j + 1]) * mul);
+              w.y = pack_bf16(__uint_as_float(o[8 * j + 2]) * mul, __uint_as_float(o[8 * j + 3]) * mul);
+              w.z = pack_bf16(__uint_as_float(o[8 * j + 4]) * mul, __uint_as_float(o[8 * j + 5]) * mul);
+              w.w = pack_bf16(__uint_as_float(o[8 * j + 6]) * mul, __uint_as_float(o[8 * j + 7]) * mul);
+              *reinterpret_cast<uint4*>(orow + c * 32 + j * 8) = w;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, KV_TM_COLS);
+  }
+}
+
 }  // namespace
 
 cudaError_t attention_fwd(const AttnArgs& a, cudaStream_t s) {
@@ -274,6 +705,44 @@ cudaError_t attention_fwd(const AttnArgs& a, cudaStream_t s) {
   dim3 grid(a.n_tiles, a.heads);
   attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, s>>>(mq, mk, mv, a);
   return cudaGetLastError();
+}
+
+
+cudaError_t attention_bwd(const AttnBwdArgs& a, cudaStream_t s) {
+  if (a.n_tiles <= 0 || a.heads <= 0) return cudaSuccess;
+  const uint64_t cols = (uint64_t)a.heads * DH;
+  CUtensorMap q128, do128, k64, v64, k128, v128, q64, do64;
+  bool ok = tma_map_bf16_sw128(&q128, a.q, a.n_rows, cols, a.ldq, 128);
+  ok &= tma_map_bf16_sw128(&do128, a.dout, a.n_rows, cols, a.lddo, 128);
+  ok &= tma_map_bf16_sw128(&k64, a.k, a.n_rows, cols, a.ldk, 64);
+  ok &= tma_map_bf16_sw128(&v64, a.v, a.n_rows, cols, a.ldv, 64);
+  ok &= tma_map_bf16_sw128(&k128, a.k, a.n_rows, cols, a.ldk, 128);
+  ok &= tma_map_bf16_sw128(&v128, a.v, a.n_rows, cols, a.ldv, 128);
+  ok &= tma_map_bf16_sw128(&q64, a.q, a.n_rows, cols, a.ldq, 64);
+  ok &= tma_map_bf16_sw128(&do64, a.dout, a.n_rows, cols, a.lddo, 64);
+  if (!ok) { fprintf(stderr, "attention_bwd: tensor map encode failed\n"); return cudaErrorInvalidValue; }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM);
+    if (e != cudaSuccess) { fprintf(stderr, "attention_bwd: dq smem attribute\n"); return e; }
+    e = cudaFuncSetAttribute(attn_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KV_SMEM);
+    if (e != cudaSuccess) { fprintf(stderr, "attention_bwd: dkdv smem attribute\n"); return e; }
+    configured = true;
+  }
+  const long warps = (long)a.n_rows * a.heads;
+  attn_delta_kernel<<<(int)((warps + 7) / 8), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(a.o), a.ldo,
+                                                          reinterpret_cast<const __nv_bfloat16*>(a.dout), a.lddo, a.delta,
+                                                          a.n_rows, a.heads);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { fprintf(stderr, "attention_bwd: delta launch\n"); return e; }
+  dim3 grid(a.n_tiles, a.heads);
+  attn_bwd_dq_kernel<<<grid, BWD_THREADS, DQ_SMEM, s>>>(q128, do128, k64, v64, a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) { fprintf(stderr, "attention_bwd: dq launch\n"); return e; }
+  attn_bwd_dkdv_kernel<<<grid, BWD_THREADS, KV_SMEM, s>>>(k128, v128, q64, do64, a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) fprintf(stderr, "attention_bwd: dkdv launch\n");
+  return e;
 }
 
 }  // namespace kmoss

@@ -398,9 +398,30 @@ void attention_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tens
   KM_CHECK_CUDA(kmoss::attention_fwd(a, cur_stream()));
 }
 
+
+void attention_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& lse,
+                   const Tensor& tiles, double scale, Tensor dq, Tensor dk, Tensor dv) {
+  c10::cuda::CUDAGuard guard(q.device());
+  check_qkv(q, "q"); check_qkv(k, "k"); check_qkv(v, "v"); check_qkv(o, "o"); check_qkv(dout, "dout");
+  check_qkv(dq, "dq"); check_qkv(dk, "dk"); check_qkv(dv, "dv");
+  Tensor delta = at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat));
+  kmoss::AttnBwdArgs a{};
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.o = o.data_ptr(); a.dout = dout.data_ptr();
+  a.ldq = q.stride(0); a.ldk = k.stride(0); a.ldv = v.stride(0); a.ldo = o.stride(0); a.lddo = dout.stride(0);
+  a.dq = dq.data_ptr(); a.dk = dk.data_ptr(); a.dv = dv.data_ptr();
+  a.lddq = dq.stride(0); a.lddk = dk.stride(0); a.lddv = dv.stride(0);
+  a.lse = lse.data_ptr<float>(); a.delta = delta.data_ptr<float>();
+  a.tiles = tiles.data_ptr<int>(); a.n_tiles = (int)tiles.size(0);
+  a.n_rows = (int)q.size(0); a.heads = (int)q.size(1); a.scale = (float)scale;
+  a.status = status_tensor().data_ptr<int>();
+  KM_CHECK_CUDA(kmoss::attention_bwd(a, cur_stream()));
+}
+
 }  // namespace
 
 TORCH_LIBRARY(kmoss_b200, m) {
+  m.def("attention_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor tiles, float scale, "
+        "Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv) -> ()", &attention_bwd);
   m.def("attention_fwd(Tensor q, Tensor k, Tensor v, Tensor tiles, float scale, Tensor(a!) o, Tensor(b!)? lse) -> ()", &attention_fwd);
   m.def("opt_record_bytes() -> int", &opt_record_bytes);
   m.def("opt_chunk_elems() -> int", &opt_chunk_elems);

@@ -22,6 +22,7 @@
 #include "gemm_sm100.cuh"
 
 #include "common.cuh"
+#include "tma_host.cuh"
 
 namespace kmoss {
 
@@ -615,6 +616,7 @@ bool make_map(CUtensorMap* map, const void* base, int elem_bytes, bool fp8, uint
               uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
+  tma_bind_context();
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {ld * (uint64_t)elem_bytes};
   cuuint32_t box[2] = {box_cols, box_rows};
