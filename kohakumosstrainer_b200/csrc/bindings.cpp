@@ -7,9 +7,11 @@
 
 #include <cmath>
 #include <optional>
+#include <vector>
 
 #include "attention_sm100.cuh"
 #include "blockops.cuh"
+#include "comm.cuh"
 #include "gemm_sm100.cuh"
 #include "optim.cuh"
 
@@ -61,7 +63,7 @@ void gemm(const Tensor& a, const Tensor& b, int64_t M, int64_t N, int64_t K, boo
           const optional<Tensor>& t, const optional<Tensor>& u, int64_t epilogue, const optional<Tensor>& aux,
           const optional<Tensor>& q_norm_w, const optional<Tensor>& k_norm_w, const optional<Tensor>& rope,
           int64_t rope_cols, double eps, const optional<Tensor>& head_rstd, int64_t splits,
-          const optional<Tensor>& workspace) {
+          const optional<Tensor>& workspace, const optional<Tensor>& timeline) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "gemm: CUDA tensors required");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "gemm: operands must be 2-D with unit inner stride");
   TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1, "gemm: out must be 2-D with unit inner stride");
@@ -119,6 +121,7 @@ void gemm(const Tensor& a, const Tensor& b, int64_t M, int64_t N, int64_t K, boo
     g.workspace = reinterpret_cast<float*>(workspace->data_ptr());
   }
   g.status = status_tensor().data_ptr<int>();
+  if (timeline.has_value() && timeline->defined()) g.timeline = reinterpret_cast<unsigned long long*>(timeline->data_ptr());
   KM_CHECK_CUDA(kmoss::gemm_launch(g, cur_stream()));
 }
 
@@ -417,9 +420,44 @@ void attention_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const T
   KM_CHECK_CUDA(kmoss::attention_bwd(a, cur_stream()));
 }
 
+
+// ---- peer-memory collectives -------------------------------------------------------------
+int64_t allreduce_flag_words() { return kmoss::AR_FLAG_WORDS; }
+
+// `ptrs` / `flag_ptrs`: device addresses (as int64) of every rank's mapping, index = rank.
+void allreduce(std::vector<int64_t> ptrs, std::vector<int64_t> flag_ptrs, int64_t mc_ptr, int64_t numel, int64_t dtype,
+               int64_t rank, double scale, int64_t epoch, int64_t blocks) {
+  const int world = (int)ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= kmoss::AR_MAX_WORLD && flag_ptrs.size() == ptrs.size(), "allreduce: world size");
+  const int64_t esize = dtype == 1 ? 2 : 4;
+  TORCH_CHECK((numel * esize) % 16 == 0, "allreduce: bucket bytes must be a multiple of 16");
+  kmoss::AllReduceArgs a{};
+  for (int i = 0; i < world; ++i) {
+    a.ptrs[i] = reinterpret_cast<void*>(ptrs[i]);
+    a.flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
+  }
+  a.mc_ptr = reinterpret_cast<void*>(mc_ptr);
+  a.n_vec = (size_t)(numel * esize / 16);
+  a.rank = (int)rank; a.world = world; a.dtype = (int)dtype; a.scale = (float)scale; a.epoch = (uint32_t)epoch;
+  a.status = status_tensor().data_ptr<int>();
+  KM_CHECK_CUDA(kmoss::allreduce_launch(a, (int)blocks, cur_stream()));
+}
+
+void bounded_wait_probe(const Tensor& flag, int64_t expect, double limit_ms) {
+  c10::cuda::CUDAGuard guard(flag.device());
+  KM_CHECK_CUDA(kmoss::bounded_wait_probe(reinterpret_cast<const uint32_t*>(flag.data_ptr()), (uint32_t)expect,
+                                          (uint64_t)(limit_ms * 1e6), status_tensor().data_ptr<int>(), cur_stream()));
+}
+
+void reset_status() { status_tensor().zero_(); }
+
 }  // namespace
 
 TORCH_LIBRARY(kmoss_b200, m) {
+  m.def("allreduce_flag_words() -> int", &allreduce_flag_words);
+  m.def("allreduce(int[] ptrs, int[] flag_ptrs, int mc_ptr, int numel, int dtype, int rank, float scale, int epoch, int blocks) -> ()", &allreduce);
+  m.def("bounded_wait_probe(Tensor flag, int expect, float limit_ms) -> ()", &bounded_wait_probe);
+  m.def("reset_status() -> ()", &reset_status);
   m.def("attention_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor tiles, float scale, "
         "Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv) -> ()", &attention_bwd);
   m.def("attention_fwd(Tensor q, Tensor k, Tensor v, Tensor tiles, float scale, Tensor(a!) o, Tensor(b!)? lse) -> ()", &attention_fwd);
@@ -436,7 +474,7 @@ TORCH_LIBRARY(kmoss_b200, m) {
       "Tensor? scale_a, Tensor? scale_b, Tensor? row_scale, Tensor? col_scale, Tensor? bias, Tensor? res, float beta, "
       "Tensor? gate, Tensor? seg, Tensor? t, Tensor? u, int epilogue, Tensor(b!)? aux, Tensor? q_norm_w, "
       "Tensor? k_norm_w, Tensor? rope, int rope_cols, float eps, Tensor(c!)? head_rstd, int splits, "
-      "Tensor(d!)? workspace) -> ()",
+      "Tensor(d!)? workspace, Tensor(e!)? timeline=None) -> ()",
       &gemm);
   m.def(
       "rms_norm_mod_fwd(Tensor x, Tensor? w, Tensor? shift, Tensor? scale, Tensor? seg, float eps, Tensor(a!) y, "

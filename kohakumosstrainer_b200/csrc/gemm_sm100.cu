@@ -69,6 +69,8 @@ struct DeviceParams {
   float* head_rstd;
   float* workspace;
   int* status;
+  unsigned long long* timeline;
+  int tma_out;  // 1: bf16 output (and aux) leave through shared memory + TMA stores
 };
 
 __device__ __forceinline__ void tile_coords(int tile, const DeviceParams& p, int& m_blk, int& n_blk,
@@ -106,7 +108,8 @@ struct Cfg {
   static constexpr uint32_t MAIN_TX = A_STAGE + B_STAGE;
   static constexpr uint32_t BYPASS_TX = A_STAGE + BN * 128;  // T 128 x 64 and U BN x 64, bf16 K-major
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr size_t SMEM = (size_t)STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int STAGING = 4 * 2 * 4096;   // per epilogue warp: two [32 rows][128 B] TMA-store buffers
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE + STAGING + 1024 /*align*/ + 256 /*barriers*/;
   // Advance of the descriptor start address per UMMA_K step, in bytes.
   static constexpr uint32_t A_KSTEP = A_MN ? (UMMA_K / 8) * 1024 : 32;
   static constexpr uint32_t B_KSTEP = B_MN ? (UMMA_K / 8) * 1024 : 32;
@@ -196,12 +199,14 @@ template <int BN, bool A_MN, bool B_MN, bool FP8>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const __grid_constant__ CUtensorMap map_t, const __grid_constant__ CUtensorMap map_u,
+            const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_aux,
             const DeviceParams p) {
   using C = Cfg<BN, A_MN, B_MN, FP8>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)C::STAGES * C::STAGE);
+  uint8_t* staging = smem + (size_t)C::STAGES * C::STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + C::STAGING);
   // barrier layout: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
   const uint32_t bar_base = smem_u32(bars);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -318,6 +323,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 300 + acc)) break;
         tc_fence_after();
+        if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[4 * (tile / gridDim.x) + 0] = global_timer_ns();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         uint32_t accumulate = 0;
         bool ok = true;
@@ -355,6 +361,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         if (!ok) break;
         tc_commit(acc_full_bar(acc));  // accumulator complete -> epilogue may read
+        if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[4 * (tile / gridDim.x) + 1] = global_timer_ns();
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
@@ -364,6 +371,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     const int row_in_tile = quarter * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
+    int buf = 0;  // staging buffer the next alternating TMA store uses (persists across tiles)
     float scalar = p.alpha;
     if (p.scale_a != nullptr) scalar *= __ldg(p.scale_a);
     if (p.scale_b != nullptr) scalar *= __ldg(p.scale_b);
@@ -374,10 +382,218 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const int n_tile = n_blk * BN;
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, 400 + acc)) break;
       tc_fence_after();
+      if (p.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.timeline[4 * (tile / gridDim.x) + 2] = global_timer_ns();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       const bool row_ok = m < p.M;
 
-      if (p.splits > 1) {
+      if (p.tma_out) {
+        // ---- bf16 output through shared memory and TMA stores (coalesced, clipped at M / N) ----
+        const int ep = warp - 2;
+        const int y0 = m_blk * BM + quarter * 32;
+        const bool has_col = p.col_scale != nullptr, has_bias = p.bias != nullptr, has_gate = p.gate != nullptr,
+                   has_res = p.res != nullptr;
+        float row_s = scalar;
+        int seg_m = 0;
+        if (row_ok) {
+          if (p.row_scale != nullptr) row_s *= __ldg(p.row_scale + m);
+          if (has_gate) seg_m = __ldg(p.seg + m);
+        }
+        auto slab_acquire = [&](bool keep_one) {
+          if (lane == 0) { if (keep_one) tma_store_wait_read<1>(); else tma_store_wait_read<0>(); }
+          __syncwarp();
+        };
+        auto slab_put = [&](int b, int half, const float (&v)[32]) {
+          uint8_t* rowp = staging + (ep * 2 + b) * 4096 + lane * 128;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint4 w;
+            w.x = pack_bf16(v[8 * c + 0], v[8 * c + 1]); w.y = pack_bf16(v[8 * c + 2], v[8 * c + 3]);
+            w.z = pack_bf16(v[8 * c + 4], v[8 * c + 5]); w.w = pack_bf16(v[8 * c + 6], v[8 * c + 7]);
+            *reinterpret_cast<uint4*>(rowp + (((half * 4 + c) ^ (lane & 7)) << 4)) = w;
+          }
+        };
+        auto slab_flush = [&](int b, const CUtensorMap* map, int x) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(map, smem_u32(staging + (ep * 2 + b) * 4096), x, y0);
+            tma_store_commit();
+          }
+        };
+        // (acc * s [* col] + bias) [* gate] [+ beta * res] on 32 columns starting at n0
+        auto linear32 = [&](const uint32_t (&r)[32], int n0, float (&v)[32]) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * row_s;
+          if (has_col) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const float4 c4 = __ldg(reinterpret_cast<const float4*>(p.col_scale + n0 + j));
+              v[j] *= c4.x; v[j + 1] *= c4.y; v[j + 2] *= c4.z; v[j + 3] *= c4.w;
+            }
+          }
+          if (has_bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              v[j] += p.bias_dtype == 0 ? __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(p.bias) + n0 + j))
+                                        : __ldg(reinterpret_cast<const float*>(p.bias) + n0 + j);
+          }
+          if (has_gate) {
+            const float* g = p.gate + (size_t)seg_m * p.gate_stride + n0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const float4 g4 = __ldg(reinterpret_cast<const float4*>(g + j));
+              v[j] *= g4.x; v[j + 1] *= g4.y; v[j + 2] *= g4.z; v[j + 3] *= g4.w;
+            }
+          }
+          if (has_res && row_ok) {
+            const uint4* r4 = reinterpret_cast<const uint4*>(p.res + (size_t)m * p.ldr + n0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint4 w = r4[i];
+              const float2 a = unpack_bf16(w.x), b = unpack_bf16(w.y), c = unpack_bf16(w.z), d = unpack_bf16(w.w);
+              v[8 * i + 0] += p.beta * a.x; v[8 * i + 1] += p.beta * a.y; v[8 * i + 2] += p.beta * b.x; v[8 * i + 3] += p.beta * b.y;
+              v[8 * i + 4] += p.beta * c.x; v[8 * i + 5] += p.beta * c.y; v[8 * i + 6] += p.beta * d.x; v[8 * i + 7] += p.beta * d.y;
+            }
+          }
+        };
+        if (p.epilogue == EPI_LINEAR) {
+#pragma unroll 1
+          for (int sl = 0; sl < BN / 64; ++sl) {
+            const int n0 = n_tile + sl * 64;
+            if (n0 >= p.N) break;
+            slab_acquire(true);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t r[32];
+              tmem_ld_32x32(t_row + sl * 64 + half * 32, r);
+              tmem_ld_wait();
+              float v[32];
+              if (n0 + half * 32 < p.N) {
+                linear32(r, n0 + half * 32, v);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = 0.f;
+              }
+              slab_put(buf, half, v);
+            }
+            slab_flush(buf, &map_out, n0);
+            buf ^= 1;
+          }
+        } else if (p.epilogue == EPI_SITU) {
+          const int out0 = n_tile / 2;
+#pragma unroll 1
+          for (int sl = 0; sl < BN / 128; ++sl) {
+            const int n0 = out0 + sl * 64;
+            if (n0 >= p.N) break;
+            float v[2][32];
+            slab_acquire(false);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t ru[32], rg[32];
+              tmem_ld_32x32(t_row + sl * 64 + half * 32, ru);
+              tmem_ld_32x32(t_row + BN / 2 + sl * 64 + half * 32, rg);
+              tmem_ld_wait();
+              float u[32], g[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                float su = row_s, sg = row_s;
+                if (has_col) {
+                  su *= __ldg(p.col_scale + n0 + half * 32 + j);
+                  sg *= __ldg(p.col_scale + p.situ_f + n0 + half * 32 + j);
+                }
+                // pre-activations rounded to bf16 exactly as they are stored for backward
+                u[j] = __bfloat162float(__float2bfloat16(__uint_as_float(ru[j]) * su));
+                g[j] = __bfloat162float(__float2bfloat16(__uint_as_float(rg[j]) * sg));
+                v[half][j] = situ_f(u[j], g[j]);
+              }
+              if (p.aux != nullptr) {
+                slab_put(0, half, u);
+                slab_put(1, half, g);
+              }
+            }
+            if (p.aux != nullptr) {
+              slab_flush(0, &map_aux, n0);
+              slab_flush(1, &map_aux, p.situ_f + n0);
+              slab_acquire(true);  // buffer 0 has been read
+            }
+            slab_put(0, 0, v[0]);
+            slab_put(0, 1, v[1]);
+            slab_flush(0, &map_out, n0);
+            buf = 1;  // buffer 0 holds the newest store
+          }
+        } else {  // EPI_QK_ROPE
+#pragma unroll 1
+          for (int h = 0; h < BN / 128; ++h) {
+            const int n_head = n_tile + h * 128;
+            const uint32_t t_head = t_row + h * 128;
+            if (n_head >= p.N) break;
+            if (n_head < p.rope_cols) {
+              const __nv_bfloat16* w = (n_head < p.rope_cols / 2) ? p.q_norm_w : p.k_norm_w;
+              float ss = 0.f;
+#pragma unroll 1
+              for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(t_head + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  float x = __uint_as_float(r[j]) * row_s;
+                  if (has_col) x *= __ldg(p.col_scale + n_head + c * 32 + j);
+                  ss += x * x;
+                }
+              }
+              const float inv = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
+              if (row_ok && p.head_rstd != nullptr) p.head_rstd[(size_t)m * (p.rope_cols / 128) + n_head / 128] = inv;
+              slab_acquire(false);
+#pragma unroll
+              for (int c = 0; c < 2; ++c) {
+                uint32_t ra[32], rb[32];
+                tmem_ld_32x32(t_head + c * 32, ra);
+                tmem_ld_32x32(t_head + 64 + c * 32, rb);
+                tmem_ld_wait();
+                float va[32], vb[32];
+                const float* cs = p.rope + (size_t)(row_ok ? m : 0) * 128 + c * 32;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const int ja = c * 32 + j, jb = 64 + ja;
+                  float sa = row_s * inv, sb = sa;
+                  if (has_col) {
+                    sa *= __ldg(p.col_scale + n_head + ja);
+                    sb *= __ldg(p.col_scale + n_head + jb);
+                  }
+                  const float a = __uint_as_float(ra[j]) * sa * __bfloat162float(__ldg(w + ja));
+                  const float b = __uint_as_float(rb[j]) * sb * __bfloat162float(__ldg(w + jb));
+                  const float co = cs[j], si = cs[64 + j];
+                  va[j] = a * co - b * si;
+                  vb[j] = b * co + a * si;
+                }
+                slab_put(0, c, va);
+                slab_put(1, c, vb);
+              }
+              slab_flush(0, &map_out, n_head);
+              slab_flush(1, &map_out, n_head + 64);
+              buf = 0;  // the older of the two stores in flight reads buffer 0
+            } else {
+#pragma unroll 1
+              for (int sl = 0; sl < 2; ++sl) {
+                const int n0 = n_head + sl * 64;
+                slab_acquire(true);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                  uint32_t r[32];
+                  tmem_ld_32x32(t_head + sl * 64 + half * 32, r);
+                  tmem_ld_wait();
+                  float v[32];
+                  linear32(r, n0 + half * 32, v);
+                  slab_put(buf, half, v);
+                }
+                slab_flush(buf, &map_out, n0);
+                buf ^= 1;
+              }
+            }
+          }
+        }
+      } else if (p.splits > 1) {
         float* ws = p.workspace + ((size_t)split * p.M + (row_ok ? m : 0)) * p.N;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -544,8 +760,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+      if (p.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.timeline[4 * (tile / gridDim.x) + 3] = global_timer_ns();
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
+    if (p.tma_out && lane == 0) tma_store_wait_all<0>();  // staged tiles must have left shared memory
   }
 
   // ---------------------------------- teardown -----------------------------------------
@@ -657,6 +875,18 @@ cudaError_t launch_cfg(const GemmProblem& g, DeviceParams& p, cudaStream_t strea
     map_t = map_a;
     map_u = map_b;
   }
+  // bf16 outputs with 16-byte aligned rows go through shared memory + TMA stores
+  CUtensorMap map_out = map_a, map_aux = map_a;
+  p.tma_out = 0;
+  if (g.out_dtype == OUT_BF16 && g.splits <= 1 && (g.ldo % 8) == 0 && (reinterpret_cast<uintptr_t>(g.out) & 15) == 0 &&
+      (g.N % 8) == 0 && (g.aux == nullptr || ((g.ldaux % 8) == 0 && (reinterpret_cast<uintptr_t>(g.aux) & 15) == 0)) &&
+      (g.col_scale == nullptr || (reinterpret_cast<uintptr_t>(g.col_scale) & 15) == 0) &&
+      (g.gate == nullptr || ((g.gate_stride % 4) == 0 && (reinterpret_cast<uintptr_t>(g.gate) & 15) == 0)) &&
+      (g.res == nullptr || ((g.ldr % 8) == 0 && (reinterpret_cast<uintptr_t>(g.res) & 15) == 0)) && (g.N % 32) == 0) {
+    ok &= tma_map_bf16_sw128(&map_out, g.out, g.M, g.N, g.ldo, 32);
+    if (g.aux != nullptr) ok &= tma_map_bf16_sw128(&map_aux, g.aux, g.M, 2 * (uint64_t)g.N, g.ldaux, 32);
+    p.tma_out = 1;
+  }
   if (!ok) return cudaErrorInvalidValue;
 
   p.num_m_blocks = (g.M + BM - 1) / BM;
@@ -679,7 +909,7 @@ cudaError_t launch_cfg(const GemmProblem& g, DeviceParams& p, cudaStream_t strea
   }
   const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
   if (grid <= 0) return cudaSuccess;
-  kern<<<grid, NUM_THREADS, C::SMEM, stream>>>(map_a, map_b, map_t, map_u, p);
+  kern<<<grid, NUM_THREADS, C::SMEM, stream>>>(map_a, map_b, map_t, map_u, map_out, map_aux, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   if (p.splits > 1) {
@@ -760,7 +990,7 @@ cudaError_t gemm_launch(const GemmProblem& g, cudaStream_t stream) {
   p.rope = g.pos;  // precomputed [M, 128] cos|sin table
   p.rope_cols = g.rope_cols; p.eps = g.eps;
   p.head_rstd = g.head_rstd;
-  p.workspace = g.workspace; p.status = g.status;
+  p.workspace = g.workspace; p.status = g.status; p.timeline = g.timeline;
 
   if (g.epilogue == EPI_SITU) {
     if (g.b_mn || g.splits > 1 || (g.N % 128) != 0) return cudaErrorInvalidValue;

@@ -73,6 +73,7 @@ struct GemmProblem {
   float* workspace;
 
   int* status;  // int[4] device status word (nullable)
+  unsigned long long* timeline;  // nullable: CTA 0 records globaltimer ns at {mma begin, mma end, epilogue begin, epilogue end} per tile
 };
 
 // Launch on `stream`. Returns cudaSuccess or the launch / argument error. No allocation.
