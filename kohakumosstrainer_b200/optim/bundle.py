@@ -138,10 +138,17 @@ class Bundle:
             self._deferred = (flags[:1], stats[:1], skip)
         if self.ema is not None and ok:
             self.ema.update(self.step_index)
-        self.optimizer.zero_grad(set_to_none=False)
+        self.zero_grad()
         self._loss = None
         self.step_index += 1
         return ok
+
+    def zero_grad(self) -> None:
+        """Zero every gradient in place with one multi-tensor launch (gradients stay views of
+        their buckets, so the optimiser and reducer tables keep their addresses)."""
+        grads = [p.grad for p in self.params if p.grad is not None]
+        if grads:
+            torch._foreach_zero_(grads)
 
     def settle(self) -> None:
         """Read back the deferred step's numbers (STEP_SYNC="deferred": called when logging)."""

@@ -1,0 +1,233 @@
+"""Data-parallel gradient reduction.
+
+`GradReducer` keeps every trainable gradient as a VIEW of a flat bucket (reverse parameter
+order, `DDP_BUCKET_MB` each, one dtype per bucket). On the step's last micro-batch the
+post-accumulate hook of a bucket's last parameter launches that bucket's SUM all-reduce on a
+communication stream, in bucket order, so it overlaps the rest of backward; `finish()` makes
+the compute stream wait (its device time is the exposed communication). Same contract as the
+reference reducer (`src/kohakumoss/parallel/ddp.py:25-224`), different transport:
+
+* `backend="kohakumoss"` (CUDA + NCCL group): buckets live in symmetric memory and are reduced
+  in place by `csrc/comm.cu` over NVLink peer mappings: bf16 gradients are summed in fp32
+  registers (no widened copies), two-shot above 256 KB, one-shot below, `multimem` through the
+  switch when the fabric offers a multicast mapping;
+* `backend="torch"`: `dist.all_reduce` on the bucket (NCCL or gloo), with an fp32 copy when
+  `reduce_dtype` is wider than the gradients: the measured baseline and the CPU path.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch import Tensor, nn
+
+MIB = 1 << 20
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def all_reduce_sum(t: Tensor, group=None) -> Tensor:
+    dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+    return t
+
+
+def broadcast_params(params, src: int = 0, group=None, chunk_bytes: int = 256 * MIB) -> None:
+    """Rank `src`'s trainable parameters to every rank, in flat chunks of <= 256 MiB."""
+    params = [p for p in params]
+    if not params or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    with torch.no_grad():
+        batch, size = [], 0
+        for p in params + [None]:
+            if p is None or (batch and (size + p.numel() * p.element_size() > chunk_bytes or p.dtype != batch[0].dtype)):
+                flat = torch.cat([q.detach().reshape(-1) for q in batch])
+                dist.broadcast(flat, src, group=group)
+                off = 0
+                for q in batch:
+                    q.copy_(flat[off : off + q.numel()].view_as(q))
+                    off += q.numel()
+                batch, size = [], 0
+            if p is not None:
+                batch.append(p)
+                size += p.numel() * p.element_size()
+
+
+class _Bucket:
+    def __init__(self, params: list[nn.Parameter], flat: Tensor, symmetric=None):
+        self.params, self.flat, self.symmetric = params, flat, symmetric
+        self.views, off = [], 0
+        for p in params:
+            n = p.numel()
+            self.views.append(flat[off : off + n].view_as(p))
+            off += n
+        self.used = off
+        self.pending = len(params)
+        self.ready = False
+        self.work = None
+        self.wide: Tensor | None = None
+
+    def attach(self) -> None:
+        for p, view in zip(self.params, self.views):
+            if p.grad is None or p.grad.data_ptr() != view.data_ptr():
+                if p.grad is not None:
+                    view.copy_(p.grad)
+                p.grad = view
+
+
+class GradReducer:
+    def __init__(self, params, group=None, bucket_mb: float = 25, reduce_dtype: str | torch.dtype | None = "fp32",
+                 backend: str = "kohakumoss", device=None, average: bool = False, comm_blocks: int = 32,
+                 use_multimem: bool = True):
+        from . import symm
+
+        self.params = [p for p in params if p.requires_grad]
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device(device) if device is not None else self.params[0].device
+        self.average = average
+        self.comm_blocks = comm_blocks
+        if isinstance(reduce_dtype, str):
+            reduce_dtype = {"fp32": torch.float32, "bf16": torch.bfloat16, "param": None}[reduce_dtype]
+        self.reduce_dtype = reduce_dtype
+        self.native = backend == "kohakumoss" and self.world > 1 and symm.available(self.device)
+        self.backend = "kohakumoss" if self.native else "torch"
+        self.flags = symm.PeerFlags(self.device, group) if self.native else None
+        self.use_multimem = use_multimem
+        self.buckets: list[_Bucket] = []
+        limit = int(bucket_mb * MIB)
+        current, size = [], 0
+        for p in reversed(self.params):
+            if current and (size >= limit or current[0].dtype != p.dtype):
+                self.buckets.append(self._make_bucket(current))
+                current, size = [], 0
+            current.append(p)
+            size += p.numel() * p.element_size()
+        if current:
+            self.buckets.append(self._make_bucket(current))
+        self._owner = {}
+        for b in self.buckets:
+            b.attach()
+            for p in b.params:
+                self._owner[id(p)] = b
+                p.register_post_accumulate_grad_hook(self._hook)
+        self.bytes = sum(b.flat.numel() * b.flat.element_size() for b in self.buckets)
+        self.comm_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+        self._last = False
+        self._next = 0
+        self._done_event = None
+        self.launches = 0
+        self.wait_ms_events: list = []
+
+    def _make_bucket(self, params) -> _Bucket:
+        from . import symm
+
+        numel = sum(p.numel() for p in params)
+        pad = 8 * self.world  # 16-byte vectors, and equal slices per rank
+        numel_padded = (numel + pad - 1) // pad * pad
+        dtype = params[0].dtype
+        if self.native and dtype in _DT:
+            sb = symm.SymmetricBuffer(numel_padded, dtype, self.device, self.group, zero=True)
+            return _Bucket(params, sb.local, sb)
+        return _Bucket(params, torch.zeros(numel_padded, dtype=dtype, device=params[0].device))
+
+    # -- step protocol ----------------------------------------------------------------------
+    def start(self, last: bool) -> None:
+        """Call before each micro-batch's backward; reductions launch only when `last`."""
+        self._last = last
+        if last:
+            self._next = 0
+            for b in self.buckets:
+                b.pending = len(b.params)
+                b.ready = False
+                b.attach()
+
+    def zero(self) -> None:
+        for b in self.buckets:
+            b.flat.zero_()
+
+    def _hook(self, p: Tensor) -> None:
+        if not self._last:
+            return
+        b = self._owner[id(p)]
+        b.pending -= 1
+        if b.pending == 0:
+            b.ready = True
+            self._launch_ready()
+
+    def _launch_ready(self) -> None:
+        while self._next < len(self.buckets) and self.buckets[self._next].ready:
+            self._reduce(self.buckets[self._next])
+            self._next += 1
+
+    def _reduce(self, b: _Bucket) -> None:
+        self.launches += 1
+        scale = 1.0 / self.world if self.average else 1.0
+        if self.world == 1:
+            return
+        if self.comm_stream is not None:
+            self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+        if self.native and b.symmetric is not None:
+            from ..ops import native
+
+            with torch.cuda.stream(self.comm_stream):
+                mc = b.symmetric.mc_ptr if self.use_multimem else 0
+                native.load().allreduce(b.symmetric.ptrs, self.flags.buffer.ptrs, mc, b.flat.numel(), _DT[b.flat.dtype],
+                                        self.rank, scale, self.flags.next_epoch(), self.comm_blocks)
+            return
+        ctx = torch.cuda.stream(self.comm_stream) if self.comm_stream is not None else _Null()
+        with ctx:
+            buf = b.flat
+            if self.reduce_dtype is not None and self.reduce_dtype != buf.dtype:
+                b.wide = buf.to(self.reduce_dtype)
+                buf = b.wide
+            dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=self.group)
+            if scale != 1.0:
+                buf.mul_(scale)
+            if b.wide is not None:
+                b.flat.copy_(b.wide)
+                b.wide = None
+
+    def finish(self) -> None:
+        """Launch anything not yet launched (unused parameters) and make the compute stream
+        wait for every reduction of this step."""
+        if self.world == 1:
+            return
+        for b in self.buckets[self._next :]:
+            self._reduce(b)
+        self._next = len(self.buckets)
+        if self.comm_stream is not None:
+            cur = torch.cuda.current_stream(self.device)
+            start = torch.cuda.Event(enable_timing=True)
+            end = torch.cuda.Event(enable_timing=True)
+            start.record(cur)
+            cur.wait_stream(self.comm_stream)
+            end.record(cur)
+            self.wait_ms_events.append((start, end))
+            if len(self.wait_ms_events) > 64:
+                self.wait_ms_events = self.wait_ms_events[-64:]
+
+    def metrics(self) -> dict:
+        """`ddp_comm_wait_ms` of the most recent finished step, `ddp_reduce_mb`, launches."""
+        wait = None
+        for s, e in reversed(self.wait_ms_events):
+            if e.query():
+                wait = s.elapsed_time(e)
+                break
+        return {"ddp_comm_wait_ms": wait, "ddp_reduce_mb": self.bytes / 1e6, "ddp_launches": len(self.buckets),
+                "ddp_backend": self.backend}
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+def wrap_torch_ddp(module: nn.Module, device=None, bucket_mb: int = 25):
+    """Stock `DistributedDataParallel` (A/B baseline for the reducers above)."""
+    from torch.nn.parallel import DistributedDataParallel
+
+    ids = None if device is None or torch.device(device).type != "cuda" else [torch.device(device).index]
+    return DistributedDataParallel(module, device_ids=ids, bucket_cap_mb=bucket_mb, gradient_as_bucket_view=True)

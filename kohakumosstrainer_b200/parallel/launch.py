@@ -1,0 +1,149 @@
+"""Process launcher without torchrun: the parent owns a TCPStore on 127.0.0.1 and an
+OS-assigned port, spawns one process per device, and every rank joins the process group
+through that store. Uneven start-up work (catalog scan, weight download, prewarm) is
+ordered with store gates instead of collectives, so a slow rank cannot trip a collective
+timeout (`src/kohakumoss/parallel/launch.py:52-317` in the reference). A failing rank prints
+its traceback, the parent kills the other ranks and exits non-zero without process-group
+teardown: nobody waits on a dead peer.
+"""
+
+from __future__ import annotations
+
+import os
+import pickle
+import sys
+import time
+import traceback
+from dataclasses import dataclass, field
+from datetime import timedelta
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def default_backend(device_type: str = "cuda") -> str:
+    if device_type == "cuda" and torch.cuda.is_available() and sys.platform.startswith("linux"):
+        return "nccl"
+    return "gloo"
+
+
+@dataclass
+class ParallelPlan:
+    world: int = 1
+    devices: tuple = (0,)
+    backend: str = "auto"          # auto | nccl | gloo
+    timeout_s: float = 900.0       # DIST_TIMEOUT: every collective and store wait
+    gate_timeout_s: float = 7200.0  # DIST_GATE_TIMEOUT: store gates around start-up work
+    device_type: str = "cuda"
+    env: dict = field(default_factory=dict)
+
+    def resolved_backend(self) -> str:
+        return default_backend(self.device_type) if self.backend == "auto" else self.backend
+
+
+_STORE: dist.Store | None = None
+_PLAN: ParallelPlan | None = None
+
+
+def store() -> dist.Store:
+    if _STORE is None:
+        raise RuntimeError("no launcher store in this process")
+    return _STORE
+
+
+# -- store gates ----------------------------------------------------------------------------
+def release_ranks(name: str, value=b"1") -> None:
+    """Rank 0 opens the gate `name` (optionally carrying a pickled value)."""
+    store().set(f"gate/{name}", value if isinstance(value, bytes) else pickle.dumps(value))
+
+
+def wait_for_rank0(name: str, timeout_s: float | None = None) -> bytes:
+    """Block until rank 0 released gate `name`; returns its payload."""
+    t = timeout_s if timeout_s is not None else (_PLAN.gate_timeout_s if _PLAN else 7200.0)
+    store().wait([f"gate/{name}"], timedelta(seconds=t))
+    return store().get(f"gate/{name}")
+
+
+def rank0_value(name: str, make, rank: int):
+    """`make()` runs on rank 0 only; every rank returns its (pickled) result."""
+    if rank == 0:
+        value = make()
+        release_ranks(name, pickle.dumps(value))
+        return value
+    return pickle.loads(wait_for_rank0(name))
+
+
+def startup_barrier(name: str, rank: int, world: int, timeout_s: float | None = None) -> None:
+    """All ranks meet through the store (no collective, so no device work is queued)."""
+    t = timeout_s if timeout_s is not None else (_PLAN.gate_timeout_s if _PLAN else 7200.0)
+    store().set(f"barrier/{name}/{rank}", b"1")
+    store().wait([f"barrier/{name}/{r}" for r in range(world)], timedelta(seconds=t))
+
+
+def store_agree(name: str, ok: bool, rank: int, world: int) -> bool:
+    """True iff every rank reported ok (used around checkpoint writes)."""
+    store().set(f"agree/{name}/{rank}", b"1" if ok else b"0")
+    store().wait([f"agree/{name}/{r}" for r in range(world)])
+    return all(store().get(f"agree/{name}/{r}") == b"1" for r in range(world))
+
+
+# -- process entry ---------------------------------------------------------------------------
+def _entry(rank: int, fn, plan: ParallelPlan, port: int, args: tuple, error_queue) -> None:
+    global _STORE, _PLAN
+    try:
+        os.environ.update({"RANK": str(rank), "LOCAL_RANK": str(rank), "WORLD_SIZE": str(plan.world),
+                           "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), **plan.env})
+        _PLAN = plan
+        backend = plan.resolved_backend()
+        device = torch.device("cpu")
+        if plan.device_type == "cuda" and torch.cuda.is_available():
+            device = torch.device("cuda", plan.devices[rank % len(plan.devices)])
+            torch.cuda.set_device(device)
+        _STORE = dist.TCPStore("127.0.0.1", port, plan.world, is_master=False, timeout=timedelta(seconds=plan.timeout_s))
+        kwargs = {"device_id": device} if backend == "nccl" else {}
+        dist.init_process_group(backend, store=dist.PrefixStore("pg", _STORE), rank=rank, world_size=plan.world,
+                                timeout=timedelta(seconds=plan.timeout_s), **kwargs)
+        fn(rank, plan.world, device, *args)
+        dist.destroy_process_group()
+    except BaseException:  # noqa: BLE001 - report, then die without teardown so peers are not waited on
+        error_queue.put((rank, traceback.format_exc()))
+        sys.stderr.write(f"[rank{rank}] failed:\n{traceback.format_exc()}\n")
+        sys.stderr.flush()
+        os._exit(1)
+
+
+def spawn(fn, plan: ParallelPlan, args: tuple = (), poll_s: float = 0.1) -> None:
+    """Run `fn(rank, world, device, *args)` on `plan.world` processes; raises RuntimeError with
+    the first failing rank's traceback and kills the rest as soon as any rank dies."""
+    ctx = mp.get_context("spawn")
+    master = dist.TCPStore("127.0.0.1", 0, plan.world, is_master=True, wait_for_workers=False,
+                           timeout=timedelta(seconds=plan.timeout_s))
+    port = master.port
+    errors = ctx.SimpleQueue()
+    procs = [ctx.Process(target=_entry, args=(r, fn, plan, port, args, errors), daemon=False) for r in range(plan.world)]
+    for p in procs:
+        p.start()
+    failed = None
+    while True:
+        alive = [p.is_alive() for p in procs]
+        bad = [i for i, p in enumerate(procs) if not p.is_alive() and p.exitcode not in (0, None)]
+        if bad:
+            failed = bad[0]
+            break
+        if not any(alive):
+            break
+        time.sleep(poll_s)
+    if failed is not None:
+        for p in procs:
+            if p.is_alive():
+                p.kill()
+        for p in procs:
+            p.join(5)
+        trace = ""
+        while not errors.empty():
+            r, tb = errors.get()
+            trace += f"\n--- rank {r} ---\n{tb}"
+        raise RuntimeError(f"rank {failed} exited with code {procs[failed].exitcode}{trace}")
+    for p in procs:
+        p.join()

@@ -1,0 +1,165 @@
+"""Self-test workers for the parallel layer, run through the real launcher.
+
+Each worker is a module-level function `fn(rank, world, device, out_dir, ...)` that writes
+`<out_dir>/rank<r>.json`; `spawn_results` launches them and collects the files. They serve
+the CPU (gloo) tests, `scripts/dist/check_comm.py` on GPUs, and the fail-fast tests, which
+make failures on the HOST only: a rank that raises, a rank that never joins
+(`src/kohakumoss/parallel/telemetry/selftest.py:44-342` is the reference's equivalent).
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import time
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+from . import launch
+from .launch import ParallelPlan
+
+
+def _write(out_dir: str, rank: int, payload: dict) -> None:
+    Path(out_dir).mkdir(parents=True, exist_ok=True)
+    tmp = Path(out_dir, f"rank{rank}.json.tmp")
+    tmp.write_text(json.dumps(payload))
+    os.replace(tmp, Path(out_dir, f"rank{rank}.json"))
+
+
+def spawn_results(fn, world: int, out_dir: str, args: tuple = (), device_type: str = "cpu", timeout_s: float = 60.0,
+                  backend: str = "auto", env: dict | None = None) -> list[dict]:
+    plan = ParallelPlan(world=world, devices=tuple(range(world)), backend=backend, timeout_s=timeout_s,
+                        gate_timeout_s=timeout_s, device_type=device_type, env=env or {})
+    launch.spawn(fn, plan, (out_dir, *args))
+    return [json.loads(Path(out_dir, f"rank{r}.json").read_text()) for r in range(world)]
+
+
+def _params(device, dtype=torch.float32, seed: int = 0):
+    g = torch.Generator().manual_seed(seed)
+    shapes = [(64, 16), (16,), (128, 8), (8, 128), (32, 32), (5,)]
+    return [torch.nn.Parameter(torch.randn(s, generator=g).to(device=device, dtype=dtype)) for s in shapes]
+
+
+def reducer_worker(rank, world, device, out_dir, backend="torch", dtype="fp32", bucket_mb=0.004, micro_batches=2):
+    """Gradients are views of the buckets, sums match the analytic total, ranks agree bitwise."""
+    from .ddp import GradReducer, broadcast_params
+
+    dt = {"fp32": torch.float32, "bf16": torch.bfloat16}[dtype]
+    params = _params(device, dt, seed=rank)  # different on every rank until broadcast
+    broadcast_params(params)
+    ref = _params(device, dt, seed=0)
+    same_after_broadcast = all(torch.equal(a, b) for a, b in zip(params, ref))
+    reducer = GradReducer(params, bucket_mb=bucket_mb, backend=backend, device=device, reduce_dtype="fp32")
+    views = all(p.grad is not None and any(p.grad.data_ptr() == v.data_ptr() for b in reducer.buckets for v in b.views) for p in params)
+    expected = [torch.zeros_like(p, dtype=torch.float32) for p in params]
+    for mb in range(micro_batches):
+        reducer.start(last=mb == micro_batches - 1)
+        loss = sum(((p.float() * (rank + 1 + mb)) ** 2).sum() for p in params)
+        loss.backward()
+        for r in range(world):
+            for e, p in zip(expected, ref):
+                e += 2 * p.float() * (r + 1 + mb) ** 2
+    reducer.finish()
+    if device.type == "cuda":
+        torch.cuda.synchronize()
+    err = max(((p.grad.float() - e).abs().max() / e.abs().max().clamp_min(1e-6)).item() for p, e in zip(params, expected))
+    digest = float(sum(p.grad.double().sum().item() for p in params))
+    gathered = [None] * world
+    dist.all_gather_object(gathered, digest)
+    status = [0, 0, 0, 0]
+    if device.type == "cuda":
+        from ..ops import native
+
+        status = native.load().kernel_status().tolist()
+    _write(out_dir, rank, {"views": views, "same_after_broadcast": same_after_broadcast, "rel_err": err,
+                           "ranks_agree": len(set(gathered)) == 1, "buckets": len(reducer.buckets),
+                           "backend": reducer.backend, "status": status, **reducer.metrics()})
+
+
+def gates_worker(rank, world, device, out_dir):
+    value = launch.rank0_value("config", lambda: {"seed": 1234, "who": "rank0"}, rank)
+    if rank == 0:
+        time.sleep(0.2)  # uneven start-up work on rank 0 only
+        launch.release_ranks("data-ready")
+    else:
+        launch.wait_for_rank0("data-ready")
+    launch.startup_barrier("built", rank, world)
+    agree = launch.store_agree("ckpt", ok=rank != 1, rank=rank, world=world)
+    _write(out_dir, rank, {"value": value, "agree": agree})
+
+
+def raise_worker(rank, world, device, out_dir, bad_rank=1):
+    """`bad_rank` raises while the others sit in a store wait that would last minutes."""
+    if rank == bad_rank:
+        time.sleep(0.3)
+        raise RuntimeError("injected failure on the host")
+    launch.wait_for_rank0("never-released", timeout_s=600)
+    _write(out_dir, rank, {"unexpected": True})
+
+
+def comm_worker(rank, world, device, out_dir, sizes_mb=(1, 16, 64), iters=5):
+    """Link measurement: all-reduce (NCCL and, on GPUs, the peer-memory kernel), all-gather,
+    reduce-scatter and a ring p2p hop; device-timed, max over ranks."""
+    rows = []
+    cuda = device.type == "cuda"
+
+    def timed(fn):
+        fn()
+        if cuda:
+            torch.cuda.synchronize()
+            dist.barrier()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(iters):
+                fn()
+            e.record()
+            torch.cuda.synchronize()
+            ms = torch.tensor([s.elapsed_time(e) / iters], device=device)
+        else:
+            dist.barrier()
+            t0 = time.perf_counter()
+            for _ in range(iters):
+                fn()
+            ms = torch.tensor([(time.perf_counter() - t0) * 1e3 / iters])
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    for mb in sizes_mb:
+        n = int(mb * (1 << 20) // 4)
+        n -= n % (8 * world)
+        x = torch.ones(n, device=device)
+        ms = timed(lambda: dist.all_reduce(x))
+        rows.append({"op": "all_reduce", "mb": mb, "ms": ms, "busbw_gbs": 2 * (world - 1) / world * n * 4 / ms / 1e6})
+        shard = torch.ones(n // world, device=device, dtype=torch.bfloat16 if cuda else torch.float32)
+        full = torch.empty(n // world * world, device=device, dtype=shard.dtype)
+        ms = timed(lambda: dist.all_gather_into_tensor(full, shard))
+        rows.append({"op": "all_gather", "mb": mb, "ms": ms})
+        if cuda:
+            ms = timed(lambda: dist.reduce_scatter_tensor(shard, full))
+            rows.append({"op": "reduce_scatter", "mb": mb, "ms": ms})
+            from . import symm
+            from ..ops import native
+
+            if symm.available(device):
+                sb = symm.SymmetricBuffer(n, torch.float32, device)
+                flags = symm.PeerFlags(device)
+                ops = native.load()
+                for label, mc in (("peer", 0), ("multimem", sb.mc_ptr)):
+                    if label == "multimem" and not mc:
+                        continue
+                    sb.local.fill_(1.0)
+                    ms = timed(lambda mc=mc: ops.allreduce(sb.ptrs, flags.buffer.ptrs, mc, n, 0, rank, 1.0, flags.next_epoch(), 32))
+                    rows.append({"op": f"kmoss_allreduce_{label}", "mb": mb, "ms": ms,
+                                 "busbw_gbs": 2 * (world - 1) / world * n * 4 / ms / 1e6})
+    if world > 1:
+        t = torch.ones(1 << 20, device=device)
+
+        def hop():
+            ops = [dist.P2POp(dist.isend, t, (rank + 1) % world), dist.P2POp(dist.irecv, torch.empty_like(t), (rank - 1) % world)]
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+
+        rows.append({"op": "ring_p2p_4MB", "ms": timed(hop)})
+    _write(out_dir, rank, {"rows": rows})

@@ -1,0 +1,42 @@
+"""Multi-GPU sanity check: reducer self-test, then all_reduce / all_gather / reduce_scatter /
+ring p2p sweeps, NCCL next to the peer-memory all-reduce kernel (device-timed, max over ranks).
+
+    python scripts/dist/check_comm.py --gpus 2 [--out runs/comm]
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import tempfile
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+from kohakumosstrainer_b200.parallel import selftest  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=2)
+    ap.add_argument("--out", default="")
+    ap.add_argument("--sizes-mb", type=float, nargs="*", default=[1, 16, 64, 256])
+    args = ap.parse_args()
+    out = Path(args.out or tempfile.mkdtemp(prefix="kmoss-comm-"))
+    report = {}
+    for backend, dtype in (("torch", "fp32"), ("kohakumoss", "fp32"), ("kohakumoss", "bf16")):
+        res = selftest.spawn_results(selftest.reducer_worker, args.gpus, str(out / f"reducer-{backend}-{dtype}"),
+                                     (backend, dtype, 0.004), device_type="cuda", timeout_s=120)
+        report[f"reducer/{backend}/{dtype}"] = res[0]
+        print(f"reducer {backend}/{dtype}: {res[0]}")
+    res = selftest.spawn_results(selftest.comm_worker, args.gpus, str(out / "sweep"), (tuple(args.sizes_mb),),
+                                 device_type="cuda", timeout_s=300)
+    report["sweep"] = res[0]["rows"]
+    for row in res[0]["rows"]:
+        print(row)
+    (out / "report.json").write_text(json.dumps(report, indent=1))
+    print("report:", out / "report.json")
+
+
+if __name__ == "__main__":
+    main()

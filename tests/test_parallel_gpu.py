@@ -1,0 +1,43 @@
+"""Peer-memory all-reduce and the DDP reducer on real GPUs, plus the bounded-wait contract."""
+
+import pytest
+import torch
+
+from kohakumosstrainer_b200.parallel import selftest
+
+
+@pytest.mark.gpu
+def test_bounded_wait_returns_status_instead_of_hanging():
+    """A wait on a flag nothing ever sets gives up after its limit and records
+    STATUS_PEER_TIMEOUT; the context stays usable."""
+    import time
+
+    from kohakumosstrainer_b200.ops import native
+
+    ops = native.load()
+    ops.reset_status()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    t0 = time.time()
+    ops.bounded_wait_probe(flag, 7, 50.0)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0
+    st = ops.kernel_status().tolist()
+    assert st[0] == 2 and st[1] == 1099 and st[3] == 7
+    with pytest.raises(RuntimeError, match="kernel status"):
+        native.check_status()
+    ops.reset_status()
+    native.check_status()
+    assert torch.ones(4, device="cuda").sum().item() == 4.0
+
+
+@pytest.mark.gpu
+@pytest.mark.multi_gpu
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_peer_memory_reducer_matches_analytic_sum(tmp_path, dtype):
+    env = {"NCCL_NVLS_ENABLE": "0"}
+    res = selftest.spawn_results(selftest.reducer_worker, 2, str(tmp_path), ("kohakumoss", dtype, 0.004),
+                                 device_type="cuda", timeout_s=120, env=env)
+    for r in res:
+        assert r["backend"] == "kohakumoss"
+        assert r["views"] and r["ranks_agree"] and r["status"][0] == 0
+        assert r["rel_err"] < (1e-5 if dtype == "fp32" else 2e-2)
