@@ -9,9 +9,17 @@ when the fabric supports it). The collectives themselves are this package's kern
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 from torch import Tensor
+
+
+# NVLS multicast mappings are opt-in (KMOSS_NVLS=1): a rank that dies while its memory is bound
+# to a multicast object can fault its peers' GPUs, and the peer load / store path needs none.
+if os.environ.get("KMOSS_NVLS", "0") != "1":
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 
 def available(device) -> bool:
