@@ -93,7 +93,43 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_two_shot_kernel(AllReduc
   const size_t begin = per_rank * a.rank;
   const size_t end = min(a.n_vec, begin + per_rank);
   const size_t stride = (size_t)gridDim.x * AR_THREADS;
-  for (size_t v = begin + (size_t)blockIdx.x * AR_THREADS + threadIdx.x; v < end; v += stride) {
+  size_t v0 = begin + (size_t)blockIdx.x * AR_THREADS + threadIdx.x;
+  if (a.mc_ptr == nullptr) {
+    // peer loads / stores, two vectors per thread in flight: every load of a round is issued
+    // before the first add, so NVLink latency is paid once per round, not once per vector
+    constexpr int U = 2;
+    for (; v0 + (U - 1) * stride < end; v0 += U * stride) {
+      uint4 w[U][AR_MAX_WORLD];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int p = 0; p < AR_MAX_WORLD; ++p)
+          if (p < a.world)
+            w[u][p] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.ptrs[p]) + (v0 + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int p = 0; p < AR_MAX_WORLD; ++p) {
+          if (p < a.world) {
+            if (BF16) {
+              float2 x0 = unpack_bf16(w[u][p].x), x1 = unpack_bf16(w[u][p].y), x2 = unpack_bf16(w[u][p].z), x3 = unpack_bf16(w[u][p].w);
+              acc[0] += x0.x; acc[1] += x0.y; acc[2] += x1.x; acc[3] += x1.y; acc[4] += x2.x; acc[5] += x2.y; acc[6] += x3.x; acc[7] += x3.y;
+            } else {
+              acc[0] += __uint_as_float(w[u][p].x); acc[1] += __uint_as_float(w[u][p].y);
+              acc[2] += __uint_as_float(w[u][p].z); acc[3] += __uint_as_float(w[u][p].w);
+            }
+          }
+        }
+        const uint4 out = pack_acc<BF16>(acc, a.scale);
+#pragma unroll
+        for (int p = 0; p < AR_MAX_WORLD; ++p)
+          if (p < a.world)
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.ptrs[p]) + (v0 + u * stride) * 16) = out;
+      }
+    }
+  }
+  for (size_t v = v0; v < end; v += stride) {
     uint4 out;
     if (a.mc_ptr != nullptr) {
       // in-switch reduction: one load returns the sum over every rank's copy

@@ -75,7 +75,7 @@ class _Bucket:
 
 class GradReducer:
     def __init__(self, params, group=None, bucket_mb: float = 25, reduce_dtype: str | torch.dtype | None = "fp32",
-                 backend: str = "kohakumoss", device=None, average: bool = False, comm_blocks: int = 32,
+                 backend: str = "kohakumoss", device=None, average: bool = False, comm_blocks: int = 48,
                  use_multimem: bool = True):
         from . import symm
 

@@ -26,7 +26,7 @@ def available(device) -> bool:
     if torch.device(device).type != "cuda" or not dist.is_initialized():
         return False
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
+        from torch.distributed import _symmetric_memory  # noqa: F401
     except ImportError:
         return False
     return dist.get_backend() == "nccl"
