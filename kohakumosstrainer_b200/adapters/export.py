@@ -1,0 +1,148 @@
+"""Adapter files: `lycoris` (native state), `comfy` (ComfyUI-loadable), `merged`, `diffusers`.
+
+Key stems are `lora_unet_<path>` or `diffusion_model.<path>`; tensor names per algorithm are the
+LyCORIS ones (`adapters/modules.py`). The `comfy` export rewrites what ComfyUI cannot read:
+DoRA magnitudes are renormalised by ||W|| / ||W + dW||, rescaled OFT leaves as a dense `diff`,
+and q / k / v LoRAs may be fused into one `proj.qkv` LoRA (block-diagonal up, concatenated down,
+alpha = rank). File metadata mirrors kohya / LyCORIS conventions
+(`src/kohakumoss/adapters/train/adapter_set.py:371-446`, `export/fused.py:44-63`).
+"""
+
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import torch
+from safetensors import safe_open
+from safetensors.torch import save_file
+from torch import Tensor
+
+FORMATS = ("lycoris", "comfy", "merged", "diffusers")
+
+
+def metadata(aset, fmt: str) -> dict[str, str]:
+    cfg = aset.cfg
+    return {
+        "kohakumoss_format": fmt, "kohakumoss_key_style": "lora_unet", "kohakumoss_prefix": cfg.prefix,
+        "kohakumoss_algo": cfg.algo, "kohakumoss_adapter_state": "1",
+        "kohakumoss_spec": json.dumps({"algo": cfg.algo, "preset": cfg.preset, "dim": cfg.dim, "alpha": cfg.alpha,
+                                       "algo_kwargs": cfg.algo_kwargs, "dora": cfg.dora, "mode": cfg.mode}),
+        "ss_network_module": "lycoris.kohya", "ss_network_dim": str(cfg.dim), "ss_network_alpha": str(cfg.alpha),
+        "ss_network_args": json.dumps({"algo": cfg.algo, "preset": cfg.preset if isinstance(cfg.preset, str) else "custom",
+                                       **{k: str(v) for k, v in cfg.algo_kwargs.items()}}),
+    }
+
+
+def fuse_qkv_lora(state: dict[str, Tensor], prefix: str) -> dict[str, Tensor]:
+    """Replace `..._proj_q/k/v` LoRA triples by one `..._proj_qkv` LoRA: concatenated down
+    [3r, in], block-diagonal up [3 out, 3r], each block scaled by its alpha / r, alpha = 3r."""
+    out = dict(state)
+    tail = "_proj_q.lora_down.weight"
+    stems = sorted(k[: -len(tail)] for k in state if k.endswith(tail))
+    for stem in stems:
+        parts = [f"{stem}_proj_{n}" for n in "qkv"]
+        if not all(f"{p}.lora_down.weight" in state for p in parts):
+            continue
+        downs = [state[f"{p}.lora_down.weight"].float() for p in parts]
+        ups = [state[f"{p}.lora_up.weight"].float() for p in parts]
+        scales = [float(state[f"{p}.alpha"]) / d.shape[0] for p, d in zip(parts, downs)]
+        r_total = sum(d.shape[0] for d in downs)
+        up = torch.zeros(sum(u.shape[0] for u in ups), r_total)
+        row = col = 0
+        for u, s in zip(ups, scales):
+            up[row : row + u.shape[0], col : col + u.shape[1]] = u * s
+            row, col = row + u.shape[0], col + u.shape[1]
+        dtype = state[f"{parts[0]}.lora_down.weight"].dtype
+        out[f"{stem}_proj_qkv.lora_down.weight"] = torch.cat(downs, 0).to(dtype)
+        out[f"{stem}_proj_qkv.lora_up.weight"] = up.to(dtype)
+        out[f"{stem}_proj_qkv.alpha"] = torch.tensor(float(r_total))
+        for p in parts:
+            for t in ("lora_down.weight", "lora_up.weight", "alpha"):
+                out.pop(f"{p}.{t}", None)
+    return out
+
+
+def comfy_state(aset, model) -> dict[str, Tensor]:
+    """Adapter state rewritten for ComfyUI's loaders."""
+    state = {}
+    paths = dict(model.named_modules())
+    for name, path, mod in aset.items():
+        lin = paths[path]
+        sd = {k: v.detach().cpu() for k, v in mod.state_dict().items()}
+        if mod.dora_scale is not None:
+            w = lin.base_weight(torch.float32).cpu()
+            merged = w + mod.delta(w).detach().cpu().float() * mod.base_scale
+            dim = 1 if mod.dora_on_output else 0
+            sd["dora_scale"] = (mod.dora_scale.detach().cpu().float() * w.norm(dim=dim, keepdim=True) /
+                                merged.norm(dim=dim, keepdim=True).clamp_min(1e-12)).to(mod.dora_scale.dtype)
+        if mod.algo == "oft" and getattr(mod, "rescale", None) is not None:
+            w = lin.base_weight(torch.float32).cpu()
+            sd = {"diff": (mod.merged(w.to(mod.oft_blocks.device)).cpu().float() - w)}
+        for k, v in sd.items():
+            state[f"{name}.{k}"] = v.contiguous()
+    for path, p in aset.norm_params.items():
+        state[f"{aset.cfg.prefix}_{path}".replace(".", "_") + ".w_norm"] = p.detach().cpu()
+    return state
+
+
+def export(aset, model, path: str | Path, fmt: str = "comfy", fused_qkv: bool = False, dtype=torch.bfloat16) -> Path:
+    """Write the adapters of `aset` in `fmt`; returns the written path."""
+    if fmt not in FORMATS:
+        raise ValueError(f"export format must be one of {FORMATS}, got {fmt}")
+    path = Path(path)
+    path.parent.mkdir(parents=True, exist_ok=True)
+    if fmt == "merged":
+        from ..models.io import save_single
+
+        save_single(model, path, dtype, merge_adapters=True, metadata={"kohakumoss_format": "merged"})
+        return path
+    if fmt == "diffusers":
+        from ..models.io import save_diffusers
+
+        save_diffusers(model, path, dtype, merge_adapters=True)
+        return path
+    state = {k: v.cpu().contiguous() for k, v in aset.adapter_state().items()} if fmt == "lycoris" else comfy_state(aset, model)
+    if fused_qkv and aset.cfg.algo in ("lora", "locon") and not aset.cfg.dora:
+        state = fuse_qkv_lora(state, aset.cfg.prefix)
+    save_file(state, str(path), metadata(aset, fmt))
+    return path
+
+
+def load_adapter_file(path: str | Path) -> tuple[dict[str, Tensor], dict]:
+    with safe_open(str(path), framework="pt") as f:
+        return {k: f.get_tensor(k) for k in f.keys()}, dict(f.metadata() or {})
+
+
+def detect_algo(state: dict[str, Tensor]) -> str:
+    keys = " ".join(state)
+    for marker, algo in (("hada_w1_a", "loha"), ("lokr_w", "lokr"), ("oft_blocks", "oft"), ("lora_down", "lora"), (".diff", "full"), ("on_input", "ia3")):
+        if marker in keys:
+            return algo
+    raise ValueError("cannot tell the adapter algorithm from the file's tensor names")
+
+
+def load_adapters(model, path: str | Path, multiplier: float = 1.0, mode: str = "merge"):
+    """Attach the adapters of a saved file (LyCORIS or comfy key style) to `model` for
+    inference; `mode="merge"` folds them into dense weights where the base is dense."""
+    from .apply import AdapterConfig, apply
+
+    state, meta = load_adapter_file(path)
+    spec = json.loads(meta.get("kohakumoss_spec", "{}")) if meta.get("kohakumoss_spec") else {}
+    algo = spec.get("algo") or detect_algo(state)
+    ranks = [v.shape[0] for k, v in state.items() if k.endswith("lora_down.weight")]
+    dim = spec.get("dim") or (ranks[0] if ranks else 8)
+    stems = sorted({k.rsplit(".", 1)[0] if not k.endswith(".weight") else k.rsplit(".", 2)[0] for k in state})
+    paths = {name: (f"lora_unet_{name}".replace(".", "_")) for name, _ in model.named_modules()}
+    targets = [name for name, stem in paths.items() if stem in stems]
+    cfg = AdapterConfig(algo=algo, preset={"target_name": [f"^{t.replace('.', chr(92) + '.')}$" for t in targets]}, dim=dim,
+                        alpha=spec.get("alpha", dim), algo_kwargs=spec.get("algo_kwargs", {}), dora=spec.get("dora", False),
+                        mode=mode, multiplier=multiplier)
+    aset = apply(model, cfg, freeze_base=False)
+    aset.load_adapter_state(state, strict=False)
+    for k, v in state.items():
+        if k.endswith(".alpha"):
+            mod = aset.modules_by_name[k[: -len(".alpha")]] if k[: -len(".alpha")] in aset.modules_by_name else None
+            if mod is not None:
+                mod._alpha = float(v)
+    return aset

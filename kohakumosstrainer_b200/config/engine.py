@@ -1,0 +1,140 @@
+"""A small engine with the behaviour of `kogine run script.py --config cfg.py --set K=V`.
+
+* A script's UPPER_CASE module globals are its knobs and their defaults
+  (`scripts/train/moss.py`).
+* A config is a Python file that assigns some of them; `use_config("layer.py")` inside a config
+  pulls in another layer first (paths relative to the including file, then to `configs/`), so
+  later assignments win (`configs/moss/recipes/*.py` in the reference compose `_base`, `algo`,
+  `data`, `parallel`, `precision`, `vram`, `weights` layers this way).
+* `--set KEY=VALUE` parses VALUE as a Python literal (falling back to a string).
+* `check` validates names (with did-you-mean hints), choices and types of ALL knobs and raises
+  one `ConfigError` (a `SystemExit`) listing every problem
+  (`src/kohakumoss_common/knobs.py:18-205`, `src/kohakumoss/training/knobs.py:68-291`).
+"""
+
+from __future__ import annotations
+
+import ast
+import difflib
+import runpy
+from pathlib import Path
+
+
+class ConfigError(SystemExit):
+    def __init__(self, problems: list[str]):
+        self.problems = list(problems)
+        super().__init__("configuration problems:\n" + "\n".join(f"  - {p}" for p in self.problems))
+
+
+def collect(namespace: dict) -> dict:
+    """UPPER_CASE names of a namespace (module globals) -> values."""
+    return {k: v for k, v in namespace.items() if k.isupper() and not k.startswith("_")}
+
+
+def script_knobs(script: str | Path) -> dict:
+    """Defaults of a script: its UPPER_CASE globals, without running `main`."""
+    return collect(runpy.run_path(str(script), run_name="__kmoss_schema__"))
+
+
+def _resolve(name: str, including: Path | None, roots: list[Path]) -> Path:
+    cands = [Path(name)]
+    if including is not None:
+        cands.append(including.parent / name)
+    cands += [r / name for r in roots]
+    for c in cands:
+        if c.is_file():
+            return c.resolve()
+    raise FileNotFoundError(f"config layer {name!r} not found (looked in {[str(c) for c in cands]})")
+
+
+def load_config(path: str | Path, roots: list[str | Path] | None = None, _seen: tuple = ()) -> dict:
+    """Knobs of a config file with its `use_config` layers applied in order."""
+    roots = [Path(r) for r in (roots or [])]
+    repo_configs = Path(__file__).resolve().parents[2] / "configs"
+    if repo_configs.is_dir() and repo_configs not in roots:
+        roots.append(repo_configs)
+    file = _resolve(str(path), None, roots)
+    if file in _seen:
+        raise ConfigError([f"config layers include each other: {' -> '.join(str(s) for s in _seen + (file,))}"])
+    merged: dict = {}
+
+    def use_config(name: str) -> None:
+        merged.update(load_config(_resolve(name, file, roots), roots, _seen + (file,)))
+
+    ns = {"use_config": use_config, "__file__": str(file)}
+    code = compile(file.read_text(), str(file), "exec")
+    exec(code, ns)  # noqa: S102 - config files are Python by design
+    merged.update(collect(ns))
+    return merged
+
+
+def apply_sets(knobs: dict, sets: list[str]) -> dict:
+    out = dict(knobs)
+    problems = []
+    for item in sets or []:
+        if "=" not in item:
+            problems.append(f"--set {item!r}: expected KEY=VALUE")
+            continue
+        key, raw = item.split("=", 1)
+        try:
+            value = ast.literal_eval(raw)
+        except (ValueError, SyntaxError):
+            value = raw
+        out[key.strip()] = value
+    if problems:
+        raise ConfigError(problems)
+    return out
+
+
+def _type_ok(value, default) -> bool:
+    if default is None or value is None:
+        return True
+    if isinstance(default, bool):
+        return isinstance(value, (bool, str)) if not isinstance(value, bool) else True
+    if isinstance(default, (int, float)) and not isinstance(default, bool):
+        return isinstance(value, (int, float, str)) and not isinstance(value, bool) or isinstance(value, str)
+    if isinstance(default, (tuple, list)):
+        return isinstance(value, (tuple, list, str, int, float))
+    if isinstance(default, dict):
+        return isinstance(value, (dict, str))
+    if isinstance(default, str):
+        return isinstance(value, (str, bool, dict, tuple, list, int, float))
+    return True
+
+
+def check(knobs: dict, defaults: dict, choices: dict | None = None, extra_checks=()) -> dict:
+    """Validate `knobs` against the script's `defaults`; returns defaults updated with knobs.
+    Raises one ConfigError with every problem found."""
+    problems = []
+    for name, value in knobs.items():
+        if name not in defaults:
+            hint = difflib.get_close_matches(name, defaults, n=2)
+            problems.append(f"unknown knob {name}" + (f" (did you mean {', '.join(hint)}?)" if hint else ""))
+            continue
+        if not _type_ok(value, defaults[name]):
+            problems.append(f"{name}: expected {type(defaults[name]).__name__}, got {type(value).__name__} ({value!r})")
+    merged = {**defaults, **{k: v for k, v in knobs.items() if k in defaults}}
+    for name, allowed in (choices or {}).items():
+        value = merged.get(name)
+        if callable(allowed):
+            msg = allowed(value)
+            if msg:
+                problems.append(f"{name}: {msg}")
+        elif isinstance(value, str) and value not in allowed:
+            hint = difflib.get_close_matches(value, [a for a in allowed if isinstance(a, str)], n=2)
+            problems.append(f"{name}={value!r} is not one of {', '.join(map(str, allowed))}" + (f" (did you mean {', '.join(hint)}?)" if hint else ""))
+    for fn in extra_checks:
+        problems += list(fn(merged) or [])
+    if problems:
+        raise ConfigError(problems)
+    return merged
+
+
+def run_script(script: str | Path, config: str | None = None, sets: list[str] | None = None, roots=None) -> dict:
+    """Resolve the knobs of `script` (defaults <- config layers <- --set) and call its `main`
+    with them installed as module globals; returns the namespace."""
+    knobs = {}
+    if config:
+        knobs.update(load_config(config, roots))
+    knobs = apply_sets(knobs, sets or [])
+    return runpy.run_path(str(script), init_globals={"__kmoss_overrides__": knobs}, run_name="__main__")

@@ -1,0 +1,190 @@
+"""Checkpoint formats of the DiT: load HF shard folders / ComfyUI single files / own saves,
+save single-file, fused-qkv and diffusers layouts.
+
+Key handling follows the reference (`src/kohakumoss/model/io/keymap.py:8-47`,
+`io/load.py:247-316`, `io/save.py:33-156`): the prefixes `model.diffusion_model.`,
+`diffusion_model.`, `transformer.` are stripped, a fused `layers.N.proj.qkv.weight` [3D, D] is
+split q;k;v, `rope.bands` is derived (optional in files), and loading accounts for every key
+(missing and unexpected keys are errors). The diffusers layout is
+`config.json` (`_class_name MOSSImageTransformer`) + `diffusion_pytorch_model-0000i-of-0000n.
+safetensors` + `diffusion_pytorch_model.safetensors.index.json`.
+"""
+
+from __future__ import annotations
+
+import json
+import re
+from pathlib import Path
+
+import torch
+from safetensors import safe_open
+from safetensors.torch import save_file
+from torch import Tensor
+
+from ..types.arch import MossArchConfig
+
+PREFIXES = ("model.diffusion_model.", "diffusion_model.", "transformer.")
+DERIVED = ("rope.bands",)
+FUSED_QKV = re.compile(r"^(layers\.\d+\.proj)\.qkv\.weight$")
+INDEX = "diffusion_pytorch_model.safetensors.index.json"
+FP8_META = "kohakumoss_fp8"
+
+
+def strip_prefix(keys) -> str:
+    keys = list(keys)
+    for prefix in PREFIXES:
+        if keys and all(k.startswith(prefix) for k in keys):
+            return prefix
+    return ""
+
+
+def split_fused_qkv(sd: dict[str, Tensor]) -> dict[str, Tensor]:
+    out = {}
+    for key, value in sd.items():
+        m = FUSED_QKV.match(key)
+        if m is None:
+            out[key] = value
+            continue
+        q, k, v = value.chunk(3, 0)
+        out[f"{m.group(1)}.q.weight"], out[f"{m.group(1)}.k.weight"], out[f"{m.group(1)}.v.weight"] = q, k, v
+    return out
+
+
+def fuse_qkv(sd: dict[str, Tensor], depth: int) -> dict[str, Tensor]:
+    out = dict(sd)
+    for i in range(depth):
+        base = f"layers.{i}.proj"
+        parts = [out.pop(f"{base}.{n}.weight") for n in ("q", "k", "v")]
+        out[f"{base}.qkv.weight"] = torch.cat(parts, 0)
+    return out
+
+
+def normalize_keys(sd: dict[str, Tensor]) -> dict[str, Tensor]:
+    prefix = strip_prefix(sd.keys())
+    sd = {k[len(prefix):]: v for k, v in sd.items()}
+    return split_fused_qkv(sd)
+
+
+def read_state(path: str | Path, device="cpu") -> tuple[dict[str, Tensor], dict]:
+    """All tensors (and safetensors metadata) of a file or a sharded folder."""
+    path = Path(path)
+    files = [path] if path.is_file() else sorted(path.glob("*.safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no .safetensors under {path}")
+    state, meta = {}, {}
+    for f in files:
+        with safe_open(str(f), framework="pt", device=str(device)) as fh:
+            meta.update(fh.metadata() or {})
+            for k in fh.keys():
+                state[k] = fh.get_tensor(k)
+    return state, meta
+
+
+def arch_from_config(folder: str | Path) -> MossArchConfig | None:
+    cfg = Path(folder) / "config.json"
+    if not cfg.exists():
+        return None
+    c = json.loads(cfg.read_text())
+    return MossArchConfig(dim=c["dim"], depth=c["num_layers"], heads=c["num_heads"], ffn_dim=c["ffn_dim"],
+                          text_dim=c["text_dim"], latent_channels=c["latent_channels"], freq_dim=c["freq_dim"],
+                          rope_base=c["rope_base"])
+
+
+def load_backbone(model, path: str | Path, strict: bool = True) -> dict:
+    """Load weights into `model` with strict key accounting; returns the file metadata."""
+    state, meta = read_state(path)
+    state = normalize_keys(state)
+    own = dict(model.state_dict())
+    missing = [k for k in own if k not in state and k not in DERIVED]
+    unexpected = [k for k in state if k not in own]
+    if strict and (missing or unexpected):
+        raise KeyError(f"checkpoint does not match the model: missing {missing[:6]} ({len(missing)}), "
+                       f"unexpected {unexpected[:6]} ({len(unexpected)})")
+    with torch.no_grad():
+        for k, p in own.items():
+            if k in state:
+                if p.shape != state[k].shape:
+                    raise ValueError(f"{k}: checkpoint shape {tuple(state[k].shape)} != model {tuple(p.shape)}")
+                p.copy_(state[k].to(p.dtype))
+    return meta
+
+
+def export_state(model, dtype: torch.dtype | None = torch.bfloat16, merge_adapters: bool = False) -> dict[str, Tensor]:
+    """Bare-key dense state of the backbone: quantised bases are dequantised, adapters merged
+    on request; derived buffers are left out."""
+    from .linear import MossLinear
+
+    out = {}
+    for name, module in model.named_modules():
+        if isinstance(module, MossLinear):
+            w = module.effective_weight(torch.float32) if merge_adapters else module.base_weight(torch.float32)
+            out[f"{name}.weight"] = w.detach().to(dtype or w.dtype).cpu().contiguous()
+            if module.bias is not None:
+                out[f"{name}.bias"] = module.bias.detach().to(dtype or module.bias.dtype).cpu().contiguous()
+    for name, p in model.state_dict().items():
+        if name in DERIVED or name in out:
+            continue
+        out[name] = p.detach().to(dtype if (dtype and p.is_floating_point()) else p.dtype).cpu().contiguous()
+    return {k: out[k] for k in sorted(out)}
+
+
+def save_single(model, path: str | Path, dtype=torch.bfloat16, fused_qkv: bool = False, prefix: str = "",
+                merge_adapters: bool = False, metadata: dict | None = None) -> None:
+    """One `.safetensors` file (ComfyUI style with `fused_qkv=True` and a prefix)."""
+    state = export_state(model, dtype, merge_adapters)
+    if fused_qkv:
+        state = fuse_qkv(state, model.cfg.depth)
+    state = {prefix + k: v for k, v in state.items()}
+    Path(path).parent.mkdir(parents=True, exist_ok=True)
+    save_file(state, str(path), {"format": "pt", **(metadata or {})})
+
+
+def write_diffusers(state: dict[str, Tensor], out_dir, cfg: MossArchConfig, shard_bytes: int = 5_000_000_000,
+                    metadata: dict | None = None) -> None:
+    out_dir = Path(out_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    shards, size = [{}], 0
+    for k, t in state.items():
+        nbytes = t.numel() * t.element_size()
+        if shards[-1] and size + nbytes > shard_bytes:
+            shards.append({})
+            size = 0
+        shards[-1][k] = t
+        size += nbytes
+    n = len(shards)
+    weight_map = {}
+    for i, shard in enumerate(shards, 1):
+        name = f"diffusion_pytorch_model-{i:05d}-of-{n:05d}.safetensors"
+        save_file(shard, str(out_dir / name), {"format": "pt", **(metadata or {})})
+        weight_map.update({k: name for k in shard})
+    total = sum(t.numel() * t.element_size() for t in state.values())
+    (out_dir / INDEX).write_text(json.dumps({"metadata": {"total_size": total, **(metadata or {})}, "weight_map": weight_map}, indent=2))
+    config = {"_class_name": "MOSSImageTransformer", "_diffusers_version": "0.38.0", "dim": cfg.dim, "ffn_dim": cfg.ffn_dim,
+              "freq_dim": cfg.freq_dim, "latent_channels": cfg.latent_channels, "num_heads": cfg.heads,
+              "num_layers": cfg.depth, "rope_base": cfg.rope_base, "text_dim": cfg.text_dim}
+    (out_dir / "config.json").write_text(json.dumps(config, indent=2))
+
+
+def save_diffusers(model, out_dir, dtype=torch.bfloat16, shard_bytes: int = 5_000_000_000, merge_adapters: bool = False) -> None:
+    write_diffusers(export_state(model, dtype, merge_adapters), out_dir, model.cfg, shard_bytes)
+
+
+def save_fp8(model, path: str | Path, recipe: str = "tensor") -> None:
+    """Pre-quantised DiT file: `<n>.weight` e4m3 + `<n>.weight_scale`, metadata `kohakumoss_fp8`
+    (the reference's `scripts/export/fp8_quant.py` format)."""
+    from ..quant.weights import _quantize
+    from .linear import MossLinear
+
+    state = {}
+    quantised = set()
+    for name, module in model.named_modules():
+        if isinstance(module, MossLinear) and re.search(r"layers\.\d+\.proj\.", name):
+            q, scale, col = _quantize(module.base_weight(torch.float32), recipe)
+            state[f"{name}.weight"] = q.cpu()
+            state[f"{name}.weight_scale"] = (scale[:1] if recipe == "tensor" else col).float().cpu()
+            quantised.add(f"{name}.weight")
+    for k, v in export_state(model, torch.bfloat16).items():
+        if k not in quantised:
+            state[k] = v
+    Path(path).parent.mkdir(parents=True, exist_ok=True)
+    save_file(state, str(path), {"format": "pt", FP8_META: json.dumps({"recipe": recipe, "dtype": "e4m3"})})

@@ -1,0 +1,182 @@
+"""Training checkpoints: directory format, atomic writes, keep-last, retry, exact resume.
+
+    <out>/checkpoints/step_XXXXXXXX/
+        trainable.safetensors   adapter state (LyCORIS names) or the full trainable weights
+        ema.safetensors         `<tag>/<name>` EMA buffers (when enabled)
+        optim.pt                {optimizer, schedule, skipped}
+        rng.<rank>.pt           torch / python / numpy / CUDA RNG + the step generators
+        state.json              step, loader state {seed, start}, token / sample counters, world
+
+Everything is written into `step_XXXXXXXX.partial` and renamed at the end; `state.json` is
+written last, so a directory with a `state.json` is complete. Writes are retried inside a time
+budget; with several ranks they agree through the launcher's store whether the write worked,
+and a failed checkpoint is skipped, not fatal (`src/kohakumoss/training/checkpoint/{io,manager,
+stream}.py` in the reference). The safetensors writer streams one tensor at a time, so a
+checkpoint never needs a second copy of the weights in host memory.
+"""
+
+from __future__ import annotations
+
+import json
+import random
+import shutil
+import struct
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+from torch import Tensor
+
+from ..utils.io import write_json
+from ..utils.log import get_logger
+from ..utils.retry import retrying
+
+log = get_logger(__name__)
+_ST_DTYPES = {torch.float32: "F32", torch.float16: "F16", torch.bfloat16: "BF16", torch.int64: "I64", torch.int32: "I32",
+              torch.uint8: "U8", torch.int8: "I8", torch.bool: "BOOL", torch.float64: "F64",
+              torch.float8_e4m3fn: "F8_E4M3", torch.float8_e5m2: "F8_E5M2"}
+
+
+def save_stream(items, path: str | Path, metadata: dict | None = None) -> None:
+    """Write `(name, tensor)` pairs as safetensors, streaming one tensor at a time: the header
+    is built from shapes alone, then each tensor is moved to host, written and dropped."""
+    items = list(items)
+    header, offset = {}, 0
+    for name, t in items:
+        n = t.numel() * t.element_size()
+        header[name] = {"dtype": _ST_DTYPES[t.dtype], "shape": list(t.shape), "data_offsets": [offset, offset + n]}
+        offset += n
+    if metadata:
+        header["__metadata__"] = {str(k): str(v) for k, v in metadata.items()}
+    blob = json.dumps(header, separators=(",", ":")).encode()
+    blob += b" " * ((8 - len(blob) % 8) % 8)
+    path = Path(path)
+    path.parent.mkdir(parents=True, exist_ok=True)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(blob)))
+        f.write(blob)
+        for _, t in items:
+            host = t.detach().reshape(-1).contiguous().cpu()
+            f.write(host.view(torch.uint8).numpy().tobytes() if host.numel() else b"")
+
+
+def capture_rng(step_rng: dict, device=None) -> dict:
+    state = {"torch": torch.get_rng_state(), "python": random.getstate(), "numpy": np.random.get_state(), "step": step_rng}
+    if device is not None and torch.device(device).type == "cuda":
+        state["cuda"] = {torch.device(device).index or 0: torch.cuda.get_rng_state(device)}
+    return state
+
+
+def restore_rng(state: dict, device=None) -> dict:
+    torch.set_rng_state(state["torch"])
+    random.setstate(state["python"])
+    np.random.set_state(state["numpy"])
+    if device is not None and torch.device(device).type == "cuda":
+        idx = torch.device(device).index or 0
+        if idx in state.get("cuda", {}):
+            torch.cuda.set_rng_state(state["cuda"][idx], device)
+    return state["step"]
+
+
+def load_pt(file: Path):
+    core = np._core.multiarray if hasattr(np, "_core") else np.core.multiarray
+    allowed = [np.ndarray, np.dtype, type(np.dtype(np.uint32)), core._reconstruct]
+    with torch.serialization.safe_globals(allowed):
+        return torch.load(file, map_location="cpu", weights_only=True)
+
+
+class CheckpointManager:
+    def __init__(self, out_dir: str | Path, keep_last: int = 3, save_every: int = 500, save_minutes: float = 0.0,
+                 rank: int = 0, world: int = 1, retry_budget_s: float = 600.0, agree=None):
+        self.root = Path(out_dir) / "checkpoints"
+        self.keep_last, self.save_every, self.save_minutes = keep_last, save_every, save_minutes
+        self.rank, self.world, self.retry_budget_s = rank, world, retry_budget_s
+        self.agree = agree  # callable(name, ok) -> bool across ranks (launch.store_agree), None for one rank
+        self._last_time = time.monotonic()
+        self.failed = 0
+
+    def dir_of(self, step: int) -> Path:
+        return self.root / f"step_{step:08d}"
+
+    def due(self, step: int) -> bool:
+        if self.save_every and step > 0 and step % self.save_every == 0:
+            return True
+        return bool(self.save_minutes and (time.monotonic() - self._last_time) >= self.save_minutes * 60)
+
+    def latest(self) -> Path | None:
+        done = sorted(p for p in self.root.glob("step_*") if p.is_dir() and (p / "state.json").exists() and not p.name.endswith(".partial"))
+        return done[-1] if done else None
+
+    def resolve(self, resume: str) -> Path | None:
+        if not resume:
+            return None
+        return self.latest() if resume == "latest" else Path(resume)
+
+    # -- save --------------------------------------------------------------------------------
+    def save(self, step: int, trainable: dict[str, Tensor], trainable_meta: dict, bundle, step_rng: dict, counters: dict,
+             ema=None, device=None, loader_state: dict | None = None) -> Path | None:
+        final = self.dir_of(step)
+        partial = final.with_name(final.name + ".partial")
+        ok = True
+        try:
+            retrying(self._write, partial, step, trainable, trainable_meta, bundle, step_rng, counters, ema, device, loader_state,
+                     budget_s=self.retry_budget_s, on_retry=lambda n, e, w: log.warning("checkpoint write failed, retrying", attempt=n, error=str(e), wait=w))
+        except OSError as err:
+            log.error("checkpoint write gave up", step=step, error=str(err))
+            ok = False
+        if self.agree is not None:
+            ok = self.agree(f"ckpt-{step}", ok)
+        if not ok:
+            self.failed += 1
+            if self.rank == 0:
+                shutil.rmtree(partial, ignore_errors=True)
+            return None
+        if self.rank == 0:
+            if final.exists():
+                shutil.rmtree(final)
+            partial.rename(final)
+            self._prune()
+        self._last_time = time.monotonic()
+        return final
+
+    def _write(self, partial, step, trainable, meta, bundle, step_rng, counters, ema, device, loader_state) -> None:
+        partial.mkdir(parents=True, exist_ok=True)
+        torch.save(capture_rng(step_rng, device), partial / f"rng.{self.rank}.pt")
+        if self.rank != 0:
+            return
+        save_stream(trainable.items(), partial / "trainable.safetensors", meta)
+        if ema is not None:
+            save_stream(ema.state_dict().items(), partial / "ema.safetensors")
+        torch.save(bundle.state_dict(), partial / "optim.pt")
+        write_json(partial / "state.json", {"step": step, "loader": loader_state or {}, "world": self.world, **counters})
+
+    def _prune(self) -> None:
+        if self.keep_last <= 0:
+            return
+        done = sorted(p for p in self.root.glob("step_*") if p.is_dir() and not p.name.endswith(".partial"))
+        for old in done[: -self.keep_last]:
+            shutil.rmtree(old, ignore_errors=True)
+
+    # -- load --------------------------------------------------------------------------------
+    def load(self, path: Path, bundle=None, ema=None, device=None) -> dict:
+        """Returns {"state": state.json, "trainable": tensors, "meta": metadata, "step_rng": ...}."""
+        from safetensors import safe_open
+
+        path = Path(path)
+        state = json.loads((path / "state.json").read_text())
+        tensors, meta = {}, {}
+        with safe_open(str(path / "trainable.safetensors"), framework="pt") as f:
+            meta = f.metadata() or {}
+            for k in f.keys():
+                tensors[k] = f.get_tensor(k)
+        if bundle is not None and (path / "optim.pt").exists():
+            bundle.load_state_dict(load_pt(path / "optim.pt"))
+        if ema is not None and (path / "ema.safetensors").exists():
+            with safe_open(str(path / "ema.safetensors"), framework="pt") as f:
+                ema.load_state_dict({k: f.get_tensor(k) for k in f.keys()})
+        step_rng = None
+        rng = path / f"rng.{self.rank}.pt"
+        if rng.exists():
+            step_rng = restore_rng(load_pt(rng), device)
+        return {"state": state, "trainable": tensors, "meta": meta, "step_rng": step_rng}

@@ -1,0 +1,217 @@
+"""`run(globals())`: the trainer's orchestration, from knobs to exports.
+
+Validate every knob once, spawn one process per device when the layout needs it, then per rank:
+run directory + `config.json` + `log.txt`, data, model / adapters / optimiser (`Trainer`),
+resume, the step loop with callbacks (metrics rows, throughput, non-finite guard, trace
+windows, checkpoints), and the final exports (`<run>-comfy.safetensors`, `<run>-lycoris.
+safetensors`, `<run>-merged.safetensors`, `<run>-diffusers/`). Mirrors the reference flow
+(`src/kohakumoss/training/entry.py:104-568`).
+"""
+
+from __future__ import annotations
+
+import signal
+import time
+from pathlib import Path
+
+import torch
+
+from ..config import check, collect, script_knobs
+from ..utils import log as log_mod
+from ..utils.io import write_json
+from .knobs import CHOICES, cross_checks
+
+log = log_mod.get_logger("entry")
+
+
+def _install_sigterm() -> None:
+    def handler(signum, frame):
+        raise SystemExit(143)
+
+    try:
+        signal.signal(signal.SIGTERM, handler)
+    except ValueError:  # not the main thread
+        pass
+
+
+def trainer_config(k: dict):
+    from .trainer import TrainerConfig
+
+    base = k["BASE_PRECISION"]
+    if base == "auto":
+        base = "auto"
+    drop = k.get("DROPOUT") or {}
+    return TrainerConfig(
+        variant=k["VARIANT"], arch_overrides=dict(k["ARCH_OVERRIDES"]), algo=k["ALGO"], preset=k["PRESET"], dim=k["DIM"],
+        alpha=float(k["ALPHA"]), algo_kwargs=dict(k["ALGO_KWARGS"]), adapter_mode=k["ADAPTER_MODE"], base_precision=base,
+        fp8_recipe=k["FP8_RECIPE"], precision="bf16" if k["PRECISION"] in ("auto", "bf16") else k["PRECISION"],
+        optimizer=k["OPTIMIZER"], optimizer_kwargs=dict(k["OPTIMIZER_KWARGS"]), lr=float(k["LR"]), betas=tuple(k["BETAS"]),
+        eps=float(k["EPS"]), weight_decay=float(k["WEIGHT_DECAY"]), wd_rules=k["WD_RULES"], schedule=dict(k["SCHEDULE"]),
+        grad_clip=float(k["GRAD_CLIP"]), step_sync=k["STEP_SYNC"], ema=float(k["EMA"]), steps=int(k["STEPS"]),
+        grad_acc=int(k["GRAD_ACC"]), checkpoint=k["CHECKPOINT"], timestep=k["TIMESTEP"], timestep_kwargs=dict(k["TIMESTEP_KWARGS"]),
+        loss=k["LOSS"], weighting=k["WEIGHTING"], seed=int(k["SEED"]), kernels=dict(k["KERNELS"]), parallel=k["PARALLEL"],
+        ddp_bucket_mb=k["DDP_BUCKET_MB"], ddp_reduce_dtype=k["DDP_REDUCE_DTYPE"], ddp_backend=k["DDP_BACKEND"],
+    )
+
+
+def build_dataset(k: dict, text_dim: int, channels: int):
+    """Dataset from the `DATASETS` knob; `{"type": "synthetic", ...}` needs no files."""
+    from ..data import SyntheticConfig, SyntheticDataset
+
+    spec = (k["DATASETS"] or [{"type": "synthetic"}])[0]
+    if spec.get("type", "synthetic") == "synthetic":
+        opts = {kk: vv for kk, vv in spec.items() if kk != "type"}
+        cfg = SyntheticConfig(max_tokens=int(k["MAX_TOKENS"]), text_dim=text_dim, channels=channels, seed=int(k["SEED"]),
+                              size_step=max(16, int(k["SIZE_STEP"])), **opts)
+        return SyntheticDataset(cfg)
+    from ..data.dataset import build_dataset as build_real
+
+    return build_real(k, text_dim, channels)
+
+
+def worker(k: dict, rank: int, world: int, device) -> dict:
+    from ..logging import build_writer
+    from .callbacks import FiniteGuard, StepTrace, Throughput, vram_row
+    from .checkpoint import CheckpointManager
+    from .trainer import Trainer
+
+    _install_sigterm()
+    run_dir = Path(k["OUTPUT_DIR"]) / (k["RUN_NAME"] or "")
+    run_dir.mkdir(parents=True, exist_ok=True)
+    log_mod.setup("INFO", str(run_dir / "log.txt") if rank == 0 else None)
+    if rank == 0:
+        write_json(run_dir / "config.json", {kk: vv for kk, vv in k.items()})
+    torch.manual_seed(int(k["SEED"]) + rank)
+    cfg = trainer_config(k)
+    trainer = Trainer(cfg, device=device, rank=rank, world=world)
+    if k["WEIGHTS"] or k["TRANSFORMER"]:
+        from ..models.io import load_backbone
+
+        load_backbone(trainer.model, k["TRANSFORMER"] or k["WEIGHTS"])
+    arch = trainer.model.cfg
+    data = build_dataset(k, arch.text_dim, arch.latent_channels)
+    agree = None
+    if world > 1:
+        from ..parallel import launch
+
+        agree = lambda name, ok: launch.store_agree(name, ok, rank, world)  # noqa: E731
+    ckpt = CheckpointManager(run_dir, int(k["KEEP_LAST"]), int(k["SAVE_EVERY"]), float(k["SAVE_MINUTES"] or 0), rank, world, agree=agree)
+    start = 0
+    resume = ckpt.resolve(k["RESUME"])
+    if resume is not None:
+        loaded = ckpt.load(resume, trainer.bundle, trainer.ema, device)
+        _load_trainable(trainer, loaded["trainable"])
+        if loaded["step_rng"] is not None:
+            trainer.step_fn.load_rng_state(loaded["step_rng"])
+        start = int(loaded["state"]["step"])
+        trainer.tokens_seen = loaded["state"].get("tokens", 0)
+        trainer.samples_seen = loaded["state"].get("samples", 0)
+        log.info("resumed", step=start, path=str(resume))
+    elif k["INIT_FROM"]:
+        from safetensors.torch import load_file
+
+        _load_trainable(trainer, load_file(k["INIT_FROM"]))
+    writer = build_writer(k["LOGGER"], run_dir, k["METRICS_LEVEL"], k["PROJECT"], k["RUN_NAME"], rank=rank)
+    speed = Throughput(arch, cfg.algo == "full", cfg.checkpoint != "none", world)
+    guard = FiniteGuard(int(k["NONFINITE_PATIENCE"]), run_dir)
+    trace = StepTrace(k["TRACE_STEPS"], k["PROFILE_STEPS"], run_dir, rank)
+    acc = cfg.grad_acc
+    last = {}
+    nxt = [data.materialize(start * acc + i, rank, world) for i in range(acc)]
+    for step in range(start, cfg.steps):
+        trace.before(step)
+        group = nxt
+        nxt = [data.materialize((step + 1) * acc + i, rank, world) for i in range(acc)] if step + 1 < cfg.steps else []
+        out = trainer.train_step(group, next_batch=nxt[0] if nxt else None)
+        speed.observe(group)
+        guard.observe(out["ok"], step, trainer, group)
+        trace.after(step)
+        if (step + 1) % max(1, int(k["LOG_EVERY"])) == 0 or step + 1 == cfg.steps:
+            row = {"loss/train": out["loss"], "opt/grad_norm": out["grad_norm"], "opt/lr": trainer.bundle.lr,
+                   "opt/skipped": trainer.bundle.skipped, **speed.row(), **vram_row(device)}
+            if trainer.parallel is not None:
+                row.update({f"ddp/{kk[4:]}": vv for kk, vv in trainer.parallel.metrics().items() if isinstance(vv, (int, float))})
+            writer.write(step + 1, row)
+            last = row
+        if ckpt.due(step + 1) and step + 1 < cfg.steps:
+            _save(ckpt, trainer, step + 1, k, device)
+    if k["FINAL_CHECKPOINT"] in ("auto", True, "always") and cfg.steps > start:
+        _save(ckpt, trainer, cfg.steps, k, device)
+    if rank == 0:
+        _export(trainer, run_dir, k)
+    writer.close()
+    return {"step": cfg.steps, **last}
+
+
+def _trainable_state(trainer):
+    if trainer.adapters is not None:
+        from ..adapters.export import metadata
+
+        return trainer.adapters.adapter_state(), metadata(trainer.adapters, "lycoris")
+    return {n: p.detach() for n, p in trainer.named_trainable}, {"kohakumoss_full_state": "1"}
+
+
+def _load_trainable(trainer, tensors: dict) -> None:
+    if trainer.adapters is not None:
+        trainer.adapters.load_adapter_state(tensors, strict=False)
+        return
+    own = dict(trainer.named_trainable)
+    with torch.no_grad():
+        for name, t in tensors.items():
+            if name in own:
+                own[name].copy_(t.to(own[name].dtype))
+
+
+def _save(ckpt, trainer, step: int, k: dict, device) -> None:
+    state, meta = _trainable_state(trainer)
+    path = ckpt.save(step, state, meta, trainer.bundle, trainer.step_fn.rng_state(),
+                     {"tokens": trainer.tokens_seen, "samples": trainer.samples_seen}, trainer.ema, device,
+                     loader_state={"seed": int(k["SEED"]), "start": step * trainer.cfg.grad_acc})
+    if path is not None and trainer.rank == 0:
+        log.info("checkpoint", step=step, path=str(path))
+
+
+def _export(trainer, run_dir: Path, k: dict) -> None:
+    fmt = k["SAVE_FORMAT"]
+    if fmt == "none":
+        return
+    name = k["RUN_NAME"] or run_dir.name
+    out = run_dir / "export"
+    if trainer.adapters is not None:
+        from ..adapters.export import export
+
+        export(trainer.adapters, trainer.model, out / f"{name}-lycoris.safetensors", "lycoris")
+        if fmt in ("comfy", "both"):
+            export(trainer.adapters, trainer.model, out / f"{name}-comfy.safetensors", "comfy", fused_qkv=bool(k["SAVE_FUSED_QKV"]))
+        if k["SAVE_MERGED"]:
+            export(trainer.adapters, trainer.model, out / f"{name}-merged.safetensors", "merged")
+        if fmt in ("hf", "both") and k["SAVE_MERGED"]:
+            export(trainer.adapters, trainer.model, out / f"{name}-diffusers", "diffusers")
+    else:
+        from ..models.io import save_diffusers, save_single
+
+        if fmt in ("comfy", "both"):
+            save_single(trainer.model, out / f"{name}-comfy.safetensors", fused_qkv=bool(k["SAVE_FUSED_QKV"]), prefix="model.diffusion_model.")
+        if fmt in ("hf", "both"):
+            save_diffusers(trainer.model, out / f"{name}-diffusers")
+
+
+def _spawned(rank, world, device, k):
+    worker(k, rank, world, device)
+
+
+def run(g: dict) -> dict | None:
+    """Entry point of `scripts/train/moss.py`: `g` is the script's globals."""
+    defaults = script_knobs(g["__file__"]) if g.get("__file__") else collect(g)
+    k = check(collect(g), defaults, CHOICES, [cross_checks])
+    devices = tuple(k["DEVICES"]) or (0,)
+    cuda = torch.cuda.is_available()
+    if k["PARALLEL"] in ("ddp", "fsdp", "pipeline") and len(devices) > 1:
+        from ..parallel import ParallelPlan, spawn
+
+        plan = ParallelPlan(world=len(devices), devices=devices, backend=k["DIST_BACKEND"], timeout_s=float(k["DIST_TIMEOUT"]),
+                            gate_timeout_s=float(k["DIST_GATE_TIMEOUT"]), device_type="cuda" if cuda else "cpu")
+        spawn(_spawned, plan, (k,))
+        return None
+    device = torch.device("cuda", devices[0]) if cuda else torch.device("cpu")
+    return worker(k, 0, 1, device)

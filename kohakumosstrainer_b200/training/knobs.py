@@ -1,0 +1,87 @@
+"""Choice tables and cross-knob checks of the trainer script (`scripts/train/moss.py`).
+
+Names and values are the reference's (`scripts/train/moss.py:13-268` there); knobs that only
+exist to fit the model into small cards (`MEMORY_PROFILE`, `STREAM`, `ACT_OFFLOAD`, ...) are
+accepted and mapped onto what a 180 GB B200 needs (`memory.resolve_profile`).
+"""
+
+from __future__ import annotations
+
+CHOICES = {
+    "VARIANT": ("base", "sft", "tiny"),
+    "RESOLUTION_MODE": ("resize", "bucket", "shifted_square", "square_crop"),
+    "UPSCALE": ("never", "to_area"),
+    "BATCHING": ("tokens", "tokens_ffd", "count"),
+    "OVERLONG": ("drop", "truncate_text", "drop_tokens"),
+    "TOKEN_BUDGET": ("estimate", "render", "exact"),
+    "LATENT_CACHE": ("off", "offline", "online"),
+    "TEXT_CACHE": ("off", "offline", "online"),
+    "CACHE_DTYPE": ("bf16", "fp16", "fp32", "fp8"),
+    "CROP": ("center", "random"),
+    "LATENT_DRAW": ("mode", "sample"),
+    "ALGO": ("lora", "locon", "loha", "lokr", "oft", "boft", "glora", "ia3", "dylora", "tlora", "dora", "full"),
+    "ADAPTER_MODE": ("bypass", "merge"),
+    "TIMESTEP": ("moss", "uniform", "logit_normal"),
+    "LOSS": ("mse", "huber", "l1", "masked_mse"),
+    "WEIGHTING": ("none", "x0", "eps"),
+    "OPTIMIZER": ("adamw", "adamw16", "adamw8bit", "adamw8bit_kernel", "muon", "prodigy", "schedule_free"),
+    "WD_RULES": ("moss", "none", "all"),
+    "WD_TARGET": ("zero", "start"),
+    "STEP_SYNC": ("step", "deferred"),
+    "PRECISION": ("bf16", "fp16", "fp32", "auto"),
+    "FP16_FIX": ("none", "online", "fp32_residual", "weights"),
+    "STREAM": ("off", "ring", "swap"),
+    "OPTIM_STATE": ("gpu", "stream", "cpu"),
+    "BASE_PRECISION": ("auto", "compute", "int8", "fp8", "fp8_compute", "mxfp8"),
+    "FP8_RECIPE": ("tensor", "row", "block", "mx"),
+    "PARALLEL": ("none", "ddp", "fsdp", "pipeline", "threaded"),
+    "DIST_BACKEND": ("auto", "nccl", "gloo"),
+    "PIPELINE_SCHEDULE": ("gpipe", "1f1b", "interleaved-1f1b", "looped-bfs", "interleaved-zb", "zbv", "dualpipe-v", "async"),
+    "FSDP_REDUCE": ("step", "micro"),
+    "FSDP_RESHARD": ("forward", "backward"),
+    "DDP_BACKEND": ("kohakumoss", "torch"),
+    "DDP_REDUCE_DTYPE": ("fp32", "param", "bf16"),
+    "DIST_BIND": ("lazy", "device"),
+    "TUNE": ("table", "off"),
+    "COMPILE": ("off", "block", "model"),
+    "DRIVER": ("native",),
+    "LOGGER": ("console", "wandb"),
+    "METRICS_LEVEL": ("train", "bench", "debug"),
+    "SAVE_FORMAT": ("comfy", "hf", "both", "none"),
+    "CFG_MODE": ("packed", "two_pass"),
+}
+
+
+def _checkpoint_mode(value):
+    if value in ("none", "block", "sub-block", "selective") or (isinstance(value, str) and value.startswith("partial:")):
+        return None
+    return "must be none | block | sub-block | selective | partial:<fraction>"
+
+
+CHOICES["CHECKPOINT"] = _checkpoint_mode
+
+
+def cross_checks(k: dict) -> list[str]:
+    """Problems that involve several knobs (the reference's `Layout.problems`)."""
+    out = []
+    n_dev = len(k.get("DEVICES") or (0,))
+    par = k.get("PARALLEL", "none")
+    if par == "none" and n_dev > 1:
+        out.append("PARALLEL='none' uses one device but DEVICES lists several")
+    if par in ("ddp", "fsdp") and n_dev < 2:
+        out.append(f"PARALLEL={par!r} needs at least two DEVICES")
+    if par in ("pipeline", "threaded") and n_dev < 2:
+        out.append(f"PARALLEL={par!r} needs at least two DEVICES (stages)")
+    if par == "threaded" and k.get("PIPELINE_SCHEDULE") not in ("gpipe", "async", "1f1b"):
+        out.append("threaded pipeline schedules are gpipe | async")
+    if k.get("ALGO") == "full" and k.get("BASE_PRECISION") in ("int8", "fp8"):
+        out.append("ALGO='full' trains the base weights: BASE_PRECISION must be auto | compute | fp8_compute | mxfp8")
+    if k.get("GRAD_ACC", 1) < 1:
+        out.append("GRAD_ACC must be >= 1")
+    if k.get("DIM", 1) < 1:
+        out.append("DIM must be >= 1")
+    if not (0.0 <= float(k.get("EMA", 0.0)) < 1.0):
+        out.append("EMA must be in [0, 1)")
+    if k.get("MICROBATCHES", 1) < 1:
+        out.append("MICROBATCHES must be >= 1")
+    return out

@@ -1,0 +1,201 @@
+"""MOSS-Image DiT trainer: the UPPER_CASE globals below are the knobs.
+
+    python -m kohakumosstrainer_b200.cli.run scripts/train/moss.py --config configs/moss/recipes/recipes_lora_b200.py --set STEPS=100
+
+Knob names, meanings and defaults follow the reference trainer script
+(`scripts/train/moss.py:13-268` there), so its configs carry over.
+"""
+
+# ---- MODEL -------------------------------------------------------------------------------
+WEIGHTS = ""                 # HF folder / ComfyUI file / own save; "" = random init (synthetic runs)
+VARIANT = "base"
+ARCH_OVERRIDES = {}
+TRANSFORMER = ""
+TEXT_ENCODER = ""
+TEXT_DEVICE = ""
+TEXT_ENCODE = {}
+VAE = ""
+ENCODE_DEVICES = ()
+ENCODE_DEPTH = 32
+ENCODE_CHUNK = 8
+VAE_ENCODE = {}
+VAE_DTYPE = "bf16"
+TRAIN_TEXT_REFINER = False
+# ---- DATA --------------------------------------------------------------------------------
+DATASETS = [{"type": "synthetic"}]
+RESOLUTION_MODE = "resize"
+TARGET_AREA = 1024 * 1024
+SIZE_STEP = 16
+ASPECT_RANGE = (0.25, 4.0)
+UPSCALE = "never"
+BATCHING = "tokens"
+MAX_TOKENS = 16384
+OVERLONG = "drop"
+BATCH_SIZE = 4
+MAX_SAMPLES = 0
+TOKEN_BUDGET = "estimate"
+CAPTION = {}
+TEXT_DROP = 0.1
+LATENT_CACHE = "off"
+TEXT_CACHE = "off"
+CACHE_DIR = ""
+CACHE_DTYPE = "bf16"
+CAPTION_VARIANTS = 4
+FLIP = False
+CROP = "center"
+PLANNER_KWARGS = {}
+LATENT_ENCODER_ID = ""
+LATENT_DRAW = "mode"
+TEXT_ENCODER_ID = ""
+BACKGROUND = (255, 255, 255)
+RESAMPLE = "lanczos"
+TEXT_CHARS_PER_TOKEN = 3.5
+TEXT_OVERHEAD_TOKENS = 12
+MAX_TEXT_TOKENS = 4096
+PREFETCH = 2
+PIN_MEMORY = True
+NUM_WORKERS = 4
+DATA_RESCAN = False
+DATA_SCAN_WORKERS = 8
+DATA_WAIT = 3600
+DATA_BALANCE = False
+SEED = 0
+# ---- ADAPTER -----------------------------------------------------------------------------
+ALGO = "lora"
+PRESET = "attn-mlp"
+DIM = 32
+ALPHA = 32.0
+ALGO_KWARGS = {}
+DORA = False
+DORA_DETACH = False
+DROPOUT = {}
+ADAPTER_MODE = "bypass"
+LORAPLUS_RATIO = 1.0
+TRAIN_NORMS = False
+# ---- OBJECTIVE ---------------------------------------------------------------------------
+TIMESTEP = "moss"
+TIMESTEP_KWARGS = {}
+LOSS = "mse"
+LOSS_KWARGS = {}
+WEIGHTING = "none"
+STREAM_LOSS = {}
+CONCENTRATION_LOSS = {}
+STREAM_LOSS_PROBE = 0
+HARD_WEIGHT = 1.0
+TEACHER = ""
+DISTILL_WEIGHT = 0.0
+DISTILL_WEIGHTING = ""
+TEACHER_PRECISION = "auto"
+TEACHER_STREAM = "compute"
+# ---- OPTIM -------------------------------------------------------------------------------
+OPTIMIZER = "adamw"
+OPTIMIZER_KWARGS = {}
+LR = 1e-4
+BETAS = (0.9, 0.95)
+EPS = 1e-8
+WEIGHT_DECAY = 0.01
+WD_RULES = "moss"
+WD_TARGET = "zero"
+OUTLIER_DECAY = {}
+SCHEDULE = {"mode": "cosine", "warmup": 100, "end": -1}
+GRAD_CLIP = 1.0
+STEP_SYNC = "step"
+EMA = 0.0
+# ---- PRECISION ---------------------------------------------------------------------------
+PRECISION = "bf16"
+KEEP_FP32 = ("time_embedding", "shared_block_modulation", "video_head_modulation")
+FP16_FIX = "none"
+FP16_FIX_KWARGS = {}
+# ---- MEMORY ------------------------------------------------------------------------------
+MEMORY_PROFILE = "speed"
+MEMORY_AUTO_FORCE = False
+STEP_RELEASE = False
+CHECKPOINT = "none"
+STREAM = "off"
+STREAM_RESIDENT = 0
+PINNED = True
+ACT_OFFLOAD = False
+OPTIM_STATE = "gpu"
+GRAD_OFFLOAD = False
+FUSED_STEP = False
+BASE_PRECISION = "auto"
+FP8_RECIPE = "tensor"
+FP8_DGRAD = True
+INT8_COMPUTE = False
+INT8_DGRAD = False
+MEMORY_OVERRIDES = {}
+# ---- PARALLEL ----------------------------------------------------------------------------
+PARALLEL = "none"
+DIST_BACKEND = "auto"
+DEVICES = (0,)
+PIPELINE_SCHEDULE = "1f1b"
+PIPELINE_SPLIT = "flops"
+MICROBATCHES = 4
+FSDP_REDUCE = "step"
+FSDP_RESHARD = "forward"
+DDP_BACKEND = "kohakumoss"
+DDP_REDUCE_DTYPE = "fp32"
+DDP_BUCKET_MB = 25
+DIST_TIMEOUT = 900
+DIST_GATE_TIMEOUT = 7200
+DIST_BIND = "lazy"
+# ---- KERNELS -----------------------------------------------------------------------------
+KERNELS = {}                 # {"all": "eager"} or per-op pins run the reference path for A/B
+TUNE = "off"
+RETUNE_STEPS = 3
+COMPILE = "off"
+# ---- RUNTIME -----------------------------------------------------------------------------
+DRIVER = "native"
+STEPS = 1000
+GRAD_ACC = 1
+OUTPUT_DIR = "runs/moss"
+RUN_NAME = ""
+# ---- LOGGING -----------------------------------------------------------------------------
+LOGGER = "console"
+PROJECT = "kohakumoss"
+LOG_EVERY = 10
+METRICS_EVERY = 10
+METRICS_LEVEL = "train"
+PROGRESS = True
+NONFINITE_PATIENCE = 8
+TRACE_STEPS = ()
+PROFILE_STEPS = ()
+# ---- SAMPLING ----------------------------------------------------------------------------
+SAMPLE_PROMPTS = []
+SAMPLE_NEGATIVE = ""
+SAMPLE_EVERY = 0
+SAMPLE_STEPS = 50
+SAMPLE_CFG = 3.0
+SAMPLE_SHIFT = 5.0
+SAMPLE_SKIP_LAYERS = (22,)
+SAMPLE_SIZE = (1024, 1024)
+SAMPLE_SEEDS = (0,)
+SAMPLE_BATCH = 4
+SAMPLE_COLUMNS = 0
+SAMPLE_AT_START = False
+VALIDATE_EVERY = 0
+VALIDATION = {}
+# ---- CHECKPOINT / EXPORT -----------------------------------------------------------------
+SAVE_EVERY = 500
+SAVE_MINUTES = 0
+KEEP_LAST = 3
+FINAL_CHECKPOINT = "auto"
+RESUME = ""
+INIT_FROM = ""
+SAVE_FORMAT = "comfy"
+SAVE_MERGED = False
+SAVE_FUSED_QKV = False
+CHECKPOINT_EXPORT = True
+EXPORT_FORMATS = None
+
+globals().update(globals().pop("__kmoss_overrides__", {}))
+
+
+def main():
+    from kohakumosstrainer_b200.training.entry import run
+
+    return run(globals())
+
+
+if __name__ == "__main__":
+    main()

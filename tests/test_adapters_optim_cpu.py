@@ -1,0 +1,130 @@
+"""Adapter algebra against hand-derived formulas; optimiser math against plain references."""
+
+import math
+
+import pytest
+import torch
+
+from kohakumosstrainer_b200 import adapters
+from kohakumosstrainer_b200.adapters import modules as M
+from kohakumosstrainer_b200.models.linear import MossLinear
+
+
+def _lin(i=24, o=32, bias=True):
+    lin = MossLinear(i, o, bias=bias)
+    lin.init_weights(0.2)
+    if bias:
+        torch.nn.init.normal_(lin.bias, std=0.1)
+    return lin
+
+
+@pytest.mark.parametrize("algo,kw", [("lora", {}), ("loha", {}), ("lokr", {}), ("lokr", {"decompose_both": True, "factor": 4}),
+                                    ("oft", {}), ("ia3", {}), ("full", {})])
+def test_bypass_equals_merged_weight(algo, kw):
+    torch.manual_seed(0)
+    lin = _lin()
+    mod = M.MODULES[algo](24, 32, 4, 2.0, **kw)
+    for p in mod.parameters():
+        torch.nn.init.normal_(p, std=0.3)
+    lin.set_adapter(mod, "bypass")
+    x = torch.randn(7, 24)
+    y_bypass = lin(x)
+    y_merge = torch.nn.functional.linear(x, mod.merged(lin.weight), lin.bias)
+    torch.testing.assert_close(y_bypass, y_merge, rtol=1e-4, atol=1e-4)
+
+
+def test_lora_delta_formula_and_scale():
+    mod = M.LoRAModule(24, 32, 8, 4.0)
+    torch.nn.init.normal_(mod.lora_up.weight)
+    dw = (mod.lora_up.weight @ mod.lora_down.weight) * (4.0 / 8)
+    w = torch.randn(32, 24)
+    torch.testing.assert_close(mod.merged(w), w + dw)
+    mod.multiplier = 0.5
+    torch.testing.assert_close(mod.merged(w), w + 0.5 * dw)
+
+
+def test_lokr_is_a_kronecker_product():
+    mod = M.LoKrModule(24, 32, 2, 2.0, factor=4)
+    for p in mod.parameters():
+        torch.nn.init.normal_(p)
+    assert mod.shape == ((4, 8), (4, 6))
+    torch.testing.assert_close(mod.delta(), torch.kron(mod.w1(), mod.w2()))
+
+
+def test_oft_rotation_is_orthogonal_and_identity_at_init():
+    mod = M.OFTModule(24, 32, 8)
+    w = torch.randn(32, 24)
+    torch.testing.assert_close(mod.merged(w), w)
+    torch.nn.init.normal_(mod.oft_blocks, std=0.2)
+    r = mod.rotation()
+    eye = torch.eye(mod.block_size).expand_as(r)
+    torch.testing.assert_close(r @ r.transpose(1, 2), eye, rtol=1e-4, atol=1e-4)
+    b = mod.oft_blocks[0]
+    q = b - b.T
+    ref = (torch.eye(8) + q) @ torch.linalg.inv(torch.eye(8) - q)
+    torch.testing.assert_close(r[0], ref, rtol=1e-4, atol=1e-5)
+
+
+def test_dora_keeps_row_norms_at_the_learned_magnitude():
+    lin = _lin(bias=False)
+    mod = M.LoRAModule(24, 32, 4, 4.0)
+    torch.nn.init.normal_(mod.lora_up.weight, std=0.5)
+    mod.enable_dora(lin.weight)
+    merged = mod.merged(lin.weight)
+    torch.testing.assert_close(merged.norm(dim=1, keepdim=True), mod.dora_scale.detach(), rtol=1e-4, atol=1e-5)
+
+
+def test_presets_target_the_documented_paths():
+    from kohakumosstrainer_b200.models import build_backbone
+    from kohakumosstrainer_b200.types import MossArchConfig
+
+    model = build_backbone(MossArchConfig(dim=64, depth=2, heads=2, ffn_dim=128, text_dim=32, text_blocks=1), seed=0)
+    counts = {}
+    for preset in ("attn", "attn-mlp", "full-block", "all", "attn+text-refiner", "attn-mlp+modulation+embed"):
+        names, _ = adapters.resolve_preset(preset)
+        counts[preset] = len(adapters.apply.__globals__["targets_of"](model, names))
+    assert counts == {"attn": 8, "attn-mlp": 12, "full-block": 17, "all": 24, "attn+text-refiner": 14, "attn-mlp+modulation+embed": 18}
+    aset = adapters.apply(model, adapters.AdapterConfig(dim=2, alpha=2, preset="attn"))
+    assert "lora_unet_layers_0_proj_q.lora_down.weight" in aset.adapter_state()
+    assert all(not p.requires_grad for p in model.parameters())
+
+
+def test_fused_adamw_reference_path_matches_torch_adamw():
+    from kohakumosstrainer_b200.optim import FusedAdamW
+
+    torch.manual_seed(0)
+    p1 = torch.nn.Parameter(torch.randn(10, 7))
+    p2 = torch.nn.Parameter(p1.detach().clone())
+    ours = FusedAdamW([p1], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ref = torch.optim.AdamW([p2], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for _ in range(5):
+        g = torch.randn(10, 7)
+        p1.grad, p2.grad = g.clone(), g.clone()
+        ours.step()
+        ref.step()
+    torch.testing.assert_close(p1, p2, rtol=1e-5, atol=1e-6)
+
+
+def test_newton_schulz_pushes_singular_values_towards_one():
+    from kohakumosstrainer_b200.optim import newton_schulz
+
+    g = torch.randn(48, 96)
+    o = newton_schulz(g, 5).float()
+    s = torch.linalg.svdvals(o)
+    assert 0.5 < s.min() and s.max() < 1.3
+    assert newton_schulz(g.T.contiguous(), 5).shape == (96, 48)
+
+
+def test_schedule_and_ema_warmup():
+    from kohakumosstrainer_b200.optim import ConstantEMA, build_schedule
+
+    f = build_schedule({"mode": "cosine", "warmup": 10, "end": -1, "min": 0.1}, 110)
+    assert f(0) == pytest.approx(0.1) and f(9) == pytest.approx(1.0)
+    assert f(60) == pytest.approx(0.1 + 0.9 * 0.5 * (1 + math.cos(math.pi * 0.5))) and f(110) == pytest.approx(0.1)
+    p = torch.nn.Parameter(torch.zeros(3))
+    ema = ConstantEMA([("p", p)], (0.9999,))
+    with torch.no_grad():
+        p.fill_(1.0)
+    ema.update(0)
+    assert ema.averaged()["p"][0].item() == pytest.approx(1 - 2 / 11)
+    assert list(ema.state_dict()) == ["ema0.9999/p"]

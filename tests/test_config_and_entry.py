@@ -1,0 +1,104 @@
+"""Config engine, knob validation, the trainer entry on CPU, checkpoints and exact resume."""
+
+import json
+from pathlib import Path
+
+import pytest
+import torch
+
+from kohakumosstrainer_b200.config import ConfigError, apply_sets, load_config, run_script, script_knobs
+
+ROOT = Path(__file__).resolve().parent.parent
+SCRIPT = str(ROOT / "scripts/train/moss.py")
+TINY = ["VARIANT='tiny'", "BASE_PRECISION='auto'", "PRECISION='fp32'", "MAX_TOKENS=400", "LOG_EVERY=1", "DIM=4", "ALPHA=4.0",
+        "ARCH_OVERRIDES={'text_dim': 256}", "SCHEDULE={'mode': 'constant'}", "LR=1e-2",
+        "DATASETS=[{'type': 'synthetic', 'min_area': 16384, 'max_area': 65536, 'max_text': 16, 'min_text': 4}]"]
+
+
+def test_layers_compose_in_order_and_sets_override(tmp_path):
+    (tmp_path / "a.py").write_text("DIM = 4\nALPHA = 4.0\n")
+    (tmp_path / "b.py").write_text("use_config('a.py')\nDIM = 16\nlower_case = 1\n")
+    cfg = load_config(tmp_path / "b.py")
+    assert cfg == {"DIM": 16, "ALPHA": 4.0}
+    assert apply_sets(cfg, ["DIM=8", "RUN_NAME=abc"]) == {"DIM": 8, "ALPHA": 4.0, "RUN_NAME": "abc"}
+
+
+def test_every_shipped_config_validates():
+    from kohakumosstrainer_b200.config import check
+    from kohakumosstrainer_b200.training.knobs import CHOICES, cross_checks
+
+    defaults = script_knobs(SCRIPT)
+    assert len(defaults) > 140
+    configs = sorted((ROOT / "configs/moss").rglob("*.py"))
+    assert len(configs) >= 15
+    for cfg in configs:
+        knobs = load_config(cfg)
+        try:
+            check(knobs, defaults, CHOICES, [cross_checks] if "recipes" in str(cfg) else [])
+        except ConfigError as err:
+            pytest.fail(f"{cfg}: {err}")
+
+
+def test_all_problems_reported_at_once():
+    with pytest.raises(ConfigError) as err:
+        run_script(SCRIPT, None, ["ALGOO='lora'", "OPTIMIZER='adamx'", "PARALLEL='ddp'", "CHECKPOINT='sometimes'"])
+    text = str(err.value)
+    assert "ALGOO" in text and "did you mean ALGO" in text
+    assert "adamx" in text and "needs at least two DEVICES" in text and "CHECKPOINT" in text
+
+
+def _adapter_state(run: Path):
+    from safetensors.torch import load_file
+
+    return load_file(str(run / "export" / f"{run.name}-lycoris.safetensors"))
+
+
+def test_run_writes_run_dir_and_resume_is_exact(tmp_path):
+    run_script(SCRIPT, None, TINY + ["STEPS=4", f"OUTPUT_DIR='{tmp_path}'", "RUN_NAME='straight'", "SAVE_EVERY=0"])
+    run_script(SCRIPT, None, TINY + ["STEPS=2", f"OUTPUT_DIR='{tmp_path}'", "RUN_NAME='resumed'", "SAVE_EVERY=0"])
+    run_script(SCRIPT, None, TINY + ["STEPS=4", f"OUTPUT_DIR='{tmp_path}'", "RUN_NAME='resumed'", "SAVE_EVERY=0", "RESUME='latest'"])
+    a, b = _adapter_state(tmp_path / "straight"), _adapter_state(tmp_path / "resumed")
+    assert a.keys() == b.keys() and len(a) > 10
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
+    run = tmp_path / "straight"
+    assert {"config.json", "log.txt", "metrics.jsonl", "checkpoints", "export"} <= {p.name for p in run.iterdir()}
+    ck = sorted((run / "checkpoints").iterdir())[-1]
+    assert {"trainable.safetensors", "optim.pt", "rng.0.pt", "state.json"} <= {p.name for p in ck.iterdir()}
+    state = json.loads((ck / "state.json").read_text())
+    assert state["step"] == 4 and state["loader"] == {"seed": 0, "start": 4}
+    rows = [json.loads(line) for line in (run / "metrics.jsonl").read_text().splitlines()]
+    assert len(rows) == 4 and "loss/train" in rows[0] and "speed/tokens_per_s" in rows[0]
+
+
+def test_checkpoint_write_failure_is_retried_then_skipped(tmp_path, monkeypatch):
+    from kohakumosstrainer_b200.training import checkpoint as ck
+
+    calls = {"n": 0}
+    real = ck.save_stream
+
+    def flaky(items, path, metadata=None):
+        calls["n"] += 1
+        if calls["n"] == 1:
+            raise OSError("disk hiccup")
+        return real(items, path, metadata)
+
+    monkeypatch.setattr(ck, "save_stream", flaky)
+    monkeypatch.setattr(ck, "retrying", lambda fn, *a, budget_s=0, on_retry=None, **kw: _retry_twice(fn, a, on_retry))
+
+    class B:
+        def state_dict(self):
+            return {"optimizer": {}, "schedule": {"step": 1}, "skipped": 0}
+
+    mgr = ck.CheckpointManager(tmp_path, keep_last=1)
+    path = mgr.save(1, {"w": torch.ones(3)}, {"m": "1"}, B(), {"step": 0}, {"tokens": 1, "samples": 1})
+    assert path is not None and (path / "state.json").exists() and calls["n"] == 2
+
+
+def _retry_twice(fn, args, on_retry):
+    try:
+        return fn(*args)
+    except OSError as err:
+        if on_retry:
+            on_retry(1, err, 0.0)
+        return fn(*args)
