@@ -65,5 +65,5 @@ PRESETS: dict[str, MossArchConfig] = {
     "base": MossArchConfig(),
     "sft": MossArchConfig(),
     # Small shapes for tests and smoke runs (not in the reference presets).
-    "tiny": MossArchConfig(dim=256, depth=4, heads=4, ffn_dim=512, text_dim=256, text_blocks=1),
+    "tiny": MossArchConfig(dim=256, depth=4, heads=4, ffn_dim=512, text_dim=256, text_blocks=1, negative_skip_layers=(2,)),
 }
