@@ -63,7 +63,10 @@ void gemm(const Tensor& a, const Tensor& b, int64_t M, int64_t N, int64_t K, boo
           const optional<Tensor>& t, const optional<Tensor>& u, int64_t epilogue, const optional<Tensor>& aux,
           const optional<Tensor>& q_norm_w, const optional<Tensor>& k_norm_w, const optional<Tensor>& rope,
           int64_t rope_cols, double eps, const optional<Tensor>& head_rstd, int64_t splits,
-          const optional<Tensor>& workspace, const optional<Tensor>& timeline) {
+          const optional<Tensor>& workspace, const optional<Tensor>& timeline,
+          const optional<std::vector<int64_t>>& gather_src, const optional<std::vector<int64_t>>& gather_flags,
+          const optional<Tensor>& gather_ready, int64_t gather_rank, int64_t gather_rows, int64_t gather_epoch,
+          int64_t gather_ctas) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "gemm: CUDA tensors required");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "gemm: operands must be 2-D with unit inner stride");
   TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1, "gemm: out must be 2-D with unit inner stride");
@@ -122,6 +125,19 @@ void gemm(const Tensor& a, const Tensor& b, int64_t M, int64_t N, int64_t K, boo
   }
   g.status = status_tensor().data_ptr<int>();
   if (timeline.has_value() && timeline->defined()) g.timeline = reinterpret_cast<unsigned long long*>(timeline->data_ptr());
+  if (gather_src.has_value() && gather_src->size() > 1) {
+    const size_t world = gather_src->size();
+    TORCH_CHECK(world <= 8 && gather_flags.has_value() && gather_flags->size() == world && gather_ready.has_value(),
+                "gemm: fused gather needs per-rank shard and flag addresses and the ready counters");
+    TORCH_CHECK(gather_ready->scalar_type() == at::kInt && gather_ready->numel() >= 8, "gemm: gather_ready must be int32[8]");
+    for (size_t r = 0; r < world; ++r) {
+      g.gather_src[r] = reinterpret_cast<const void*>((*gather_src)[r]);
+      g.gather_flags[r] = reinterpret_cast<unsigned int*>((*gather_flags)[r]);
+    }
+    g.gather_ready = reinterpret_cast<unsigned int*>(gather_ready->data_ptr());
+    g.gather_world = (int)world; g.gather_rank = (int)gather_rank; g.gather_rows = (int)gather_rows;
+    g.gather_epoch = (unsigned int)gather_epoch; g.gather_ctas = (int)gather_ctas;
+  }
   KM_CHECK_CUDA(kmoss::gemm_launch(g, cur_stream()));
 }
 
@@ -451,9 +467,60 @@ void bounded_wait_probe(const Tensor& flag, int64_t expect, double limit_ms) {
 
 void reset_status() { status_tensor().zero_(); }
 
+
+// Reduce-scatter + sharded AdamW on one tensor: `grad_ptrs[r]` = rank r's full gradient buffer.
+void reduce_scatter_adamw(std::vector<int64_t> grad_ptrs, std::vector<int64_t> flag_ptrs, int64_t shard_offset, int64_t shard_numel,
+                          int64_t grad_dtype, Tensor master, Tensor exp_avg, Tensor exp_avg_sq, const optional<Tensor>& ema,
+                          const optional<Tensor>& compute, const optional<Tensor>& grad_out, const optional<Tensor>& sumsq,
+                          const optional<Tensor>& grad_scale, const optional<Tensor>& skip, double lr, double beta1, double beta2, double eps, double weight_decay,
+                          int64_t step, double ema_decay, int64_t rank, int64_t epoch, int64_t blocks) {
+  c10::cuda::CUDAGuard guard(master.device());
+  const int world = (int)grad_ptrs.size();
+  const int64_t per_vec = grad_dtype == 1 ? 8 : 4;
+  TORCH_CHECK(shard_offset % per_vec == 0 && shard_numel % per_vec == 0, "reduce_scatter_adamw: shard must be 16-byte aligned");
+  TORCH_CHECK(master.numel() >= shard_numel && exp_avg.numel() >= shard_numel && exp_avg_sq.numel() >= shard_numel, "reduce_scatter_adamw: state size");
+  kmoss::ReduceScatterAdamWArgs a{};
+  for (int i = 0; i < world; ++i) {
+    a.grads[i] = reinterpret_cast<const void*>(grad_ptrs[i]);
+    a.flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
+  }
+  a.shard_offset_vec = (size_t)(shard_offset / per_vec); a.shard_vec = (size_t)(shard_numel / per_vec);
+  a.grad_dtype = (int)grad_dtype;
+  a.master = master.data_ptr<float>(); a.exp_avg = exp_avg.data_ptr<float>(); a.exp_avg_sq = exp_avg_sq.data_ptr<float>();
+  a.ema = mptr<float>(ema); a.compute = mptr<void>(compute); a.sumsq = mptr<float>(sumsq); a.grad_out = mptr<float>(grad_out);
+  a.grad_scale = cptr<float>(grad_scale); a.skip = cptr<int>(skip);
+  a.lr = (float)lr; a.beta1 = (float)beta1; a.beta2 = (float)beta2; a.eps = (float)eps; a.weight_decay = (float)weight_decay;
+  a.inv_bc1 = (float)(1.0 / (1.0 - std::pow(beta1, (double)step)));
+  a.inv_sqrt_bc2 = (float)(1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step)));
+  a.ema_decay = (float)ema_decay;
+  a.rank = (int)rank; a.world = world; a.epoch = (uint32_t)epoch;
+  a.status = status_tensor().data_ptr<int>();
+  KM_CHECK_CUDA(kmoss::reduce_scatter_adamw_launch(a, (int)blocks, cur_stream()));
+}
+
+void allgather(std::vector<int64_t> src_ptrs, std::vector<int64_t> flag_ptrs, Tensor dst, int64_t shard_bytes, int64_t rank,
+               int64_t epoch, int64_t blocks) {
+  c10::cuda::CUDAGuard guard(dst.device());
+  const int world = (int)src_ptrs.size();
+  TORCH_CHECK((int64_t)dst.numel() * dst.element_size() >= shard_bytes * world, "allgather: destination too small");
+  kmoss::AllGatherArgs a{};
+  for (int i = 0; i < world; ++i) {
+    a.src[i] = reinterpret_cast<const void*>(src_ptrs[i]);
+    a.flags[i] = reinterpret_cast<uint32_t*>(flag_ptrs[i]);
+  }
+  a.dst = dst.data_ptr(); a.shard_bytes = (size_t)shard_bytes; a.rank = (int)rank; a.world = world; a.epoch = (uint32_t)epoch;
+  a.status = status_tensor().data_ptr<int>();
+  KM_CHECK_CUDA(kmoss::allgather_launch(a, (int)blocks, cur_stream()));
+}
+
 }  // namespace
 
 TORCH_LIBRARY(kmoss_b200, m) {
+  m.def("reduce_scatter_adamw(int[] grad_ptrs, int[] flag_ptrs, int shard_offset, int shard_numel, int grad_dtype, Tensor(a!) master, "
+        "Tensor(b!) exp_avg, Tensor(c!) exp_avg_sq, Tensor(d!)? ema, Tensor(e!)? compute, Tensor(g!)? grad_out, Tensor(f!)? sumsq, Tensor? grad_scale, "
+        "Tensor? skip, float lr, float beta1, float beta2, float eps, float weight_decay, int step, float ema_decay, int rank, "
+        "int epoch, int blocks) -> ()", &reduce_scatter_adamw);
+  m.def("allgather(int[] src_ptrs, int[] flag_ptrs, Tensor(a!) dst, int shard_bytes, int rank, int epoch, int blocks) -> ()", &allgather);
   m.def("allreduce_flag_words() -> int", &allreduce_flag_words);
   m.def("allreduce(int[] ptrs, int[] flag_ptrs, int mc_ptr, int numel, int dtype, int rank, float scale, int epoch, int blocks) -> ()", &allreduce);
   m.def("bounded_wait_probe(Tensor flag, int expect, float limit_ms) -> ()", &bounded_wait_probe);
@@ -474,7 +541,8 @@ TORCH_LIBRARY(kmoss_b200, m) {
       "Tensor? scale_a, Tensor? scale_b, Tensor? row_scale, Tensor? col_scale, Tensor? bias, Tensor? res, float beta, "
       "Tensor? gate, Tensor? seg, Tensor? t, Tensor? u, int epilogue, Tensor(b!)? aux, Tensor? q_norm_w, "
       "Tensor? k_norm_w, Tensor? rope, int rope_cols, float eps, Tensor(c!)? head_rstd, int splits, "
-      "Tensor(d!)? workspace, Tensor(e!)? timeline=None) -> ()",
+      "Tensor(d!)? workspace, Tensor(e!)? timeline=None, int[]? gather_src=None, int[]? gather_flags=None, "
+      "Tensor(f!)? gather_ready=None, int gather_rank=0, int gather_rows=0, int gather_epoch=0, int gather_ctas=16) -> ()",
       &gemm);
   m.def(
       "rms_norm_mod_fwd(Tensor x, Tensor? w, Tensor? shift, Tensor? scale, Tensor? seg, float eps, Tensor(a!) y, "

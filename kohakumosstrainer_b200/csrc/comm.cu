@@ -194,6 +194,112 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_one_shot_kernel(AllReduc
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// reduce-scatter + sharded AdamW (+ EMA, + squared-norm accumulation) in one kernel
+// ---------------------------------------------------------------------------------------
+template <class Args>
+__device__ __forceinline__ bool flag_barrier(const Args& a, int phase, volatile int* failed) {
+  __syncthreads();
+  if (threadIdx.x < a.world) {
+    const int peer = threadIdx.x;
+    const size_t slot = ((size_t)phase * AR_MAX_BLOCKS + blockIdx.x) * AR_MAX_WORLD;
+    __threadfence_system();
+    st_release_sys(a.flags[peer] + slot + a.rank, a.epoch);
+    const uint32_t* mine = a.flags[a.rank] + slot + peer;
+    const uint64_t t0 = global_timer_ns();
+    bool ok = false;
+    for (uint32_t it = 0; it < (1u << 30); ++it) {
+      if ((int32_t)(ld_acquire_sys(mine) - a.epoch) >= 0) { ok = true; break; }
+      if ((it & 255u) == 255u && global_timer_ns() - t0 > kWaitNsLimit) break;
+    }
+    if (!ok) {
+      *failed = 1;
+      report_status(a.status, STATUS_PEER_TIMEOUT, 1200 + phase, peer);
+    }
+  }
+  __syncthreads();
+  return *failed == 0;
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(AR_THREADS) reduce_scatter_adamw_kernel(ReduceScatterAdamWArgs a) {
+  __shared__ int failed;
+  __shared__ float red[AR_THREADS / 32];
+  if (threadIdx.x == 0) failed = 0;
+  if (!flag_barrier(a, 0, &failed)) return;  // every rank's gradient buffer is final
+  const bool skipped = a.skip != nullptr && *a.skip != 0;
+  const float gs = a.grad_scale != nullptr ? *a.grad_scale : 1.f;
+  constexpr int E = BF16 ? 8 : 4;  // elements per 16-byte vector
+  const size_t stride = (size_t)gridDim.x * AR_THREADS;
+  float sq = 0.f;
+  for (size_t v = (size_t)blockIdx.x * AR_THREADS + threadIdx.x; v < a.shard_vec; v += stride) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+    for (int p = 0; p < a.world; ++p) load_acc<BF16>(a.grads[p], a.shard_offset_vec + v, acc);  // fixed order
+    uint32_t packed[4];
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+      const size_t i = v * E + j;
+      sq += acc[j] * acc[j];
+      if (a.grad_out != nullptr) {
+        a.grad_out[i] = acc[j];  // reduce-scatter only: the optimiser runs later, after the global norm
+      } else if (!skipped) {
+        const float g = acc[j] * gs;
+        float m = a.exp_avg[i], w = a.exp_avg_sq[i], p = a.master[i];
+        m = a.beta1 * m + (1.f - a.beta1) * g;
+        w = a.beta2 * w + (1.f - a.beta2) * g * g;
+        p = p * (1.f - a.lr * a.weight_decay) - a.lr * a.inv_bc1 * m / (sqrtf(w) * a.inv_sqrt_bc2 + a.eps);
+        a.exp_avg[i] = m; a.exp_avg_sq[i] = w; a.master[i] = p;
+        if (a.ema != nullptr) a.ema[i] += (1.f - a.ema_decay) * (p - a.ema[i]);
+        acc[j] = p;
+      } else {
+        acc[j] = a.master[i];
+      }
+    }
+    if (a.compute != nullptr && a.grad_out == nullptr) {
+      if (BF16) {
+        packed[0] = pack_bf16(acc[0], acc[1]); packed[1] = pack_bf16(acc[2], acc[3]);
+        packed[2] = pack_bf16(acc[4], acc[5]); packed[3] = pack_bf16(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.compute) + v * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      } else {  // fp32 gradients: 4 values per vector, compute copy is bf16 (8 bytes)
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(a.compute) + v * 8) = make_uint2(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]));
+      }
+    }
+  }
+  if (a.sumsq != nullptr) {
+    sq = warp_sum(sq);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = 0.f;
+      for (int i = 0; i < AR_THREADS / 32; ++i) s += red[i];
+      atomicAdd(a.sumsq, s);
+    }
+  }
+  flag_barrier(a, 1, &failed);  // peers have finished reading this rank's gradient buffer
+}
+
+__global__ void __launch_bounds__(AR_THREADS) allgather_kernel(AllGatherArgs a) {
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  if (!flag_barrier(a, 0, &failed)) return;  // every rank's shard is final
+  const size_t n_vec = a.shard_bytes / 16;
+  const size_t stride = (size_t)gridDim.x * AR_THREADS;
+  for (int i = 0; i < a.world; ++i) {
+    const int s = (a.rank + i) % a.world;
+    const uint4* src = reinterpret_cast<const uint4*>(a.src[s]);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.dst) + (size_t)s * a.shard_bytes);
+    size_t v = (size_t)blockIdx.x * AR_THREADS + threadIdx.x;
+    for (; v + stride < n_vec; v += 2 * stride) {
+      const uint4 x = src[v], y = src[v + stride];
+      dst[v] = x; dst[v + stride] = y;
+    }
+    for (; v < n_vec; v += stride) dst[v] = src[v];
+  }
+  flag_barrier(a, 1, &failed);  // nobody still reads a shard its owner may overwrite next
+}
+
 // Waits on a flag that nothing sets: used by tests to check that a bounded wait returns with
 // STATUS_PEER_TIMEOUT instead of hanging (limit shortened to `limit_ns`).
 __global__ void bounded_wait_probe_kernel(const uint32_t* flag, uint32_t expect, uint64_t limit_ns, int* status) {
@@ -228,6 +334,24 @@ cudaError_t allreduce_launch(const AllReduceArgs& a, int blocks, cudaStream_t s)
   }
   if (bf16) allreduce_two_shot_kernel<true><<<blocks, AR_THREADS, 0, s>>>(a);
   else allreduce_two_shot_kernel<false><<<blocks, AR_THREADS, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+
+cudaError_t reduce_scatter_adamw_launch(const ReduceScatterAdamWArgs& a, int blocks, cudaStream_t s) {
+  if (a.world < 1 || a.world > AR_MAX_WORLD) return cudaErrorInvalidValue;
+  if (blocks < 1) blocks = 1;
+  if (blocks > AR_MAX_BLOCKS) blocks = AR_MAX_BLOCKS;
+  if (a.grad_dtype == 1) reduce_scatter_adamw_kernel<true><<<blocks, AR_THREADS, 0, s>>>(a);
+  else reduce_scatter_adamw_kernel<false><<<blocks, AR_THREADS, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t allgather_launch(const AllGatherArgs& a, int blocks, cudaStream_t s) {
+  if (a.world < 1 || a.world > AR_MAX_WORLD || a.shard_bytes % 16) return cudaErrorInvalidValue;
+  if (blocks < 1) blocks = 1;
+  if (blocks > AR_MAX_BLOCKS) blocks = AR_MAX_BLOCKS;
+  allgather_kernel<<<blocks, AR_THREADS, 0, s>>>(a);
   return cudaGetLastError();
 }
 

@@ -24,7 +24,46 @@ struct AllReduceArgs {
   int* status;
 };
 
+// Reduce-scatter fused with the sharded AdamW step: this rank sums ITS slice of every rank's
+// gradient buffer (fp32 registers), applies the clip coefficient, updates the fp32 master / m / v
+// of its shard, writes the compute copy (bf16, symmetric: peers gather it next step), the EMA,
+// and accumulates the squared norm of the reduced gradient for the next step's clip coefficient.
+struct ReduceScatterAdamWArgs {
+  const void* grads[AR_MAX_WORLD];  // every rank's full gradient buffer of this tensor (index = rank)
+  uint32_t* flags[AR_MAX_WORLD];
+  size_t shard_offset_vec;          // first 16-byte vector of this rank's slice inside the gradient buffer
+  size_t shard_vec;                 // slice length in 16-byte vectors
+  int grad_dtype;                   // 0 = fp32, 1 = bf16
+  float* master;                    // [shard] fp32
+  float* exp_avg;
+  float* exp_avg_sq;
+  float* ema;                       // nullable
+  void* compute;                    // [shard] bf16 compute copy (nullable)
+  float* grad_out;                  // nullable: write the reduced (unscaled) slice here as fp32 and do NOT step
+  float* sumsq;                     // device scalar accumulated with the slice's squared gradient norm (nullable)
+  const float* grad_scale;          // device scalar (clip coefficient of the previous step), nullable
+  const int* skip;                  // device flag, nullable
+  float lr, beta1, beta2, eps, weight_decay, inv_bc1, inv_sqrt_bc2, ema_decay;
+  int rank, world;
+  uint32_t epoch;
+  int* status;
+};
+
+// All-gather by peer copies: every rank's [shard] block into a local full buffer (used to hand
+// Muon the whole update matrix and as the unfused baseline of the fused gather in the GEMM).
+struct AllGatherArgs {
+  const void* src[AR_MAX_WORLD];
+  uint32_t* flags[AR_MAX_WORLD];
+  void* dst;
+  size_t shard_bytes;
+  int rank, world;
+  uint32_t epoch;
+  int* status;
+};
+
 int allreduce_max_blocks();
+cudaError_t reduce_scatter_adamw_launch(const ReduceScatterAdamWArgs& a, int blocks, cudaStream_t s);
+cudaError_t allgather_launch(const AllGatherArgs& a, int blocks, cudaStream_t s);
 cudaError_t allreduce_launch(const AllReduceArgs& a, int blocks, cudaStream_t s);
 cudaError_t bounded_wait_probe(const uint32_t* flag, uint32_t expect, uint64_t limit_ns, int* status, cudaStream_t s);
 

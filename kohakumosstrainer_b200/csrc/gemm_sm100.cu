@@ -71,10 +71,25 @@ struct DeviceParams {
   int* status;
   unsigned long long* timeline;
   int tma_out;  // 1: bf16 output (and aux) leave through shared memory + TMA stores
+  // fused all-gather of B
+  const uint8_t* gather_src[8];
+  uint32_t* gather_flags[8];
+  uint32_t* gather_ready;
+  uint8_t* gather_dst;
+  size_t gather_slab_bytes;
+  int gather_world, gather_rank, gather_rows, gather_ctas;
+  uint32_t gather_epoch;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, const DeviceParams& p, int& m_blk, int& n_blk,
                                             int& split) {
+  if (p.gather_world > 1) {
+    // slab-major order, own slab first: the tiles that need remote slabs come last
+    split = 0;
+    m_blk = tile % p.num_m_blocks;
+    n_blk = (tile / p.num_m_blocks + p.gather_rank * p.num_n_blocks / p.gather_world) % p.num_n_blocks;
+    return;
+  }
   split = tile % p.splits;
   int t = tile / p.splits;
   int per_group = GROUP_M * p.num_n_blocks;
@@ -233,23 +248,96 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
   }
-  if (warp == 1) {
+  const bool needs_tmem = (int)blockIdx.x < (int)gridDim.x - p.gather_ctas;
+  if (warp == 1 && needs_tmem) {
     tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = needs_tmem ? *tmem_slot : 0u;
 
   const int bypass_steps = p.has_bypass ? (p.R + 15) / 16 : 0;
+  const int compute_ctas = (int)gridDim.x - p.gather_ctas;
+  const bool is_gather_cta = (int)blockIdx.x >= compute_ctas;
+
+  if (is_gather_cta) {
+    // ---------------------------- all-gather CTAs (no tensor work) ------------------------
+    // Copy every rank's row slab of B into the local full buffer, own slab first, and count
+    // each finished slab in `gather_ready` so compute CTAs can start on it.
+    __shared__ int gather_failed;
+    const int g = (int)blockIdx.x - compute_ctas;
+    if (threadIdx.x == 0) gather_failed = 0;
+    if (g == 0 && threadIdx.x < p.gather_world) {
+      __threadfence_system();
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.gather_flags[threadIdx.x] + p.gather_rank), "r"(p.gather_epoch) : "memory");
+    }
+    __syncthreads();
+    const size_t n_vec = p.gather_slab_bytes / 16;
+    const size_t stride = (size_t)p.gather_ctas * NUM_THREADS;
+    for (int i = 0; i < p.gather_world; ++i) {
+      const int s = (p.gather_rank + i) % p.gather_world;
+      if (s != p.gather_rank && threadIdx.x == 0) {
+        const uint32_t* flag = p.gather_flags[p.gather_rank] + s;
+        const uint64_t t0 = global_timer_ns();
+        bool ok = false;
+        for (uint32_t it = 0; it < (1u << 30); ++it) {
+          uint32_t v;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+          if ((int32_t)(v - p.gather_epoch) >= 0) { ok = true; break; }
+          if ((it & 255u) == 255u && global_timer_ns() - t0 > kWaitNsLimit) break;
+        }
+        if (!ok) {
+          gather_failed = 1;
+          report_status(p.status, STATUS_PEER_TIMEOUT, 1100, s);
+        }
+      }
+      __syncthreads();
+      if (gather_failed) break;
+      const uint4* src = reinterpret_cast<const uint4*>(p.gather_src[s]);
+      uint4* dst = reinterpret_cast<uint4*>(p.gather_dst + (size_t)s * p.gather_slab_bytes);
+      size_t v = (size_t)g * NUM_THREADS + threadIdx.x;
+      for (; v + 3 * stride < n_vec; v += 4 * stride) {
+        const uint4 a = src[v], b = src[v + stride], c = src[v + 2 * stride], d = src[v + 3 * stride];
+        dst[v] = a; dst[v + stride] = b; dst[v + 2 * stride] = c; dst[v + 3 * stride] = d;
+      }
+      for (; v < n_vec; v += stride) dst[v] = src[v];
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) atomicAdd(p.gather_ready + s, 1u);
+    }
+    return;
+  }
+
+  // compute CTAs wait for a slab of B before their first load from it
+  uint32_t slabs_seen = 0;
+  auto wait_slab = [&](int s) -> bool {
+    if (slabs_seen & (1u << s)) return true;
+    const uint32_t target = p.gather_epoch * (uint32_t)p.gather_ctas;
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t it = 0; it < (1u << 30); ++it) {
+      uint32_t v;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.gather_ready + s) : "memory");
+      if ((int32_t)(v - target) >= 0) {
+        slabs_seen |= 1u << s;
+        asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy copies -> TMA (async proxy) reads
+        return true;
+      }
+      if (*abort_flag) return false;
+      if ((it & 255u) == 255u && global_timer_ns() - t0 > kWaitNsLimit) break;
+    }
+    *abort_flag = 1;
+    report_status(p.status, STATUS_WAIT_TIMEOUT, 1101, s);
+    return false;
+  };
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------------
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < p.total_tiles; tile += compute_ctas) {
         int m_blk, n_blk, split;
         tile_coords(tile, p, m_blk, n_blk, split);
         const int m0 = m_blk * BM;
@@ -277,13 +365,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           mbar_expect_tx(full_bar(stage), C::MAIN_TX);
           const uint32_t a_dst = smem_base + stage * C::STAGE;
           const uint32_t b_dst = a_dst + C::A_STAGE;
-          const int k0 = kb * C::BK;
+          int kb_eff = kb;
+          if (B_MN && p.gather_world > 1)  // start the reduction at this rank's own slab of B
+            kb_eff = (kb + p.gather_rank * p.num_k_blocks / p.gather_world) % p.num_k_blocks;
+          const int k0 = kb_eff * C::BK;
           if constexpr (!A_MN) {
             tma_load_2d(a_dst, &map_a, full_bar(stage), k0, m0);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / C::CHUNK; ++c)
               tma_load_2d(a_dst + c * (C::BK * 128), &map_a, full_bar(stage), m0 + c * C::CHUNK, k0);
+          }
+          if (p.gather_world > 1) {
+            // rows of B this k-block / tile reads: K-major B -> N rows of the tile; MN-major B -> K rows
+            const int r0 = B_MN ? k0 : n0, r1 = B_MN ? min(p.K, k0 + C::BK) - 1 : min(p.N, n0 + BN) - 1;
+            bool ready = true;
+            for (int s2 = r0 / p.gather_rows; s2 <= r1 / p.gather_rows && ready; ++s2) ready = wait_slab(s2);
+            if (!ready) { ok = false; break; }
           }
           if constexpr (!B_MN) {
             if (p.epilogue == EPI_SITU) {
@@ -316,14 +414,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const uint32_t fmt_b = FP8 ? (uint32_t)p.b_e5m2 : 1u;
       const uint32_t idesc = idesc_main | (fmt_a << 7) | (fmt_b << 10);
       const uint32_t idesc_bypass = umma_idesc(1, 1, 0, 0, BM, BN);
-      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < p.total_tiles; tile += compute_ctas) {
         int m_blk, n_blk, split;
         tile_coords(tile, p, m_blk, n_blk, split);
         const int kb_begin = split * p.k_blocks_per_split;
         const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 300 + acc)) break;
         tc_fence_after();
-        if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[4 * (tile / gridDim.x) + 0] = global_timer_ns();
+        if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[4 * (tile / compute_ctas) + 0] = global_timer_ns();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         uint32_t accumulate = 0;
         bool ok = true;
@@ -361,7 +459,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         if (!ok) break;
         tc_commit(acc_full_bar(acc));  // accumulator complete -> epilogue may read
-        if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[4 * (tile / gridDim.x) + 1] = global_timer_ns();
+        if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[4 * (tile / compute_ctas) + 1] = global_timer_ns();
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
@@ -375,14 +473,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     float scalar = p.alpha;
     if (p.scale_a != nullptr) scalar *= __ldg(p.scale_a);
     if (p.scale_b != nullptr) scalar *= __ldg(p.scale_b);
-    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+    for (int tile = blockIdx.x; tile < p.total_tiles; tile += compute_ctas) {
       int m_blk, n_blk, split;
       tile_coords(tile, p, m_blk, n_blk, split);
       const int m = m_blk * BM + row_in_tile;
       const int n_tile = n_blk * BN;
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, 400 + acc)) break;
       tc_fence_after();
-      if (p.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.timeline[4 * (tile / gridDim.x) + 2] = global_timer_ns();
+      if (p.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.timeline[4 * (tile / compute_ctas) + 2] = global_timer_ns();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       const bool row_ok = m < p.M;
 
@@ -760,7 +858,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(acc));
-      if (p.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.timeline[4 * (tile / gridDim.x) + 3] = global_timer_ns();
+      if (p.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.timeline[4 * (tile / compute_ctas) + 3] = global_timer_ns();
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
     if (p.tma_out && lane == 0) tma_store_wait_all<0>();  // staged tiles must have left shared memory
@@ -907,8 +1005,14 @@ cudaError_t launch_cfg(const GemmProblem& g, DeviceParams& p, cudaStream_t strea
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+  int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
   if (grid <= 0) return cudaSuccess;
+  if (p.gather_ctas > 0) {
+    // compute CTAs + gather CTAs must all be resident at once (one CTA per SM)
+    if (p.gather_ctas >= sm_count()) return cudaErrorInvalidValue;
+    if (grid > sm_count() - p.gather_ctas) grid = sm_count() - p.gather_ctas;
+    grid += p.gather_ctas;
+  }
   kern<<<grid, NUM_THREADS, C::SMEM, stream>>>(map_a, map_b, map_t, map_u, map_out, map_aux, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
@@ -991,6 +1095,28 @@ cudaError_t gemm_launch(const GemmProblem& g, cudaStream_t stream) {
   p.rope_cols = g.rope_cols; p.eps = g.eps;
   p.head_rstd = g.head_rstd;
   p.workspace = g.workspace; p.status = g.status; p.timeline = g.timeline;
+  p.gather_world = g.gather_world > 1 ? g.gather_world : 0;
+  p.gather_ctas = 0;
+  if (p.gather_world > 1) {
+    // the slabs partition the stored rows of B: N rows when K-major ([N, K]), K rows when MN-major ([K, N])
+    const int b_rows = g.b_mn ? g.K : g.N;
+    const long b_cols = g.b_mn ? g.N : g.K;
+    if (g.gather_world > 8 || g.gather_ready == nullptr || g.gather_rows <= 0 || g.splits > 1 || g.epilogue == EPI_SITU ||
+        g.ldb != b_cols || (long)g.gather_rows * g.gather_world != b_rows)
+      return cudaErrorInvalidValue;
+    const size_t eb2 = fp8 ? 1 : 2;
+    const size_t row_bytes = (size_t)(g.b_mn ? g.N : g.K) * eb2;
+    p.gather_slab_bytes = (size_t)g.gather_rows * row_bytes;
+    if (p.gather_slab_bytes % 16) return cudaErrorInvalidValue;
+    for (int r = 0; r < g.gather_world; ++r) {
+      p.gather_src[r] = reinterpret_cast<const uint8_t*>(g.gather_src[r]);
+      p.gather_flags[r] = g.gather_flags[r];
+    }
+    p.gather_ready = g.gather_ready;
+    p.gather_dst = reinterpret_cast<uint8_t*>(const_cast<void*>(g.B));
+    p.gather_rank = g.gather_rank; p.gather_rows = g.gather_rows; p.gather_epoch = g.gather_epoch;
+    p.gather_ctas = g.gather_ctas > 0 ? g.gather_ctas : 16;
+  }
 
   if (g.epilogue == EPI_SITU) {
     if (g.b_mn || g.splits > 1 || (g.N % 128) != 0) return cudaErrorInvalidValue;

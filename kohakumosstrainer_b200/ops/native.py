@@ -51,7 +51,7 @@ _LAUNCHES_PER_OP = {
     "qk_norm_rope_fwd": 1, "qk_norm_rope_bwd": 1, "situ_fwd": 1, "situ_bwd": 1, "gated_residual": 1, "seg_scale": 1,
     "token_mse_fwd": 2, "token_mse_bwd": 1, "quantize_fp8_tensor": 3, "cast_fp8": 1, "quantize_fp8_rows": 1,
     "adamw_multi": 1, "grad_norm_multi": 2, "ema_multi": 1, "attention_fwd": 1, "attention_bwd": 3,
-    "allreduce": 1,
+    "allreduce": 1, "reduce_scatter_adamw": 1, "allgather": 1,
 }
 LAUNCHES = {"count": 0}
 
@@ -72,13 +72,13 @@ class _CountingOps:
             if n == 0:
                 fn = raw
             elif name == "gemm":
-                def fn(*args, _raw=raw):
-                    LAUNCHES["count"] += 2 if args[-2] > 1 else 1
-                    return _raw(*args)
+                def fn(*args, _raw=raw, **kw):
+                    LAUNCHES["count"] += 2 if args[28] > 1 else 1  # split-K adds the reduction launch
+                    return _raw(*args, **kw)
             else:
-                def fn(*args, _raw=raw, _n=n):
+                def fn(*args, _raw=raw, _n=n, **kw):
                     LAUNCHES["count"] += _n
-                    return _raw(*args)
+                    return _raw(*args, **kw)
             self._cache[name] = fn
         return fn
 
@@ -141,6 +141,7 @@ def gemm(
     eps: float = 1e-6,
     head_rstd: Tensor | None = None,
     splits: int | None = 1,
+    gather: dict | None = None,
 ) -> Tensor:
     """`out = epilogue(A . B^T)` on the tcgen05 GEMM.
 
@@ -164,6 +165,7 @@ def gemm(
     ops.gemm(
         a, b, M, N, K, a_mn, b_mn, out, alpha, scale_a, scale_b, row_scale, col_scale, bias, res, beta,
         gate, seg, t, u, epilogue, aux, q_norm_w, k_norm_w, rope, rope_cols, eps, head_rstd, splits, ws,
+        None, **(gather or {}),
     )
     return out
 

@@ -42,15 +42,16 @@ class WeightPack:
     {dequant, quant}) for a per-tensor recipe, `col_scale` fp32 [out] always (constant for a
     per-tensor recipe, per-row for the row recipe, piecewise for fused q|k|v)."""
 
-    __slots__ = ("kind", "w", "scale", "col_scale", "per_tensor", "trainable", "params")
+    __slots__ = ("kind", "w", "scale", "col_scale", "per_tensor", "trainable", "params", "fsdp")
 
-    def __init__(self, kind, w, scale=None, col_scale=None, per_tensor=True, trainable=False, params=()):
+    def __init__(self, kind, w, scale=None, col_scale=None, per_tensor=True, trainable=False, params=(), fsdp=None):
         self.kind, self.w, self.scale, self.col_scale = kind, w, scale, col_scale
         self.per_tensor, self.trainable, self.params = per_tensor, trainable, tuple(params)
+        self.fsdp = fsdp  # parallel.fsdp.ShardedWeight: `w` is assembled by the GEMM's gather CTAs
 
     @property
     def out_features(self) -> int:
-        return self.w.shape[0]
+        return self.fsdp.out if self.fsdp is not None else self.w.shape[0]
 
 
 class LoraPack:
@@ -70,6 +71,9 @@ class LoraPack:
 def _main_gemm(x, xq, xs, wp: WeightPack, **kw) -> Tensor:
     if wp.kind == "fp8":
         return native.gemm(xq, wp.w, scale_a=xs[:1], col_scale=wp.col_scale, **kw)
+    if wp.fsdp is not None:  # sharded weight: the GEMM gathers it from the peers while it computes
+        full, gather = wp.fsdp.gather_args()
+        return native.gemm(x, full, gather=gather, **kw)
     return native.gemm(x, wp.w, **kw)
 
 
@@ -128,9 +132,20 @@ class _LinearCore:
                     tb = native.gemm(d, lp.up, b_mn=True, col_scale=lp.plain_scale, scale_a=ds[1:2],
                                      scale_b=None if sb is None else wp.scale[1:2])
                 dx = native.gemm(dq, wp.w, b_mn=True, scale_a=ds[:1], scale_b=sb, t=tb, u=ub)
+            elif wp.fsdp is not None:
+                full, gather = wp.fsdp.gather_args()  # resharded after forward: gather again, fused into dgrad
+                dx = native.gemm(d, full, b_mn=True, t=tb, u=ub, gather=gather)
             else:
                 dx = native.gemm(d, wp.w, b_mn=True, t=tb, u=ub)
-        if wp.trainable:
+        if wp.fsdp is not None:
+            sw = wp.fsdp
+            gbuf = sw.grad_buffer()
+            first = sw.first_write
+            native.gemm(d, x, a_mn=True, b_mn=True, out=gbuf, res=None if first else gbuf, beta=1.0)
+            sw.first_write = False
+            if sw.engine.last_micro:
+                sw.reduce()  # reduce-scatter (+ optimiser when fused) overlaps the rest of backward
+        elif wp.trainable:
             dW = native.gemm(d, x, a_mn=True, b_mn=True, out_dtype=torch.float32)
         if need_bias:
             dbias = d.float().sum(0)
@@ -345,6 +360,14 @@ def weight_pack(lins) -> WeightPack:
     if cached is not None and cached[0] == len(lins):
         return cached[1]
     bases = [lin.base for lin in lins]
+    sw = first.__dict__.get("fsdp")
+    if sw is not None:
+        members = first.__dict__.get("fsdp_members", [])
+        if len(members) != len(lins) or any(a is not b for a, b in zip(members, lins)):
+            return None
+        pack = WeightPack("bf16", None, trainable=True, params=(sw.param,), fsdp=sw)
+        first.__dict__["_kmoss_wpack"] = (len(lins), pack)
+        return pack
     if all(b is not None and getattr(b, "kind", "") == "fp8" for b in bases):
         if len(lins) == 1:
             b0 = bases[0]

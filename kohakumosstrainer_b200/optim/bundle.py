@@ -57,7 +57,8 @@ def build_optimizer(named_params, name: str = "adamw", lr: float = 1e-4, betas=(
 class Bundle:
     def __init__(self, optimizer, params: list[Tensor], total_steps: int = 1000, schedule: dict | None = None,
                  grad_clip: float = 1.0, step_sync: str = "step", reduce_flags: Callable | None = None,
-                 reduce_norm_sq: Callable | None = None, ema=None, finish_grads: Callable | None = None):
+                 reduce_norm_sq: Callable | None = None, ema=None, finish_grads: Callable | None = None,
+                 norm_params: list[Tensor] | None = None, extra_sumsq: Callable | None = None, post_step: Callable | None = None):
         self.optimizer = optimizer
         self.params = [p for p in params if p.requires_grad]
         self.base_lrs = [g["lr"] for g in optimizer.param_groups]
@@ -68,6 +69,10 @@ class Bundle:
         self.reduce_norm_sq = reduce_norm_sq    # SUM all-reduce of the squared norm (sharded grads)
         self.finish_grads = finish_grads        # waits for the gradient reduction
         self.ema = ema
+        # gradients that enter the local norm (replicated ones); sharded gradients come in through `extra_sumsq`
+        self.norm_params = [p for p in (norm_params if norm_params is not None else self.params) if p.requires_grad]
+        self.extra_sumsq = extra_sumsq  # () -> fp32[1] squared norm of gradients held elsewhere (already global)
+        self.post_step = post_step
         self.step_index = 0
         self.skipped = 0
         self.last_loss = float("nan")
@@ -89,13 +94,13 @@ class Bundle:
 
     def _norm(self) -> tuple[Tensor, Tensor]:
         """(stats fp32[3] = {norm, clip coefficient, sumsq}, nonfinite int32[1]) on device."""
-        grads = [p.grad for p in self.params if p.grad is not None]
+        grads = [p.grad for p in self.norm_params if p.grad is not None]
         dev = self.params[0].device
         bad = torch.zeros(1, dtype=torch.int32, device=dev)
         if dev.type == "cuda" and all(g.dtype in (torch.float32, torch.bfloat16) for g in grads):
             from ..ops import native
 
-            entries = [dict(param=p.data, grad=p.grad) for p in self.params if p.grad is not None]
+            entries = [dict(param=p.data, grad=p.grad) for p in self.norm_params if p.grad is not None]
             keys = tuple((e["param"].data_ptr(), e["grad"].data_ptr()) for e in entries)
             if self._table is None or self._table.keys != keys:
                 self._table = ParamTable(entries, dev)
@@ -106,6 +111,11 @@ class Bundle:
             clip = torch.clamp(self.grad_clip / (norm + 1e-6), max=1.0) if self.grad_clip > 0 else torch.ones_like(norm)
             stats = torch.stack((norm, clip, sumsq))
             bad += (~torch.isfinite(norm)).to(torch.int32)
+        if self.extra_sumsq is not None:
+            sumsq = stats[2:3] + self.extra_sumsq().to(stats.dtype)
+            norm = sumsq.sqrt()
+            clip = torch.clamp(self.grad_clip / (norm + 1e-6), max=1.0) if self.grad_clip > 0 else torch.ones_like(norm)
+            stats = torch.cat((norm, clip, sumsq))
         if self.reduce_norm_sq is not None:
             sumsq = self.reduce_norm_sq(stats[2:3].clone())
             norm = sumsq.sqrt()
@@ -128,6 +138,9 @@ class Bundle:
         if self.ema is not None:
             self.ema.before_step(self.step_index)
         self.optimizer.step(grad_scale=stats[1:2] if self.grad_clip > 0 else None, skip=skip)
+        self.last_clip, self.last_skip = stats[1:2], skip
+        if self.post_step is not None:
+            self.post_step()
         ok = True
         if self.step_sync == "step":
             loss_v, norm_v, skip_v = torch.cat((flags[:1], stats[:1], skip.float())).tolist()  # the one host sync

@@ -112,9 +112,9 @@ class MuonHybrid(torch.optim.Optimizer):
             if self.shard_gather is not None:
                 upd = self.shard_gather(p, upd)
             ortho = torch.cat([newton_schulz(c, group["ns_steps"]) for c in upd.chunk(n, 0)], 0)
+            rows = ortho.shape[0] // n  # rows of one whole (unsharded) matrix
             if self.shard_gather is not None:
                 ortho = self.shard_gather(p, ortho, scatter=True)
-            rows = p.shape[0] // n if self.shard_gather is None else ortho.shape[0] // n
             scale = group["rms_match"] * math.sqrt(max(rows, p.shape[1]))
             new_p = p.float() * (1 - lr * wd) - ortho.float() * (lr * scale)
             if keep is not None:  # non-finite step: leave parameter and momentum untouched

@@ -1,0 +1,259 @@
+"""Sharded full finetune (FSDP2 / ZeRO-3 role) with the collectives fused into the kernels.
+
+The reference wraps `torch.distributed.fsdp.fully_shard` (`src/kohakumoss/parallel/fsdp.py:34-170`):
+NCCL all-gather before each unit, NCCL reduce-scatter after, fp32 reduce dtype, SUM gradients.
+Here the sharded tensors are the joint blocks' GEMM groups (`qkv`, `o`, `ffn_up_gate`,
+`ffn_down`: 99 % of the parameters), row-sharded over the ranks, and the collectives live inside
+this package's kernels:
+
+* **all-gather -> GEMM.** A rank's shard (bf16 compute copy) sits in symmetric memory. The first
+  GEMM that consumes a weight runs with `gather_ctas` extra CTAs that copy every rank's slab
+  into a local full buffer over NVLink while the other CTAs already compute on the slabs that
+  have landed (own slab first); compute CTAs wait, bounded, only for the slabs their tile reads
+  (`csrc/gemm_sm100.cu`). Forward (K-major B) and dgrad (MN-major B, reduction rotated to the own
+  slab) both use it, so resharding after forward costs no separate gather kernel in backward.
+* **reduce-scatter -> optimiser.** wgrad writes the full dW into a symmetric gradient buffer; one
+  kernel (`csrc/comm.cu::reduce_scatter_adamw`) meets the peers, sums THIS rank's rows from every
+  rank in fp32 registers, accumulates the squared norm, and either applies AdamW (+ EMA, + the bf16
+  compute copy the peers gather next step) in the same pass (`fused_step=True`, clip coefficient
+  of the previous step, like the reference's fused step) or writes the reduced fp32 shard gradient
+  for the regular bundle (`fused_step=False`: exact global-norm clipping, Muon).
+* **Muon under sharding.** Newton-Schulz needs the whole matrix: `gather_update` all-gathers the
+  momentum-updated row shards with the peer-copy kernel, every rank orthogonalises and keeps its
+  rows (`optim.muon.MuonHybrid.shard_gather`).
+
+Small tensors (norms, biases, conditioning, embedders, head) stay replicated and go through
+`parallel.ddp.GradReducer`. Checkpoints hold full tensors (`full_state`), re-sharded on load.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch import Tensor, nn
+
+from . import symm
+
+GROUPS = (("qkv", ("q", "k", "v")), ("o", ("o",)), ("ffn_up_gate", ("ffn_up_gate",)), ("ffn_down", ("ffn_down",)))
+
+
+class _Pool:
+    """Buffers reused by every layer: full weights (local) and full gradients (symmetric)."""
+
+    def __init__(self, device, group):
+        self.device, self.group = device, group
+        self.weights: dict[tuple, list[Tensor]] = {}
+        self.grads: dict[tuple, list] = {}
+        self._w_next: dict[tuple, int] = {}
+        self._g_next: dict[tuple, int] = {}
+
+    def weight(self, shape, slots: int = 2) -> Tensor:
+        key = tuple(shape)
+        bufs = self.weights.setdefault(key, [])
+        if len(bufs) < slots:
+            bufs.append(torch.empty(shape, dtype=torch.bfloat16, device=self.device))
+            return bufs[-1]
+        i = self._w_next.get(key, 0)
+        self._w_next[key] = (i + 1) % slots
+        return bufs[i]
+
+    def grad(self, shape, slots: int = 2):
+        key = tuple(shape)
+        bufs = self.grads.setdefault(key, [])
+        if len(bufs) < slots:
+            n = shape[0] * shape[1]
+            bufs.append(symm.SymmetricBuffer(n, torch.bfloat16, self.device, self.group, zero=True))
+            return bufs[-1]
+        i = self._g_next.get(key, 0)
+        self._g_next[key] = (i + 1) % slots
+        return bufs[i]
+
+
+class ShardedWeight:
+    """One GEMM group's weight `[out, in]`, rows split evenly over the ranks."""
+
+    def __init__(self, name: str, full: Tensor, engine: "FsdpEngine"):
+        self.name, self.engine = name, engine
+        self.out, self.inp = full.shape
+        w, r = engine.world, engine.rank
+        if self.out % w:
+            raise ValueError(f"{name}: {self.out} rows do not split over {w} ranks")
+        self.rows = self.out // w
+        self.shard_sym = symm.SymmetricBuffer(self.rows * self.inp, torch.bfloat16, engine.device, engine.group, zero=False)
+        mine = full[r * self.rows : (r + 1) * self.rows].detach()
+        self.shard_sym.local.copy_(mine.reshape(-1).to(torch.bfloat16))
+        # the trainable parameter IS the fp32 master shard; `shard_sym` is its bf16 compute copy
+        self.param = nn.Parameter(mine.float().contiguous().clone(), requires_grad=True)
+        self.master = self.param.data
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+        self.ema: Tensor | None = None
+        self.flags = symm.SymmetricBuffer(8, torch.int32, engine.device, engine.group, zero=True)
+        self.ready = torch.zeros(8, dtype=torch.int32, device=engine.device)
+        self.epoch = 0
+        self.full: Tensor | None = None       # valid between a gather and the next pool reuse
+        self.full_epoch = -1
+        self.grad_sym = None
+        self.grad_live = False
+
+    # -- forward / backward operands ---------------------------------------------------------
+    def gather_args(self) -> tuple[Tensor, dict]:
+        """(full buffer the GEMM reads as B, kwargs that make the GEMM assemble it)."""
+        self.epoch += 1
+        self.full = self.engine.pool.weight((self.out, self.inp))
+        gather = dict(gather_src=self.shard_sym.ptrs, gather_flags=self.flags.ptrs, gather_ready=self.ready,
+                      gather_rank=self.engine.rank, gather_rows=self.rows, gather_epoch=self.epoch,
+                      gather_ctas=self.engine.gather_ctas)
+        return self.full, gather
+
+    def grad_buffer(self) -> Tensor:
+        """Symmetric `[out, in]` bf16 buffer wgrad writes (fresh per step, accumulated over
+        micro-batches)."""
+        if not self.grad_live:
+            self.grad_sym = self.engine.pool.grad((self.out, self.inp))
+            free = getattr(self.grad_sym, "free_event", None)
+            if free is not None:  # the reduction that last read this buffer must be over
+                torch.cuda.current_stream(self.engine.device).wait_event(free)
+            self.grad_live = True
+            self.first_write = True
+        return self.grad_sym.local.view(self.out, self.inp)
+
+    def reduce(self) -> None:
+        """Reduce-scatter this weight's gradient (and step, when fused) on the comm stream."""
+        eng = self.engine
+        from ..ops import native
+
+        h = eng.hyper
+        grad_out = None
+        if not eng.fused_step:
+            if self.param.grad is None:
+                self.param.grad = torch.empty(self.rows, self.inp, dtype=torch.float32, device=eng.device)
+            grad_out = self.param.grad
+        eng.comm_stream.wait_stream(torch.cuda.current_stream(eng.device))
+        with torch.cuda.stream(eng.comm_stream):
+            native.load().reduce_scatter_adamw(
+                self.grad_sym.ptrs, eng.flags.buffer.ptrs, eng.rank * self.rows * self.inp, self.rows * self.inp, 1,
+                self.master, self.exp_avg, self.exp_avg_sq, self.ema, self.shard_sym.local, grad_out, eng.sumsq,
+                h.get("grad_scale"), h.get("skip"), h["lr"], h["beta1"], h["beta2"], h["eps"], h["weight_decay"], h["step"],
+                h.get("ema_decay", 1.0), eng.rank, eng.flags.next_epoch(), eng.comm_blocks)
+            self.grad_sym.free_event = torch.cuda.Event()
+            self.grad_sym.free_event.record(eng.comm_stream)
+        self.grad_live = False
+
+    # -- checkpoints ---------------------------------------------------------------------------
+    def full_tensor(self, source: str = "master") -> Tensor:
+        """All ranks' rows concatenated (fp32 from the masters, gathered with torch collectives:
+        checkpoint path, not a hot path)."""
+        local = {"master": self.master, "ema": self.ema if self.ema is not None else self.master}[source]
+        parts = [torch.empty_like(local) for _ in range(self.engine.world)]
+        dist.all_gather(parts, local.contiguous(), group=self.engine.group)
+        return torch.cat(parts, 0)
+
+    def load_full(self, full: Tensor) -> None:
+        r = self.engine.rank
+        mine = full[r * self.rows : (r + 1) * self.rows].to(self.master.device)
+        self.master.copy_(mine.float())
+        self.shard_sym.local.copy_(mine.reshape(-1).to(torch.bfloat16))
+
+
+class FsdpEngine:
+    def __init__(self, model, device, group=None, fused_step: bool = False, gather_ctas: int = 16, comm_blocks: int = 48,
+                 reshard: str = "forward"):
+        if not symm.available(device):
+            raise RuntimeError("the FSDP engine needs CUDA peers in one NCCL process group")
+        self.model, self.device, self.group = model, torch.device(device), group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.fused_step, self.gather_ctas, self.comm_blocks, self.reshard = fused_step, gather_ctas, comm_blocks, reshard
+        self.pool = _Pool(self.device, group)
+        self.flags = symm.PeerFlags(self.device, group)
+        self.comm_stream = torch.cuda.Stream(self.device)
+        self.sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.hyper: dict = {}
+        self.weights: dict[str, ShardedWeight] = {}
+        self.last_micro = True
+        self._shard(model)
+
+    def _shard(self, model) -> None:
+        holder = nn.ParameterDict()
+        for i, block in enumerate(model.layers):
+            for gname, members in GROUPS:
+                lins = [block.proj[m] for m in members]
+                full = torch.cat([lin.weight.detach() for lin in lins], 0)
+                name = f"layers.{i}.proj.{gname}"
+                sw = ShardedWeight(name, full, self)
+                self.weights[name] = sw
+                holder[name.replace(".", "__")] = sw.param
+                for lin in lins:
+                    lin.drop_weight()
+                    lin.__dict__["fsdp"] = sw
+                    lin.__dict__["fsdp_members"] = lins
+                del full
+        model.fsdp_shards = holder
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        from ..ops import native_ops
+
+        native_ops.invalidate_packs(model)
+
+    def sharded_parameters(self) -> list[nn.Parameter]:
+        return [sw.param for sw in self.weights.values()]
+
+    def named_sharded_parameters(self) -> list[tuple[str, nn.Parameter]]:
+        return [(name + ".weight", sw.param) for name, sw in self.weights.items()]
+
+    def replicated_parameters(self) -> list[nn.Parameter]:
+        ids = {id(p) for p in self.sharded_parameters()}
+        return [p for p in self.model.parameters() if id(p) not in ids and p.requires_grad]
+
+    # -- step protocol ---------------------------------------------------------------------------
+    def begin_step(self, **hyper) -> None:
+        """Hyper-parameters of the coming optimiser step (fused mode reads them in backward)."""
+        self.hyper = hyper
+        self.sumsq.zero_()
+
+    def start(self, last: bool) -> None:
+        self.last_micro = last
+
+    def finish(self) -> None:
+        torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+
+    def global_sumsq(self) -> Tensor:
+        """Squared norm of all sharded gradients of the step (every rank holds distinct rows)."""
+        t = self.sumsq.clone()
+        dist.all_reduce(t, group=self.group)
+        return t
+
+    def after_optimizer(self) -> None:
+        """`fused_step=False`: the bundle's optimiser updated the fp32 shard parameters' masters;
+        refresh the bf16 compute copies the peers will gather."""
+        for sw in self.weights.values():
+            sw.shard_sym.local.copy_(sw.param.data.reshape(-1))
+
+    def gather_update(self, p: Tensor, local: Tensor, scatter: bool = False) -> Tensor:
+        """`MuonHybrid.shard_gather`: row shards of an update -> the whole matrix (and back)."""
+        sw = next(w for w in self.weights.values() if w.param is p)
+        if scatter:
+            return local[self.rank * sw.rows : (self.rank + 1) * sw.rows]
+        parts = [torch.empty_like(local) for _ in range(self.world)]
+        dist.all_gather(parts, local.contiguous(), group=self.group)
+        return torch.cat(parts, 0)
+
+    def full_state(self, source: str = "master") -> dict[str, Tensor]:
+        """Full fp32 tensors under the backbone's own state-dict keys (q / k / v split again)."""
+        out = {}
+        for name, sw in self.weights.items():
+            full = sw.full_tensor(source)
+            base, gname = name.rsplit(".", 1)
+            members = dict(GROUPS)[gname]
+            for m, part in zip(members, full.chunk(len(members), 0)):
+                out[f"{base}.{m}.weight"] = part
+        return out
+
+    def load_full_state(self, state: dict[str, Tensor]) -> None:
+        for name, sw in self.weights.items():
+            base, gname = name.rsplit(".", 1)
+            sw.load_full(torch.cat([state[f"{base}.{m}.weight"] for m in dict(GROUPS)[gname]], 0))
+
+
+def shard(model, device, **kw) -> FsdpEngine:
+    return FsdpEngine(model, device, **kw)

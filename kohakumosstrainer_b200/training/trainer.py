@@ -61,6 +61,7 @@ class TrainerConfig:
     ddp_bucket_mb: int = 25
     ddp_reduce_dtype: str = "fp32"
     ddp_backend: str = "kohakumoss"
+    fused_step: bool = False           # FSDP: apply AdamW inside the reduce-scatter kernel (clip lags one step)
 
 
 class Trainer:
@@ -92,11 +93,35 @@ class Trainer:
             )
             self.adapters = adapters_pkg.apply(self.model, acfg)
             named = [(n, p) for n, p in self.adapters.named_parameters() if p.requires_grad]
-        self.named_trainable = named
-        self.params = [p for _, p in named]
         self.parallel = None
+        self.fsdp = None
         reduce_flags = reduce_tokens = None
         finish = None
+        norm_params = extra_sumsq = post_step = None
+        if cfg.parallel == "fsdp" and world > 1:
+            from ..parallel.ddp import GradReducer, all_reduce_sum, broadcast_params
+            from ..parallel.fsdp import FsdpEngine
+
+            if cfg.algo != "full":
+                raise ValueError("PARALLEL='fsdp' shards the base weights: it needs ALGO='full'")
+            broadcast_params(list(self.model.parameters()))
+            self.fsdp = FsdpEngine(self.model, self.device, fused_step=cfg.fused_step)
+            replicated = self.fsdp.replicated_parameters()
+            rep_ids = {id(p) for p in replicated}
+            named = [(n, p) for n, p in self.model.named_parameters() if id(p) in rep_ids]
+            norm_params = [p for _, p in named]
+            self.parallel = GradReducer(norm_params, bucket_mb=cfg.ddp_bucket_mb, backend=cfg.ddp_backend, device=self.device)
+            if not cfg.fused_step:
+                named = named + self.fsdp.named_sharded_parameters()
+            extra_sumsq = self.fsdp.global_sumsq
+            post_step = None if cfg.fused_step else self.fsdp.after_optimizer
+            reduce_flags = reduce_tokens = all_reduce_sum
+
+            def finish():
+                self.parallel.finish()
+                self.fsdp.finish()
+        self.named_trainable = named
+        self.params = [p for _, p in named]
         if cfg.parallel == "ddp" and world > 1:
             from ..parallel.ddp import GradReducer, all_reduce_sum, broadcast_params
 
@@ -107,15 +132,26 @@ class Trainer:
             finish = self.parallel.finish
         opt = build_optimizer(named, cfg.optimizer, cfg.lr, cfg.betas, cfg.eps, cfg.weight_decay, cfg.wd_rules,
                               cfg.optimizer_kwargs)
+        if self.fsdp is not None and hasattr(opt, "shard_gather"):
+            opt.shard_gather = self.fsdp.gather_update
         self.ema = ConstantEMA(named, (cfg.ema,)) if cfg.ema > 0 else None
         self.bundle = Bundle(opt, self.params, cfg.steps, cfg.schedule, cfg.grad_clip, cfg.step_sync,
-                             reduce_flags=reduce_flags, ema=self.ema, finish_grads=finish)
+                             reduce_flags=reduce_flags, ema=self.ema, finish_grads=finish, norm_params=norm_params,
+                             extra_sumsq=extra_sumsq, post_step=post_step)
         self.normalizer = TokenNormalizer(reduce_tokens, 1)
         self.step_fn = TrainStep(self.model, self.device, cfg.timestep, cfg.timestep_kwargs, cfg.loss, None,
                                  cfg.weighting, cfg.seed, rank, dtype)
         self.batcher = DeviceBatcher(self.device, torch.float32, dtype)
         self.tokens_seen = 0
         self.samples_seen = 0
+
+    def _begin_fsdp_step(self) -> None:
+        b = self.bundle
+        g = b.optimizer.param_groups[0]
+        lr = b.base_lrs[0] * b.factor(b.step_index)
+        self.fsdp.begin_step(lr=lr, beta1=g["betas"][0], beta2=g["betas"][1], eps=g["eps"], weight_decay=self.cfg.weight_decay,
+                             step=b.step_index + 1, grad_scale=getattr(b, "last_clip", None) if self.cfg.grad_clip > 0 else None,
+                             skip=None, ema_decay=1.0)
 
     def train_step(self, host_batches: list[HostBatch] | HostBatch, next_batch: HostBatch | None = None) -> dict:
         """One optimiser step over the given micro-batches. Returns host-side numbers
@@ -132,6 +168,10 @@ class Trainer:
                 self.batcher.prefetch(nxt)
             if self.parallel is not None:
                 self.parallel.start(last=i == n - 1)
+            if self.fsdp is not None:
+                if i == 0:
+                    self._begin_fsdp_step()
+                self.fsdp.start(last=i == n - 1)
             loss = self.step_fn(batch, denom)
             loss.backward()
             self.bundle.observe(loss)

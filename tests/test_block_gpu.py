@@ -171,3 +171,93 @@ def test_model_lora_step_matches_fp32_reference(base):
         if err > (0.1 if base == "bf16" else 0.3):
             bad.append((n, err))
     assert not bad, bad[:6]
+
+
+def test_full_finetune_grads_match_fp32_reference():
+    """ALGO=full: every trainable weight's gradient through the native path (wgrad on the
+    tcgen05 GEMM, norm / modulation / qk-norm grads) against the fp32 eager twin."""
+    import copy
+
+    from kohakumosstrainer_b200.models import build_backbone
+    from kohakumosstrainer_b200.models.build import apply_param_dtypes
+    from kohakumosstrainer_b200.ops import EagerOps, native
+
+    cfg = MossArchConfig(dim=256, depth=2, heads=2, ffn_dim=512, text_dim=256, text_blocks=1)
+    ref = build_backbone(cfg, device="cuda", dtype=torch.float32, seed=5)
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.copy_(p.bfloat16().float())
+    model = copy.deepcopy(ref)
+    apply_param_dtypes(model, torch.bfloat16)
+    model.bind_ops()
+    ref.bind_ops(EagerOps())
+    seq = _seq("cuda")
+    g = torch.Generator(device="cuda").manual_seed(4)
+    z = torch.randn(seq.n_img, 128, device="cuda", generator=g).bfloat16()
+    text = torch.randn(seq.n_txt, 256, device="cuda", generator=g).bfloat16()
+    sigma = torch.rand(3, device="cuda", generator=g)
+    target = torch.randn(seq.n_img, 128, device="cuda", generator=g)
+    ones = torch.ones(3, device="cuda")
+    v = model(z, text, sigma, seq)
+    (model.ops.token_mse(v, target, seq.seg_img, ones) / seq.n_img).backward()
+    native.check_status()
+    rv = ref(z.float(), text.float(), sigma, seq)
+    (ref.ops.token_mse(rv, target, seq.seg_img, ones) / seq.n_img).backward()
+    assert _rel(v, rv) < 0.03
+    rg = dict(ref.named_parameters())
+    bad, checked = [], 0
+    for n, p in model.named_parameters():
+        assert p.grad is not None, n
+        if rg[n].grad.norm() == 0:
+            continue
+        err = _rel(p.grad, rg[n].grad)
+        checked += 1
+        if err > 0.12:
+            bad.append((n, round(err, 3)))
+    assert checked > 40 and not bad, bad[:8]
+
+
+def test_muon_newton_schulz_on_the_tcgen05_gemm_matches_torch():
+    from kohakumosstrainer_b200.optim.muon import _ns_native, _ns_torch
+
+    g = torch.Generator(device="cuda").manual_seed(8)
+    x = torch.randn(256, 768, device="cuda", generator=g).bfloat16()
+    x = (x / x.norm()).contiguous()
+    a, b = _ns_native(x, 5).float(), _ns_torch(x, 5).float()
+    assert _rel(a, b) < 0.05
+    s = torch.linalg.svdvals(a)
+    assert 0.4 < s.min() and s.max() < 1.4
+
+
+def test_fused_adamw_kernel_matches_reference_math():
+    from kohakumosstrainer_b200.optim import FusedAdamW
+
+    g = torch.Generator(device="cuda").manual_seed(9)
+    shapes = [(300, 17), (8192 * 3 + 5,), (64, 64)]
+    ps = [torch.nn.Parameter(torch.randn(s, device="cuda", generator=g).bfloat16()) for s in shapes]
+    rs = [torch.nn.Parameter(p.detach().float().cpu()) for p in ps]
+    ours = FusedAdamW(ps, lr=1e-2, weight_decay=0.1, master_weights=True)
+    ref = torch.optim.AdamW(rs, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ema = {id(p): p.detach().float().clone() for p in ps}
+    ours.attach_ema(ema)
+    ours.ema_decay = 0.9
+    ema_ref = [r.detach().clone() for r in rs]
+    scale = torch.tensor([0.5], device="cuda")
+    for _ in range(4):
+        for p, r in zip(ps, rs):
+            gr = torch.randn(p.shape, device="cuda", generator=g).bfloat16()
+            p.grad = gr
+            r.grad = gr.float().cpu() * 0.5
+        ours.step(grad_scale=scale)
+        ref.step()
+        for e, r in zip(ema_ref, rs):
+            e.lerp_(r.detach(), 0.1)
+    for p, r, e in zip(ps, rs, ema_ref):
+        master = ours.state[p]["master"]
+        torch.testing.assert_close(master.cpu(), r.detach(), rtol=2e-5, atol=2e-6)
+        torch.testing.assert_close(p.detach().float().cpu(), r.detach().bfloat16().float(), rtol=1e-2, atol=1e-3)
+        torch.testing.assert_close(ema[id(p)].cpu(), e, rtol=1e-4, atol=1e-5)
+    skip = torch.ones(1, dtype=torch.int32, device="cuda")
+    before = [p.detach().clone() for p in ps]
+    ours.step(skip=skip)
+    assert all(torch.equal(a, b) for a, b in zip(before, ps))

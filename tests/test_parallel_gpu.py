@@ -41,3 +41,18 @@ def test_peer_memory_reducer_matches_analytic_sum(tmp_path, dtype):
         assert r["backend"] == "kohakumoss"
         assert r["views"] and r["ranks_agree"] and r["status"][0] == 0
         assert r["rel_err"] < (1e-5 if dtype == "fp32" else 2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.multi_gpu
+@pytest.mark.parametrize("fused_step,optimizer", [(False, "adamw"), (True, "adamw"), (False, "muon")])
+def test_sharded_full_finetune_tracks_the_unsharded_run(tmp_path, fused_step, optimizer):
+    """FSDP engine (all-gather fused into the GEMMs, reduce-scatter fused with the optimiser)
+    on two GPUs against the same training done unsharded."""
+    res = selftest.spawn_results(selftest.fsdp_worker, 2, str(tmp_path), (fused_step, optimizer), device_type="cuda",
+                                 timeout_s=240, env={"NCCL_NVLS_ENABLE": "0"})
+    assert all(r["status"][0] == 0 for r in res)
+    r0 = res[0]
+    assert all(abs(a - b) / abs(b) < 0.15 for a, b in zip(r0["losses"], r0["ref_losses"])), (r0["losses"], r0["ref_losses"])
+    # update directions of every sharded weight agree with the unsharded run
+    assert r0["min_cos"] > (0.7 if fused_step else 0.85), (r0["min_cos"], r0["worst"])
