@@ -378,9 +378,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
           if (p.gather_world > 1) {
             // rows of B this k-block / tile reads: K-major B -> N rows of the tile; MN-major B -> K rows
-            const int r0 = B_MN ? k0 : n0, r1 = B_MN ? min(p.K, k0 + C::BK) - 1 : min(p.N, n0 + BN) - 1;
             bool ready = true;
-            for (int s2 = r0 / p.gather_rows; s2 <= r1 / p.gather_rows && ready; ++s2) ready = wait_slab(s2);
+            if (!B_MN && p.epilogue == EPI_SITU) {
+              // paired tile: up rows [n0/2, n0/2 + BN/2) and gate rows [F + n0/2, F + n0/2 + BN/2)
+              for (int part = 0; part < 2 && ready; ++part) {
+                const int r0 = part * p.situ_f + n0 / 2, r1 = min(part * p.situ_f + p.N, r0 + BN / 2) - 1;
+                for (int s2 = r0 / p.gather_rows; s2 <= r1 / p.gather_rows && ready; ++s2) ready = wait_slab(s2);
+              }
+            } else {
+              const int r0 = B_MN ? k0 : n0, r1 = B_MN ? min(p.K, k0 + C::BK) - 1 : min(p.N, n0 + BN) - 1;
+              for (int s2 = r0 / p.gather_rows; s2 <= r1 / p.gather_rows && ready; ++s2) ready = wait_slab(s2);
+            }
             if (!ready) { ok = false; break; }
           }
           if constexpr (!B_MN) {
@@ -1099,9 +1107,9 @@ cudaError_t gemm_launch(const GemmProblem& g, cudaStream_t stream) {
   p.gather_ctas = 0;
   if (p.gather_world > 1) {
     // the slabs partition the stored rows of B: N rows when K-major ([N, K]), K rows when MN-major ([K, N])
-    const int b_rows = g.b_mn ? g.K : g.N;
+    const int b_rows = g.b_mn ? g.K : (g.epilogue == EPI_SITU ? 2 * g.N : g.N);
     const long b_cols = g.b_mn ? g.N : g.K;
-    if (g.gather_world > 8 || g.gather_ready == nullptr || g.gather_rows <= 0 || g.splits > 1 || g.epilogue == EPI_SITU ||
+    if (g.gather_world > 8 || g.gather_ready == nullptr || g.gather_rows <= 0 || g.splits > 1 ||
         g.ldb != b_cols || (long)g.gather_rows * g.gather_world != b_rows)
       return cudaErrorInvalidValue;
     const size_t eb2 = fp8 ? 1 : 2;

@@ -660,9 +660,15 @@ class NativeOps(OpSet):
         wp, lp, down, up = prep
         cfg = dict(wp=wp, lp=lp, mode="qkrope", q_norm_w=q_weight.detach(), k_norm_w=k_weight.detach(),
                    table=_table(pos, bands), rope_cols=2 * dim, eps=eps)
-        if q_weight.requires_grad or k_weight.requires_grad or q_weight.dtype != BF16:
-            return OpSet.qkv_rope(self, y, lin_q, lin_k, lin_v, heads, q_weight, k_weight, pos, bands, eps)
         weights = wp.params if wp.trainable else ()
+        if q_weight.requires_grad or k_weight.requires_grad or q_weight.dtype != BF16:
+            # trainable qk-norm weights: one fused q|k|v GEMM, then the standalone norm + RoPE
+            # kernel, whose backward also yields the norm-weight gradients
+            lin_cfg = dict(wp=wp, lp=lp, mode="linear", bias_dtype=None)
+            out = FusedLinearFn.apply(lin_cfg, y.contiguous(), None, None, None, down, up, *weights)
+            q, k, v = out.unflatten(1, (3, heads, 128)).unbind(1)
+            q, k = self.qk_norm_rope(q, k, q_weight, k_weight, pos, bands, eps)
+            return q, k, v
         out = FusedLinearFn.apply(cfg, y.contiguous(), None, None, None, down, up, *weights)
         q, k, v = out.unflatten(1, (3, heads, 128)).unbind(1)
         return q, k, v

@@ -231,7 +231,9 @@ class FsdpEngine:
 
     def gather_update(self, p: Tensor, local: Tensor, scatter: bool = False) -> Tensor:
         """`MuonHybrid.shard_gather`: row shards of an update -> the whole matrix (and back)."""
-        sw = next(w for w in self.weights.values() if w.param is p)
+        sw = next((w for w in self.weights.values() if w.param is p), None)
+        if sw is None:  # a replicated matrix (text refiner): already whole on every rank
+            return local
         if scatter:
             return local[self.rank * sw.rows : (self.rank + 1) * sw.rows]
         parts = [torch.empty_like(local) for _ in range(self.world)]

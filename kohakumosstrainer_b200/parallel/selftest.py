@@ -188,14 +188,24 @@ def fsdp_worker(rank, world, device, out_dir, fused_step=False, optimizer="adamw
     state = tr.fsdp.full_state()
     result = {"losses": losses, "status": status, "fused": fused_step}
     if rank == 0:
+        from ..training.step import TrainStep
+
         ref = Trainer(TrainerConfig(parallel="none", **common), device=device, rank=0, world=1)
-        # the reference draws the same sigma / noise streams only on rank 0's data; compare
-        # what does not depend on them: both runs start from identical weights and see the
-        # same batches, so the parameter update directions must agree closely
+        # one step function per emulated rank, so every micro-batch sees the sigma / noise draws
+        # its rank saw in the sharded run
+        fns = [TrainStep(ref.model, device, "logit_normal", None, "mse", None, "none", 3, r, torch.bfloat16) for r in range(world)]
         ref_losses = []
         for s in range(steps):
             group = [data.materialize(s, r, world) for r in range(world)]
-            ref_losses.append(ref.train_step(group)["loss"])
+            denom = ref.normalizer.denominator(sum(hb.image_tokens for hb in group), device)
+            for r, hb in enumerate(group):
+                loss = fns[r](hb.to_device(device, torch.float32, torch.bfloat16), denom)
+                loss.backward()
+                ref.bundle.observe(loss)
+            ref.bundle.step()
+            for fn in fns:
+                fn.step_index += 1
+            ref_losses.append(ref.bundle.last_loss)
         ref_state = dict(ref.model.state_dict())
         init = Trainer(TrainerConfig(parallel="none", **common), device=device, rank=0, world=1).model.state_dict()
         errs = {}
