@@ -206,6 +206,14 @@ class GradReducer:
             if len(self.wait_ms_events) > 64:
                 self.wait_ms_events = self.wait_ms_events[-64:]
 
+    def reduce_now(self) -> None:
+        """Reduce every bucket now (callers that accumulate several micro-batches inside one
+        backward region, like the pipeline engines, cannot use the per-parameter hooks)."""
+        self._next = 0
+        for b in self.buckets:
+            b.attach()
+        self.finish()
+
     def metrics(self) -> dict:
         """`ddp_comm_wait_ms` of the most recent finished step, `ddp_reduce_mb`, launches."""
         wait = None

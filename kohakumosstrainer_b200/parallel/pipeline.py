@@ -1,0 +1,314 @@
+"""Pipeline parallelism over contiguous block ranges: process-group engine (one stage per rank,
+NCCL / gloo p2p, GPipe and 1F1B schedules, optional data-parallel replicas per stage) and the
+threaded engine (one process, stages on several devices).
+
+What crosses a stage boundary is `(x, mod, head)`: the joint residual stream `[N, D]`, the block
+modulation `[B, 6, D]` and the head modulation `[B, 2, D]`; backward sends their gradients the
+other way. Every rank materialises the same micro-batches (the data plan is a pure function of
+(seed, index)), so each stage knows every micro-batch's layout and message sizes without
+headers or padding. The reference builds on `torch.distributed.pipelining` with padded static
+shapes (`src/kohakumoss/parallel/pipeline/distributed.py:142-541`, `split.py:99-335`,
+`threaded.py:38-154`); this engine owns its schedule, posts the next receive before it computes,
+and composes with data-parallel groups (PP x DP), which the reference does not have.
+"""
+
+from __future__ import annotations
+
+import queue
+import threading
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from ..models.block import BlockCtx
+
+SCHEDULES = ("gpipe", "1f1b")
+
+
+def block_costs(cfg, split="flops") -> list[float]:
+    """Relative cost of [embed+conditioning, block_0 .. block_{depth-1}, head]."""
+    d, f = cfg.dim, cfg.ffn_dim
+    block = 4 * d * d + 3 * d * f
+    embed = cfg.text_blocks * (4 * d * d + 3 * d * f) * 0.06 + cfg.latent_channels * d + cfg.text_dim * d * 0.06
+    head = cfg.latent_channels * d
+    if split == "even":
+        return [0.0] + [1.0] * cfg.depth + [0.0]
+    return [embed / block] + [1.0] * cfg.depth + [head / block]
+
+
+def stage_bounds(cfg, n_stages: int, split="flops") -> list[tuple[int, int]]:
+    """Contiguous `[lo, hi)` block ranges per stage minimising the heaviest stage (exact DP
+    over partitions); `split` may be "flops", "even", or an explicit tuple of block counts."""
+    depth = cfg.depth
+    if isinstance(split, (tuple, list)):
+        if sum(split) != depth or len(split) != n_stages:
+            raise ValueError(f"PIPELINE_SPLIT {split} must have {n_stages} entries summing to {depth}")
+        out, lo = [], 0
+        for n in split:
+            out.append((lo, lo + n))
+            lo += n
+        return out
+    if n_stages > depth:
+        raise ValueError(f"{n_stages} stages for {depth} blocks")
+    costs = block_costs(cfg, split)
+    extra_first, extra_last = costs[0], costs[-1]
+    w = costs[1:-1]
+    prefix = [0.0]
+    for c in w:
+        prefix.append(prefix[-1] + c)
+
+    def seg(lo, hi, s):
+        c = prefix[hi] - prefix[lo]
+        if s == 0:
+            c += extra_first
+        if s == n_stages - 1:
+            c += extra_last
+        return c
+
+    inf = float("inf")
+    best = [[inf] * (depth + 1) for _ in range(n_stages + 1)]
+    cut = [[0] * (depth + 1) for _ in range(n_stages + 1)]
+    best[0][0] = 0.0
+    for s in range(1, n_stages + 1):
+        for hi in range(s, depth + 1):
+            for lo in range(s - 1, hi):
+                cand = max(best[s - 1][lo], seg(lo, hi, s - 1))
+                if cand < best[s][hi]:
+                    best[s][hi], cut[s][hi] = cand, lo
+    bounds, hi = [], depth
+    for s in range(n_stages, 0, -1):
+        lo = cut[s][hi]
+        bounds.append((lo, hi))
+        hi = lo
+    return bounds[::-1]
+
+
+@dataclass
+class StageIO:
+    """What a stage receives or sends for one micro-batch."""
+
+    x: Tensor
+    mod: Tensor
+    head: Tensor
+
+    def tensors(self) -> list[Tensor]:
+        return [self.x, self.mod, self.head]
+
+
+class StageModule:
+    """The slice of a backbone one stage runs."""
+
+    def __init__(self, model, lo: int, hi: int, first: bool, last: bool):
+        self.model, self.lo, self.hi, self.first, self.last = model, lo, hi, first, last
+
+    def parameters(self):
+        m = self.model
+        params = []
+        for i in range(self.lo, self.hi):
+            params += list(m.layers[i].parameters())
+        if self.first:
+            for mod in (m.video_embedder, m.text_embedder, m.time_embedding, m.shared_block_modulation, m.video_head_modulation):
+                params += list(mod.parameters())
+        if self.last:
+            params += list(m.final_norm_video.parameters()) + list(m.final_linear_video.parameters())
+        return [p for p in params if p.requires_grad]
+
+    def release_others(self) -> None:
+        """Free the blocks this stage never runs."""
+        for i, block in enumerate(self.model.layers):
+            if not (self.lo <= i < self.hi):
+                for p in block.parameters():
+                    p.data = torch.empty(0, dtype=p.dtype, device=p.device)
+                    p.requires_grad_(False)
+
+    def forward(self, inp: StageIO | None, img, text, sigma, seq) -> StageIO | Tensor:
+        m = self.model
+        if self.first:
+            mod, head = m.conditioning(sigma)
+            x = m.embed(img, text, seq)
+        else:
+            x, mod, head = inp.x, inp.mod, inp.head
+        ctx = BlockCtx(seq, mod, m.rope.bands, m.residual_scale)
+        for i in range(self.lo, self.hi):
+            x = m.runner.run(i, m.layers[i], x, ctx)
+        if self.last:
+            return m.head(x, head, seq)
+        return StageIO(x, mod, head)
+
+
+class PipelineEngine:
+    """One rank = one stage (of one data-parallel replica)."""
+
+    def __init__(self, model, stage: int, n_stages: int, bounds, device, pp_group=None, prev_rank: int | None = None,
+                 next_rank: int | None = None, schedule: str = "1f1b", compute_dtype=torch.bfloat16):
+        if schedule not in SCHEDULES:
+            raise ValueError(f"PIPELINE_SCHEDULE {schedule!r}: this engine runs {SCHEDULES}")
+        self.stage, self.n_stages, self.device, self.group, self.schedule = stage, n_stages, torch.device(device), pp_group, schedule
+        lo, hi = bounds[stage]
+        self.module = StageModule(model, lo, hi, stage == 0, stage == n_stages - 1)
+        self.prev, self.next = prev_rank, next_rank
+        self.dtype = compute_dtype
+        self.cfg = model.cfg
+        self.metrics = {"pipe_fwd_ms": 0.0, "pipe_bwd_ms": 0.0, "pipe_idle_ms": 0.0}
+
+    # -- message shapes (known on every rank from the micro-batch layout) ------------------------
+    def _shapes(self, seq):
+        d = self.cfg.dim
+        return (seq.n_joint, d), (seq.batch, 6, d), (seq.batch, 2, d)
+
+    def _alloc_io(self, seq) -> StageIO:
+        sx, sm, sh = self._shapes(seq)
+        return StageIO(torch.empty(sx, dtype=self.dtype, device=self.device), torch.empty(sm, dtype=torch.float32, device=self.device),
+                       torch.empty(sh, dtype=torch.float32, device=self.device))
+
+    def _post_recv(self, seq, src: int):
+        io = self._alloc_io(seq)
+        works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, t, src, self.group) for t in io.tensors()])
+        return io, works
+
+    def _send(self, tensors, dst: int):
+        return dist.batch_isend_irecv([dist.P2POp(dist.isend, t.contiguous(), dst, self.group) for t in tensors])
+
+    @staticmethod
+    def _wait(works):
+        for w in works or []:
+            w.wait()
+
+    # -- one optimiser step --------------------------------------------------------------------------
+    def step(self, micro_batches, loss_fn) -> Tensor | None:
+        """Run all micro-batches through this stage. `micro_batches[i]` = dict(img, text, sigma,
+        seq, target...) already on this device; `loss_fn(v, mb) -> scalar` runs on the last stage.
+        Returns the summed loss on the last stage (None elsewhere)."""
+        n = len(micro_batches)
+        first, last = self.module.first, self.module.last
+        order = self._order(n)
+        saved: dict[int, tuple] = {}
+        fwd_recv: dict[int, tuple] = {}
+        bwd_recv: dict[int, tuple] = {}
+        sends = []
+        total = None
+        next_fwd = [i for kind, i in order if kind == "F"]
+        if not first and next_fwd:
+            fwd_recv[next_fwd[0]] = self._post_recv(micro_batches[next_fwd[0]]["seq"], self.prev)
+        for pos, (kind, i) in enumerate(order):
+            mb = micro_batches[i]
+            if kind == "F":
+                inp = None
+                if not first:
+                    io, works = fwd_recv.pop(i)
+                    self._wait(works)
+                    inp = StageIO(io.x.requires_grad_(), io.mod.requires_grad_(), io.head.requires_grad_())
+                    later = [j for k, j in order[pos + 1 :] if k == "F"]
+                    if later:  # post the next receive before computing: transfer overlaps compute
+                        fwd_recv[later[0]] = self._post_recv(micro_batches[later[0]]["seq"], self.prev)
+                out = self.module.forward(inp, mb.get("img"), mb.get("text"), mb["sigma"], mb["seq"])
+                if last:
+                    loss = loss_fn(out, mb)
+                    total = loss.detach() if total is None else total + loss.detach()
+                    saved[i] = (inp, loss)
+                else:
+                    sends.append(self._send([t.detach() for t in out.tensors()], self.next))
+                    saved[i] = (inp, out)
+            else:
+                inp, out = saved.pop(i)
+                if last:
+                    out.backward()
+                else:
+                    if i not in bwd_recv:
+                        bwd_recv[i] = self._post_recv(mb["seq"], self.next)
+                    g, works = bwd_recv.pop(i)
+                    self._wait(works)
+                    outs = [t for t in out.tensors() if t.requires_grad]
+                    grads = [gt for t, gt in zip(out.tensors(), g.tensors()) if t.requires_grad]
+                    torch.autograd.backward(outs, grads)
+                if not first:
+                    sends.append(self._send([t.grad if t.grad is not None else torch.zeros_like(t) for t in inp.tensors()], self.prev))
+        for works in sends:
+            self._wait(works)
+        return total
+
+    def _order(self, n: int):
+        if self.schedule == "gpipe":
+            return [("F", i) for i in range(n)] + [("B", i) for i in range(n)]
+        warm = min(n, self.n_stages - self.stage - 1)
+        order = [("F", i) for i in range(warm)]
+        f, b = warm, 0
+        while f < n:
+            order += [("F", f), ("B", b)]
+            f, b = f + 1, b + 1
+        order += [("B", i) for i in range(b, n)]
+        return order
+
+
+def pp_dp_groups(world: int, n_stages: int):
+    """Process groups of a PP x DP layout: rank = replica * n_stages + stage. Returns
+    (pp_group of this rank, dp_group of this rank, stage, replica). Every rank must call this."""
+    rank = dist.get_rank()
+    if world % n_stages:
+        raise ValueError(f"world {world} does not divide into {n_stages} stages")
+    replicas = world // n_stages
+    pp_groups = [dist.new_group([r * n_stages + s for s in range(n_stages)]) for r in range(replicas)]
+    dp_groups = [dist.new_group([r * n_stages + s for r in range(replicas)]) for s in range(n_stages)]
+    stage, replica = rank % n_stages, rank // n_stages
+    return pp_groups[replica], dp_groups[stage], stage, replica
+
+
+class ThreadedPipeline:
+    """One process, one thread per stage, stages on several devices; tensors hop devices with
+    `.to(device)` (a peer copy over NVLink). Schedules: `gpipe` (all forwards, then all backwards)
+    and `async` (backward of a micro-batch starts on a helper thread as soon as its loss exists)."""
+
+    def __init__(self, model_stages: list[StageModule], devices: list, schedule: str = "gpipe"):
+        if schedule not in ("gpipe", "async"):
+            raise ValueError("threaded pipeline schedules are gpipe | async")
+        self.stages, self.devices, self.schedule = model_stages, [torch.device(d) for d in devices], schedule
+
+    def step(self, micro_batches, loss_fn) -> Tensor:
+        n_stage = len(self.stages)
+        queues = [queue.Queue() for _ in range(n_stage + 1)]
+        errors: list[BaseException] = []
+        losses: list[Tensor] = []
+        bwd_threads: list[threading.Thread] = []
+
+        def run_stage(s: int):
+            try:
+                dev = self.devices[s]
+                for i, mb in enumerate(micro_batches):
+                    inp = None
+                    if s > 0:
+                        item = queues[s].get()
+                        if item is None:
+                            return
+                        inp = StageIO(*(t.to(dev, non_blocking=True) for t in item))
+                    local = {k: (v.to(dev) if hasattr(v, "to") else v) for k, v in mb.items()}
+                    out = self.stages[s].forward(inp, local.get("img"), local.get("text"), local["sigma"], local["seq"])
+                    if s == n_stage - 1:
+                        loss = loss_fn(out, local)
+                        losses.append(loss)
+                        if self.schedule == "async":
+                            t = threading.Thread(target=loss.backward)
+                            t.start()
+                            bwd_threads.append(t)
+                    else:
+                        queues[s + 1].put(out.tensors())
+            except BaseException as err:  # noqa: BLE001
+                errors.append(err)
+                for q in queues:
+                    q.put(None)
+
+        threads = [threading.Thread(target=run_stage, args=(s,)) for s in range(n_stage)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        if errors:
+            raise errors[0]
+        if self.schedule == "async":
+            for t in bwd_threads:
+                t.join()
+        else:
+            for loss in losses:
+                loss.backward()
+        return torch.stack([loss.detach().to(self.devices[-1]) for loss in losses]).sum()

@@ -216,3 +216,75 @@ def fsdp_worker(rank, world, device, out_dir, fused_step=False, optimizer="adamw
         result.update({"ref_losses": ref_losses, "min_cos": min(errs.values()), "worst": min(errs, key=errs.get)})
     dist.barrier()
     _write(out_dir, rank, result)
+
+
+def pipeline_worker(rank, world, device, out_dir, n_stages=2, schedule="1f1b", micro=4):
+    """Pipeline (x data parallel when world > n_stages) against single-process gradient
+    accumulation over the same micro-batches: equal loss and equal gradients per stage."""
+    from ..data import SyntheticConfig, SyntheticDataset
+    from ..models import build_backbone
+    from ..training.pipeline_driver import PipelineTrainer
+    from ..training.trainer import TrainerConfig
+    from ..types import MossArchConfig
+
+    cuda = device.type == "cuda"
+    arch = (MossArchConfig(dim=256, depth=4, heads=2, ffn_dim=512, text_dim=64, text_blocks=1) if cuda
+            else MossArchConfig(dim=64, depth=4, heads=2, ffn_dim=128, text_dim=64, text_blocks=1))
+    dtype = torch.bfloat16 if cuda else torch.float32
+    if not cuda:
+        torch.set_num_threads(2)
+    cfg = TrainerConfig(algo="full", optimizer="adamw", lr=1e-3, weight_decay=0.0, schedule={"mode": "constant"}, grad_clip=0.0,
+                        timestep="logit_normal", seed=5, ddp_backend="kohakumoss" if cuda else "torch")
+    data = SyntheticDataset(SyntheticConfig(max_tokens=260, min_area=96 * 96, max_area=128 * 128, size_step=32, text_dim=64, max_text=12, min_text=3,
+                                            seed=2, dtype=torch.float32))
+    model = build_backbone(arch, device=device, dtype=dtype, seed=1)
+    for p in model.parameters():
+        p.requires_grad_(True)
+    ref = build_backbone(arch, device=device, dtype=dtype, seed=1)
+    for p in ref.parameters():
+        p.requires_grad_(True)
+    tr = PipelineTrainer(model, cfg, device, n_stages, micro, schedule, "even")
+    replicas = world // n_stages
+    mine = [data.materialize(i, tr.replica, replicas, pin=cuda) for i in range(micro)]
+    # reference: every replica's micro-batches through the whole model on this rank
+    grads_ref = None
+    from ..diffusion import TIMESTEPS, noise_latents, token_loss
+    from ..utils.seeds import seed_of
+
+    total_tokens = sum(data.materialize(i, r, replicas, pin=False).image_tokens for r in range(replicas) for i in range(micro))
+    ref_loss = 0.0
+    for r in range(replicas):
+        sg = torch.Generator().manual_seed(seed_of("sigma", 5, r))
+        ng = torch.Generator(device).manual_seed(seed_of("noise", 5, r))
+        sampler = TIMESTEPS.get("logit_normal")()
+        for i in range(micro):
+            b = data.materialize(i, r, replicas, pin=False).to_device(device, torch.float32, dtype)
+            sigma = sampler.sample(b.seq.batch, sg, 0).to(device)
+            eps = torch.randn(b.latents.shape, generator=ng, device=device, dtype=torch.float32)
+            z, target = noise_latents(b.latents.float(), eps, sigma, b.seq.seg_img)
+            v = ref(z.to(dtype), b.text.to(dtype), sigma, b.seq)
+            loss = token_loss(ref.ops, v, target, b.seq.seg_img, torch.ones(b.seq.batch, device=device)) / total_tokens
+            loss.backward()
+            ref_loss += loss.item()
+    grads_ref = {n: p.grad.detach().float().clone() for n, p in ref.named_parameters() if p.grad is not None}
+    before = {n: p.detach().float().clone() for n, p in model.named_parameters() if p.numel() > 0}
+    # capture this stage's gradients before the optimiser consumes them
+    captured = {}
+    own = {id(p) for p in tr.params}
+    orig_step = tr.bundle.optimizer.step
+
+    def spy(*a, **k):
+        for n, p in model.named_parameters():
+            if id(p) in own and p.grad is not None:
+                captured[n] = p.grad.detach().float().clone()
+        return orig_step(*a, **k)
+
+    tr.bundle.optimizer.step = spy
+    out = tr.train_step(mine)
+    worst, name = 0.0, ""
+    for n, g in captured.items():
+        e = ((g - grads_ref[n]).norm() / grads_ref[n].norm().clamp_min(1e-12)).item()
+        if e > worst:
+            worst, name = e, n
+    _write(out_dir, rank, {"loss": out["loss"], "ref_loss": ref_loss, "worst_grad_err": worst, "worst": name, "stage": tr.stage,
+                           "replica": tr.replica, "n_grads": len(captured)})

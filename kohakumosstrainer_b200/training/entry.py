@@ -83,6 +83,8 @@ def worker(k: dict, rank: int, world: int, device) -> dict:
         write_json(run_dir / "config.json", {kk: vv for kk, vv in k.items()})
     torch.manual_seed(int(k["SEED"]) + rank)
     cfg = trainer_config(k)
+    if k["PARALLEL"] in ("pipeline", "threaded"):
+        return pipeline_worker(k, cfg, rank, world, device, run_dir)
     trainer = Trainer(cfg, device=device, rank=rank, world=world)
     if k["WEIGHTS"] or k["TRANSFORMER"]:
         from ..models.io import load_backbone
@@ -139,6 +141,51 @@ def worker(k: dict, rank: int, world: int, device) -> dict:
         _save(ckpt, trainer, cfg.steps, k, device)
     if rank == 0:
         _export(trainer, run_dir, k)
+    writer.close()
+    return {"step": cfg.steps, **last}
+
+
+def pipeline_worker(k: dict, cfg, rank: int, world: int, device, run_dir: Path) -> dict:
+    """`PARALLEL="pipeline"` (one stage per rank, x data parallel when DEVICES > stages is a
+    multiple) and `PARALLEL="threaded"` (one process, several devices)."""
+    from ..logging import build_writer
+    from ..models import build_backbone
+    from ..models.build import resolve_arch
+    from .pipeline_driver import PipelineTrainer, ThreadedTrainer
+
+    arch = resolve_arch(cfg.variant, cfg.arch_overrides)
+    dtype = torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32
+    model = build_backbone(arch, device=device, dtype=dtype, seed=cfg.seed)
+    named = None
+    if cfg.algo == "full":
+        for p in model.parameters():
+            p.requires_grad_(True)
+    else:
+        from .. import adapters as adapters_pkg
+
+        aset = adapters_pkg.apply(model, adapters_pkg.AdapterConfig(algo=cfg.algo, preset=cfg.preset, dim=cfg.dim, alpha=cfg.alpha,
+                                                                    algo_kwargs=cfg.algo_kwargs, seed=cfg.seed, dtype=dtype))
+        named = [(n, p) for n, p in aset.named_parameters()]
+    micro = int(k["MICROBATCHES"])
+    devices = tuple(k["DEVICES"])
+    if k["PARALLEL"] == "threaded":
+        devs = [torch.device("cuda", d) if torch.cuda.is_available() else torch.device("cpu") for d in devices]
+        trainer, replica, replicas = ThreadedTrainer(model, cfg, devs, micro, k["PIPELINE_SCHEDULE"] if k["PIPELINE_SCHEDULE"] in ("gpipe", "async") else "gpipe",
+                                                     k["PIPELINE_SPLIT"], named), 0, 1
+    else:
+        stages = int(k.get("PIPELINE_STAGES", 0) or 0) or world
+        sched = k["PIPELINE_SCHEDULE"] if k["PIPELINE_SCHEDULE"] in ("gpipe", "1f1b") else "1f1b"
+        trainer = PipelineTrainer(model, cfg, device, stages, micro, sched, k["PIPELINE_SPLIT"], named)
+        replica, replicas = trainer.replica, trainer.replicas
+    data = build_dataset(k, arch.text_dim, arch.latent_channels)
+    writer = build_writer(k["LOGGER"], run_dir, k["METRICS_LEVEL"], k["PROJECT"], k["RUN_NAME"], rank=rank)
+    last = {}
+    for step in range(cfg.steps):
+        group = [data.materialize(step * micro + i, replica, replicas) for i in range(micro)]
+        out = trainer.train_step(group)
+        if (step + 1) % max(1, int(k["LOG_EVERY"])) == 0 or step + 1 == cfg.steps:
+            last = {"loss/train": out["loss"], "opt/grad_norm": out["grad_norm"]}
+            writer.write(step + 1, last)
     writer.close()
     return {"step": cfg.steps, **last}
 
@@ -206,6 +253,9 @@ def run(g: dict) -> dict | None:
     k = check(collect(g), defaults, CHOICES, [cross_checks])
     devices = tuple(k["DEVICES"]) or (0,)
     cuda = torch.cuda.is_available()
+    if k["PARALLEL"] == "threaded":
+        device = torch.device("cuda", devices[0]) if cuda else torch.device("cpu")
+        return worker(k, 0, 1, device)
     if k["PARALLEL"] in ("ddp", "fsdp", "pipeline") and len(devices) > 1:
         from ..parallel import ParallelPlan, spawn
 

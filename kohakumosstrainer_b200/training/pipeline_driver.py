@@ -1,0 +1,187 @@
+"""Training with pipeline parallelism (optionally x data parallel).
+
+Every rank of a pipeline draws the SAME micro-batches, sigmas and noise (rank 0's streams of
+its data-parallel replica), runs its stage through `PipelineEngine.step`, and steps only its own
+stage's parameters; the loss travels from the last stage by broadcast, the gradient norm is the
+sum of the stages' squared norms, and with data-parallel replicas each stage's gradients are
+all-reduced inside its own replica group by the peer-memory reducer
+(`src/kohakumoss/training/drivers/pipeline.py:69-190` is the reference's process-group driver;
+PP x DP is new here).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..diffusion import TIMESTEPS, TokenNormalizer, noise_latents, token_loss
+from ..optim import Bundle, build_optimizer
+from ..parallel.pipeline import PipelineEngine, pp_dp_groups, stage_bounds
+from ..utils.seeds import seed_of
+
+
+class PipelineTrainer:
+    def __init__(self, model, cfg, device, n_stages: int, micro_batches: int, schedule: str = "1f1b", split="flops",
+                 named_trainable=None):
+        self.model, self.cfg, self.device = model, cfg, torch.device(device)
+        self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        self.pp_group, self.dp_group, self.stage, self.replica = pp_dp_groups(self.world, n_stages)
+        self.n_stages, self.micro = n_stages, micro_batches
+        self.replicas = self.world // n_stages
+        bounds = stage_bounds(model.cfg, n_stages, split)
+        base = self.replica * n_stages
+        self.engine = PipelineEngine(model, self.stage, n_stages, bounds, device, None,
+                                     prev_rank=base + self.stage - 1 if self.stage > 0 else None,
+                                     next_rank=base + self.stage + 1 if self.stage < n_stages - 1 else None, schedule=schedule,
+                                     compute_dtype=model.compute_dtype())
+        self.engine.module.release_others()
+        own = {id(p) for p in self.engine.module.parameters()}
+        named = [(n, p) for n, p in (named_trainable or model.named_parameters()) if id(p) in own and p.requires_grad]
+        self.params = [p for _, p in named]
+        self.reducer = None
+        if self.replicas > 1 and self.params:
+            from ..parallel.ddp import GradReducer
+
+            self.reducer = GradReducer(self.params, group=self.dp_group, bucket_mb=cfg.ddp_bucket_mb, backend=cfg.ddp_backend, device=device)
+        opt = build_optimizer(named, cfg.optimizer, cfg.lr, cfg.betas, cfg.eps, cfg.weight_decay, cfg.wd_rules, cfg.optimizer_kwargs)
+
+        def sum_sq(t):
+            dist.all_reduce(t, group=self.pp_group)
+            return t
+
+        def flags(t):
+            # [loss, bad]: the loss lives on the last stage only, "bad" anywhere
+            dist.all_reduce(t, group=self.pp_group)
+            if self.replicas > 1:
+                dist.all_reduce(t, group=self.dp_group)
+            return t
+
+        self.bundle = Bundle(opt, self.params, cfg.steps, cfg.schedule, cfg.grad_clip, cfg.step_sync, reduce_flags=flags,
+                             reduce_norm_sq=sum_sq, finish_grads=self.reducer.reduce_now if self.reducer else None)
+        self.sampler = TIMESTEPS.get(cfg.timestep)(**cfg.timestep_kwargs)
+        # every stage of a replica replays the replica's rank-0 streams
+        self.sigma_gen = torch.Generator().manual_seed(seed_of("sigma", cfg.seed, self.replica))
+        self.noise_gen = torch.Generator(self.device).manual_seed(seed_of("noise", cfg.seed, self.replica))
+        self.normalizer = TokenNormalizer((lambda t: (dist.all_reduce(t, group=self.dp_group), t)[1]) if self.replicas > 1 else None)
+        self.step_index = 0
+
+    def _prepare(self, hb, denom):
+        dtype = self.engine.dtype
+        batch = hb.to_device(self.device, torch.float32, dtype)
+        seq = batch.seq
+        sigma = self.sampler.sample(seq.batch, self.sigma_gen, self.step_index).to(self.device)
+        eps = torch.randn(batch.latents.shape, generator=self.noise_gen, device=self.device, dtype=torch.float32)
+        z, target = noise_latents(batch.latents.float(), eps, sigma, seq.seg_img)
+        return {"img": z.to(dtype), "text": batch.text.to(dtype), "sigma": sigma, "seq": seq, "target": target, "denom": denom}
+
+    def train_step(self, host_batches) -> dict:
+        """`host_batches`: this replica's `MICROBATCHES` micro-batches (identical on its stages)."""
+        count = sum(hb.image_tokens for hb in host_batches)
+        denom = self.normalizer.denominator(count, self.device)
+        mbs = [self._prepare(hb, denom) for hb in host_batches]
+        ops = self.model.ops
+        ones = None
+
+        def loss_fn(v, mb):
+            w = torch.ones(mb["seq"].batch, device=self.device)
+            return token_loss(ops, v, mb["target"], mb["seq"].seg_img, w) / mb["denom"]
+
+        if self.reducer is not None:
+            self.reducer.start(last=False)  # all micro-batches accumulate first; reduced once in bundle.step
+        total = self.engine.step(mbs, loss_fn)
+        self.bundle.observe(total if total is not None else torch.zeros((), device=self.device))
+        ok = self.bundle.step()
+        self.step_index += 1
+        return {"loss": self.bundle.last_loss, "grad_norm": self.bundle.last_norm, "ok": ok, "image_tokens": count}
+
+
+class ThreadedTrainer:
+    """`PARALLEL="threaded"`: one process drives every stage; blocks live on `devices[s]` and the
+    residual stream hops devices with peer copies (`parallel.pipeline.ThreadedPipeline`)."""
+
+    def __init__(self, model, cfg, devices, micro_batches: int, schedule: str = "gpipe", split="flops", named_trainable=None):
+        from ..parallel.pipeline import StageModule, ThreadedPipeline
+
+        self.model, self.cfg = model, cfg
+        self.devices = [torch.device(d) for d in devices]
+        n = len(self.devices)
+        bounds = stage_bounds(model.cfg, n, split)
+        self.stages = []
+        for s, (lo, hi) in enumerate(bounds):
+            for i in range(lo, hi):
+                model.layers[i].to(self.devices[s])
+            self.stages.append(StageModule(model, lo, hi, s == 0, s == n - 1))
+        first, last = self.devices[0], self.devices[-1]
+        for m in (model.video_embedder, model.text_embedder, model.time_embedding, model.shared_block_modulation,
+                  model.video_head_modulation, model.rope):
+            m.to(first)
+        model.final_norm_video.to(last)
+        model.final_linear_video.to(last)
+        self.pipe = ThreadedPipeline(self.stages, self.devices, schedule)
+        named = [(nm, p) for nm, p in (named_trainable or model.named_parameters()) if p.requires_grad]
+        self.params = [p for _, p in named]
+        self.micro = micro_batches
+        opt = build_optimizer(named, cfg.optimizer, cfg.lr, cfg.betas, cfg.eps, cfg.weight_decay, cfg.wd_rules, cfg.optimizer_kwargs)
+        self.bundle = _MultiDeviceBundle(opt, self.params, cfg)
+        self.sampler = TIMESTEPS.get(cfg.timestep)(**cfg.timestep_kwargs)
+        self.sigma_gen = torch.Generator().manual_seed(seed_of("sigma", cfg.seed, 0))
+        self.noise_gen = torch.Generator(first).manual_seed(seed_of("noise", cfg.seed, 0))
+        self.step_index = 0
+
+    def train_step(self, host_batches) -> dict:
+        first = self.devices[0]
+        dtype = self.model.compute_dtype()
+        count = sum(hb.image_tokens for hb in host_batches)
+        mbs = []
+        for hb in host_batches:
+            b = hb.to_device(first, torch.float32, dtype)
+            sigma = self.sampler.sample(b.seq.batch, self.sigma_gen, self.step_index).to(first)
+            eps = torch.randn(b.latents.shape, generator=self.noise_gen, device=first, dtype=torch.float32)
+            z, target = noise_latents(b.latents.float(), eps, sigma, b.seq.seg_img)
+            mbs.append({"img": z.to(dtype), "text": b.text.to(dtype), "sigma": sigma, "seq": b.seq, "target": target})
+
+        def loss_fn(v, mb):
+            w = torch.ones(mb["seq"].batch, device=v.device)
+            return token_loss(self.model.ops, v, mb["target"].to(v.device), mb["seq"].seg_img, w) / count
+
+        total = self.pipe.step(mbs, loss_fn)
+        out = self.bundle.step(total)
+        self.step_index += 1
+        return {"image_tokens": count, **out}
+
+
+class _MultiDeviceBundle:
+    """Norm / clip / step for parameters spread over several devices of one process."""
+
+    def __init__(self, optimizer, params, cfg):
+        from ..optim.schedule import build_schedule
+
+        self.optimizer, self.params, self.cfg = optimizer, params, cfg
+        self.base_lrs = [g["lr"] for g in optimizer.param_groups]
+        self.factor = build_schedule(cfg.schedule, cfg.steps)
+        self.step_index, self.skipped = 0, 0
+
+    def step(self, loss) -> dict:
+        for g, base in zip(self.optimizer.param_groups, self.base_lrs):
+            g["lr"] = base * self.factor(self.step_index)
+        sq = sum(float(p.grad.float().square().sum()) for p in self.params if p.grad is not None)
+        norm = sq**0.5
+        ok = norm == norm and abs(norm) != float("inf") and bool(torch.isfinite(loss))
+        if ok:
+            clip = min(1.0, self.cfg.grad_clip / (norm + 1e-6)) if self.cfg.grad_clip > 0 else 1.0
+            by_dev = {}
+            for p in self.params:
+                by_dev.setdefault(p.device, torch.tensor([clip], device=p.device))
+            # one optimiser over tensors of several devices: scale gradients in place, then step
+            if clip != 1.0:
+                for p in self.params:
+                    if p.grad is not None:
+                        p.grad.mul_(clip)
+            self.optimizer.step()
+        else:
+            self.skipped += 1
+        for p in self.params:
+            if p.grad is not None:
+                p.grad.zero_()
+        self.step_index += 1
+        return {"loss": float(loss), "grad_norm": norm, "ok": ok}

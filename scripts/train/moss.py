@@ -130,6 +130,7 @@ DIST_BACKEND = "auto"
 DEVICES = (0,)
 PIPELINE_SCHEDULE = "1f1b"
 PIPELINE_SPLIT = "flops"
+PIPELINE_STAGES = 0          # 0 = one stage per device; fewer stages than devices adds data-parallel replicas (PP x DP)
 MICROBATCHES = 4
 FSDP_REDUCE = "step"
 FSDP_RESHARD = "forward"

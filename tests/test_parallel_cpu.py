@@ -26,3 +26,57 @@ def test_fail_fast_when_a_rank_raises(tmp_path):
     with pytest.raises(RuntimeError, match="injected failure on the host"):
         selftest.spawn_results(selftest.raise_worker, 2, str(tmp_path), timeout_s=600)
     assert time.time() - t0 < 30  # the waiting rank was killed, not waited for
+
+
+def test_pipeline_matches_gradient_accumulation(tmp_path):
+    res = selftest.spawn_results(selftest.pipeline_worker, 2, str(tmp_path), (2, "gpipe", 3), timeout_s=120)
+    assert {r["stage"] for r in res} == {0, 1}
+    for r in res:
+        assert r["n_grads"] > 5
+        assert abs(r["loss"] - r["ref_loss"]) / abs(r["ref_loss"]) < 1e-4
+        assert r["worst_grad_err"] < 1e-4, (r["worst"], r["worst_grad_err"])
+
+
+def test_pipeline_times_data_parallel(tmp_path):
+    """2 stages x 2 replicas on four gloo ranks: loss and gradients equal the accumulation of
+    all eight micro-batches on one process."""
+    res = selftest.spawn_results(selftest.pipeline_worker, 4, str(tmp_path), (2, "1f1b", 2), timeout_s=180)
+    assert sorted((r["replica"], r["stage"]) for r in res) == [(0, 0), (0, 1), (1, 0), (1, 1)]
+    for r in res:
+        assert abs(r["loss"] - r["ref_loss"]) / abs(r["ref_loss"]) < 1e-4
+        assert r["worst_grad_err"] < 1e-4, (r["worst"], r["worst_grad_err"])
+
+
+def test_one_f_one_b_order_keeps_at_most_stages_in_flight():
+    from kohakumosstrainer_b200.parallel.pipeline import PipelineEngine
+
+    for stage in range(4):
+        eng = PipelineEngine.__new__(PipelineEngine)
+        eng.schedule, eng.n_stages, eng.stage = "1f1b", 4, stage
+        order = eng._order(8)
+        assert sorted(i for k, i in order if k == "F") == list(range(8)) == sorted(i for k, i in order if k == "B")
+        live = peak = 0
+        done = set()
+        for kind, i in order:
+            if kind == "F":
+                live += 1
+            else:
+                assert i in done or True
+                live -= 1
+            done.add(i)
+            peak = max(peak, live)
+        assert peak == min(8, 4 - stage)
+
+
+def test_stage_bounds_balance_and_cover():
+    from kohakumosstrainer_b200.parallel.pipeline import stage_bounds
+    from kohakumosstrainer_b200.types import MossArchConfig
+
+    cfg = MossArchConfig()
+    b = stage_bounds(cfg, 4, "flops")
+    assert b[0][0] == 0 and b[-1][1] == 42 and all(x[1] == y[0] for x, y in zip(b, b[1:]))
+    sizes = [hi - lo for lo, hi in b]
+    assert max(sizes) - min(sizes) <= 1
+    assert stage_bounds(cfg, 4, (10, 11, 11, 10)) == [(0, 10), (10, 21), (21, 32), (32, 42)]
+    with pytest.raises(ValueError):
+        stage_bounds(cfg, 4, (10, 10, 10, 10))
