@@ -61,8 +61,8 @@ def build_dataset(k: dict, text_dim: int, channels: int):
     spec = (k["DATASETS"] or [{"type": "synthetic"}])[0]
     if spec.get("type", "synthetic") == "synthetic":
         opts = {kk: vv for kk, vv in spec.items() if kk != "type"}
-        cfg = SyntheticConfig(max_tokens=int(k["MAX_TOKENS"]), text_dim=text_dim, channels=channels, seed=int(k["SEED"]),
-                              size_step=max(16, int(k["SIZE_STEP"])), **opts)
+        opts.setdefault("size_step", max(16, int(k["SIZE_STEP"])))
+        cfg = SyntheticConfig(max_tokens=int(k["MAX_TOKENS"]), text_dim=text_dim, channels=channels, seed=int(k["SEED"]), **opts)
         return SyntheticDataset(cfg)
     from ..data.dataset import build_dataset as build_real
 
