@@ -1,0 +1,377 @@
+"""Epoch planning: which rows, at what size, in which batch.
+
+Everything is a pure function of (seed, catalog): epoch e's row multiset and order, each
+occurrence's crop / flip / caption variant, the over-long fit, and the batches. Global batch
+g of rank r at index i is `i * world + r` (round robin), or with `balance` the rank's share of
+a cost-balanced step block. Semantics follow the reference planner base and batching
+functions (`src/kohakumoss_data/resolution/base.py:60-251`, `resolution/batching.py:23-72`,
+`resolution/overlong.py:8-27`, `bucket.py`, `square.py`, `resize.py`).
+
+Design: an epoch is planned on arrays, not objects. Targets are an int64 `[N, 2]` table built
+once (vectorised fit), per-occurrence token counts come from array lookups, greedy batching
+is one cumulative-sum sweep, and an epoch's batches are kept as a CSR pair (`order`, `starts`)
+of occurrence indices. `PlanItem`s (with their seeded crop / flip / variant draws) are only
+built for the batch being materialised.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, replace
+
+import numpy as np
+
+from ..utils.registry import Registry
+from ..utils.seeds import seed_of
+from .geometry import Geometry, nearest_bucket_many
+
+PLANNERS = Registry("resolution planner")
+BATCHINGS = ("tokens", "tokens_ffd", "count")
+OVERLONG = ("drop", "truncate_text", "drop_tokens")
+EPOCH_CACHE = 5
+
+
+def rng_of(tag: str, *counters: int) -> np.random.Generator:
+    return np.random.Generator(np.random.PCG64(seed_of(tag, *counters)))
+
+
+@dataclass(frozen=True)
+class PlanItem:
+    """One sample of a planned batch (`src/kohakumoss_data/types.py:38-52`)."""
+
+    row_id: int
+    target_hw: tuple[int, int]
+    crop_ltrb: tuple[int, int, int, int]
+    flip: bool = False
+    caption_variant: int = 0
+    text_limit: int = 0      # > 0: keep the first text tokens
+    img_keep: int = 0        # > 0: keep this many image tokens, drawn by keep_seed
+    keep_seed: int = 0
+
+
+@dataclass
+class BatchPlan:
+    index: int
+    items: list[PlanItem]
+    token_budget: int = 0
+
+
+def keep_indices(item: PlanItem, n_tokens: int) -> np.ndarray | None:
+    """Sorted indices of the image tokens a `drop_tokens` fit keeps (None: all)."""
+    if not item.img_keep:
+        return None
+    picked = np.random.Generator(np.random.PCG64(item.keep_seed)).choice(n_tokens, size=item.img_keep, replace=False)
+    return np.sort(picked.astype(np.int64))
+
+
+def epoch_order(weights: np.ndarray, seed: int, epoch: int) -> np.ndarray:
+    """Row ids of one epoch: row i appears floor(w_i) times plus once more with probability
+    frac(w_i); the multiset is then permuted."""
+    rng = rng_of("epoch-order", seed, epoch)
+    w = np.asarray(weights, dtype=np.float32)
+    whole = np.floor(w)
+    extra = rng.random(len(w), dtype=np.float32) < (w - whole)
+    ids = np.repeat(np.arange(len(w), dtype=np.int64), whole.astype(np.int64) + extra)
+    return ids[rng.permutation(len(ids))]
+
+
+# ---- batching on arrays: each returns `starts` into a permutation `order` of 0..n-1 ----------
+def batch_greedy(tokens: np.ndarray, max_tokens: int, cap: int) -> tuple[np.ndarray, np.ndarray]:
+    n = len(tokens)
+    starts, used, count = [0], 0, 0
+    for i, t in enumerate(tokens.tolist()):
+        if count and (used + t > max_tokens or count >= cap):
+            starts.append(i)
+            used, count = 0, 0
+        used += t
+        count += 1
+    starts.append(n)
+    return np.arange(n, dtype=np.int64), np.asarray(starts if n else [0], dtype=np.int64)
+
+
+def batch_ffd(tokens: np.ndarray, max_tokens: int, cap: int, window: int) -> tuple[np.ndarray, np.ndarray]:
+    """First-fit-decreasing inside windows of `window` consecutive occurrences."""
+    order, starts = [], [0]
+    for lo in range(0, len(tokens), window):
+        t = tokens[lo : lo + window]
+        idx = np.lexsort((np.arange(len(t)), -t))
+        bins: list[list[int]] = []
+        room: list[int] = []
+        for j in idx.tolist():
+            tj = int(t[j])
+            for b, free in enumerate(room):
+                if tj <= free and len(bins[b]) < cap:
+                    bins[b].append(lo + j)
+                    room[b] -= tj
+                    break
+            else:
+                bins.append([lo + j])
+                room.append(max_tokens - tj)
+        for b in bins:
+            order.extend(b)
+            starts.append(len(order))
+    return np.asarray(order, dtype=np.int64), np.asarray(starts, dtype=np.int64)
+
+
+def batch_count(n: int, batch_size: int, drop_last: bool) -> tuple[np.ndarray, np.ndarray]:
+    full = n // batch_size * batch_size
+    stop = full if drop_last else n
+    starts = list(range(0, stop, batch_size)) + [stop]
+    return np.arange(stop, dtype=np.int64), np.asarray(starts if stop else [0], dtype=np.int64)
+
+
+class _Epoch:
+    """Batches of one epoch: occurrence arrays + CSR batch table."""
+
+    __slots__ = ("rows", "pos", "text_limit", "img_keep", "tokens", "order", "starts", "dropped")
+
+    def __len__(self) -> int:
+        return max(0, len(self.starts) - 1)
+
+    def members(self, b: int) -> np.ndarray:
+        return self.order[self.starts[b] : self.starts[b + 1]]
+
+
+class Planner:
+    """`target_table()` is the only thing a planner kind defines (plus optional grouping)."""
+
+    grouped = False
+
+    def __init__(self, catalog, geometry: Geometry, seed: int = 0, flip: bool = False, caption_variants: int = 1, text_len=None,
+                 batching: str = "tokens", overlong: str = "drop", max_tokens: int = 16384, batch_size: int = 4, window: int = 256,
+                 max_samples: int = 0, drop_last: bool = True, balance: int = 0, attn_tokens: int = 18432):
+        if batching not in BATCHINGS:
+            raise ValueError(f"batching must be one of {sorted(BATCHINGS)}")
+        if overlong not in OVERLONG:
+            raise ValueError(f"overlong must be one of {sorted(OVERLONG)}")
+        self.catalog, self.geometry, self.seed, self.flip = catalog, geometry, seed, flip
+        self.caption_variants = max(1, caption_variants)
+        self.text_len = text_len
+        self.batching, self.overlong = batching, overlong
+        self.max_tokens, self.batch_size, self.window = max_tokens, batch_size, window
+        self.max_samples, self.drop_last = max_samples, drop_last
+        self.balance, self.attn_tokens = balance, attn_tokens
+        self.targets = self.target_table()
+        self.image_tokens = geometry.tokens_many(self.targets)
+        self._epochs: dict[int, _Epoch] = {}
+        self._counts: list[int] = []
+        self._blocks: dict = {}
+        self.drops: dict[int, int] = {}
+        self.unbatched: dict[int, int] = {}
+
+    def __getstate__(self):
+        s = dict(self.__dict__)
+        s["_epochs"], s["_counts"], s["_blocks"] = {}, [], {}
+        return s
+
+    # -- per kind -------------------------------------------------------------------------------
+    def target_table(self) -> np.ndarray:
+        raise NotImplementedError
+
+    # -- occurrences ----------------------------------------------------------------------------
+    def variant_of(self, epoch: int, pos: int, row_id: int) -> int:
+        return int(self._item_rng(epoch, pos, row_id, skip=True))
+
+    def _item_rng(self, epoch: int, pos: int, row_id: int, skip: bool = False):
+        """The occurrence's draws in a fixed order: crop box (random crop only), flip (flip
+        only), caption variant."""
+        rng = rng_of("item", self.seed, epoch, pos, row_id)
+        w, h = int(self.catalog.w[row_id]), int(self.catalog.h[row_id])
+        target = (int(self.targets[row_id, 0]), int(self.targets[row_id, 1]))
+        box = self.geometry.box(w, h, target, rng)
+        flip = bool(rng.random() < 0.5) if self.flip else False
+        variant = int(rng.integers(self.caption_variants))
+        return variant if skip else (target, box, flip, variant)
+
+    def _text_tokens(self, rows: np.ndarray, epoch: int, positions: np.ndarray) -> np.ndarray:
+        if self.text_len is None:
+            return np.zeros(len(rows), dtype=np.int64)
+        vec = getattr(self.text_len, "many", None)
+        if vec is not None:  # column estimate: no per-variant rendering needed
+            return vec(rows)
+        return np.array([self.text_len(int(r), self.variant_of(epoch, int(p), int(r))) for r, p in zip(rows, positions)], dtype=np.int64)
+
+    def _plan_epoch(self, e: int) -> _Epoch:
+        weights = np.where(np.asarray(self.catalog.live, dtype=bool), self.catalog.weight, 0.0)
+        rows = epoch_order(weights, self.seed, e)
+        pos = np.arange(len(rows), dtype=np.int64)
+        img = self.image_tokens[rows].astype(np.int64)
+        text = self._text_tokens(rows, e, pos)
+        text_limit = np.zeros(len(rows), dtype=np.int64)
+        img_keep = np.zeros(len(rows), dtype=np.int64)
+        over = img + text > self.max_tokens
+        keep = np.ones(len(rows), dtype=bool)
+        if over.any():
+            if self.overlong == "drop":
+                keep &= ~over
+            elif self.overlong == "truncate_text":
+                limit = self.max_tokens - img
+                keep &= ~(over & (limit < 1))
+                text_limit = np.where(over, limit, 0)
+                text = np.where(over, np.minimum(text, limit), text)
+            else:
+                room = self.max_tokens - text
+                keep &= ~(over & (room < 1))
+                img_keep = np.where(over, room, 0)
+                img = np.where(over, room, img)
+        ep = _Epoch()
+        ep.dropped = int((~keep).sum())
+        ep.rows, ep.pos = rows[keep], pos[keep]
+        ep.text_limit, ep.img_keep = text_limit[keep], img_keep[keep]
+        ep.tokens = (img + text)[keep]
+        n = len(ep.rows)
+        cap = self.max_samples or n + 1
+        streams = self._streams(ep)
+        orders, starts, base = [], [np.zeros(1, dtype=np.int64)], 0
+        for members in streams:
+            t = ep.tokens[members]
+            if self.batching == "tokens":
+                o, s = batch_greedy(t, self.max_tokens, cap)
+            elif self.batching == "tokens_ffd":
+                o, s = batch_ffd(t, self.max_tokens, cap, self.window)
+            else:
+                o, s = batch_count(len(t), self.batch_size, self.drop_last)
+            orders.append(members[o])
+            starts.append(s[1:] + base)
+            base += len(o)
+        ep.order = np.concatenate(orders) if orders else np.zeros(0, dtype=np.int64)
+        ep.starts = np.concatenate(starts)
+        if self.grouped or self.batching == "tokens_ffd":
+            perm = rng_of("batch-order", self.seed, e).permutation(len(ep))
+            sizes = np.diff(ep.starts)[perm]
+            ep.order = np.concatenate([ep.members(int(b)) for b in perm]) if len(perm) else ep.order
+            ep.starts = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+        self.drops[e] = ep.dropped
+        self.unbatched[e] = n - len(ep.order)
+        return ep
+
+    def _streams(self, ep: _Epoch) -> list[np.ndarray]:
+        return [np.arange(len(ep.rows), dtype=np.int64)]
+
+    # -- lookup ---------------------------------------------------------------------------------
+    def epoch(self, e: int) -> _Epoch:
+        if e not in self._epochs:
+            if len(self._epochs) >= EPOCH_CACHE:
+                self._epochs.pop(min(self._epochs))
+            self._epochs[e] = self._plan_epoch(e)
+        return self._epochs[e]
+
+    def epoch_length(self, e: int = 0) -> int:
+        while len(self._counts) <= e:
+            self._counts.append(len(self.epoch(len(self._counts))))
+        return self._counts[e]
+
+    def locate(self, g: int) -> tuple[int, int]:
+        e = 0
+        while True:
+            n = self.epoch_length(e)
+            if n == 0:
+                raise ValueError("planner produced an empty epoch")
+            if g < n:
+                return e, g
+            g -= n
+            e += 1
+
+    def batch_items(self, g: int) -> list[PlanItem]:
+        e, b = self.locate(g)
+        ep = self.epoch(e)
+        items = []
+        for k in ep.members(b).tolist():
+            row, pos = int(ep.rows[k]), int(ep.pos[k])
+            target, box, flip, variant = self._item_rng(e, pos, row)
+            keep = int(ep.img_keep[k])
+            items.append(PlanItem(row, target, box, flip, variant, int(ep.text_limit[k]), keep,
+                                  seed_of("img-keep", self.seed, e, pos, row) if keep else 0))
+        return items
+
+    def batch_tokens(self, g: int) -> np.ndarray:
+        e, b = self.locate(g)
+        ep = self.epoch(e)
+        return ep.tokens[ep.members(b)]
+
+    def cost(self, g: int) -> float:
+        """Estimated compute of a batch: per sample L + L^2 / attn_tokens."""
+        t = self.batch_tokens(g).astype(np.float64)
+        return float((t + t * t / self.attn_tokens).sum())
+
+    def balanced(self, block: int, world: int) -> list[list[int]]:
+        """Step block `block`'s `world * balance` batches dealt longest-cost first to the rank
+        with the least cost so far, `balance` batches per rank, each rank's ids ascending."""
+        key = (block, world)
+        if key not in self._blocks:
+            if len(self._blocks) >= 4 * EPOCH_CACHE:
+                self._blocks.pop(min(self._blocks))
+            per = self.balance
+            ids = range(block * world * per, (block + 1) * world * per)
+            loads = [0.0] * world
+            dealt: list[list[int]] = [[] for _ in range(world)]
+            for c, g in sorted(((self.cost(g), g) for g in ids), reverse=True):
+                r = min((r for r in range(world) if len(dealt[r]) < per), key=loads.__getitem__)
+                loads[r] += c
+                dealt[r].append(g)
+            self._blocks[key] = [sorted(d) for d in dealt]
+        return self._blocks[key]
+
+    def global_batch(self, index: int, rank: int, world: int) -> int:
+        if self.balance <= 1 or world <= 1:
+            return index * world + rank
+        block, slot = divmod(index, self.balance)
+        return self.balanced(block, world)[rank][slot]
+
+    def plan(self, index: int, rank: int = 0, world: int = 1) -> BatchPlan:
+        g = self.global_batch(index, rank, world)
+        return BatchPlan(index, self.batch_items(g), int(self.batch_tokens(g).sum()))
+
+
+@PLANNERS.register("resize")
+class ResizePlanner(Planner):
+    """Native aspect (clamped), area about `TARGET_AREA`; smaller images stay native under
+    `upscale="never"`."""
+
+    def target_table(self) -> np.ndarray:
+        return self.geometry.fit_many(self.catalog.w, self.catalog.h)
+
+
+@PLANNERS.register("bucket")
+class BucketPlanner(Planner):
+    """Nearest log-aspect bucket of about `area`; a row smaller than its bucket keeps its native
+    fit under `upscale="never"`. A batch never mixes sizes; batches are shuffled."""
+
+    grouped = True
+
+    def target_table(self) -> np.ndarray:
+        buckets = np.asarray(self.geometry.buckets(), dtype=np.int64)
+        w, h = np.asarray(self.catalog.w), np.asarray(self.catalog.h)
+        if len(w) == 0:
+            return np.zeros((0, 2), dtype=np.int64)
+        out = buckets[nearest_bucket_many(w, h, buckets)]
+        if self.geometry.upscale == "never":
+            small = w * h < out[:, 0] * out[:, 1]
+            if small.any():
+                out[small] = self.geometry.fit_many(w[small], h[small])
+        return out
+
+    def _streams(self, ep: _Epoch) -> list[np.ndarray]:
+        t = self.targets[ep.rows]
+        key = t[:, 0] * (1 << 20) + t[:, 1]
+        return [np.nonzero(key == k)[0] for k in np.unique(key)]
+
+
+@PLANNERS.register("square_crop")
+class SquareCropPlanner(Planner):
+    """sqrt(area)-sided squares from a centre crop."""
+
+    crop_mode = "center"
+
+    def __init__(self, catalog, geometry, **kw):
+        super().__init__(catalog, replace(geometry, crop=self.crop_mode), **kw)
+
+    def target_table(self) -> np.ndarray:
+        side = self.geometry.square()
+        return np.full((len(self.catalog), 2), side, dtype=np.int64)
+
+
+@PLANNERS.register("shifted_square")
+class ShiftedSquarePlanner(SquareCropPlanner):
+    """Square crops at a seeded random position."""
+
+    crop_mode = "random"

@@ -1,0 +1,540 @@
+"""Dataset sources: where images and their caption fields come from.
+
+Every source has `scan() -> list[Row]` (headers only: sizes are probed without decoding
+pixels) and `open(locator) -> bytes`. Kinds and options follow the reference sources
+(`src/kohakumoss_data/sources/{folder,kohya,jsonl,parquet,webdataset,moss_shard,gbc}.py`,
+sidecar rules in `sources/base.py:42-83`): `folder`, `kohya` (`<repeats>_<name>` folders, repeats
+become row weight), `jsonl` manifests, `parquet` tables (paths or embedded bytes),
+`webdataset` tars (members grouped by key, read by byte offset), `moss_shard` (this
+framework's packed image shards with their own catalog) and `gbc` (region-graph records next
+to images). Scans fan out over a thread pool: probing is I/O bound.
+"""
+
+from __future__ import annotations
+
+import glob
+import io
+import json
+import os
+import posixpath
+import re
+import struct
+import tarfile
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+
+from ..utils.registry import Registry
+from .captions import split_tags
+from .catalog import Catalog, Row
+from .store import content_hash
+
+SOURCES = Registry("data source")
+IMAGE_EXTS = (".jpg", ".jpeg", ".png", ".webp", ".bmp", ".jxl", ".avif")
+IMAGE_KEYS = ("image", "file", "file_name", "path", "filename")
+_ALPHA = {"RGBA", "LA", "PA", "RGBa", "La"}
+
+
+def is_image(name: str) -> bool:
+    return name.lower().endswith(IMAGE_EXTS)
+
+
+def probe_image(source) -> tuple[int, int, bool]:
+    """(w, h, has_alpha) after EXIF orientation, header only."""
+    from PIL import Image
+
+    stream = io.BytesIO(source) if isinstance(source, (bytes, bytearray, memoryview)) else source
+    with Image.open(stream) as img:
+        w, h = img.size
+        orientation = img.getexif().get(0x0112, 1)
+        alpha = img.mode in _ALPHA or (img.mode == "P" and "transparency" in img.info)
+    if orientation in (5, 6, 7, 8):
+        w, h = h, w
+    return w, h, alpha
+
+
+def file_stamp(path: str) -> str:
+    st = os.stat(path)
+    return f"stat:{os.path.normcase(os.path.abspath(path))}:{st.st_size}:{st.st_mtime_ns}"
+
+
+def _read_text(path: str) -> str | None:
+    if not os.path.exists(path):
+        return None
+    with open(path, encoding="utf-8", errors="replace") as f:
+        return f.read().strip()
+
+
+def apply_json(row: Row, meta: dict) -> None:
+    """Metadata dict onto row fields; unknown keys stay in `row.json`."""
+    meta = dict(meta)
+    tags = meta.pop("tags", None)
+    if tags is not None:
+        row.tags = split_tags(tags) if isinstance(tags, str) else list(tags)
+    for k in ("caption", "text", "caption_nl"):
+        if k in meta:
+            row.caption_nl = meta.pop(k)
+    for k in ("artist", "rating"):
+        if k in meta:
+            setattr(row, k, meta.pop(k))
+    if meta:
+        row.json = {**(row.json or {}), **meta}
+
+
+def apply_sidecars(row: Row, stem: str, txt_as: str) -> None:
+    txt = _read_text(stem + ".txt")
+    if txt is not None:
+        if txt_as == "tags":
+            row.tags = split_tags(txt)
+        elif txt_as == "nl":
+            row.caption_nl = txt
+        else:
+            raise ValueError(f"txt_as must be 'tags' or 'nl', got {txt_as}")
+    cap = _read_text(stem + ".caption")
+    if cap is not None:
+        row.caption_nl = cap
+    meta = _read_text(stem + ".json")
+    if meta is not None:
+        apply_json(row, json.loads(meta))
+
+
+def image_row(full: str, locator: str, group: str, hash_content: bool, txt_as: str | None = None, weight: float = 1.0, artist=None) -> Row:
+    w, h, alpha = probe_image(full)
+    row = Row(locator=locator, w=w, h=h, has_alpha=alpha, group=group, weight=weight)
+    if hash_content:
+        with open(full, "rb") as f:
+            row.extra["hash"] = content_hash(f.read())
+    else:
+        row.extra["hash"] = file_stamp(full)
+    if txt_as is not None:
+        apply_sidecars(row, os.path.splitext(full)[0], txt_as)
+    if artist and not row.artist:
+        row.artist = artist
+    return row
+
+
+def _probe_all(jobs: list[tuple], workers: int = 8) -> list[Row]:
+    """`image_row(*job)` for every job, in order, over a thread pool; unreadable files are skipped."""
+
+    def one(job):
+        try:
+            return image_row(*job)
+        except (OSError, ValueError):
+            return None
+
+    if workers <= 1 or len(jobs) < 32:
+        rows = [one(j) for j in jobs]
+    else:
+        with ThreadPoolExecutor(workers) as pool:
+            rows = list(pool.map(one, jobs, chunksize=16))
+    return [r for r in rows if r is not None]
+
+
+class _FileSource:
+    workers = 8
+
+    def open(self, locator: str) -> bytes:
+        with open(os.path.join(self.root, locator), "rb") as f:
+            return f.read()
+
+    @staticmethod
+    def problems(entry: dict) -> list[str]:
+        path = entry.get("path")
+        if not path:
+            return [f"dataset {entry.get('source')!r} needs a path"]
+        if "*" not in str(path) and not os.path.exists(path):
+            return [f"dataset path {path} does not exist"]
+        return []
+
+
+@SOURCES.register("folder")
+class FolderSource(_FileSource):
+    """Every image under `path` (recursive by default); sidecars `stem.txt|caption|json`."""
+
+    def __init__(self, path: str, recursive: bool = True, txt_as: str = "tags", hash_content: bool = False):
+        self.path = self.root = path
+        self.recursive, self.txt_as, self.hash_content = recursive, txt_as, hash_content
+
+    def scan(self) -> list[Row]:
+        jobs = []
+        for folder, dirs, files in os.walk(self.path):
+            dirs.sort()
+            if not self.recursive:
+                dirs.clear()
+            rel = os.path.relpath(folder, self.path).replace("\\", "/")
+            rel = "" if rel == "." else rel
+            for name in sorted(files):
+                if is_image(name):
+                    loc = f"{rel}/{name}" if rel else name
+                    jobs.append((os.path.join(folder, name), loc, rel, self.hash_content, self.txt_as))
+        return _probe_all(jobs, self.workers)
+
+
+_PREFIX = re.compile(r"^((?:\d+_)+)(.*)$")
+
+
+def parse_folder(name: str, mode: str) -> tuple[float, str]:
+    """(repeats, remainder) of a kohya folder name; `mode` first | product | ignore."""
+    m = _PREFIX.match(name)
+    if m is None:
+        return 1.0, name
+    nums = [int(p) for p in m.group(1).strip("_").split("_")]
+    if mode == "first":
+        return float(nums[0]), m.group(2)
+    if mode == "product":
+        return float(np.prod(nums)), m.group(2)
+    if mode == "ignore":
+        return 1.0, m.group(2)
+    raise ValueError(f"repeat_prefix must be first|product|ignore, got {mode}")
+
+
+def artist_of(folder_name: str, pattern: str | None) -> str | None:
+    if not pattern:
+        return None
+    if pattern == "name":
+        return folder_name
+    found = re.search(pattern, folder_name)
+    if found is None:
+        return None
+    return found.group(1) if found.groups() else found.group(0)
+
+
+@SOURCES.register("kohya")
+class KohyaSource(_FileSource):
+    """Images of the first-level subfolders `<repeats>_<name>` (and of `path` itself with
+    `include_root`, repeat 1)."""
+
+    def __init__(self, path: str, repeat_prefix: str = "first", artist_from_folder: str | None = None, txt_as: str = "tags",
+                 hash_content: bool = False, include_root: bool = False):
+        self.path = self.root = path
+        self.repeat_prefix, self.artist_from_folder = repeat_prefix, artist_from_folder
+        self.txt_as, self.hash_content, self.include_root = txt_as, hash_content, include_root
+
+    def scan(self) -> list[Row]:
+        jobs = []
+        names = sorted(os.listdir(self.path))
+        if self.include_root:
+            for f in names:
+                if is_image(f) and os.path.isfile(os.path.join(self.path, f)):
+                    jobs.append((os.path.join(self.path, f), f, "", self.hash_content, self.txt_as, 1.0, None))
+        for d in names:
+            full = os.path.join(self.path, d)
+            if not os.path.isdir(full):
+                continue
+            repeats, rest = parse_folder(d, self.repeat_prefix)
+            artist = artist_of(rest, self.artist_from_folder)
+            for f in sorted(os.listdir(full)):
+                if is_image(f) and os.path.isfile(os.path.join(full, f)):
+                    jobs.append((os.path.join(full, f), f"{d}/{f}", d, self.hash_content, self.txt_as, repeats, artist))
+        return _probe_all(jobs, self.workers)
+
+
+@SOURCES.register("jsonl")
+class JsonlSource(_FileSource):
+    """One JSON object per line: an image key (`image|file|file_name|path|filename`) relative
+    to `root`, optional `weight`, `group`, and caption fields."""
+
+    def __init__(self, path: str, root: str | None = None, hash_content: bool = False):
+        self.path = path
+        self.root = root or os.path.dirname(os.path.abspath(path))
+        self.hash_content = hash_content
+
+    def scan(self) -> list[Row]:
+        rows = []
+        with open(self.path, encoding="utf-8") as f:
+            for no, line in enumerate(f):
+                line = line.strip()
+                if not line:
+                    continue
+                meta = json.loads(line)
+                key = next((k for k in IMAGE_KEYS if k in meta), None)
+                if key is None:
+                    raise ValueError(f"{self.path}:{no + 1}: no image key")
+                loc = str(meta.pop(key)).replace("\\", "/")
+                weight, group = float(meta.pop("weight", 1.0)), str(meta.pop("group", ""))
+                if "width" in meta and "height" in meta:
+                    row = Row(locator=loc, w=int(meta.pop("width")), h=int(meta.pop("height")), group=group, weight=weight)
+                    row.extra["hash"] = f"{loc}:{row.w}x{row.h}"
+                else:
+                    row = image_row(os.path.join(self.root, loc), loc, group, self.hash_content, None, weight)
+                apply_json(row, meta)
+                rows.append(row)
+        return rows
+
+
+@SOURCES.register("parquet")
+class ParquetSource(_FileSource):
+    """A parquet table: `image_col` holds paths relative to `root`, or `bytes_col` embedded
+    image bytes (locator `row:<i>`); other columns map like a jsonl line."""
+
+    def __init__(self, path: str, image_col: str | None = "image", bytes_col: str | None = None, root: str | None = None, hash_content: bool = False):
+        if not (image_col or bytes_col):
+            raise ValueError("the parquet source needs image_col or bytes_col")
+        self.path, self.image_col, self.bytes_col = path, image_col, bytes_col
+        self.root = root or os.path.dirname(os.path.abspath(path))
+        self.hash_content = hash_content
+        self._table = None
+
+    def __getstate__(self):
+        return {**self.__dict__, "_table": None}
+
+    def _load(self):
+        if self._table is None:
+            import pyarrow.parquet as pq
+
+            self._table = pq.read_table(self.path)
+        return self._table
+
+    def scan(self) -> list[Row]:
+        table = self._load()
+        cols = table.column_names
+        records = table.to_pylist()
+        rows = []
+        for i, meta in enumerate(records):
+            meta = {k: v for k, v in meta.items() if v is not None}
+            weight, group = float(meta.pop("weight", 1.0)), str(meta.pop("group", ""))
+            if self.bytes_col and self.bytes_col in cols:
+                data = meta.pop(self.bytes_col)
+                data = data["bytes"] if isinstance(data, dict) else data
+                w, h, alpha = probe_image(bytes(data))
+                row = Row(locator=f"row:{i}", w=w, h=h, has_alpha=alpha, group=group, weight=weight)
+                row.extra["hash"] = content_hash(bytes(data))
+                meta.pop(self.image_col, None)
+            else:
+                loc = str(meta.pop(self.image_col)).replace("\\", "/")
+                row = image_row(os.path.join(self.root, loc), loc, group, self.hash_content, None, weight)
+            apply_json(row, meta)
+            rows.append(row)
+        return rows
+
+    def open(self, locator: str) -> bytes:
+        if locator.startswith("row:"):
+            data = self._load().column(self.bytes_col)[int(locator[4:])].as_py()
+            return bytes(data["bytes"] if isinstance(data, dict) else data)
+        return super().open(locator)
+
+
+def _wds_split(name: str) -> tuple[str, str]:
+    folder, base = posixpath.split(name)
+    key, _, ext = base.partition(".")
+    return posixpath.join(folder, key), "." + ext.lower()
+
+
+def _wds_image(members: dict):
+    plain = sorted(e for e in members if e in IMAGE_EXTS)
+    dotted = sorted(e for e in members if e.endswith(IMAGE_EXTS))
+    ext = (plain or dotted or [None])[0]
+    return None if ext is None else members[ext]
+
+
+@SOURCES.register("webdataset")
+class WebDatasetSource:
+    """`path` is a glob of uncompressed .tar shards; locator `tar_index:offset:size`, read with
+    one `pread`. Keys without an image member are listed in `skipped`."""
+
+    def __init__(self, path: str, txt_as: str = "tags"):
+        self.path, self.txt_as = path, txt_as
+        self.tars = sorted(glob.glob(path))
+        self.skipped: list[str] = []
+        self._fds: dict[int, int] = {}
+
+    def __getstate__(self):
+        return {**self.__dict__, "_fds": {}}
+
+    def scan(self) -> list[Row]:
+        rows, self.skipped = [], []
+        for t, path in enumerate(self.tars):
+            name = os.path.basename(path)
+            with tarfile.open(path, "r:") as tar:
+                groups: dict[str, dict] = {}
+                for m in tar:
+                    if m.isfile():
+                        key, ext = _wds_split(m.name)
+                        groups.setdefault(key, {})[ext] = m
+                for key in sorted(groups):
+                    members = groups[key]
+                    img = _wds_image(members)
+                    if img is None:
+                        self.skipped.append(f"{name}:{key}")
+                        continue
+                    data = tar.extractfile(img).read()
+                    w, h, alpha = probe_image(data)
+                    row = Row(locator=f"{t}:{img.offset_data}:{img.size}", w=w, h=h, has_alpha=alpha, group=name)
+                    row.extra.update(hash=content_hash(data), key=key)
+                    if ".txt" in members:
+                        text = tar.extractfile(members[".txt"]).read().decode("utf-8").strip()
+                        if self.txt_as == "tags":
+                            row.tags = split_tags(text)
+                        else:
+                            row.caption_nl = text
+                    if ".json" in members:
+                        apply_json(row, json.loads(tar.extractfile(members[".json"]).read()))
+                    rows.append(row)
+        return rows
+
+    def open(self, locator: str) -> bytes:
+        t, off, size = (int(x) for x in locator.split(":"))
+        fd = self._fds.get(t)
+        if fd is None:
+            fd = self._fds[t] = os.open(self.tars[t], os.O_RDONLY)
+        return os.pread(fd, size, off)
+
+    @staticmethod
+    def problems(entry: dict) -> list[str]:
+        path = entry.get("path")
+        return [] if path and glob.glob(path) else [f"webdataset path {path!r} matches no .tar file"]
+
+
+# ---- packed image shards ------------------------------------------------------------------------
+SHARD_RECORD = struct.Struct("<QIHHBB6xQ")   # offset, size, w, h, codec, flags, pad, hash64
+CODECS = {"jpeg": 1, "png": 2, "webp": 3, "jxl": 4, "avif": 5, "bmp": 6, "other": 0}
+SHARD_BYTES = 1 << 30
+
+
+def codec_of(name: str) -> int:
+    ext = os.path.splitext(name)[1].lower().lstrip(".")
+    return CODECS.get("jpeg" if ext in ("jpg", "jpeg") else ext, 0)
+
+
+class ShardWriter:
+    """Appends encoded images to `root/shards/NNNNN.{bin,idx}`, rolling over at `shard_bytes`
+    (record layout of `src/kohakumoss_data/format/shard.py:1-20`). Locator: `shard:record`."""
+
+    def __init__(self, root: str, shard_bytes: int = SHARD_BYTES):
+        self.dir = os.path.join(root, "shards")
+        os.makedirs(self.dir, exist_ok=True)
+        self.shard_bytes, self.shard, self._bin, self._idx = shard_bytes, -1, None, None
+        self._roll()
+
+    def _roll(self) -> None:
+        self.close()
+        self.shard += 1
+        stem = os.path.join(self.dir, f"{self.shard:05d}")
+        self._bin, self._idx = open(stem + ".bin", "wb"), open(stem + ".idx", "wb")
+        self._offset, self._count = 0, 0
+
+    def add(self, data: bytes, w: int, h: int, name: str = "", alpha: bool = False) -> str:
+        if self._offset and self._offset + len(data) > self.shard_bytes:
+            self._roll()
+        h64 = int.from_bytes(bytes.fromhex(content_hash(data))[:8], "little")
+        self._bin.write(data)
+        self._idx.write(SHARD_RECORD.pack(self._offset, len(data), min(w, 65535), min(h, 65535), codec_of(name), int(alpha), h64))
+        loc = f"{self.shard}:{self._count}"
+        self._offset += len(data)
+        self._count += 1
+        return loc
+
+    def close(self) -> None:
+        for f in (self._bin, self._idx):
+            if f is not None:
+                f.close()
+        self._bin = self._idx = None
+
+
+@SOURCES.register("moss_shard")
+class MossShardSource:
+    """A dataset imported into packed shards: `path/shards/*.bin|idx` + `path/catalog.kmc`."""
+
+    def __init__(self, path: str):
+        self.path = path
+        self._idx: dict[int, np.ndarray] = {}
+        self._fds: dict[int, int] = {}
+
+    def __getstate__(self):
+        return {"path": self.path, "_idx": {}, "_fds": {}}
+
+    def catalog(self) -> Catalog:
+        if not os.path.isdir(os.path.join(self.path, "shards")):
+            raise FileNotFoundError(f"moss_shard {self.path}: no shards/ folder (re-run the import that wrote this dataset)")
+        return Catalog.load(os.path.join(self.path, "catalog.kmc"))
+
+    def scan(self) -> list[Row]:
+        cat = self.catalog()
+        return [cat[i] for i in range(len(cat))]
+
+    def open(self, locator: str) -> bytes:
+        s, r = (int(x) for x in locator.split(":"))
+        if s not in self._idx:
+            stem = os.path.join(self.path, "shards", f"{s:05d}")
+            self._idx[s] = np.fromfile(stem + ".idx", dtype=np.uint8).reshape(-1, SHARD_RECORD.size)
+            self._fds[s] = os.open(stem + ".bin", os.O_RDONLY)
+        off, size, *_ = SHARD_RECORD.unpack(self._idx[s][r].tobytes())
+        return os.pread(self._fds[s], size, off)
+
+    @staticmethod
+    def problems(entry: dict) -> list[str]:
+        path = entry.get("path")
+        return [] if path and os.path.isdir(os.path.join(path, "shards")) else [f"moss_shard path {path!r} has no shards/ folder"]
+
+
+def import_to_shards(source, rows: list[Row], root: str, shard_bytes: int = SHARD_BYTES) -> Catalog:
+    """Copy every image of `rows` into packed shards under `root` and write its catalog."""
+    writer = ShardWriter(root, shard_bytes)
+    out = []
+    for row in rows:
+        data = source.open(row.locator)
+        loc = writer.add(data, row.w, row.h, row.locator, row.has_alpha)
+        new = Row(**{**row.__dict__, "locator": loc})
+        new.extra = {**row.extra, "hash": content_hash(data), "origin": row.locator}
+        out.append(new)
+    writer.close()
+    cat = Catalog(out)
+    cat.save(os.path.join(root, "catalog.kmc"))
+    return cat
+
+
+@SOURCES.register("gbc")
+class GbcSource(FolderSource):
+    """A folder of images with region-graph records: `stem.gbc.json` next to each image, or one
+    `records` JSONL (`{"image": ..., "gbc": {...}}`). `record(locator)` serves the `gbc` caption
+    template; an `index` file (locator -> byte offset, built by the image-index script) lets
+    workers seek instead of loading the manifest."""
+
+    def __init__(self, path: str, records: str | None = None, recursive: bool = True, hash_content: bool = False):
+        super().__init__(path, recursive, "nl", hash_content)
+        self.records = records
+        self._offsets: dict[str, int] | None = None
+
+    def _index(self) -> dict[str, int]:
+        if self._offsets is None:
+            self._offsets = {}
+            if self.records:
+                idx = self.records + ".index.json"
+                if os.path.exists(idx) and os.path.getmtime(idx) >= os.path.getmtime(self.records):
+                    with open(idx, encoding="utf-8") as f:
+                        self._offsets = json.load(f)
+                else:
+                    self._offsets = build_record_index(self.records)
+        return self._offsets
+
+    def record(self, locator: str) -> dict:
+        side = os.path.join(self.path, os.path.splitext(locator)[0] + ".gbc.json")
+        if os.path.exists(side):
+            with open(side, encoding="utf-8") as f:
+                return json.load(f)
+        off = self._index().get(locator)
+        if off is None:
+            return {}
+        with open(self.records, "rb") as f:
+            f.seek(off)
+            return json.loads(f.readline()).get("gbc", {})
+
+
+def build_record_index(records: str) -> dict[str, int]:
+    """locator -> byte offset of its line in a GBC records JSONL."""
+    out, off = {}, 0
+    with open(records, "rb") as f:
+        for line in f:
+            if line.strip():
+                meta = json.loads(line)
+                key = next((k for k in IMAGE_KEYS if k in meta), None)
+                if key is not None:
+                    out[str(meta[key]).replace("\\", "/")] = off
+            off += len(line)
+    return out
+
+
+def build_source(entry: dict):
+    """A source from a dataset entry (dataset-level keys stripped)."""
+    kw = {k: v for k, v in entry.items() if k not in ("weight", "caption", "loss_weight", "catalog", "import_to", "source", "type")}
+    return SOURCES.get(entry.get("source") or entry.get("type"))(**kw)

@@ -18,17 +18,39 @@ from ..types.seqinfo import SeqInfo, build_seqinfo
 
 @dataclass
 class HostBatch:
-    latents: Tensor          # [N_img, C] fp32 / bf16
-    text: Tensor             # [N_txt, text_dim]
+    latents: Tensor | None   # [N_img, C] fp32 / bf16 (None until encoded: `pixels` holds the images)
+    text: Tensor | None      # [N_txt, text_dim] (None until encoded: `prompts` holds the captions)
     hw: Tensor               # [B, 2] latent grid per sample
     text_len: Tensor         # [B]
     seq: SeqInfo | None = None
     index: int = 0
     meta: dict = field(default_factory=dict)
+    ids: Tensor | None = None            # [B] catalog row ids
+    text_drop: Tensor | None = None      # [B] bool: caption dropped this step
+    weight: Tensor | None = None         # [B] per-sample loss weight
+    img_keep: list | None = None         # per sample: kept image-token indices or None (all)
+    pixels: list | None = None           # uint8 [H, W, 3] per sample, when latents are not cached
+    prompts: list | None = None          # captions, when text embeddings are not cached
+    rank: int = 0
+    latent_keys: list = field(default_factory=list)
+    text_keys: list = field(default_factory=list)
+    text_limit: list = field(default_factory=list)
 
     def __post_init__(self):
-        if self.seq is None:
-            self.seq = build_seqinfo(self.hw, self.text_len)
+        if self.seq is None and self.latents is not None and self.text is not None:
+            self.finalize()
+
+    @property
+    def encoded(self) -> bool:
+        return self.latents is not None and self.text is not None
+
+    def finalize(self) -> "HostBatch":
+        """Build the packed layout once latents, text and `text_len` are known. With
+        `img_keep` (image tokens dropped to fit the budget) the layout uses each sample's kept
+        positions, so RoPE still sees the original grid coordinates."""
+        keep = self.img_keep if self.img_keep and any(k is not None for k in self.img_keep) else None
+        self.seq = build_seqinfo(self.hw, self.text_len, img_keep=keep) if keep is not None else build_seqinfo(self.hw, self.text_len)
+        return self
 
     @property
     def samples(self) -> int:
@@ -44,9 +66,14 @@ class HostBatch:
 
     def pin_memory(self) -> "HostBatch":
         if torch.cuda.is_available():
-            self.latents = self.latents.pin_memory()
-            self.text = self.text.pin_memory()
-            self.seq.pin_memory()
+            if self.latents is not None:
+                self.latents = self.latents.pin_memory()
+            if self.text is not None:
+                self.text = self.text.pin_memory()
+            if self.seq is not None:
+                self.seq.pin_memory()
+            if self.weight is not None:
+                self.weight = self.weight.pin_memory()
         return self
 
     def nbytes(self) -> int:
@@ -60,7 +87,10 @@ class HostBatch:
             z = z.to(latent_dtype)
         if text_dtype is not None:
             t = t.to(text_dtype)
-        return DeviceBatch(z, t, self.seq.to(device), self.samples, self.image_tokens, self.nbytes())
+        w = None
+        if self.weight is not None and bool((self.weight != 1).any()):
+            w = self.weight.to(device, non_blocking=True)
+        return DeviceBatch(z, t, self.seq.to(device), self.samples, self.image_tokens, self.nbytes(), w)
 
 
 @dataclass
@@ -71,3 +101,4 @@ class DeviceBatch:
     samples: int
     image_tokens: int
     h2d_bytes: int = 0
+    weight: Tensor | None = None     # [B] per-sample loss weight (None = all ones)

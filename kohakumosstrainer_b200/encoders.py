@@ -67,3 +67,72 @@ class FluxVae:
     def decode(self, latents: Tensor):
         z = latents * self.std.to(latents)[None, :, None, None] + self.mean.to(latents)[None, :, None, None]
         return self.vae.decode(unpatchify(z)).sample
+
+
+# ---- encoder factories for the data layer (`IMAGE_ENCODER` / `TEXT_ENCODER_FN` knobs) ----------------
+def vae_encoder(path: str, device="cuda", dtype=torch.bfloat16):
+    """`encode(pixels: list[uint8 HWC], hw [B, 2]) -> packed latents [sum(h*w), 128]`."""
+    vae = FluxVae(path, device, dtype)
+
+    def encode(pixels, hw):
+        out = []
+        for px in pixels:
+            img = px.to(device).permute(2, 0, 1)[None].to(dtype) / 127.5 - 1.0
+            z = vae.encode(img)[0]
+            out.append(z.permute(1, 2, 0).reshape(-1, z.shape[0]))
+        return torch.cat(out)
+
+    encode.encoder_id, encode.encoder_spec = "flux2-vae", str(dtype).replace("torch.", "")
+    return encode
+
+
+def text_encoder(path: str, device="cuda", dtype=torch.bfloat16, max_tokens: int = 4096):
+    """`encode(prompts) -> list[[L_i, 4096]]`."""
+    enc = QwenTextEncoder(path, device, dtype, max_tokens)
+
+    def encode(prompts):
+        return enc.encode(list(prompts))
+
+    encode.encoder_id, encode.encoder_spec = "qwen3.5-9b", str(dtype).replace("torch.", "")
+    return encode
+
+
+def synthetic_image_encoder(channels: int = 128, seed: int = 0):
+    """Stand-in image encoder (no weights): each latent token is the mean colour of its 16 x 16
+    pixel patch pushed through a fixed random projection. Deterministic, resolution-faithful;
+    for pipeline tests, loader benchmarks and dry runs of the cache passes."""
+    g = torch.Generator().manual_seed(seed)
+    proj = torch.randn(3, channels, generator=g)
+
+    def encode(pixels, hw):
+        out = []
+        for px, (h, w) in zip(pixels, hw.tolist()):
+            x = px.float().div(127.5).sub(1.0)
+            x = x[: h * 16, : w * 16].reshape(h, 16, w, 16, 3).mean((1, 3)).reshape(h * w, 3)
+            out.append(x @ proj)
+        return torch.cat(out)
+
+    encode.encoder_id, encode.encoder_spec = "synthetic-image", f"c{channels}s{seed}"
+    return encode
+
+
+def synthetic_text_encoder(dim: int = 4096, chars_per_token: float = 3.5, overhead: int = 12, seed: int = 0):
+    """Stand-in text encoder: ceil(len / chars_per_token) + overhead tokens per prompt, each a
+    hash-seeded N(0, 1) vector, so equal prompts give equal embeddings."""
+
+    def encode(prompts):
+        out = []
+        for p in prompts:
+            n = -(-len(p) // max(chars_per_token, 1e-6)) + overhead
+            g = torch.Generator().manual_seed((hash_text(p) + seed) & 0x7FFFFFFFFFFF)
+            out.append(torch.randn(int(n), dim, generator=g))
+        return out
+
+    encode.encoder_id, encode.encoder_spec = "synthetic-text", f"d{dim}s{seed}"
+    return encode
+
+
+def hash_text(text: str) -> int:
+    import hashlib
+
+    return int.from_bytes(hashlib.blake2b(text.encode("utf-8"), digest_size=8).digest(), "little")

@@ -10,6 +10,8 @@ safetensors`, `<run>-merged.safetensors`, `<run>-diffusers/`). Mirrors the refer
 
 from __future__ import annotations
 
+import os
+
 import signal
 import time
 from pathlib import Path
@@ -59,14 +61,60 @@ def build_dataset(k: dict, text_dim: int, channels: int):
     from ..data import SyntheticConfig, SyntheticDataset
 
     spec = (k["DATASETS"] or [{"type": "synthetic"}])[0]
-    if spec.get("type", "synthetic") == "synthetic":
-        opts = {kk: vv for kk, vv in spec.items() if kk != "type"}
+    if (spec.get("source") or spec.get("type", "synthetic")) == "synthetic":
+        opts = {kk: vv for kk, vv in spec.items() if kk not in ("type", "source")}
         opts.setdefault("size_step", max(16, int(k["SIZE_STEP"])))
         cfg = SyntheticConfig(max_tokens=int(k["MAX_TOKENS"]), text_dim=text_dim, channels=channels, seed=int(k["SEED"]), **opts)
         return SyntheticDataset(cfg)
     from ..data.dataset import build_dataset as build_real
 
-    return build_real(k, text_dim, channels)
+    rank = int(os.environ.get("RANK", "0")) if "RANK" in os.environ else 0
+    return _Encoded(build_real(k, text_dim, channels, writer=rank == 0, rank=rank), k)
+
+
+class _Encoded:
+    """A real dataset whose batches leave `materialize` ready for the trainer: what the caches
+    do not hold is encoded here (`VAE`, `TEXT_ENCODER` knobs; loaded on first need) and, with
+    online caches, written back by a background thread."""
+
+    def __init__(self, dataset, k: dict):
+        self.dataset, self.cfg, self.k = dataset, dataset.cfg, k
+        self._vae = self._text = self._writer = None
+
+    def __getattr__(self, name):
+        return getattr(self.__dict__["dataset"], name)
+
+    def _images(self, pixels, hw):
+        if self._vae is None:
+            if not self.k["VAE"]:
+                raise RuntimeError("LATENT_CACHE misses and no VAE is set: build the latent cache or set VAE")
+            from ..encoders import FluxVae
+
+            dev = self.k["ENCODE_DEVICES"][0] if self.k["ENCODE_DEVICES"] else "cuda"
+            self._vae = FluxVae(self.k["VAE"], device=dev)
+        out = []
+        for px in pixels:
+            img = px.to(self._vae.vae.device).permute(2, 0, 1)[None].to(self._vae.vae.dtype) / 127.5 - 1.0
+            z = self._vae.encode(img)[0]
+            out.append(z.permute(1, 2, 0).reshape(-1, z.shape[0]))
+        return torch.cat(out)
+
+    def _prompts(self, prompts):
+        if self._text is None:
+            if not self.k["TEXT_ENCODER"]:
+                raise RuntimeError("TEXT_CACHE misses and no TEXT_ENCODER is set: build the text cache or set TEXT_ENCODER")
+            from ..encoders import QwenTextEncoder
+
+            self._text = QwenTextEncoder(self.k["TEXT_ENCODER"], device=self.k["TEXT_DEVICE"] or "cuda")
+        return self._text.encode(prompts)
+
+    def materialize(self, index: int, rank: int = 0, world: int = 1, pin: bool = True):
+        from ..data.dataset import encode_missing
+
+        hb = self.dataset.materialize(index, rank, world)
+        if not hb.encoded:
+            hb = encode_missing(hb, self.dataset, self._images, self._prompts)
+        return hb.pin_memory() if pin else hb
 
 
 def worker(k: dict, rank: int, world: int, device) -> dict:

@@ -81,6 +81,8 @@ class TrainStep:
         z, target = noise_latents(z0, eps, sigma, seq.seg_img)
         v = self.model(z.to(self.compute_dtype), batch.text.to(self.compute_dtype), sigma, seq)
         weight = self.weighting(sigma)
+        if batch.weight is not None:
+            weight = weight * batch.weight.to(weight.dtype)
         total = token_loss(self.model.ops, v, target, seq.seg_img, weight, None, self.loss, **self.loss_kwargs)
         return total / denom
 

@@ -1,0 +1,58 @@
+"""Offline latent cache pass: every live row at its planned target with the centre crop (and its
+mirrored twin when FLIP is on). Only missing keys are encoded, so the pass resumes.
+
+    python -m kohakumosstrainer_b200.cli.run scripts/data/cache_latents.py --config configs/moss/data/data_kohya.py \
+        --set IMAGE_ENCODER_KWARGS="{'path': '/weights/vae'}"
+
+The encoder factory's id must match LATENT_ENCODER_ID of the training run (it is part of every
+key). Same role as `scripts/data/cache_latents.py` of the reference.
+"""
+
+DATASETS = []
+RESOLUTION_MODE = "resize"
+TARGET_AREA = 1024 * 1024
+SIZE_STEP = 16
+ASPECT_RANGE = (0.25, 4.0)
+UPSCALE = "never"
+CROP = "center"
+MAX_TOKENS = 16384
+FLIP = False
+CACHE_DIR = ""
+CACHE_DTYPE = "bf16"
+LATENT_ENCODER_ID = "flux2-vae"
+LATENT_ENCODER_SPEC = ""
+BACKGROUND = "white"
+RESAMPLE = "lanczos"
+LATENT_DRAW = "mode"
+SEED = 0
+IMAGE_ENCODER = "kohakumosstrainer_b200.encoders.vae_encoder"
+IMAGE_ENCODER_KWARGS = {"path": "", "device": "cuda"}
+BATCH = 8
+
+globals().update(globals().pop("__kmoss_overrides__", {}))
+
+
+def main():
+    from tqdm.auto import tqdm
+
+    from kohakumosstrainer_b200.config import collect
+    from kohakumosstrainer_b200.data.cache_build import build_latent_cache
+    from kohakumosstrainer_b200.data.scripting import build_encoder, open_dataset
+
+    k = collect(globals())
+    ds = open_dataset(k, latent_cache="offline", text_cache="off", text_drop=0.0)
+    enc = build_encoder(k["IMAGE_ENCODER"], dict(k["IMAGE_ENCODER_KWARGS"]))
+    bar = tqdm(desc="latents", unit="img")
+
+    def progress(done, total):
+        bar.total, bar.n = total, done
+        bar.refresh()
+
+    out = build_latent_cache(ds, enc, int(k["BATCH"]), progress)
+    bar.close()
+    print(f"latent cache: encoded {out['encoded']}, present {out['present']}")
+    return out
+
+
+if __name__ == "__main__":
+    main()

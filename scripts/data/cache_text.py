@@ -1,0 +1,54 @@
+"""Offline text cache pass: every caption variant of every live row, plus "" when TEXT_DROP > 0.
+Only missing keys are encoded. Same role as `scripts/data/cache_text.py` of the reference.
+
+    python -m kohakumosstrainer_b200.cli.run scripts/data/cache_text.py --config configs/moss/data/data_kohya.py \
+        --set TEXT_ENCODER_KWARGS="{'path': '/weights/text_encoder'}"
+"""
+
+DATASETS = []
+RESOLUTION_MODE = "resize"
+TARGET_AREA = 1024 * 1024
+SIZE_STEP = 16
+ASPECT_RANGE = (0.25, 4.0)
+UPSCALE = "never"
+CROP = "center"
+MAX_TOKENS = 16384
+CAPTION = {}
+CAPTION_VARIANTS = 4
+TEXT_DROP = 0.1
+CACHE_DIR = ""
+CACHE_DTYPE = "bf16"
+TEXT_ENCODER_ID = "qwen3.5-9b"
+TEXT_ENCODER_SPEC = ""
+SEED = 0
+TEXT_ENCODER_FN = "kohakumosstrainer_b200.encoders.text_encoder"
+TEXT_ENCODER_KWARGS = {"path": "", "device": "cuda"}
+BATCH = 16
+
+globals().update(globals().pop("__kmoss_overrides__", {}))
+
+
+def main():
+    from tqdm.auto import tqdm
+
+    from kohakumosstrainer_b200.config import collect
+    from kohakumosstrainer_b200.data.cache_build import build_text_cache
+    from kohakumosstrainer_b200.data.scripting import build_encoder, open_dataset
+
+    k = collect(globals())
+    ds = open_dataset(k, latent_cache="off", text_cache="offline", token_budget="estimate")
+    enc = build_encoder(k["TEXT_ENCODER_FN"], dict(k["TEXT_ENCODER_KWARGS"]))
+    bar = tqdm(desc="captions", unit="cap")
+
+    def progress(done, total):
+        bar.total, bar.n = total, done
+        bar.refresh()
+
+    out = build_text_cache(ds, enc, int(k["BATCH"]), progress)
+    bar.close()
+    print(f"text cache: encoded {out['encoded']}, present {out['present']}")
+    return out
+
+
+if __name__ == "__main__":
+    main()

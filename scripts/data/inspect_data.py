@@ -1,0 +1,58 @@
+"""Print what the data config plans: catalog size, target-size histogram, epoch length, token
+fill of the first batches, sample captions, cache coverage. Role of `scripts/data/inspect_data.py`."""
+
+DATASETS = []
+RESOLUTION_MODE = "resize"
+TARGET_AREA = 1024 * 1024
+SIZE_STEP = 16
+ASPECT_RANGE = (0.25, 4.0)
+UPSCALE = "never"
+CROP = "center"
+BATCHING = "tokens"
+MAX_TOKENS = 16384
+MAX_SAMPLES = 0
+OVERLONG = "drop"
+BATCH_SIZE = 4
+CAPTION = {}
+CAPTION_VARIANTS = 4
+TEXT_DROP = 0.1
+LATENT_CACHE = "off"
+TEXT_CACHE = "off"
+CACHE_DIR = ""
+CACHE_DTYPE = "bf16"
+FLIP = False
+SEED = 0
+BATCHES = 8
+CAPTIONS = 3
+
+globals().update(globals().pop("__kmoss_overrides__", {}))
+
+
+def main():
+    from collections import Counter
+
+    import numpy as np
+
+    from kohakumosstrainer_b200.config import collect
+    from kohakumosstrainer_b200.data.scripting import open_dataset
+
+    k = collect(globals())
+    ds = open_dataset(k)
+    cat, plan = ds.catalog, ds.planner
+    print(f"catalog: {len(cat)} rows, {int(cat.live.sum())} live, weight sum {float(cat.weight.sum()):.1f}")
+    sizes = Counter(map(tuple, plan.targets.tolist()))
+    for (h, w), n in sizes.most_common(10):
+        print(f"  target {w}x{h}: {n} rows ({ds.geometry.tokens((h, w))} tokens)")
+    n = plan.epoch_length(0)
+    print(f"epoch 0: {n} batches, dropped {plan.drops.get(0, 0)}, unbatched {plan.unbatched.get(0, 0)}")
+    fills = [plan.batch_tokens(g).sum() / k["MAX_TOKENS"] for g in range(min(n, int(k["BATCHES"])))]
+    print(f"token fill of the first {len(fills)} batches: mean {np.mean(fills):.3f}, min {np.min(fills):.3f}")
+    for i in range(min(len(cat), int(k["CAPTIONS"]))):
+        print(f"  caption[{i}]: {ds.caption(i, 0)[:160]!r}")
+    if ds.latents.enabled:
+        print(f"latent cache: {len(ds.latents.store)} values; text cache: {len(ds.texts.store) if ds.texts.enabled else 0} values")
+    return {"rows": len(cat), "batches": n}
+
+
+if __name__ == "__main__":
+    main()

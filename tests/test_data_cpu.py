@@ -1,0 +1,395 @@
+"""Data layer on synthetic file trees: geometry, planners, batching, captions, sources, catalog,
+tensor store, dataset materialisation, stateless loader, offline / online caches."""
+
+import io
+import json
+import os
+import pickle
+import tarfile
+
+import numpy as np
+import pytest
+import torch
+from PIL import Image
+
+from kohakumosstrainer_b200.data import (Catalog, DataConfig, Geometry, MossDataset, Row, TensorStore, build_loader, build_template,
+                                         data_problems, decode_tensor, encode_missing, encode_tensor, merge_shards)
+from kohakumosstrainer_b200.data.cache_build import OnlineWriter, build_latent_cache, build_text_cache
+from kohakumosstrainer_b200.data.catalog import merge_scan
+from kohakumosstrainer_b200.data.planner import PLANNERS, batch_ffd, batch_greedy, epoch_order, rng_of
+from kohakumosstrainer_b200.data.sources import SOURCES, import_to_shards, parse_folder
+
+
+def _image(path, w, h, color=(200, 30, 30), mode="RGB"):
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    Image.new(mode, (w, h), color if mode == "RGB" else color + (128,)).save(path)
+
+
+@pytest.fixture()
+def tree(tmp_path):
+    root = tmp_path / "ds"
+    sizes = [(640, 480), (480, 640), (512, 512), (1024, 256), (300, 900), (800, 800), (256, 256), (700, 500)]
+    for i, (w, h) in enumerate(sizes):
+        p = root / f"{2 if i % 2 else 1}_set{i % 2}" / f"img{i}.png"
+        _image(str(p), w, h, mode="RGBA" if i == 2 else "RGB")
+        (p.with_suffix(".txt")).write_text(f"tag_a, tag_{i}, long_tag_name_{i}, \\(escaped\\)")
+        if i % 3 == 0:
+            (p.with_suffix(".json")).write_text(json.dumps({"artist": f"artist{i}", "rating": "g", "caption": f"a natural caption {i}"}))
+    return root
+
+
+def _rows(sizes):
+    return Catalog([Row(locator=f"{i}.png", w=w, h=h, tags=[f"t{i}"]) for i, (w, h) in enumerate(sizes)])
+
+
+# ---- geometry / planner ------------------------------------------------------------------------
+def test_fit_respects_area_step_and_aspect():
+    g = Geometry(area=512 * 512, step=32)
+    for w, h in [(4000, 3000), (300, 200), (5000, 500), (100, 4000)]:
+        th, tw = g.fit(w, h)
+        assert th % 32 == 0 and tw % 32 == 0 and th * tw <= 512 * 512
+        assert 0.25 <= tw / th <= 4.0
+    assert g.fit(300, 200) == (192, 288)            # never upscaled
+    up = Geometry(area=512 * 512, step=32, upscale="to_area").fit(300, 200)
+    assert up[0] * up[1] > 300 * 200
+    many = g.fit_many(np.array([4000, 300]), np.array([3000, 200]))
+    assert [tuple(r) for r in many] == [g.fit(4000, 3000), g.fit(300, 200)]
+    assert all(abs(h * w - 512 * 512) < 512 * 64 for h, w in g.buckets())
+
+
+def test_batching_rules():
+    t = np.array([500, 400, 300, 900, 100, 100, 100])
+    order, starts = batch_greedy(t, 1000, 99)
+    groups = [t[order[a:b]].tolist() for a, b in zip(starts[:-1], starts[1:])]
+    assert groups == [[500, 400], [300], [900, 100], [100, 100]]
+    order, starts = batch_greedy(t, 1000, 1)
+    assert len(starts) - 1 == len(t)
+    order, starts = batch_ffd(t, 1000, 99, 256)
+    groups = [t[order[a:b]].tolist() for a, b in zip(starts[:-1], starts[1:])]
+    assert sorted(map(sum, groups)) == [400, 1000, 1000] and sorted(order.tolist()) == list(range(len(t)))
+
+
+def test_epoch_order_weights():
+    w = np.array([2.0, 0.0, 1.5, 1.0], dtype=np.float32)
+    counts = np.zeros(4)
+    for e in range(200):
+        ids = epoch_order(w, 7, e)
+        counts += np.bincount(ids, minlength=4)
+    assert counts[0] == 400 and counts[1] == 0 and counts[3] == 200 and 260 < counts[2] < 340
+    assert (epoch_order(w, 7, 3) == epoch_order(w, 7, 3)).all()
+
+
+def test_planners_pure_and_rank_disjoint():
+    cat = _rows([(640 + 16 * (i % 7), 480 + 32 * (i % 5)) for i in range(64)])
+    geo = Geometry(area=256 * 256, step=16)
+    for kind in ("resize", "bucket", "square_crop", "shifted_square"):
+        p = PLANNERS.get(kind)(cat, geo, seed=3, max_tokens=1200, caption_variants=4, flip=True)
+        q = pickle.loads(pickle.dumps(p))
+        a = [p.plan(i, r, 2) for i in range(3) for r in range(2)]
+        b = [q.plan(i, r, 2) for i in range(3) for r in range(2)]
+        assert [x.items for x in a] == [x.items for x in b]
+        n = p.epoch_length(0)
+        seen = [it.row_id for g in range(n) for it in p.batch_items(g)]
+        assert sorted(seen) == list(range(64))
+        for plan in a:
+            assert plan.token_budget <= 1200
+            if kind == "bucket":
+                assert len({it.target_hw for it in plan.items}) == 1
+    sq = PLANNERS.get("square_crop")(cat, geo)
+    assert {tuple(t) for t in sq.targets} == {(256, 256)}
+
+
+def test_overlong_fits():
+    cat = _rows([(1024, 1024)] * 4)
+    geo = Geometry(area=512 * 512, step=16)   # 1024 image tokens
+    text = lambda r, v: 200                   # noqa: E731
+    drop = PLANNERS.get("resize")(cat, geo, max_tokens=1100, text_len=text, overlong="drop")
+    with pytest.raises(ValueError):
+        drop.plan(0)
+    trunc = PLANNERS.get("resize")(cat, geo, max_tokens=1100, text_len=text, overlong="truncate_text")
+    it = trunc.plan(0).items[0]
+    assert it.text_limit == 76 and trunc.plan(0).token_budget == 1100
+    dt = PLANNERS.get("resize")(cat, geo, max_tokens=1100, text_len=text, overlong="drop_tokens")
+    it = dt.plan(0).items[0]
+    assert it.img_keep == 900 and it.keep_seed != 0
+
+
+def test_rank_balance_deals_by_cost():
+    cat = _rows([(256 + 64 * (i % 9), 256 + 64 * (i % 4)) for i in range(96)])
+    p = PLANNERS.get("resize")(cat, Geometry(area=512 * 512, step=16), max_tokens=1500, balance=2)
+    dealt = p.balanced(0, 2)
+    assert sorted(dealt[0] + dealt[1]) == [0, 1, 2, 3]
+    loads = [sum(p.cost(g) for g in d) for d in dealt]
+    naive = [p.cost(0) + p.cost(2), p.cost(1) + p.cost(3)]
+    assert abs(loads[0] - loads[1]) <= abs(naive[0] - naive[1]) + 1e-6
+    assert p.global_batch(1, 0, 2) in dealt[0]
+
+
+# ---- captions -----------------------------------------------------------------------------------
+def test_tag_template_seeded_and_normalised():
+    row = Row(locator="x", w=1, h=1, tags=["keep_me", "|||", "a_b", "\\(c\\)", "%%", "d", "e"], artist="art")
+    t = build_template({"template": "tags", "tag_dropout": 0.0, "shuffle": True})
+    one = t.render(row, rng_of("caption", 0, 1, 0))
+    assert one == t.render(row, rng_of("caption", 0, 1, 0))
+    assert one.startswith("art, keep me") and "(c)" in one and "%%" not in one and "|||" not in one
+    texts = {t.render(row, rng_of("caption", 0, 1, v)) for v in range(8)}
+    assert len(texts) > 1
+    dropped = build_template({"template": "tags", "tag_dropout": 1.0}).render(row, rng_of("c", 0))
+    assert dropped == "art, keep me"
+
+
+def test_nl_mix_json_gbc_templates():
+    row = Row(locator="x", w=100, h=100, tags=["a", "b"], caption_nl="a cat", artist="art", json={"k": 1})
+    assert build_template({"template": "nl", "keep": ("artist",)}).render(row, rng_of("c", 0)) == "art. a cat"
+    assert build_template("nl").render(Row(locator="y", w=1, h=1, tags=["z"]), rng_of("c", 0)) == "z"
+    out = {build_template({"template": "mix", "p_nl": 0.5}).render(row, rng_of("c", v)) for v in range(16)}
+    assert len(out) >= 2
+    js = build_template({"template": "json", "order": ("tags",), "style": "lines"}).render(row, rng_of("c", 0))
+    assert js.splitlines()[0] == "tags: a, b" and "k: 1" in js
+    row.json = {"gbc": {"short": "a cat", "detail": "a cat on a mat", "regions": [
+        {"label": "cat", "text": "fluffy", "box": [0.1, 0.1, 0.5, 0.5], "children": [{"label": "ear", "box": [0.1, 0.1, 0.2, 0.2]}]},
+        {"label": "offscreen", "box": [0.9, 0.0, 1.0, 0.1]}]}}
+    g = build_template({"template": "gbc", "formats": [("nl", "graph")], "max_depth": 2})
+    text = g.render(row, rng_of("c", 1))
+    assert "cat" in text
+    catl = Catalog([row])
+    assert (g.estimate_chars(catl) > 0).all()
+
+
+# ---- catalog / store ----------------------------------------------------------------------------
+def test_catalog_file_roundtrip_and_merge(tmp_path):
+    rows = [Row(locator=f"{i}.png", w=10 + i, h=20, tags=["a", f"b{i}"], caption_nl="nl" if i % 2 else None, extra={"hash": f"h{i}"})
+            for i in range(5)]
+    cat = Catalog(rows)
+    path = str(tmp_path / "c.kmc")
+    cat.save(path)
+    back = Catalog.load(path)
+    assert len(back) == 5 and back[3].tags == ["a", "b3"] and back[3].w == 13 and back.locator(4) == "4.png"
+    assert (back.chars["tags_chars"] == cat.chars["tags_chars"]).all()
+    again = pickle.loads(pickle.dumps(back))
+    assert again[1].caption_nl == "nl"
+    found = [r for r in rows if r.locator != "1.png"] + [Row(locator="9.png", w=5, h=5, extra={"hash": "h9"})]
+    found[0] = Row(locator="0.png", w=99, h=20, extra={"hash": "changed"})
+    merged, stats = merge_scan(back, found)
+    assert stats == {"new": 1, "kept": 3, "changed": 1, "dead": 1}
+    assert merged.live.tolist() == [True, False, True, True, True, True] and merged[0].w == 99 and merged.locator(5) == "9.png"
+    both = Catalog.concat([cat, merged], [1.0, 2.0])
+    assert len(both) == 11 and both.source.tolist() == [0] * 5 + [1] * 6 and both.weight[6] == 2.0 and both[5].w == 99
+
+
+@pytest.mark.parametrize("storage,tol", [("bf16", 1e-2), ("fp16", 1e-3), ("fp32", 0.0), ("fp8", 0.08)])
+def test_tensor_value_format(storage, tol):
+    t = torch.randn(7, 16)
+    data = encode_tensor(t, storage)
+    assert data[:4] == b"KMT1"
+    back = decode_tensor(data, torch.float32)
+    assert back.shape == t.shape and (back - t).abs().max() <= tol * t.abs().max() + 1e-12
+
+
+def test_tensor_store_shards_and_merge(tmp_path):
+    stem = str(tmp_path / "cache" / "latents")
+    k = lambda i: f"{i:032x}"      # noqa: E731
+    main = TensorStore(stem, "bf16")
+    main.put(k(1), torch.ones(3, 4))
+    r0, r1 = TensorStore(stem, "bf16", writer_rank=0), TensorStore(stem, "bf16", writer_rank=1)
+    r0.put(k(2), torch.full((5, 4), 2.0))
+    r1.put(k(3), torch.full((6, 4), 3.0))
+    r1.put(k(1), torch.zeros(3, 4))                     # present in the main file: skipped
+    reader = pickle.loads(pickle.dumps(TensorStore(stem, "bf16")))
+    assert len(reader) == 3 and reader.get(k(3)).shape == (6, 4) and float(reader.get(k(1)).sum()) == 12.0
+    assert reader.get(k(9)) is None
+    lengths = reader.lengths()
+    assert lengths.get(k(2)) == 5 and lengths.get(k(3)) == 6 and lengths.get(k(7)) is None
+    for s in (main, r0, r1):
+        s.close()
+    assert merge_shards(stem, "bf16") == 2
+    merged = TensorStore(stem, "bf16")
+    assert len(merged) == 3 and float(merged.get(k(2)).float().mean()) == 2.0
+    assert not [f for f in os.listdir(tmp_path / "cache") if ".r0." in f or ".r1." in f]
+
+
+# ---- sources ------------------------------------------------------------------------------------
+def test_kohya_and_folder_sources(tree):
+    assert parse_folder("10_3_name", "first") == (10.0, "name") and parse_folder("10_3_name", "product") == (30.0, "name")
+    rows = SOURCES.get("kohya")(str(tree), artist_from_folder="name").scan()
+    assert len(rows) == 8
+    by = {r.locator: r for r in rows}
+    r1 = by["2_set1/img1.png"]
+    assert r1.weight == 2.0 and r1.artist == "set1" and (r1.w, r1.h) == (480, 640) and r1.tags[0] == "tag_a"
+    r0 = by["1_set0/img0.png"]
+    assert r0.artist == "artist0" and r0.caption_nl == "a natural caption 0" and r0.rating == "g"
+    assert by["1_set0/img2.png"].has_alpha
+    flat = SOURCES.get("folder")(str(tree)).scan()
+    assert len(flat) == 8 and all(r.weight == 1.0 for r in flat)
+    src = SOURCES.get("folder")(str(tree))
+    assert src.open(flat[0].locator)[:4] == b"\x89PNG"
+
+
+def test_jsonl_parquet_webdataset_shard_sources(tree, tmp_path):
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    files = sorted(str(p.relative_to(tree)) for p in tree.rglob("*.png"))
+    manifest = tmp_path / "m.jsonl"
+    manifest.write_text("\n".join(json.dumps({"image": f, "tags": "x, y", "weight": 1.5, "score": 3}) for f in files))
+    rows = SOURCES.get("jsonl")(str(manifest), root=str(tree)).scan()
+    assert len(rows) == 8 and rows[0].weight == 1.5 and rows[0].tags == ["x", "y"] and rows[0].json == {"score": 3}
+    blobs = [open(tree / f, "rb").read() for f in files]
+    pq.write_table(pa.table({"image": files, "data": blobs, "caption": [f"c{i}" for i in range(8)]}), tmp_path / "t.parquet")
+    by_path = SOURCES.get("parquet")(str(tmp_path / "t.parquet"), root=str(tree))
+    assert by_path.scan()[2].caption_nl == "c2"
+    emb = SOURCES.get("parquet")(str(tmp_path / "t.parquet"), bytes_col="data")
+    rows = emb.scan()
+    assert rows[1].locator == "row:1" and emb.open("row:1") == blobs[1]
+    with tarfile.open(tmp_path / "s-000.tar", "w") as tar:
+        for i, (f, b) in enumerate(zip(files, blobs)):
+            for ext, payload in ((".png", b), (".txt", f"wd_{i}".encode()), (".json", json.dumps({"rating": "s"}).encode())):
+                info = tarfile.TarInfo(f"{i:04d}{ext}")
+                info.size = len(payload)
+                tar.addfile(info, io.BytesIO(payload))
+        info = tarfile.TarInfo("orphan.txt")
+        info.size = 1
+        tar.addfile(info, io.BytesIO(b"x"))
+    wds = SOURCES.get("webdataset")(str(tmp_path / "s-*.tar"))
+    rows = wds.scan()
+    assert len(rows) == 8 and wds.skipped == ["s-000.tar:orphan"] and rows[3].tags == ["wd_3"] and rows[3].rating == "s"
+    assert pickle.loads(pickle.dumps(wds)).open(rows[3].locator) == blobs[3]
+    cat = import_to_shards(wds, rows, str(tmp_path / "packed"), shard_bytes=4096)
+    shard = SOURCES.get("moss_shard")(str(tmp_path / "packed"))
+    assert len(shard.catalog()) == 8 and shard.open(cat.locator(5)) == blobs[5]
+    assert len(os.listdir(tmp_path / "packed" / "shards")) > 2
+
+
+# ---- dataset ------------------------------------------------------------------------------------
+def _encoders(dim=8, channels=4):
+    def images(pixels, hw):
+        out = []
+        for px, (h, w) in zip(pixels, hw.tolist()):
+            mean = px.float().mean() / 255
+            out.append(torch.full((h * w, channels), float(mean)) + torch.arange(h * w)[:, None] * 1e-3)
+        return torch.cat(out)
+
+    def text(prompts):
+        return [torch.full((max(1, len(p) // 4), dim), float(len(p))) for p in prompts]
+
+    return images, text
+
+
+def _cfg(tree, **kw):
+    base = dict(datasets=[{"source": "kohya", "path": str(tree), "loss_weight": 0.5}], target_area=256 * 256, size_step=16, max_tokens=700,
+                latent_cache="off", text_cache="off", seed=5, text_drop=0.25, caption_variants=2, num_workers=0)
+    base.update(kw)
+    return DataConfig(**base)
+
+
+def test_dataset_materialize_pixels_then_encode(tree):
+    ds = MossDataset(_cfg(tree))
+    hb = ds.materialize(0)
+    assert hb.latents is None and len(hb.pixels) == hb.hw.shape[0] == len(hb.prompts)
+    for px, (h, w) in zip(hb.pixels, hb.hw.tolist()):
+        assert px.shape == (h * 16, w * 16, 3) and px.dtype == torch.uint8
+    images, text = _encoders()
+    done = encode_missing(hb, ds, images, text)
+    assert done.encoded and done.latents.shape[0] == done.seq.n_img and done.text.shape[0] == int(done.text_len.sum())
+    assert done.seq.n_joint <= 700 + 64 and (done.weight == 0.5).all()
+    again = MossDataset(_cfg(tree)).materialize(0)
+    assert torch.equal(again.hw, hb.hw) and again.prompts == ds.materialize(0).prompts
+    other = ds.materialize(0, rank=1, world=2)
+    assert not set(other.ids.tolist()) & set(ds.materialize(0, rank=0, world=2).ids.tolist())
+    assert data_problems(_cfg(tree, latent_cache="offline", crop="random"))
+    with pytest.raises(ValueError):
+        MossDataset(_cfg(tree, batching="nope"))
+
+
+def test_offline_caches_and_loader_resume(tree, tmp_path):
+    cfg = _cfg(tree, latent_cache="offline", text_cache="offline", cache_dir=str(tmp_path / "cache"), token_budget="exact", num_workers=2)
+    ds = MossDataset(cfg)
+    with pytest.raises(KeyError):
+        ds.materialize(0)
+    images, text = _encoders()
+    assert build_latent_cache(ds, images, batch=3)["encoded"] == 8
+    assert build_text_cache(ds, text)["encoded"] >= 9
+    assert build_latent_cache(MossDataset(cfg), images)["encoded"] == 0
+    ds = MossDataset(cfg)
+    hb = ds.materialize(0)
+    assert hb.encoded and hb.seq.n_joint <= 700 and hb.latents.dtype == torch.bfloat16
+    loader = build_loader(ds)
+    assert loader.workers_mode == "thread"
+    it = iter(loader)
+    first = [next(it) for _ in range(3)]
+    state = loader.state_dict()
+    assert state == {"seed": 5, "start": 3}
+    it.close()
+    resumed = build_loader(MossDataset(cfg))
+    resumed.load_state_dict(state)
+    nxt = next(iter(resumed))
+    assert nxt.index == 3 and torch.equal(nxt.latents, ds.materialize(3).latents)
+    assert [b.index for b in first] == [0, 1, 2] and torch.equal(first[1].text, ds.materialize(1).text)
+    procs = build_loader(ds, workers_mode="process")
+    got = next(iter(procs))
+    procs.shutdown()
+    assert torch.equal(got.latents, first[0].latents)
+
+
+def test_online_cache_write_back(tree, tmp_path):
+    cfg = _cfg(tree, latent_cache="online", text_cache="online", cache_dir=str(tmp_path / "cache"), text_drop=0.0)
+    ds = MossDataset(cfg, rank=0)
+    images, text = _encoders()
+    hb = ds.materialize(0)
+    assert hb.pixels is not None and hb.latent_keys
+    writer = OnlineWriter(ds)
+    full = images(hb.pixels, hb.hw)
+    parts = text(hb.prompts)
+    assert writer.submit(hb, full, parts)
+    writer.close()
+    assert not writer.errors and os.path.exists(tmp_path / "cache" / "latents.r0.kmts")
+    warm = MossDataset(cfg, rank=0).materialize(0)
+    assert warm.encoded and warm.pixels is None
+    assert torch.allclose(warm.latents.float(), full.to(torch.bfloat16).float())
+
+
+def test_training_entry_on_a_real_dataset(tree, tmp_path):
+    """Folder of images -> offline caches (stand-in encoders) -> two trainer steps through the
+    public entry, then a resumed third step that replays the loader position."""
+    from kohakumosstrainer_b200.config import run_script, script_knobs
+    from kohakumosstrainer_b200.data import build_dataset
+
+    sets = {"VARIANT": "tiny", "PRECISION": "fp32", "MAX_TOKENS": 700, "TARGET_AREA": 256 * 256, "DIM": 4, "ALPHA": 4.0,
+            "ARCH_OVERRIDES": {"text_dim": 32, "latent_channels": 8}, "DATASETS": [{"source": "kohya", "path": str(tree)}],
+            "LATENT_CACHE": "offline", "TEXT_CACHE": "offline", "CACHE_DIR": str(tmp_path / "cache"), "CAPTION_VARIANTS": 2,
+            "OUTPUT_DIR": str(tmp_path / "runs"), "RUN_NAME": "real", "LOG_EVERY": 1, "SAVE_EVERY": 2, "STEPS": 2}
+    knobs = {**script_knobs("scripts/train/moss.py"), **sets}
+    ds = build_dataset(knobs)
+    images, text = _encoders(dim=32, channels=8)
+    build_latent_cache(ds, images)
+    build_text_cache(ds, text)
+    out = run_script("scripts/train/moss.py", None, [f"{k}={v!r}" for k, v in sets.items()])
+    assert os.path.isdir(tmp_path / "runs" / "real")
+    sets["STEPS"], sets["RESUME"] = 3, "latest"
+    run_script("scripts/train/moss.py", None, [f"{k}={v!r}" for k, v in sets.items()])
+    rows = [json.loads(line) for line in open(tmp_path / "runs" / "real" / "metrics.jsonl")]
+    assert [r["step"] for r in rows][-3:] == [1, 2, 3] and all(np.isfinite(r["loss/train"]) for r in rows)
+
+
+def test_data_scripts(tree, tmp_path):
+    from kohakumosstrainer_b200.config import run_script
+
+    cache = str(tmp_path / "cache")
+    ds = [{"source": "kohya", "path": str(tree)}]
+    common = [f"DATASETS={ds!r}", f"CACHE_DIR={cache!r}", "TARGET_AREA=65536"]
+    out = run_script("scripts/data/catalog_build.py", None, common[:2])
+    lat = run_script("scripts/data/cache_latents.py", None, common + [
+        "IMAGE_ENCODER='kohakumosstrainer_b200.encoders.synthetic_image_encoder'", "IMAGE_ENCODER_KWARGS={'channels': 8}",
+        "LATENT_ENCODER_ID='synthetic-image'"])
+    txt = run_script("scripts/data/cache_text.py", None, common + [
+        "TEXT_ENCODER_FN='kohakumosstrainer_b200.encoders.synthetic_text_encoder'", "TEXT_ENCODER_KWARGS={'dim': 16}",
+        "TEXT_ENCODER_ID='synthetic-text'", "CAPTION_VARIANTS=2"])
+    run_script("scripts/data/inspect_data.py", None, common + ["LATENT_CACHE='offline'", "MAX_TOKENS=800"])
+    run_script("scripts/data/cache_merge.py", None, [f"CACHE_DIR={cache!r}"])
+    run_script("scripts/data/catalog_cache.py", None, [f"CACHE_DIR={cache!r}", "ACTION='list'"])
+    store = TensorStore(os.path.join(cache, "latents"))
+    assert len(store) == 8 and len(TensorStore(os.path.join(cache, "text"))) >= 9
+    rec = tmp_path / "rec.jsonl"
+    rec.write_text(json.dumps({"image": "a.png", "gbc": {"short": "s"}}) + "\n" + json.dumps({"image": "b.png", "gbc": {"short": "t"}}) + "\n")
+    run_script("scripts/data/image_index.py", None, [f"RECORDS={str(rec)!r}"])
+    assert set(json.load(open(str(rec) + ".index.json"))) == {"a.png", "b.png"}
