@@ -1,0 +1,9 @@
+"""Memory plans, the analytic estimate, the `auto` planner and the offload engines."""
+
+from .plan import ORDER, PROFILES, MemoryPlan, catalog, checkpoint_mode, resolve_profile
+from .estimate import Workload, estimate, fits, relative_cost
+from .planner import device_bytes, plan_auto
+from .apply import build_plan_optimizer, build_plan_runner
+
+__all__ = ["ORDER", "PROFILES", "MemoryPlan", "catalog", "checkpoint_mode", "resolve_profile", "Workload", "estimate", "fits",
+           "relative_cost", "device_bytes", "plan_auto", "build_plan_optimizer", "build_plan_runner"]

@@ -1,0 +1,55 @@
+"""Plan application: a `MemoryPlan` becomes a block runner, streamed weights and an optimiser.
+
+`build_plan_runner` composes the runner (checkpoint mode, activation offload, weight ring);
+`build_plan_optimizer` picks where the optimiser state lives. Same role as the reference's
+`memory/apply.py` + `memory/runners.py:191-210`.
+"""
+
+from __future__ import annotations
+
+from ..models.runners import build_runner
+from .offload import ActivationOffload, OffloadCheckpointRunner, StreamRunner, WeightRing
+from .plan import MemoryPlan, checkpoint_mode
+
+
+def build_plan_runner(plan: MemoryPlan, model, device):
+    """-> (runner, parts) where parts holds the live engines (`ring`, `act_offload`)."""
+    depth = len(model.layers)
+    parts = {}
+    mode, frac = checkpoint_mode(plan.checkpoint)
+    if plan.act_offload and mode != "none":
+        parts["act_offload"] = ActivationOffload(device, pinned=plan.pinned)
+        runner = OffloadCheckpointRunner(parts["act_offload"], frac, depth)
+    else:
+        runner = build_runner(plan.checkpoint, depth)
+    if plan.stream in ("ring", "swap") and 0 < plan.stream_resident < depth:
+        parts["ring"] = WeightRing(list(model.layers), device, plan.stream_resident, plan.pinned)
+        runner = StreamRunner(runner, parts["ring"])
+        from ..ops import native_ops
+
+        native_ops.invalidate_packs(model)
+    return runner, parts
+
+
+def build_plan_optimizer(plan: MemoryPlan, named, name: str, lr, betas, eps, weight_decay, wd_rules, kwargs):
+    """-> (optimizer, parts). `gpu` keeps the fused device optimisers; `cpu` / `stream` are AdamW
+    with host state (Muon and EMA need device state and stay on `gpu`)."""
+    from ..optim import build_optimizer
+    from ..optim.groups import param_groups
+
+    if plan.optim_state == "gpu":
+        return build_optimizer(named, name, lr, betas, eps, weight_decay, wd_rules, kwargs), {}
+    if name not in ("adamw", "adamw16", "adamw8bit", "adamw8bit_block"):
+        raise ValueError(f"OPTIM_STATE={plan.optim_state!r} supports the AdamW family, not OPTIMIZER={name!r}")
+    from .host_optim import GradOffload, HostAdamW, StreamedAdamW
+
+    groups = param_groups([(n, p) for n, p in named if p.requires_grad], weight_decay, wd_rules, (), None)
+    cls = HostAdamW if plan.optim_state == "cpu" else StreamedAdamW
+    opt = cls(groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, pinned=plan.pinned)
+    parts = {}
+    if plan.grad_offload:
+        if plan.optim_state != "cpu":
+            raise ValueError("GRAD_OFFLOAD=True needs OPTIM_STATE='cpu' in this build (the update runs where the gradients are)")
+        parts["grad_offload"] = GradOffload([p for _, p in named], plan.pinned)
+        opt.grad_source = parts["grad_offload"]
+    return opt, parts

@@ -1,0 +1,241 @@
+"""AdamW with its state off the device: `OPTIM_STATE="cpu"` and `"stream"`, plus gradient offload.
+
+* `HostAdamW` (`cpu`): fp32 masters and both moments live in pinned host memory; gradients
+  arrive through pinned staging buffers (copied on a side stream as soon as they are final),
+  the update runs on the host (vectorised torch ops over flat buffers, so a handful of passes
+  over memory rather than a Python loop per parameter) and the new weights return with one
+  host-to-device copy per flat buffer.
+* `StreamedAdamW` (`stream`): the moments live in pinned host memory but the update runs on
+  the device with the fused multi-tensor kernel; state chunks of `chunk_bytes` stream in and
+  out on a copy stream, double-buffered, so device residency is two chunks instead of 8 bytes
+  per parameter.
+
+Roles of the reference's `offload/optim/{cpu_optim,stream_optim,grad}.py`.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import Tensor
+
+
+class _Flat:
+    """Parameters of one dtype / device flattened into one host buffer set."""
+
+    def __init__(self, params: list[Tensor], pinned: bool):
+        self.params = params
+        self.numel = sum(p.numel() for p in params)
+        pin = pinned and torch.cuda.is_available()
+        mk = lambda: torch.zeros(self.numel, dtype=torch.float32, device="cpu", pin_memory=pin)  # noqa: E731
+        self.master, self.m, self.v, self.grad = mk(), mk(), mk(), mk()
+        self.out = torch.empty(self.numel, dtype=params[0].dtype, device="cpu", pin_memory=pin)
+        off = 0
+        self.spans = []
+        for p in params:
+            n = p.numel()
+            self.master[off : off + n].copy_(p.detach().reshape(-1).float())
+            self.spans.append((off, n))
+            off += n
+
+
+class HostAdamW(torch.optim.Optimizer):
+    def __init__(self, params, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01, pinned: bool = True):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, lr_mul=1.0))
+        self.pinned = pinned
+        self._flats: dict[int, _Flat] = {}
+        self._steps: dict[int, int] = {}
+        self.stream = torch.cuda.Stream() if torch.cuda.is_available() else None
+        self.bytes_d2h = self.bytes_h2d = 0
+        self.grad_source = None         # a `GradOffload`: gradients are already on the host
+
+    def _flat(self, gi: int, group) -> _Flat:
+        if gi not in self._flats:
+            self._flats[gi] = _Flat([p for p in group["params"] if p.requires_grad], self.pinned)
+        return self._flats[gi]
+
+    @torch.no_grad()
+    def step(self, closure=None, grad_scale: Tensor | float | None = None, skip=None):
+        """`grad_scale` multiplies gradients first (the clip coefficient); a true `skip` leaves
+        everything untouched (non-finite step). Device scalars are read here: the host update
+        cannot start before they are known anyway."""
+        if skip is not None and bool(skip):
+            return None
+        scale = float(grad_scale) if grad_scale is not None else 1.0
+        host_grads = self.grad_source.gather() if self.grad_source is not None else None
+        for gi, group in enumerate(self.param_groups):
+            flat = self._flat(gi, group)
+            cuda = flat.params[0].is_cuda
+            if cuda:
+                self.stream.wait_stream(torch.cuda.current_stream())
+            ctx = torch.cuda.stream(self.stream) if cuda else _null()
+            with ctx:
+                for p, (off, n) in zip(flat.params, flat.spans):
+                    g = host_grads[id(p)] if host_grads is not None else p.grad
+                    if g is None:
+                        flat.grad[off : off + n].zero_()
+                    else:
+                        flat.grad[off : off + n].copy_(g.reshape(-1), non_blocking=True)
+                        self.bytes_d2h += n * g.element_size()
+            if cuda:
+                self.stream.synchronize()
+            step = self._steps[gi] = self._steps.get(gi, 0) + 1
+            b1, b2 = group["betas"]
+            lr = group["lr"] * group.get("lr_mul", 1.0)
+            g = flat.grad.mul_(scale) if scale != 1.0 else flat.grad
+            flat.m.mul_(b1).add_(g, alpha=1 - b1)
+            flat.v.mul_(b2).addcmul_(g, g, value=1 - b2)
+            c1, c2 = 1 - b1**step, 1 - b2**step
+            denom = flat.v.sqrt().div_(math.sqrt(c2)).add_(group["eps"])
+            if group["weight_decay"]:
+                flat.master.mul_(1 - lr * group["weight_decay"])
+            flat.master.addcdiv_(flat.m, denom, value=-lr / c1)
+            flat.out.copy_(flat.master)
+            with ctx:
+                for p, (off, n) in zip(flat.params, flat.spans):
+                    p.copy_(flat.out[off : off + n].view_as(p), non_blocking=True)
+                    self.bytes_h2d += n * p.element_size()
+            if cuda:
+                torch.cuda.current_stream().wait_stream(self.stream)
+        return None
+
+    def state_dict(self):
+        return {"steps": dict(self._steps), "flats": {gi: {"master": f.master.clone(), "m": f.m.clone(), "v": f.v.clone()} for gi, f in self._flats.items()},
+                "param_groups": [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups]}
+
+    def load_state_dict(self, state):
+        self._steps = {int(k): int(v) for k, v in state["steps"].items()}
+        for gi, parts in state["flats"].items():
+            flat = self._flat(int(gi), self.param_groups[int(gi)])
+            for name in ("master", "m", "v"):
+                getattr(flat, name).copy_(parts[name])
+        for g, saved in zip(self.param_groups, state["param_groups"]):
+            g.update(saved)
+
+
+class StreamedAdamW(torch.optim.Optimizer):
+    """Device update, host-resident moments, streamed in chunks."""
+
+    def __init__(self, params, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01, chunk_bytes: int = 256 << 20, pinned: bool = True):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, lr_mul=1.0))
+        self.chunk_elems = max(1, chunk_bytes // 8)
+        self.pinned = pinned and torch.cuda.is_available()
+        self._host: dict[int, tuple[Tensor, Tensor]] = {}
+        self._steps: dict[int, int] = {}
+        self.stream = torch.cuda.Stream() if torch.cuda.is_available() else None
+        self.bytes_moved = 0
+
+    def _moments(self, p: Tensor) -> tuple[Tensor, Tensor]:
+        if id(p) not in self._host:
+            mk = lambda: torch.zeros(p.numel(), dtype=torch.float32, device="cpu", pin_memory=self.pinned)  # noqa: E731
+            self._host[id(p)] = (mk(), mk())
+        return self._host[id(p)]
+
+    @torch.no_grad()
+    def step(self, closure=None, grad_scale: Tensor | float | None = None, skip=None):
+        if skip is not None and bool(skip):
+            return None
+        scale = grad_scale
+        for gi, group in enumerate(self.param_groups):
+            step = self._steps[gi] = self._steps.get(gi, 0) + 1
+            b1, b2 = group["betas"]
+            lr = group["lr"] * group.get("lr_mul", 1.0)
+            c1, c2 = 1 - b1**step, 1 - b2**step
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                hm, hv = self._moments(p)
+                flat_p, flat_g = p.view(-1), p.grad.reshape(-1)
+                for lo in range(0, p.numel(), self.chunk_elems):
+                    hi = min(p.numel(), lo + self.chunk_elems)
+                    dev = p.device
+                    if self.stream is not None and p.is_cuda:
+                        with torch.cuda.stream(self.stream):
+                            m = hm[lo:hi].to(dev, non_blocking=True)
+                            v = hv[lo:hi].to(dev, non_blocking=True)
+                        torch.cuda.current_stream().wait_stream(self.stream)
+                    else:
+                        m, v = hm[lo:hi].to(dev), hv[lo:hi].to(dev)
+                    g = flat_g[lo:hi].float()
+                    if scale is not None:
+                        g = g * scale
+                    m.mul_(b1).add_(g, alpha=1 - b1)
+                    v.mul_(b2).addcmul_(g, g, value=1 - b2)
+                    w = flat_p[lo:hi].float()
+                    if group["weight_decay"]:
+                        w.mul_(1 - lr * group["weight_decay"])
+                    w.addcdiv_(m, v.sqrt().div_(math.sqrt(c2)).add_(group["eps"]), value=-lr / c1)
+                    flat_p[lo:hi].copy_(w)
+                    if self.stream is not None and p.is_cuda:
+                        self.stream.wait_stream(torch.cuda.current_stream())
+                        with torch.cuda.stream(self.stream):
+                            hm[lo:hi].copy_(m, non_blocking=True)
+                            hv[lo:hi].copy_(v, non_blocking=True)
+                        m.record_stream(self.stream)
+                        v.record_stream(self.stream)
+                    else:
+                        hm[lo:hi].copy_(m)
+                        hv[lo:hi].copy_(v)
+                    self.bytes_moved += 16 * (hi - lo)
+        if self.stream is not None:
+            torch.cuda.current_stream().wait_stream(self.stream)
+        return None
+
+
+class GradOffload:
+    """`GRAD_OFFLOAD=True`: a parameter's gradient leaves the device as soon as it is final
+    (post-accumulate hook), accumulating into a pinned fp32 host buffer; the device gradient is
+    freed. `gather()` hands the optimiser host gradients."""
+
+    def __init__(self, params, pinned: bool = True):
+        self.params = [p for p in params if p.requires_grad]
+        pin = pinned and torch.cuda.is_available()
+        self.host = {id(p): torch.zeros(p.shape, dtype=torch.float32, device="cpu", pin_memory=pin) for p in self.params}
+        self.stream = torch.cuda.Stream() if torch.cuda.is_available() else None
+        self.bytes = 0
+        self._stage: list = []
+        for p in self.params:
+            p.register_post_accumulate_grad_hook(self._hook)
+
+    def _hook(self, p: Tensor) -> None:
+        g = p.grad
+        if g is None:
+            return
+        host = self.host[id(p)]
+        self.bytes += g.numel() * g.element_size()
+        if self.stream is None or not g.is_cuda:
+            host.add_(g.float().cpu())
+        else:
+            self.stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.stream):
+                stage = g.float().to("cpu", non_blocking=True)
+            g.record_stream(self.stream)
+            self._stage.append((host, stage))
+        p.grad = None
+
+    def gather(self) -> dict[int, Tensor]:
+        if self.stream is not None:
+            self.stream.synchronize()
+        for host, stage in self._stage:
+            host.add_(stage)
+        self._stage.clear()
+        return self.host
+
+    def zero(self) -> None:
+        for h in self.host.values():
+            h.zero_()
+
+    def sumsq(self, device) -> Tensor:
+        """fp32[1] squared gradient norm, computed where the gradients are."""
+        host = self.gather()
+        total = sum(float(h.square().sum()) for h in host.values())
+        return torch.tensor([total], dtype=torch.float32).to(device)
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False

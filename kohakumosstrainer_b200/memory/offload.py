@@ -1,0 +1,289 @@
+"""Offload engines: activation offload and weight-ring streaming.
+
+Both ride on CUDA streams and events, never on host synchronisation:
+
+* `ActivationOffload`: the inputs of checkpointed blocks (the only activations a checkpointed
+  block keeps) move to pinned host memory on a copy stream as soon as the forward of the block
+  has consumed them, and come back one block ahead of the backward sweep. Saved-tensor hooks,
+  like the reference's activation offload (`src/kohakumoss/offload/activation.py`), but the
+  prefetch is driven by the block order instead of a guess.
+* `WeightRing` (`STREAM="ring"`): the large frozen tensors of block i live in pinned host
+  memory; the device holds `resident` ring slots; block i always uses slot `i % resident`, so
+  device addresses never change (cached weight packs, TMA descriptors and CUDA graphs stay
+  valid) and loading block i is ONE host-to-device copy of a flat buffer. Forward prefetches
+  i + 1 while i computes; backward prefetches i - 1. Role of the reference's ring streamer
+  (`src/kohakumoss/offload/weights/stream.py`, `weights/streaming/ring.py`).
+
+On a CPU-only host every copy is synchronous and the same code paths run (tests).
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+from torch.utils.checkpoint import checkpoint
+
+MIN_STREAM_BYTES = 1 << 20
+ALIGN = 256
+
+
+def _cuda(device) -> bool:
+    return torch.device(device).type == "cuda"
+
+
+class ActivationOffload:
+    """Saved-tensor hooks that park tensors of at least `min_bytes` on the host."""
+
+    def __init__(self, device, min_bytes: int = 1 << 20, pinned: bool = True):
+        self.device = torch.device(device)
+        self.min_bytes, self.pinned = min_bytes, pinned and _cuda(device)
+        self.stream = torch.cuda.Stream(self.device) if _cuda(device) else None
+        self.bytes_out = self.bytes_in = 0
+        self._pool: dict[tuple, list[Tensor]] = {}
+
+    def _host(self, t: Tensor) -> Tensor:
+        key = (tuple(t.shape), t.dtype)
+        free = self._pool.get(key)
+        if free:
+            return free.pop()
+        return torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=self.pinned)
+
+    def pack(self, t: Tensor):
+        if not isinstance(t, Tensor) or t.device != self.device or t.numel() * t.element_size() < self.min_bytes \
+                or isinstance(t, torch.nn.Parameter):
+            return t
+        host = self._host(t)
+        self.bytes_out += host.numel() * host.element_size()
+        if self.stream is None:
+            host.copy_(t)
+            return ("host", host, None, t.device)
+        self.stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self.stream):
+            host.copy_(t, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(self.stream)
+        t.record_stream(self.stream)
+        return ("host", host, done, t.device)
+
+    def unpack(self, packed):
+        if not (isinstance(packed, tuple) and len(packed) == 4 and packed[0] == "host"):
+            return packed
+        _, host, done, device = packed
+        self.bytes_in += host.numel() * host.element_size()
+        if self.stream is None:
+            out = host.to(device)
+        else:
+            with torch.cuda.stream(self.stream):
+                if done is not None:
+                    self.stream.wait_event(done)
+                out = host.to(device, non_blocking=True)
+            torch.cuda.current_stream(self.device).wait_stream(self.stream)
+            out.record_stream(torch.cuda.current_stream(self.device))
+        self._pool.setdefault((tuple(host.shape), host.dtype), []).append(host)
+        return out
+
+    def hooks(self):
+        return torch.autograd.graph.saved_tensors_hooks(self.pack, self.unpack)
+
+
+class OffloadCheckpointRunner:
+    """Block checkpointing whose saved block inputs live on the host (`ACT_OFFLOAD=True`)."""
+
+    name = "block+offload"
+
+    def __init__(self, offload: ActivationOffload, fraction: float = 1.0, depth: int = 0):
+        self.offload, self.cut = offload, int(round(fraction * depth)) if depth else 1 << 30
+
+    def run(self, index, block, x, ctx):
+        if not torch.is_grad_enabled() or index >= self.cut:
+            return block(x, ctx)
+        with self.offload.hooks():
+            return checkpoint(block, x, ctx, use_reentrant=False)
+
+
+# ---- weight ring ----------------------------------------------------------------------------------
+def _big_tensors(block) -> list[Tensor]:
+    """The large frozen tensors of a block: dense frozen weights and stored fp8 payloads (a
+    fused q|k|v group buffer and the member views into it are all listed)."""
+    out = []
+    for m in block.modules():
+        w = m.__dict__.get("_parameters", {}).get("weight")
+        if w is not None and not w.requires_grad and w.numel() * w.element_size() >= MIN_STREAM_BYTES:
+            out.append(w)
+        base = getattr(m, "base", None)
+        if base is not None and hasattr(base, "q"):
+            out.append(base.q)
+            if getattr(base, "group", None) is not None:
+                out.append(base.group.q)
+    uniq, seen = [], set()
+    for t in out:
+        if id(t) not in seen:
+            seen.add(id(t))
+            uniq.append(t)
+    return uniq
+
+
+class _BlockLayout:
+    """Byte layout of one block's streamed tensors inside a flat buffer (overlapping views are
+    merged into one extent)."""
+
+    def __init__(self, tensors: list[Tensor]):
+        spans = sorted({(t.data_ptr(), t.data_ptr() + t.numel() * t.element_size()) for t in tensors})
+        extents: list[list[int]] = []
+        for lo, hi in spans:
+            if extents and lo < extents[-1][1]:
+                extents[-1][1] = max(extents[-1][1], hi)
+            else:
+                extents.append([lo, hi])
+        self.extents, self.offsets, pos = extents, [], 0
+        for lo, hi in extents:
+            self.offsets.append(pos)
+            pos += (hi - lo + ALIGN - 1) // ALIGN * ALIGN
+        self.nbytes = pos
+        self.tensors = tensors
+        self.where = []
+        for t in tensors:
+            k = next(i for i, (lo, hi) in enumerate(extents) if lo <= t.data_ptr() < hi)
+            self.where.append(self.offsets[k] + t.data_ptr() - extents[k][0])
+
+    def gather(self, flat: Tensor) -> None:
+        """Copy the tensors' current bytes into `flat` (uint8)."""
+        for t, off in zip(self.tensors, self.where):
+            n = t.numel() * t.element_size()
+            flat[off : off + n].copy_(t.detach().contiguous().view(-1).view(torch.uint8))
+
+    def repoint(self, flat: Tensor) -> None:
+        """Make every tensor a view into `flat` (tensor objects keep their identity)."""
+        with torch.no_grad():
+            for t, off in zip(self.tensors, self.where):
+                size, stride = t.size(), t.stride()
+                t.set_(flat.untyped_storage(), (flat.storage_offset() + off) // t.element_size(), size, stride)
+
+
+class WeightRing:
+    def __init__(self, blocks, device, resident: int = 4, pinned: bool = True):
+        self.device = torch.device(device)
+        self.depth = len(blocks)
+        self.resident = max(2, min(resident, self.depth))
+        self.layouts = [_BlockLayout(_big_tensors(b)) for b in blocks]
+        slot_bytes = max((lay.nbytes for lay in self.layouts), default=0)
+        cuda = _cuda(device)
+        self.host = []
+        for lay in self.layouts:
+            flat = torch.empty(lay.nbytes, dtype=torch.uint8, device="cpu", pin_memory=pinned and cuda)
+            lay.gather(flat)
+            self.host.append(flat)
+        self.slots = [torch.empty(slot_bytes, dtype=torch.uint8, device=self.device) for _ in range(self.resident)]
+        for i, lay in enumerate(self.layouts):
+            lay.repoint(self.slots[i % self.resident][: lay.nbytes] if lay.nbytes else self.slots[0][:0])
+        self.stream = torch.cuda.Stream(self.device) if cuda else None
+        self.loaded = [-1] * self.resident          # which block each slot holds
+        self.load_event = [None] * self.resident
+        self.free_event = [None] * self.resident
+        self.bytes_h2d = 0
+        self.streamed_bytes = sum(lay.nbytes for lay in self.layouts)
+        self.device_bytes = slot_bytes * self.resident
+
+    def _load(self, index: int) -> None:
+        if not 0 <= index < self.depth:
+            return
+        s = index % self.resident
+        if self.loaded[s] == index:
+            return
+        lay, src = self.layouts[index], self.host[index]
+        self.bytes_h2d += lay.nbytes
+        if self.stream is None:
+            self.slots[s][: lay.nbytes].copy_(src)
+        else:
+            with torch.cuda.stream(self.stream):
+                if self.free_event[s] is not None:
+                    self.stream.wait_event(self.free_event[s])      # the slot's previous block has finished computing
+                self.slots[s][: lay.nbytes].copy_(src, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.stream)
+                self.load_event[s] = ev
+        self.loaded[s] = index
+
+    def acquire(self, index: int, direction: int = 1) -> None:
+        """Block `index` is about to run: make sure it is (being) loaded, make the compute stream
+        wait for it, and start loading its neighbour in `direction`."""
+        self._load(index)
+        s = index % self.resident
+        if self.stream is not None and self.load_event[s] is not None:
+            torch.cuda.current_stream(self.device).wait_event(self.load_event[s])
+        nxt = index + direction
+        if 0 <= nxt < self.depth and nxt % self.resident != s:
+            self._load(nxt)
+
+    def release(self, index: int) -> None:
+        """Block `index` has been enqueued: its slot may be overwritten once the work is done."""
+        if self.stream is not None:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self.free_event[index % self.resident] = ev
+
+    def write_back(self, index: int) -> None:
+        """After an in-place update of block `index`'s device copy (e.g. a merged adapter),
+        refresh the host copy."""
+        s = index % self.resident
+        if self.loaded[s] == index:
+            self.host[index].copy_(self.slots[s][: self.layouts[index].nbytes])
+
+
+class _Gate(torch.autograd.Function):
+    """Identity whose backward calls `fn` (acquire before a block's backward when placed on its
+    output, release after it when placed on its input)."""
+
+    @staticmethod
+    def forward(ctx, x, fn):
+        ctx.fn = fn
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.fn()
+        return g, None
+
+
+class StreamRunner:
+    """Wraps another runner: every execution of block i (forward, recompute, backward) happens
+    between `ring.acquire(i)` and `ring.release(i)`."""
+
+    def __init__(self, inner, ring: WeightRing):
+        self.inner, self.ring = inner, ring
+        self.name = f"{getattr(inner, 'name', 'none')}+ring{ring.resident}"
+
+    def run(self, index, block, x, ctx):
+        ring = self.ring
+
+        guarded = _Guarded(block, ring, index)
+        if torch.is_grad_enabled() and x.requires_grad:
+            x = _Gate.apply(x, lambda: ring.release(index))
+        out = self.inner.run(index, guarded, x, ctx)
+        if torch.is_grad_enabled() and isinstance(out, Tensor) and out.requires_grad:
+            out = _Gate.apply(out, lambda: ring.acquire(index, -1))
+        return out
+
+
+class _Guarded:
+    """A block (or one of its sub-blocks) executed between acquire and release; called in forward
+    and again by a checkpoint's recompute during backward."""
+
+    def __init__(self, fn, ring: WeightRing, index: int, whole=None):
+        self.fn, self.ring, self.index, self.whole = fn, ring, index, whole or fn
+
+    def __call__(self, x, ctx):
+        self.ring.acquire(self.index, -1 if _in_backward() else 1)
+        out = self.fn(x, ctx)
+        self.ring.release(self.index)
+        return out
+
+    def sub_blocks(self):
+        return [_Guarded(part, self.ring, self.index, self.whole) for part in self.whole.sub_blocks()]
+
+
+def _in_backward() -> bool:
+    try:
+        return torch._C._current_graph_task_id() != -1
+    except AttributeError:
+        return False

@@ -1,0 +1,131 @@
+"""Memory plans: what a `MEMORY_PROFILE` name turns into.
+
+A `MemoryPlan` is the resolved set of memory knobs of one run: activation checkpointing mode,
+activation offload, weight streaming, where optimiser state lives, gradient offload, fused
+in-backward step, base precision. Profiles and knob names follow the reference
+(`src/kohakumoss/memory/profiles.py:36-74`, `types/plans.py:28`); the defaults are re-tuned
+for a 180 GB B200, where the full bf16 DiT (13.7 GB), its fp32 masters and AdamW state fit
+without any streaming: `speed` is the default there, and the lower profiles exist for
+many-sample batches, full finetunes with Muon + EMA, and smaller cards of the same family.
+
+`MEMORY_PROFILE` may be a profile name, `auto` (planner picks the fastest plan that fits) or
+`manual` (only the explicit knobs count). Explicit knobs and `MEMORY_OVERRIDES` win over the
+profile.
+"""
+
+from __future__ import annotations
+
+from dataclasses import asdict, dataclass, field, replace
+
+CHECKPOINTS = ("none", "block", "sub-block", "selective")
+STREAMS = ("off", "ring", "swap")
+OPTIM_STATES = ("gpu", "stream", "cpu")
+ORDER = ("speed", "balanced", "low", "minimal")
+
+
+@dataclass(frozen=True)
+class MemoryPlan:
+    profile: str = "speed"
+    checkpoint: str = "none"          # none | block | sub-block | selective | partial:f
+    act_offload: bool = False
+    stream: str = "off"               # off | ring (weights stream through a device ring) | swap (masters on host)
+    stream_resident: int = 0          # blocks kept on the device (0 = all)
+    pinned: bool = True
+    optim_state: str = "gpu"          # gpu | stream | cpu
+    grad_offload: bool = False
+    fused_step: bool = False
+    step_release: bool = False
+    base_precision: str = "auto"
+    overrides: dict = field(default_factory=dict)
+
+    def checkpoint_mode(self) -> tuple[str, float]:
+        return checkpoint_mode(self.checkpoint)
+
+    def to_dict(self) -> dict:
+        return asdict(self)
+
+
+PROFILES: dict[str, dict] = {
+    "speed": dict(checkpoint="none", act_offload=False, stream="off", optim_state="gpu", fused_step=False),
+    "balanced": dict(checkpoint="block", act_offload=False, stream="off", optim_state="gpu", fused_step=False),
+    "low": dict(checkpoint="block", act_offload=True, stream="ring", stream_resident=16, optim_state="stream", fused_step=True),
+    "minimal": dict(checkpoint="block", act_offload=True, stream="ring", stream_resident=2, optim_state="cpu", fused_step=True,
+                    grad_offload=True),
+}
+
+
+def checkpoint_mode(value: str) -> tuple[str, float]:
+    """`"partial:0.5"` -> ("block", 0.5); otherwise (mode, 1.0) or ("none", 0.0)."""
+    if value.startswith("partial:"):
+        return "block", float(value.split(":", 1)[1])
+    return value, 0.0 if value == "none" else 1.0
+
+
+def catalog() -> dict[str, dict]:
+    """Every named plan: the four base profiles plus their variants
+    `<profile>+<checkpoint>[+fp8][+offload]`, the grid the `auto` planner searches."""
+    out = {name: dict(spec) for name, spec in PROFILES.items()}
+    for ck in ("none", "partial:0.25", "partial:0.5", "partial:0.75", "sub-block", "block"):
+        for base in ("auto", "fp8"):
+            for off in (False, True):
+                for stream, resident in (("off", 0), ("ring", 16), ("ring", 4)):
+                    for opt in OPTIM_STATES:
+                        name = f"ck={ck},base={base},act_offload={int(off)},stream={stream}{resident or ''},optim={opt}"
+                        out[name] = dict(checkpoint=ck, base_precision=base, act_offload=off, stream=stream, stream_resident=resident,
+                                         optim_state=opt, fused_step=opt != "gpu")
+    return out
+
+
+_KNOBS = {"CHECKPOINT": "checkpoint", "ACT_OFFLOAD": "act_offload", "STREAM": "stream", "STREAM_RESIDENT": "stream_resident",
+          "PINNED": "pinned", "OPTIM_STATE": "optim_state", "GRAD_OFFLOAD": "grad_offload", "FUSED_STEP": "fused_step",
+          "STEP_RELEASE": "step_release", "BASE_PRECISION": "base_precision"}
+
+
+KNOB_DEFAULTS = {"CHECKPOINT": "none", "ACT_OFFLOAD": False, "STREAM": "off", "STREAM_RESIDENT": 0, "PINNED": True, "OPTIM_STATE": "gpu",
+                 "GRAD_OFFLOAD": False, "FUSED_STEP": False, "STEP_RELEASE": False, "BASE_PRECISION": "auto"}
+
+
+def plan_problems(plan: MemoryPlan) -> list[str]:
+    out = []
+    mode, frac = checkpoint_mode(plan.checkpoint)
+    if mode not in CHECKPOINTS or not 0.0 <= frac <= 1.0:
+        out.append(f"CHECKPOINT={plan.checkpoint!r} is not one of {list(CHECKPOINTS)} or 'partial:<0..1>'")
+    if plan.stream not in STREAMS:
+        out.append(f"STREAM={plan.stream!r} is not one of {list(STREAMS)}")
+    if plan.optim_state not in OPTIM_STATES:
+        out.append(f"OPTIM_STATE={plan.optim_state!r} is not one of {list(OPTIM_STATES)}")
+    if plan.stream != "off" and plan.stream_resident < 0:
+        out.append("STREAM_RESIDENT must be >= 0")
+    if plan.grad_offload and plan.optim_state == "gpu":
+        out.append("GRAD_OFFLOAD=True needs OPTIM_STATE='stream' or 'cpu' (the step runs where the gradients land)")
+    if plan.act_offload and checkpoint_mode(plan.checkpoint)[0] == "none":
+        out.append("ACT_OFFLOAD=True needs a CHECKPOINT mode (block inputs are what is offloaded)")
+    return out
+
+
+def resolve_profile(knobs: dict, defaults: dict | None = None) -> MemoryPlan:
+    """Profile -> plan; a knob that differs from the script default, and every key of
+    `MEMORY_OVERRIDES`, wins over the profile. `auto` resolves later (`planner.plan_auto`)."""
+    name = knobs.get("MEMORY_PROFILE", "speed")
+    cat = catalog()
+    if name in ("auto", "manual"):
+        spec = {}
+    elif name in cat:
+        spec = dict(cat[name])
+    else:
+        raise ValueError(f"MEMORY_PROFILE={name!r} is not auto, manual, or one of {list(ORDER)} (or a catalog name)")
+    defaults = {**KNOB_DEFAULTS, **(defaults or {})}
+    for knob, fld in _KNOBS.items():
+        if knob in knobs and (name == "manual" or knob not in defaults or knobs[knob] != defaults[knob]):
+            spec[fld] = knobs[knob]
+    over = dict(knobs.get("MEMORY_OVERRIDES") or {})
+    spec.update({k.lower(): v for k, v in over.items() if k.lower() in MemoryPlan.__dataclass_fields__})
+    plan = MemoryPlan(profile=name, overrides=over, **spec)
+    problems = plan_problems(plan)
+    if problems:
+        raise ValueError("memory plan: " + "; ".join(problems))
+    return plan
+
+
+def with_(plan: MemoryPlan, **kw) -> MemoryPlan:
+    return replace(plan, **kw)

@@ -53,7 +53,29 @@ def trainer_config(k: dict):
         grad_acc=int(k["GRAD_ACC"]), checkpoint=k["CHECKPOINT"], timestep=k["TIMESTEP"], timestep_kwargs=dict(k["TIMESTEP_KWARGS"]),
         loss=k["LOSS"], weighting=k["WEIGHTING"], seed=int(k["SEED"]), kernels=dict(k["KERNELS"]), parallel=k["PARALLEL"],
         ddp_bucket_mb=k["DDP_BUCKET_MB"], ddp_reduce_dtype=k["DDP_REDUCE_DTYPE"], ddp_backend=k["DDP_BACKEND"],
+        fused_step=bool(k["FUSED_STEP"]) and k["PARALLEL"] == "fsdp", memory=memory_plan(k),
     )
+
+
+def memory_plan(k: dict):
+    """`MEMORY_PROFILE` and the memory knobs -> `MemoryPlan`; `auto` is planned against the
+    device this rank runs on (estimate from MAX_TOKENS, the architecture and the algorithm)."""
+    from ..memory import Workload, device_bytes, plan_auto, resolve_profile
+    from ..models.build import resolve_arch
+
+    plan = resolve_profile(k)
+    if plan.profile != "auto":
+        return plan
+    arch = resolve_arch(k["VARIANT"], k["ARCH_OVERRIDES"])
+    full = k["ALGO"] == "full"
+    lora = 0 if full else int(k["DIM"]) * 2 * arch.depth * (4 * arch.dim + 2 * (arch.dim + arch.ffn_dim))
+    work = Workload(arch, int(k["MAX_TOKENS"]), 0, trainable_params=lora, full_ft=full, world=max(1, len(k["DEVICES"] or (0,))),
+                    sharded=k["PARALLEL"] == "fsdp", ema_decays=int(float(k["EMA"] or 0) > 0),
+                    stored_precision="compute" if k["BASE_PRECISION"] in ("auto", "compute") else k["BASE_PRECISION"])
+    pinned = {f: getattr(plan, f) for f in ("checkpoint", "stream", "optim_state") if f.upper() in (plan.overrides or {})}
+    chosen, report = plan_auto(work, device_bytes(), pinned, force=bool(k["MEMORY_AUTO_FORCE"]))
+    log.info("memory plan (auto)", plan=chosen.profile, estimate_gib=round(report["estimate"]["total"] / 2**30, 1))
+    return chosen
 
 
 def build_dataset(k: dict, text_dim: int, channels: int):

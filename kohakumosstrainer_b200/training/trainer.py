@@ -62,6 +62,7 @@ class TrainerConfig:
     ddp_reduce_dtype: str = "fp32"
     ddp_backend: str = "kohakumoss"
     fused_step: bool = False           # FSDP: apply AdamW inside the reduce-scatter kernel (clip lags one step)
+    memory: object = None              # a resolved `memory.MemoryPlan` (None = CHECKPOINT only)
 
 
 class Trainer:
@@ -130,8 +131,24 @@ class Trainer:
                                         backend=cfg.ddp_backend, device=self.device)
             reduce_flags = reduce_tokens = all_reduce_sum
             finish = self.parallel.finish
-        opt = build_optimizer(named, cfg.optimizer, cfg.lr, cfg.betas, cfg.eps, cfg.weight_decay, cfg.wd_rules,
-                              cfg.optimizer_kwargs)
+        self.memory_parts = {}
+        plan = cfg.memory
+        if plan is not None:
+            from ..memory.apply import build_plan_optimizer, build_plan_runner
+
+            runner, parts = build_plan_runner(plan, self.model, self.device)
+            self.model.set_runner(runner)
+            self.memory_parts.update(parts)
+        if plan is not None and plan.optim_state != "gpu" and self.fsdp is None:
+            opt, parts = build_plan_optimizer(plan, named, cfg.optimizer, cfg.lr, cfg.betas, cfg.eps, cfg.weight_decay, cfg.wd_rules,
+                                              cfg.optimizer_kwargs)
+            self.memory_parts.update(parts)
+            off = parts.get("grad_offload")
+            if off is not None:
+                norm_params, extra_sumsq, post_step = [], (lambda: off.sumsq(self.device)), off.zero
+        else:
+            opt = build_optimizer(named, cfg.optimizer, cfg.lr, cfg.betas, cfg.eps, cfg.weight_decay, cfg.wd_rules,
+                                  cfg.optimizer_kwargs)
         if self.fsdp is not None and hasattr(opt, "shard_gather"):
             opt.shard_gather = self.fsdp.gather_update
         self.ema = ConstantEMA(named, (cfg.ema,)) if cfg.ema > 0 else None

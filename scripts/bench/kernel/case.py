@@ -1,0 +1,180 @@
+"""One kernel, one small case: the workload the profiler captures and the roofline line printed
+beside it.
+
+    python scripts/bench/kernel/case.py --op gemm_fp8 [--iters 5]
+
+Every case keeps its inputs above the L2 size (so DRAM counters mean something) and within a few
+hundred MB (so a multi-pass capture stays short). Prints one JSON line: device time (CUDA events
+around each launch, L2 flushed between launches, median), algorithmic FLOPs and bytes, and the
+fractions of the measured peaks (`MEASURED_PEAKS.json` when present).
+
+Cases: gemm_bf16, gemm_fp8, gemm_fp8_dgrad, gemm_wgrad, gemm_situ, gemm_qkrope, attn_fwd,
+attn_bwd, rms_norm_mod, rms_norm_mod_bwd, situ, quant_fp8, token_mse, adamw.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[3]))
+from kohakumosstrainer_b200.ops import native  # noqa: E402
+
+
+def peaks() -> dict:
+    for cand in (Path("MEASURED_PEAKS.json"), Path(__file__).resolve().parents[3] / "MEASURED_PEAKS.json"):
+        if cand.exists():
+            return json.loads(cand.read_text())
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "fallback": True}
+
+
+def run(fn, iters: int, warmup: int = 3) -> float:
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    return sorted(times)[len(times) // 2]
+
+
+def bf16(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).bfloat16()
+
+
+def build(op: str, tokens: int):
+    """-> (callable, flops, bytes)"""
+    M, D, F, H = tokens, 3072, 8192, 24
+    if op in ("gemm_bf16", "gemm_fp8", "gemm_fp8_dgrad", "gemm_wgrad"):
+        N, K = 9216, D
+        x, w = bf16(M, K), bf16(N, K, scale=0.02)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        flops = 2.0 * M * N * K
+        if op == "gemm_bf16":
+            return (lambda: native.gemm(x, w, out=out)), flops, 2 * (M * K + N * K + M * N)
+        xq, xs = native.quantize_fp8(x)
+        wq, ws = native.quantize_fp8(w)
+        if op == "gemm_fp8":
+            return (lambda: native.gemm(xq, wq, out=out, scale_a=xs[:1], scale_b=ws[:1])), flops, M * K + N * K + 2 * M * N
+        if op == "gemm_fp8_dgrad":
+            dy = bf16(M, N)
+            dyq, dys = native.quantize_fp8(dy, torch.float8_e5m2)
+            dx = torch.empty(M, K, device="cuda", dtype=torch.bfloat16)
+            return (lambda: native.gemm(dyq, wq, b_mn=True, out=dx, scale_a=dys[:1], scale_b=ws[:1])), flops, M * N + N * K + 2 * M * K
+        dy = bf16(M, N)
+        dw = torch.empty(N, K, device="cuda", dtype=torch.float32)
+        return (lambda: native.gemm(dy, x, a_mn=True, b_mn=True, out=dw)), flops, 2 * (M * N + M * K) + 4 * N * K
+    if op == "gemm_situ":
+        x, w = bf16(M, D), bf16(2 * F, D, scale=0.02)
+        out = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
+        return (lambda: native.gemm(x, w, out=out, epilogue=native.EPI_SITU)), 2.0 * M * 2 * F * D, 2 * (M * D + 2 * F * D + M * F)
+    if op == "gemm_qkrope":
+        from kohakumosstrainer_b200.models.components import default_bands
+
+        x, w = bf16(M, D), bf16(3 * D, D, scale=0.02)
+        out = torch.empty(M, 3 * D, device="cuda", dtype=torch.bfloat16)
+        pos = torch.zeros(M, 4, device="cuda")
+        pos[:, 1] = torch.arange(M, device="cuda") % 1024
+        table = native.rope_table(pos, default_bands(16, 10000.0, "cuda"))
+        qn, kn = torch.ones(128, device="cuda"), torch.ones(128, device="cuda")
+        call = lambda: native.gemm(x, w, out=out, epilogue=native.EPI_QK_ROPE, q_norm_w=qn, k_norm_w=kn, rope=table, rope_cols=2 * D)  # noqa: E731
+        return call, 2.0 * M * 3 * D * D, 2 * (M * D + 3 * D * D + 3 * M * D)
+    if op in ("attn_fwd", "attn_bwd"):
+        from kohakumosstrainer_b200.ops.attention import attention_varlen
+
+        seg = 4352
+        n = max(1, M // seg)
+        T = n * seg
+        q, k, v = (bf16(T, H, 128).requires_grad_(op == "attn_bwd") for _ in range(3))
+        cu = torch.arange(0, T + 1, seg, device="cuda", dtype=torch.int32)
+        lengths = (seg,) * n
+        flops = 4.0 * n * seg * seg * H * 128
+        if op == "attn_fwd":
+            with torch.no_grad():
+                return (lambda: attention_varlen(q, k, v, cu, seg, 128**-0.5, lengths)), flops, 2 * 4 * T * H * 128
+        o = attention_varlen(q, k, v, cu, seg, 128**-0.5, lengths)
+        do = torch.randn_like(o)
+
+        def bwd():
+            q.grad = k.grad = v.grad = None
+            o.backward(do, retain_graph=True)
+
+        return bwd, 2.5 * flops, 2 * 8 * T * H * 128
+    if op in ("rms_norm_mod", "rms_norm_mod_bwd", "situ", "quant_fp8", "token_mse"):
+        from kohakumosstrainer_b200.ops import native_ops
+
+        ops = native_ops.NativeOps()
+        rows = 4 * M
+        x = bf16(rows, D).requires_grad_(op.endswith("bwd"))
+        seg = (torch.arange(rows, device="cuda") // 4096).int()
+        B = int(seg.max()) + 1
+        if op.startswith("rms_norm_mod"):
+            w = torch.ones(D, device="cuda")
+            shift, scale = torch.randn(B, D, device="cuda") * 0.1, torch.randn(B, D, device="cuda") * 0.1
+            if op == "rms_norm_mod":
+                with torch.no_grad():
+                    return (lambda: ops.rms_norm_mod(x, w, shift, scale, seg, 1e-6)), 0.0, 2 * 2 * rows * D
+            y = ops.rms_norm_mod(x, w, shift, scale, seg, 1e-6)
+            dy = torch.randn_like(y)
+
+            def bwd():
+                x.grad = None
+                y.backward(dy, retain_graph=True)
+
+            return bwd, 0.0, 2 * 3 * rows * D
+        if op == "situ":
+            ug = bf16(M, 2 * F)
+            with torch.no_grad():
+                return (lambda: ops.situ_glu(ug)), 0.0, 2 * 3 * M * F
+        if op == "quant_fp8":
+            return (lambda: native.quantize_fp8(x.detach())), 0.0, rows * D * (2 + 2 + 1)
+        pred, target = bf16(rows, 128), torch.randn(rows, 128, device="cuda")
+        wt = torch.ones(B, device="cuda")
+        with torch.no_grad():
+            return (lambda: ops.token_mse(pred, target, seg, wt, None)), 0.0, rows * 128 * 6
+    if op == "adamw":
+        from kohakumosstrainer_b200.optim.adamw import FusedAdamW
+
+        params = [torch.nn.Parameter(torch.randn(4096, 3072, device="cuda")) for _ in range(6)]
+        for p in params:
+            p.grad = torch.randn_like(p)
+        opt = FusedAdamW(params, lr=1e-4)
+        n = sum(p.numel() for p in params)
+        return (lambda: opt.step()), 0.0, n * 4 * 7
+    raise SystemExit(f"unknown op {op}")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", required=True)
+    ap.add_argument("--tokens", type=int, default=8704)
+    ap.add_argument("--iters", type=int, default=5)
+    args = ap.parse_args()
+    pk = peaks()
+    fn, flops, nbytes = build(args.op, args.tokens)
+    ms = run(fn, args.iters)
+    native.check_status()
+    row = {"op": args.op, "tokens": args.tokens, "ms": round(ms, 4)}
+    suffix = "of_fallback" if pk.get("fallback") else "of_measured"
+    if flops:
+        row["tflops"] = round(flops / ms / 1e9, 1)
+        row[f"tensor_{suffix}_bf16_peak"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 3)
+    row["algorithmic_gb"] = round(nbytes / 1e9, 3)
+    row["gbs"] = round(nbytes / ms / 1e6, 1)
+    row[f"hbm_{suffix}_copy_peak"] = round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3)
+    print(json.dumps(row), flush=True)
+
+
+if __name__ == "__main__":
+    main()
