@@ -163,14 +163,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int i = 0; i < 32; ++i) { sr[i] = lo[i]; sr[32 + i] = hi[i]; }
       }
       const int valid = min(BN, seg_end - (seg_start + j * BN));
-      float mx = -INFINITY;
+      if (valid < BN) {  // the segment's last key tile: keys past the end never win the maximum and weigh 0
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        float v = __uint_as_float(sr[i]) * sc;
-        v = i < valid ? v : -INFINITY;
-        sr[i] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
+        for (int i = 0; i < 64; ++i) sr[i] = i < valid ? sr[i] : 0xff800000u;
       }
+      // row maximum of the RAW scores (the softmax scale is positive, so it commutes with max)
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 64; i += 8) {
+        m0 = max3(m0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+        m1 = max3(m1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+        m2 = max3(m2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+        m3 = max3(m3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
+      }
+      const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * sc;
       float alpha = 1.f;
       const bool grow = mx > m_used + RESCALE_THRESHOLD;
       const bool any_grow = __any_sync(0xffffffffu, grow) && j > 0;
@@ -178,14 +184,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         alpha = exp2f(m_used - mx);  // 0 on the first tile (m_used = -inf)
         m_used = mx;
       }
-      float sum = 0.f;
+      // p = 2^(s * sc - m): one packed FMA per pair, one MUFU per element, packed partial sums
+      const uint64_t sc2 = f32x2(sc, sc);
+      const uint64_t nm2 = f32x2(-m_used, -m_used);
+      uint64_t acc0 = 0ull, acc1 = 0ull, acc2 = 0ull, acc3 = 0ull;
       uint32_t pk[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float p0 = exp2f(__uint_as_float(sr[2 * i]) - m_used);
-        const float p1 = exp2f(__uint_as_float(sr[2 * i + 1]) - m_used);
-        sum += p0 + p1;
-        pk[i] = pack_bf16(p0, p1);
+      for (int i = 0; i < 32; i += 4) {
+        float a0, a1, b0, b1, c0, c1, d0, d1;
+        f32x2_split(fma_f32x2(f32x2(sr[2 * i], sr[2 * i + 1]), sc2, nm2), a0, a1);
+        f32x2_split(fma_f32x2(f32x2(sr[2 * i + 2], sr[2 * i + 3]), sc2, nm2), b0, b1);
+        f32x2_split(fma_f32x2(f32x2(sr[2 * i + 4], sr[2 * i + 5]), sc2, nm2), c0, c1);
+        f32x2_split(fma_f32x2(f32x2(sr[2 * i + 6], sr[2 * i + 7]), sc2, nm2), d0, d1);
+        a0 = ex2_approx(a0); a1 = ex2_approx(a1);
+        b0 = ex2_approx(b0); b1 = ex2_approx(b1);
+        c0 = ex2_approx(c0); c1 = ex2_approx(c1);
+        d0 = ex2_approx(d0); d1 = ex2_approx(d1);
+        acc0 = add_f32x2(acc0, f32x2(a0, a1));
+        acc1 = add_f32x2(acc1, f32x2(b0, b1));
+        acc2 = add_f32x2(acc2, f32x2(c0, c1));
+        acc3 = add_f32x2(acc3, f32x2(d0, d1));
+        pk[i] = pack_bf16(a0, a1);
+        pk[i + 1] = pack_bf16(b0, b1);
+        pk[i + 2] = pack_bf16(c0, c1);
+        pk[i + 3] = pack_bf16(d0, d1);
+      }
+      float sum;
+      {
+        float lo, hi;
+        f32x2_split(add_f32x2(add_f32x2(acc0, acc1), add_f32x2(acc2, acc3)), lo, hi);
+        sum = lo + hi;
       }
       l = l * alpha + sum;
       if (j > 0) {
@@ -402,6 +430,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const float sc = a.scale * LOG2E;
     const float lse = live ? a.lse[(size_t)head * a.n_rows + row] : INFINITY;
     const float dl = live ? a.delta[(size_t)head * a.n_rows + row] : 0.f;
+    const uint64_t sc2 = f32x2(sc, sc), nl2 = f32x2(-lse, -lse), nd2 = f32x2(-dl, -dl);
     bool ok = !*abort_flag;
     for (int j = 0; ok && j < n_kv; ++j) {
       const int st = j & 1;
@@ -415,12 +444,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tmem_ld_32x32(tmem + lane_base + DQ_TM_S + st * BN + half * 32, s_);
         tmem_ld_32x32(tmem + lane_base + DQ_TM_DP + st * BN + half * 32, d_);
         tmem_ld_wait();
+        // dS = 2^(s * sc - lse) * (dP - delta), two elements per packed instruction
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float v0 = 0.f, v1 = 0.f;
+          float e0, e1;
+          f32x2_split(fma_f32x2(f32x2(s_[2 * i], s_[2 * i + 1]), sc2, nl2), e0, e1);
+          const uint64_t p2 = f32x2(ex2_approx(e0), ex2_approx(e1));
+          float v0, v1;
+          f32x2_split(mul_f32x2(p2, add_f32x2(f32x2(d_[2 * i], d_[2 * i + 1]), nd2)), v0, v1);
           const int c0 = half * 32 + 2 * i;
-          if (c0 < valid) v0 = exp2f(__uint_as_float(s_[2 * i]) * sc - lse) * (__uint_as_float(d_[2 * i]) - dl);
-          if (c0 + 1 < valid) v1 = exp2f(__uint_as_float(s_[2 * i + 1]) * sc - lse) * (__uint_as_float(d_[2 * i + 1]) - dl);
+          if (valid < BN) {  // last key tile of the segment
+            v0 = c0 < valid ? v0 : 0.f;
+            v1 = c0 + 1 < valid ? v1 : 0.f;
+          }
           pk[half * 16 + i] = pack_bf16(v0, v1);
         }
       }
@@ -592,6 +628,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
     const bool live = key < seg_end;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const float sc = a.scale * LOG2E;
+    const uint64_t sc2 = f32x2(sc, sc);
     bool ok = !*abort_flag;
     for (int i = 0; ok && i < n_q; ++i) {
       const int st = i & 1;
@@ -621,14 +658,22 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
         tmem_ld_32x32(tmem + lane_base + KV_TM_DP + st * BQ + half * 32, d_);
         tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
+        for (int c = 0; c < 16; c += 2) {
+          // four query columns per step: their lse / delta come as one 16-byte shared load each
           const int c0 = half * 32 + 2 * c;
-          const float p0 = exp2f(__uint_as_float(s_[2 * c]) * sc - lse[c0]);
-          const float p1 = exp2f(__uint_as_float(s_[2 * c + 1]) * sc - lse[c0 + 1]);
-          const float g0 = p0 * (__uint_as_float(d_[2 * c]) - dl[c0]);
-          const float g1 = p1 * (__uint_as_float(d_[2 * c + 1]) - dl[c0 + 1]);
-          pkp[half * 16 + c] = pack_bf16(p0, p1);
+          const float4 l4 = *reinterpret_cast<const float4*>(lse + c0);
+          const float4 d4 = *reinterpret_cast<const float4*>(dl + c0);
+          float e0, e1, e2, e3;
+          f32x2_split(fma_f32x2(f32x2(s_[2 * c], s_[2 * c + 1]), sc2, f32x2(-l4.x, -l4.y)), e0, e1);
+          f32x2_split(fma_f32x2(f32x2(s_[2 * c + 2], s_[2 * c + 3]), sc2, f32x2(-l4.z, -l4.w)), e2, e3);
+          e0 = ex2_approx(e0); e1 = ex2_approx(e1); e2 = ex2_approx(e2); e3 = ex2_approx(e3);
+          float g0, g1, g2, g3;
+          f32x2_split(mul_f32x2(f32x2(e0, e1), add_f32x2(f32x2(d_[2 * c], d_[2 * c + 1]), f32x2(-d4.x, -d4.y))), g0, g1);
+          f32x2_split(mul_f32x2(f32x2(e2, e3), add_f32x2(f32x2(d_[2 * c + 2], d_[2 * c + 3]), f32x2(-d4.z, -d4.w))), g2, g3);
+          pkp[half * 16 + c] = pack_bf16(e0, e1);
+          pkp[half * 16 + c + 1] = pack_bf16(e2, e3);
           pkd[half * 16 + c] = pack_bf16(g0, g1);
+          pkd[half * 16 + c + 1] = pack_bf16(g2, g3);
         }
       }
       if (!mbar_wait(bar(9 + st), ((i >> 1) & 1) ^ 1, abort_flag, a.status, 880 + st)) { ok = false; break; }

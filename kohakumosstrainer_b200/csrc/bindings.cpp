@@ -14,6 +14,7 @@
 #include "comm.cuh"
 #include "gemm_sm100.cuh"
 #include "optim.cuh"
+#include "quant.cuh"
 
 namespace {
 
@@ -42,6 +43,7 @@ int gemm_dtype_of(const Tensor& t) {
     case at::kBFloat16: return kmoss::GEMM_BF16;
     case at::kFloat8_e4m3fn: return kmoss::GEMM_E4M3;
     case at::kFloat8_e5m2: return kmoss::GEMM_E5M2;
+    case at::kChar: return kmoss::GEMM_S8;
     default: TORCH_CHECK(false, "gemm operand must be bf16, float8_e4m3fn or float8_e5m2, got ", t.scalar_type());
   }
 }
@@ -355,6 +357,42 @@ std::tuple<Tensor, Tensor> quantize_fp8_rows(const Tensor& x) {
   return {q, rs};
 }
 
+Tensor group_hadamard(const Tensor& x, int64_t group) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "group_hadamard: bf16 rows");
+  Tensor y = at::empty({x.size(0), x.size(1)}, x.options());
+  KM_CHECK_CUDA(kmoss::group_hadamard(x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), (int)x.size(0), (int)x.size(1), (int)group,
+                                      cur_stream()));
+  return y;
+}
+
+std::tuple<Tensor, Tensor> quantize_int8_rows(const Tensor& x, int64_t group) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "quantize_int8_rows: bf16 rows");
+  Tensor q = at::empty({x.size(0), x.size(1)}, x.options().dtype(at::kChar));
+  Tensor rs = at::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  KM_CHECK_CUDA(kmoss::quant_rows_int8(x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), rs.data_ptr<float>(), (int)x.size(0),
+                                       (int)x.size(1), (int)group, cur_stream()));
+  return {q, rs};
+}
+
+void cast_int8_bf16(const Tensor& q, Tensor& y) {
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.scalar_type() == at::kChar && y.scalar_type() == at::kBFloat16 && q.is_contiguous() && y.is_contiguous() &&
+                  q.numel() == y.numel(), "cast_int8_bf16: contiguous int8 -> bf16 of equal size");
+  KM_CHECK_CUDA(kmoss::cast_int8_bf16(q.data_ptr(), y.data_ptr(), q.numel(), cur_stream()));
+}
+
+std::tuple<Tensor, Tensor> quantize_mxfp8(const Tensor& x) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && x.size(1) % 32 == 0, "quantize_mxfp8: bf16 rows, K % 32 == 0");
+  Tensor q = at::empty({x.size(0), x.size(1)}, x.options().dtype(at::kFloat8_e4m3fn));
+  Tensor sc = at::empty({x.size(0), x.size(1) / 32}, x.options().dtype(at::kByte));
+  KM_CHECK_CUDA(kmoss::quant_mxfp8(x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), sc.data_ptr(), sc.stride(0), (int)x.size(0),
+                                   (int)x.size(1), cur_stream()));
+  return {q, sc};
+}
+
 
 // ---- optimiser ---------------------------------------------------------------------------
 // `table` is a uint8 CUDA tensor holding OptTensor records, `chunks` an int32 [n, 2] CUDA tensor.
@@ -571,4 +609,8 @@ TORCH_LIBRARY(kmoss_b200, m) {
   m.def("quantize_fp8_tensor(Tensor x, bool e5m2) -> (Tensor, Tensor)", &quantize_fp8_tensor);
   m.def("cast_fp8(Tensor x, Tensor qscale, Tensor(a!) q) -> ()", &cast_fp8);
   m.def("quantize_fp8_rows(Tensor x) -> (Tensor, Tensor)", &quantize_fp8_rows);
+  m.def("group_hadamard(Tensor x, int group) -> Tensor", &group_hadamard);
+  m.def("quantize_int8_rows(Tensor x, int group) -> (Tensor, Tensor)", &quantize_int8_rows);
+  m.def("cast_int8_bf16(Tensor q, Tensor(a!) y) -> ()", &cast_int8_bf16);
+  m.def("quantize_mxfp8(Tensor x) -> (Tensor, Tensor)", &quantize_mxfp8);
 }

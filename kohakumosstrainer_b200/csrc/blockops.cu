@@ -33,6 +33,16 @@ __device__ __forceinline__ void load8f(const float* p, float (&v)[8]) {
   float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
   v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
+// fp32 modulation vectors: one 2 x 16-byte load when the row is 16-byte aligned (the usual
+// [B, 6, D] layout), eight scalar loads otherwise
+__device__ __forceinline__ void load8m(const float* p, bool vec, float (&v)[8]) {
+  if (vec) {
+    load8f(p, v);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = p[j];
+  }
+}
 // weight vectors may be bf16 or fp32 (fp32 masters)
 __device__ __forceinline__ void load8w(const void* p, int is_f32, int idx, float (&v)[8]) {
   if (is_f32) load8f(reinterpret_cast<const float*>(p) + idx, v);
@@ -69,16 +79,19 @@ rms_norm_mod_fwd_kernel(NormModArgs a) {
   __nv_bfloat16* y = a.y + (size_t)row * a.ldy;
   float amax = 0.f;
   const float qs = a.q_scale != nullptr ? *a.q_scale : 1.f;
+  const bool vec_mod = ((reinterpret_cast<uintptr_t>(shift) | reinterpret_cast<uintptr_t>(scale)) & 15) == 0;
   for (int i = lane * 8; i < a.dim; i += 256) {
-    float v[8], w[8];
+    float v[8], w[8], sc8[8], sh8[8];
     load8(x + i, v);
     if (a.w != nullptr) load8w(a.w, a.w_f32, i, w);
+    if (scale != nullptr) load8m(scale + i, vec_mod, sc8);
+    if (shift != nullptr) load8m(shift + i, vec_mod, sh8);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float t = v[j] * rstd;
       if (a.w != nullptr) t *= w[j];
-      if (scale != nullptr) t *= 1.f + scale[i + j];
-      if (shift != nullptr) t += shift[i + j];
+      if (scale != nullptr) t *= 1.f + sc8[j];
+      if (shift != nullptr) t += sh8[j];
       v[j] = t;
     }
     store8(y + i, v);
@@ -117,16 +130,18 @@ rms_norm_mod_bwd_kernel(NormModBwdArgs a) {
   const int s = a.seg != nullptr ? a.seg[row] : 0;
   const float* scale = a.scale != nullptr ? a.scale + (size_t)s * a.mod_stride : nullptr;
   float dot = 0.f;
+  const bool vec_mod = (reinterpret_cast<uintptr_t>(scale) & 15) == 0;
   for (int i = lane * 8; i < a.dim; i += 256) {
-    float v[8], g[8], w[8];
+    float v[8], g[8], w[8], sc8[8];
     load8(x + i, v);
     load8(dy + i, g);
     if (a.w != nullptr) load8w(a.w, a.w_f32, i, w);
+    if (scale != nullptr) load8m(scale + i, vec_mod, sc8);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float t = g[j];
       if (a.w != nullptr) t *= w[j];
-      if (scale != nullptr) t *= 1.f + scale[i + j];
+      if (scale != nullptr) t *= 1.f + sc8[j];
       dot += t * v[j] * rstd;
     }
   }
@@ -134,16 +149,17 @@ rms_norm_mod_bwd_kernel(NormModBwdArgs a) {
   __nv_bfloat16* dx = a.dx + (size_t)row * a.lddx;
   const __nv_bfloat16* dres = a.dres != nullptr ? a.dres + (size_t)row * a.lddres : nullptr;
   for (int i = lane * 8; i < a.dim; i += 256) {
-    float v[8], g[8], w[8], r[8];
+    float v[8], g[8], w[8], r[8], sc8[8];
     load8(x + i, v);
     load8(dy + i, g);
     if (a.w != nullptr) load8w(a.w, a.w_f32, i, w);
     if (dres != nullptr) load8(dres + i, r);
+    if (scale != nullptr) load8m(scale + i, vec_mod, sc8);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float t = g[j];
       if (a.w != nullptr) t *= w[j];
-      if (scale != nullptr) t *= 1.f + scale[i + j];
+      if (scale != nullptr) t *= 1.f + sc8[j];
       float o = rstd * (t - v[j] * rstd * dot);
       if (dres != nullptr) o += a.dres_scale * r[j];
       v[j] = o;

@@ -41,6 +41,7 @@ struct DeviceParams {
   int has_bypass;  // 1 when T / U maps are valid
   int R;
   int a_e5m2, b_e5m2;
+  int int8;  // operands are signed int8, the accumulator holds int32 (linear epilogue only)
   int epilogue;
   void* out;
   long ldo;
@@ -420,7 +421,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       // Operand formats: bf16 = 1 for kind::f16; e4m3 = 0 / e5m2 = 1 for kind::f8f6f4.
       const uint32_t fmt_a = FP8 ? (uint32_t)p.a_e5m2 : 1u;
       const uint32_t fmt_b = FP8 ? (uint32_t)p.b_e5m2 : 1u;
-      const uint32_t idesc = idesc_main | (fmt_a << 7) | (fmt_b << 10);
+      // kind::i8: accumulator format S32 (2) instead of F32 (1), operand format S8 = 1
+      const uint32_t idesc = p.int8 ? ((idesc_main & ~(3u << 4)) | (2u << 4) | (1u << 7) | (1u << 10))
+                                    : (idesc_main | (fmt_a << 7) | (fmt_b << 10));
       const uint32_t idesc_bypass = umma_idesc(1, 1, 0, 0, BM, BN);
       for (int tile = blockIdx.x; tile < p.total_tiles; tile += compute_ctas) {
         int m_blk, n_blk, split;
@@ -458,8 +461,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           for (int k = 0; k < C::K_STEPS; ++k) {
             const uint64_t ad = a_desc + (uint64_t)((k * C::A_KSTEP) >> 4);
             const uint64_t bd = b_desc + (uint64_t)((k * C::B_KSTEP) >> 4);
-            if constexpr (FP8) mma_f8_ss(d_tmem, ad, bd, idesc, accumulate);
-            else mma_f16_ss(d_tmem, ad, bd, idesc, accumulate);
+            if constexpr (FP8) {
+              if (p.int8) mma_i8_ss(d_tmem, ad, bd, idesc, accumulate);
+              else mma_f8_ss(d_tmem, ad, bd, idesc, accumulate);
+            } else {
+              mma_f16_ss(d_tmem, ad, bd, idesc, accumulate);
+            }
             accumulate = 1;
           }
           tc_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
@@ -529,7 +536,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         // (acc * s [* col] + bias) [* gate] [+ beta * res] on 32 columns starting at n0
         auto linear32 = [&](const uint32_t (&r)[32], int n0, float (&v)[32]) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * row_s;
+          for (int j = 0; j < 32; ++j) v[j] = (p.int8 ? (float)(int)r[j] : __uint_as_float(r[j])) * row_s;
           if (has_col) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
@@ -729,7 +736,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           if (row_ok && n0 < p.N) {
             float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            for (int j = 0; j < 32; ++j) v[j] = p.int8 ? (float)(int)r[j] : __uint_as_float(r[j]);
             linear_epilogue_chunk(p, m, n0, row_s, seg_m, v);
             store_row_chunk(p, m, n0, v);
           }
@@ -1071,6 +1078,9 @@ cudaError_t gemm_launch(const GemmProblem& g, cudaStream_t stream) {
   if (g.M <= 0 || g.N <= 0) return cudaSuccess;
   const bool fp8 = g.a_dtype != GEMM_BF16;
   if (fp8 != (g.b_dtype != GEMM_BF16)) return cudaErrorInvalidValue;
+  if ((g.a_dtype == GEMM_S8) != (g.b_dtype == GEMM_S8)) return cudaErrorInvalidValue;
+  if (g.a_dtype == GEMM_S8 && (g.epilogue != EPI_LINEAR || g.a_mn || g.b_mn || g.splits > 1 || (g.T != nullptr && g.R > 0)))
+    return cudaErrorInvalidValue;  // integer accumulators: plain K-major product with the linear epilogue only
   const int eb = fp8 ? 1 : 2;
   // TMA needs 16-byte aligned bases and row strides.
   if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.B) & 15)) return cudaErrorMisalignedAddress;
@@ -1086,6 +1096,7 @@ cudaError_t gemm_launch(const GemmProblem& g, cudaStream_t stream) {
   }
   p.R = g.R;
   p.a_e5m2 = g.a_dtype == GEMM_E5M2 ? 1 : 0;
+  p.int8 = g.a_dtype == GEMM_S8 ? 1 : 0;
   p.b_e5m2 = g.b_dtype == GEMM_E5M2 ? 1 : 0;
   p.epilogue = g.epilogue;
   p.out = g.out; p.ldo = g.ldo; p.out_dtype = g.out_dtype;

@@ -6,7 +6,7 @@
 
 namespace kmoss {
 
-enum GemmDtype : int { GEMM_BF16 = 0, GEMM_E4M3 = 1, GEMM_E5M2 = 2 };
+enum GemmDtype : int { GEMM_BF16 = 0, GEMM_E4M3 = 1, GEMM_E5M2 = 2, GEMM_S8 = 3 };  // S8: int8 x int8 -> int32 (kind::i8), EPI_LINEAR only
 enum GemmOut : int { OUT_BF16 = 0, OUT_F32 = 1 };
 enum GemmEpilogue : int {
   EPI_LINEAR = 0,   // out = (acc*s + bias) * gate[seg[m], n] + beta * res[m, n]

@@ -1,0 +1,233 @@
+// Quantisation helpers around the GEMM family (sm_100a):
+//   * group_hadamard: x . blockdiag(H_g), g = 4^j, regular (not Sylvester) Hadamard built as the
+//     Kronecker power of H4 = [[1,1,1,-1],[1,1,-1,1],[1,-1,1,1],[-1,1,1,1]] / 2; fp32 butterflies
+//     in shared memory, one rounding at the store;
+//   * quant_rows_int8: per-row symmetric int8 with an optional fused group rotation (ConvRot:
+//     the activation is rotated and quantised in one pass over memory);
+//   * cast_int8_bf16: exact widening of stored int8 weights (the per-channel scale is applied in
+//     the GEMM epilogue, so weight-only int8 costs one cast pass and no extra rounding);
+//   * quant_mxfp8: OCP microscaling e4m3 with one UE8M0 scale per 32 elements along K.
+// All kernels are bandwidth bound: 128-bit global accesses, one block per row (or row tile).
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "quant.cuh"
+
+namespace kmoss {
+namespace {
+
+// One 4-point stage of the regular Hadamard transform on digit `a` (stride 4^a), in place in
+// shared memory: y_k = (x0 + x1 + x2 + x3) - 2 x_(3-k). `n` elements, `n / 4` butterflies.
+__device__ __forceinline__ void hadamard_stage(float* buf, int n, int stride, int tid, int nthreads) {
+  for (int b = tid; b < n / 4; b += nthreads) {
+    const int lo = b % stride;
+    const int hi = b / stride;
+    const int base = hi * stride * 4 + lo;
+    const float x0 = buf[base], x1 = buf[base + stride], x2 = buf[base + 2 * stride], x3 = buf[base + 3 * stride];
+    const float total = ((x0 + x1) + x2) + x3;
+    buf[base] = total - 2.f * x3;
+    buf[base + stride] = total - 2.f * x2;
+    buf[base + 2 * stride] = total - 2.f * x1;
+    buf[base + 3 * stride] = total - 2.f * x0;
+  }
+}
+
+// Rotate a row held in shared memory: groups of `group` consecutive elements, `stages` = log4(group).
+// The Kronecker power applies H4 to every base-4 digit of the in-group index; digit d has stride
+// 4^(stages - 1 - d) for the left-most factor first, and the factors commute, so any order works.
+__device__ __forceinline__ void rotate_row(float* buf, int dim, int group, int stages, int tid, int nthreads) {
+  int stride = 1;
+  for (int s = 0; s < stages; ++s) {
+    hadamard_stage(buf, dim, stride, tid, nthreads);  // butterflies never cross a group: stride * 4 <= group
+    stride *= 4;
+    __syncthreads();
+  }
+  const float norm = 1.f / (float)(1 << stages);
+  for (int i = tid; i < dim; i += nthreads) buf[i] *= norm;
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(256) hadamard_kernel(const __nv_bfloat16* x, long ldx, __nv_bfloat16* y, long ldy, int rows,
+                                                       int dim, int group, int stages) {
+  extern __shared__ float buf[];
+  const int row = blockIdx.x;
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + (long)row * ldx;
+  for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      buf[i + 2 * j] = f.x;
+      buf[i + 2 * j + 1] = f.y;
+    }
+  }
+  __syncthreads();
+  rotate_row(buf, dim, group, stages, threadIdx.x, blockDim.x);
+  __nv_bfloat16* yr = y + (long)row * ldy;
+  for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
+    uint4 v;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(buf[i + 2 * j], buf[i + 2 * j + 1]);
+    *reinterpret_cast<uint4*>(yr + i) = v;
+  }
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float w = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) w = fmaxf(w, __shfl_xor_sync(0xffffffffu, w, o));
+    if (lane == 0) red[0] = w;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+__global__ void __launch_bounds__(256) quant_rows_int8_kernel(const __nv_bfloat16* x, long ldx, int8_t* q, long ldq, float* row_scale,
+                                                              int rows, int dim, int group, int stages) {
+  extern __shared__ float buf[];
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + (long)row * ldx;
+  for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      buf[i + 2 * j] = f.x;
+      buf[i + 2 * j + 1] = f.y;
+    }
+  }
+  __syncthreads();
+  if (stages > 0) rotate_row(buf, dim, group, stages, threadIdx.x, blockDim.x);
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) amax = fmaxf(amax, fabsf(buf[i]));
+  amax = block_max(amax, red);
+  const float scale = amax > 0.f ? amax / 127.f : 1.f;
+  const float inv = 1.f / scale;
+  if (threadIdx.x == 0) row_scale[row] = scale;
+  int8_t* qr = q + (long)row * ldq;
+  for (int i = threadIdx.x * 16; i < dim; i += blockDim.x * 16) {
+    uint4 v;
+    int8_t* b = reinterpret_cast<int8_t*>(&v);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float r = rintf(buf[i + j] * inv);
+      b[j] = (int8_t)fminf(fmaxf(r, -127.f), 127.f);
+    }
+    *reinterpret_cast<uint4*>(qr + i) = v;
+  }
+}
+
+__global__ void __launch_bounds__(256) cast_int8_bf16_kernel(const int8_t* q, __nv_bfloat16* y, long n) {
+  const long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 16;
+  if (i >= n) return;
+  const uint4 v = *reinterpret_cast<const uint4*>(q + i);
+  const int8_t* b = reinterpret_cast<const int8_t*>(&v);
+  uint4 o[2];
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(o);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn((float)b[2 * j], (float)b[2 * j + 1]);
+  *reinterpret_cast<uint4*>(y + i) = o[0];
+  *reinterpret_cast<uint4*>(y + i + 8) = o[1];
+}
+
+// One warp per (row, 32 x 32-element span): lane l owns block l of 32 consecutive elements.
+__global__ void __launch_bounds__(256) quant_mxfp8_kernel(const __nv_bfloat16* x, long ldx, uint8_t* q, long ldq, uint8_t* scales,
+                                                          long lds, int rows, int dim) {
+  const int blocks_per_row = dim / 32;
+  const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long row = gid / blocks_per_row;
+  const int blk = (int)(gid % blocks_per_row);
+  if (row >= rows) return;
+  const __nv_bfloat16* src = x + row * ldx + blk * 32;
+  float v[32];
+  float amax = 0.f;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint4 u = *reinterpret_cast<const uint4*>(src + c * 8);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      v[c * 8 + 2 * j] = f.x;
+      v[c * 8 + 2 * j + 1] = f.y;
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+  // UE8M0: scale = 2^e with e = ceil(log2(amax / 448)); stored byte = e + 127
+  int e = -127;
+  if (amax > 0.f) {
+    int ex;
+    const float m = frexpf(amax / 448.f, &ex);  // amax / 448 = m * 2^ex, m in [0.5, 1)
+    e = (m == 0.5f) ? ex - 1 : ex;
+    e = max(-127, min(127, e));
+  }
+  scales[row * lds + blk] = (uint8_t)(e + 127);
+  const float inv = exp2f((float)-e);
+  uint4 out[2];
+  uint8_t* o = reinterpret_cast<uint8_t*>(out);
+#pragma unroll
+  for (int j = 0; j < 32; ++j) o[j] = (uint8_t)__nv_cvt_float_to_fp8(v[j] * inv, __NV_SATFINITE, __NV_E4M3);
+  uint8_t* dst = q + row * ldq + blk * 32;
+  *reinterpret_cast<uint4*>(dst) = out[0];
+  *reinterpret_cast<uint4*>(dst + 16) = out[1];
+}
+
+int stages_of(int group) {
+  int j = 0;
+  while (group > 1 && group % 4 == 0) { group /= 4; ++j; }
+  return group == 1 ? j : -1;
+}
+
+}  // namespace
+
+cudaError_t group_hadamard(const void* x, long ldx, void* y, long ldy, int rows, int dim, int group, cudaStream_t stream) {
+  const int stages = stages_of(group);
+  if (stages <= 0 || dim % group || dim % 8 || dim > 8192) return cudaErrorInvalidValue;
+  if (rows == 0) return cudaSuccess;
+  hadamard_kernel<<<rows, 256, dim * sizeof(float), stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx,
+                                                              reinterpret_cast<__nv_bfloat16*>(y), ldy, rows, dim, group, stages);
+  return cudaGetLastError();
+}
+
+cudaError_t quant_rows_int8(const void* x, long ldx, void* q, long ldq, float* row_scale, int rows, int dim, int group,
+                            cudaStream_t stream) {
+  const int stages = group > 1 ? stages_of(group) : 0;
+  if (stages < 0 || (group > 1 && dim % group) || dim % 16 || dim > 8192) return cudaErrorInvalidValue;
+  if (rows == 0) return cudaSuccess;
+  quant_rows_int8_kernel<<<rows, 256, dim * sizeof(float), stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx,
+                                                                     reinterpret_cast<int8_t*>(q), ldq, row_scale, rows, dim, group, stages);
+  return cudaGetLastError();
+}
+
+cudaError_t cast_int8_bf16(const void* q, void* y, long n, cudaStream_t stream) {
+  if (n % 16) return cudaErrorInvalidValue;
+  if (n == 0) return cudaSuccess;
+  const long threads = n / 16;
+  cast_int8_bf16_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const int8_t*>(q),
+                                                                                 reinterpret_cast<__nv_bfloat16*>(y), n);
+  return cudaGetLastError();
+}
+
+cudaError_t quant_mxfp8(const void* x, long ldx, void* q, long ldq, void* scales, long lds, int rows, int dim, cudaStream_t stream) {
+  if (dim % 32 || ldx % 8 || ldq % 16) return cudaErrorInvalidValue;
+  if (rows == 0) return cudaSuccess;
+  const long total = (long)rows * (dim / 32);
+  quant_mxfp8_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx,
+                                                                          reinterpret_cast<uint8_t*>(q), ldq,
+                                                                          reinterpret_cast<uint8_t*>(scales), lds, rows, dim);
+  return cudaGetLastError();
+}
+
+}  // namespace kmoss

@@ -1,0 +1,17 @@
+// Host entry points of quant.cu (rotation, int8 row quantiser, int8 widening, MXFP8 quantiser).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace kmoss {
+
+// y = x . blockdiag(H_group) over the last dim (bf16 rows, fp32 butterflies); group = 4^j, dim <= 8192.
+cudaError_t group_hadamard(const void* x, long ldx, void* y, long ldy, int rows, int dim, int group, cudaStream_t stream);
+// Per-row symmetric int8: q = round(rot(x) / s), s = amax / 127; `group` <= 1 skips the rotation.
+cudaError_t quant_rows_int8(const void* x, long ldx, void* q, long ldq, float* row_scale, int rows, int dim, int group,
+                            cudaStream_t stream);
+// y[i] = (bf16) q[i] for n int8 values (n multiple of 16).
+cudaError_t cast_int8_bf16(const void* q, void* y, long n, cudaStream_t stream);
+// e4m3 payload + one UE8M0 byte per 32 elements along the row (scales [rows, dim / 32], row stride lds).
+cudaError_t quant_mxfp8(const void* x, long ldx, void* q, long ldq, void* scales, long lds, int rows, int dim, cudaStream_t stream);
+
+}  // namespace kmoss

@@ -1,0 +1,278 @@
+"""Stored-weight formats beyond per-tensor / per-row fp8: int8 (weight-only or int8 compute,
+optionally ConvRot-rotated) and MXFP8 (e4m3 payload, one UE8M0 scale per 32 input features).
+
+Semantics follow the reference (`src/kohakumoss/quant/weights.py`, `quant/compute.py:45-164`,
+kernels `quant_linear`, `quant_linear_rotated`, `int8_linear`, `group_hadamard` of
+`src/kohakumoss_kernels/ops.py`):
+
+* weight-only: `y = (x q^T) * scale + b`, activations stay 16-bit; dgrad `dy (q * scale)`;
+* rotated (ConvRot): the stored weight is `Q(W R)` for the group-Hadamard rotation R (its own
+  inverse), and the linear computes `(x R) Q(W R)^T`; dgrad is rotated back;
+* int8 compute: `y = Q_rows(x R) q^T * s_x s_w + b` with int32 accumulation.
+
+On a B200: the rotation and the per-row int8 quantiser are ONE kernel over the activation
+(`csrc/quant.cu`), the int8 product is the tcgen05 `kind::i8` GEMM with both scales in its
+epilogue, and weight-only int8 is an exact int8 -> bf16 widening into a reused staging buffer
+followed by the bf16 GEMM with the channel scale in the epilogue. The CPU path is plain torch
+with the same rounding points.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+BF16 = torch.bfloat16
+H4 = ((1, 1, 1, -1), (1, 1, -1, 1), (1, -1, 1, 1), (-1, 1, 1, 1))
+
+
+def hadamard_stages(group: int) -> int:
+    j, g = 0, int(group)
+    while g > 1 and g % 4 == 0:
+        g //= 4
+        j += 1
+    if g != 1 or j == 0:
+        raise ValueError(f"Hadamard group {group} is not a power of 4 >= 4")
+    return j
+
+
+def hadamard_matrix(group: int, dtype=torch.float32, device="cpu") -> Tensor:
+    j = hadamard_stages(group)
+    h4 = torch.tensor(H4, dtype=torch.float32)
+    h = h4
+    for _ in range(j - 1):
+        h = torch.kron(h, h4)
+    return (h * 2.0**-j).to(device=device, dtype=dtype)
+
+
+def _native(x: Tensor) -> bool:
+    return x.is_cuda and x.dtype == BF16
+
+
+class _Hadamard(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        from ..ops import native
+
+        ctx.group = group
+        return native.load().group_hadamard(x.reshape(-1, x.shape[-1]).contiguous(), group).reshape(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import native
+
+        return native.load().group_hadamard(dy.reshape(-1, dy.shape[-1]).contiguous(), ctx.group).reshape(dy.shape), None
+
+
+def group_hadamard(x: Tensor, group: int) -> Tensor:
+    """x . blockdiag(H_group) over the last dim (self-inverse, self-adjoint)."""
+    hadamard_stages(group)
+    if x.shape[-1] % group:
+        raise ValueError(f"last dim {x.shape[-1]} is not a multiple of group {group}")
+    if _native(x) and x.shape[-1] <= 8192 and x.shape[-1] % 8 == 0:
+        return _Hadamard.apply(x, group)
+    h = hadamard_matrix(group, torch.float32, x.device)
+    return (x.float().reshape(-1, group) @ h).reshape(x.shape).to(x.dtype)
+
+
+def quantize_rows_int8(x: Tensor, group: int = 0) -> tuple[Tensor, Tensor]:
+    """(q int8 [M, K], scale fp32 [M]) of rot(x): symmetric, scale = amax / 127."""
+    if _native(x) and x.shape[-1] % 16 == 0 and x.shape[-1] <= 8192:
+        from ..ops import native
+
+        return native.load().quantize_int8_rows(x.contiguous(), group)
+    v = group_hadamard(x.float(), group) if group > 1 else x.float()
+    amax = v.abs().amax(-1)
+    scale = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+    return torch.clamp(torch.round(v / scale[:, None]), -127, 127).to(torch.int8), scale.float()
+
+
+def quantize_weight_int8(w: Tensor, group: int = 0) -> tuple[Tensor, Tensor]:
+    """Per-output-channel symmetric int8 of (rotated) W [N, K] (one-off: plain torch)."""
+    v = w.detach().float()
+    if group > 1:
+        v = (v.reshape(-1, group) @ hadamard_matrix(group, torch.float32, v.device)).reshape(v.shape)
+    amax = v.abs().amax(1)
+    scale = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+    return torch.clamp(torch.round(v / scale[:, None]), -127, 127).to(torch.int8), scale.float()
+
+
+class _Staging:
+    """One reusable bf16 buffer per (device, numel): the widened copy of the int8 weight lives
+    only for the GEMM that reads it (126 MB of L2 keep most of a projection resident)."""
+
+    bufs: dict = {}
+
+    @classmethod
+    def get(cls, device, shape) -> Tensor:
+        n = shape[0] * shape[1]
+        key = (str(device), n)
+        if key not in cls.bufs:
+            cls.bufs[key] = torch.empty(n, dtype=BF16, device=device)
+        return cls.bufs[key].view(shape)
+
+
+def _widen(q: Tensor) -> Tensor:
+    from ..ops import native
+
+    out = _Staging.get(q.device, tuple(q.shape))
+    native.load().cast_int8_bf16(q.contiguous(), out)
+    return out
+
+
+class _Int8LinearFn(torch.autograd.Function):
+    """int8 x int8 compute (`compute=True`) or weight-only (`compute=False`); native kernels on a
+    B200, the same rounding points in plain torch elsewhere."""
+
+    @staticmethod
+    def forward(ctx, x, q, w_scale, bias, group, compute):
+        x2 = x.reshape(-1, x.shape[-1])
+        ctx.save_for_backward(q, w_scale)
+        ctx.group, ctx.shape = group, x.shape
+        ctx.native = _native(x) and x.shape[-1] % 16 == 0 and q.shape[0] % 16 == 0 and x.shape[-1] <= 8192
+        if ctx.native:
+            from ..ops import native
+
+            if compute:
+                xq, xs = quantize_rows_int8(x2, group)
+                y = native.gemm(xq, q, row_scale=xs, col_scale=w_scale, bias=bias)
+            else:
+                xr = group_hadamard(x2, group) if group > 1 else x2.contiguous()
+                y = native.gemm(xr, _widen(q), col_scale=w_scale, bias=bias)
+        else:
+            if compute:
+                xq, xs = quantize_rows_int8(x2, group)
+                y = (xq.float() @ q.float().t()) * xs[:, None] * w_scale[None, :]
+            else:
+                xr = group_hadamard(x2, group) if group > 1 else x2
+                y = xr.float() @ (q.float() * w_scale[:, None]).t()
+            y = (y if bias is None else y + bias.float()).to(x.dtype)
+        return y.reshape(*x.shape[:-1], q.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        q, w_scale = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if ctx.native:
+            from ..ops import native
+
+            scaled = (dy2.float() * w_scale[None, :]).to(BF16)      # the channel scale sits on the contraction dim: fold it into dy
+            dx = native.gemm(scaled, _widen(q), b_mn=True)
+        else:
+            dx = ((dy2.float() * w_scale[None, :]) @ q.float()).to(dy.dtype)
+        if ctx.group > 1:
+            dx = group_hadamard(dx, ctx.group)
+        return dx.reshape(ctx.shape), None, None, None, None, None
+
+
+class _FrozenDenseFn(torch.autograd.Function):
+    """y = x W^T + b with a frozen bf16 W on the native GEMM (forward K-major, dgrad MN-major)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        from ..ops import native
+
+        ctx.save_for_backward(w)
+        ctx.shape = x.shape
+        return native.gemm(x.reshape(-1, x.shape[-1]).contiguous(), w, bias=bias).reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import native
+
+        (w,) = ctx.saved_tensors
+        return native.gemm(dy.reshape(-1, dy.shape[-1]).contiguous(), w, b_mn=True).reshape(ctx.shape), None, None
+
+
+class Int8Weight:
+    """Stored int8 weight: `kind="int8"`; `compute=True` also quantises activations."""
+
+    kind = "int8"
+
+    def __init__(self, q: Tensor, scale: Tensor, group: int = 0, compute: bool = False):
+        self.q, self.scale, self.group, self.compute = q, scale, int(group), bool(compute)
+
+    @classmethod
+    def from_dense(cls, w: Tensor, group: int = 0, compute: bool = False) -> "Int8Weight":
+        q, s = quantize_weight_int8(w, group)
+        return cls(q, s, group, compute)
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+    def weight(self, dtype=BF16) -> Tensor:
+        w = self.q.float() * self.scale[:, None]
+        if self.group > 1:
+            w = (w.reshape(-1, self.group) @ hadamard_matrix(self.group, torch.float32, w.device)).reshape(w.shape)
+        return w.to(dtype)
+
+    def linear(self, x: Tensor, bias: Tensor | None) -> Tensor:
+        return _Int8LinearFn.apply(x, self.q, self.scale, bias, self.group, self.compute)
+
+    def _apply(self, fn) -> None:
+        self.q = fn(self.q)      # module casts leave integer tensors alone
+        self.scale = fn(self.scale).float()
+
+    def state(self, prefix: str) -> dict[str, Tensor]:
+        out = {prefix + "weight": self.q, prefix + "weight_scale": self.scale}
+        if self.group > 1:
+            out[prefix + "rotation_group"] = torch.tensor(self.group, dtype=torch.int32)
+        return out
+
+
+# ---- MXFP8 ---------------------------------------------------------------------------------------
+def quantize_mxfp8(x: Tensor) -> tuple[Tensor, Tensor]:
+    """(e4m3 payload [M, K], UE8M0 scale bytes [M, K / 32]): scale = 2^ceil(log2(amax / 448))."""
+    if _native(x) and x.dim() == 2:
+        from ..ops import native
+
+        return native.load().quantize_mxfp8(x.contiguous())
+    v = x.float().reshape(x.shape[0], -1, 32)
+    amax = v.abs().amax(-1)
+    e = torch.where(amax > 0, torch.ceil(torch.log2(amax / 448.0)), torch.full_like(amax, -127.0)).clamp(-127, 127)
+    q = (v * torch.exp2(-e)[..., None]).clamp(-448, 448).reshape(x.shape).to(torch.float8_e4m3fn)
+    return q, (e + 127).to(torch.uint8)
+
+
+def dequantize_mxfp8(q: Tensor, scales: Tensor, dtype=BF16) -> Tensor:
+    e = scales.float() - 127.0
+    return (q.float().reshape(q.shape[0], -1, 32) * torch.exp2(e)[..., None]).reshape(q.shape).to(dtype)
+
+
+class MxFp8Weight:
+    """Stored MXFP8 weight (`kind="mxfp8"`). The product runs as a dequantised bf16 GEMM on the
+    tcgen05 family: block scales along K cannot ride in a per-tensor epilogue, and the
+    block-scaled MMA form (`kind::mxf8f6f4.block_scale`) is not wired into the GEMM yet."""
+
+    kind = "mxfp8"
+
+    def __init__(self, q: Tensor, scales: Tensor):
+        self.q, self.scales = q, scales
+        self._dense: Tensor | None = None
+
+    @classmethod
+    def from_dense(cls, w: Tensor) -> "MxFp8Weight":
+        q, s = quantize_mxfp8(w.detach().to(BF16) if w.is_cuda else w.detach())
+        return cls(q, s)
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+    def weight(self, dtype=BF16) -> Tensor:
+        return dequantize_mxfp8(self.q, self.scales, dtype)
+
+    def linear(self, x: Tensor, bias: Tensor | None) -> Tensor:
+        w = self.weight(x.dtype)
+        if _native(x) and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0:
+            return _FrozenDenseFn.apply(x, w, bias)
+        return F.linear(x, w, bias)
+
+    def _apply(self, fn) -> None:
+        self.q = fn(self.q.view(torch.uint8)).view(torch.float8_e4m3fn)
+        self.scales = fn(self.scales)
+
+    def state(self, prefix: str) -> dict[str, Tensor]:
+        return {prefix + "weight": self.q, prefix + "weight_scale_mx": self.scales}

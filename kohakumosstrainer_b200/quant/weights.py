@@ -98,19 +98,41 @@ def quantize_group(lins, recipe: str = "tensor", drop_dense: bool = True) -> Qua
     return group
 
 
-def apply_base_precision(model, base_precision: str = "fp8_compute", recipe: str = "tensor", drop_dense: bool = True) -> int:
+def apply_base_precision(model, base_precision: str = "fp8_compute", recipe: str = "tensor", drop_dense: bool = True,
+                         int8_compute: bool = False, rotation_group: int = 0) -> int:
     """Quantise the joint-block projections of a backbone in place; returns how many linears
-    changed. `bf16` / `compute` / `auto` leave the dense weights alone."""
+    changed. `bf16` / `compute` / `auto` leave the dense weights alone. `fp8` / `fp8_compute`
+    store e4m3 with per-tensor or per-row scales (fp8 MMA); `int8` stores per-channel int8
+    (weight-only, or int8 x int8 with `int8_compute`; `int8_rot` / `rotation_group` applies the
+    ConvRot group rotation first); `mxfp8` stores e4m3 with one power-of-two scale per 32
+    inputs."""
     if base_precision in ("auto", "compute", "bf16", "none", ""):
         return 0
-    if base_precision not in ("fp8_compute", "fp8"):
+    if base_precision not in ("fp8_compute", "fp8", "int8", "int8_rot", "int8_compute", "mxfp8"):
         raise ValueError(f"BASE_PRECISION {base_precision!r} is not handled here")
     count = 0
+    names = ("q", "k", "v", "o", "ffn_up_gate", "ffn_down")
     for block in model.layers:
         p = block.proj
-        quantize_group([p["q"], p["k"], p["v"]], recipe, drop_dense)
-        for name in ("o", "ffn_up_gate", "ffn_down"):
-            quantize_linear(p[name], recipe, drop_dense)
+        if base_precision in ("fp8_compute", "fp8"):
+            quantize_group([p["q"], p["k"], p["v"]], recipe, drop_dense)
+            for name in ("o", "ffn_up_gate", "ffn_down"):
+                quantize_linear(p[name], recipe, drop_dense)
+        else:
+            from .formats import Int8Weight, MxFp8Weight
+
+            for name in names:
+                lin = p[name]
+                if base_precision == "mxfp8":
+                    base = MxFp8Weight.from_dense(lin.weight)
+                else:
+                    group = rotation_group or (64 if base_precision == "int8_rot" else 0)
+                    if group and lin.in_features % group:
+                        group = 0
+                    base = Int8Weight.from_dense(lin.weight, group, int8_compute or base_precision == "int8_compute")
+                lin.set_base(base)
+                if drop_dense:
+                    lin.drop_weight()
         count += 6
     from ..ops import native_ops
 

@@ -53,7 +53,7 @@ def trainer_config(k: dict):
         grad_acc=int(k["GRAD_ACC"]), checkpoint=k["CHECKPOINT"], timestep=k["TIMESTEP"], timestep_kwargs=dict(k["TIMESTEP_KWARGS"]),
         loss=k["LOSS"], weighting=k["WEIGHTING"], seed=int(k["SEED"]), kernels=dict(k["KERNELS"]), parallel=k["PARALLEL"],
         ddp_bucket_mb=k["DDP_BUCKET_MB"], ddp_reduce_dtype=k["DDP_REDUCE_DTYPE"], ddp_backend=k["DDP_BACKEND"],
-        fused_step=bool(k["FUSED_STEP"]) and k["PARALLEL"] == "fsdp", memory=memory_plan(k),
+        fused_step=bool(k["FUSED_STEP"]) and k["PARALLEL"] == "fsdp", memory=memory_plan(k), int8_compute=bool(k["INT8_COMPUTE"]),
     )
 
 

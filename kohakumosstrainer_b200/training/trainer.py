@@ -62,6 +62,7 @@ class TrainerConfig:
     ddp_reduce_dtype: str = "fp32"
     ddp_backend: str = "kohakumoss"
     fused_step: bool = False           # FSDP: apply AdamW inside the reduce-scatter kernel (clip lags one step)
+    int8_compute: bool = False         # INT8_COMPUTE: quantise activations too under an int8 base
     memory: object = None              # a resolved `memory.MemoryPlan` (None = CHECKPOINT only)
 
 
@@ -87,7 +88,7 @@ class Trainer:
                 p.requires_grad_(True)
             named = list(self.model.named_parameters())
         else:
-            apply_base_precision(self.model, cfg.base_precision, cfg.fp8_recipe)
+            apply_base_precision(self.model, cfg.base_precision, cfg.fp8_recipe, int8_compute=cfg.int8_compute)
             acfg = adapters_pkg.AdapterConfig(
                 algo=cfg.algo, preset=cfg.preset, dim=cfg.dim, alpha=cfg.alpha, algo_kwargs=cfg.algo_kwargs,
                 mode=cfg.adapter_mode, seed=cfg.seed, dtype=dtype,

@@ -128,3 +128,26 @@ def test_schedule_and_ema_warmup():
     ema.update(0)
     assert ema.averaged()["p"][0].item() == pytest.approx(1 - 2 / 11)
     assert list(ema.state_dict()) == ["ema0.9999/p"]
+
+
+def test_int8_and_mxfp8_formats_cpu():
+    from kohakumosstrainer_b200.quant import formats as F
+
+    torch.manual_seed(0)
+    w = torch.randn(32, 64) * 0.1
+    x = torch.randn(5, 64, requires_grad=True)
+    for group in (0, 16, 64):
+        for compute in (False, True):
+            iw = F.Int8Weight.from_dense(w, group, compute)
+            y = iw.linear(x, None)
+            ref = x @ w.t()
+            assert (y - ref).abs().max() < 0.03 * ref.abs().max()
+            y.sum().backward()
+            assert (x.grad - torch.ones(5, 32) @ w).abs().max() < 0.03 * w.abs().sum(0).max()
+            x.grad = None
+            assert (iw.weight(torch.float32) - w).abs().max() < 0.01
+    h = F.hadamard_matrix(64)
+    assert torch.allclose(h @ h, torch.eye(64), atol=1e-6) and torch.equal(h, h.t())
+    mx = F.MxFp8Weight.from_dense(w)
+    assert (mx.weight(torch.float32) - w).abs().max() < 0.07 * w.abs().max()
+    assert set(mx.state("l.")) == {"l.weight", "l.weight_scale_mx"} and mx.scales.shape == (32, 2)
