@@ -37,10 +37,11 @@ def script_knobs(script: str | Path) -> dict:
 
 
 def _resolve(name: str, including: Path | None, roots: list[Path]) -> Path:
-    cands = [Path(name)]
+    names = [name] if name.endswith(".py") else [name, name + ".py"]      # the reference's layer names carry no extension
+    cands = [Path(n) for n in names]
     if including is not None:
-        cands.append(including.parent / name)
-    cands += [r / name for r in roots]
+        cands += [including.parent / n for n in names]
+    cands += [r / n for r in roots for n in names]
     for c in cands:
         if c.is_file():
             return c.resolve()

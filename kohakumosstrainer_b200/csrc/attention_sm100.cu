@@ -53,9 +53,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t sbase = smem_u32(smem);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM_BAR);
   const uint32_t bar0 = smem_u32(bars);
-  // barriers: 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 kv_empty | 7,8 s_full | 9 p_full | 10 o_done
+  // barriers: 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 k_empty | 7,8 s_full | 9 p_full | 10 o_done | 11,12 v_empty.
+  // K_j is free as soon as S_j = Q K_j^T has completed, V_j only after P_j V_j: releasing them separately lets the
+  // producer request K_(j+2) a whole iteration earlier, which takes the TMA latency off the per-tile critical path.
   auto bar = [&](int i) { return bar0 + 8u * i; };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -65,7 +67,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     if ((sbase & 1023u) != 0) report_status(a.status, STATUS_BAD_ARGUMENT, 900, (int)(sbase & 1023u));
-    for (int i = 0; i < 11; ++i) mbar_init(bar(i), i == 9 ? 4 : 1);
+    for (int i = 0; i < 13; ++i) mbar_init(bar(i), i == 9 ? 4 : 1);
     *abort_flag = (sbase & 1023u) != 0 ? 1 : 0;
     mbar_fence_init();
     tma_prefetch_desc(&map_q);
@@ -94,6 +96,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mbar_expect_tx(bar(1 + st), 16384);
         tma_load_2d(kdst, &map_k, bar(1 + st), head * DH, row);
         tma_load_2d(kdst + 8192, &map_k, bar(1 + st), head * DH + 64, row);
+        if (!mbar_wait(bar(11 + st), ((j >> 1) & 1) ^ 1, abort_flag, a.status, 502 + st)) break;
         mbar_expect_tx(bar(3 + st), 16384);
         tma_load_2d(vdst, &map_v, bar(3 + st), head * DH, row);
         tma_load_2d(vdst + 8192, &map_v, bar(3 + st), head * DH + 64, row);
@@ -115,6 +118,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           for (int k = 0; k < 4; ++k) mma_f16_ss(d, qd + 2 * k, kd + 2 * k, idesc_s, (kb | k) != 0);
         }
         tc_commit(bar(7 + st));
+        tc_commit(bar(5 + st));  // K stage free
       };
       bool ok = mbar_wait(bar(0), 0, abort_flag, a.status, 600);
       ok = ok && mbar_wait(bar(1), 0, abort_flag, a.status, 601);
@@ -136,8 +140,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const uint64_t vd = umma_smem_desc(sbase + SM_KV + st * 32768 + 16384, 8192, 1024);
 #pragma unroll
         for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + TM_O, pd + 2 * k, vd + 128 * k, idesc_o, (j | k) != 0);
-        tc_commit(bar(5 + st));  // K / V stage free
-        tc_commit(bar(10));      // O updated, P buffer free
+        tc_commit(bar(11 + st));  // V stage free
+        tc_commit(bar(10));       // O updated, P buffer free
       }
     }
   } else {
@@ -314,8 +318,9 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* o,
 // ---- dQ ------------------------------------------------------------------------------------
 constexpr int DQ_SM_Q = 0;                      // 32 KB
 constexpr int DQ_SM_DO = 32768;                 // 32 KB
-constexpr int DQ_SM_KV = 65536;                 // 2 stages x (K 16 KB + V 16 KB)
-constexpr int DQ_SM_DS = DQ_SM_KV + 65536;      // 2 buffers x 16 KB
+constexpr int DQ_KV_STAGES = 3;                 // the load of tile j + 2 is in flight while tile j computes
+constexpr int DQ_SM_KV = 65536;                 // 3 stages x (K 16 KB + V 16 KB)
+constexpr int DQ_SM_DS = DQ_SM_KV + DQ_KV_STAGES * 32768;  // 2 buffers x 16 KB
 constexpr int DQ_SM_BAR = DQ_SM_DS + 32768;
 constexpr int DQ_SMEM = DQ_SM_BAR + 256;
 constexpr uint32_t DQ_TM_S = 0, DQ_TM_DP = 128, DQ_TM_DQ = 256, DQ_TM_COLS = 512;
@@ -328,7 +333,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const uint32_t sbase = smem_u32(smem);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DQ_SM_BAR);
   const uint32_t bar0 = smem_u32(bars);
-  // 0 qdo_full | 1,2 k_full | 3,4 v_full | 5,6 kv_empty | 7,8 sdp_full | 9,10 ds_full | 11,12 ds_empty | 13 done
+  // 0 qdo_full | 1,2,3 kv_full | 4,5,6 kv_empty | 7,8 sdp_full | 9,10 ds_full | 11,12 ds_empty | 13 done
   auto bar = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -360,16 +365,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       tma_load_2d(sbase + DQ_SM_DO, &map_do, bar(0), head * DH, q0);
       tma_load_2d(sbase + DQ_SM_DO + 16384, &map_do, bar(0), head * DH + 64, q0);
       for (int j = 0; j < n_kv; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(bar(5 + st), ((j >> 1) & 1) ^ 1, abort_flag, a.status, 800 + st)) break;
-        const uint32_t kdst = sbase + DQ_SM_KV + st * 32768, vdst = kdst + 16384;
+        const int ks = j % DQ_KV_STAGES;
+        if (!mbar_wait(bar(4 + ks), ((j / DQ_KV_STAGES) & 1) ^ 1, abort_flag, a.status, 800 + ks)) break;
+        const uint32_t kdst = sbase + DQ_SM_KV + ks * 32768, vdst = kdst + 16384;
         const int row = seg_start + j * BN;
-        mbar_expect_tx(bar(1 + st), 16384);
-        tma_load_2d(kdst, &map_k, bar(1 + st), head * DH, row);
-        tma_load_2d(kdst + 8192, &map_k, bar(1 + st), head * DH + 64, row);
-        mbar_expect_tx(bar(3 + st), 16384);
-        tma_load_2d(vdst, &map_v, bar(3 + st), head * DH, row);
-        tma_load_2d(vdst + 8192, &map_v, bar(3 + st), head * DH + 64, row);
+        mbar_expect_tx(bar(1 + ks), 32768);
+        tma_load_2d(kdst, &map_k, bar(1 + ks), head * DH, row);
+        tma_load_2d(kdst + 8192, &map_k, bar(1 + ks), head * DH + 64, row);
+        tma_load_2d(vdst, &map_v, bar(1 + ks), head * DH, row);
+        tma_load_2d(vdst + 8192, &map_v, bar(1 + ks), head * DH + 64, row);
       }
     }
   } else if (warp == 1) {
@@ -378,7 +382,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       constexpr uint32_t idesc_dq = umma_idesc(1, 1, 0, 1, BM, DH);
       auto issue_sdp = [&](int j) {
         const int st = j & 1;
-        const uint32_t kaddr = sbase + DQ_SM_KV + st * 32768, vaddr = kaddr + 16384;
+        const uint32_t kaddr = sbase + DQ_SM_KV + (j % DQ_KV_STAGES) * 32768, vaddr = kaddr + 16384;
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb) {
           const uint64_t qd = umma_smem_desc(sbase + DQ_SM_Q + kb * 16384, 16, 1024);
@@ -395,8 +399,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         tc_commit(bar(7 + st));
       };
-      bool ok = mbar_wait(bar(0), 0, abort_flag, a.status, 810) && mbar_wait(bar(1), 0, abort_flag, a.status, 811) &&
-                mbar_wait(bar(3), 0, abort_flag, a.status, 812);
+      bool ok = mbar_wait(bar(0), 0, abort_flag, a.status, 810) && mbar_wait(bar(1), 0, abort_flag, a.status, 811);
       if (ok) {
         tc_fence_after();
         issue_sdp(0);
@@ -405,18 +408,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       for (; ok && j < n_kv; ++j) {
         const int st = j & 1;
         if (j + 1 < n_kv) {
-          const int sn = (j + 1) & 1, pn = ((j + 1) >> 1) & 1;
-          if (!mbar_wait(bar(1 + sn), pn, abort_flag, a.status, 813) || !mbar_wait(bar(3 + sn), pn, abort_flag, a.status, 814)) break;
+          const int sn = (j + 1) % DQ_KV_STAGES, pn = ((j + 1) / DQ_KV_STAGES) & 1;
+          if (!mbar_wait(bar(1 + sn), pn, abort_flag, a.status, 813)) break;
           tc_fence_after();
           issue_sdp(j + 1);
         }
         if (!mbar_wait(bar(9 + st), (j >> 1) & 1, abort_flag, a.status, 815)) break;
         tc_fence_after();
         const uint64_t sd = umma_smem_desc(sbase + DQ_SM_DS + st * 16384, 16, 1024);
-        const uint64_t kd = umma_smem_desc(sbase + DQ_SM_KV + st * 32768, 8192, 1024);  // K_j read MN-major
+        const uint64_t kd = umma_smem_desc(sbase + DQ_SM_KV + (j % DQ_KV_STAGES) * 32768, 8192, 1024);  // K_j read MN-major
 #pragma unroll
         for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + DQ_TM_DQ, sd + 2 * k, kd + 128 * k, idesc_dq, (j | k) != 0);
-        tc_commit(bar(5 + st));
+        tc_commit(bar(4 + j % DQ_KV_STAGES));
         tc_commit(bar(11 + st));
       }
       if (ok && j == n_kv) tc_commit(bar(13));
@@ -510,9 +513,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 constexpr int BQ = 64;                           // query rows per iteration
 constexpr int KV_SM_K = 0;                       // 32 KB: 2 k-blocks x [128 keys][128 B]
 constexpr int KV_SM_V = 32768;                   // 32 KB
-constexpr int KV_SM_QDO = 65536;                 // 2 stages x (Q 16 KB + dO 16 KB)
-constexpr int KV_SM_PDS = KV_SM_QDO + 65536;     // 2 buffers x (P^T 16 KB + dS^T 16 KB)
-constexpr int KV_SM_VEC = KV_SM_PDS + 65536;     // per warp: 2 x (lse[64] | delta[64]) fp32
+constexpr int KV_Q_STAGES = 3;                   // the load of query tile i + 2 is in flight while tile i computes
+constexpr int KV_SM_QDO = 65536;                 // 3 stages x (Q 16 KB + dO 16 KB)
+constexpr int KV_SM_PDS = KV_SM_QDO + KV_Q_STAGES * 32768;  // P^T 16 KB + dS^T 16 KB (one buffer: written after dV / dK of the tile before)
+constexpr int KV_SM_VEC = KV_SM_PDS + 32768;     // per warp: 2 x (lse[64] | delta[64]) fp32
 constexpr int KV_SM_BAR = KV_SM_VEC + 4096;
 constexpr int KV_SMEM = KV_SM_BAR + 256;
 constexpr uint32_t KV_TM_S = 0, KV_TM_DP = 128, KV_TM_DV = 256, KV_TM_DK = 384, KV_TM_COLS = 512;
@@ -525,7 +529,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
   const uint32_t sbase = smem_u32(smem);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + KV_SM_BAR);
   const uint32_t bar0 = smem_u32(bars);
-  // 0 kv_full | 1,2 qdo_full | 3,4 qdo_empty | 5,6 sdp_full | 7,8 pds_full | 9,10 pds_empty | 11 done
+  // 0 kv_full | 1,2,3 qdo_full | 4,5,6 qdo_empty | 7,8 sdp_full | 9 pds_full | 10 pds_empty | 11 done
   auto bar = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -537,7 +541,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
 
   if (threadIdx.x == 0) {
     if ((sbase & 1023u) != 0) report_status(a.status, STATUS_BAD_ARGUMENT, 902, (int)(sbase & 1023u));
-    for (int i = 0; i < 12; ++i) mbar_init(bar(i), (i == 7 || i == 8) ? 4 : 1);
+    for (int i = 0; i < 12; ++i) mbar_init(bar(i), i == 9 ? 4 : 1);
     *abort_flag = (sbase & 1023u) != 0 ? 1 : 0;
     mbar_fence_init();
   }
@@ -558,15 +562,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       tma_load_2d(sbase + KV_SM_V, &map_v, bar(0), head * DH, k0);
       tma_load_2d(sbase + KV_SM_V + 16384, &map_v, bar(0), head * DH + 64, k0);
       for (int i = 0; i < n_q; ++i) {
-        const int st = i & 1;
-        if (!mbar_wait(bar(3 + st), ((i >> 1) & 1) ^ 1, abort_flag, a.status, 850 + st)) break;
-        const uint32_t qdst = sbase + KV_SM_QDO + st * 32768, ddst = qdst + 16384;
+        const int qs = i % KV_Q_STAGES;
+        if (!mbar_wait(bar(4 + qs), ((i / KV_Q_STAGES) & 1) ^ 1, abort_flag, a.status, 850 + qs)) break;
+        const uint32_t qdst = sbase + KV_SM_QDO + qs * 32768, ddst = qdst + 16384;
         const int row = seg_start + i * BQ;
-        mbar_expect_tx(bar(1 + st), 32768);
-        tma_load_2d(qdst, &map_q, bar(1 + st), head * DH, row);
-        tma_load_2d(qdst + 8192, &map_q, bar(1 + st), head * DH + 64, row);
-        tma_load_2d(ddst, &map_do, bar(1 + st), head * DH, row);
-        tma_load_2d(ddst + 8192, &map_do, bar(1 + st), head * DH + 64, row);
+        mbar_expect_tx(bar(1 + qs), 32768);
+        tma_load_2d(qdst, &map_q, bar(1 + qs), head * DH, row);
+        tma_load_2d(qdst + 8192, &map_q, bar(1 + qs), head * DH + 64, row);
+        tma_load_2d(ddst, &map_do, bar(1 + qs), head * DH, row);
+        tma_load_2d(ddst + 8192, &map_do, bar(1 + qs), head * DH + 64, row);
       }
     }
   } else if (warp == 1) {
@@ -575,7 +579,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       constexpr uint32_t idesc_acc = umma_idesc(1, 1, 0, 1, BM, DH);
       auto issue_sdp = [&](int i) {
         const int st = i & 1;
-        const uint32_t qaddr = sbase + KV_SM_QDO + st * 32768, daddr = qaddr + 16384;
+        const uint32_t qaddr = sbase + KV_SM_QDO + (i % KV_Q_STAGES) * 32768, daddr = qaddr + 16384;
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb) {
           const uint64_t kd = umma_smem_desc(sbase + KV_SM_K + kb * 16384, 16, 1024);
@@ -590,7 +594,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
 #pragma unroll
           for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + KV_TM_DP + st * BQ, vd + 2 * k, dd + 2 * k, idesc_s, (kb | k) != 0);
         }
-        tc_commit(bar(5 + st));
+        tc_commit(bar(7 + st));
       };
       bool ok = mbar_wait(bar(0), 0, abort_flag, a.status, 860) && mbar_wait(bar(1), 0, abort_flag, a.status, 861);
       if (ok) {
@@ -601,23 +605,23 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       for (; ok && i < n_q; ++i) {
         const int st = i & 1;
         if (i + 1 < n_q) {
-          if (!mbar_wait(bar(1 + ((i + 1) & 1)), ((i + 1) >> 1) & 1, abort_flag, a.status, 862)) break;
+          if (!mbar_wait(bar(1 + (i + 1) % KV_Q_STAGES), ((i + 1) / KV_Q_STAGES) & 1, abort_flag, a.status, 862)) break;
           tc_fence_after();
           issue_sdp(i + 1);
         }
-        if (!mbar_wait(bar(7 + st), (i >> 1) & 1, abort_flag, a.status, 863)) break;
+        if (!mbar_wait(bar(9), i & 1, abort_flag, a.status, 863)) break;
         tc_fence_after();
-        const uint32_t qaddr = sbase + KV_SM_QDO + st * 32768, daddr = qaddr + 16384;
-        const uint64_t pd = umma_smem_desc(sbase + KV_SM_PDS + st * 32768, 16, 1024);
-        const uint64_t sd = umma_smem_desc(sbase + KV_SM_PDS + st * 32768 + 16384, 16, 1024);
+        const uint32_t qaddr = sbase + KV_SM_QDO + (i % KV_Q_STAGES) * 32768, daddr = qaddr + 16384;
+        const uint64_t pd = umma_smem_desc(sbase + KV_SM_PDS, 16, 1024);
+        const uint64_t sd = umma_smem_desc(sbase + KV_SM_PDS + 16384, 16, 1024);
         const uint64_t dod = umma_smem_desc(daddr, 8192, 1024);  // dO_i read MN-major
         const uint64_t qd = umma_smem_desc(qaddr, 8192, 1024);   // Q_i read MN-major
 #pragma unroll
         for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + KV_TM_DV, pd + 2 * k, dod + 128 * k, idesc_acc, (i | k) != 0);
 #pragma unroll
         for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + KV_TM_DK, sd + 2 * k, qd + 128 * k, idesc_acc, (i | k) != 0);
-        tc_commit(bar(3 + st));
-        tc_commit(bar(9 + st));
+        tc_commit(bar(4 + i % KV_Q_STAGES));
+        tc_commit(bar(10));
       }
       if (ok && i == n_q) tc_commit(bar(11));
     }
@@ -648,7 +652,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       }
       const float* lse = vec + (quarter * 2 + st) * 128;
       const float* dl = lse + 64;
-      if (!mbar_wait(bar(5 + st), (i >> 1) & 1, abort_flag, a.status, 870 + st)) { ok = false; break; }
+      if (!mbar_wait(bar(7 + st), (i >> 1) & 1, abort_flag, a.status, 870 + st)) { ok = false; break; }
       tc_fence_after();
       uint32_t pkp[32], pkd[32];
 #pragma unroll
@@ -676,8 +680,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
           pkd[half * 16 + c + 1] = pack_bf16(g2, g3);
         }
       }
-      if (!mbar_wait(bar(9 + st), ((i >> 1) & 1) ^ 1, abort_flag, a.status, 880 + st)) { ok = false; break; }
-      uint8_t* prow = smem + KV_SM_PDS + st * 32768 + r * 128;
+      if (!mbar_wait(bar(10), (i & 1) ^ 1, abort_flag, a.status, 880 + st)) { ok = false; break; }
+      uint8_t* prow = smem + KV_SM_PDS + r * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         const int off = (c ^ (r & 7)) << 4;
@@ -687,7 +691,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(7 + st));
+      if (lane == 0) mbar_arrive(bar(9));
     }
     if (ok && mbar_wait(bar(11), 0, abort_flag, a.status, 890)) {
       tc_fence_after();
