@@ -299,7 +299,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 // Two kernels instead of one with fp32 atomics on dQ: every output element has exactly one
 // writer, so gradients are bitwise reproducible.
 // =========================================================================================
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;  // TMA warp, MMA warp, 8 element-wise warps: two per TMEM lane quarter, half of the columns each,
+                                   // so one warp's tensor-memory load latency hides behind the other's arithmetic
 
 __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* o, long ldo, const __nv_bfloat16* dout,
                                                          long lddo, float* delta, int n_rows, int heads) {
@@ -344,7 +345,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   if (threadIdx.x == 0) {
     if ((sbase & 1023u) != 0) report_status(a.status, STATUS_BAD_ARGUMENT, 901, (int)(sbase & 1023u));
-    for (int i = 0; i < 14; ++i) mbar_init(bar(i), (i == 9 || i == 10) ? 4 : 1);
+    for (int i = 0; i < 14; ++i) mbar_init(bar(i), (i == 9 || i == 10) ? 8 : 1);
     *abort_flag = (sbase & 1023u) != 0 ? 1 : 0;
     mbar_fence_init();
   }
@@ -434,15 +435,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const float lse = live ? a.lse[(size_t)head * a.n_rows + row] : INFINITY;
     const float dl = live ? a.delta[(size_t)head * a.n_rows + row] : 0.f;
     const uint64_t sc2 = f32x2(sc, sc), nl2 = f32x2(-lse, -lse), nd2 = f32x2(-dl, -dl);
+    const int half = (warp - 2) >> 2;  // which 32 of the tile's 64 key columns this warp owns
     bool ok = !*abort_flag;
     for (int j = 0; ok && j < n_kv; ++j) {
       const int st = j & 1;
       if (!mbar_wait(bar(7 + st), (j >> 1) & 1, abort_flag, a.status, 820 + st)) { ok = false; break; }
       tc_fence_after();
       const int valid = min(BN, seg_end - (seg_start + j * BN));
-      uint32_t pk[32];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      uint32_t pk[16];
+      {
         uint32_t s_[32], d_[32];
         tmem_ld_32x32(tmem + lane_base + DQ_TM_S + st * BN + half * 32, s_);
         tmem_ld_32x32(tmem + lane_base + DQ_TM_DP + st * BN + half * 32, d_);
@@ -460,14 +461,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             v0 = c0 < valid ? v0 : 0.f;
             v1 = c0 + 1 < valid ? v1 : 0.f;
           }
-          pk[half * 16 + i] = pack_bf16(v0, v1);
+          pk[i] = pack_bf16(v0, v1);
         }
       }
       if (!mbar_wait(bar(11 + st), ((j >> 1) & 1) ^ 1, abort_flag, a.status, 830 + st)) { ok = false; break; }
       uint8_t* prow = smem + DQ_SM_DS + st * 16384 + r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      for (int c = 0; c < 4; ++c)
+        *reinterpret_cast<uint4*>(prow + (((half * 4 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
@@ -477,7 +478,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       tc_fence_after();
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(a.dq) + (size_t)(live ? row : 0) * a.lddq + head * DH;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t o[32];
         tmem_ld_32x32(tmem + lane_base + DQ_TM_DQ + c * 32, o);
         tmem_ld_wait();
@@ -516,8 +517,8 @@ constexpr int KV_SM_V = 32768;                   // 32 KB
 constexpr int KV_Q_STAGES = 3;                   // the load of query tile i + 2 is in flight while tile i computes
 constexpr int KV_SM_QDO = 65536;                 // 3 stages x (Q 16 KB + dO 16 KB)
 constexpr int KV_SM_PDS = KV_SM_QDO + KV_Q_STAGES * 32768;  // P^T 16 KB + dS^T 16 KB (one buffer: written after dV / dK of the tile before)
-constexpr int KV_SM_VEC = KV_SM_PDS + 32768;     // per warp: 2 x (lse[64] | delta[64]) fp32
-constexpr int KV_SM_BAR = KV_SM_VEC + 4096;
+constexpr int KV_SM_VEC = KV_SM_PDS + 32768;     // per element-wise warp: 2 x (lse[64] | delta[64]) fp32
+constexpr int KV_SM_BAR = KV_SM_VEC + 8192;
 constexpr int KV_SMEM = KV_SM_BAR + 256;
 constexpr uint32_t KV_TM_S = 0, KV_TM_DP = 128, KV_TM_DV = 256, KV_TM_DK = 384, KV_TM_COLS = 512;
 
@@ -541,7 +542,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
 
   if (threadIdx.x == 0) {
     if ((sbase & 1023u) != 0) report_status(a.status, STATUS_BAD_ARGUMENT, 902, (int)(sbase & 1023u));
-    for (int i = 0; i < 12; ++i) mbar_init(bar(i), i == 9 ? 4 : 1);
+    for (int i = 0; i < 12; ++i) mbar_init(bar(i), i == 9 ? 8 : 1);
     *abort_flag = (sbase & 1023u) != 0 ? 1 : 0;
     mbar_fence_init();
   }
@@ -633,11 +634,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const float sc = a.scale * LOG2E;
     const uint64_t sc2 = f32x2(sc, sc);
+    const int half = (warp - 2) >> 2;  // which 32 of the tile's 64 query columns this warp owns
     bool ok = !*abort_flag;
     for (int i = 0; ok && i < n_q; ++i) {
       const int st = i & 1;
       {  // each warp stages lse / delta of this query tile for its own 32 rows (no CTA-wide barrier)
-        float* mine = vec + (quarter * 2 + st) * 128;
+        float* mine = vec + ((warp - 2) * 2 + st) * 128;
         __syncwarp();
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -650,13 +652,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
         }
         __syncwarp();
       }
-      const float* lse = vec + (quarter * 2 + st) * 128;
+      const float* lse = vec + ((warp - 2) * 2 + st) * 128;
       const float* dl = lse + 64;
       if (!mbar_wait(bar(7 + st), (i >> 1) & 1, abort_flag, a.status, 870 + st)) { ok = false; break; }
       tc_fence_after();
-      uint32_t pkp[32], pkd[32];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      uint32_t pkp[16], pkd[16];
+      {
         uint32_t s_[32], d_[32];
         tmem_ld_32x32(tmem + lane_base + KV_TM_S + st * BQ + half * 32, s_);
         tmem_ld_32x32(tmem + lane_base + KV_TM_DP + st * BQ + half * 32, d_);
@@ -674,17 +675,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
           float g0, g1, g2, g3;
           f32x2_split(mul_f32x2(f32x2(e0, e1), add_f32x2(f32x2(d_[2 * c], d_[2 * c + 1]), f32x2(-d4.x, -d4.y))), g0, g1);
           f32x2_split(mul_f32x2(f32x2(e2, e3), add_f32x2(f32x2(d_[2 * c + 2], d_[2 * c + 3]), f32x2(-d4.z, -d4.w))), g2, g3);
-          pkp[half * 16 + c] = pack_bf16(e0, e1);
-          pkp[half * 16 + c + 1] = pack_bf16(e2, e3);
-          pkd[half * 16 + c] = pack_bf16(g0, g1);
-          pkd[half * 16 + c + 1] = pack_bf16(g2, g3);
+          pkp[c] = pack_bf16(e0, e1);
+          pkp[c + 1] = pack_bf16(e2, e3);
+          pkd[c] = pack_bf16(g0, g1);
+          pkd[c + 1] = pack_bf16(g2, g3);
         }
       }
       if (!mbar_wait(bar(10), (i & 1) ^ 1, abort_flag, a.status, 880 + st)) { ok = false; break; }
       uint8_t* prow = smem + KV_SM_PDS + r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const int off = (c ^ (r & 7)) << 4;
+      for (int c = 0; c < 4; ++c) {
+        const int off = ((half * 4 + c) ^ (r & 7)) << 4;
         *reinterpret_cast<uint4*>(prow + off) = make_uint4(pkp[4 * c], pkp[4 * c + 1], pkp[4 * c + 2], pkp[4 * c + 3]);
         *reinterpret_cast<uint4*>(prow + 16384 + off) = make_uint4(pkd[4 * c], pkd[4 * c + 1], pkd[4 * c + 2], pkd[4 * c + 3]);
       }
@@ -702,7 +703,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
         const long ld = which == 0 ? a.lddv : a.lddk;
         __nv_bfloat16* orow = base + (size_t)(live ? key : 0) * ld + head * DH;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 2 * half; c < 2 * half + 2; ++c) {
           uint32_t o[32];
           tmem_ld_32x32(tmem + lane_base + (which == 0 ? KV_TM_DV : KV_TM_DK) + c * 32, o);
           tmem_ld_wait();

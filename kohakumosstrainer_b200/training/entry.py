@@ -54,6 +54,8 @@ def trainer_config(k: dict):
         loss=k["LOSS"], weighting=k["WEIGHTING"], seed=int(k["SEED"]), kernels=dict(k["KERNELS"]), parallel=k["PARALLEL"],
         ddp_bucket_mb=k["DDP_BUCKET_MB"], ddp_reduce_dtype=k["DDP_REDUCE_DTYPE"], ddp_backend=k["DDP_BACKEND"],
         fused_step=bool(k["FUSED_STEP"]) and k["PARALLEL"] == "fsdp", memory=memory_plan(k), int8_compute=bool(k["INT8_COMPUTE"]),
+        extras={n: k[n] for n in ("STREAM_LOSS", "CONCENTRATION_LOSS", "STREAM_LOSS_PROBE", "TEACHER", "DISTILL_WEIGHT", "HARD_WEIGHT")
+                if k.get(n) not in (None, "", {}, 0, 0.0) and not (n == "HARD_WEIGHT" and float(k[n]) == 1.0)},
     )
 
 

@@ -1,0 +1,242 @@
+"""Extra loss terms and probes of a training step: residual-stream penalties (`STREAM_LOSS`,
+`CONCENTRATION_LOSS`), teacher distillation (`TEACHER`, `DISTILL_WEIGHT`) and the per-term
+gradient probe (`STREAM_LOSS_PROBE`).
+
+Definitions follow the reference (`src/kohakumoss/training/stream_loss.py:1-320`,
+`training/distill.py:32-150`, `training/grad_probe.py:28-110`):
+
+* `concentration`: share of each block output's energy held by its top-k channels, mean over
+  blocks (`dilute=False` detaches the total so only the top channels shrink);
+* `peak`: per sample, the mean of the top `top` fraction of |x| per block through a soft hinge
+  `softplus((log m - log cap) / tau)`, mean over blocks, weighted per sample by sigma;
+* `rms`: per sample whole-stream RMS per block pulled to `target`, `(R / target - 1)^2`;
+* distillation: MSE between the student's and a frozen teacher's velocity prediction on the
+  same noisy input, added with `DISTILL_WEIGHT` (the data loss keeps `HARD_WEIGHT`).
+
+Block outputs are tapped with forward hooks on the joint blocks, so the terms see exactly
+what the next block reads; nothing is tapped when no term is configured.
+"""
+
+from __future__ import annotations
+
+import math
+from contextlib import contextmanager
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+TERMS = {"concentration": {"weight", "k", "dilute"}, "peak": {"weight", "cap", "top", "tau", "sigma"}, "rms": {"weight", "target", "sigma"}}
+DEFAULTS = {"concentration": {"k": 32, "dilute": True}, "peak": {"cap": 32768.0, "top": 1e-4, "tau": 0.25, "sigma": "sigma"},
+            "rms": {"target": 1.0, "sigma": "none"}}
+SIGMA_WEIGHTS = ("sigma", "one_minus_sigma", "none")
+
+
+def spec_of(k: dict) -> dict:
+    """`STREAM_LOSS` terms with defaults filled; `CONCENTRATION_LOSS` is its `concentration` term."""
+    spec = {name: {**DEFAULTS[name], **dict(term)} for name, term in dict(k.get("STREAM_LOSS") or {}).items()}
+    legacy = dict(k.get("CONCENTRATION_LOSS") or {})
+    if legacy and "concentration" not in spec:
+        spec["concentration"] = {**DEFAULTS["concentration"], **legacy}
+    return {n: t for n, t in spec.items() if float(t.get("weight", 0)) > 0}
+
+
+def stream_loss_problems(k: dict, dim: int | None = None) -> list[str]:
+    out = []
+    for name, term in dict(k.get("STREAM_LOSS") or {}).items():
+        if name not in TERMS:
+            out.append(f"STREAM_LOSS term {name!r} is not one of {sorted(TERMS)}")
+            continue
+        extra = set(term) - TERMS[name]
+        if extra:
+            out.append(f"STREAM_LOSS[{name!r}] has unknown keys {sorted(extra)}")
+        if "sigma" in term and term["sigma"] not in SIGMA_WEIGHTS:
+            out.append(f"STREAM_LOSS[{name!r}]['sigma'] must be one of {list(SIGMA_WEIGHTS)}")
+        if name == "concentration" and dim is not None and int(term.get("k", 32)) >= dim:
+            out.append(f"STREAM_LOSS['concentration']['k'] must be below the model width {dim}")
+    if int(k.get("STREAM_LOSS_PROBE") or 0) > 0 and not spec_of(k) and not float(k.get("DISTILL_WEIGHT") or 0):
+        out.append("STREAM_LOSS_PROBE needs at least one STREAM_LOSS term or a teacher")
+    return out
+
+
+def top_share(h: Tensor, k: int, dilute: bool = True) -> Tensor:
+    e = torch.linalg.vector_norm(h.reshape(-1, h.shape[-1]), dim=0, dtype=torch.float32).square()
+    total = e.sum().clamp_min(torch.finfo(torch.float32).tiny)
+    if not dilute:
+        total = total.detach()
+    return e.topk(k).values.sum() / total
+
+
+def sigma_weight(sigma: Tensor, mode: str) -> Tensor:
+    if mode == "sigma":
+        return sigma
+    if mode == "one_minus_sigma":
+        return 1.0 - sigma
+    return torch.ones_like(sigma)
+
+
+class StreamPenalty:
+    def __init__(self, layers, spec: dict):
+        self.spec, self.outputs, self.active = spec, [], False
+        for layer in layers:
+            layer.register_forward_hook(self._hook)
+
+    def _hook(self, module, inputs, output) -> None:
+        if self.active and isinstance(output, Tensor):
+            self.outputs.append(output)
+
+    @contextmanager
+    def collecting(self):
+        self.outputs, self.active = [], True
+        try:
+            yield self
+        finally:
+            self.active = False
+
+    def take(self, seq, sigma: Tensor) -> tuple[Tensor, dict]:
+        """-> (weighted sum of the terms, {term: value}) over the tapped block outputs."""
+        outs, self.outputs = self.outputs, []
+        device = sigma.device
+        total, parts = torch.zeros((), device=device), {}
+        if not outs:
+            return total, parts
+        seg = seq.seg_joint.long() if hasattr(seq, "seg_joint") else None
+        B = int(sigma.shape[0])
+        for name, term in self.spec.items():
+            if name == "concentration":
+                value = torch.stack([top_share(h, int(term["k"]), bool(term["dilute"])) for h in outs]).mean()
+            elif name == "peak":
+                vals = []
+                for h in outs:
+                    per = []
+                    for b in range(B):
+                        rows = h[seg == b] if seg is not None else h
+                        flat = rows.abs().float().reshape(-1)
+                        n = max(1, int(flat.numel() * float(term["top"])))
+                        per.append(flat.topk(n).values.mean())
+                    m = torch.stack(per).clamp_min(1e-30)
+                    vals.append(F.softplus((m.log() - math.log(float(term["cap"]))) / float(term["tau"])))
+                value = (torch.stack(vals).mean(0) * sigma_weight(sigma, term["sigma"])).mean()
+            else:  # rms
+                vals = []
+                for h in outs:
+                    sq = h.float().square().mean(-1)
+                    if seg is not None:
+                        s = torch.zeros(B, device=device).index_add_(0, seg, sq)
+                        n = torch.zeros(B, device=device).index_add_(0, seg, torch.ones_like(sq)).clamp_min(1)
+                        r = (s / n).sqrt()
+                    else:
+                        r = sq.mean().sqrt().expand(B)
+                    vals.append((r / float(term["target"]) - 1.0).square())
+                value = (torch.stack(vals).mean(0) * sigma_weight(sigma, term["sigma"])).mean()
+            parts[name] = value.detach()
+            total = total + float(term["weight"]) * value
+        return total, parts
+
+
+def build_penalty(k: dict, backbone) -> StreamPenalty | None:
+    spec = spec_of(k)
+    return StreamPenalty(backbone.layers, spec) if spec else None
+
+
+# ---- distillation ---------------------------------------------------------------------------------
+class Teacher:
+    """A frozen copy of the model predicting on the student's noisy input."""
+
+    def __init__(self, model, dtype: torch.dtype):
+        self.model, self.dtype = model.eval().requires_grad_(False), dtype
+
+    @torch.no_grad()
+    def __call__(self, z: Tensor, text: Tensor, sigma: Tensor, seq) -> Tensor:
+        return self.model(z.to(self.dtype), text.to(self.dtype), sigma, seq)
+
+
+def distill_problems(k: dict) -> list[str]:
+    out = []
+    w = float(k.get("DISTILL_WEIGHT") or 0)
+    if w < 0:
+        out.append("DISTILL_WEIGHT must be >= 0")
+    if w > 0 and not k.get("TEACHER"):
+        out.append("DISTILL_WEIGHT > 0 needs TEACHER (a weights path, or 'base' for the frozen base under an adapter)")
+    if k.get("TEACHER") and w == 0:
+        out.append("TEACHER is set but DISTILL_WEIGHT is 0")
+    if k.get("TEACHER") == "base" and k.get("ALGO") == "full":
+        out.append("TEACHER='base' needs an adapter run (the base weights are what a full finetune trains)")
+    if float(k.get("HARD_WEIGHT", 1.0)) < 0:
+        out.append("HARD_WEIGHT must be >= 0")
+    return out
+
+
+def build_teacher(k: dict, device, student=None):
+    """`TEACHER='base'`: the student with its adapters switched off (no second copy of the
+    weights); a path: a second frozen backbone loaded from it."""
+    if not k.get("TEACHER") or not float(k.get("DISTILL_WEIGHT") or 0):
+        return None
+    dtype = torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32
+    if k["TEACHER"] == "base":
+        return BaseTeacher(student, dtype)
+    from ..models import build_backbone
+    from ..models.build import resolve_arch
+    from ..models.io import load_weights
+
+    model = build_backbone(resolve_arch(k["VARIANT"], k["ARCH_OVERRIDES"]), device=device, dtype=dtype, seed=0)
+    load_weights(model, k["TEACHER"])
+    return Teacher(model, dtype)
+
+
+class BaseTeacher:
+    """The student's own frozen base: adapters are detached for the teacher pass."""
+
+    def __init__(self, student, dtype):
+        self.student, self.dtype = student, dtype
+
+    @torch.no_grad()
+    def __call__(self, z, text, sigma, seq):
+        lins = [m for m in self.student.modules() if getattr(m, "adapter", None) is not None]
+        saved = [(m, m.adapter) for m in lins]
+        for m in lins:
+            m.__dict__["adapter"] = None
+        try:
+            return self.student(z.to(self.dtype), text.to(self.dtype), sigma, seq)
+        finally:
+            for m, a in saved:
+                m.__dict__["adapter"] = a
+
+
+# ---- gradient probe ---------------------------------------------------------------------------------
+def group_of(name: str) -> str:
+    for key in ("attn", "q", "k", "v", "o"):
+        if f".{key}." in name or name.endswith(f".{key}"):
+            return "attn"
+    return "ffn" if "ffn" in name else "other"
+
+
+class GradProbe:
+    """Every `every` steps: the gradient norm each loss term alone would send to each parameter
+    group (`torch.autograd.grad` with retained graph; the step's own backward is untouched)."""
+
+    def __init__(self, named: list, every: int):
+        self.named, self.every = [(n, p) for n, p in named if p.requires_grad], int(every)
+
+    def due(self, step: int) -> bool:
+        return self.every > 0 and step % self.every == 0
+
+    def measure(self, values: dict[str, Tensor]) -> dict[str, float]:
+        out = {}
+        params = [p for _, p in self.named]
+        for term, value in values.items():
+            if not isinstance(value, Tensor) or not value.requires_grad:
+                continue
+            grads = torch.autograd.grad(value, params, retain_graph=True, allow_unused=True)
+            sums: dict[str, float] = {}
+            for (name, _), g in zip(self.named, grads):
+                if g is not None:
+                    sums[group_of(name)] = sums.get(group_of(name), 0.0) + float(g.float().square().sum())
+            for group, sq in sums.items():
+                out[f"probe/{term}/{group}"] = sq**0.5
+        return out
+
+
+def build_probe(k: dict, named) -> GradProbe | None:
+    every = int(k.get("STREAM_LOSS_PROBE") or 0)
+    return GradProbe(list(named), every) if every > 0 else None

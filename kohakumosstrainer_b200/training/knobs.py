@@ -64,6 +64,9 @@ CHOICES["CHECKPOINT"] = _checkpoint_mode
 def cross_checks(k: dict) -> list[str]:
     """Problems that involve several knobs (the reference's `Layout.problems`)."""
     out = []
+    from .extras import distill_problems, stream_loss_problems
+
+    out += stream_loss_problems(k) + distill_problems(k)
     n_dev = len(k.get("DEVICES") or (0,))
     par = k.get("PARALLEL", "none")
     if par == "none" and n_dev > 1:

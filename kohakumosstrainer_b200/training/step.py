@@ -63,6 +63,12 @@ class TrainStep:
         self.sigma_gen = torch.Generator().manual_seed(seed_of("sigma", seed, rank))
         self.noise_gen = torch.Generator(self.device).manual_seed(seed_of("noise", seed, rank))
         self.step_index = 0
+        # optional extras (`training.extras`): stream penalties, teacher distillation, gradient probe
+        self.penalty = None
+        self.teacher = None
+        self.distill_weight, self.hard_weight = 0.0, 1.0
+        self.probe = None
+        self.last_terms: dict = {}
 
     def draw_sigma(self, batch: int) -> Tensor:
         """fp32 [B] on the device; drawn on the host generator, copied through pinned memory."""
@@ -79,12 +85,33 @@ class TrainStep:
         z0 = batch.latents.float()
         eps = torch.randn(z0.shape, generator=self.noise_gen, device=self.device, dtype=torch.float32)
         z, target = noise_latents(z0, eps, sigma, seq.seg_img)
-        v = self.model(z.to(self.compute_dtype), batch.text.to(self.compute_dtype), sigma, seq)
+        zc, tc = z.to(self.compute_dtype), batch.text.to(self.compute_dtype)
+        if self.penalty is not None:
+            with self.penalty.collecting():
+                v = self.model(zc, tc, sigma, seq)
+        else:
+            v = self.model(zc, tc, sigma, seq)
         weight = self.weighting(sigma)
         if batch.weight is not None:
             weight = weight * batch.weight.to(weight.dtype)
         total = token_loss(self.model.ops, v, target, seq.seg_img, weight, None, self.loss, **self.loss_kwargs)
-        return total / denom
+        if self.penalty is None and self.teacher is None:
+            return total / denom
+        terms = {"data": total / denom}
+        share = batch.image_tokens / denom          # batch means enter the step loss with this micro-batch's token share
+        out = terms["data"] * self.hard_weight
+        if self.penalty is not None:
+            pen, parts = self.penalty.take(seq, sigma)
+            terms["stream"] = pen * share
+            out = out + terms["stream"]
+            self.last_terms = {f"stream/{k}": float(val) for k, val in parts.items()} if self.step_index % 16 == 0 else self.last_terms
+        if self.teacher is not None and self.distill_weight > 0:
+            tv = self.teacher(zc, tc, sigma, seq)
+            terms["distill"] = token_loss(self.model.ops, v, tv.float(), seq.seg_img, weight, None, "mse") / denom
+            out = out + self.distill_weight * terms["distill"]
+        if self.probe is not None and self.probe.due(self.step_index):
+            self.last_terms.update(self.probe.measure(terms))
+        return out
 
     def rng_state(self) -> dict:
         return {"sigma": self.sigma_gen.get_state(), "noise": self.noise_gen.get_state(), "step": self.step_index}

@@ -62,6 +62,7 @@ class TrainerConfig:
     ddp_reduce_dtype: str = "fp32"
     ddp_backend: str = "kohakumoss"
     fused_step: bool = False           # FSDP: apply AdamW inside the reduce-scatter kernel (clip lags one step)
+    extras: dict = field(default_factory=dict)   # STREAM_LOSS / CONCENTRATION_LOSS / STREAM_LOSS_PROBE / TEACHER / DISTILL_WEIGHT / HARD_WEIGHT knobs
     int8_compute: bool = False         # INT8_COMPUTE: quantise activations too under an int8 base
     memory: object = None              # a resolved `memory.MemoryPlan` (None = CHECKPOINT only)
 
@@ -159,6 +160,15 @@ class Trainer:
         self.normalizer = TokenNormalizer(reduce_tokens, 1)
         self.step_fn = TrainStep(self.model, self.device, cfg.timestep, cfg.timestep_kwargs, cfg.loss, None,
                                  cfg.weighting, cfg.seed, rank, dtype)
+        if cfg.extras:
+            from . import extras as ex
+
+            k = {"VARIANT": cfg.variant, "ARCH_OVERRIDES": cfg.arch_overrides, "ALGO": cfg.algo, **cfg.extras}
+            self.step_fn.penalty = ex.build_penalty(k, self.model)
+            self.step_fn.teacher = ex.build_teacher(k, self.device, self.model)
+            self.step_fn.distill_weight = float(k.get("DISTILL_WEIGHT") or 0.0)
+            self.step_fn.hard_weight = float(k.get("HARD_WEIGHT", 1.0))
+            self.step_fn.probe = ex.build_probe(k, named)
         self.batcher = DeviceBatcher(self.device, torch.float32, dtype)
         self.tokens_seen = 0
         self.samples_seen = 0

@@ -102,3 +102,32 @@ def _retry_twice(fn, args, on_retry):
         if on_retry:
             on_retry(1, err, 0.0)
         return fn(*args)
+
+
+def test_stream_penalties_distillation_and_probe():
+    import torch
+
+    from kohakumosstrainer_b200.data import SyntheticConfig, SyntheticDataset
+    from kohakumosstrainer_b200.training import extras as ex
+    from kohakumosstrainer_b200.training.trainer import Trainer, TrainerConfig
+
+    assert ex.stream_loss_problems({"STREAM_LOSS": {"nope": {}}}) and ex.distill_problems({"DISTILL_WEIGHT": 0.5})
+    assert not ex.stream_loss_problems({"STREAM_LOSS": {"peak": {"weight": 1.0, "cap": 8.0}}})
+    h = torch.zeros(10, 16)
+    h[:, :2] = 3.0
+    h[:, 2:] = 0.1
+    assert ex.top_share(h, 2) > 0.95
+    ds = SyntheticDataset(SyntheticConfig(max_tokens=300, min_area=96 * 96, max_area=128 * 128, size_step=32, min_text=2, max_text=8,
+                                          channels=8, text_dim=32, dtype=torch.float32))
+    base = dict(variant="tiny", arch_overrides={"text_dim": 32, "latent_channels": 8}, precision="fp32", dim=4, alpha=4.0, steps=4, base_precision="auto")
+    plain = Trainer(TrainerConfig(**base), device="cpu")
+    extras = {"STREAM_LOSS": {"concentration": {"weight": 0.5, "k": 8}, "rms": {"weight": 0.1, "target": 1.0}, "peak": {"weight": 0.1, "cap": 4.0}},
+              "TEACHER": "base", "DISTILL_WEIGHT": 0.25, "STREAM_LOSS_PROBE": 1}
+    rich = Trainer(TrainerConfig(**base, extras=extras), device="cpu")
+    hb = ds.materialize(0, 0, 1)
+    a, b = plain.train_step(hb), rich.train_step(hb)
+    assert b["loss"] > a["loss"] and b["ok"]                     # penalties add to the loss; the LoRA starts at the base, so distill = 0
+    terms = rich.step_fn.last_terms
+    assert {"stream/concentration", "stream/rms", "stream/peak"} <= set(terms) and any(k.startswith("probe/stream/") for k in terms)
+    out = rich.train_step(ds.materialize(1, 0, 1))
+    assert out["ok"]
