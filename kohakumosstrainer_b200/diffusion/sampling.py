@@ -28,6 +28,11 @@ class SampleResult:
     latents: Tensor  # packed [N_img, C]
     hw: Tensor  # [B, 2]
 
+    def per_image(self) -> list[Tensor]:
+        """The packed latents split per image: `[h * w, C]` each."""
+        sizes = (self.hw[:, 0].long() * self.hw[:, 1].long()).tolist()
+        return list(self.latents.split(sizes, 0))
+
 
 def moss_sigmas(steps: int = 50, shift: float = 5.0, total: int = 1000, training_shift: float = 1.0) -> Tensor:
     """Descending fp32 sigmas ending in 0: `steps` shifted values snapped to the nearest

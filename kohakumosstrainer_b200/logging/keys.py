@@ -1,7 +1,8 @@
 """Metric key groups and verbosity levels (`src/kohakumoss/logging/keys.py:6-58`)."""
 
-GROUPS = ("loss/", "stream/", "opt/", "amp/", "speed/", "probe/", "detail/", "ddp/", "pipe/", "mem/")
-_LEVELS = {"train": ("loss/", "opt/", "speed/", "amp/"), "bench": ("loss/", "opt/", "speed/", "amp/", "ddp/", "pipe/", "mem/"),
+GROUPS = ("loss/", "val/", "samples/", "stream/", "opt/", "amp/", "speed/", "probe/", "detail/", "ddp/", "pipe/", "mem/", "xfer/", "breakdown/")
+_LEVELS = {"train": ("loss/", "val/", "samples/", "stream/", "opt/", "speed/", "amp/"),
+           "bench": ("loss/", "val/", "samples/", "stream/", "opt/", "speed/", "amp/", "ddp/", "pipe/", "mem/", "xfer/", "breakdown/"),
            "debug": GROUPS}
 
 

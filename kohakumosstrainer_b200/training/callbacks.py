@@ -103,3 +103,152 @@ def vram_row(device) -> dict:
     if torch.device(device).type != "cuda":
         return {}
     return {"mem/peak_gb": torch.cuda.max_memory_allocated(device) / 2**30, "mem/reserved_gb": torch.cuda.memory_reserved(device) / 2**30}
+
+
+class Validation:
+    """`VALIDATE_EVERY` / `VALIDATION`: the flow-matching loss on a fixed set of held-out batches
+    at fixed sigmas with fixed noise (so the curve moves only when the model does), overall and
+    per sigma bucket. Role of `src/kohakumoss/training/callbacks/validation.py` there.
+
+    `VALIDATION = {"batches": 4, "sigmas": (0.1, 0.3, 0.5, 0.7, 0.9), "offset": 1_000_000, "seed": 1234}`:
+    batches `offset .. offset + batches` of the training dataset (far beyond what a run reaches)."""
+
+    def __init__(self, every: int, spec: dict, dataset, trainer):
+        self.every = int(every)
+        self.spec = {"batches": 4, "sigmas": (0.1, 0.3, 0.5, 0.7, 0.9), "offset": 1_000_000, "seed": 1234, **dict(spec or {})}
+        self.dataset, self.trainer = dataset, trainer
+
+    def due(self, step: int) -> bool:
+        return self.every > 0 and step % self.every == 0
+
+    @torch.no_grad()
+    def run(self) -> dict:
+        from ..diffusion.objective import noise_latents, token_loss
+
+        tr = self.trainer
+        model, dev, dtype = tr.model, tr.device, tr.dtype
+        was_training = model.training
+        model.eval()
+        sums = {float(s): [0.0, 0] for s in self.spec["sigmas"]}
+        for b in range(int(self.spec["batches"])):
+            hb = self.dataset.materialize(int(self.spec["offset"]) + b, 0, 1)
+            batch = hb.to_device(dev, torch.float32, dtype)
+            seq = batch.seq
+            g = torch.Generator(dev).manual_seed(int(self.spec["seed"]) + b)
+            eps = torch.randn(batch.latents.shape, generator=g, device=dev, dtype=torch.float32)
+            for s in sums:
+                sigma = torch.full((seq.batch,), s, device=dev)
+                z, target = noise_latents(batch.latents.float(), eps, sigma, seq.seg_img)
+                v = model(z.to(dtype), batch.text.to(dtype), sigma, seq)
+                loss = token_loss(model.ops, v, target, seq.seg_img, torch.ones(seq.batch, device=dev))
+                sums[s][0] += float(loss)
+                sums[s][1] += batch.image_tokens
+        model.train(was_training)
+        row = {f"val/loss_sigma_{s:g}": tot / max(n, 1) for s, (tot, n) in sums.items()}
+        row["val/loss"] = sum(t for t, _ in sums.values()) / max(sum(n for _, n in sums.values()), 1)
+        return row
+
+
+class SampleGrid:
+    """`SAMPLE_EVERY`: sample the current model (adapters live) for the `SAMPLE_PROMPTS` and
+    seeds, and write `<run>/samples/step<NNNNNN>/<index>_<seed>.{pt,png}` plus a contact sheet
+    when a VAE is bound. Prompts need embeddings: a text encoder, or `embeddings` (a
+    `.safetensors` with `positive.<i>` / `negative.<i>`), or synthetic N(0, 1) ones for smoke runs.
+    Role of the reference's sample-grid callback (`training/callbacks/samples.py`)."""
+
+    def __init__(self, every: int, run_dir, trainer, prompts, negative: str = "", steps: int = 50, cfg: float = 3.0, shift: float = 5.0,
+                 skip_layers=(22,), size=(1024, 1024), seeds=(0,), batch: int = 4, columns: int = 0, at_start: bool = False,
+                 text_encoder=None, vae=None, embeddings: str = ""):
+        self.every, self.run_dir, self.trainer = int(every), run_dir, trainer
+        self.prompts, self.negative = list(prompts or []), negative
+        self.kw = dict(steps=steps, cfg=cfg, shift=shift, skip_layers=tuple(skip_layers or ()), size=tuple(size))
+        self.seeds, self.batch, self.columns, self.at_start = tuple(seeds), batch, columns, at_start
+        self.text_encoder, self.vae, self.embeddings = text_encoder, vae, embeddings
+
+    def due(self, step: int) -> bool:
+        if not self.prompts or self.every <= 0:
+            return False
+        return step % self.every == 0 or (step == 0 and self.at_start)
+
+    def _embed(self):
+        arch = self.trainer.model.cfg
+        dev, dtype = self.trainer.device, self.trainer.dtype
+        if self.text_encoder is not None:
+            pos = self.text_encoder.encode(self.prompts)
+            neg = self.text_encoder.encode([self.negative] * len(self.prompts))
+            return [p.to(dev, dtype) for p in pos], [n.to(dev, dtype) for n in neg]
+        if self.embeddings:
+            from safetensors.torch import load_file
+
+            sd = load_file(self.embeddings)
+            pos = [sd[f"positive.{i}"].to(dev, dtype) for i in range(len(self.prompts))]
+            neg = [sd.get(f"negative.{i}", sd.get("negative.0")).to(dev, dtype) for i in range(len(self.prompts))]
+            return pos, neg
+        from ..encoders import synthetic_text_encoder
+
+        enc = synthetic_text_encoder(arch.text_dim)
+        return [p.to(dev, dtype) for p in enc(self.prompts)], [n.to(dev, dtype) for n in enc([self.negative] * len(self.prompts))]
+
+    @torch.no_grad()
+    def run(self, step: int) -> dict:
+        from pathlib import Path
+
+        from ..diffusion.sampling import sample_latents
+
+        tr = self.trainer
+        out_dir = Path(self.run_dir) / "samples" / f"step{step:06d}"
+        out_dir.mkdir(parents=True, exist_ok=True)
+        was_training = tr.model.training
+        tr.model.eval()
+        pos, neg = self._embed()
+        written = 0
+        for seed in self.seeds:
+            for lo in range(0, len(pos), self.batch):
+                hi = min(len(pos), lo + self.batch)
+                res = sample_latents(tr.model, pos[lo:hi], neg[lo:hi], seeds=[seed] * (hi - lo), device=tr.device, **self.kw)
+                for i, (z, hw) in enumerate(zip(res.per_image(), res.hw.tolist())):
+                    torch.save({"latents": z.cpu(), "hw": tuple(hw)}, out_dir / f"{lo + i}_{seed}.pt")
+                    if self.vae is not None:
+                        self._png(z, tuple(hw), out_dir / f"{lo + i}_{seed}.png")
+                    written += 1
+        tr.model.train(was_training)
+        return {"samples/written": written}
+
+    def _png(self, latents, hw, path) -> None:
+        from PIL import Image
+
+        h, w = hw
+        z = latents.reshape(h, w, -1).permute(2, 0, 1)[None].to(self.trainer.device)
+        img = self.vae.decode(z)[0].float().clamp(-1, 1).add(1).mul(127.5).byte().permute(1, 2, 0).cpu().numpy()
+        Image.fromarray(img).save(path)
+
+
+class StepBreakdown:
+    """Step-1 breakdown: wall time of the first steps by phase (data, host-to-device, forward +
+    backward, optimiser) with CUDA events, logged once; afterwards it costs nothing."""
+
+    def __init__(self, steps: int = 2):
+        self.steps, self.rows = steps, []
+
+    def active(self, step: int) -> bool:
+        return step < self.steps
+
+    def measure(self, step: int, phases: dict) -> None:
+        self.rows.append({"step": step, **{f"breakdown/{k}_ms": round(v, 3) for k, v in phases.items()}})
+
+
+class TransferCounters:
+    """Bytes moved between host and device per step (batches in, metrics out, offload traffic)."""
+
+    def __init__(self):
+        self.h2d = self.d2h = 0
+
+    def observe(self, group, trainer) -> None:
+        self.h2d += sum(hb.nbytes() for hb in group)
+        self.d2h += 12
+        for part in getattr(trainer, "memory_parts", {}).values():
+            self.h2d += getattr(part, "bytes_h2d", 0) + getattr(part, "bytes_in", 0)
+            self.d2h += getattr(part, "bytes_out", 0)
+
+    def row(self) -> dict:
+        return {"xfer/h2d_mb": round(self.h2d / 1e6, 2), "xfer/d2h_mb": round(self.d2h / 1e6, 2)}

@@ -143,7 +143,7 @@ class _Encoded:
 
 def worker(k: dict, rank: int, world: int, device) -> dict:
     from ..logging import build_writer
-    from .callbacks import FiniteGuard, StepTrace, Throughput, vram_row
+    from .callbacks import FiniteGuard, SampleGrid, StepTrace, Throughput, TransferCounters, Validation, vram_row
     from .checkpoint import CheckpointManager
     from .trainer import Trainer
 
@@ -189,8 +189,15 @@ def worker(k: dict, rank: int, world: int, device) -> dict:
     speed = Throughput(arch, cfg.algo == "full", cfg.checkpoint != "none", world)
     guard = FiniteGuard(int(k["NONFINITE_PATIENCE"]), run_dir)
     trace = StepTrace(k["TRACE_STEPS"], k["PROFILE_STEPS"], run_dir, rank)
+    valid = Validation(k["VALIDATE_EVERY"], k["VALIDATION"], data, trainer) if rank == 0 else None
+    grid = SampleGrid(k["SAMPLE_EVERY"], run_dir, trainer, k["SAMPLE_PROMPTS"], k["SAMPLE_NEGATIVE"], k["SAMPLE_STEPS"], k["SAMPLE_CFG"],
+                      k["SAMPLE_SHIFT"], k["SAMPLE_SKIP_LAYERS"], k["SAMPLE_SIZE"], k["SAMPLE_SEEDS"], k["SAMPLE_BATCH"],
+                      k["SAMPLE_COLUMNS"], k["SAMPLE_AT_START"]) if rank == 0 and k["PARALLEL"] in ("none", "ddp") else None
+    xfer = TransferCounters()
     acc = cfg.grad_acc
     last = {}
+    if grid is not None and grid.due(0) and start == 0:
+        grid.run(0)
     nxt = [data.materialize(start * acc + i, rank, world) for i in range(acc)]
     for step in range(start, cfg.steps):
         trace.before(step)
@@ -198,6 +205,7 @@ def worker(k: dict, rank: int, world: int, device) -> dict:
         nxt = [data.materialize((step + 1) * acc + i, rank, world) for i in range(acc)] if step + 1 < cfg.steps else []
         out = trainer.train_step(group, next_batch=nxt[0] if nxt else None)
         speed.observe(group)
+        xfer.observe(group, trainer)
         guard.observe(out["ok"], step, trainer, group)
         trace.after(step)
         if (step + 1) % max(1, int(k["LOG_EVERY"])) == 0 or step + 1 == cfg.steps:
@@ -205,8 +213,14 @@ def worker(k: dict, rank: int, world: int, device) -> dict:
                    "opt/skipped": trainer.bundle.skipped, **speed.row(), **vram_row(device)}
             if trainer.parallel is not None:
                 row.update({f"ddp/{kk[4:]}": vv for kk, vv in trainer.parallel.metrics().items() if isinstance(vv, (int, float))})
+            row.update(xfer.row())
+            row.update(trainer.step_fn.last_terms)
             writer.write(step + 1, row)
             last = row
+        if valid is not None and valid.due(step + 1):
+            writer.write(step + 1, valid.run())
+        if grid is not None and grid.due(step + 1):
+            writer.write(step + 1, grid.run(step + 1))
         if ckpt.due(step + 1) and step + 1 < cfg.steps:
             _save(ckpt, trainer, step + 1, k, device)
     if k["FINAL_CHECKPOINT"] in ("auto", True, "always") and cfg.steps > start:

@@ -177,10 +177,10 @@ def build_teacher(k: dict, device, student=None):
         return BaseTeacher(student, dtype)
     from ..models import build_backbone
     from ..models.build import resolve_arch
-    from ..models.io import load_weights
+    from ..models.io import load_backbone
 
     model = build_backbone(resolve_arch(k["VARIANT"], k["ARCH_OVERRIDES"]), device=device, dtype=dtype, seed=0)
-    load_weights(model, k["TEACHER"])
+    load_backbone(model, k["TEACHER"])
     return Teacher(model, dtype)
 
 
