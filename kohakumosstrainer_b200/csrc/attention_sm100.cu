@@ -299,6 +299,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 // Two kernels instead of one with fp32 atomics on dQ: every output element has exactly one
 // writer, so gradients are bitwise reproducible.
 // =========================================================================================
+__device__ __forceinline__ void probe(const AttnBwdArgs& a, int iter, int slot) {
+  if (a.timeline != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && iter < a.timeline_iters) a.timeline[iter * 8 + slot] = clock64();
+}
+
 constexpr int BWD_THREADS = 320;  // TMA warp, MMA warp, 8 element-wise warps: two per TMEM lane quarter, half of the columns each,
                                    // so one warp's tensor-memory load latency hides behind the other's arithmetic
 
@@ -610,6 +614,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
           tc_fence_after();
           issue_sdp(i + 1);
         }
+        probe(a, i, 6);
         if (!mbar_wait(bar(9), i & 1, abort_flag, a.status, 863)) break;
         tc_fence_after();
         const uint32_t qaddr = sbase + KV_SM_QDO + (i % KV_Q_STAGES) * 32768, daddr = qaddr + 16384;
@@ -623,6 +628,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
         for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + KV_TM_DK, sd + 2 * k, qd + 128 * k, idesc_acc, (i | k) != 0);
         tc_commit(bar(4 + i % KV_Q_STAGES));
         tc_commit(bar(10));
+        probe(a, i, 7);
       }
       if (ok && i == n_q) tc_commit(bar(11));
     }
@@ -635,33 +641,47 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
     const float sc = a.scale * LOG2E;
     const uint64_t sc2 = f32x2(sc, sc);
     const int half = (warp - 2) >> 2;  // which 32 of the tile's 64 query columns this warp owns
+    // per warp: 2 stages x (lse[64] | delta[64]); lane l holds entries 4 l .. 4 l + 3
+    auto stage_load = [&](int tile_i, float (&v)[4]) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = lane * 4 + u;  // 0..63 lse, 64..127 delta
+        const int qrow = seg_start + tile_i * BQ + (idx & 63);
+        if (idx < 64) v[u] = qrow < seg_end ? a.lse[(size_t)head * a.n_rows + qrow] : INFINITY;
+        else v[u] = qrow < seg_end ? a.delta[(size_t)head * a.n_rows + qrow] : 0.f;
+      }
+    };
+    auto stage_store = [&](int tile_i, const float (&v)[4]) {
+      float* mine = vec + ((warp - 2) * 2 + (tile_i & 1)) * 128;
+      *reinterpret_cast<float4*>(mine + lane * 4) = make_float4(v[0], v[1], v[2], v[3]);
+    };
+    if (n_q > 0) {
+      float first[4];
+      stage_load(0, first);
+      stage_store(0, first);
+    }
+    __syncwarp();
     bool ok = !*abort_flag;
     for (int i = 0; ok && i < n_q; ++i) {
       const int st = i & 1;
-      {  // each warp stages lse / delta of this query tile for its own 32 rows (no CTA-wide barrier)
-        float* mine = vec + ((warp - 2) * 2 + st) * 128;
-        __syncwarp();
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int idx = lane * 4 + u;  // 0..63 lse, 64..127 delta
-          const int qrow = seg_start + i * BQ + (idx & 63);
-          float v;
-          if (idx < 64) v = qrow < seg_end ? a.lse[(size_t)head * a.n_rows + qrow] : INFINITY;
-          else v = qrow < seg_end ? a.delta[(size_t)head * a.n_rows + qrow] : 0.f;
-          mine[idx] = v;
-        }
-        __syncwarp();
-      }
+      // lse / delta of query tile i + 1 are requested now and parked in shared memory after this
+      // tile's arithmetic, so their global-memory latency never sits between two tiles
+      float nxt[4];
+      if (i + 1 < n_q) stage_load(i + 1, nxt);
       const float* lse = vec + ((warp - 2) * 2 + st) * 128;
       const float* dl = lse + 64;
+      const bool stamp = threadIdx.x == 64;
+      if (stamp) probe(a, i, 0);
       if (!mbar_wait(bar(7 + st), (i >> 1) & 1, abort_flag, a.status, 870 + st)) { ok = false; break; }
       tc_fence_after();
+      if (stamp) probe(a, i, 1);
       uint32_t pkp[16], pkd[16];
       {
         uint32_t s_[32], d_[32];
         tmem_ld_32x32(tmem + lane_base + KV_TM_S + st * BQ + half * 32, s_);
         tmem_ld_32x32(tmem + lane_base + KV_TM_DP + st * BQ + half * 32, d_);
         tmem_ld_wait();
+        if (stamp) probe(a, i, 2);
 #pragma unroll
         for (int c = 0; c < 16; c += 2) {
           // four query columns per step: their lse / delta come as one 16-byte shared load each
@@ -681,7 +701,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
           pkd[c + 1] = pack_bf16(g2, g3);
         }
       }
+      if (i + 1 < n_q) stage_store(i + 1, nxt);  // read by this warp only, after the __syncwarp below
+      if (stamp) probe(a, i, 3);
       if (!mbar_wait(bar(10), (i & 1) ^ 1, abort_flag, a.status, 880 + st)) { ok = false; break; }
+      if (stamp) probe(a, i, 4);
       uint8_t* prow = smem + KV_SM_PDS + r * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -693,6 +716,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(9));
+      if (stamp) probe(a, i, 5);
     }
     if (ok && mbar_wait(bar(11), 0, abort_flag, a.status, 890)) {
       tc_fence_after();
@@ -758,7 +782,17 @@ cudaError_t attention_fwd(const AttnArgs& a, cudaStream_t s) {
 }
 
 
-cudaError_t attention_bwd(const AttnBwdArgs& a, cudaStream_t s) {
+static unsigned long long* g_timeline = nullptr;
+static int g_timeline_iters = 0;
+void attention_set_timeline(unsigned long long* buf, int iters) {
+  g_timeline = buf;
+  g_timeline_iters = iters;
+}
+
+cudaError_t attention_bwd(const AttnBwdArgs& a_in, cudaStream_t s) {
+  AttnBwdArgs a = a_in;
+  a.timeline = g_timeline;
+  a.timeline_iters = g_timeline_iters;
   if (a.n_tiles <= 0 || a.heads <= 0) return cudaSuccess;
   const uint64_t cols = (uint64_t)a.heads * DH;
   CUtensorMap q128, do128, k64, v64, k128, v128, q64, do64;

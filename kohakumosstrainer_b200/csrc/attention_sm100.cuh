@@ -37,7 +37,15 @@ struct AttnBwdArgs {
   int heads;
   float scale;
   int* status;
+  // nullable probe: block (0, 0) records %clock64 per loop iteration, 8 slots each:
+  // element-wise warp 2 {loop top, operands ready, loaded from tensor memory, computed, staging free, stored}, MMA thread {6: products of
+  // the next tile issued, 7: accumulation issued}. Slots past `timeline_iters` iterations are not written.
+  unsigned long long* timeline;
+  int timeline_iters;
 };
+
+// Install (or clear, with nullptr) the probe buffer used by the next backward launches.
+void attention_set_timeline(unsigned long long* buf, int iters);
 
 cudaError_t attention_fwd(const AttnArgs& a, cudaStream_t s);
 cudaError_t attention_bwd(const AttnBwdArgs& a, cudaStream_t s);

@@ -474,6 +474,16 @@ void attention_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const T
   KM_CHECK_CUDA(kmoss::attention_bwd(a, cur_stream()));
 }
 
+// Probe buffer for the backward attention kernels (int64 [iters, 8]; None clears it).
+void attention_set_timeline(const optional<Tensor>& buf) {
+  if (buf.has_value() && buf->defined()) {
+    TORCH_CHECK(buf->scalar_type() == at::kLong && buf->is_cuda() && buf->is_contiguous() && buf->numel() % 8 == 0, "timeline: int64 CUDA [iters, 8]");
+    kmoss::attention_set_timeline(reinterpret_cast<unsigned long long*>(buf->data_ptr()), (int)(buf->numel() / 8));
+  } else {
+    kmoss::attention_set_timeline(nullptr, 0);
+  }
+}
+
 
 // ---- peer-memory collectives -------------------------------------------------------------
 int64_t allreduce_flag_words() { return kmoss::AR_FLAG_WORDS; }
@@ -565,6 +575,7 @@ TORCH_LIBRARY(kmoss_b200, m) {
   m.def("reset_status() -> ()", &reset_status);
   m.def("attention_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor tiles, float scale, "
         "Tensor(a!) dq, Tensor(b!) dk, Tensor(c!) dv) -> ()", &attention_bwd);
+  m.def("attention_set_timeline(Tensor? buf) -> ()", &attention_set_timeline);
   m.def("attention_fwd(Tensor q, Tensor k, Tensor v, Tensor tiles, float scale, Tensor(a!) o, Tensor(b!)? lse) -> ()", &attention_fwd);
   m.def("opt_record_bytes() -> int", &opt_record_bytes);
   m.def("opt_chunk_elems() -> int", &opt_chunk_elems);
