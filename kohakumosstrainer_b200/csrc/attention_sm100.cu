@@ -136,10 +136,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (!mbar_wait(bar(9), j & 1, abort_flag, a.status, 603)) break;
         if (!mbar_wait(bar(3 + st), (j >> 1) & 1, abort_flag, a.status, 604)) break;
         tc_fence_after();
-        const uint64_t pd = umma_smem_desc(sbase + SM_P, 16, 1024);
+        // A = P_j read from tensor memory: 64 bf16 per row packed two per 32-bit column, 8 columns per K = 16 step;
+        // it lives in the first 32 columns of the S_j buffer, which S_(j+2) only overwrites after this product
+        const uint32_t pt = tmem + TM_S + (uint32_t)(st * BN);
         const uint64_t vd = umma_smem_desc(sbase + SM_KV + st * 32768 + 16384, 8192, 1024);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + TM_O, pd + 2 * k, vd + 128 * k, idesc_o, (j | k) != 0);
+        for (int k = 0; k < 4; ++k) mma_f16_ts(tmem + TM_O, pt + 8 * k, vd + 128 * k, idesc_o, (j | k) != 0);
         tc_commit(bar(11 + st));  // V stage free
         tc_commit(bar(10));       // O updated, P buffer free
       }
@@ -220,31 +222,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         sum = lo + hi;
       }
       l = l * alpha + sum;
-      if (j > 0) {
-        // previous P V must be complete: the P buffer is reused and O may be rescaled
+      if (any_grow) {
+        // O is rescaled in place: P_(j-1) V_(j-1) must have completed (j > 0 here)
         if (!mbar_wait(bar(10), (j - 1) & 1, abort_flag, a.status, 710)) { ok = false; break; }
         tc_fence_after();
-        if (any_grow) {
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld_32x32(tmem + lane_base + TM_O + c * 32, o);
-            tmem_ld_wait();
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem + lane_base + TM_O + c * 32, o);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x32(tmem + lane_base + TM_O + c * 32, o);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32(tmem + lane_base + TM_O + c * 32, o);
         }
       }
-      // P row -> shared memory, 16-byte chunks XOR-swizzled by (row & 7)
-      uint8_t* prow = smem + SM_P + r * 128;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint4 w = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = w;
-      }
-      fence_proxy_async_smem();
+      // P row -> tensor memory, over the S columns this thread has already read
+      tmem_st_32x32(tmem + lane_base + TM_S + st * BN, pk);
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(9));
@@ -299,8 +293,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 // Two kernels instead of one with fp32 atomics on dQ: every output element has exactly one
 // writer, so gradients are bitwise reproducible.
 // =========================================================================================
-__device__ __forceinline__ void probe(const AttnBwdArgs& a, int iter, int slot) {
-  if (a.timeline != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && iter < a.timeline_iters) a.timeline[iter * 8 + slot] = clock64();
+// kernel 0 = dQ, 1 = dK / dV: each owns `timeline_iters` rows of 8 slots
+template <int KERNEL>
+__device__ __forceinline__ void probe_k(const AttnBwdArgs& a, int iter, int slot) {
+  if (a.timeline != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && iter < a.timeline_iters)
+    a.timeline[(KERNEL * a.timeline_iters + iter) * 8 + slot] = clock64();
 }
 
 constexpr int BWD_THREADS = 320;  // TMA warp, MMA warp, 8 element-wise warps: two per TMEM lane quarter, half of the columns each,
@@ -418,6 +415,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           tc_fence_after();
           issue_sdp(j + 1);
         }
+        probe_k<0>(a, j, 6);
         if (!mbar_wait(bar(9 + st), (j >> 1) & 1, abort_flag, a.status, 815)) break;
         tc_fence_after();
         const uint64_t sd = umma_smem_desc(sbase + DQ_SM_DS + st * 16384, 16, 1024);
@@ -426,6 +424,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + DQ_TM_DQ, sd + 2 * k, kd + 128 * k, idesc_dq, (j | k) != 0);
         tc_commit(bar(4 + j % DQ_KV_STAGES));
         tc_commit(bar(11 + st));
+        probe_k<0>(a, j, 7);
       }
       if (ok && j == n_kv) tc_commit(bar(13));
     }
@@ -443,8 +442,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     bool ok = !*abort_flag;
     for (int j = 0; ok && j < n_kv; ++j) {
       const int st = j & 1;
+      const bool stamp = threadIdx.x == 64;
+      if (stamp) probe_k<0>(a, j, 0);
       if (!mbar_wait(bar(7 + st), (j >> 1) & 1, abort_flag, a.status, 820 + st)) { ok = false; break; }
       tc_fence_after();
+      if (stamp) probe_k<0>(a, j, 1);
       const int valid = min(BN, seg_end - (seg_start + j * BN));
       uint32_t pk[16];
       {
@@ -452,6 +454,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tmem_ld_32x32(tmem + lane_base + DQ_TM_S + st * BN + half * 32, s_);
         tmem_ld_32x32(tmem + lane_base + DQ_TM_DP + st * BN + half * 32, d_);
         tmem_ld_wait();
+        if (stamp) probe_k<0>(a, j, 2);
         // dS = 2^(s * sc - lse) * (dP - delta), two elements per packed instruction
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -468,7 +471,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           pk[i] = pack_bf16(v0, v1);
         }
       }
+      if (stamp) probe_k<0>(a, j, 3);
       if (!mbar_wait(bar(11 + st), ((j >> 1) & 1) ^ 1, abort_flag, a.status, 830 + st)) { ok = false; break; }
+      if (stamp) probe_k<0>(a, j, 4);
       uint8_t* prow = smem + DQ_SM_DS + st * 16384 + r * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c)
@@ -477,6 +482,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(9 + st));
+      if (stamp) probe_k<0>(a, j, 5);
     }
     if (ok && mbar_wait(bar(13), 0, abort_flag, a.status, 840)) {
       tc_fence_after();
@@ -614,7 +620,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
           tc_fence_after();
           issue_sdp(i + 1);
         }
-        probe(a, i, 6);
+        probe_k<1>(a, i, 6);
         if (!mbar_wait(bar(9), i & 1, abort_flag, a.status, 863)) break;
         tc_fence_after();
         const uint32_t qaddr = sbase + KV_SM_QDO + (i % KV_Q_STAGES) * 32768, daddr = qaddr + 16384;
@@ -628,7 +634,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
         for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + KV_TM_DK, sd + 2 * k, qd + 128 * k, idesc_acc, (i | k) != 0);
         tc_commit(bar(4 + i % KV_Q_STAGES));
         tc_commit(bar(10));
-        probe(a, i, 7);
+        probe_k<1>(a, i, 7);
       }
       if (ok && i == n_q) tc_commit(bar(11));
     }
@@ -671,17 +677,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       const float* lse = vec + ((warp - 2) * 2 + st) * 128;
       const float* dl = lse + 64;
       const bool stamp = threadIdx.x == 64;
-      if (stamp) probe(a, i, 0);
+      if (stamp) probe_k<1>(a, i, 0);
       if (!mbar_wait(bar(7 + st), (i >> 1) & 1, abort_flag, a.status, 870 + st)) { ok = false; break; }
       tc_fence_after();
-      if (stamp) probe(a, i, 1);
+      if (stamp) probe_k<1>(a, i, 1);
       uint32_t pkp[16], pkd[16];
       {
         uint32_t s_[32], d_[32];
         tmem_ld_32x32(tmem + lane_base + KV_TM_S + st * BQ + half * 32, s_);
         tmem_ld_32x32(tmem + lane_base + KV_TM_DP + st * BQ + half * 32, d_);
         tmem_ld_wait();
-        if (stamp) probe(a, i, 2);
+        if (stamp) probe_k<1>(a, i, 2);
 #pragma unroll
         for (int c = 0; c < 16; c += 2) {
           // four query columns per step: their lse / delta come as one 16-byte shared load each
@@ -702,9 +708,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
         }
       }
       if (i + 1 < n_q) stage_store(i + 1, nxt);  // read by this warp only, after the __syncwarp below
-      if (stamp) probe(a, i, 3);
+      if (stamp) probe_k<1>(a, i, 3);
       if (!mbar_wait(bar(10), (i & 1) ^ 1, abort_flag, a.status, 880 + st)) { ok = false; break; }
-      if (stamp) probe(a, i, 4);
+      if (stamp) probe_k<1>(a, i, 4);
       uint8_t* prow = smem + KV_SM_PDS + r * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -716,7 +722,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(9));
-      if (stamp) probe(a, i, 5);
+      if (stamp) probe_k<1>(a, i, 5);
     }
     if (ok && mbar_wait(bar(11), 0, abort_flag, a.status, 890)) {
       tc_fence_after();

@@ -37,7 +37,7 @@ struct AttnBwdArgs {
   int heads;
   float scale;
   int* status;
-  // nullable probe: block (0, 0) records %clock64 per loop iteration, 8 slots each:
+  // nullable probe [2, timeline_iters, 8] (dQ kernel rows, then dK / dV rows): block (0, 0) records %clock64 per loop iteration:
   // element-wise warp 2 {loop top, operands ready, loaded from tensor memory, computed, staging free, stored}, MMA thread {6: products of
   // the next tile issued, 7: accumulation issued}. Slots past `timeline_iters` iterations are not written.
   unsigned long long* timeline;

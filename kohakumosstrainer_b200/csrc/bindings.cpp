@@ -477,8 +477,8 @@ void attention_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const T
 // Probe buffer for the backward attention kernels (int64 [iters, 8]; None clears it).
 void attention_set_timeline(const optional<Tensor>& buf) {
   if (buf.has_value() && buf->defined()) {
-    TORCH_CHECK(buf->scalar_type() == at::kLong && buf->is_cuda() && buf->is_contiguous() && buf->numel() % 8 == 0, "timeline: int64 CUDA [iters, 8]");
-    kmoss::attention_set_timeline(reinterpret_cast<unsigned long long*>(buf->data_ptr()), (int)(buf->numel() / 8));
+    TORCH_CHECK(buf->scalar_type() == at::kLong && buf->is_cuda() && buf->is_contiguous() && buf->numel() % 16 == 0, "timeline: int64 CUDA [2, iters, 8] (dQ rows, then dK / dV rows)");
+    kmoss::attention_set_timeline(reinterpret_cast<unsigned long long*>(buf->data_ptr()), (int)(buf->numel() / 16));
   } else {
     kmoss::attention_set_timeline(nullptr, 0);
   }
