@@ -37,8 +37,7 @@ constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units: P stays below 2^8
 // shared memory map (bytes, from a 1024-aligned base)
 constexpr int SM_Q = 0;                       // 2 k-blocks x [128 rows][128 B]
 constexpr int SM_KV = 32768;                  // 2 stages x (K 16 KB + V 16 KB)
-constexpr int SM_P = SM_KV + 2 * 32768;       // [128 rows][128 B]
-constexpr int SM_BAR = SM_P + 16384;
+constexpr int SM_BAR = SM_KV + 2 * 32768;     // (P is parked in tensor memory)
 constexpr int FWD_SMEM = SM_BAR + 256;
 
 // TMEM columns
@@ -222,9 +221,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         sum = lo + hi;
       }
       l = l * alpha + sum;
+      // Every phase of o_done is consumed in order (a parity wait that skipped phases could alias an older one); by now
+      // P_(j-1) V_(j-1), issued a whole tile ago, has normally completed, so this does not stall.
+      if (j > 0 && !mbar_wait(bar(10), (j - 1) & 1, abort_flag, a.status, 710)) { ok = false; break; }
       if (any_grow) {
-        // O is rescaled in place: P_(j-1) V_(j-1) must have completed (j > 0 here)
-        if (!mbar_wait(bar(10), (j - 1) & 1, abort_flag, a.status, 710)) { ok = false; break; }
+        // O is rescaled in place (j > 0 here)
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -322,8 +323,7 @@ constexpr int DQ_SM_Q = 0;                      // 32 KB
 constexpr int DQ_SM_DO = 32768;                 // 32 KB
 constexpr int DQ_KV_STAGES = 3;                 // the load of tile j + 2 is in flight while tile j computes
 constexpr int DQ_SM_KV = 65536;                 // 3 stages x (K 16 KB + V 16 KB)
-constexpr int DQ_SM_DS = DQ_SM_KV + DQ_KV_STAGES * 32768;  // 2 buffers x 16 KB
-constexpr int DQ_SM_BAR = DQ_SM_DS + 32768;
+constexpr int DQ_SM_BAR = DQ_SM_KV + DQ_KV_STAGES * 32768;  // dS never touches shared memory: it is parked in tensor memory
 constexpr int DQ_SMEM = DQ_SM_BAR + 256;
 constexpr uint32_t DQ_TM_S = 0, DQ_TM_DP = 128, DQ_TM_DQ = 256, DQ_TM_COLS = 512;
 
@@ -418,10 +418,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         probe_k<0>(a, j, 6);
         if (!mbar_wait(bar(9 + st), (j >> 1) & 1, abort_flag, a.status, 815)) break;
         tc_fence_after();
-        const uint64_t sd = umma_smem_desc(sbase + DQ_SM_DS + st * 16384, 16, 1024);
+        // A = dS_j from tensor memory: the warp of key half h parks its 32 bf16 per row in columns [32 h, 32 h + 16) of the
+        // S_j buffer (inside the range it alone reads), so K = 16 steps 0, 1 sit at +0, +8 and steps 2, 3 at +32, +40
+        const uint32_t dst = tmem + DQ_TM_S + (uint32_t)(st * BN);
         const uint64_t kd = umma_smem_desc(sbase + DQ_SM_KV + (j % DQ_KV_STAGES) * 32768, 8192, 1024);  // K_j read MN-major
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + DQ_TM_DQ, sd + 2 * k, kd + 128 * k, idesc_dq, (j | k) != 0);
+        for (int k = 0; k < 4; ++k) mma_f16_ts(tmem + DQ_TM_DQ, dst + (k >> 1) * 32 + (k & 1) * 8, kd + 128 * k, idesc_dq, (j | k) != 0);
         tc_commit(bar(4 + j % DQ_KV_STAGES));
         tc_commit(bar(11 + st));
         probe_k<0>(a, j, 7);
@@ -472,13 +474,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
       }
       if (stamp) probe_k<0>(a, j, 3);
-      if (!mbar_wait(bar(11 + st), ((j >> 1) & 1) ^ 1, abort_flag, a.status, 830 + st)) { ok = false; break; }
+      // S_j's buffer is free for dS_j: dQ_(j-2), its previous reader, was issued before S_j, which has completed
+      tmem_st_32x16(tmem + lane_base + DQ_TM_S + st * BN + half * 32, pk);
+      tmem_st_wait();
       if (stamp) probe_k<0>(a, j, 4);
-      uint8_t* prow = smem + DQ_SM_DS + st * 16384 + r * 128;
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-        *reinterpret_cast<uint4*>(prow + (((half * 4 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-      fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(9 + st));
@@ -526,8 +525,8 @@ constexpr int KV_SM_K = 0;                       // 32 KB: 2 k-blocks x [128 key
 constexpr int KV_SM_V = 32768;                   // 32 KB
 constexpr int KV_Q_STAGES = 3;                   // the load of query tile i + 2 is in flight while tile i computes
 constexpr int KV_SM_QDO = 65536;                 // 3 stages x (Q 16 KB + dO 16 KB)
-constexpr int KV_SM_PDS = KV_SM_QDO + KV_Q_STAGES * 32768;  // P^T 16 KB + dS^T 16 KB (one buffer: written after dV / dK of the tile before)
-constexpr int KV_SM_VEC = KV_SM_PDS + 32768;     // per element-wise warp: 2 x (lse[64] | delta[64]) fp32
+constexpr int KV_SM_VEC = KV_SM_QDO + KV_Q_STAGES * 32768;  // (P^T / dS^T are parked in tensor memory)
+//    // per element-wise warp: 2 x (lse[64] | delta[64]) fp32
 constexpr int KV_SM_BAR = KV_SM_VEC + 8192;
 constexpr int KV_SMEM = KV_SM_BAR + 256;
 constexpr uint32_t KV_TM_S = 0, KV_TM_DP = 128, KV_TM_DV = 256, KV_TM_DK = 384, KV_TM_COLS = 512;
@@ -540,7 +539,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
   const uint32_t sbase = smem_u32(smem);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + KV_SM_BAR);
   const uint32_t bar0 = smem_u32(bars);
-  // 0 kv_full | 1,2,3 qdo_full | 4,5,6 qdo_empty | 7,8 sdp_full | 9 pds_full | 10 pds_empty | 11 done
+  // 0 kv_full | 1,2,3 qdo_full | 4,5,6 qdo_empty | 7,8 sdp_full | 9,10 pds_full (P^T / dS^T parked in tensor memory) | 11 done
   auto bar = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -552,7 +551,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
 
   if (threadIdx.x == 0) {
     if ((sbase & 1023u) != 0) report_status(a.status, STATUS_BAD_ARGUMENT, 902, (int)(sbase & 1023u));
-    for (int i = 0; i < 12; ++i) mbar_init(bar(i), i == 9 ? 8 : 1);
+    for (int i = 0; i < 12; ++i) mbar_init(bar(i), (i == 9 || i == 10) ? 8 : 1);
     *abort_flag = (sbase & 1023u) != 0 ? 1 : 0;
     mbar_fence_init();
   }
@@ -621,19 +620,19 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
           issue_sdp(i + 1);
         }
         probe_k<1>(a, i, 6);
-        if (!mbar_wait(bar(9), i & 1, abort_flag, a.status, 863)) break;
+        if (!mbar_wait(bar(9 + st), (i >> 1) & 1, abort_flag, a.status, 863)) break;
         tc_fence_after();
         const uint32_t qaddr = sbase + KV_SM_QDO + (i % KV_Q_STAGES) * 32768, daddr = qaddr + 16384;
-        const uint64_t pd = umma_smem_desc(sbase + KV_SM_PDS, 16, 1024);
-        const uint64_t sd = umma_smem_desc(sbase + KV_SM_PDS + 16384, 16, 1024);
+        // A = P^T_i / dS^T_i from tensor memory, parked over the S^T_i / dP^T_i buffers: the warp of query half h
+        // writes columns [32 h, 32 h + 16) (inside the range it alone reads): K = 16 steps at +0, +8, +32, +40
+        const uint32_t pt = tmem + KV_TM_S + (uint32_t)(st * BQ), dt = tmem + KV_TM_DP + (uint32_t)(st * BQ);
         const uint64_t dod = umma_smem_desc(daddr, 8192, 1024);  // dO_i read MN-major
         const uint64_t qd = umma_smem_desc(qaddr, 8192, 1024);   // Q_i read MN-major
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + KV_TM_DV, pd + 2 * k, dod + 128 * k, idesc_acc, (i | k) != 0);
+        for (int k = 0; k < 4; ++k) mma_f16_ts(tmem + KV_TM_DV, pt + (k >> 1) * 32 + (k & 1) * 8, dod + 128 * k, idesc_acc, (i | k) != 0);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_f16_ss(tmem + KV_TM_DK, sd + 2 * k, qd + 128 * k, idesc_acc, (i | k) != 0);
+        for (int k = 0; k < 4; ++k) mma_f16_ts(tmem + KV_TM_DK, dt + (k >> 1) * 32 + (k & 1) * 8, qd + 128 * k, idesc_acc, (i | k) != 0);
         tc_commit(bar(4 + i % KV_Q_STAGES));
-        tc_commit(bar(10));
         probe_k<1>(a, i, 7);
       }
       if (ok && i == n_q) tc_commit(bar(11));
@@ -709,19 +708,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       }
       if (i + 1 < n_q) stage_store(i + 1, nxt);  // read by this warp only, after the __syncwarp below
       if (stamp) probe_k<1>(a, i, 3);
-      if (!mbar_wait(bar(10), (i & 1) ^ 1, abort_flag, a.status, 880 + st)) { ok = false; break; }
+      // the S^T_i / dP^T_i buffers are free for P^T_i / dS^T_i: their previous readers (dV, dK of tile i - 2) were
+      // issued before S^T_i, which has completed
+      tmem_st_32x16(tmem + lane_base + KV_TM_S + st * BQ + half * 32, pkp);
+      tmem_st_32x16(tmem + lane_base + KV_TM_DP + st * BQ + half * 32, pkd);
+      tmem_st_wait();
       if (stamp) probe_k<1>(a, i, 4);
-      uint8_t* prow = smem + KV_SM_PDS + r * 128;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int off = ((half * 4 + c) ^ (r & 7)) << 4;
-        *reinterpret_cast<uint4*>(prow + off) = make_uint4(pkp[4 * c], pkp[4 * c + 1], pkp[4 * c + 2], pkp[4 * c + 3]);
-        *reinterpret_cast<uint4*>(prow + 16384 + off) = make_uint4(pkd[4 * c], pkd[4 * c + 1], pkd[4 * c + 2], pkd[4 * c + 3]);
-      }
-      fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(9));
+      if (lane == 0) mbar_arrive(bar(9 + st));
       if (stamp) probe_k<1>(a, i, 5);
     }
     if (ok && mbar_wait(bar(11), 0, abort_flag, a.status, 890)) {
