@@ -62,6 +62,10 @@ def fuse_qkv(sd: dict[str, Tensor], depth: int) -> dict[str, Tensor]:
 def normalize_keys(sd: dict[str, Tensor]) -> dict[str, Tensor]:
     prefix = strip_prefix(sd.keys())
     sd = {k[len(prefix):]: v for k, v in sd.items()}
+    if any(k.endswith(".comfy_quant") or k.endswith(".weight_scale") or k.endswith(".scale_weight") for k in sd):
+        from ..quant.comfy import split_fused
+
+        return split_fused(sd)      # quantised files: codes, scales and records of a fused q | k | v split together
     return split_fused_qkv(sd)
 
 
@@ -94,6 +98,16 @@ def load_backbone(model, path: str | Path, strict: bool = True) -> dict:
     """Load weights into `model` with strict key accounting; returns the file metadata."""
     state, meta = read_state(path)
     state = normalize_keys(state)
+    if any(k.endswith(".comfy_quant") or k.endswith(".weight_scale") or k.endswith(".scale_weight") for k in state):
+        from ..quant.comfy import attach_quantized
+
+        state, _ = attach_quantized(model, state)     # stored int8 / fp8 bases attach as they are: no 16-bit copy
+        state = {k: v for k, v in state.items() if not k.endswith(".config")}
+    fix = (meta or {}).get("kohakumoss_fp16_fix")
+    if fix:
+        import json
+
+        model.__dict__["stream_scale"] = float(json.loads(fix).get("scale", 1.0))
     own = dict(model.state_dict())
     missing = [k for k in own if k not in state and k not in DERIVED]
     unexpected = [k for k in state if k not in own]

@@ -1,0 +1,66 @@
+"""Export a training state's adapters: ComfyUI / LyCORIS file, or a merged transformer
+(role of `scripts/export/export.py` in the reference).
+
+    python -m kohakumosstrainer_b200.cli.run scripts/export/export.py --set WEIGHTS=<model dir> \
+        --set ADAPTER=<run>/checkpoints/step_00001000/trainable.safetensors --set OUT=lora.safetensors
+    ... --set FORMAT=merged --set OUT=merged.safetensors
+"""
+
+WEIGHTS = ""            # base transformer (HF dir, single file); "" with VARIANT builds random weights (tests)
+VARIANT = "base"
+ARCH_OVERRIDES = {}
+ADAPTER = ""            # a run checkpoint's trainable.safetensors
+OUT = ""
+FORMAT = "comfy"        # comfy | lycoris (= hf) | merged | diffusers
+SAVE_DTYPE = "bf16"
+MULTIPLIER = 1.0
+FUSED_QKV = False
+DEVICE = "cpu"
+ALGO = "lora"           # what the state holds (recorded in the checkpoint's metadata when present)
+PRESET = "attn-mlp"
+DIM = 8
+ALPHA = 8.0
+ALGO_KWARGS = {}
+
+globals().update(globals().pop("__kmoss_overrides__", {}))
+
+
+def main():
+    import torch
+    from safetensors import safe_open
+    from safetensors.torch import load_file
+
+    from kohakumosstrainer_b200 import adapters as A
+    from kohakumosstrainer_b200.adapters.export import export
+    from kohakumosstrainer_b200.models import build_backbone
+    from kohakumosstrainer_b200.models.build import resolve_arch
+    from kohakumosstrainer_b200.models.io import load_backbone, save_diffusers, save_single
+
+    if not OUT or not ADAPTER:
+        raise SystemExit("set ADAPTER and OUT")
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[SAVE_DTYPE]
+    model = build_backbone(resolve_arch(VARIANT, ARCH_OVERRIDES), device=DEVICE, dtype=torch.float32, seed=0, init=not WEIGHTS)
+    if WEIGHTS:
+        load_backbone(model, WEIGHTS)
+    with safe_open(ADAPTER, "pt") as f:
+        meta = f.metadata() or {}
+    cfg = A.AdapterConfig(algo=meta.get("kohakumoss_algo", ALGO), preset=meta.get("kohakumoss_preset", PRESET), dim=int(meta.get("kohakumoss_dim", DIM)),
+                          alpha=float(meta.get("kohakumoss_alpha", ALPHA)), algo_kwargs=dict(ALGO_KWARGS), dtype=torch.float32)
+    aset = A.apply(model, cfg)
+    missing = aset.load_state_dict(load_file(ADAPTER), strict=False) if hasattr(aset, "load_state_dict") else None
+    fmt = {"hf": "lycoris"}.get(FORMAT, FORMAT)
+    if fmt in ("comfy", "lycoris"):
+        path = export(aset, model, OUT, fmt, fused_qkv=bool(FUSED_QKV), dtype=dtype)
+    elif fmt == "merged":
+        aset.set_multiplier(MULTIPLIER) if hasattr(aset, "set_multiplier") else None
+        path = save_single(model, OUT, dtype=dtype, fused_qkv=bool(FUSED_QKV), merge_adapters=True)
+    elif fmt == "diffusers":
+        path = save_diffusers(model, OUT, dtype=dtype, merge_adapters=True)
+    else:
+        raise SystemExit(f"FORMAT={FORMAT!r} is not comfy | lycoris | hf | merged | diffusers")
+    print(f"wrote {OUT} ({fmt})")
+    return {"path": str(path or OUT), "missing": missing}
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,35 @@
+"""Merge adapter files into a transformer and write it as one file (role of `scripts/export/merge.py`).
+
+    ... scripts/export/merge.py --set WEIGHTS=<model> --set ADAPTERS="[('lora.safetensors', 1.0)]" --set OUT=merged.safetensors
+"""
+
+WEIGHTS = ""
+VARIANT = "base"
+ARCH_OVERRIDES = {}
+ADAPTERS = []           # [(path, multiplier)]
+OUT = ""
+SAVE_DTYPE = "bf16"
+FUSED_QKV = False
+DEVICE = "cpu"
+
+globals().update(globals().pop("__kmoss_overrides__", {}))
+
+
+def main():
+    import torch
+
+    from kohakumosstrainer_b200.inference import MossPipeline
+    from kohakumosstrainer_b200.models.io import save_single
+
+    if not OUT:
+        raise SystemExit("set OUT")
+    pipe = MossPipeline.from_pretrained(WEIGHTS, VARIANT, dict(ARCH_OVERRIDES), device=DEVICE, precision="fp32", adapters=list(ADAPTERS),
+                                        adapter_mode="merge")
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[SAVE_DTYPE]
+    save_single(pipe.backbone, OUT, dtype=dtype, fused_qkv=bool(FUSED_QKV))
+    print(f"wrote {OUT}")
+    return OUT
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,43 @@
+"""Quantise the linears of any safetensors checkpoint (the text encoder's, for one) to int8 or fp8
+weight-only in the ComfyUI quantised layout (role of `scripts/export/text_quant.py`).
+
+    ... scripts/export/text_quant.py --set WEIGHTS=text_encoder.safetensors --set FORMAT=int8 --set OUT=text_encoder_int8.safetensors
+"""
+
+WEIGHTS = ""
+FORMAT = "int8"        # int8 | fp8
+LAYERS = r".*(q_proj|k_proj|v_proj|o_proj|gate_proj|up_proj|down_proj|in_proj\w*|out_proj)"
+MIN_FEATURES = 256
+SAVE_DTYPE = "bf16"
+OUT = ""
+
+globals().update(globals().pop("__kmoss_overrides__", {}))
+
+
+def main():
+    import torch
+    from safetensors.torch import load_file, save_file
+
+    from kohakumosstrainer_b200.quant.comfy import fp8_state, int8_convrot_state
+
+    if not WEIGHTS or not OUT:
+        raise SystemExit("set WEIGHTS and OUT")
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16}[SAVE_DTYPE]
+    sd = load_file(WEIGHTS)
+    small = {k for k, v in sd.items() if k.endswith(".weight") and (v.dim() != 2 or min(v.shape) < int(MIN_FEATURES))}
+    keep = {k: sd.pop(k) for k in small}
+    if FORMAT == "int8":
+        out = int8_convrot_state(sd, LAYERS, 0, dtype, fuse_qkv=False)
+    elif FORMAT == "fp8":
+        out = fp8_state(sd, LAYERS, "row", dtype, int(MIN_FEATURES))
+    else:
+        raise SystemExit("FORMAT must be int8 or fp8")
+    out.update({k: v.to(dtype) if v.is_floating_point() else v for k, v in keep.items()})
+    save_file({k: v.contiguous() for k, v in out.items()}, OUT, metadata={"kohakumoss_format": f"text-{FORMAT}"})
+    n = sum(k.endswith(".comfy_quant") for k in out)
+    print(f"wrote {OUT}: {n} quantised linears")
+    return n
+
+
+if __name__ == "__main__":
+    main()

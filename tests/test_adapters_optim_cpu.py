@@ -151,3 +151,66 @@ def test_int8_and_mxfp8_formats_cpu():
     mx = F.MxFp8Weight.from_dense(w)
     assert (mx.weight(torch.float32) - w).abs().max() < 0.07 * w.abs().max()
     assert set(mx.state("l.")) == {"l.weight", "l.weight_scale_mx"} and mx.scales.shape == (32, 2)
+
+
+def test_export_scripts_roundtrip(tmp_path):
+    """Train-state -> exports; dense -> fp8 / int8 ConvRot files -> loaded back with stored bases."""
+    from safetensors.torch import load_file, save_file
+
+    from kohakumosstrainer_b200 import adapters as A
+    from kohakumosstrainer_b200.config import run_script
+    from kohakumosstrainer_b200.models import build_backbone
+    from kohakumosstrainer_b200.models.build import resolve_arch
+    from kohakumosstrainer_b200.models.io import load_backbone, save_single
+    from kohakumosstrainer_b200.types.seqinfo import build_seqinfo
+
+    over = {"text_dim": 32, "latent_channels": 8}
+    arch = resolve_arch("tiny", over)
+    model = build_backbone(arch, device="cpu", dtype=torch.float32, seed=3).eval()
+    dense = tmp_path / "dense.safetensors"
+    save_single(model, dense, dtype=torch.float32)
+    seq = build_seqinfo(torch.tensor([[4, 4]]), torch.tensor([5]))
+    z, t, s = torch.randn(16, 8), torch.randn(5, 32), torch.tensor([0.4])
+    with torch.no_grad():
+        ref = model(z, t, s, seq)
+    common = [f"WEIGHTS={str(dense)!r}", "VARIANT='tiny'", f"ARCH_OVERRIDES={over!r}"]
+    for script, extra, key in (("fp8_quant.py", ["MIN_FEATURES=16"], "fp8"), ("comfy_int8.py", ["GROUP=64", "ATTENTION_HINT=''"], "int8")):
+        out = tmp_path / f"{key}.safetensors"
+        run_script(f"scripts/export/{script}", None, common + extra + [f"OUT={str(out)!r}"])
+        sd = load_file(out)
+        assert any(k.endswith(".comfy_quant") for k in sd)
+        assert (key == "int8") == any(".proj.qkv.weight" in k for k in sd)          # the ConvRot layout stores q | k | v fused
+        fresh = build_backbone(arch, device="cpu", dtype=torch.float32, seed=9).eval()
+        load_backbone(fresh, out)
+        assert fresh.layers[0].proj["q"].base is not None
+        with torch.no_grad():
+            got = fresh(z, t, s, seq)
+        assert (got - ref).abs().max() < 0.02 * ref.abs().max()
+    aset = A.apply(model, A.AdapterConfig(algo="lora", preset="attn-mlp", dim=4, alpha=4.0, dtype=torch.float32))
+    for p in aset.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    state = tmp_path / "trainable.safetensors"
+    save_file({k: v.detach().contiguous() for k, v in aset.state_dict().items()}, state,
+              metadata={"kohakumoss_algo": "lora", "kohakumoss_preset": "attn-mlp", "kohakumoss_dim": "4", "kohakumoss_alpha": "4.0"})
+    with torch.no_grad():
+        tuned = model(z, t, s, seq)
+    for fmt in ("comfy", "lycoris", "merged"):
+        out = tmp_path / f"out_{fmt}.safetensors"
+        run_script("scripts/export/export.py", None, common + [f"ADAPTER={str(state)!r}", f"OUT={str(out)!r}", f"FORMAT={fmt!r}", "SAVE_DTYPE='fp32'"])
+        assert out.exists()
+    merged = build_backbone(arch, device="cpu", dtype=torch.float32, seed=5).eval()
+    load_backbone(merged, tmp_path / "out_merged.safetensors")
+    with torch.no_grad():
+        assert (merged(z, t, s, seq) - tuned).abs().max() < 1e-4 * tuned.abs().max() + 1e-5
+    out = tmp_path / "merged2.safetensors"
+    run_script("scripts/export/merge.py", None, common + [f"ADAPTERS=[({str(tmp_path / 'out_comfy.safetensors')!r}, 1.0)]", f"OUT={str(out)!r}", "SAVE_DTYPE='fp32'"])
+    again = build_backbone(arch, device="cpu", dtype=torch.float32, seed=6).eval()
+    load_backbone(again, out)
+    with torch.no_grad():
+        assert (again(z, t, s, seq) - tuned).abs().max() < 1e-3 * tuned.abs().max() + 1e-5
+    run_script("scripts/export/fp16_fix.py", None, common + [f"OUT={str(tmp_path / 'folded.safetensors')!r}", "SCALE=4.0", "SAVE_DTYPE='fp32'"])
+    folded = build_backbone(arch, device="cpu", dtype=torch.float32, seed=7).eval()
+    load_backbone(folded, tmp_path / "folded.safetensors")
+    assert folded.__dict__["stream_scale"] == 4.0
+    run_script("scripts/export/text_quant.py", None, [f"WEIGHTS={str(dense)!r}", f"OUT={str(tmp_path / 'tq.safetensors')!r}", "LAYERS='.*proj\\\\.(q|k|v|o)'", "MIN_FEATURES=16"])
+    assert any(k.endswith(".comfy_quant") for k in load_file(tmp_path / "tq.safetensors"))
