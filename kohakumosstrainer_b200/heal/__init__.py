@@ -1,0 +1,10 @@
+"""Massive-channel heal of the DiT: stream taps at the reader norms, channel calibration, the
+channel-weighted RMSNorm and its anneal, distillation from the original model, the exact uniform
+stream rescale, merging a run into a plain DiT file (`src/kohakumoss/heal/*` in the reference)."""
+
+from .channels import apply_shrink, channel_mean_square, peak_ratio, reader_norms, shrink_scales, top_channels, writer_params
+from .trainer import Heal, HealConfig, merge_student, rescale_stream
+from .wnorm import WeightedOps, anneal_lam, anneal_t
+
+__all__ = ["apply_shrink", "channel_mean_square", "peak_ratio", "reader_norms", "shrink_scales", "top_channels", "writer_params", "Heal",
+           "HealConfig", "merge_student", "rescale_stream", "WeightedOps", "anneal_lam", "anneal_t"]

@@ -1,0 +1,59 @@
+"""Pre-compute the heal's training records: noised inputs and the TEACHER's velocity for a fixed set of
+batches and sigmas, stored as one `.pt` per batch, so later heal runs skip the teacher forward (role of
+`scripts/heal/cache.py`)."""
+
+WEIGHTS = ""
+VARIANT = "base"
+ARCH_OVERRIDES = {}
+DATASETS = [{"type": "synthetic"}]
+MAX_TOKENS = 8192
+SIZE_STEP = 64
+SEED = 0
+BATCHES = 64
+SIGMAS = (0.1, 0.3, 0.5, 0.7, 0.9)
+OUT = "runs/heal/records"
+DEVICE = "cuda"
+
+globals().update(globals().pop("__kmoss_overrides__", {}))
+
+
+def main():
+    from pathlib import Path
+
+    import torch
+
+    from kohakumosstrainer_b200.config import collect
+    from kohakumosstrainer_b200.diffusion.objective import noise_latents
+    from kohakumosstrainer_b200.models import build_backbone
+    from kohakumosstrainer_b200.models.build import resolve_arch
+    from kohakumosstrainer_b200.models.io import load_backbone
+    from kohakumosstrainer_b200.training.entry import build_dataset
+
+    k = collect(globals())
+    device = torch.device(DEVICE if torch.cuda.is_available() else "cpu")
+    dtype = torch.float32 if device.type == "cpu" else torch.bfloat16
+    arch = resolve_arch(VARIANT, ARCH_OVERRIDES)
+    model = build_backbone(arch, device=device, dtype=dtype, seed=SEED, init=not WEIGHTS).eval()
+    if WEIGHTS:
+        load_backbone(model, WEIGHTS)
+    data = build_dataset({**k, "SIZE_STEP": SIZE_STEP}, arch.text_dim, arch.latent_channels)
+    out = Path(OUT)
+    out.mkdir(parents=True, exist_ok=True)
+    g = torch.Generator(device).manual_seed(SEED)
+    for i in range(int(BATCHES)):
+        b = data.materialize(i, 0, 1).to_device(device, torch.float32, dtype)
+        rec = {"hw": b.seq.hw.cpu() if hasattr(b.seq, "hw") else None, "text": b.text.cpu(), "latents": b.latents.cpu(), "teacher": {}}
+        eps = torch.randn(b.latents.shape, generator=g, device=device, dtype=torch.float32)
+        for s in SIGMAS:
+            sigma = torch.full((b.seq.batch,), float(s), device=device)
+            z, _ = noise_latents(b.latents.float(), eps, sigma, b.seq.seg_img)
+            with torch.no_grad():
+                rec["teacher"][float(s)] = model(z.to(dtype), b.text.to(dtype), sigma, b.seq).cpu()
+        rec["eps"] = eps.cpu()
+        torch.save(rec, out / f"{i:06d}.pt")
+    print(f"wrote {BATCHES} records to {out}")
+    return int(BATCHES)
+
+
+if __name__ == "__main__":
+    main()

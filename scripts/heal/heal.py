@@ -1,0 +1,85 @@
+"""Heal run: calibrate the massive channels of WEIGHTS, shrink them in a student copy and distil
+the student from the original while the channel-weighted norms anneal to plain RMSNorm; writes
+`<OUT>/healed.safetensors` and `<OUT>/report.json`. Multi-GPU: launch with torchrun (gradients are
+averaged with a plain all-reduce). Role of `scripts/heal/heal.py` in the reference.
+
+    python -m kohakumosstrainer_b200.cli.run scripts/heal/heal.py --config configs/heal/recipes/recipes_anneal_5k.py --set WEIGHTS=<model>
+"""
+
+WEIGHTS = ""
+VARIANT = "base"
+ARCH_OVERRIDES = {}
+DATASETS = [{"type": "synthetic"}]
+MAX_TOKENS = 8192
+SIZE_STEP = 64
+SEED = 0
+TAU = 8.0
+STEPS = 5000
+ANNEAL_STEPS = 3000
+WARMUP = 100
+LR = 1e-5
+HARD_WEIGHT = 0.0
+CONC_WEIGHT = 0.0
+CONC_K = 8
+CALIB_BATCHES = 8
+LOG_EVERY = 50
+OUT = "runs/heal"
+DEVICE = "cuda"
+SAVE_DTYPE = "bf16"
+
+globals().update(globals().pop("__kmoss_overrides__", {}))
+
+
+def main():
+    import json
+    import os
+    from pathlib import Path
+
+    import torch
+    import torch.distributed as dist
+
+    from kohakumosstrainer_b200.config import collect
+    from kohakumosstrainer_b200.heal import Heal, HealConfig, merge_student
+    from kohakumosstrainer_b200.models import build_backbone
+    from kohakumosstrainer_b200.models.build import resolve_arch
+    from kohakumosstrainer_b200.models.io import load_backbone, save_single
+    from kohakumosstrainer_b200.training.entry import build_dataset
+
+    k = collect(globals())
+    if "RANK" in os.environ and not dist.is_initialized():
+        dist.init_process_group("nccl" if torch.cuda.is_available() and DEVICE != "cpu" else "gloo")
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    device = torch.device(DEVICE if DEVICE == "cpu" or not torch.cuda.is_available() else f"cuda:{int(os.environ.get('LOCAL_RANK', 0))}")
+    if not torch.cuda.is_available():
+        device = torch.device("cpu")
+    dtype = torch.float32 if device.type == "cpu" else torch.bfloat16
+    arch = resolve_arch(VARIANT, ARCH_OVERRIDES)
+    model = build_backbone(arch, device=device, dtype=dtype, seed=SEED, init=not WEIGHTS)
+    if WEIGHTS:
+        load_backbone(model, WEIGHTS)
+    data = build_dataset({**k, "SIZE_STEP": SIZE_STEP}, arch.text_dim, arch.latent_channels)
+    cfg = HealConfig(TAU, STEPS, ANNEAL_STEPS, WARMUP, LR, HARD_WEIGHT, CONC_WEIGHT, CONC_K, CALIB_BATCHES, SEED)
+    heal = Heal(model, cfg, data, device, dtype)
+    out = Path(OUT)
+    out.mkdir(parents=True, exist_ok=True)
+    if rank == 0:
+        print(f"massive channels (channel, peak ratio): {heal.report['top']}; shrunk {heal.report['shrunk']}")
+    log = []
+    for step in range(STEPS):
+        row = heal.train_step()
+        if rank == 0 and ((step + 1) % LOG_EVERY == 0 or step + 1 == STEPS):
+            print(f"step {step + 1} " + " ".join(f"{a}={b:.4g}" for a, b in row.items()))
+            log.append({"step": step + 1, **row})
+    if rank == 0:
+        final = heal.evaluate()
+        healed = merge_student(heal)
+        save_single(healed, out / "healed.safetensors", dtype={"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[SAVE_DTYPE],
+                    metadata={"kohakumoss_heal": json.dumps({"tau": TAU, "steps": STEPS})})
+        (out / "report.json").write_text(json.dumps({"top": heal.report["top"], "shrunk": heal.report["shrunk"], "final": final, "log": log}, indent=1))
+        print(f"wrote {out / 'healed.safetensors'}; plain rel_sq vs teacher {final['plain']:.3e}")
+        return final
+    return None
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,36 @@
+"""Convert a heal run's `healed.safetensors` into the requested layout (single file with fused q | k | v, or a
+diffusers folder) (role of `scripts/heal/merge.py`)."""
+
+PARTS = "runs/heal/healed.safetensors"
+VARIANT = "base"
+ARCH_OVERRIDES = {}
+OUT = ""
+FORMAT = "single"      # single | diffusers
+FUSED_QKV = False
+SAVE_DTYPE = "bf16"
+
+globals().update(globals().pop("__kmoss_overrides__", {}))
+
+
+def main():
+    import torch
+
+    from kohakumosstrainer_b200.models import build_backbone
+    from kohakumosstrainer_b200.models.build import resolve_arch
+    from kohakumosstrainer_b200.models.io import load_backbone, save_diffusers, save_single
+
+    if not OUT:
+        raise SystemExit("set OUT")
+    model = build_backbone(resolve_arch(VARIANT, ARCH_OVERRIDES), device="cpu", dtype=torch.float32, seed=0, init=False)
+    load_backbone(model, PARTS)
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[SAVE_DTYPE]
+    if FORMAT == "diffusers":
+        save_diffusers(model, OUT, dtype=dtype)
+    else:
+        save_single(model, OUT, dtype=dtype, fused_qkv=bool(FUSED_QKV))
+    print(f"wrote {OUT}")
+    return OUT
+
+
+if __name__ == "__main__":
+    main()

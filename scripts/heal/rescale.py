@@ -1,0 +1,52 @@
+"""Exact uniform rescale of a model's residual stream (writers / C, reader-norm eps / C^2); C="auto" picks the
+power of two that brings the mean block RMS near 1 (role of `scripts/heal/rescale.py`)."""
+
+WEIGHTS = ""
+VARIANT = "base"
+ARCH_OVERRIDES = {}
+C = "auto"
+OUT = ""
+SAVE_DTYPE = "bf16"
+DEVICE = "cpu"
+
+globals().update(globals().pop("__kmoss_overrides__", {}))
+
+
+def main():
+    import math
+
+    import torch
+
+    from kohakumosstrainer_b200.heal import rescale_stream
+    from kohakumosstrainer_b200.models import build_backbone
+    from kohakumosstrainer_b200.models.build import resolve_arch
+    from kohakumosstrainer_b200.models.io import load_backbone, save_single
+    from kohakumosstrainer_b200.types.seqinfo import build_seqinfo
+
+    if not OUT:
+        raise SystemExit("set OUT")
+    arch = resolve_arch(VARIANT, ARCH_OVERRIDES)
+    model = build_backbone(arch, device=DEVICE, dtype=torch.float32, seed=0, init=not WEIGHTS).eval()
+    if WEIGHTS:
+        load_backbone(model, WEIGHTS)
+    c = C
+    if c == "auto":
+        rms = []
+        hooks = [layer.register_forward_hook(lambda m, a, out: rms.append(float(out.float().square().mean().sqrt()))) for layer in model.layers]
+        seq = build_seqinfo(torch.tensor([[16, 16]]), torch.tensor([32])).to(DEVICE)
+        g = torch.Generator().manual_seed(0)
+        with torch.no_grad():
+            model(torch.randn(seq.n_img, arch.latent_channels, generator=g).to(DEVICE), torch.randn(32, arch.text_dim, generator=g).to(DEVICE),
+                  torch.tensor([0.5], device=DEVICE), seq)
+        for h in hooks:
+            h.remove()
+        c = 2.0 ** round(math.log2(max(sum(rms) / len(rms), 1e-12)))
+        print(f"mean block RMS {sum(rms) / len(rms):.3g}: C = {c:g}")
+    rescale_stream(model, float(c))
+    save_single(model, OUT, dtype={"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[SAVE_DTYPE])
+    print(f"wrote {OUT}")
+    return float(c)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,79 @@
+"""Massive-channel heal: calibration finds the planted channel, the shrink is exact at t = 0,
+training brings the plain (lam = 1) student back to the teacher, the uniform rescale is exact."""
+
+import torch
+
+from kohakumosstrainer_b200.data import SyntheticConfig, SyntheticDataset
+from kohakumosstrainer_b200.heal import Heal, HealConfig, merge_student, rescale_stream, writer_params
+from kohakumosstrainer_b200.models import build_backbone
+from kohakumosstrainer_b200.models.build import resolve_arch
+from kohakumosstrainer_b200.types.seqinfo import build_seqinfo
+
+
+def _model(seed=0):
+    arch = resolve_arch("tiny", {"text_dim": 32, "latent_channels": 8})
+    m = build_backbone(arch, device="cpu", dtype=torch.float32, seed=seed)
+    with torch.no_grad():                                 # a stream of O(1) magnitude with one massive channel
+        for name, p in writer_params(m):
+            if p.dim() == 2:
+                p.mul_(20.0)
+                p[7].mul_(40.0)
+    return m
+
+
+def _data():
+    return SyntheticDataset(SyntheticConfig(max_tokens=200, min_area=64 * 64, max_area=96 * 96, size_step=32, min_text=2, max_text=6,
+                                            channels=8, text_dim=32, dtype=torch.float32))
+
+
+def test_calibration_shrink_and_heal():
+    torch.manual_seed(0)
+    heal = Heal(_model(), HealConfig(tau=4.0, steps=30, anneal_steps=20, warmup=2, lr=2e-4, calib_batches=2), _data())
+    assert heal.report["top"][0][0] == 7 and heal.report["shrunk"] >= 1 and float(heal.d[7]) < 0.5
+    start = heal.evaluate()
+    assert start["current"] < 1e-6                        # exact at t = 0 with the channel-weighted norm
+    assert start["plain"] > 10 * max(start["current"], 1e-9)
+    for _ in range(30):
+        out = heal.train_step()
+    assert out["t"] == 1.0 and out["loss"] == out["loss"]
+    end = heal.evaluate()
+    assert end["plain"] < start["plain"]                  # the plain student moved toward the teacher
+    healed = merge_student(heal)
+    peak = float(torch.stack([p.detach().abs().max(1).values for n, p in writer_params(healed) if p.dim() == 2 and "layers" in n]).max(0).values[7])
+    other = float(torch.stack([p.detach().abs().max(1).values for n, p in writer_params(healed) if p.dim() == 2 and "layers" in n]).max(0).values.median())
+    assert peak < 40 * other
+
+
+def test_uniform_rescale_is_exact():
+    m = _model(1).eval()
+    seq = build_seqinfo(torch.tensor([[4, 4], [2, 6]]), torch.tensor([3, 5]))
+    z, t, s = torch.randn(seq.n_img, 8), torch.randn(8, 32), torch.tensor([0.3, 0.7])
+    with torch.no_grad():
+        ref = m(z, t, s, seq)
+        rescale_stream(m, 16.0)
+        out = m(z, t, s, seq)
+    assert (out - ref).abs().max() < 1e-4 * ref.abs().max()
+
+
+def test_heal_scripts(tmp_path):
+    import json
+
+    from kohakumosstrainer_b200.config import run_script
+    from kohakumosstrainer_b200.models.io import save_single
+
+    dense = tmp_path / "dense.safetensors"
+    save_single(_model(2), dense, dtype=torch.float32)
+    over = {"text_dim": 32, "latent_channels": 8}
+    ds = [{"type": "synthetic", "min_area": 4096, "max_area": 9216, "size_step": 32, "min_text": 2, "max_text": 6}]
+    common = [f"WEIGHTS={str(dense)!r}", "VARIANT='tiny'", f"ARCH_OVERRIDES={over!r}", "DEVICE='cpu'"]
+    data = [f"DATASETS={ds!r}", "MAX_TOKENS=200", "SIZE_STEP=32"]
+    run_script("scripts/heal/calibrate.py", None, common + data + ["CALIB_BATCHES=2", f"OUT={str(tmp_path / 'cal.json')!r}"])
+    assert json.load(open(tmp_path / "cal.json"))["top"][0][0] == 7
+    run_script("scripts/heal/heal.py", None, common + data + ["STEPS=4", "ANNEAL_STEPS=3", "WARMUP=1", "CALIB_BATCHES=2", "TAU=4.0", "LOG_EVERY=2",
+                                                              f"OUT={str(tmp_path / 'heal')!r}", "SAVE_DTYPE='fp32'"])
+    assert (tmp_path / "heal" / "healed.safetensors").exists() and "final" in json.load(open(tmp_path / "heal" / "report.json"))
+    run_script("scripts/heal/merge.py", None, [f"PARTS={str(tmp_path / 'heal' / 'healed.safetensors')!r}", "VARIANT='tiny'", f"ARCH_OVERRIDES={over!r}",
+                                               f"OUT={str(tmp_path / 'merged.safetensors')!r}", "FUSED_QKV=True"])
+    run_script("scripts/heal/rescale.py", None, common[:3] + [f"OUT={str(tmp_path / 'rescaled.safetensors')!r}", "SAVE_DTYPE='fp32'"])
+    run_script("scripts/heal/cache.py", None, common + data + ["BATCHES=2", "SIGMAS=(0.5,)", f"OUT={str(tmp_path / 'records')!r}"])
+    assert len(list((tmp_path / "records").glob("*.pt"))) == 2
