@@ -1,0 +1,57 @@
+"""Scaling report from bench lines: reads the JSON lines `bench.py` printed at N = 1, 2, 4, 8 (one file per run or
+one file with several lines) and prints tokens/s, speed-up and weak-scaling efficiency per N as a markdown table
+(role of `scripts/dist/scaling_report.py` in the reference).
+
+    python scripts/dist/scaling_report.py runs/bench_n1.json runs/bench_n2.json ... [--out report.md]
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+
+def load(paths):
+    rows = []
+    for p in paths:
+        with open(p, encoding="utf-8") as f:
+            for line in f:
+                line = line.strip()
+                if line.startswith("{"):
+                    try:
+                        rows.append(json.loads(line))
+                    except json.JSONDecodeError:
+                        pass
+    return sorted((r for r in rows if "value" in r and "n_gpus" in r), key=lambda r: r["n_gpus"])
+
+
+def table(rows) -> str:
+    if not rows:
+        return "no bench lines found"
+    base = rows[0]["value"] / rows[0]["n_gpus"]
+    lines = ["| GPUs | value | unit | ms/step | speed-up | efficiency | e2e | clocks (MHz) | reasons |", "|---|---|---|---|---|---|---|---|---|"]
+    for r in rows:
+        n = r["n_gpus"]
+        eff = r["value"] / (base * n)
+        clocks = r.get("clocks", {})
+        lines.append(f"| {n} | {r['value']:.1f} | {r.get('unit', '')} | {r.get('ms_per_step', 0):.1f} | {r['value'] / rows[0]['value']:.2f}x | {eff:.3f} | "
+                     f"{r.get('e2e', {}).get('value', '-')} | {clocks.get('sm_mhz', '-')} | {','.join(clocks.get('reasons', [])) or '-'} |")
+    return "\n".join(lines)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("files", nargs="+")
+    ap.add_argument("--out", default="")
+    args = ap.parse_args(argv)
+    text = table(load(args.files))
+    print(text)
+    if args.out:
+        with open(args.out, "w", encoding="utf-8") as f:
+            f.write(text + "\n")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
