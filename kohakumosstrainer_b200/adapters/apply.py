@@ -38,7 +38,7 @@ MODIFIERS = {
     "modulation": ([MODULATION], []),
     "embed": ([EMBED_HEAD], [FINAL_NORM]),
 }
-ALGOS = ("lora", "locon", "loha", "lokr", "oft", "ia3", "full", "diff", "dora")
+ALGOS = ("lora", "locon", "loha", "lokr", "oft", "ia3", "full", "diff", "dora", "dylora", "tlora")
 
 
 def resolve_preset(preset: str | dict) -> tuple[list[str], list[str]]:
@@ -94,7 +94,45 @@ def lora_name_of(prefix: str, path: str) -> str:
     return f"{prefix}_{path}".replace(".", "_")
 
 
+def dylora_rank(step: int, seed: int, rank: int, unit: int = 1) -> int:
+    """DyLoRA: the rank trained at `step`, drawn uniformly from {unit, 2 unit, ..., rank} by a counter-based seed."""
+    from ..utils.seeds import seed_of
+
+    choices = max(1, rank // max(1, unit))
+    return max(1, (seed_of("dylora", seed, step) % choices + 1) * max(1, unit))
+
+
+def tlora_rank(sigma: float, rank: int, min_rank: int = 1, alpha_rank: float = 1.0) -> int:
+    """T-LoRA: ranks active at noise level sigma in [0, 1]: high noise trains few ranks, low noise all of them,
+    `r(sigma) = floor((1 - sigma)^alpha_rank * (rank - min_rank)) + min_rank`."""
+    return int((1.0 - min(max(sigma, 0.0), 1.0)) ** alpha_rank * (rank - min_rank)) + min_rank
+
+
 class AdapterSet(nn.Module):
+    def begin_step(self, step: int, sigma=None) -> int | None:
+        """Per-step adapter state (`src/kohakumoss/adapters/train/{steps,tlora}.py` there): DyLoRA draws the trained
+        rank, T-LoRA masks ranks by the batch's mean sigma; other algorithms have none. Returns the active rank."""
+        cfg = self.cfg
+        if cfg.algo not in ("dylora", "tlora"):
+            return None
+        kw = cfg.algo_kwargs or {}
+        if cfg.algo == "dylora":
+            active = dylora_rank(step, cfg.seed, cfg.dim, int(kw.get("unit", 1)))
+        else:
+            s = float(sigma.float().mean()) if sigma is not None else 0.0
+            active = tlora_rank(s, cfg.dim, int(kw.get("min_rank", 1)), float(kw.get("alpha_rank", 1.0)))
+        for mod in self.modules_by_name.values():
+            dev = mod.lora_down.weight.device
+            mask = (torch.arange(mod.rank, device=dev) < active).float()
+            mod.__dict__["rank_mask"] = mask
+            mod.fusable = False        # the masked product runs through the composed path
+        return active
+
+    def end_training(self) -> None:
+        """Drop the step state: inference uses every rank."""
+        for mod in self.modules_by_name.values():
+            mod.__dict__.pop("rank_mask", None)
+
     """The adapters of one backbone: an `nn.ModuleDict` keyed by LyCORIS name, the target
     paths, and (with `train_norms`) the norm weights made trainable."""
 
@@ -182,7 +220,7 @@ def apply(model: nn.Module, cfg: AdapterConfig, freeze_base: bool = True) -> Ada
     if freeze_base:
         for p in model.parameters():
             p.requires_grad_(False)
-    algo = "lora" if cfg.algo == "dora" else cfg.algo
+    algo = "lora" if cfg.algo in ("dora", "dylora", "tlora") else cfg.algo
     cls = MODULES[algo]
     gen_state = torch.random.get_rng_state()
     torch.manual_seed(cfg.seed)
@@ -190,6 +228,9 @@ def apply(model: nn.Module, cfg: AdapterConfig, freeze_base: bool = True) -> Ada
         for path, lin in targets_of(model, names):
             dev = lin.weight_like.device
             kwargs = dict(cfg.algo_kwargs)
+            if cfg.algo in ("dylora", "tlora"):       # their options are step state of the set, not module arguments
+                for key in ("unit", "min_rank", "alpha_rank"):
+                    kwargs.pop(key, None)
             mod: AdapterModule = cls(
                 lin.in_features, lin.out_features, cfg.dim, cfg.alpha, multiplier=cfg.multiplier,
                 dropout=cfg.dropout, rank_dropout=cfg.rank_dropout, module_dropout=cfg.module_dropout, **kwargs,

@@ -145,6 +145,9 @@ class LoRAModule(AdapterModule):
             h = F.dropout(h, self.dropout)
         t = F.linear(h, self.lora_down.weight.to(x.dtype))
         scale = self.scale
+        mask = self.__dict__.get("rank_mask")
+        if mask is not None:                      # DyLoRA / T-LoRA step state: only the leading ranks are active
+            t = t * mask.to(t.dtype)
         if self.training and self.rank_dropout > 0:
             keep = (torch.rand(self.rank, device=x.device) > self.rank_dropout).to(t.dtype)
             t = t * keep

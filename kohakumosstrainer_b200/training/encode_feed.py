@@ -1,0 +1,113 @@
+"""Encode feed: the text encoder and the VAE run in their own processes (on their own GPUs when
+`ENCODE_DEVICES` names some) and hand encoded batches to the trainer rank through a bounded queue,
+so a training step never waits for an encoder and the encoders never share the trainer's memory.
+
+Worker w of W serves batch indices `start + w, start + w + W, ...` of ONE trainer rank: it
+materialises the batch (`dataset.materialize`), encodes what the caches did not hold
+(`data.dataset.encode_missing` with encoders built in the worker from dotted factory paths), writes
+online caches back, and ships the finished `HostBatch` (CPU tensors, shared memory). The consumer
+re-orders by index. `ENCODE_DEPTH` bounds the batches in flight per worker. Role of the reference's
+`training/encode/{feed,service,streamed}.py`.
+"""
+
+from __future__ import annotations
+
+import multiprocessing as mp
+import queue
+
+import torch
+
+
+def _serve(dataset, factories, device, rank, world, start, worker, workers, out, stop):
+    try:
+        from ..data.dataset import encode_missing
+
+        torch.set_num_threads(2)
+        image_enc = _build(*factories["image"], device=device) if factories.get("image") else None
+        text_enc = _build(*factories["text"], device=device) if factories.get("text") else None
+        index = start + worker
+        while not stop.is_set():
+            hb = dataset.materialize(index, rank, world)
+            if not hb.encoded:
+                hb = encode_missing(hb, dataset, image_enc, text_enc)
+            item = (index, hb, None)
+            while not stop.is_set():
+                try:
+                    out.put(item, timeout=0.2)
+                    break
+                except queue.Full:
+                    continue
+            index += workers
+    except BaseException as exc:  # the consumer re-raises
+        try:
+            out.put((-1, None, f"{type(exc).__name__}: {exc}"), timeout=5)
+        except Exception:
+            pass
+
+
+def _build(path, kwargs, device=None):
+    from ..data.scripting import build_encoder
+
+    kw = dict(kwargs)
+    if device is not None and "device" in kw:
+        kw["device"] = device
+    return build_encoder(path, kw)
+
+
+class EncodeFeed:
+    def __init__(self, dataset, image_encoder: tuple | None = None, text_encoder: tuple | None = None, devices=(), depth: int = 4,
+                 rank: int = 0, world: int = 1, start: int = 0):
+        """`image_encoder` / `text_encoder`: `(dotted factory path, kwargs)`; `devices`: one worker per entry
+        (e.g. `("cuda:6", "cuda:7")`), or a single CPU worker when empty."""
+        self.dataset, self.rank, self.world, self.start = dataset, rank, world, start
+        self.factories = {"image": image_encoder, "text": text_encoder}
+        self.devices = list(devices) or ["cpu"]
+        self.depth = max(1, depth)
+        self.ctx = mp.get_context("spawn")
+        self.stop = self.ctx.Event()
+        self.queues = [self.ctx.Queue(self.depth) for _ in self.devices]
+        self.procs = []
+        self.next_index = start
+
+    def __enter__(self):
+        n = len(self.devices)
+        for w, dev in enumerate(self.devices):
+            p = self.ctx.Process(target=_serve, daemon=True,
+                                 args=(self.dataset, self.factories, dev, self.rank, self.world, self.start, w, n, self.queues[w], self.stop))
+            p.start()
+            self.procs.append(p)
+        return self
+
+    def get(self, timeout: float = 600.0):
+        """The next batch in index order."""
+        w = (self.next_index - self.start) % len(self.devices)
+        waited = 0.0
+        while True:
+            try:
+                index, hb, err = self.queues[w].get(timeout=1.0)
+                break
+            except queue.Empty:
+                waited += 1.0
+                if not self.procs[w].is_alive():
+                    raise RuntimeError(f"encode worker {w} ({self.devices[w]}) died before batch {self.next_index}")
+                if waited >= timeout:
+                    raise TimeoutError(f"no encoded batch {self.next_index} after {timeout:.0f}s")
+        if err is not None:
+            raise RuntimeError(f"encode worker {w} ({self.devices[w]}) failed: {err}")
+        assert index == self.next_index, (index, self.next_index)
+        self.next_index += 1
+        return hb
+
+    def __exit__(self, *exc):
+        self.stop.set()
+        for q in self.queues:
+            try:
+                while True:
+                    q.get_nowait()
+            except Exception:
+                pass
+        for p in self.procs:
+            p.join(timeout=5)
+            if p.is_alive():
+                p.terminate()
+        return False

@@ -132,9 +132,24 @@ class _Encoded:
             self._text = QwenTextEncoder(self.k["TEXT_ENCODER"], device=self.k["TEXT_DEVICE"] or "cuda")
         return self._text.encode(prompts)
 
+    def start_feed(self, start: int, rank: int, world: int) -> None:
+        """`ENCODE_DEVICES`: encoders run in their own processes on those devices and feed this rank in index order."""
+        from .encode_feed import EncodeFeed
+
+        devices = [f"cuda:{d}" if isinstance(d, int) else str(d) for d in self.k["ENCODE_DEVICES"]]
+        image = ("kohakumosstrainer_b200.encoders.vae_encoder", {"path": self.k["VAE"], "device": "cuda"}) if self.k["VAE"] else None
+        text = ("kohakumosstrainer_b200.encoders.text_encoder", {"path": self.k["TEXT_ENCODER"], "device": "cuda"}) if self.k["TEXT_ENCODER"] else None
+        self._feed = EncodeFeed(self.dataset, image, text, devices, int(self.k["ENCODE_DEPTH"]), rank, world, start).__enter__()
+        self._feed_next = start
+
     def materialize(self, index: int, rank: int = 0, world: int = 1, pin: bool = True):
         from ..data.dataset import encode_missing
 
+        feed = self.__dict__.get("_feed")
+        if feed is not None and index == self._feed_next:
+            self._feed_next += 1
+            hb = feed.get()
+            return hb.pin_memory() if pin else hb
         hb = self.dataset.materialize(index, rank, world)
         if not hb.encoded:
             hb = encode_missing(hb, self.dataset, self._images, self._prompts)
@@ -198,6 +213,8 @@ def worker(k: dict, rank: int, world: int, device) -> dict:
     last = {}
     if grid is not None and grid.due(0) and start == 0:
         grid.run(0)
+    if k["ENCODE_DEVICES"] and hasattr(data, "start_feed"):
+        data.start_feed(start * cfg.grad_acc, rank, world)
     nxt = [data.materialize(start * acc + i, rank, world) for i in range(acc)]
     for step in range(start, cfg.steps):
         trace.before(step)

@@ -64,6 +64,7 @@ class TrainStep:
         self.noise_gen = torch.Generator(self.device).manual_seed(seed_of("noise", seed, rank))
         self.step_index = 0
         # optional extras (`training.extras`): stream penalties, teacher distillation, gradient probe
+        self.adapters = None            # an `AdapterSet` with per-step state (DyLoRA, T-LoRA)
         self.penalty = None
         self.teacher = None
         self.distill_weight, self.hard_weight = 0.0, 1.0
@@ -86,6 +87,8 @@ class TrainStep:
         eps = torch.randn(z0.shape, generator=self.noise_gen, device=self.device, dtype=torch.float32)
         z, target = noise_latents(z0, eps, sigma, seq.seg_img)
         zc, tc = z.to(self.compute_dtype), batch.text.to(self.compute_dtype)
+        if self.adapters is not None:
+            self.adapters.begin_step(self.step_index, sigma)
         if self.penalty is not None:
             with self.penalty.collecting():
                 v = self.model(zc, tc, sigma, seq)

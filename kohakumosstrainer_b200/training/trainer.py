@@ -160,6 +160,8 @@ class Trainer:
         self.normalizer = TokenNormalizer(reduce_tokens, 1)
         self.step_fn = TrainStep(self.model, self.device, cfg.timestep, cfg.timestep_kwargs, cfg.loss, None,
                                  cfg.weighting, cfg.seed, rank, dtype)
+        if self.adapters is not None and cfg.algo in ("dylora", "tlora"):
+            self.step_fn.adapters = self.adapters
         if cfg.extras:
             from . import extras as ex
 

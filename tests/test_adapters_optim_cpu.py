@@ -214,3 +214,25 @@ def test_export_scripts_roundtrip(tmp_path):
     assert folded.__dict__["stream_scale"] == 4.0
     run_script("scripts/export/text_quant.py", None, [f"WEIGHTS={str(dense)!r}", f"OUT={str(tmp_path / 'tq.safetensors')!r}", "LAYERS='.*proj\\\\.(q|k|v|o)'", "MIN_FEATURES=16"])
     assert any(k.endswith(".comfy_quant") for k in load_file(tmp_path / "tq.safetensors"))
+
+
+def test_dylora_and_tlora_step_state():
+    from kohakumosstrainer_b200.adapters.apply import dylora_rank, tlora_rank
+    from kohakumosstrainer_b200.data import SyntheticConfig, SyntheticDataset
+    from kohakumosstrainer_b200.training.trainer import Trainer, TrainerConfig
+
+    assert {dylora_rank(s, 0, 8, 2) for s in range(64)} == {2, 4, 6, 8} and dylora_rank(5, 0, 8) == dylora_rank(5, 0, 8)
+    assert tlora_rank(1.0, 16, 2) == 2 and tlora_rank(0.0, 16, 2) == 16 and tlora_rank(0.5, 16, 2) == 9
+    ds = SyntheticDataset(SyntheticConfig(max_tokens=300, min_area=96 * 96, max_area=128 * 128, size_step=32, min_text=2, max_text=8,
+                                          channels=8, text_dim=32, dtype=torch.float32))
+    for algo, kw in (("dylora", {"unit": 2}), ("tlora", {"min_rank": 1})):
+        tr = Trainer(TrainerConfig(variant="tiny", arch_overrides={"text_dim": 32, "latent_channels": 8}, precision="fp32", algo=algo, dim=8, alpha=8.0,
+                                   algo_kwargs=kw, steps=4, base_precision="auto"), device="cpu")
+        seen = set()
+        for i in range(3):
+            out = tr.train_step(ds.materialize(i, 0, 1))
+            assert out["ok"]
+            seen.add(int(next(iter(tr.adapters.modules_by_name.values())).__dict__["rank_mask"].sum()))
+        assert all(1 <= r <= 8 for r in seen)
+        tr.adapters.end_training()
+        assert "rank_mask" not in next(iter(tr.adapters.modules_by_name.values())).__dict__

@@ -393,3 +393,18 @@ def test_data_scripts(tree, tmp_path):
     rec.write_text(json.dumps({"image": "a.png", "gbc": {"short": "s"}}) + "\n" + json.dumps({"image": "b.png", "gbc": {"short": "t"}}) + "\n")
     run_script("scripts/data/image_index.py", None, [f"RECORDS={str(rec)!r}"])
     assert set(json.load(open(str(rec) + ".index.json"))) == {"a.png", "b.png"}
+
+
+def test_encode_feed_processes(tree, tmp_path):
+    """Encoders in their own process hand finished batches to the consumer in index order."""
+    from kohakumosstrainer_b200.training.encode_feed import EncodeFeed
+
+    cfg = _cfg(tree, latent_cache="online", text_cache="online", cache_dir=str(tmp_path / "cache"), text_drop=0.0, latent_encoder_id="synthetic-image",
+               text_encoder_id="synthetic-text")
+    ds = MossDataset(cfg, rank=0)
+    feed = EncodeFeed(ds, ("kohakumosstrainer_b200.encoders.synthetic_image_encoder", {"channels": 8}),
+                      ("kohakumosstrainer_b200.encoders.synthetic_text_encoder", {"dim": 16}), devices=(), depth=2)
+    with feed:
+        got = [feed.get(timeout=120) for _ in range(3)]
+    assert [b.index for b in got] == [0, 1, 2] and all(b.encoded and b.latents.shape[1] == 8 and b.text.shape[1] == 16 for b in got)
+    assert os.path.exists(tmp_path / "cache" / "latents.r0.kmts")      # the worker wrote the online cache back
