@@ -128,9 +128,10 @@ class _LinearCore:
             if fp8:
                 sb = wp.scale[:1] if wp.per_tensor else None
                 if lp is not None:
-                    # keep the bypass out of the fp8 rescale: divide it by s_d (* s_w)
-                    tb = native.gemm(d, lp.up, b_mn=True, col_scale=lp.plain_scale, scale_a=ds[1:2],
-                                     scale_b=None if sb is None else wp.scale[1:2])
+                    # keep the bypass out of the fp8 rescale: divide it by s_d (* s_w). t2 already holds (d up) * s,
+                    # so this is an element-wise pass over [M, R] instead of another product over the wide d
+                    inv = ds[1:2] if sb is None else ds[1:2] * wp.scale[1:2]
+                    tb = (t2.float() * inv).to(BF16)
                 dx = native.gemm(dq, wp.w, b_mn=True, scale_a=ds[:1], scale_b=sb, t=tb, u=ub)
             elif wp.fsdp is not None:
                 full, gather = wp.fsdp.gather_args()  # resharded after forward: gather again, fused into dgrad

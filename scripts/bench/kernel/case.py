@@ -8,7 +8,7 @@ hundred MB (so a multi-pass capture stays short). Prints one JSON line: device t
 around each launch, L2 flushed between launches, median), algorithmic FLOPs and bytes, and the
 fractions of the measured peaks (`MEASURED_PEAKS.json` when present).
 
-Cases: gemm_bf16, gemm_fp8, gemm_fp8_dgrad, gemm_wgrad, gemm_situ, gemm_qkrope, attn_fwd,
+Cases: gemm_bf16, gemm_fp8, gemm_fp8_dgrad, gemm_wgrad, gemm_situ, gemm_qkrope, gemm_fp8_situ, gemm_fp8_qkrope, gemm_fp8_residual, attn_fwd,
 attn_bwd, rms_norm_mod, rms_norm_mod_bwd, situ, quant_fp8, token_mse, adamw.
 """
 
@@ -75,6 +75,37 @@ def build(op: str, tokens: int):
         dy = bf16(M, N)
         dw = torch.empty(N, K, device="cuda", dtype=torch.float32)
         return (lambda: native.gemm(dy, x, a_mn=True, b_mn=True, out=dw)), flops, 2 * (M * N + M * K) + 4 * N * K
+    if op in ("gemm_fp8_situ", "gemm_fp8_qkrope", "gemm_fp8_residual"):
+        from kohakumosstrainer_b200.models.components import default_bands
+
+        if op == "gemm_fp8_situ":
+            N, K, rows_b = F, D, 2 * F
+        elif op == "gemm_fp8_qkrope":
+            N, K, rows_b = 3 * D, D, 3 * D
+        else:
+            N, K, rows_b = D, F, D
+        x, w = bf16(M, K), bf16(rows_b, K, scale=0.02)
+        xq, xs = native.quantize_fp8(x)
+        wq, ws = native.quantize_fp8(w)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        flops = 2.0 * M * rows_b * K
+        nbytes = M * K + rows_b * K + 2 * M * N
+        if op == "gemm_fp8_situ":
+            aux = torch.empty(M, 2 * F, device="cuda", dtype=torch.bfloat16)
+            return (lambda: native.gemm(xq, wq, out=out, scale_a=xs[:1], scale_b=ws[:1], epilogue=native.EPI_SITU, aux=aux)), flops, nbytes + 4 * M * F
+        if op == "gemm_fp8_qkrope":
+            pos = torch.zeros(M, 4, device="cuda")
+            pos[:, 1] = torch.arange(M, device="cuda") % 1024
+            table = native.rope_table(pos, default_bands(16, 10000.0, "cuda"))
+            qn, kn = torch.ones(128, device="cuda").bfloat16(), torch.ones(128, device="cuda").bfloat16()
+            rstd = torch.empty(M, 2 * D // 128, device="cuda")
+            call = lambda: native.gemm(xq, wq, out=out, scale_a=xs[:1], scale_b=ws[:1], epilogue=native.EPI_QK_ROPE, q_norm_w=qn, k_norm_w=kn,  # noqa: E731
+                                       rope=table, rope_cols=2 * D, head_rstd=rstd)
+            return call, flops, nbytes
+        res = bf16(M, N)
+        seg = (torch.arange(M, device="cuda") // 4096).int()
+        gate = torch.randn(int(seg.max()) + 1, N, device="cuda")
+        return (lambda: native.gemm(xq, wq, out=out, scale_a=xs[:1], scale_b=ws[:1], res=res, gate=gate, seg=seg)), flops, nbytes + 2 * M * N
     if op == "gemm_situ":
         x, w = bf16(M, D), bf16(2 * F, D, scale=0.02)
         out = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
@@ -87,7 +118,7 @@ def build(op: str, tokens: int):
         pos = torch.zeros(M, 4, device="cuda")
         pos[:, 1] = torch.arange(M, device="cuda") % 1024
         table = native.rope_table(pos, default_bands(16, 10000.0, "cuda"))
-        qn, kn = torch.ones(128, device="cuda"), torch.ones(128, device="cuda")
+        qn, kn = torch.ones(128, device="cuda").bfloat16(), torch.ones(128, device="cuda").bfloat16()
         call = lambda: native.gemm(x, w, out=out, epilogue=native.EPI_QK_ROPE, q_norm_w=qn, k_norm_w=kn, rope=table, rope_cols=2 * D)  # noqa: E731
         return call, 2.0 * M * 3 * D * D, 2 * (M * D + 3 * D * D + 3 * M * D)
     if op in ("attn_fwd", "attn_bwd"):
