@@ -94,9 +94,45 @@ class StepTrace:
             out = self.run_dir / "ranks"
             out.mkdir(parents=True, exist_ok=True)
             self.prof.export_chrome_trace(str(out / f"trace.rank{self.rank}.json.gz"))
+            write_trace_summary(self.prof, out / f"trace_summary.rank{self.rank}.json", self.trace[1] - self.trace[0])
             self.prof = None
         if self.profile and step + 1 == self.profile[1] and torch.cuda.is_available():
             torch.cuda.cudart().cudaProfilerStop()
+
+
+def trace_summary(prof, steps: int = 1, top: int = 40) -> dict:
+    """Per-step device milliseconds of a profiled window: per phase (`kohakumoss.*` ranges), per class of work
+    (our kernels, library GEMMs, NCCL, copies, other) and the top kernels (what the reference's telemetry report lists)."""
+    steps = max(1, steps)
+    events = prof.key_averages()
+    kernels = [(e.key, e.device_time_total / 1e3, e.count) for e in events if e.device_time_total > 0 and str(getattr(e, "device_type", "")).endswith("CUDA")]
+    phases = {e.key.split(".", 1)[1]: round(e.device_time_total / 1e3 / steps, 3) for e in events if e.key.startswith("kohakumoss.")}
+    groups = {"ours": 0.0, "nccl": 0.0, "copy": 0.0, "library_gemm": 0.0, "other": 0.0}
+    for key, ms, _ in kernels:
+        low = key.lower()
+        if "kmoss" in low:
+            groups["ours"] += ms
+        elif "nccl" in low:
+            groups["nccl"] += ms
+        elif "memcpy" in low or "memset" in low:
+            groups["copy"] += ms
+        elif "gemm" in low or "cutlass" in low or "cublas" in low:
+            groups["library_gemm"] += ms
+        else:
+            groups["other"] += ms
+    total = sum(groups.values())
+    return {"steps": steps, "device_ms_per_step": round(total / steps, 3), "by_class_ms": {k: round(v / steps, 3) for k, v in groups.items()},
+            "phases_ms": phases, "top_kernels": [{"name": k[:120], "ms": round(ms / steps, 3), "launches": int(c / steps)}
+                                                 for k, ms, c in sorted(kernels, key=lambda r: -r[1])[:top]]}
+
+
+def write_trace_summary(prof, path, steps: int = 1) -> None:
+    import json
+
+    try:
+        Path(path).write_text(json.dumps(trace_summary(prof, steps), indent=1))
+    except Exception as exc:  # a summary must never break a training run
+        Path(path).write_text(json.dumps({"error": f"{type(exc).__name__}: {exc}"}))
 
 
 def vram_row(device) -> dict:

@@ -18,6 +18,7 @@ from ..data.types import HostBatch
 from ..diffusion import TokenNormalizer
 from ..models import build_backbone
 from ..models.build import resolve_arch
+from ..logging.phases import phase
 from ..models.runners import build_runner
 from ..optim import Bundle, ConstantEMA, build_optimizer
 from ..quant import apply_base_precision
@@ -192,7 +193,8 @@ class Trainer:
         denom = self.normalizer.denominator(count, self.device)
         n = len(host_batches)
         for i, hb in enumerate(host_batches):
-            batch = self.batcher(hb)
+            with phase("data"):
+                batch = self.batcher(hb)
             nxt = host_batches[i + 1] if i + 1 < n else next_batch
             if nxt is not None:
                 self.batcher.prefetch(nxt)
@@ -202,10 +204,13 @@ class Trainer:
                 if i == 0:
                     self._begin_fsdp_step()
                 self.fsdp.start(last=i == n - 1)
-            loss = self.step_fn(batch, denom)
-            loss.backward()
+            with phase("forward"):
+                loss = self.step_fn(batch, denom)
+            with phase("backward"):
+                loss.backward()
             self.bundle.observe(loss)
-        ok = self.bundle.step()
+        with phase("optimizer"):
+            ok = self.bundle.step()
         self.step_fn.step_index += 1
         self.tokens_seen += count
         self.samples_seen += sum(hb.samples for hb in host_batches)
