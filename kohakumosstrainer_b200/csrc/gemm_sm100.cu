@@ -665,7 +665,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 tmem_ld_32x32(t_head + 64 + c * 32, rb);
                 tmem_ld_wait();
                 float va[32], vb[32];
-                const float* cs = p.rope + (size_t)(row_ok ? m : 0) * 128 + c * 32;
+                // this row's cos | sin and the norm gains come in 16-byte loads: a thread owns a whole table row, so
+                // 4-byte loads would cost four times the cache requests for the same sectors
+                const float4* cs4 = reinterpret_cast<const float4*>(p.rope + (size_t)(row_ok ? m : 0) * 128 + c * 32);
+                float co[32], si[32], wa[32], wb[32];
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4) {
+                  const float4 c4 = __ldg(cs4 + q4), s4 = __ldg(cs4 + 16 + q4);
+                  co[4 * q4] = c4.x; co[4 * q4 + 1] = c4.y; co[4 * q4 + 2] = c4.z; co[4 * q4 + 3] = c4.w;
+                  si[4 * q4] = s4.x; si[4 * q4 + 1] = s4.y; si[4 * q4 + 2] = s4.z; si[4 * q4 + 3] = s4.w;
+                }
+#pragma unroll
+                for (int q8 = 0; q8 < 4; ++q8) {
+                  const uint4 ua = __ldg(reinterpret_cast<const uint4*>(w + c * 32) + q8);
+                  const uint4 ub = __ldg(reinterpret_cast<const uint4*>(w + 64 + c * 32) + q8);
+                  const uint32_t pa[4] = {ua.x, ua.y, ua.z, ua.w}, pb[4] = {ub.x, ub.y, ub.z, ub.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 fa = unpack_bf16(pa[e]), fb = unpack_bf16(pb[e]);
+                    wa[8 * q8 + 2 * e] = fa.x; wa[8 * q8 + 2 * e + 1] = fa.y;
+                    wb[8 * q8 + 2 * e] = fb.x; wb[8 * q8 + 2 * e + 1] = fb.y;
+                  }
+                }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                   const int ja = c * 32 + j, jb = 64 + ja;
@@ -674,11 +695,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                     sa *= __ldg(p.col_scale + n_head + ja);
                     sb *= __ldg(p.col_scale + n_head + jb);
                   }
-                  const float a = __uint_as_float(ra[j]) * sa * __bfloat162float(__ldg(w + ja));
-                  const float b = __uint_as_float(rb[j]) * sb * __bfloat162float(__ldg(w + jb));
-                  const float co = cs[j], si = cs[64 + j];
-                  va[j] = a * co - b * si;
-                  vb[j] = b * co + a * si;
+                  const float a = __uint_as_float(ra[j]) * sa * wa[j];
+                  const float b = __uint_as_float(rb[j]) * sb * wb[j];
+                  va[j] = a * co[j] - b * si[j];
+                  vb[j] = b * co[j] + a * si[j];
                 }
                 slab_put(0, c, va);
                 slab_put(1, c, vb);

@@ -128,3 +128,15 @@ def relative_cost(plan: MemoryPlan) -> float:
     if plan.grad_offload:
         cost *= 1.05
     return cost
+
+
+def estimate_inference(arch: MossArchConfig, tokens: int, base_precision: str = "compute", compute_bytes: int = 2, cfg_packed: bool = True) -> dict:
+    """Device memory of sampling: weights in their stored precision, one block's activations for the packed
+    cond + uncond token count, the text / latent buffers and the workspace."""
+    wbytes = PRECISION_BYTES.get(base_precision) or compute_bytes
+    per_block = arch.block_params()
+    weights = arch.depth * per_block * wbytes + (arch.n_params() - arch.depth * per_block) * compute_bytes
+    n = tokens * (2 if cfg_packed else 1)
+    acts = n * (2 * arch.dim * 6 + 2 * 2 * arch.ffn_dim) + n * arch.heads * 4
+    total = (weights + acts + WORKSPACE_BYTES) * FRAGMENTATION + CONTEXT_BYTES
+    return {"weights": int(weights), "activations": int(acts), "total": int(total)}

@@ -40,12 +40,18 @@ def candidates(pinned: dict) -> list[MemoryPlan]:
     return out
 
 
-def plan_auto(work: Workload, total_bytes: int, pinned: dict | None = None, margin: float = 0.92, force: bool = False) -> tuple[MemoryPlan, dict]:
-    """-> (plan, report). `force` returns the smallest plan even when nothing fits."""
+def plan_auto(work: Workload, total_bytes: int, pinned: dict | None = None, margin: float = 0.92, force: bool = False,
+              host_bytes: int | None = None) -> tuple[MemoryPlan, dict]:
+    """-> (plan, report). `force` returns the smallest plan even when nothing fits. `host_bytes` (default: the
+    cgroup-aware room of this host) bounds what a plan may park in host memory."""
+    if host_bytes is None:
+        from ..utils.hostmem import host_room
+
+        host_bytes = host_room()
     pool = candidates(dict(pinned or {}))
     scored = sorted(pool, key=lambda p: (relative_cost(p), estimate(work, p)["total"]))
     for plan in scored:
-        if fits(work, plan, total_bytes, margin):
+        if fits(work, plan, total_bytes, margin) and estimate(work, plan)["host"] <= host_bytes:
             est = estimate(work, plan)
             return replace(plan, profile=f"auto:{plan.profile}"), {"estimate": est, "device_bytes": total_bytes, "considered": len(pool),
                                                                   "relative_cost": relative_cost(plan)}
