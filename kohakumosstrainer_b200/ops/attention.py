@@ -80,6 +80,38 @@ class AttentionFn(torch.autograd.Function):
         return dq, dk, dv, None, None, None
 
 
+class AttentionQkvFn(torch.autograd.Function):
+    """Attention on the fused projection output `qkv` [N, 3, H, 128]: forward reads q / k / v as strided views,
+    backward lets the dQ and dK/dV kernels write straight into one `d qkv` buffer (no concatenation of three
+    gradients afterwards)."""
+
+    @staticmethod
+    def forward(ctx, qkv, tiles, scale):
+        ops = native.load()
+        q, k, v = qkv.unbind(1)
+        o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        lse = torch.empty(q.shape[1], q.shape[0], dtype=torch.float32, device=q.device)
+        ops.attention_fwd(q, k, v, tiles, scale, o, lse)
+        ctx.save_for_backward(qkv, o, lse, tiles)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        ops = native.load()
+        qkv, o, lse, tiles = ctx.saved_tensors
+        q, k, v = qkv.unbind(1)
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = dqkv.unbind(1)
+        ops.attention_bwd(_dense(do), q, k, v, o, lse, tiles, ctx.scale, dq, dk, dv)
+        return dqkv, None, None
+
+
+def attention_qkv(qkv: Tensor, lengths, scale: float) -> Tensor:
+    """`qkv` [N, 3, H, 128] bf16 (contiguous) -> o [N, H, 128]."""
+    return AttentionQkvFn.apply(qkv, _tiles_for(tuple(lengths), qkv.device), float(scale))
+
+
 def _dense(t: Tensor) -> Tensor:
     """[N, H, Dh] with unit inner stride and Dh-contiguous heads (views of a fused qkv
     projection qualify: row stride 3*H*Dh)."""

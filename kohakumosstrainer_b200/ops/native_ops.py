@@ -648,6 +648,19 @@ class NativeOps(OpSet):
         if self.pins.get("attention_varlen") == "eager":
             self.attention_varlen = eager.attention_varlen
 
+    def attention(self, q, k, v, plan):
+        """q / k / v that are the three slices of one fused projection output take the fused path: the backward kernels
+        then write one `d qkv` buffer in place."""
+        fused = getattr(q, "_kmoss_fused", None)
+        if (fused is not None and fused.is_cuda and fused.dtype == BF16 and fused.is_contiguous() and plan.lengths is not None
+                and k.data_ptr() == fused.data_ptr() + fused.stride(1) * 2 and v.data_ptr() == fused.data_ptr() + 2 * fused.stride(1) * 2
+                and self.pins.get("attention_varlen") != "eager"):
+            from .attention import _native_ready, attention_qkv
+
+            if _native_ready():
+                return attention_qkv(fused, plan.lengths, q.shape[-1] ** -0.5)
+        return OpSet.attention(self, q, k, v, plan)
+
     # -- layer-level fused ops -----------------------------------------------------------
     def qkv_rope(self, y, lin_q, lin_k, lin_v, heads, q_weight, k_weight, pos, bands, eps):
         lins = [lin_q, lin_k, lin_v]
@@ -671,7 +684,9 @@ class NativeOps(OpSet):
             q, k = self.qk_norm_rope(q, k, q_weight, k_weight, pos, bands, eps)
             return q, k, v
         out = FusedLinearFn.apply(cfg, y.contiguous(), None, None, None, down, up, *weights)
-        q, k, v = out.unflatten(1, (3, heads, 128)).unbind(1)
+        fused = out.unflatten(1, (3, heads, 128))
+        q, k, v = fused.unbind(1)
+        q._kmoss_fused = fused      # `attention` below runs on the fused tensor: one gradient buffer for q | k | v
         return q, k, v
 
     def linear_situ(self, y, lin):
