@@ -538,12 +538,15 @@ class FusedLinearFn(torch.autograd.Function):
         elif mode == "qkrope":
             rc = cfg["rope_cols"]
             heads = rc // 256
-            d = torch.empty_like(dout)
+            # each (row, head) is read and written by one warp, so the kernel may run in place; the v columns then need
+            # no copy. `dout` is this node's own gradient buffer when the fused attention path produced it.
+            inplace = dout._base is None and not dout.requires_grad
+            d = dout if inplace else torch.empty_like(dout)
             for i, w in enumerate((cfg["q_norm_w"], cfg["k_norm_w"])):
                 sl = slice(i * rc // 2, (i + 1) * rc // 2)
                 ops.qk_norm_rope_bwd(out[:, sl], dout[:, sl], w, cfg["table"], head_rstd[:, i * heads : (i + 1) * heads],
                                      d[:, sl], None, heads)
-            if dout.shape[1] > rc:
+            if dout.shape[1] > rc and not inplace:
                 d[:, rc:] = dout[:, rc:]
         else:
             d = dout
