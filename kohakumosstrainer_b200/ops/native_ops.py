@@ -540,7 +540,7 @@ class FusedLinearFn(torch.autograd.Function):
             heads = rc // 256
             # each (row, head) is read and written by one warp, so the kernel may run in place; the v columns then need
             # no copy. `dout` is this node's own gradient buffer when the fused attention path produced it.
-            inplace = dout._base is None and not dout.requires_grad
+            inplace = (dout._base is None or dout._base.numel() == dout.numel()) and not dout.requires_grad
             d = dout if inplace else torch.empty_like(dout)
             for i, w in enumerate((cfg["q_norm_w"], cfg["k_norm_w"])):
                 sl = slice(i * rc // 2, (i + 1) * rc // 2)
