@@ -38,7 +38,7 @@ MODIFIERS = {
     "modulation": ([MODULATION], []),
     "embed": ([EMBED_HEAD], [FINAL_NORM]),
 }
-ALGOS = ("lora", "locon", "loha", "lokr", "oft", "ia3", "full", "diff", "dora", "dylora", "tlora")
+ALGOS = ("lora", "locon", "loha", "lokr", "oft", "boft", "glora", "ia3", "full", "diff", "dora", "dylora", "tlora")
 
 
 def resolve_preset(preset: str | dict) -> tuple[list[str], list[str]]:

@@ -76,7 +76,7 @@ def comfy_state(aset, model) -> dict[str, Tensor]:
             dim = 1 if mod.dora_on_output else 0
             sd["dora_scale"] = (mod.dora_scale.detach().cpu().float() * w.norm(dim=dim, keepdim=True) /
                                 merged.norm(dim=dim, keepdim=True).clamp_min(1e-12)).to(mod.dora_scale.dtype)
-        if mod.algo == "oft" and getattr(mod, "rescale", None) is not None:
+        if mod.algo in ("oft", "boft") and getattr(mod, "rescale", None) is not None:
             w = lin.base_weight(torch.float32).cpu()
             sd = {"diff": (mod.merged(w.to(mod.oft_blocks.device)).cpu().float() - w)}
         for k, v in sd.items():
@@ -116,8 +116,10 @@ def load_adapter_file(path: str | Path) -> tuple[dict[str, Tensor], dict]:
 
 def detect_algo(state: dict[str, Tensor]) -> str:
     keys = " ".join(state)
-    for marker, algo in (("hada_w1_a", "loha"), ("lokr_w", "lokr"), ("oft_blocks", "oft"), ("lora_down", "lora"), (".diff", "full"), ("on_input", "ia3")):
+    for marker, algo in (("hada_w1_a", "loha"), ("lokr_w", "lokr"), ("oft_blocks", "oft"), (".a1.weight", "glora"), ("lora_down", "lora"), (".diff", "full"), ("on_input", "ia3")):
         if marker in keys:
+            if algo == "oft" and any(k.endswith("oft_blocks") and v.ndim == 4 for k, v in state.items()):
+                return "boft"
             return algo
     raise ValueError("cannot tell the adapter algorithm from the file's tensor names")
 

@@ -290,6 +290,111 @@ class OFTModule(AdapterModule):
         return out if bias is None else out + bias
 
 
+class BOFTModule(OFTModule):
+    """Butterfly OFT: `m` sparse orthogonal factors, each block-diagonal after a stride
+    permutation of the output rows (stage i pairs rows 2^i * b/2 apart), so that
+    m = log2(n_blocks) + 1 stages of b x b blocks reach every row pair. Stored as
+    `oft_blocks [m, n_blocks, b, b]` (`src/kohakumoss/adapters/kinds/rotation.py:48-58`)."""
+
+    algo = "boft"
+
+    def __init__(self, in_features, out_features, rank, alpha=0.0, rescaled: bool = False, **kw):
+        block = max(2, rank - rank % 2)
+        while out_features % block or block % 2:
+            block -= 2
+            if block < 2:
+                raise ValueError(f"BOFT needs an even block size dividing {out_features}")
+        n = out_features // block
+        AdapterModule.__init__(self, in_features, out_features, block, alpha, **kw)
+        self.block_size, self.n_blocks = block, n
+        self.stages = bin(n - 1).count("1") + 1 if n > 1 else 1
+        while self.stages > 1 and out_features % (2 ** (self.stages - 1) * block):
+            self.stages -= 1
+        self.constraint = float(alpha) * out_features
+        self.oft_blocks = nn.Parameter(torch.zeros(self.stages, n, block, block))
+        self.rescale = nn.Parameter(torch.ones(out_features, 1)) if rescaled else None
+
+    def rotation(self, multiplier: float = 1.0) -> Tensor:
+        b = self.oft_blocks.float()
+        q = b - b.transpose(-1, -2)
+        if self.constraint > 0:
+            norm = q.norm() + 1e-8
+            if norm > self.constraint:
+                q = q * (self.constraint / norm)
+        eye = torch.eye(self.block_size, device=q.device).expand_as(q)
+        r = (eye + q) @ torch.linalg.inv(eye - q)
+        if multiplier != 1.0:
+            r = r * multiplier + eye * (1.0 - multiplier)
+        return r
+
+    def _apply(self, r: Tensor, rows: Tensor) -> Tensor:
+        """Rotate `rows [out, ...]` by the butterfly product of the stages in `r`."""
+        b, half = self.block_size, self.block_size // 2
+        x = rows
+        for i in range(self.stages):
+            k = (2 ** i) * half
+            x = x.unflatten(0, (-1, 2, k)).transpose(1, 2).flatten(0, 2).unflatten(0, (-1, b))
+            x = torch.einsum("nij,nj...->ni...", r[i].to(x.dtype), x)
+            x = x.flatten(0, 1).unflatten(0, (-1, k, 2)).transpose(1, 2).flatten(0, 2)
+        return x
+
+    def merged(self, w: Tensor) -> Tensor:
+        wf = w.float()
+        new = self._apply(self.rotation(self.multiplier), wf)
+        if self.rescale is not None:
+            new = new * self.rescale.float()
+        return new.to(w.dtype)
+
+    def bypass(self, x, y, lin):
+        if self._skip():
+            return y
+        bias = None if lin.bias is None else lin.bias.to(y.dtype)
+        core = y if bias is None else y - bias
+        flat = core.reshape(-1, core.shape[-1]).transpose(0, 1)  # [out, tokens]
+        out = self._apply(self.rotation(self.multiplier), flat.float()).transpose(0, 1).to(y.dtype).reshape_as(core)
+        if self.rescale is not None:
+            out = out * self.rescale.to(y.dtype).squeeze(-1)
+        return out if bias is None else out + bias
+
+
+class GLoRAModule(AdapterModule):
+    """Generalised LoRA: dW = scale (W a2 a1 + b2 b1), a low-rank term that rescales the base
+    weight from the input side plus a plain low-rank term
+    (`src/kohakumoss/adapters/bind/bodies.py:93-95`). `a1 [r, in]`, `a2 [in, r]`, `b1 [r, in]`,
+    `b2 [out, r]`; a2 and b2 start at zero."""
+
+    algo = "glora"
+
+    def __init__(self, in_features, out_features, rank, alpha, **kw):
+        super().__init__(in_features, out_features, rank, alpha, **kw)
+        self.a1 = nn.Linear(in_features, rank, bias=False)
+        self.a2 = nn.Linear(rank, in_features, bias=False)
+        self.b1 = nn.Linear(in_features, rank, bias=False)
+        self.b2 = nn.Linear(rank, out_features, bias=False)
+        nn.init.kaiming_uniform_(self.a1.weight, a=5 ** 0.5)
+        nn.init.kaiming_uniform_(self.b1.weight, a=5 ** 0.5)
+        nn.init.zeros_(self.a2.weight)
+        nn.init.zeros_(self.b2.weight)
+
+    def delta(self, base=None) -> Tensor:
+        if base is None:
+            raise ValueError("GLoRA needs the base weight to express itself as a delta")
+        w = base.float()
+        return (w @ self.a2.weight.float()) @ self.a1.weight.float() + self.b2.weight.float() @ self.b1.weight.float()
+
+    def bypass(self, x, y, lin):
+        """y + scale (W a2 a1 x + b2 b1 x): the input-side term goes through the base GEMM
+        as a second, rank-r-wide input (x -> a1 -> a2 -> W) rather than building W a2 a1."""
+        if self._skip():
+            return y
+        if self.dora_scale is not None:
+            return super().bypass(x, y, lin)
+        dt = x.dtype
+        h = F.linear(F.linear(x, self.a1.weight.to(dt)), self.a2.weight.to(dt))
+        h = F.linear(h, lin.base_weight(dt))
+        return y + (h + F.linear(F.linear(x, self.b1.weight.to(dt)), self.b2.weight.to(dt))) * self.scale
+
+
 class IA3Module(AdapterModule):
     """(IA)^3: a learned per-channel gain on the input (`on_input`) or the output."""
 
@@ -344,6 +449,8 @@ MODULES: dict[str, type[AdapterModule]] = {
     "loha": LoHaModule,
     "lokr": LoKrModule,
     "oft": OFTModule,
+    "boft": BOFTModule,
+    "glora": GLoRAModule,
     "ia3": IA3Module,
     "full": DiffModule,
     "diff": DiffModule,

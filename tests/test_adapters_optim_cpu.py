@@ -19,7 +19,7 @@ def _lin(i=24, o=32, bias=True):
 
 
 @pytest.mark.parametrize("algo,kw", [("lora", {}), ("loha", {}), ("lokr", {}), ("lokr", {"decompose_both": True, "factor": 4}),
-                                    ("oft", {}), ("ia3", {}), ("full", {})])
+                                    ("oft", {}), ("boft", {}), ("glora", {}), ("ia3", {}), ("full", {})])
 def test_bypass_equals_merged_weight(algo, kw):
     torch.manual_seed(0)
     lin = _lin()
@@ -63,6 +63,36 @@ def test_oft_rotation_is_orthogonal_and_identity_at_init():
     q = b - b.T
     ref = (torch.eye(8) + q) @ torch.linalg.inv(torch.eye(8) - q)
     torch.testing.assert_close(r[0], ref, rtol=1e-4, atol=1e-5)
+
+
+def test_boft_is_an_orthogonal_butterfly_and_bypass_equals_merge():
+    lin = _lin(bias=True)                       # 24 -> 32
+    mod = M.BOFTModule(24, 32, 4)               # 8 blocks of 4 -> 4 butterfly stages
+    assert mod.oft_blocks.shape == (4, 8, 4, 4)
+    w = lin.weight.detach()
+    torch.testing.assert_close(mod.merged(w), w)
+    torch.nn.init.normal_(mod.oft_blocks, std=0.2)
+    full = mod._apply(mod.rotation(), torch.eye(32))     # the dense 32 x 32 rotation
+    torch.testing.assert_close(full @ full.T, torch.eye(32), rtol=1e-4, atol=1e-4)
+    assert (full.abs() > 1e-6).float().mean() > 0.9      # the stages mix every pair of rows
+    torch.testing.assert_close(mod.merged(w), full @ w, rtol=1e-4, atol=1e-5)
+    x = torch.randn(5, 24)
+    y = torch.nn.functional.linear(x, w, lin.bias)
+    torch.testing.assert_close(mod.bypass(x, y, lin), torch.nn.functional.linear(x, mod.merged(w), lin.bias), rtol=1e-4, atol=1e-4)
+
+
+def test_glora_delta_and_bypass_agree():
+    lin = _lin(bias=False)
+    mod = M.GLoRAModule(24, 32, 4, 2.0)
+    w = lin.weight.detach()
+    torch.testing.assert_close(mod.merged(w), w)          # a2 and b2 start at zero
+    for p in mod.parameters():
+        torch.nn.init.normal_(p, std=0.3)
+    dw = (w @ mod.a2.weight @ mod.a1.weight + mod.b2.weight @ mod.b1.weight) * 0.5
+    torch.testing.assert_close(mod.merged(w), w + dw, rtol=1e-4, atol=1e-5)
+    x = torch.randn(5, 24)
+    y = torch.nn.functional.linear(x, w)
+    torch.testing.assert_close(mod.bypass(x, y, lin), torch.nn.functional.linear(x, w + dw), rtol=1e-4, atol=1e-4)
 
 
 def test_dora_keeps_row_norms_at_the_learned_magnitude():
