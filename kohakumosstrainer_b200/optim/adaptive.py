@@ -1,0 +1,210 @@
+"""Learning-rate-free optimisers: Prodigy and schedule-free AdamW.
+
+Both are offered by the `OPTIMIZER` knob (`src/kohakumoss/training/optim/optimizers/factory.py`
+there builds them from third-party packages). They are written here as multi-tensor
+(`torch._foreach_*`) updates: every per-parameter pass is one fused launch over the whole
+group, and the few scalars Prodigy needs (its distance numerator and denominator) stay on the
+device, so a step does not synchronise with the host.
+
+* Prodigy (Mishchenko and Defazio, 2023) estimates the distance to the solution `d` from
+  `<g, x0 - x>` and the accumulated gradient `s`, and scales an Adam step by it; `lr` stays 1.
+* Schedule-free AdamW (Defazio et al., 2024) keeps two sequences, `z` (the plain step) and the
+  averaged `x`; gradients are taken at `y`, an interpolation of the two, which is what the
+  parameters hold during training. `eval_mode()` / `train_mode()` swap the parameters between
+  `y` and `x`; checkpoints and samples are taken in eval mode.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+from torch.optim import Optimizer
+
+
+def _active(group):
+    return [p for p in group["params"] if p.grad is not None]
+
+
+class Prodigy(Optimizer):
+    def __init__(self, params, lr: float = 1.0, betas=(0.9, 0.999), beta3: float | None = None, eps: float = 1e-8,
+                 weight_decay: float = 0.0, d0: float = 1e-6, d_coef: float = 1.0, growth_rate: float = float("inf"),
+                 use_bias_correction: bool = False, safeguard_warmup: bool = False):
+        if d0 <= 0 or lr <= 0:
+            raise ValueError("Prodigy needs lr > 0 and d0 > 0")
+        defaults = dict(lr=lr, betas=tuple(betas), beta3=beta3, eps=eps, weight_decay=weight_decay, d0=d0, d_coef=d_coef,
+                        growth_rate=growth_rate, use_bias_correction=use_bias_correction, safeguard_warmup=safeguard_warmup)
+        super().__init__(params, defaults)
+        self._scalars: dict | None = None
+
+    def _globals(self, device):
+        if self._scalars is None:
+            d0 = self.param_groups[0]["d0"]
+            self._scalars = dict(d=torch.full((), d0, device=device), d_max=torch.full((), d0, device=device),
+                                 numerator=torch.zeros((), device=device), k=0)
+        return self._scalars
+
+    @property
+    def d(self) -> float:
+        return float(self._scalars["d"]) if self._scalars else self.param_groups[0]["d0"]
+
+    def state_dict(self):
+        out = super().state_dict()
+        if self._scalars is not None:
+            out["prodigy"] = {k: (v.clone() if torch.is_tensor(v) else v) for k, v in self._scalars.items()}
+        return out
+
+    def load_state_dict(self, state_dict):
+        extra = state_dict.pop("prodigy", None) if isinstance(state_dict, dict) else None
+        super().load_state_dict(state_dict)
+        if extra is not None:
+            first = self.param_groups[0]["params"][0]
+            self._scalars = {k: (v.to(first.device) if torch.is_tensor(v) else v) for k, v in extra.items()}
+            state_dict["prodigy"] = extra
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        first = next((p for g in self.param_groups for p in _active(g)), None)
+        if first is None:
+            return loss
+        g0 = self.param_groups[0]
+        sc = self._globals(first.device)
+        beta1, beta2 = g0["betas"]
+        beta3 = g0["beta3"] if g0["beta3"] is not None else math.sqrt(beta2)
+        k = sc["k"]
+        bias = (math.sqrt(1 - beta2 ** (k + 1)) / (1 - beta1 ** (k + 1))) if g0["use_bias_correction"] else 1.0
+        d, d0 = sc["d"], g0["d0"]
+        sc["numerator"].mul_(beta3)
+        denom_sum = torch.zeros((), device=first.device)
+        for group in self.param_groups:
+            params = _active(group)
+            if not params:
+                continue
+            dlr = d * (group["lr"] * bias)
+            grads = [p.grad.float() for p in params]
+            for p in params:
+                st = self.state[p]
+                if not st:
+                    st["p0"] = p.detach().float().clone()
+                    st["s"] = torch.zeros_like(p, dtype=torch.float32)
+                    st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                    st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+            p0 = [self.state[p]["p0"] for p in params]
+            s = [self.state[p]["s"] for p in params]
+            m = [self.state[p]["exp_avg"] for p in params]
+            v = [self.state[p]["exp_avg_sq"] for p in params]
+            # numerator += (d / d0) dlr <g, x0 - x>
+            diff = torch._foreach_sub(p0, [p.float() for p in params])
+            dots = torch.stack([(g * x).sum() for g, x in zip(grads, diff)]).sum()
+            sc["numerator"].add_(dots * (d / d0) * dlr)
+            torch._foreach_mul_(m, beta1)
+            torch._foreach_mul_(v, beta2)
+            gd = torch._foreach_mul(grads, d * (1 - beta1))
+            torch._foreach_add_(m, gd)
+            g2 = torch._foreach_mul(grads, grads)
+            torch._foreach_mul_(g2, d * d * (1 - beta2))
+            torch._foreach_add_(v, g2)
+            torch._foreach_mul_(s, beta3)
+            step_scale = (d / d0) * (d if group["safeguard_warmup"] else dlr)
+            torch._foreach_add_(s, torch._foreach_mul(grads, step_scale))
+            denom_sum += torch.stack([x.abs().sum() for x in s]).sum()
+        # the new distance estimate; stays put while the gradients carry no signal
+        d_hat = g0["d_coef"] * sc["numerator"] / denom_sum.clamp_min(1e-30)
+        usable = denom_sum > 0
+        grown = torch.minimum(torch.maximum(sc["d_max"], d_hat), d * g0["growth_rate"]) if math.isfinite(g0["growth_rate"]) \
+            else torch.maximum(sc["d_max"], d_hat)
+        new_dmax = torch.where(usable, torch.maximum(sc["d_max"], d_hat), sc["d_max"])
+        new_d = torch.where(usable, torch.maximum(d, grown), d)
+        for group in self.params_groups_active():
+            params = _active(group)
+            dlr = d * (group["lr"] * bias)
+            m = [self.state[p]["exp_avg"] for p in params]
+            v = [self.state[p]["exp_avg_sq"] for p in params]
+            denom = torch._foreach_sqrt(v)
+            torch._foreach_add_(denom, d * group["eps"])
+            upd = torch._foreach_div(m, denom)
+            for p, u in zip(params, upd):
+                pf = p.float()
+                if group["weight_decay"]:
+                    pf = pf * (1 - group["weight_decay"] * dlr)
+                p.copy_(pf - dlr * u)
+        sc["d"], sc["d_max"] = new_d, new_dmax
+        sc["k"] = k + 1
+        return loss
+
+    def params_groups_active(self):
+        return [g for g in self.param_groups if _active(g)]
+
+
+class ScheduleFreeAdamW(Optimizer):
+    def __init__(self, params, lr: float = 2.5e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
+                 warmup_steps: int = 0, r: float = 0.0, weight_lr_power: float = 2.0):
+        defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay, warmup_steps=warmup_steps, r=r,
+                        weight_lr_power=weight_lr_power, k=0, train_mode=True, weight_sum=0.0, lr_max=-1.0)
+        super().__init__(params, defaults)
+
+    def _swap(self, to_train: bool) -> None:
+        for group in self.param_groups:
+            if group["train_mode"] == to_train:
+                continue
+            beta1 = group["betas"][0]
+            w = (1 - beta1) if to_train else (1 - 1 / beta1)
+            for p in group["params"]:
+                st = self.state.get(p)
+                if st and "z" in st:
+                    p.copy_(torch.lerp(p.float(), st["z"], w))
+            group["train_mode"] = to_train
+
+    @torch.no_grad()
+    def eval_mode(self) -> None:
+        """Parameters <- x, the averaged iterate (for validation, samples and checkpoints)."""
+        self._swap(False)
+
+    @torch.no_grad()
+    def train_mode(self) -> None:
+        """Parameters <- y, the point gradients are taken at."""
+        self._swap(True)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for group in self.param_groups:
+            if not group["train_mode"]:
+                raise RuntimeError("schedule-free step in eval mode: call train_mode() first")
+            params = _active(group)
+            if not params:
+                continue
+            beta1, beta2 = group["betas"]
+            k = group["k"]
+            sched = min(1.0, (k + 1) / group["warmup_steps"]) if group["warmup_steps"] > 0 else 1.0
+            bc2 = 1 - beta2 ** (k + 1)
+            lr = group["lr"] * sched
+            group["lr_max"] = max(lr, group["lr_max"])
+            weight = ((k + 1) ** group["r"]) * (group["lr_max"] ** group["weight_lr_power"])
+            group["weight_sum"] += weight
+            ckp1 = weight / group["weight_sum"] if group["weight_sum"] > 0 else 0.0
+            for p in params:
+                st = self.state[p]
+                if not st:
+                    st["z"] = p.detach().float().clone()
+                    st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+            grads = [p.grad.float() for p in params]
+            z = [self.state[p]["z"] for p in params]
+            v = [self.state[p]["exp_avg_sq"] for p in params]
+            torch._foreach_mul_(v, beta2)
+            torch._foreach_addcmul_(v, grads, grads, 1 - beta2)
+            denom = torch._foreach_div(v, bc2)
+            torch._foreach_sqrt_(denom)
+            torch._foreach_add_(denom, group["eps"])
+            gn = torch._foreach_div(grads, denom)
+            y = [p.float() for p in params]
+            if group["weight_decay"]:
+                torch._foreach_add_(gn, y, alpha=group["weight_decay"])
+            torch._foreach_lerp_(y, z, ckp1)
+            torch._foreach_add_(y, gn, alpha=lr * (beta1 * (1 - ckp1) - 1))
+            torch._foreach_sub_(z, gn, alpha=lr)
+            for p, yy in zip(params, y):
+                p.copy_(yy)
+            group["k"] = k + 1
+        return loss

@@ -47,9 +47,16 @@ def build_optimizer(named_params, name: str = "adamw", lr: float = 1e-4, betas=(
                 sp.append(s)
             groups.append(dict(params=[p for _, p in muon], use_muon=True, splits=sp, weight_decay=weight_decay))
         return MuonHybrid(groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, **kwargs)
-    if name in ("prodigy", "schedule_free"):
-        raise NotImplementedError(f"OPTIMIZER={name} is not available in this build")
     groups = param_groups(named, weight_decay, wd_rules, decay_to_one, lr_mul)
+    if name == "prodigy":
+        from .adaptive import Prodigy
+
+        # lr multiplies the estimated distance: the knob's 1e-4 style values would cancel the estimate
+        return Prodigy(groups, lr=kwargs.pop("lr", 1.0), betas=betas, eps=eps, weight_decay=weight_decay, **kwargs)
+    if name == "schedule_free":
+        from .adaptive import ScheduleFreeAdamW
+
+        return ScheduleFreeAdamW(groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, **kwargs)
     master = name in ("adamw16",) or kwargs.pop("master_weights", False)
     return FusedAdamW(groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, master_weights=master)
 
@@ -86,6 +93,16 @@ class Bundle:
     @property
     def lr(self) -> float:
         return float(self.optimizer.param_groups[0]["lr"])
+
+    def eval_mode(self) -> None:
+        """Schedule-free optimisers hold the gradient point in the parameters while training;
+        validation, samples and checkpoints read the averaged iterate instead."""
+        if hasattr(self.optimizer, "eval_mode"):
+            self.optimizer.eval_mode()
+
+    def train_mode(self) -> None:
+        if hasattr(self.optimizer, "train_mode"):
+            self.optimizer.train_mode()
 
     def observe(self, loss: Tensor) -> None:
         """Accumulate the (detached) loss of a micro-batch for logging and the finite check."""

@@ -162,6 +162,12 @@ class Validation:
         from ..diffusion.objective import noise_latents, token_loss
 
         tr = self.trainer
+        with tr.averaged_weights():
+            return self._run(tr)
+
+    def _run(self, tr) -> dict:
+        from ..diffusion.objective import noise_latents, token_loss
+
         model, dev, dtype = tr.model, tr.device, tr.dtype
         was_training = model.training
         model.eval()
@@ -227,6 +233,10 @@ class SampleGrid:
 
     @torch.no_grad()
     def run(self, step: int) -> dict:
+        with self.trainer.averaged_weights():
+            return self._run(step)
+
+    def _run(self, step: int) -> dict:
         from pathlib import Path
 
         from ..diffusion.sampling import sample_latents

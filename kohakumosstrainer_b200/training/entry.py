@@ -243,7 +243,8 @@ def worker(k: dict, rank: int, world: int, device) -> dict:
     if k["FINAL_CHECKPOINT"] in ("auto", True, "always") and cfg.steps > start:
         _save(ckpt, trainer, cfg.steps, k, device)
     if rank == 0:
-        _export(trainer, run_dir, k)
+        with trainer.averaged_weights():
+            _export(trainer, run_dir, k)
     writer.close()
     return {"step": cfg.steps, **last}
 

@@ -9,6 +9,8 @@ loop (`src/kohakumoss/training/drivers/native.py:53-99`, `drivers/common.py:59-9
 
 from __future__ import annotations
 
+import contextlib
+
 from dataclasses import dataclass, field
 
 import torch
@@ -175,6 +177,16 @@ class Trainer:
         self.batcher = DeviceBatcher(self.device, torch.float32, dtype)
         self.tokens_seen = 0
         self.samples_seen = 0
+
+    @contextlib.contextmanager
+    def averaged_weights(self):
+        """Validation, samples and exports read the optimiser's averaged iterate where it keeps
+        one apart from the training point (schedule-free); a no-op for the others."""
+        self.bundle.eval_mode()
+        try:
+            yield
+        finally:
+            self.bundle.train_mode()
 
     def _begin_fsdp_step(self) -> None:
         b = self.bundle

@@ -9,7 +9,9 @@ around each launch, L2 flushed between launches, median), algorithmic FLOPs and 
 fractions of the measured peaks (`MEASURED_PEAKS.json` when present).
 
 Cases: gemm_bf16, gemm_fp8, gemm_fp8_dgrad, gemm_wgrad, gemm_situ, gemm_qkrope, gemm_fp8_situ, gemm_fp8_qkrope, gemm_fp8_residual, attn_fwd,
-attn_bwd, rms_norm_mod, rms_norm_mod_bwd, situ, quant_fp8, token_mse, adamw.
+attn_bwd, rms_norm_mod, rms_norm_mod_bwd, situ, quant_fp8, token_mse, adamw; the skinny products of a
+rank-8 adapter over a `--width`-wide activation: lora_down (x A^T), lora_dt (d up), lora_dup (d^T t),
+lora_ddown (x^T t2), each with `--splits` (0 = the library's choice).
 """
 
 from __future__ import annotations
@@ -53,9 +55,23 @@ def bf16(*shape, scale=1.0):
     return (torch.randn(*shape, device="cuda") * scale).bfloat16()
 
 
-def build(op: str, tokens: int):
+def build(op: str, tokens: int, width: int = 3072, splits: int = 0):
     """-> (callable, flops, bytes)"""
     M, D, F, H = tokens, 3072, 8192, 24
+    if op.startswith("lora_"):
+        R, sp = 8, (splits or None)
+        x = bf16(M, width)
+        nbytes = 2 * M * width
+        if op == "lora_down":
+            a = bf16(R, width, scale=0.02)
+            return (lambda: native.gemm(x, a, splits=sp)), 2.0 * M * R * width, nbytes
+        if op == "lora_dt":
+            up = bf16(width, R, scale=0.02)
+            return (lambda: native.gemm(x, up, b_mn=True, splits=sp)), 2.0 * M * R * width, nbytes
+        t = bf16(M, R)
+        if op in ("lora_dup", "lora_ddown"):
+            return (lambda: native.gemm(x, t, a_mn=True, b_mn=True, out_dtype=torch.float32, splits=sp)), 2.0 * M * R * width, nbytes
+        raise SystemExit(f"unknown op {op}")
     if op in ("gemm_bf16", "gemm_fp8", "gemm_fp8_dgrad", "gemm_wgrad"):
         N, K = 9216, D
         x, w = bf16(M, K), bf16(N, K, scale=0.02)
@@ -191,12 +207,16 @@ def main():
     ap.add_argument("--op", required=True)
     ap.add_argument("--tokens", type=int, default=8704)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--width", type=int, default=3072)
+    ap.add_argument("--splits", type=int, default=0)
     args = ap.parse_args()
     pk = peaks()
-    fn, flops, nbytes = build(args.op, args.tokens)
+    fn, flops, nbytes = build(args.op, args.tokens, args.width, args.splits)
     ms = run(fn, args.iters)
     native.check_status()
     row = {"op": args.op, "tokens": args.tokens, "ms": round(ms, 4)}
+    if args.op.startswith("lora_"):
+        row.update(width=args.width, splits=args.splits)
     suffix = "of_fallback" if pk.get("fallback") else "of_measured"
     if flops:
         row["tflops"] = round(flops / ms / 1e9, 1)

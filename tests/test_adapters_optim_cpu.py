@@ -266,3 +266,50 @@ def test_dylora_and_tlora_step_state():
         assert all(1 <= r <= 8 for r in seen)
         tr.adapters.end_training()
         assert "rank_mask" not in next(iter(tr.adapters.modules_by_name.values())).__dict__
+
+
+def _quadratic(opt_factory, steps):
+    torch.manual_seed(0)
+    target = torch.randn(16, 8)
+    w = torch.nn.Parameter(torch.zeros(16, 8))
+    opt = opt_factory([w])
+    for _ in range(steps):
+        opt.zero_grad()
+        loss = ((w - target) ** 2).mean()
+        loss.backward()
+        opt.step()
+    return w, target, opt
+
+
+def test_prodigy_finds_its_own_step_size():
+    from kohakumosstrainer_b200.optim.adaptive import Prodigy
+
+    w, target, opt = _quadratic(lambda p: Prodigy(p, lr=1.0, betas=(0.9, 0.99)), 400)
+    assert opt.d > 1e-3                      # grew from d0 = 1e-6 by orders of magnitude
+    assert float(((w.detach() - target) ** 2).mean()) < 1e-2
+    sd = opt.state_dict()
+    assert "prodigy" in sd and float(sd["prodigy"]["d"]) == pytest.approx(opt.d)
+
+
+def test_schedule_free_averages_and_swaps_modes():
+    from kohakumosstrainer_b200.optim.adaptive import ScheduleFreeAdamW
+
+    w, target, opt = _quadratic(lambda p: ScheduleFreeAdamW(p, lr=0.05, warmup_steps=10), 300)
+    y = w.detach().clone()
+    opt.eval_mode()
+    assert float(((w.detach() - target) ** 2).mean()) < 1e-2
+    with pytest.raises(RuntimeError):
+        w.grad = torch.zeros_like(w)
+        opt.step()
+    opt.train_mode()
+    torch.testing.assert_close(w.detach(), y, rtol=1e-5, atol=1e-6)   # eval -> train is the inverse swap
+
+
+def test_build_optimizer_offers_every_knob_value():
+    from kohakumosstrainer_b200.optim.bundle import OPTIMIZERS, build_optimizer
+
+    for name in OPTIMIZERS:
+        lin = torch.nn.Linear(8, 8)
+        opt = build_optimizer(list(lin.named_parameters()), name)
+        lin(torch.randn(2, 8)).sum().backward()
+        opt.step()
