@@ -1,13 +1,16 @@
-"""Optimisers (fused AdamW, Muon hybrid), schedules, EMA and the step bundle."""
+"""Optimisers (fused AdamW, Muon hybrid, Prodigy, schedule-free AdamW), schedules, EMA, loss scalers and the step bundle."""
 
 from .adamw import FusedAdamW
+from .adaptive import Prodigy, ScheduleFreeAdamW
 from .bundle import Bundle, build_optimizer
 from .ema import ConstantEMA, PowerEMA
 from .groups import param_groups, weight_decay_rule
 from .muon import MuonHybrid, newton_schulz
+from .scaler import DeviceScaler, DynamicScaler, NoScaler, build_scaler
 from .schedule import build_schedule
 
 __all__ = [
     "FusedAdamW", "Bundle", "build_optimizer", "ConstantEMA", "PowerEMA", "param_groups", "weight_decay_rule",
-    "MuonHybrid", "newton_schulz", "build_schedule",
+    "MuonHybrid", "newton_schulz", "build_schedule", "Prodigy", "ScheduleFreeAdamW", "DeviceScaler", "DynamicScaler",
+    "NoScaler", "build_scaler",
 ]

@@ -18,6 +18,7 @@ from torch import Tensor
 from .adamw import FusedAdamW, ParamTable
 from .groups import is_muon_param, param_groups
 from .muon import MuonHybrid
+from .scaler import NoScaler
 from .schedule import build_schedule
 
 OPTIMIZERS = ("adamw", "adamw16", "adamw8bit", "adamw8bit_kernel", "muon", "prodigy", "schedule_free")
@@ -65,7 +66,8 @@ class Bundle:
     def __init__(self, optimizer, params: list[Tensor], total_steps: int = 1000, schedule: dict | None = None,
                  grad_clip: float = 1.0, step_sync: str = "step", reduce_flags: Callable | None = None,
                  reduce_norm_sq: Callable | None = None, ema=None, finish_grads: Callable | None = None,
-                 norm_params: list[Tensor] | None = None, extra_sumsq: Callable | None = None, post_step: Callable | None = None):
+                 norm_params: list[Tensor] | None = None, extra_sumsq: Callable | None = None, post_step: Callable | None = None,
+                 scaler=None):
         self.optimizer = optimizer
         self.params = [p for p in params if p.requires_grad]
         self.base_lrs = [g["lr"] for g in optimizer.param_groups]
@@ -80,6 +82,9 @@ class Bundle:
         self.norm_params = [p for p in (norm_params if norm_params is not None else self.params) if p.requires_grad]
         self.extra_sumsq = extra_sumsq  # () -> fp32[1] squared norm of gradients held elsewhere (already global)
         self.post_step = post_step
+        self.scaler = scaler if scaler is not None else NoScaler()
+        # FusedAdamW / MuonHybrid read the clip coefficient and the skip flag on the device
+        self._device_args = isinstance(optimizer, (FusedAdamW, MuonHybrid))
         self.step_index = 0
         self.skipped = 0
         self.last_loss = float("nan")
@@ -147,6 +152,11 @@ class Bundle:
         for g, base in zip(self.optimizer.param_groups, self.base_lrs):
             g["lr"] = base * self.factor(self.step_index)
         stats, bad = self._norm()
+        inv = self.scaler.inv_scale(stats.device)
+        if inv is not None:  # gradients carry the loss scale: norm and clip are of the unscaled ones
+            norm = stats[0:1] * inv
+            clip = torch.clamp(self.grad_clip / (norm + 1e-6), max=1.0) if self.grad_clip > 0 else torch.ones_like(norm)
+            stats = torch.cat((norm, clip * inv, stats[2:3] * inv * inv))
         loss = self._loss if self._loss is not None else torch.zeros((), device=stats.device)
         flags = torch.stack((loss.reshape(()), (bad[0] > 0).float() + (~torch.isfinite(stats[0])).float()))
         if self.reduce_flags is not None:
@@ -154,7 +164,15 @@ class Bundle:
         skip = ((flags[1] > 0) | ~torch.isfinite(flags[0])).to(torch.int32).reshape(1)
         if self.ema is not None:
             self.ema.before_step(self.step_index)
-        self.optimizer.step(grad_scale=stats[1:2] if self.grad_clip > 0 else None, skip=skip)
+        scale_grads = self.grad_clip > 0 or inv is not None
+        if self._device_args:
+            self.optimizer.step(grad_scale=stats[1:2] if scale_grads else None, skip=skip)
+        else:  # a plain torch optimiser: scale the gradients in place and decide the skip on the host
+            if scale_grads:
+                torch._foreach_mul_([p.grad for p in self.params if p.grad is not None], stats[1])
+            if not bool(skip):
+                self.optimizer.step()
+        self.scaler.update(skip[0])
         self.last_clip, self.last_skip = stats[1:2], skip
         if self.post_step is not None:
             self.post_step()
@@ -189,9 +207,11 @@ class Bundle:
             self._deferred = None
 
     def state_dict(self) -> dict:
-        return {"optimizer": self.optimizer.state_dict(), "schedule": {"step": self.step_index}, "skipped": self.skipped}
+        return {"optimizer": self.optimizer.state_dict(), "schedule": {"step": self.step_index}, "skipped": self.skipped,
+                "scaler": self.scaler.state_dict()}
 
     def load_state_dict(self, sd: dict) -> None:
         self.optimizer.load_state_dict(sd["optimizer"])
         self.step_index = sd["schedule"]["step"]
         self.skipped = sd.get("skipped", 0)
+        self.scaler.load_state_dict(sd.get("scaler") or {})

@@ -22,7 +22,7 @@ from ..models import build_backbone
 from ..models.build import resolve_arch
 from ..logging.phases import phase
 from ..models.runners import build_runner
-from ..optim import Bundle, ConstantEMA, build_optimizer
+from ..optim import Bundle, ConstantEMA, build_optimizer, build_scaler
 from ..quant import apply_base_precision
 from .step import DeviceBatcher, TrainStep
 
@@ -159,7 +159,8 @@ class Trainer:
         self.ema = ConstantEMA(named, (cfg.ema,)) if cfg.ema > 0 else None
         self.bundle = Bundle(opt, self.params, cfg.steps, cfg.schedule, cfg.grad_clip, cfg.step_sync,
                              reduce_flags=reduce_flags, ema=self.ema, finish_grads=finish, norm_params=norm_params,
-                             extra_sumsq=extra_sumsq, post_step=post_step)
+                             extra_sumsq=extra_sumsq, post_step=post_step,
+                             scaler=build_scaler(cfg.precision, self.device, cfg.step_sync))
         self.normalizer = TokenNormalizer(reduce_tokens, 1)
         self.step_fn = TrainStep(self.model, self.device, cfg.timestep, cfg.timestep_kwargs, cfg.loss, None,
                                  cfg.weighting, cfg.seed, rank, dtype)
@@ -219,7 +220,7 @@ class Trainer:
             with phase("forward"):
                 loss = self.step_fn(batch, denom)
             with phase("backward"):
-                loss.backward()
+                self.bundle.scaler.scale_loss(loss).backward()
             self.bundle.observe(loss)
         with phase("optimizer"):
             ok = self.bundle.step()

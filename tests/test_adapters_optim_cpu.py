@@ -313,3 +313,51 @@ def test_build_optimizer_offers_every_knob_value():
         opt = build_optimizer(list(lin.named_parameters()), name)
         lin(torch.randn(2, 8)).sum().backward()
         opt.step()
+
+
+def test_device_scaler_follows_the_host_scaler():
+    from kohakumosstrainer_b200.optim.scaler import DeviceScaler, DynamicScaler
+
+    kw = dict(init_scale=2.0**10, growth_interval=3, floor=1.0)
+    host, dev = DynamicScaler(**kw), DeviceScaler("cpu", **kw)
+    pattern = [0, 0, 0, 1, 0, 1, 1, 0, 0, 0, 0, 0, 0] + [1] * 14
+    for bad in pattern:
+        host.update(bad)
+        dev.update(torch.tensor(float(bad)))
+        assert dev.host_scale() == host.host_scale()
+    assert host.host_scale() == 1.0                       # floored
+    dev2 = DeviceScaler("cpu", **kw)
+    dev2.load_state_dict(dev.state_dict())
+    assert dev2.state_dict() == dev.state_dict()
+
+
+def test_bundle_unscales_through_the_clip_coefficient_and_steps_plain_optimisers():
+    from kohakumosstrainer_b200.optim import Bundle
+    from kohakumosstrainer_b200.optim.scaler import DynamicScaler
+
+    def run(scaler):
+        torch.manual_seed(0)
+        lin = torch.nn.Linear(8, 8)
+        opt = torch.optim.SGD(lin.parameters(), lr=0.1)
+        b = Bundle(opt, list(lin.parameters()), schedule={"mode": "constant"}, grad_clip=0.5, scaler=scaler)
+        x = torch.randn(4, 8)
+        for _ in range(3):
+            loss = lin(x).square().mean()
+            b.scaler.scale_loss(loss).backward()
+            b.observe(loss)
+            assert b.step()
+        return lin.weight.detach().clone(), b.last_norm
+
+    (w0, n0), (w1, n1) = run(None), run(DynamicScaler(init_scale=256.0))
+    torch.testing.assert_close(w0, w1, rtol=1e-5, atol=1e-6)
+    assert n0 == pytest.approx(n1, rel=1e-5)
+    # a non-finite gradient skips the step and backs the scale off
+    lin = torch.nn.Linear(4, 4)
+    sc = DynamicScaler(init_scale=256.0)
+    b = Bundle(torch.optim.SGD(lin.parameters(), lr=0.1), list(lin.parameters()), schedule={"mode": "constant"}, scaler=sc)
+    before = lin.weight.detach().clone()
+    for p in lin.parameters():
+        p.grad = torch.full_like(p, float("inf"))
+    assert not b.step()
+    torch.testing.assert_close(lin.weight.detach(), before)
+    assert sc.host_scale() == 128.0 and b.skipped == 1
