@@ -407,6 +407,7 @@ void adamw_multi(const Tensor& table, const Tensor& chunks, double lr, double be
   h.inv_bc1 = (float)(1.0 / (1.0 - std::pow(beta1, (double)step)));
   h.inv_sqrt_bc2 = (float)(1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step)));
   h.ema_decay = (float)ema_decay;
+  h.seed = (unsigned)step * 2654435761u + 0x51ED27u;
   h.grad_scale = cptr<float>(grad_scale);
   h.skip = cptr<int>(skip);
   KM_CHECK_CUDA(kmoss::adamw_multi(reinterpret_cast<const kmoss::OptTensor*>(table.data_ptr()),

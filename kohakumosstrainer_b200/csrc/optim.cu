@@ -29,8 +29,66 @@ __device__ __forceinline__ void store_elem(void* p, int dtype, long i, float v) 
   else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16(v);
 }
 
+// counter-based 32-bit mix of (element index, seed): the random bits of stochastic rounding
+__device__ __forceinline__ unsigned mix32(unsigned idx, unsigned seed) {
+  unsigned h = idx * 0x9E3779B1u + seed;
+  h ^= h >> 16; h *= 0x7FEB352Du;
+  h ^= h >> 15; h *= 0x846CA68Bu;
+  h ^= h >> 16;
+  return h;
+}
+
+// fp32 -> bf16 with the low 16 bits rounded up with probability (low bits) / 2^16
+__device__ __forceinline__ __nv_bfloat16 stochastic_bf16(float v, unsigned rnd) {
+  unsigned bits = __float_as_uint(v);
+  if ((bits & 0x7F800000u) != 0x7F800000u) bits += rnd & 0xFFFFu;
+  return __ushort_as_bfloat16((unsigned short)(bits >> 16));
+}
+
+struct AdamWElem { float p, m, v; };
+
+__device__ __forceinline__ void adamw_update(AdamWElem& e, float g, const OptTensor& t, const AdamWHyper& h, float lr,
+                                             float decay) {
+  e.m = h.beta1 * e.m + (1.f - h.beta1) * g;
+  e.v = h.beta2 * e.v + (1.f - h.beta2) * g * g;
+  const float denom = sqrtf(e.v) * h.inv_sqrt_bc2 + h.eps;
+  if (t.decay_to_one) e.p = 1.f + (e.p - 1.f) * decay;  // norm weights decay towards 1
+  else e.p *= decay;
+  e.p -= lr * h.inv_bc1 * e.m / denom;
+}
+
+__device__ __forceinline__ float load_param(const OptTensor& t, long i) {
+  if (t.master != nullptr) return t.master[i];
+  float p = load_elem(t.param, t.param_dtype, i);
+  if (t.mode == 2 && t.comp != nullptr) p += load_elem(t.comp, t.param_dtype, i);
+  return p;
+}
+
+__device__ __forceinline__ void store_param(const OptTensor& t, long i, float p, unsigned seed) {
+  if (t.master != nullptr) t.master[i] = p;
+  if (t.param_dtype == 1 && t.master == nullptr && t.mode == 1) {
+    reinterpret_cast<__nv_bfloat16*>(t.param)[i] = stochastic_bf16(p, mix32((unsigned)i, seed));
+  } else {
+    store_elem(t.param, t.param_dtype, i, p);
+    if (t.mode == 2 && t.comp != nullptr && t.master == nullptr)
+      store_elem(t.comp, t.param_dtype, i, p - load_elem(t.param, t.param_dtype, i));
+  }
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  __syncthreads();  // red is reused between calls
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float m = red[0];
+#pragma unroll
+  for (int i = 1; i < OPT_THREADS / 32; ++i) m = fmaxf(m, red[i]);
+  return m;
+}
+
 __global__ void __launch_bounds__(OPT_THREADS)
 adamw_multi_kernel(const OptTensor* __restrict__ tensors, const int2* __restrict__ chunks, AdamWHyper h) {
+  __shared__ float red[OPT_THREADS / 32];
   if (h.skip != nullptr && *h.skip != 0) return;
   const int2 c = chunks[blockIdx.x];
   const OptTensor t = tensors[c.x];
@@ -39,21 +97,47 @@ adamw_multi_kernel(const OptTensor* __restrict__ tensors, const int2* __restrict
   const float gs = h.grad_scale != nullptr ? *h.grad_scale : 1.f;
   const float lr = h.lr * t.lr_mul;
   const float decay = 1.f - lr * t.weight_decay;
-  for (long i = begin + threadIdx.x; i < end; i += OPT_THREADS) {
-    const float g = load_elem(t.grad, t.grad_dtype, i) * gs;
-    float p = t.master != nullptr ? t.master[i] : load_elem(t.param, t.param_dtype, i);
-    float m = t.exp_avg[i], v = t.exp_avg_sq[i];
-    m = h.beta1 * m + (1.f - h.beta1) * g;
-    v = h.beta2 * v + (1.f - h.beta2) * g * g;
-    const float denom = sqrtf(v) * h.inv_sqrt_bc2 + h.eps;
-    if (t.decay_to_one) p = 1.f + (p - 1.f) * decay;  // norm weights decay towards 1
-    else p *= decay;
-    p -= lr * h.inv_bc1 * m / denom;
-    t.exp_avg[i] = m;
-    t.exp_avg_sq[i] = v;
-    if (t.master != nullptr) t.master[i] = p;
-    store_elem(t.param, t.param_dtype, i, p);
-    if (t.ema != nullptr) t.ema[i] += (1.f - h.ema_decay) * (p - t.ema[i]);
+  if (t.mq == nullptr) {
+    for (long i = begin + threadIdx.x; i < end; i += OPT_THREADS) {
+      const float g = load_elem(t.grad, t.grad_dtype, i) * gs;
+      AdamWElem e{load_param(t, i), t.exp_avg[i], t.exp_avg_sq[i]};
+      adamw_update(e, g, t, h, lr, decay);
+      t.exp_avg[i] = e.m;
+      t.exp_avg_sq[i] = e.v;
+      store_param(t, i, e.p, h.seed);
+      if (t.ema != nullptr) t.ema[i] += (1.f - h.ema_decay) * (e.p - t.ema[i]);
+    }
+    return;
+  }
+  // 8-bit states: one 256-element quantisation block per pass, thread i owns element i of the block
+  static_assert(OPT_THREADS == 256 && OPT_CHUNK % 256 == 0, "state blocks are one element per thread");
+  for (long base = begin; base < end; base += OPT_THREADS) {  // uniform trip count: every thread reaches the barriers
+    const long i = base + threadIdx.x;
+    const long blk = base / OPT_THREADS;
+    const bool live = i < end;
+    AdamWElem e{0.f, 0.f, 0.f};
+    if (live) {
+      const float qm = (float)t.mq[i], qr = (float)t.rq[i];
+      const float am = fabsf(qm) * (1.f / 127.f), ar = qr * (1.f / 255.f);
+      e.m = copysignf(am * am * t.ms[blk], qm);
+      const float r = ar * ar * t.rs[blk];
+      e.v = r * r;
+      e.p = load_param(t, i);
+      adamw_update(e, load_elem(t.grad, t.grad_dtype, i) * gs, t, h, lr, decay);
+    }
+    const float r_new = sqrtf(e.v);
+    const float m_scale = fmaxf(block_max(live ? fabsf(e.m) : 0.f, red), 1e-30f);
+    const float r_scale = fmaxf(block_max(live ? r_new : 0.f, red), 1e-30f);
+    if (live) {
+      t.mq[i] = (signed char)copysignf(rintf(sqrtf(fabsf(e.m) / m_scale) * 127.f), e.m);
+      t.rq[i] = (unsigned char)rintf(sqrtf(r_new / r_scale) * 255.f);
+      store_param(t, i, e.p, h.seed);
+      if (t.ema != nullptr) t.ema[i] += (1.f - h.ema_decay) * (e.p - t.ema[i]);
+    }
+    if (threadIdx.x == 0) {
+      t.ms[blk] = m_scale;
+      t.rs[blk] = r_scale;
+    }
   }
 }
 

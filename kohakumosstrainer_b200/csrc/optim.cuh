@@ -20,7 +20,14 @@ struct OptTensor {
   int param_dtype;
   int grad_dtype;
   int decay_to_one;
-  int pad;
+  int mode;        // writeback of a bf16 parameter without master: 0 nearest, 1 stochastic rounding, 2 Kahan (uses comp)
+  void* comp;      // Kahan compensation, same dtype as the parameter (nullable)
+  // 8-bit states (nullable; when set, exp_avg / exp_avg_sq are unused): blockwise (256) sqrt-companded codes of the
+  // first moment (int8) and of r = sqrt(second moment) (uint8), with one fp32 absmax per block
+  signed char* mq;
+  unsigned char* rq;
+  float* ms;
+  float* rs;
 };
 
 struct AdamWHyper {
@@ -28,6 +35,7 @@ struct AdamWHyper {
   float inv_bc1;        // 1 / (1 - beta1^t)
   float inv_sqrt_bc2;   // 1 / sqrt(1 - beta2^t)
   float ema_decay;
+  unsigned seed;        // stochastic rounding: hashed with the element index, changes every step
   const float* grad_scale;  // device scalar multiplied into every gradient (clip coefficient), nullable
   const int* skip;          // device flag: non-zero skips the whole step, nullable
 };

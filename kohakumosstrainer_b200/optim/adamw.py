@@ -1,4 +1,4 @@
-"""AdamW as one multi-tensor CUDA launch (fp32 states, optional fp32 masters, fused EMA).
+"""AdamW as one multi-tensor CUDA launch (fp32 or 8-bit states, optional fp32 masters, fused EMA).
 
 Semantics of the reference AdamW (`src/kohakumoss_kernels/optim/reference.py:13-131`,
 defaults `scripts/train/moss.py:137-151`): decoupled weight decay, bias-corrected moments,
@@ -6,6 +6,12 @@ decay-to-one for the norm weights the `moss` rule marks. On CUDA the step is
 `csrc/optim.cu::adamw_multi`: the descriptor table is built once (addresses are stable), the
 clip coefficient and the skip flag stay on the device, so `step()` never synchronises. On CPU
 the same math runs in plain torch (the test oracle).
+
+`states="8bit"` keeps the first moment as int8 and r = sqrt(second moment) as uint8 codes,
+sqrt-companded within blocks of 256 elements with one fp32 absmax each (2 bytes + 1/32 per
+element instead of 8); `writeback` chooses how a bf16 parameter without an fp32 master takes the
+fp32 result: `nearest`, `stochastic` (unbiased, counter-based random bits) or `kahan` (a bf16
+compensation buffer carries the rounding error to the next step).
 """
 
 from __future__ import annotations
@@ -16,6 +22,50 @@ import torch
 from torch import Tensor
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
+WRITEBACK = {"nearest": 0, "stochastic": 1, "kahan": 2}
+STATE_BLOCK = 256
+
+
+def quant_state(x: Tensor, signed: bool) -> tuple[Tensor, Tensor]:
+    """Blockwise sqrt-companded 8-bit codes of a flat fp32 tensor and the fp32 block scales."""
+    n = x.numel()
+    xf = torch.nn.functional.pad(x.float().reshape(-1), (0, (-n) % STATE_BLOCK)).view(-1, STATE_BLOCK)
+    scale = xf.abs().amax(1).clamp_min(1e-30)
+    t = (xf.abs() / scale[:, None]).sqrt()
+    q = (torch.sign(xf) * torch.round(t * 127)).to(torch.int8) if signed else torch.round(t * 255).to(torch.uint8)
+    return q.reshape(-1)[:n].clone(), scale
+
+
+def dequant_state(q: Tensor, scale: Tensor, signed: bool) -> Tensor:
+    n = q.numel()
+    qf = torch.nn.functional.pad(q.float().reshape(-1), (0, (-n) % STATE_BLOCK)).view(-1, STATE_BLOCK)
+    t = qf.abs() / (127.0 if signed else 255.0)
+    v = t * t * scale[:, None]
+    return (v * torch.sign(qf) if signed else v).reshape(-1)[:n]
+
+
+def _mix32(idx: Tensor, seed: int) -> Tensor:
+    m = 0xFFFFFFFF
+    h = (idx.to(torch.int64) * 0x9E3779B1 + seed) & m
+    h ^= h >> 16
+    h = (h * 0x7FEB352D) & m
+    h ^= h >> 15
+    h = (h * 0x846CA68B) & m
+    h ^= h >> 16
+    return h
+
+
+def stochastic_bf16(x: Tensor, seed: int) -> Tensor:
+    """fp32 -> bf16, rounding up with probability (dropped bits) / 2^16; the same bits as the CUDA step."""
+    bits = x.float().contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    rnd = _mix32(torch.arange(x.numel(), device=x.device).view(x.shape), seed) & 0xFFFF
+    out = (bits + rnd) & 0xFFFF0000
+    out = torch.where(out >= 2**31, out - 2**32, out).to(torch.int32)
+    return out.view(torch.float32).to(torch.bfloat16)
+
+
+def step_seed(step: int) -> int:
+    return (step * 2654435761 + 0x51ED27) & 0xFFFFFFFF
 
 
 class ParamTable:
@@ -31,12 +81,13 @@ class ParamTable:
         for ti, e in enumerate(entries):
             p, g = e["param"], e["grad"]
             rec += struct.pack(
-                "<7q2f4i", p.data_ptr(), g.data_ptr(), e["m"].data_ptr() if e.get("m") is not None else 0,
+                "<7q2f4i5q", p.data_ptr(), g.data_ptr(), e["m"].data_ptr() if e.get("m") is not None else 0,
                 e["v"].data_ptr() if e.get("v") is not None else 0,
                 e["master"].data_ptr() if e.get("master") is not None else 0,
                 e["ema"].data_ptr() if e.get("ema") is not None else 0,
                 p.numel(), float(e.get("lr_mul", 1.0)), float(e.get("wd", 0.0)), _DT[p.dtype], _DT[g.dtype],
-                int(bool(e.get("decay_to_one", False))), 0,
+                int(bool(e.get("decay_to_one", False))), int(e.get("mode", 0)),
+                *(e[k].data_ptr() if e.get(k) is not None else 0 for k in ("comp", "mq", "rq", "ms", "rs")),
             )
             for c in range((p.numel() + chunk - 1) // chunk):
                 chunks.append((ti, c))
@@ -47,10 +98,14 @@ class ParamTable:
 
 
 class FusedAdamW(torch.optim.Optimizer):
-    def __init__(self, params, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01, master_weights: bool = False):
+    def __init__(self, params, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01, master_weights: bool = False,
+                 states: str = "fp32", writeback: str = "nearest"):
+        if states not in ("fp32", "8bit") or writeback not in WRITEBACK:
+            raise ValueError("states: fp32 | 8bit; writeback: nearest | stochastic | kahan")
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, lr_mul=1.0, decay_to_one=False)
         super().__init__(params, defaults)
         self.master_weights = master_weights
+        self.states, self.writeback = states, writeback
         self.ema_buffers: dict[int, Tensor] = {}
         self.ema_decay = 1.0
         self._tables: dict[int, ParamTable] = {}
@@ -65,10 +120,19 @@ class FusedAdamW(torch.optim.Optimizer):
     def _state(self, p: Tensor) -> dict:
         st = self.state[p]
         if not st:
-            st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
-            st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+            if self.states == "8bit":
+                blocks = (p.numel() + STATE_BLOCK - 1) // STATE_BLOCK
+                st["mq"] = torch.zeros(p.numel(), dtype=torch.int8, device=p.device)
+                st["rq"] = torch.zeros(p.numel(), dtype=torch.uint8, device=p.device)
+                st["ms"] = torch.full((blocks,), 1e-30, dtype=torch.float32, device=p.device)
+                st["rs"] = torch.full((blocks,), 1e-30, dtype=torch.float32, device=p.device)
+            else:
+                st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
             if self.master_weights and p.dtype != torch.float32:
                 st["master"] = p.detach().float().clone()
+            elif self.writeback == "kahan" and p.dtype == torch.bfloat16:
+                st["comp"] = torch.zeros_like(p)
         return st
 
     def _entries(self, group) -> list[dict]:
@@ -77,7 +141,9 @@ class FusedAdamW(torch.optim.Optimizer):
             if p.grad is None:
                 continue
             st = self._state(p)
-            out.append(dict(param=p.data, grad=p.grad, m=st["exp_avg"], v=st["exp_avg_sq"], master=st.get("master"),
+            out.append(dict(param=p.data, grad=p.grad, m=st.get("exp_avg"), v=st.get("exp_avg_sq"), master=st.get("master"),
+                            mode=WRITEBACK[self.writeback], comp=st.get("comp"), mq=st.get("mq"), rq=st.get("rq"),
+                            ms=st.get("ms"), rs=st.get("rs"),
                             ema=self.ema_buffers.get(id(p)), lr_mul=group.get("lr_mul", 1.0), wd=group["weight_decay"],
                             decay_to_one=group.get("decay_to_one", False)))
         return out
@@ -113,16 +179,35 @@ class FusedAdamW(torch.optim.Optimizer):
         for e in entries:
             g = e["grad"].float() * gs
             p = e["master"] if e["master"] is not None else e["param"].float()
+            if e["master"] is None and e.get("comp") is not None:
+                p = p + e["comp"].float()
             lr = group["lr"] * e["lr_mul"]
-            e["m"].mul_(b1).add_(g, alpha=1 - b1)
-            e["v"].mul_(b2).addcmul_(g, g, value=1 - b2)
-            denom = e["v"].sqrt() / bc2**0.5 + group["eps"]
+            eight = e.get("mq") is not None
+            if eight:
+                shape = e["param"].shape
+                m = dequant_state(e["mq"], e["ms"], True).view(shape)
+                v = dequant_state(e["rq"], e["rs"], False).view(shape).square()
+            else:
+                m, v = e["m"], e["v"]
+            m.mul_(b1).add_(g, alpha=1 - b1)
+            v.mul_(b2).addcmul_(g, g, value=1 - b2)
+            denom = v.sqrt() / bc2**0.5 + group["eps"]
             decay = 1 - lr * e["wd"]
             p = 1 + (p - 1) * decay if e["decay_to_one"] else p * decay
-            p = p - lr / bc1 * e["m"] / denom
+            p = p - lr / bc1 * m / denom
+            if eight:
+                for key_q, key_s, val, signed in (("mq", "ms", m, True), ("rq", "rs", v.sqrt(), False)):
+                    q, s = quant_state(val, signed)
+                    e[key_q].copy_(q)
+                    e[key_s].copy_(s)
             if e["master"] is not None:
                 e["master"].copy_(p)
-            e["param"].copy_(p.to(e["param"].dtype))
+            if e["master"] is None and e["param"].dtype == torch.bfloat16 and e.get("mode") == 1:
+                e["param"].copy_(stochastic_bf16(p, step_seed(self._steps)))
+            else:
+                e["param"].copy_(p.to(e["param"].dtype))
+                if e["master"] is None and e.get("comp") is not None:
+                    e["comp"].copy_((p - e["param"].float()).to(e["comp"].dtype))
             if e["ema"] is not None:
                 e["ema"].add_((p - e["ema"]) * (1 - self.ema_decay))
 

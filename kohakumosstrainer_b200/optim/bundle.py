@@ -27,9 +27,9 @@ OPTIMIZERS = ("adamw", "adamw16", "adamw8bit", "adamw8bit_kernel", "muon", "prod
 def build_optimizer(named_params, name: str = "adamw", lr: float = 1e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                     weight_decay: float = 0.01, wd_rules: str = "moss", kwargs: dict | None = None,
                     decay_to_one: tuple[str, ...] = (), lr_mul: dict | None = None, splits: dict | None = None):
-    """`OPTIMIZER` knob -> optimiser. `adamw16` / `adamw8bit*` map onto the fused AdamW with
-    fp32 masters (B200 has the memory for fp32 states; the low-memory state formats of the
-    reference exist to fit 24 GB cards)."""
+    """`OPTIMIZER` knob -> optimiser. `adamw16` is the fused AdamW on bf16 parameters with fp32
+    masters (or `writeback="kahan" | "stochastic"` through the kwargs, without them); `adamw8bit*`
+    is the same kernel on blockwise 8-bit states."""
     named = [(n, p) for n, p in named_params if p.requires_grad]
     kwargs = dict(kwargs or {})
     if name not in OPTIMIZERS:
@@ -58,8 +58,11 @@ def build_optimizer(named_params, name: str = "adamw", lr: float = 1e-4, betas=(
         from .adaptive import ScheduleFreeAdamW
 
         return ScheduleFreeAdamW(groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, **kwargs)
-    master = name in ("adamw16",) or kwargs.pop("master_weights", False)
-    return FusedAdamW(groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, master_weights=master)
+    writeback = kwargs.pop("writeback", "nearest")
+    master = kwargs.pop("master_weights", name == "adamw16" and writeback == "nearest")
+    states = "8bit" if name.startswith("adamw8bit") else kwargs.pop("states", "fp32")
+    return FusedAdamW(groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, master_weights=master,
+                      states=states, writeback=writeback)
 
 
 class Bundle:

@@ -361,3 +361,29 @@ def test_bundle_unscales_through_the_clip_coefficient_and_steps_plain_optimisers
     assert not b.step()
     torch.testing.assert_close(lin.weight.detach(), before)
     assert sc.host_scale() == 128.0 and b.skipped == 1
+
+
+def test_adamw_8bit_states_track_fp32_states_and_stochastic_rounding_is_unbiased():
+    from kohakumosstrainer_b200.optim.adamw import FusedAdamW, dequant_state, quant_state, stochastic_bf16
+
+    x = torch.randn(1000) * torch.logspace(-3, 1, 1000)
+    q, s = quant_state(x, True)
+    back = dequant_state(q, s, True)
+    assert q.dtype == torch.int8 and s.numel() == 4
+    # sqrt companding: the error scales with sqrt(|x| * block max), small values keep relative precision
+    assert ((back - x).abs() <= 1.1 * (x.abs() * s.repeat_interleave(256)[:1000]).sqrt() / 127 + 1e-12).all()
+
+    torch.manual_seed(0)
+    w0 = torch.randn(64, 33)
+    a, b = torch.nn.Parameter(w0.clone()), torch.nn.Parameter(w0.clone())
+    oa, ob = FusedAdamW([a], lr=1e-2, states="8bit"), FusedAdamW([b], lr=1e-2)
+    for _ in range(20):
+        g = torch.randn(64, 33)
+        a.grad, b.grad = g.clone(), g.clone()
+        oa.step()
+        ob.step()
+    assert (a - b).abs().max() < 0.02 and (b - w0).abs().max() > 0.05    # same trajectory within the code resolution
+
+    v = torch.full((20000,), 1.0 + 2.0**-9)           # a quarter of the way between two bf16 values (ulp 2^-7)
+    up = torch.stack([(stochastic_bf16(v, seed).float() > 1.0).float().mean() for seed in range(8)]).mean()
+    assert abs(float(up) - 0.25) < 0.02

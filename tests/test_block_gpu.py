@@ -261,3 +261,38 @@ def test_fused_adamw_kernel_matches_reference_math():
     before = [p.detach().clone() for p in ps]
     ours.step(skip=skip)
     assert all(torch.equal(a, b) for a, b in zip(before, ps))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("states,writeback", [("8bit", "nearest"), ("fp32", "kahan"), ("fp32", "stochastic"), ("8bit", "kahan")])
+def test_fused_adamw_state_formats_match_the_cpu_reference(states, writeback):
+    """8-bit blockwise states and the bf16 writeback modes: the CUDA step against the same
+    optimiser's plain PyTorch fp32 path on CPU, fed the same gradients."""
+    from kohakumosstrainer_b200.optim import FusedAdamW
+
+    g = torch.Generator().manual_seed(3)
+    shapes = [(300, 17), (8192 + 77,), (64, 64)]
+    init = [torch.randn(s, generator=g).bfloat16() for s in shapes]
+    dev = [torch.nn.Parameter(t.clone().cuda()) for t in init]
+    cpu = [torch.nn.Parameter(t.clone()) for t in init]
+    kw = dict(lr=1e-2, weight_decay=0.1, states=states, writeback=writeback)
+    a, b = FusedAdamW(dev, **kw), FusedAdamW(cpu, **kw)
+    for _ in range(5):
+        for p, r in zip(dev, cpu):
+            gr = torch.randn(r.shape, generator=g).bfloat16()
+            p.grad, r.grad = gr.cuda(), gr.clone()
+        a.step()
+        b.step()
+    for p, r in zip(dev, cpu):
+        # one bf16 ulp of slack: device and host may round a tie differently after five steps
+        torch.testing.assert_close(p.detach().float().cpu(), r.detach().float(), rtol=8e-3, atol=1e-3)
+        sa, sb = a.state[p], b.state[r]
+        if states == "8bit":
+            assert (sa["mq"].cpu().int() - sb["mq"].int()).abs().max() <= 1
+            assert (sa["rq"].cpu().int() - sb["rq"].int()).abs().max() <= 1
+            torch.testing.assert_close(sa["ms"].cpu(), sb["ms"], rtol=1e-3, atol=1e-12)
+        if writeback == "kahan":
+            full_a = p.detach().float().cpu() + sa["comp"].float().cpu()
+            full_b = r.detach().float() + sb["comp"].float()
+            torch.testing.assert_close(full_a, full_b, rtol=1e-3, atol=2e-4)
+
