@@ -1,0 +1,306 @@
+"""Pipeline schedules with several model chunks per rank: looped-bfs, interleaved-1f1b, zbv.
+
+A rank of a `P`-rank pipeline holds `V` chunks (virtual stages); a micro-batch visits all
+`P * V` virtual stages in order. Placement is round-robin (virtual stage `v` on rank `v % P`)
+for looped-bfs and interleaved-1f1b and V-shaped for zbv (rank `r` holds stages `r` and
+`2P - 1 - r`, so the first and the last stage share rank 0 and the turn needs no transfer).
+The reference gets these from `torch.distributed.pipelining`
+(`src/kohakumoss/parallel/pipeline/distributed.py:23-35,54-80,479-503`).
+
+How this engine is put together:
+
+* **Orders are pure functions.** `rank_order(schedule, P, V, n, rank)` returns the rank's list
+  of `(kind, micro_batch, chunk)`; every rank can compute every other rank's list, so the
+  sequence of messages on each link is known everywhere and nothing is negotiated at run time.
+  looped-bfs runs all micro-batches through a chunk before the next chunk; interleaved-1f1b is
+  the depth-first order in groups of `P` micro-batches (needs `n % P == 0`); zbv comes from a
+  deterministic list scheduler (backward first, forward while fewer than `2P` activations are
+  held). Backward is one autograd pass: the weight-gradient half is not split off, because
+  with adapters it is a few percent of the pass.
+* **One communicator per directed link and kind.** Forward activations from rank a to rank b,
+  and gradients from b to a, each get their own two-rank group (`make_links`). A send can then
+  never queue behind a receive that waits for the peer's send, whatever the schedule; within a
+  link messages are FIFO and the receiver posts its receives in the sender's order, stashing
+  what arrives before its consumer runs.
+* What crosses a boundary is the same `(x, mod, head)` triple as in the one-chunk engine.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from .pipeline import StageIO, StageModule
+
+SCHEDULES_VIRTUAL = ("looped-bfs", "interleaved-1f1b", "zbv")
+Op = tuple[str, int, int]  # (kind "F" | "B", micro-batch, chunk)
+
+
+def chunks_per_rank(schedule: str, virtual: int = 2) -> int:
+    return 2 if schedule == "zbv" else max(1, int(virtual))
+
+
+def stage_of(schedule: str, P: int, rank: int, chunk: int) -> int:
+    if schedule == "zbv":
+        return rank if chunk == 0 else 2 * P - 1 - rank
+    return chunk * P + rank
+
+
+def place_of(schedule: str, P: int, stage: int) -> tuple[int, int]:
+    """Virtual stage -> (rank, chunk)."""
+    if schedule == "zbv":
+        return (stage, 0) if stage < P else (2 * P - 1 - stage, 1)
+    return stage % P, stage // P
+
+
+def _simulated(schedule: str, P: int, V: int, n: int) -> list[list[Op]]:
+    """Deterministic list scheduling of all ranks with unit costs (F = 1, B = 2)."""
+    S = P * V
+    done_f = [[-1.0] * S for _ in range(n)]  # finish times, -1 = not run
+    done_b = [[-1.0] * S for _ in range(n)]
+    orders: list[list[Op]] = [[] for _ in range(P)]
+    free_at = [0.0] * P
+    held = [0] * P
+    cap = 2 * P
+    left = 2 * n * S
+    t = 0.0
+    while left:
+        progressed = False
+        for r in range(P):
+            if free_at[r] > t:
+                continue
+            pick = None
+            # backward first, deepest stage first, oldest micro-batch first
+            for c in reversed(range(V)):
+                s = stage_of(schedule, P, r, c)
+                for i in range(n):
+                    if done_b[i][s] >= 0 or done_f[i][s] < 0 or done_f[i][s] > t:
+                        continue
+                    if s < S - 1 and not (0 <= done_b[i][s + 1] <= t):
+                        continue
+                    pick = ("B", i, c)
+                    break
+                if pick:
+                    break
+            if pick is None and held[r] < cap:
+                for c in reversed(range(V)):  # deeper chunks first: they free memory sooner
+                    s = stage_of(schedule, P, r, c)
+                    for i in range(n):
+                        if done_f[i][s] >= 0:
+                            continue
+                        if s > 0 and not (0 <= done_f[i][s - 1] <= t):
+                            continue
+                        pick = ("F", i, c)
+                        break
+                    if pick:
+                        break
+            if pick is None:
+                continue
+            kind, i, c = pick
+            s = stage_of(schedule, P, r, c)
+            cost = 1.0 if kind == "F" else 2.0
+            (done_f if kind == "F" else done_b)[i][s] = t + cost
+            held[r] += 1 if kind == "F" else -1
+            free_at[r] = t + cost
+            orders[r].append(pick)
+            left -= 1
+            progressed = True
+        if not progressed or all(f > t for f in free_at):
+            nxt = [f for f in free_at if f > t]
+            if not nxt:
+                raise RuntimeError(f"{schedule}: no operation is ready with {left} left (P={P}, n={n})")
+            t = min(nxt)
+    return orders
+
+
+def rank_order(schedule: str, P: int, V: int, n: int, rank: int) -> list[Op]:
+    if schedule == "looped-bfs":
+        return [("F", i, c) for c in range(V) for i in range(n)] + [("B", i, c) for c in reversed(range(V)) for i in range(n)]
+    if schedule == "interleaved-1f1b":
+        if n % P:
+            raise ValueError(f"interleaved-1f1b runs micro-batches in groups of {P}: MICROBATCHES={n} is not a multiple")
+        total = n * V
+        warm = min((P - rank - 1) * 2 + (V - 1) * P, total)
+
+        def op(kind, k):
+            c = (k // P) % V
+            return kind, (k // (P * V)) * P + k % P, c if kind == "F" else V - 1 - c
+
+        order = [op("F", k) for k in range(warm)]
+        for k in range(total - warm):
+            order += [op("F", warm + k), op("B", k)]
+        return order + [op("B", k) for k in range(total - warm, total)]
+    if schedule == "zbv":
+        return _simulated(schedule, P, 2, n)[rank]
+    raise ValueError(f"schedule {schedule!r}: the multi-chunk engine runs {SCHEDULES_VIRTUAL}")
+
+
+def make_links(ranks_of_replicas: list[list[int]], backend: str | None = None) -> dict:
+    """Two-rank groups for every directed neighbour link and kind of every replica's ring.
+    Collective: every rank of the world calls it with the same argument. -> {(src, dst, kind): group}."""
+    links = {}
+    for ranks in ranks_of_replicas:
+        P = len(ranks)
+        if P < 2:
+            continue
+        pairs = sorted({(ranks[s], ranks[(s + d) % P]) for s in range(P) for d in (1, -1)})
+        for src, dst in pairs:
+            for kind in ("F", "B"):
+                links[(src, dst, kind)] = dist.new_group(sorted((src, dst)), backend=backend)
+    return links
+
+
+class _Chunks:
+    """The rank's chunks seen as one module (parameters, release of what it does not run)."""
+
+    def __init__(self, model, mods: list[StageModule]):
+        self.model, self.mods = model, mods
+        self.first, self.last = any(m.first for m in mods), any(m.last for m in mods)
+
+    def parameters(self):
+        seen, out = set(), []
+        for m in self.mods:
+            for p in m.parameters():
+                if id(p) not in seen:
+                    seen.add(id(p))
+                    out.append(p)
+        return out
+
+    def release_others(self) -> None:
+        keep = {i for m in self.mods for i in range(m.lo, m.hi)}
+        for i, block in enumerate(self.model.layers):
+            if i not in keep:
+                for p in block.parameters():
+                    p.data = torch.empty(0, dtype=p.dtype, device=p.device)
+                    p.requires_grad_(False)
+
+
+class VirtualPipelineEngine:
+    """One rank = `V` chunks of one data-parallel replica's pipeline."""
+
+    def __init__(self, model, stage: int, n_stages: int, bounds, device, ranks: list[int], links: dict, schedule: str = "interleaved-1f1b",
+                 virtual: int = 2, compute_dtype=torch.bfloat16):
+        if schedule not in SCHEDULES_VIRTUAL:
+            raise ValueError(f"PIPELINE_SCHEDULE {schedule!r}: the multi-chunk engine runs {SCHEDULES_VIRTUAL}")
+        self.P, self.V, self.rank_in_pipe, self.schedule = n_stages, chunks_per_rank(schedule, virtual), stage, schedule
+        self.S = self.P * self.V
+        if len(bounds) != self.S:
+            raise ValueError(f"{len(bounds)} stage bounds for {self.S} virtual stages")
+        self.device, self.dtype, self.cfg = torch.device(device), compute_dtype, model.cfg
+        self.ranks, self.links = list(ranks), links
+        self.mods = []
+        for c in range(self.V):
+            s = stage_of(schedule, self.P, stage, c)
+            lo, hi = bounds[s]
+            self.mods.append(StageModule(model, lo, hi, s == 0, s == self.S - 1))
+        self.module = _Chunks(model, self.mods)
+        self.metrics = {"pipe_fwd_ms": 0.0, "pipe_bwd_ms": 0.0, "pipe_idle_ms": 0.0}
+
+    # -- messages ---------------------------------------------------------------------------------
+    def _alloc_io(self, seq) -> StageIO:
+        d = self.cfg.dim
+        return StageIO(torch.empty((seq.n_joint, d), dtype=self.dtype, device=self.device),
+                       torch.empty((seq.batch, 6, d), dtype=torch.float32, device=self.device),
+                       torch.empty((seq.batch, 2, d), dtype=torch.float32, device=self.device))
+
+    def _incoming(self, kind: str, n: int) -> dict[int, list[tuple[int, int]]]:
+        """Per source rank (index in the pipe): the (micro-batch, my chunk) keys of the messages
+        of `kind` it sends me, in its sending order."""
+        out: dict[int, list[tuple[int, int]]] = {}
+        me = self.rank_in_pipe
+        for src in range(self.P):
+            if src == me:
+                continue
+            keys = []
+            for k, i, c in rank_order(self.schedule, self.P, self.V, n, src):
+                if k != kind:
+                    continue
+                s = stage_of(self.schedule, self.P, src, c)
+                t = s + 1 if kind == "F" else s - 1
+                if not 0 <= t < self.S:
+                    continue
+                r, cc = place_of(self.schedule, self.P, t)
+                if r == me:
+                    keys.append((i, cc))
+            if keys:
+                out[src] = keys
+        return out
+
+    def step(self, micro_batches, loss_fn) -> Tensor | None:
+        n = len(micro_batches)
+        me = self.rank_in_pipe
+        order = rank_order(self.schedule, self.P, self.V, n, me)
+        incoming = {"F": self._incoming("F", n), "B": self._incoming("B", n)}
+        cursor = {(kind, src): 0 for kind in incoming for src in incoming[kind]}
+        source = {(kind, key): src for kind in incoming for src, keys in incoming[kind].items() for key in keys}
+        stash: dict[tuple, tuple] = {}
+        local: dict[tuple, list[Tensor]] = {}
+        saved: dict[tuple[int, int], tuple] = {}
+        sends = []
+        total = None
+
+        def post(kind: str, src: int) -> None:
+            keys = incoming[kind][src]
+            pos = cursor[(kind, src)]
+            if pos >= len(keys):
+                return
+            i, c = keys[pos]
+            cursor[(kind, src)] = pos + 1
+            io = self._alloc_io(micro_batches[i]["seq"])
+            g_src = self.ranks[src]
+            group = self.links[(g_src, self.ranks[me], kind)]
+            works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, t, g_src, group) for t in io.tensors()])
+            stash[(kind, i, c)] = (io, works)
+
+        def take(kind: str, i: int, c: int) -> list[Tensor]:
+            if (kind, i, c) in local:
+                return local.pop((kind, i, c))
+            src = source[(kind, (i, c))]
+            while (kind, i, c) not in stash:
+                post(kind, src)
+            io, works = stash.pop((kind, i, c))
+            post(kind, src)  # the next message of this link transfers while this one is consumed
+            for w in works or []:
+                w.wait()
+            return io.tensors()
+
+        def give(kind: str, i: int, target_stage: int, tensors: list[Tensor]) -> None:
+            r, cc = place_of(self.schedule, self.P, target_stage)
+            if r == me:
+                local[(kind, i, cc)] = [t.detach() for t in tensors]
+                return
+            dst = self.ranks[r]
+            group = self.links[(self.ranks[me], dst, kind)]
+            sends.append(dist.batch_isend_irecv([dist.P2POp(dist.isend, t.detach().contiguous(), dst, group) for t in tensors]))
+
+        for kind, i, c in order:
+            mb, mod = micro_batches[i], self.mods[c]
+            s = stage_of(self.schedule, self.P, me, c)
+            if kind == "F":
+                inp = None
+                if not mod.first:
+                    x, m_, h = take("F", i, c)
+                    inp = StageIO(x.requires_grad_(), m_.requires_grad_(), h.requires_grad_())
+                out = mod.forward(inp, mb.get("img"), mb.get("text"), mb["sigma"], mb["seq"])
+                if mod.last:
+                    loss = loss_fn(out, mb)
+                    total = loss.detach() if total is None else total + loss.detach()
+                    saved[(i, c)] = (inp, loss)
+                else:
+                    give("F", i, s + 1, out.tensors())
+                    saved[(i, c)] = (inp, out)
+            else:
+                inp, out = saved.pop((i, c))
+                if mod.last:
+                    out.backward()
+                else:
+                    grads = take("B", i, c)
+                    pairs = [(t, g) for t, g in zip(out.tensors(), grads) if t.requires_grad]
+                    torch.autograd.backward([t for t, _ in pairs], [g for _, g in pairs])
+                if not mod.first:
+                    give("B", i, s - 1, [t.grad if t.grad is not None else torch.zeros_like(t) for t in inp.tensors()])
+        for works in sends:
+            for w in works or []:
+                w.wait()
+        return total

@@ -278,8 +278,8 @@ def pipeline_worker(k: dict, cfg, rank: int, world: int, device, run_dir: Path) 
                                                      k["PIPELINE_SPLIT"], named), 0, 1
     else:
         stages = int(k.get("PIPELINE_STAGES", 0) or 0) or world
-        sched = k["PIPELINE_SCHEDULE"] if k["PIPELINE_SCHEDULE"] in ("gpipe", "1f1b") else "1f1b"
-        trainer = PipelineTrainer(model, cfg, device, stages, micro, sched, k["PIPELINE_SPLIT"], named)
+        sched = k["PIPELINE_SCHEDULE"]
+        trainer = PipelineTrainer(model, cfg, device, stages, micro, sched, k["PIPELINE_SPLIT"], named, int(k.get("PIPELINE_VIRTUAL", 2)))
         replica, replicas = trainer.replica, trainer.replicas
     data = build_dataset(k, arch.text_dim, arch.latent_channels)
     writer = build_writer(k["LOGGER"], run_dir, k["METRICS_LEVEL"], k["PROJECT"], k["RUN_NAME"], rank=rank)

@@ -77,6 +77,15 @@ def cross_checks(k: dict) -> list[str]:
         out.append(f"PARALLEL={par!r} needs at least two DEVICES (stages)")
     if par == "threaded" and k.get("PIPELINE_SCHEDULE") not in ("gpipe", "async", "1f1b"):
         out.append("threaded pipeline schedules are gpipe | async")
+    if par == "pipeline":
+        sched = k.get("PIPELINE_SCHEDULE", "1f1b")
+        if sched in ("interleaved-zb", "dualpipe-v", "async"):
+            out.append(f"PIPELINE_SCHEDULE={sched!r} is not offered by the process-group pipeline: "
+                       "gpipe | 1f1b | looped-bfs | interleaved-1f1b | zbv")
+        stages = max(1, n_dev // max(1, int(k.get("PIPELINE_REPLICAS", 1) or 1)))
+        if sched == "interleaved-1f1b" and k.get("MICROBATCHES", 1) % stages:
+            out.append(f"PIPELINE_SCHEDULE='interleaved-1f1b' runs MICROBATCHES in groups of the {stages} stages: "
+                       f"{k.get('MICROBATCHES')} is not a multiple")
     if k.get("ALGO") == "full" and k.get("BASE_PRECISION") in ("int8", "fp8"):
         out.append("ALGO='full' trains the base weights: BASE_PRECISION must be auto | compute | fp8_compute | mxfp8")
     if k.get("GRAD_ACC", 1) < 1:

@@ -17,23 +17,32 @@ import torch.distributed as dist
 from ..diffusion import TIMESTEPS, TokenNormalizer, noise_latents, token_loss
 from ..optim import Bundle, build_optimizer
 from ..parallel.pipeline import PipelineEngine, pp_dp_groups, stage_bounds
+from ..parallel.pipeline_virtual import SCHEDULES_VIRTUAL, VirtualPipelineEngine, chunks_per_rank, make_links
 from ..utils.seeds import seed_of
 
 
 class PipelineTrainer:
     def __init__(self, model, cfg, device, n_stages: int, micro_batches: int, schedule: str = "1f1b", split="flops",
-                 named_trainable=None):
+                 named_trainable=None, virtual: int = 2):
         self.model, self.cfg, self.device = model, cfg, torch.device(device)
         self.world, self.rank = dist.get_world_size(), dist.get_rank()
         self.pp_group, self.dp_group, self.stage, self.replica = pp_dp_groups(self.world, n_stages)
         self.n_stages, self.micro = n_stages, micro_batches
         self.replicas = self.world // n_stages
-        bounds = stage_bounds(model.cfg, n_stages, split)
         base = self.replica * n_stages
-        self.engine = PipelineEngine(model, self.stage, n_stages, bounds, device, None,
-                                     prev_rank=base + self.stage - 1 if self.stage > 0 else None,
-                                     next_rank=base + self.stage + 1 if self.stage < n_stages - 1 else None, schedule=schedule,
-                                     compute_dtype=model.compute_dtype())
+        if schedule in SCHEDULES_VIRTUAL:  # several chunks per rank
+            chunks = chunks_per_rank(schedule, virtual)
+            bounds = stage_bounds(model.cfg, n_stages * chunks, split)
+            rings = [[r * n_stages + s for s in range(n_stages)] for r in range(self.replicas)]
+            links = make_links(rings)
+            self.engine = VirtualPipelineEngine(model, self.stage, n_stages, bounds, device, rings[self.replica], links, schedule,
+                                                chunks, compute_dtype=model.compute_dtype())
+        else:
+            bounds = stage_bounds(model.cfg, n_stages, split)
+            self.engine = PipelineEngine(model, self.stage, n_stages, bounds, device, None,
+                                         prev_rank=base + self.stage - 1 if self.stage > 0 else None,
+                                         next_rank=base + self.stage + 1 if self.stage < n_stages - 1 else None, schedule=schedule,
+                                         compute_dtype=model.compute_dtype())
         self.engine.module.release_others()
         own = {id(p) for p in self.engine.module.parameters()}
         named = [(n, p) for n, p in (named_trainable or model.named_parameters()) if id(p) in own and p.requires_grad]

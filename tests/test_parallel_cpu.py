@@ -47,6 +47,46 @@ def test_pipeline_times_data_parallel(tmp_path):
         assert r["worst_grad_err"] < 1e-4, (r["worst"], r["worst_grad_err"])
 
 
+@pytest.mark.parametrize("world,schedule,micro", [(2, "interleaved-1f1b", 4), (4, "zbv", 3), (2, "looped-bfs", 3)])
+def test_multi_chunk_pipeline_schedules_match_gradient_accumulation(tmp_path, world, schedule, micro):
+    """Two chunks per rank (four virtual stages of one block each; x 2 replicas for zbv): loss
+    and every stage's gradients equal one process accumulating the same micro-batches."""
+    res = selftest.spawn_results(selftest.pipeline_worker, world, str(tmp_path), (2, schedule, micro), timeout_s=240)
+    assert {r["stage"] for r in res} == {0, 1}
+    for r in res:
+        assert r["n_grads"] > 5
+        assert abs(r["loss"] - r["ref_loss"]) / abs(r["ref_loss"]) < 1e-4
+        assert r["worst_grad_err"] < 1e-4, (r["worst"], r["worst_grad_err"])
+
+
+def test_multi_chunk_orders_are_complete_and_respect_dependencies():
+    from kohakumosstrainer_b200.parallel.pipeline_virtual import chunks_per_rank, rank_order, stage_of
+
+    for schedule in ("looped-bfs", "interleaved-1f1b", "zbv"):
+        for P in (1, 2, 3, 4):
+            for n in ((P, 3 * P) if schedule == "interleaved-1f1b" else (1, 3, 8)):
+                V = chunks_per_rank(schedule, 2)
+                S = P * V
+                orders = [rank_order(schedule, P, V, n, r) for r in range(P)]
+                pos, fwd, bwd = [0] * P, set(), set()
+                while any(pos[r] < len(orders[r]) for r in range(P)):
+                    moved = False
+                    for r in range(P):
+                        if pos[r] == len(orders[r]):
+                            continue
+                        kind, i, c = orders[r][pos[r]]
+                        s = stage_of(schedule, P, r, c)
+                        ready = (s == 0 or (i, s - 1) in fwd) if kind == "F" else ((i, s) in fwd and (s == S - 1 or (i, s + 1) in bwd))
+                        if ready:
+                            (fwd if kind == "F" else bwd).add((i, s))
+                            pos[r] += 1
+                            moved = True
+                    assert moved, (schedule, P, n, pos)      # some rank can always run its next operation
+                assert len(fwd) == len(bwd) == n * S
+    with pytest.raises(ValueError, match="multiple"):
+        rank_order("interleaved-1f1b", 2, 2, 3, 0)
+
+
 def test_one_f_one_b_order_keeps_at_most_stages_in_flight():
     from kohakumosstrainer_b200.parallel.pipeline import PipelineEngine
 
