@@ -347,13 +347,15 @@ void cast_fp8(const Tensor& x, const Tensor& qscale, Tensor q) {
                                 q.scalar_type() == at::kFloat8_e5m2, cur_stream()));
 }
 
-std::tuple<Tensor, Tensor> quantize_fp8_rows(const Tensor& x) {
+// Per-row fp8 quantisation in one pass over the rows: (q, scales). `both` returns fp32 [2, rows] =
+// {dequant, quant} scales, otherwise fp32 [rows] dequant scales.
+std::tuple<Tensor, Tensor> quantize_fp8_rows(const Tensor& x, bool e5m2, bool both) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "quantize_fp8_rows: bf16 rows");
-  Tensor q = at::empty({x.size(0), x.size(1)}, x.options().dtype(at::kFloat8_e4m3fn));
-  Tensor rs = at::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  Tensor q = at::empty({x.size(0), x.size(1)}, x.options().dtype(e5m2 ? at::kFloat8_e5m2 : at::kFloat8_e4m3fn));
+  Tensor rs = both ? at::empty({2, x.size(0)}, x.options().dtype(at::kFloat)) : at::empty({x.size(0)}, x.options().dtype(at::kFloat));
   KM_CHECK_CUDA(kmoss::fp8_cast_rows(x.data_ptr(), x.stride(0), (int)x.size(0), (int)x.size(1), q.data_ptr(), q.stride(0),
-                                     rs.data_ptr<float>(), cur_stream()));
+                                     rs.data_ptr<float>(), e5m2, both, cur_stream()));
   return {q, rs};
 }
 
@@ -620,7 +622,7 @@ TORCH_LIBRARY(kmoss_b200, m) {
         &token_mse_bwd);
   m.def("quantize_fp8_tensor(Tensor x, bool e5m2) -> (Tensor, Tensor)", &quantize_fp8_tensor);
   m.def("cast_fp8(Tensor x, Tensor qscale, Tensor(a!) q) -> ()", &cast_fp8);
-  m.def("quantize_fp8_rows(Tensor x) -> (Tensor, Tensor)", &quantize_fp8_rows);
+  m.def("quantize_fp8_rows(Tensor x, bool e5m2=False, bool both=False) -> (Tensor, Tensor)", &quantize_fp8_rows);
   m.def("group_hadamard(Tensor x, int group) -> Tensor", &group_hadamard);
   m.def("quantize_int8_rows(Tensor x, int group) -> (Tensor, Tensor)", &quantize_int8_rows);
   m.def("cast_int8_bf16(Tensor q, Tensor(a!) y) -> ()", &cast_int8_bf16);

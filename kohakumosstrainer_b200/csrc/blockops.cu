@@ -503,13 +503,17 @@ __global__ void cast_fp8_kernel(const __nv_bfloat16* x, long n, const float* qsc
   }
 }
 
-// One warp per row: row amax -> scale -> e4m3 row; row_scale[r] = amax / 448.
+// One warp per row: row amax -> scale -> fp8 row. row_scale[r] = amax / fmax (dequant) and, when the
+// buffer holds two rows of scales, row_scale[rows + r] = fmax / amax (quant). The second read of the
+// row comes from L1 / L2: a row is at most a few tens of KB.
+template <bool E5M2>
 __global__ void __launch_bounds__(32 * ROWS_PER_BLOCK)
-cast_fp8_rows_kernel(const __nv_bfloat16* x, long ldx, int rows, int dim, uint8_t* q, long ldq, float* row_scale) {
+cast_fp8_rows_kernel(const __nv_bfloat16* x, long ldx, int rows, int dim, uint8_t* q, long ldq, float* row_scale, int with_inverse) {
   const int row = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   const __nv_bfloat16* xr = x + (size_t)row * ldx;
+  constexpr float FMAX = E5M2 ? 57344.f : 448.f;
   float m = 0.f;
   for (int i = lane * 8; i < dim; i += 256) {
     float v[8];
@@ -518,15 +522,24 @@ cast_fp8_rows_kernel(const __nv_bfloat16* x, long ldx, int rows, int dim, uint8_
     for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[j]));
   }
   m = fmaxf(warp_max(m), 1e-12f);
-  const float s = 448.f / m;
-  if (lane == 0) row_scale[row] = m / 448.f;
+  const float s = FMAX / m;
+  if (lane == 0) {
+    row_scale[row] = m / FMAX;
+    if (with_inverse) row_scale[rows + row] = s;
+  }
   for (int i = lane * 8; i < dim; i += 256) {
     float v[8];
     load8(xr + i, v);
-    __nv_fp8x4_e4m3 lo(make_float4(v[0] * s, v[1] * s, v[2] * s, v[3] * s));
-    __nv_fp8x4_e4m3 hi(make_float4(v[4] * s, v[5] * s, v[6] * s, v[7] * s));
     uint2 o;
-    o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+    if constexpr (E5M2) {
+      __nv_fp8x4_e5m2 lo(make_float4(v[0] * s, v[1] * s, v[2] * s, v[3] * s));
+      __nv_fp8x4_e5m2 hi(make_float4(v[4] * s, v[5] * s, v[6] * s, v[7] * s));
+      o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+    } else {
+      __nv_fp8x4_e4m3 lo(make_float4(v[0] * s, v[1] * s, v[2] * s, v[3] * s));
+      __nv_fp8x4_e4m3 hi(make_float4(v[4] * s, v[5] * s, v[6] * s, v[7] * s));
+      o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+    }
     *reinterpret_cast<uint2*>(q + (size_t)row * ldq + i) = o;
   }
 }
@@ -649,11 +662,15 @@ cudaError_t fp8_cast(const void* x, long n, const float* qscale, void* q, int e5
   else cast_fp8_kernel<false><<<g, 256, 0, s>>>((const __nv_bfloat16*)x, n, qscale, (uint8_t*)q);
   return cudaGetLastError();
 }
-cudaError_t fp8_cast_rows(const void* x, long ldx, int rows, int dim, void* q, long ldq, float* row_scale, cudaStream_t s) {
+cudaError_t fp8_cast_rows(const void* x, long ldx, int rows, int dim, void* q, long ldq, float* row_scale, bool e5m2,
+                          bool with_inverse, cudaStream_t s) {
   if (rows <= 0) return cudaSuccess;
   if (dim % 8) return cudaErrorInvalidValue;
-  cast_fp8_rows_kernel<<<(rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK, 32 * ROWS_PER_BLOCK, 0, s>>>(
-      (const __nv_bfloat16*)x, ldx, rows, dim, (uint8_t*)q, ldq, row_scale);
+  const int grid = (rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
+  if (e5m2) cast_fp8_rows_kernel<true><<<grid, 32 * ROWS_PER_BLOCK, 0, s>>>((const __nv_bfloat16*)x, ldx, rows, dim, (uint8_t*)q, ldq,
+                                                                            row_scale, with_inverse);
+  else cast_fp8_rows_kernel<false><<<grid, 32 * ROWS_PER_BLOCK, 0, s>>>((const __nv_bfloat16*)x, ldx, rows, dim, (uint8_t*)q, ldq,
+                                                                        row_scale, with_inverse);
   return cudaGetLastError();
 }
 

@@ -96,6 +96,8 @@ cudaError_t token_mse_bwd(const TokenMseArgs& a, const float* dloss, void* dpred
 cudaError_t fp8_amax(const void* x, long n, float* amax, cudaStream_t s);
 cudaError_t fp8_scale_from_amax(const float* amax, float fmax, float* scale_out, cudaStream_t s);
 cudaError_t fp8_cast(const void* x, long n, const float* qscale, void* q, int e5m2, cudaStream_t s);
-cudaError_t fp8_cast_rows(const void* x, long ldx, int rows, int dim, void* q, long ldq, float* row_scale, cudaStream_t s);
+// row_scale: fp32 [rows] dequant scales, or [2, rows] = {dequant, quant} with `with_inverse`
+cudaError_t fp8_cast_rows(const void* x, long ldx, int rows, int dim, void* q, long ldq, float* row_scale, bool e5m2,
+                          bool with_inverse, cudaStream_t s);
 
 }  // namespace kmoss

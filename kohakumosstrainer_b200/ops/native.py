@@ -175,8 +175,10 @@ def quantize_fp8(x: Tensor, dtype: torch.dtype = torch.float8_e4m3fn) -> tuple[T
     return load().quantize_fp8_tensor(x.contiguous(), dtype == torch.float8_e5m2)
 
 
-def quantize_fp8_rows(x: Tensor) -> tuple[Tensor, Tensor]:
-    return load().quantize_fp8_rows(x)
+def quantize_fp8_rows(x: Tensor, dtype: torch.dtype = torch.float8_e4m3fn, both: bool = False) -> tuple[Tensor, Tensor]:
+    """Per-row dynamic quantisation in one pass -> (q, scales): fp32 `[rows]` dequant scales, or
+    `[2, rows]` = {dequant, quant} with `both`."""
+    return load().quantize_fp8_rows(x, dtype == torch.float8_e5m2, both)
 
 
 def rope_table(pos: Tensor, bands: Tensor) -> Tensor:

@@ -68,8 +68,20 @@ class LoraPack:
         self.R = down.shape[0]
 
 
+# fp8 activations are scaled per row (token) by default: one pass computes the row maximum and writes
+# the codes (the row is re-read from cache), where a per-tensor scale needs a full pass for the maximum
+# before the cast; it is also the finer scale. False selects the per-tensor path.
+FP8_ACT_ROWS = True
+
+
+def _rows(xs) -> bool:
+    return xs is not None and xs.dim() == 2
+
+
 def _main_gemm(x, xq, xs, wp: WeightPack, **kw) -> Tensor:
     if wp.kind == "fp8":
+        if _rows(xs):
+            return native.gemm(xq, wp.w, row_scale=xs[0], col_scale=wp.col_scale, **kw)
         return native.gemm(xq, wp.w, scale_a=xs[:1], col_scale=wp.col_scale, **kw)
     if wp.fsdp is not None:  # sharded weight: the GEMM gathers it from the peers while it computes
         full, gather = wp.fsdp.gather_args()
@@ -89,10 +101,13 @@ class _LinearCore:
     def forward(x, wp: WeightPack, bias, lp: LoraPack | None, **epi):
         xq = xs = None
         if wp.kind == "fp8":
-            xq, xs = native.quantize_fp8(x, E4M3)
+            xq, xs = native.quantize_fp8_rows(x, E4M3, both=True) if FP8_ACT_ROWS else native.quantize_fp8(x, E4M3)
         t = None
         if lp is not None:
-            t = native.gemm(x, lp.down, col_scale=lp.t_scale, scale_a=None if xs is None else xs[1:2])
+            if _rows(xs):  # the bypass shares the accumulator the epilogue rescales per row: pre-divide per row
+                t = native.gemm(x, lp.down, col_scale=lp.t_scale, row_scale=xs[1], splits=None)
+            else:
+                t = native.gemm(x, lp.down, col_scale=lp.t_scale, scale_a=None if xs is None else xs[1:2], splits=None)
         out = _main_gemm(x, xq, xs, wp, bias=bias, t=t, u=None if lp is None else lp.up, **epi)
         return out, t, xs
 
@@ -104,16 +119,16 @@ class _LinearCore:
         fp8 = wp.kind == "fp8"
         dq = ds = None
         if fp8 and need_dx:
-            if not wp.per_tensor:
-                d_main = (d.float() * wp.col_scale).to(BF16)  # row recipe: scale varies along K
-                dq, ds = native.quantize_fp8(d_main, E5M2)
-            else:
-                dq, ds = native.quantize_fp8(d, E5M2)
+            d_main = d if wp.per_tensor else (d.float() * wp.col_scale).to(BF16)  # row recipe: scale varies along K
+            dq, ds = native.quantize_fp8_rows(d_main, E5M2, both=True) if FP8_ACT_ROWS else native.quantize_fp8(d_main, E5M2)
         if lp is not None:
             # t2 = (d up) * s: gradient w.r.t. the rank activations, [M, R]
-            t2 = native.gemm(d, lp.up, b_mn=True, col_scale=lp.plain_scale)
+            t2 = native.gemm(d, lp.up, b_mn=True, col_scale=lp.plain_scale, splits=None)
             # d up = d^T T_plain, where T_plain = t * (s_x * s_w) under fp8
-            if fp8:
+            if fp8 and _rows(xs):  # the saved t is per-row scaled: undo it over [M, R] before the reduction over rows
+                t_plain = (t.float() * xs[0].unsqueeze(1)).to(BF16)
+                d_up = native.gemm(d, t_plain, a_mn=True, b_mn=True, out_dtype=torch.float32, splits=None, col_scale=lp.ratio)
+            elif fp8:
                 d_up = native.gemm(d, t, a_mn=True, b_mn=True, out_dtype=torch.float32, splits=None,
                                    scale_a=xs[:1], col_scale=lp.ratio)
             else:
@@ -130,9 +145,15 @@ class _LinearCore:
                 if lp is not None:
                     # keep the bypass out of the fp8 rescale: divide it by s_d (* s_w). t2 already holds (d up) * s,
                     # so this is an element-wise pass over [M, R] instead of another product over the wide d
-                    inv = ds[1:2] if sb is None else ds[1:2] * wp.scale[1:2]
+                    if _rows(ds):
+                        inv = ds[1].unsqueeze(1) if sb is None else ds[1].unsqueeze(1) * wp.scale[1:2]
+                    else:
+                        inv = ds[1:2] if sb is None else ds[1:2] * wp.scale[1:2]
                     tb = (t2.float() * inv).to(BF16)
-                dx = native.gemm(dq, wp.w, b_mn=True, scale_a=ds[:1], scale_b=sb, t=tb, u=ub)
+                if _rows(ds):
+                    dx = native.gemm(dq, wp.w, b_mn=True, row_scale=ds[0], scale_b=sb, t=tb, u=ub)
+                else:
+                    dx = native.gemm(dq, wp.w, b_mn=True, scale_a=ds[:1], scale_b=sb, t=tb, u=ub)
             elif wp.fsdp is not None:
                 full, gather = wp.fsdp.gather_args()  # resharded after forward: gather again, fused into dgrad
                 dx = native.gemm(d, full, b_mn=True, t=tb, u=ub, gather=gather)

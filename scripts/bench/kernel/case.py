@@ -9,7 +9,7 @@ around each launch, L2 flushed between launches, median), algorithmic FLOPs and 
 fractions of the measured peaks (`MEASURED_PEAKS.json` when present).
 
 Cases: gemm_bf16, gemm_fp8, gemm_fp8_dgrad, gemm_wgrad, gemm_situ, gemm_qkrope, gemm_fp8_situ, gemm_fp8_qkrope, gemm_fp8_residual, attn_fwd,
-attn_bwd, rms_norm_mod, rms_norm_mod_bwd, situ, quant_fp8, token_mse, adamw; the skinny products of a
+attn_bwd, rms_norm_mod, rms_norm_mod_bwd, situ, quant_fp8, quant_fp8_rows, token_mse, adamw; the skinny products of a
 rank-8 adapter over a `--width`-wide activation: lora_down (x A^T), lora_dt (d up), lora_dup (d^T t),
 lora_ddown (x^T t2), each with `--splits` (0 = the library's choice).
 """
@@ -158,7 +158,7 @@ def build(op: str, tokens: int, width: int = 3072, splits: int = 0):
             o.backward(do, retain_graph=True)
 
         return bwd, 2.5 * flops, 2 * 8 * T * H * 128
-    if op in ("rms_norm_mod", "rms_norm_mod_bwd", "situ", "quant_fp8", "token_mse"):
+    if op in ("rms_norm_mod", "rms_norm_mod_bwd", "situ", "quant_fp8", "quant_fp8_rows", "token_mse"):
         from kohakumosstrainer_b200.ops import native_ops
 
         ops = native_ops.NativeOps()
@@ -186,6 +186,8 @@ def build(op: str, tokens: int, width: int = 3072, splits: int = 0):
                 return (lambda: ops.situ_glu(ug)), 0.0, 2 * 3 * M * F
         if op == "quant_fp8":
             return (lambda: native.quantize_fp8(x.detach())), 0.0, rows * D * (2 + 2 + 1)
+        if op == "quant_fp8_rows":
+            return (lambda: native.quantize_fp8_rows(x.detach(), both=True)), 0.0, rows * D * (2 + 1)
         pred, target = bf16(rows, 128), torch.randn(rows, 128, device="cuda")
         wt = torch.ones(B, device="cuda")
         with torch.no_grad():

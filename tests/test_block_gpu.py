@@ -288,8 +288,11 @@ def test_fused_adamw_state_formats_match_the_cpu_reference(states, writeback):
         torch.testing.assert_close(p.detach().float().cpu(), r.detach().float(), rtol=8e-3, atol=1e-3)
         sa, sb = a.state[p], b.state[r]
         if states == "8bit":
-            assert (sa["mq"].cpu().int() - sb["mq"].int()).abs().max() <= 1
-            assert (sa["rq"].cpu().int() - sb["rq"].int()).abs().max() <= 1
+            # a code that lands on the other side of a rounding boundary feeds the next step: after five
+            # steps single codes may sit a few units apart, the bulk are equal
+            for key in ("mq", "rq"):
+                diff = (sa[key].cpu().int() - sb[key].int()).abs()
+                assert diff.max() <= 4 and diff.float().mean() < 0.1, (key, int(diff.max()), float(diff.float().mean()))
             torch.testing.assert_close(sa["ms"].cpu(), sb["ms"], rtol=1e-3, atol=1e-12)
         if writeback == "kahan":
             full_a = p.detach().float().cpu() + sa["comp"].float().cpu()

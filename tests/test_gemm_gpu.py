@@ -68,6 +68,12 @@ def test_quantize_matches_torch_cast():
     torch.testing.assert_close(rs, ramax / 448.0)
     refr = (x.float() * (448.0 / ramax)[:, None]).to(torch.float8_e4m3fn)
     assert (qr.view(torch.uint8) != refr.view(torch.uint8)).float().mean() < 1e-3
+    q5, rs5 = native.quantize_fp8_rows(x, torch.float8_e5m2, both=True)
+    assert q5.dtype == torch.float8_e5m2 and rs5.shape == (2, 333)
+    torch.testing.assert_close(rs5[0], ramax / 57344.0)
+    torch.testing.assert_close(rs5[1], 57344.0 / ramax)
+    ref5 = (x.float() * (57344.0 / ramax)[:, None]).to(torch.float8_e5m2)
+    assert (q5.view(torch.uint8) != ref5.view(torch.uint8)).float().mean() < 1e-3
 
 
 def test_linear_epilogue_scales_bias_gate_residual():
