@@ -126,7 +126,7 @@ class _LinearCore:
             t2 = native.gemm(d, lp.up, b_mn=True, col_scale=lp.plain_scale, splits=None)
             # d up = d^T T_plain, where T_plain = t * (s_x * s_w) under fp8
             if fp8 and _rows(xs):  # the saved t is per-row scaled: undo it over [M, R] before the reduction over rows
-                t_plain = (t.float() * xs[0].unsqueeze(1)).to(BF16)
+                t_plain = (t * xs[0].unsqueeze(1)).to(BF16)  # bf16 x fp32 promotes: the product is taken in fp32
                 d_up = native.gemm(d, t_plain, a_mn=True, b_mn=True, out_dtype=torch.float32, splits=None, col_scale=lp.ratio)
             elif fp8:
                 d_up = native.gemm(d, t, a_mn=True, b_mn=True, out_dtype=torch.float32, splits=None,
@@ -149,7 +149,7 @@ class _LinearCore:
                         inv = ds[1].unsqueeze(1) if sb is None else ds[1].unsqueeze(1) * wp.scale[1:2]
                     else:
                         inv = ds[1:2] if sb is None else ds[1:2] * wp.scale[1:2]
-                    tb = (t2.float() * inv).to(BF16)
+                    tb = (t2 * inv).to(BF16)
                 if _rows(ds):
                     dx = native.gemm(dq, wp.w, b_mn=True, row_scale=ds[0], scale_b=sb, t=tb, u=ub)
                 else:

@@ -66,7 +66,11 @@ class FiniteGuard:
             path.parent.mkdir(parents=True, exist_ok=True)
             payload = {"step": step, "loss": trainer.bundle.last_loss if trainer else None,
                        "batches": [{"hw": hb.hw, "text_len": hb.text_len, "index": hb.index} for hb in (host_batches or [])],
-                       "rng": trainer.step_fn.rng_state() if trainer else None}
+                       "rng": trainer.step_fn.rng_state() if trainer else None,
+                       # the trained values at the failing step (adapters, or the trainable base in a full finetune when small)
+                       "trainable": ({n: p.detach().cpu() for n, p in trainer.named_trainable()}
+                                     if trainer is not None and hasattr(trainer, "named_trainable")
+                                     and sum(p.numel() for _, p in trainer.named_trainable()) < 2**28 else None)}
             torch.save(payload, path)
             raise RuntimeError(f"{self.bad} consecutive non-finite steps; repro written to {path}")
 
@@ -298,3 +302,104 @@ class TransferCounters:
 
     def row(self) -> dict:
         return {"xfer/h2d_mb": round(self.h2d / 1e6, 2), "xfer/d2h_mb": round(self.d2h / 1e6, 2)}
+
+
+class StackSampler:
+    """Wall-time attribution by stack sampling (`src/kohakumoss/training/callbacks/sampler.py`):
+    a daemon thread samples every thread's Python stack at a fixed interval and charges the
+    sample to the first category whose (module prefix, function names) matches a frame, innermost
+    first; unmatched samples go to `other:<module>.<function>` of the innermost frame. Native
+    code is charged to the Python frame that called it. `report()` returns seconds per category."""
+
+    CATEGORIES: tuple = (
+        ("extension_build", "kohakumosstrainer_b200.csrc.build", None),
+        ("extension_load", "kohakumosstrainer_b200.ops.native", frozenset({"load"})),
+        ("data_wait", "kohakumosstrainer_b200.data.loader", None),
+        ("data_plan", "kohakumosstrainer_b200.data.planner", None),
+        ("encode", "kohakumosstrainer_b200.training.encode_feed", None),
+        ("offload_wait", "kohakumosstrainer_b200.memory.offload", frozenset({"wait", "_wait", "repoint", "prefetch"})),
+        ("checkpoint_io", "kohakumosstrainer_b200.training.checkpoint", None),
+        ("collective", "torch.distributed", None),
+        ("optimizer", "kohakumosstrainer_b200.optim", None),
+        ("autograd", "torch.autograd", None),
+        ("forward", "kohakumosstrainer_b200.models", None),
+        ("sampling", "kohakumosstrainer_b200.diffusion.sampling", None),
+    )
+
+    def __init__(self, interval: float = 0.005, categories: tuple | None = None):
+        import threading
+        from collections import Counter
+
+        self.interval = float(interval)
+        self.categories = tuple(categories) if categories is not None else self.CATEGORIES
+        self.counts: Counter = Counter()
+        self.samples = 0
+        self._known: dict[tuple[str, str], int] = {}
+        self._stop = threading.Event()
+        self._thread: threading.Thread | None = None
+        self.elapsed = 0.0
+        self._t0 = 0.0
+
+    def _category(self, module: str, func: str) -> int:
+        key = (module, func)
+        hit = self._known.get(key)
+        if hit is None:
+            hit = -1
+            for i, (_, prefix, names) in enumerate(self.categories):
+                if module.startswith(prefix) and (names is None or func in names):
+                    hit = i
+                    break
+            self._known[key] = hit
+        return hit
+
+    def _charge(self, frame) -> str:
+        inner = None
+        while frame is not None:
+            module = frame.f_globals.get("__name__", "")
+            func = frame.f_code.co_name
+            if inner is None:
+                inner = f"other:{module}.{func}"
+            c = self._category(module, func)
+            if c >= 0:
+                return self.categories[c][0]
+            frame = frame.f_back
+        return inner or "other:?"
+
+    def _run(self) -> None:
+        import sys
+        import threading
+
+        me = threading.get_ident()
+        while not self._stop.wait(self.interval):
+            for tid, frame in sys._current_frames().items():
+                if tid != me:
+                    self.counts[self._charge(frame)] += 1
+            self.samples += 1
+
+    def start(self) -> "StackSampler":
+        import threading
+
+        if self._thread is None:
+            import time
+
+            self._stop.clear()
+            self._t0 = time.perf_counter()
+            self._thread = threading.Thread(target=self._run, name="stack-sampler", daemon=True)
+            self._thread.start()
+        return self
+
+    def stop(self) -> None:
+        if self._thread is not None:
+            import time
+
+            self._stop.set()
+            self._thread.join(timeout=2.0)
+            self._thread = None
+            self.elapsed += time.perf_counter() - self._t0
+
+    def report(self, top: int = 12) -> dict:
+        # a busy interpreter delays the sampler, so a sample stands for elapsed / samples seconds, not for the interval
+        per = self.elapsed / self.samples if self.samples and self.elapsed else self.interval
+        rows = {f"breakdown/stack_{name.replace(':', '_')}_s": n * per for name, n in self.counts.most_common(top)}
+        rows["breakdown/stack_samples"] = self.samples
+        return rows

@@ -48,7 +48,8 @@ def trainer_config(k: dict):
         alpha=float(k["ALPHA"]), algo_kwargs=dict(k["ALGO_KWARGS"]), adapter_mode=k["ADAPTER_MODE"], base_precision=base,
         fp8_recipe=k["FP8_RECIPE"], precision="bf16" if k["PRECISION"] in ("auto", "bf16") else k["PRECISION"],
         optimizer=k["OPTIMIZER"], optimizer_kwargs=dict(k["OPTIMIZER_KWARGS"]), lr=float(k["LR"]), betas=tuple(k["BETAS"]),
-        eps=float(k["EPS"]), weight_decay=float(k["WEIGHT_DECAY"]), wd_rules=k["WD_RULES"], schedule=dict(k["SCHEDULE"]),
+        eps=float(k["EPS"]), weight_decay=float(k["WEIGHT_DECAY"]), wd_rules=k["WD_RULES"], wd_target=k.get("WD_TARGET", "zero"),
+        outlier_decay=dict(k.get("OUTLIER_DECAY") or {}), schedule=dict(k["SCHEDULE"]),
         grad_clip=float(k["GRAD_CLIP"]), step_sync=k["STEP_SYNC"], ema=float(k["EMA"]), steps=int(k["STEPS"]),
         grad_acc=int(k["GRAD_ACC"]), checkpoint=k["CHECKPOINT"], timestep=k["TIMESTEP"], timestep_kwargs=dict(k["TIMESTEP_KWARGS"]),
         loss=k["LOSS"], weighting=k["WEIGHTING"], seed=int(k["SEED"]), kernels=dict(k["KERNELS"]), parallel=k["PARALLEL"],

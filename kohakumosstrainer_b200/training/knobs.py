@@ -66,7 +66,9 @@ def cross_checks(k: dict) -> list[str]:
     out = []
     from .extras import distill_problems, stream_loss_problems
 
-    out += stream_loss_problems(k) + distill_problems(k)
+    from ..optim.regularizers import regularizer_problems
+
+    out += stream_loss_problems(k) + distill_problems(k) + regularizer_problems(k)
     n_dev = len(k.get("DEVICES") or (0,))
     par = k.get("PARALLEL", "none")
     if par == "none" and n_dev > 1:

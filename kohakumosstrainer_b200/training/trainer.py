@@ -23,6 +23,7 @@ from ..models.build import resolve_arch
 from ..logging.phases import phase
 from ..models.runners import build_runner
 from ..optim import Bundle, ConstantEMA, build_optimizer, build_scaler
+from ..optim.regularizers import OutlierDecay, StartAnchors
 from ..quant import apply_base_precision
 from .step import DeviceBatcher, TrainStep
 
@@ -47,6 +48,8 @@ class TrainerConfig:
     eps: float = 1e-8
     weight_decay: float = 0.01
     wd_rules: str = "moss"
+    wd_target: str = "zero"            # zero | start (decay towards the weights the run started from)
+    outlier_decay: dict = field(default_factory=dict)   # OUTLIER_DECAY: {"rate", "cap", "cap_start", "cap_anneal", "warmup", "targets", "exclude", "include_1d"}
     schedule: dict = field(default_factory=lambda: {"mode": "cosine", "warmup": 100, "end": -1})
     grad_clip: float = 1.0
     step_sync: str = "step"
@@ -157,6 +160,21 @@ class Trainer:
         if self.fsdp is not None and hasattr(opt, "shard_gather"):
             opt.shard_gather = self.fsdp.gather_update
         self.ema = ConstantEMA(named, (cfg.ema,)) if cfg.ema > 0 else None
+        self._named = named
+        self.regularizers = []
+        if cfg.wd_target == "start":
+            self.regularizers.append(StartAnchors(opt))
+        if cfg.outlier_decay and float(cfg.outlier_decay.get("rate", 0)) > 0:
+            self.regularizers.append(OutlierDecay(named, opt, cfg.outlier_decay))
+        if self.regularizers:
+            inner = post_step
+
+            def post_step():
+                if inner is not None:
+                    inner()
+                for reg in self.regularizers:
+                    reg.apply(self.bundle.last_skip)
+
         self.bundle = Bundle(opt, self.params, cfg.steps, cfg.schedule, cfg.grad_clip, cfg.step_sync,
                              reduce_flags=reduce_flags, ema=self.ema, finish_grads=finish, norm_params=norm_params,
                              extra_sumsq=extra_sumsq, post_step=post_step,
@@ -178,6 +196,10 @@ class Trainer:
         self.batcher = DeviceBatcher(self.device, torch.float32, dtype)
         self.tokens_seen = 0
         self.samples_seen = 0
+
+    def named_trainable(self):
+        """(name, parameter) of everything the optimiser steps on this rank."""
+        return list(self._named)
 
     @contextlib.contextmanager
     def averaged_weights(self):

@@ -387,3 +387,58 @@ def test_adamw_8bit_states_track_fp32_states_and_stochastic_rounding_is_unbiased
     v = torch.full((20000,), 1.0 + 2.0**-9)           # a quarter of the way between two bf16 values (ulp 2^-7)
     up = torch.stack([(stochastic_bf16(v, seed).float() > 1.0).float().mean() for seed in range(8)]).mean()
     assert abs(float(up) - 0.25) < 0.02
+
+
+def test_start_anchors_turn_decay_into_a_pull_towards_the_start_and_outlier_decay_caps_excess():
+    from kohakumosstrainer_b200.optim.regularizers import OutlierDecay, StartAnchors, regularizer_problems
+
+    torch.manual_seed(0)
+    w = torch.nn.Parameter(torch.randn(16, 16))
+    start = w.detach().clone()
+    opt = torch.optim.SGD([w], lr=0.1, weight_decay=0.0)
+    opt.param_groups[0]["weight_decay"] = 0.5          # the decoupled-decay coefficient the anchors mirror
+    anchors = StartAnchors(opt)
+    w.data.add_(1.0)                                   # drifted weights, zero gradient
+    before = w.detach().clone()
+    w.data.mul_(1 - 0.1 * 0.5)                         # what the optimiser's decoupled decay does
+    anchors.apply()
+    expect = before - 0.1 * 0.5 * (before - start.bfloat16().float())
+    torch.testing.assert_close(w.detach(), expect, rtol=1e-5, atol=1e-6)
+    kept = w.detach().clone()
+    anchors.apply(skip=torch.ones(1, dtype=torch.int32))       # a skipped step adds nothing
+    torch.testing.assert_close(w.detach(), kept)
+
+    v = torch.nn.Parameter(torch.randn(32, 32) * 0.1)
+    r0 = v.detach().square().mean().sqrt()
+    v.data[0, 0] = 10.0
+    opt2 = torch.optim.SGD([v], lr=0.5)
+    od = OutlierDecay([("blk.w", v), ("blk.b", torch.nn.Parameter(torch.zeros(4)))], opt2, {"rate": 1.0, "cap": 4.0, "warmup": 2})
+    assert od.names == ["blk.w"]
+    inside = v.detach().clone()
+    od.apply()                                          # warm-up: half rate
+    assert float(v[0, 0]) == pytest.approx(10.0 - 0.5 * 0.5 * (10.0 - 4.0 * float(od.r0[id(v)])), rel=1e-5)
+    mask = torch.ones_like(v, dtype=torch.bool)
+    mask[0, 0] = False
+    torch.testing.assert_close(v.detach()[mask], inside[mask])   # elements under the cap do not move
+    assert abs(float(od.r0[id(v)]) - float(r0)) < 0.5           # r0 is the tensor's start RMS (the outlier included)
+    assert regularizer_problems({"WD_TARGET": "start", "ALGO": "lora", "WEIGHT_DECAY": 0.0, "OPTIMIZER": "prodigy"})
+    assert not regularizer_problems({"WD_TARGET": "start", "ALGO": "full", "WEIGHT_DECAY": 0.01, "OPTIMIZER": "adamw"})
+    assert regularizer_problems({"OUTLIER_DECAY": {"rat": 1.0}})
+
+
+def test_stack_sampler_charges_wall_time_to_categories():
+    import time
+
+    from kohakumosstrainer_b200.training.callbacks import StackSampler
+
+    def busy_wait(seconds):
+        end = time.perf_counter() + seconds
+        while time.perf_counter() < end:
+            pass
+
+    sampler = StackSampler(interval=0.002, categories=(("spin", __name__, frozenset({"busy_wait"})),)).start()
+    busy_wait(0.15)
+    sampler.stop()
+    rep = sampler.report()
+    assert rep["breakdown/stack_samples"] > 5
+    assert rep.get("breakdown/stack_spin_s", 0.0) > 0.1           # nearly all of the 0.15 s went to the spin
