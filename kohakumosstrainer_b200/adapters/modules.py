@@ -327,7 +327,7 @@ class BOFTModule(OFTModule):
             r = r * multiplier + eye * (1.0 - multiplier)
         return r
 
-    def _apply(self, r: Tensor, rows: Tensor) -> Tensor:
+    def _butterfly(self, r: Tensor, rows: Tensor) -> Tensor:
         """Rotate `rows [out, ...]` by the butterfly product of the stages in `r`."""
         b, half = self.block_size, self.block_size // 2
         x = rows
@@ -340,7 +340,7 @@ class BOFTModule(OFTModule):
 
     def merged(self, w: Tensor) -> Tensor:
         wf = w.float()
-        new = self._apply(self.rotation(self.multiplier), wf)
+        new = self._butterfly(self.rotation(self.multiplier), wf)
         if self.rescale is not None:
             new = new * self.rescale.float()
         return new.to(w.dtype)
@@ -351,7 +351,7 @@ class BOFTModule(OFTModule):
         bias = None if lin.bias is None else lin.bias.to(y.dtype)
         core = y if bias is None else y - bias
         flat = core.reshape(-1, core.shape[-1]).transpose(0, 1)  # [out, tokens]
-        out = self._apply(self.rotation(self.multiplier), flat.float()).transpose(0, 1).to(y.dtype).reshape_as(core)
+        out = self._butterfly(self.rotation(self.multiplier), flat.float()).transpose(0, 1).to(y.dtype).reshape_as(core)
         if self.rescale is not None:
             out = out * self.rescale.to(y.dtype).squeeze(-1)
         return out if bias is None else out + bias

@@ -1,0 +1,112 @@
+"""fp16 residual-stream study with fp32 as the reference (role of `scripts/probe/fp16_study.py`):
+per-block stream maxima of the original and of the folded model, the non-finite rate and the first
+overflowing block in plain fp16, and the sweep over the fold factor c (headroom under the fp16
+maximum, fp16-vs-fp32 velocity error, subnormal / zero counts of the scaled weights). Works on
+real weights (`--weights`) or, for a dry run of the tooling, on a random-init model whose stream is
+inflated on purpose (`--inflate`). One JSON report.
+
+    python scripts/probe/fp16_study.py [--weights <root>/base] [--inflate 300] --out runs/fp16/base
+"""
+
+from __future__ import annotations
+
+import argparse
+import copy
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[2]))
+from kohakumosstrainer_b200.models import build_backbone  # noqa: E402
+from kohakumosstrainer_b200.models.build import resolve_arch  # noqa: E402
+from kohakumosstrainer_b200.models.numerics import SaturationCounter, fold_stream_scale  # noqa: E402
+from kohakumosstrainer_b200.types import build_seqinfo  # noqa: E402
+
+SMALL = {"dim": 128, "depth": 4, "heads": 2, "ffn_dim": 256, "text_dim": 64, "text_blocks": 1}
+FP16_MAX = 65504.0
+
+
+def rel(a, b):
+    return float((a.double() - b.double()).norm() / b.double().norm().clamp_min(1e-30))
+
+
+def probe_inputs(cfg, seeds, device):
+    for s in seeds:
+        g = torch.Generator().manual_seed(s)
+        seq = build_seqinfo(torch.tensor([[16, 16], [8, 24]]), torch.tensor([20, 11]))
+        yield (torch.randn(seq.n_img, cfg.latent_channels, generator=g).to(device), torch.randn(seq.n_txt, cfg.text_dim, generator=g).to(device),
+               torch.rand(2, generator=g).to(device), seq.to(device))
+
+
+def block_maxima(model, inputs):
+    counter = SaturationCounter(model, threshold=FP16_MAX)
+    with torch.no_grad():
+        outs = [model(*a) for a in inputs]
+    return [counter.peaks.get(i, 0.0) for i in range(len(model.layers))], outs
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--weights", default="")
+    ap.add_argument("--variant", default="base")
+    ap.add_argument("--inflate", type=float, default=0.0, help="dry run: multiply the first block's output projection by this")
+    ap.add_argument("--factors", default="1,4,16,64,256")
+    ap.add_argument("--seeds", default="0,1,2")
+    ap.add_argument("--out", default="runs/fp16/study")
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    args = ap.parse_args()
+    out = Path(args.out)
+    out.mkdir(parents=True, exist_ok=True)
+    arch = resolve_arch(args.variant, None if args.weights else SMALL)
+    model = build_backbone(arch, device=args.device, dtype=torch.float32, seed=0, init=not args.weights).eval()
+    if args.weights:
+        from kohakumosstrainer_b200.models.io import load_backbone
+
+        load_backbone(model, args.weights)
+    if args.inflate:
+        with torch.no_grad():
+            model.layers[0].ffn_down.weight.mul_(args.inflate) if hasattr(model.layers[0], "ffn_down") else \
+                next(p for n, p in model.layers[0].named_parameters() if n.endswith("weight") and p.ndim == 2).mul_(args.inflate)
+    seeds = [int(s) for s in args.seeds.split(",")]
+    inputs = list(probe_inputs(model.cfg, seeds, args.device))
+    peaks32, ref = block_maxima(model, inputs)
+    report = {"weights": args.weights or "random-init small", "fp32_block_maxima": peaks32, "fp32_stream_peak": max(peaks32), "sweep": []}
+    half_ok = torch.device(args.device).type == "cuda"  # fp16 matmuls on the host are slow or missing: emulate by rounding there
+    for c in [float(f) for f in args.factors.split(",")]:
+        m = copy.deepcopy(model)
+        with torch.no_grad():
+            if c != 1.0:
+                fold_stream_scale(m, c)
+        peaks, outs = block_maxima(m, inputs)
+        row = {"c": c, "stream_peak": max(peaks), "headroom": FP16_MAX / max(max(peaks), 1e-30),
+               "fp32_fold_error": max(rel(o, r) for o, r in zip(outs, ref))}
+        tiny = zero = total = 0
+        for p in m.parameters():
+            h = p.detach().to(torch.float16)
+            nz = p.detach() != 0
+            tiny += int(((h.abs() < 6.1035e-5) & (h != 0)).sum())
+            zero += int(((h == 0) & nz).sum())
+            total += p.numel()
+        row.update(fp16_subnormal_weights=tiny, fp16_flushed_weights=zero, weights=total)
+        if half_ok:
+            mh = m.to(torch.float16)
+            counter = SaturationCounter(mh, threshold=FP16_MAX)
+            with torch.no_grad():
+                outs16 = [mh(a[0].half(), a[1].half(), a[2], a[3]) for a in inputs]
+            bad = [not bool(torch.isfinite(o).all()) for o in outs16]
+            row["fp16_nonfinite_rate"] = sum(bad) / len(bad)
+            row["fp16_first_overflow_block"] = min(counter.counts) if counter.counts else None
+            row["fp16_vs_fp32"] = max((rel(o.float(), r) for o, r, b in zip(outs16, ref, bad) if not b), default=None)
+        else:
+            row["fp16_would_overflow"] = max(peaks) > FP16_MAX
+        report["sweep"].append(row)
+    safe = [r for r in report["sweep"] if r["headroom"] >= 4.0]
+    report["chosen_c"] = min(safe, key=lambda r: r["c"])["c"] if safe else None
+    (out / "fp16_study.json").write_text(json.dumps(report, indent=1))
+    print(json.dumps({k: report[k] for k in ("fp32_stream_peak", "chosen_c")} | {"sweep": [(r["c"], round(r["headroom"], 2)) for r in report["sweep"]]}))
+
+
+if __name__ == "__main__":
+    main()

@@ -72,7 +72,7 @@ def test_boft_is_an_orthogonal_butterfly_and_bypass_equals_merge():
     w = lin.weight.detach()
     torch.testing.assert_close(mod.merged(w), w)
     torch.nn.init.normal_(mod.oft_blocks, std=0.2)
-    full = mod._apply(mod.rotation(), torch.eye(32))     # the dense 32 x 32 rotation
+    full = mod._butterfly(mod.rotation(), torch.eye(32))     # the dense 32 x 32 rotation
     torch.testing.assert_close(full @ full.T, torch.eye(32), rtol=1e-4, atol=1e-4)
     assert (full.abs() > 1e-6).float().mean() > 0.9      # the stages mix every pair of rows
     torch.testing.assert_close(mod.merged(w), full @ w, rtol=1e-4, atol=1e-5)
