@@ -10,8 +10,9 @@ A quantised layer `<n>` stores its codes as `<n>.weight`, its scales as `<n>.wei
 | `float8_e4m3fn` | weight e4m3 [N, K], weight_scale | `Fp8Weight` (row or tensor scaled) |
 
 A record-less int8 / fp8 `<n>.weight` next to a scale key is read the same way (no rotation).
-Joint q / k / v stored fused (`proj.qkv`) are split on load and fused on save. `asym_w4a8_int8`
-files are recognised and refused with a clear message.
+| `asym_w4a8_int8` | packed 4- / 6-bit codes, weight_s_rel e4m3, weight_s_channel, optional codebook / correction; `group_size` | decoded once at load into `Int8Weight` (`quant/w4a8.py`) |
+
+Joint q / k / v stored fused (`proj.qkv`) are split on load and fused on save.
 """
 
 from __future__ import annotations
@@ -38,6 +39,7 @@ class ComfyLayer:
     fmt: str            # int8 | fp8 | w4a8
     rotation: int       # ConvRot group (0 = none)
     keys: tuple
+    group: int = 0      # w4a8: input columns per group scale
 
 
 def write_record(fmt: str, rotation: int = 0) -> Tensor:
@@ -66,6 +68,10 @@ def scan_layers(sd: dict[str, Tensor]) -> dict[str, ComfyLayer]:
             if fmt is None:
                 raise ValueError(f"{path}: unknown comfy_quant format {rec.get('format')!r}")
             rot = int(rec.get("convrot_groupsize", 0)) if rec.get("convrot") else 0
+            if fmt == "w4a8":
+                extra = tuple(k for k in (f"{path}.weight_{n}" for n in ("s_rel", "s_channel", "codebook", "correction")) if k in sd)
+                out[path] = ComfyLayer(path, fmt, rot, (key, rec_key) + extra, int(rec.get("group_size", 0)))
+                continue
         elif scale_key is not None and t.dtype in (torch.int8, torch.float8_e4m3fn):
             fmt, rot = ("int8" if t.dtype == torch.int8 else "fp8"), 0
         else:
@@ -78,7 +84,9 @@ def scan_layers(sd: dict[str, Tensor]) -> dict[str, ComfyLayer]:
 def base_of(layer: ComfyLayer, sd: dict[str, Tensor], int8_compute: bool = False):
     """The stored-weight object of one quantised layer."""
     if layer.fmt == "w4a8":
-        raise NotImplementedError(f"{layer.path}: asym_w4a8_int8 layers are not supported; requantise the file as int8 or fp8")
+        from .w4a8 import load_layer
+
+        return load_layer(layer.path, sd, layer.group, layer.rotation, int8_compute)
     w = sd[f"{layer.path}.weight"]
     scale = next(sd[f"{layer.path}.{s}"] for s in SCALE_KEYS if f"{layer.path}.{s}" in sd).float().reshape(-1)
     if scale.numel() == 1:
@@ -125,8 +133,13 @@ def attach_quantized(model, sd: dict[str, Tensor], int8_compute: bool = False) -
         mod = modules.get(path)
         if mod is None or not hasattr(mod, "set_base"):
             continue
-        mod.set_base(base_of(layer, sd, int8_compute))
-        mod.drop_weight()
+        base = base_of(layer, sd, int8_compute)
+        if torch.is_tensor(base):      # a W4A8 layer with a correction term decodes to a dense weight
+            with torch.no_grad():
+                mod.weight.copy_(base.to(mod.weight))
+        else:
+            mod.set_base(base)
+            mod.drop_weight()
         for k in layer.keys:
             rest.pop(k, None)
         count += 1

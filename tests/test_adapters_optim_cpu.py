@@ -442,3 +442,40 @@ def test_stack_sampler_charges_wall_time_to_categories():
     rep = sampler.report()
     assert rep["breakdown/stack_samples"] > 5
     assert rep.get("breakdown/stack_spin_s", 0.0) > 0.1           # nearly all of the 0.15 s went to the spin
+
+
+def test_w4a8_codes_pack_decode_and_load_as_int8_weights():
+    from kohakumosstrainer_b200.quant import comfy, w4a8
+
+    torch.manual_seed(0)
+    for bits in (4, 6):
+        codes = torch.randint(0, 1 << bits, (5, 64))
+        packed = w4a8.pack_codes(codes, bits)
+        assert packed.shape == (5, 64 * bits // 8) and packed.dtype == torch.int8
+        assert torch.equal(w4a8.unpack_codes(packed, 64, bits), codes.int())
+    w = torch.randn(48, 128) * 0.05
+    for bits, tol in ((4, 0.2), (6, 0.05)):
+        st = w4a8.quantize_w4a8(w, group=32, bits=bits)
+        n, k, b = w4a8.geometry(st["weight"], st["weight_s_rel"], 32)
+        assert (n, k, b) == (48, 128, bits)
+        sd = {f"lin.{k_}": v for k_, v in st.items()}
+        base = w4a8.load_layer("lin", sd, 32)
+        err = (base.weight(torch.float32) - w).norm() / w.norm()
+        assert err < tol, (bits, float(err))
+    # a codebook replaces the uniform grid; a correction term turns the layer dense
+    st = w4a8.quantize_w4a8(w, group=32, bits=4)
+    sd = {f"lin.{k_}": v for k_, v in st.items()}
+    sd["lin.weight_codebook"] = torch.arange(16).float() - 8
+    same = w4a8.load_layer("lin", sd, 32)
+    torch.testing.assert_close(same.weight(torch.float32), w4a8.load_layer("lin", {k_: v for k_, v in sd.items() if "codebook" not in k_}, 32).weight(torch.float32))
+    sd["lin.weight_correction"] = torch.full((4, 48), 0.5)
+    dense = w4a8.load_layer("lin", sd, 32, dtype=torch.float32)
+    torch.testing.assert_close(dense, same.weight(torch.float32) + 0.5, rtol=1e-5, atol=1e-5)
+    # the file scanner routes the record to the decoder
+    sd = {f"layers.0.proj.q.{k_}": v for k_, v in st.items()}
+    rec = {"format": "asym_w4a8_int8", "group_size": 32}
+    import json
+    sd[f"layers.0.proj.q.{comfy.RECORD}"] = torch.tensor(list(json.dumps(rec).encode()), dtype=torch.uint8)
+    layers = comfy.scan_layers(sd)
+    assert layers["layers.0.proj.q"].fmt == "w4a8" and layers["layers.0.proj.q"].group == 32
+    assert comfy.base_of(layers["layers.0.proj.q"], sd).q.dtype == torch.int8
