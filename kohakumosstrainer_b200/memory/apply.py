@@ -31,9 +31,11 @@ def build_plan_runner(plan: MemoryPlan, model, device):
     return runner, parts
 
 
-def build_plan_optimizer(plan: MemoryPlan, named, name: str, lr, betas, eps, weight_decay, wd_rules, kwargs):
+def build_plan_optimizer(plan: MemoryPlan, named, name: str, lr, betas, eps, weight_decay, wd_rules, kwargs, shared: bool = False):
     """-> (optimizer, parts). `gpu` keeps the fused device optimisers; `cpu` / `stream` are AdamW
-    with host state (Muon and EMA need device state and stay on `gpu`)."""
+    with host state (Muon and EMA need device state and stay on `gpu`). `shared` (data-parallel
+    ranks of one node, `cpu` state): the masters live once per node in shared host memory and each
+    rank steps its slice (`memory.shared_host.SharedHostAdamW`)."""
     from ..optim import build_optimizer
     from ..optim.groups import param_groups
 
@@ -44,6 +46,10 @@ def build_plan_optimizer(plan: MemoryPlan, named, name: str, lr, betas, eps, wei
     from .host_optim import GradOffload, HostAdamW, StreamedAdamW
 
     groups = param_groups([(n, p) for n, p in named if p.requires_grad], weight_decay, wd_rules, (), None)
+    if shared and plan.optim_state == "cpu" and not plan.grad_offload:
+        from .shared_host import SharedHostAdamW
+
+        return SharedHostAdamW(groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, pinned=plan.pinned), {}
     cls = HostAdamW if plan.optim_state == "cpu" else StreamedAdamW
     opt = cls(groups, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, pinned=plan.pinned)
     parts = {}

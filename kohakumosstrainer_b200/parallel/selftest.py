@@ -288,3 +288,27 @@ def pipeline_worker(rank, world, device, out_dir, n_stages=2, schedule="1f1b", m
             worst, name = e, n
     _write(out_dir, rank, {"loss": out["loss"], "ref_loss": ref_loss, "worst_grad_err": worst, "worst": name, "stage": tr.stage,
                            "replica": tr.replica, "n_grads": len(captured)})
+
+
+def shared_host_worker(rank, world, device, out_dir, steps=4):
+    """Node-shared host masters: every rank steps its slice; the result equals one process's
+    `HostAdamW` on the same gradients, on every rank."""
+    from ..memory.host_optim import HostAdamW
+    from ..memory.shared_host import SharedHostAdamW
+
+    torch.manual_seed(3)
+    shapes = [(33, 17), (1200,), (64, 40)]
+    init = [torch.randn(s) for s in shapes]
+    ps = [torch.nn.Parameter(t.clone().to(device)) for t in init]
+    ref = [torch.nn.Parameter(t.clone()) for t in init]
+    ours, theirs = SharedHostAdamW(ps, lr=1e-2, weight_decay=0.1, pinned=False), HostAdamW(ref, lr=1e-2, weight_decay=0.1, pinned=False)
+    g = torch.Generator().manual_seed(11)
+    for _ in range(steps):
+        for p, r in zip(ps, ref):
+            gr = torch.randn(r.shape, generator=g)   # the same on every rank: what an all-reduce leaves
+            p.grad, r.grad = gr.to(device), gr.clone()
+        ours.step(grad_scale=0.5)
+        theirs.step(grad_scale=0.5)
+    worst = max(float((p.detach().cpu() - r.detach()).abs().max()) for p, r in zip(ps, ref))
+    owned = [hi - lo for lo, hi in ours.bounds]
+    _write(out_dir, rank, {"worst": worst, "owned": owned, "d2h": ours.bytes_d2h, "total": sum(t.numel() for t in init)})

@@ -149,7 +149,7 @@ class Trainer:
             self.memory_parts.update(parts)
         if plan is not None and plan.optim_state != "gpu" and self.fsdp is None:
             opt, parts = build_plan_optimizer(plan, named, cfg.optimizer, cfg.lr, cfg.betas, cfg.eps, cfg.weight_decay, cfg.wd_rules,
-                                              cfg.optimizer_kwargs)
+                                              cfg.optimizer_kwargs, shared=cfg.parallel == "ddp" and world > 1)
             self.memory_parts.update(parts)
             off = parts.get("grad_offload")
             if off is not None:

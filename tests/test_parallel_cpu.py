@@ -120,3 +120,13 @@ def test_stage_bounds_balance_and_cover():
     assert stage_bounds(cfg, 4, (10, 11, 11, 10)) == [(0, 10), (10, 21), (21, 32), (32, 42)]
     with pytest.raises(ValueError):
         stage_bounds(cfg, 4, (10, 10, 10, 10))
+
+
+def test_shared_host_masters_step_like_one_host_optimiser(tmp_path):
+    res = selftest.spawn_results(selftest.shared_host_worker, 2, str(tmp_path), timeout_s=120)
+    total = res[0]["total"]
+    assert sum(r["owned"][0] for r in res) == total          # the slices tile the parameter space
+    for r in res:
+        assert r["worst"] < 1e-6
+        assert r["d2h"] == r["owned"][0] * 4 * 4             # a rank fetches only its own slice of the gradients, each of 4 steps
+
