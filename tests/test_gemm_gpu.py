@@ -173,3 +173,95 @@ def test_qk_rope_epilogue_matches_eager():
     assert _rel(out[:, 2 * D :], v) < 6e-3
     ref_rstd = torch.rsqrt(q.unflatten(1, (H, 128)).square().mean(-1) + 1e-6)
     assert _rel(rstd[:, :H], ref_rstd) < 1e-3
+
+
+# ---- CTA-pair tiles (256 rows per pair): shapes large enough that the launcher picks them ----------------
+PAIR_M = 4900   # 20 pair tiles, the last one ragged (a 128-row half with 36 rows, then nothing)
+
+
+@pytest.mark.gpu
+def test_pair_tiles_linear_epilogue_and_bypass_bf16():
+    from kohakumosstrainer_b200.ops import native
+
+    M, N, K, B, R = PAIR_M, 1024, 640, 3, 16
+    g = torch.Generator(device="cuda").manual_seed(11)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    b = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+    t = torch.randn(M, R, device="cuda", generator=g).bfloat16()
+    u = torch.randn(N, R, device="cuda", generator=g).bfloat16()
+    bias = torch.randn(N, device="cuda", generator=g).bfloat16()
+    res = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+    mod = torch.randn(B, 6, N, device="cuda", generator=g)
+    seg = torch.randint(0, B, (M,), device="cuda", generator=g, dtype=torch.int32).sort().values
+    row_scale = torch.rand(M, device="cuda", generator=g) + 0.5
+    col_scale = torch.rand(N, device="cuda", generator=g) + 0.5
+    acc = a.float() @ b.float().t() + t.float() @ u.float().t()
+    ref = (acc * 0.5 * row_scale[:, None] * col_scale[None] + bias.float()) * mod[:, 2][seg.long()] + 0.7 * res.float()
+    for dtype in (torch.float32, torch.bfloat16):       # direct stores, and the staged TMA-store path
+        out = native.gemm(a, b, alpha=0.5, row_scale=row_scale, col_scale=col_scale, bias=bias, res=res, beta=0.7,
+                          gate=mod[:, 2], seg=seg, t=t, u=u, out_dtype=dtype)
+        native.check_status()
+        assert _rel(out, ref) < (2e-3 if dtype == torch.float32 else 6e-3)
+    plain = native.gemm(a, b)
+    native.check_status()
+    assert _rel(plain, a.float() @ b.float().t()) < 6e-3
+
+
+@pytest.mark.gpu
+def test_pair_tiles_fp8_rows_with_bypass():
+    from kohakumosstrainer_b200.ops import native
+
+    M, N, K, R = PAIR_M, 1280, 768, 8
+    g = torch.Generator(device="cuda").manual_seed(12)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
+    xq, xs = native.quantize_fp8_rows(x, both=True)
+    wq, ws = native.quantize_fp8(w)
+    t = torch.randn(M, R, device="cuda", generator=g).bfloat16()
+    u = torch.randn(N, R, device="cuda", generator=g).bfloat16()
+    out = native.gemm(xq, wq, row_scale=xs[0], scale_b=ws[:1], t=t, u=u, out_dtype=torch.float32)
+    native.check_status()
+    deq = (xq.float() * xs[0][:, None]) @ (wq.float() * ws[0]).t()
+    bypass = (t.float() @ u.float().t()) * xs[0][:, None] * ws[0]      # the bypass shares the rescaled accumulator
+    assert _rel(out, deq + bypass) < 2e-3
+    for e5 in (False, True):
+        dq, ds = native.quantize_fp8_rows(x, torch.float8_e5m2 if e5 else torch.float8_e4m3fn, both=True)
+        o = native.gemm(dq, wq, row_scale=ds[0], scale_b=ws[:1])
+        native.check_status()
+        assert _rel(o, (dq.float() * ds[0][:, None]) @ (wq.float() * ws[0]).t()) < 6e-3
+
+
+@pytest.mark.gpu
+def test_pair_tiles_situ_and_qk_rope_epilogues():
+    from kohakumosstrainer_b200.ops import eager, native
+
+    M, F, K = PAIR_M, 512, 640
+    g = torch.Generator(device="cuda").manual_seed(13)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(2 * F, K, device="cuda", generator=g) * 0.1).bfloat16()
+    t = (torch.randn(M, 8, device="cuda", generator=g) * 0.3).bfloat16()
+    u = (torch.randn(2 * F, 8, device="cuda", generator=g) * 0.3).bfloat16()
+    aux = torch.empty(M, 2 * F, device="cuda", dtype=torch.bfloat16)
+    out = native.gemm(a, w, epilogue=native.EPI_SITU, aux=aux, t=t, u=u)
+    native.check_status()
+    h = a.float() @ w.float().t() + t.float() @ u.float().t()
+    assert _rel(aux, h) < 6e-3
+    assert _rel(out, eager.situ_glu(aux.float())) < 6e-3
+
+    H = 3
+    D = H * 128
+    wq = (torch.randn(3 * D, K, device="cuda", generator=g) * 0.1).bfloat16()
+    qw = (torch.rand(128, device="cuda", generator=g) + 0.5).bfloat16()
+    kw = (torch.rand(128, device="cuda", generator=g) + 0.5).bfloat16()
+    pos = torch.randn(M, 4, device="cuda", generator=g) * 20
+    bands = 1.0 / (10000 ** (torch.arange(16, device="cuda", dtype=torch.float32) / 16))
+    table = native.rope_table(pos, bands)
+    rstd = torch.empty(M, 2 * H, device="cuda")
+    o = native.gemm(a, wq, epilogue=native.EPI_QK_ROPE, q_norm_w=qw, k_norm_w=kw, rope=table, rope_cols=2 * D, eps=1e-6, head_rstd=rstd)
+    native.check_status()
+    lin = a.float() @ wq.float().t()
+    q, k, v = lin.split(D, 1)
+    rq, rk = eager.qk_norm_rope(q.unflatten(1, (H, 128)), k.unflatten(1, (H, 128)), qw, kw, pos, bands, 1e-6)
+    assert _rel(o[:, :D], rq.flatten(1)) < 8e-3
+    assert _rel(o[:, D : 2 * D], rk.flatten(1)) < 8e-3
+    assert _rel(o[:, 2 * D :], v) < 6e-3
