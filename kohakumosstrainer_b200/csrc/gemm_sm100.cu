@@ -112,10 +112,11 @@ __device__ __forceinline__ float situ_f(float u, float g) {
 
 // PAIR: two CTAs of a cluster share one 256 x BN tile (tcgen05 cta_group::2). Each CTA stages its own 128 rows
 // of A and HALF of the B tile, so a k-block costs a CTA 32 KB instead of 48 KB of L2 -> shared-memory traffic
-// (what bounds the fp8 product) and the ring is six stages deep instead of four. K-major operands only.
+// (what bounds the fp8 product) and the ring is six stages deep instead of four. A is K-major; an MN-major B
+// (dgrad) splits by whole 128-byte column chunks.
 template <int BN, bool A_MN, bool B_MN, bool FP8, bool PAIR = false>
 struct Cfg {
-  static_assert(!PAIR || (!A_MN && !B_MN && BN == 256), "CTA pairs: K-major operands, 256-wide tiles");
+  static_assert(!PAIR || (!A_MN && BN == 256), "CTA pairs: K-major A, 256-wide tiles");
   static constexpr int BK = FP8 ? 128 : 64;       // elements per k-block (128 bytes)
   static constexpr int UMMA_K = FP8 ? 32 : 16;    // elements per instruction
   static constexpr int K_STEPS = BK / UMMA_K;     // 4
@@ -124,7 +125,8 @@ struct Cfg {
   // An MN-major B tile is stored as whole 128-byte-wide chunks of BK rows each.
   static constexpr int B_CHUNKS = (BN + CHUNK - 1) / CHUNK;
   static constexpr int B_ROWS = PAIR ? BN / 2 : BN;   // rows of a K-major B tile this CTA stages
-  static constexpr int B_STAGE = B_MN ? B_CHUNKS * BK * 128 : B_ROWS * 128;
+  static constexpr int B_CHUNKS_CTA = PAIR ? B_CHUNKS / 2 : B_CHUNKS;   // MN-major chunks this CTA stages
+  static constexpr int B_STAGE = B_MN ? B_CHUNKS_CTA * BK * 128 : B_ROWS * 128;
   static constexpr int STAGE = A_STAGE + B_STAGE;
   static constexpr int STAGES = PAIR ? 6 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
   // Bytes one k-block / one bypass block deposits on a full barrier.
@@ -398,7 +400,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const uint32_t fb = map_to_cta(full_bar(stage), 0);
             if (cr == 0) mbar_expect_tx(full_bar(stage), 2 * C::MAIN_TX);
             tma_load_2d_pair(a_dst, &map_a, fb, kb * C::BK, m0);
-            tma_load_2d_pair(b_dst, &map_b, fb, kb * C::BK, b_row);
+            if constexpr (!B_MN) {
+              tma_load_2d_pair(b_dst, &map_b, fb, kb * C::BK, b_row);
+            } else {
+#pragma unroll
+              for (int c = 0; c < C::B_CHUNKS_CTA; ++c)
+                tma_load_2d_pair(b_dst + c * (C::BK * 128), &map_b, fb, n0 + ((int)cr * C::B_CHUNKS_CTA + c) * C::CHUNK, kb * C::BK);
+            }
             if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
             continue;
           }
@@ -1162,7 +1170,10 @@ cudaError_t launch_bn(const GemmProblem& g, DeviceParams& p, cudaStream_t s) {
       if constexpr (BN == 256) if (use_pair(g, p)) return launch_cfg<BN, false, false, false, true>(g, p, s);
       return launch_cfg<BN, false, false, false>(g, p, s);
     }
-    if (!g.a_mn && g.b_mn) return launch_cfg<BN, false, true, false>(g, p, s);
+    if (!g.a_mn && g.b_mn) {
+      if constexpr (BN == 256) if (use_pair(g, p)) return launch_cfg<BN, false, true, false, true>(g, p, s);
+      return launch_cfg<BN, false, true, false>(g, p, s);
+    }
     if (g.a_mn && g.b_mn) return launch_cfg<BN, true, true, false>(g, p, s);
     return launch_cfg<BN, true, false, false>(g, p, s);
   }
@@ -1170,7 +1181,10 @@ cudaError_t launch_bn(const GemmProblem& g, DeviceParams& p, cudaStream_t s) {
     if constexpr (BN == 256) if (use_pair(g, p)) return launch_cfg<BN, false, false, true, true>(g, p, s);
     return launch_cfg<BN, false, false, true>(g, p, s);
   }
-  if (!g.a_mn && g.b_mn) return launch_cfg<BN, false, true, true>(g, p, s);
+  if (!g.a_mn && g.b_mn) {
+    if constexpr (BN == 256) if (use_pair(g, p)) return launch_cfg<BN, false, true, true, true>(g, p, s);
+    return launch_cfg<BN, false, true, true>(g, p, s);
+  }
   if (g.a_mn && g.b_mn) return launch_cfg<BN, true, true, true>(g, p, s);
   return launch_cfg<BN, true, false, true>(g, p, s);
 }

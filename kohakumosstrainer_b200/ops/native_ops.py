@@ -80,9 +80,11 @@ def _rows(xs) -> bool:
 
 def _main_gemm(x, xq, xs, wp: WeightPack, **kw) -> Tensor:
     if wp.kind == "fp8":
+        # one scale for the whole weight rides as a scalar: the epilogue then loads no per-column vector
+        ws = dict(scale_b=wp.scale[:1]) if wp.per_tensor else dict(col_scale=wp.col_scale)
         if _rows(xs):
-            return native.gemm(xq, wp.w, row_scale=xs[0], col_scale=wp.col_scale, **kw)
-        return native.gemm(xq, wp.w, scale_a=xs[:1], col_scale=wp.col_scale, **kw)
+            return native.gemm(xq, wp.w, row_scale=xs[0], **ws, **kw)
+        return native.gemm(xq, wp.w, scale_a=xs[:1], **ws, **kw)
     if wp.fsdp is not None:  # sharded weight: the GEMM gathers it from the peers while it computes
         full, gather = wp.fsdp.gather_args()
         return native.gemm(x, full, gather=gather, **kw)

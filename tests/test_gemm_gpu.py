@@ -265,3 +265,22 @@ def test_pair_tiles_situ_and_qk_rope_epilogues():
     assert _rel(o[:, :D], rq.flatten(1)) < 8e-3
     assert _rel(o[:, D : 2 * D], rk.flatten(1)) < 8e-3
     assert _rel(o[:, 2 * D :], v) < 6e-3
+
+
+def test_pair_tiles_mn_major_b_dgrad_shape():
+    from kohakumosstrainer_b200.ops import native
+
+    M, N, K, R = PAIR_M, 1024, 768, 8
+    g = torch.Generator(device="cuda").manual_seed(14)
+    d = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(K, N, device="cuda", generator=g) * 0.05).bfloat16()      # [out, in]: dgrad reads it MN-major
+    t = torch.randn(M, R, device="cuda", generator=g).bfloat16()
+    u = torch.randn(N, R, device="cuda", generator=g).bfloat16()
+    out = native.gemm(d, w, b_mn=True, t=t, u=u, out_dtype=torch.float32)
+    native.check_status()
+    assert _rel(out, d.float() @ w.float() + t.float() @ u.float().t()) < 2e-3
+    dq, ds = native.quantize_fp8_rows(d, torch.float8_e5m2, both=True)
+    wq, ws = native.quantize_fp8(w)
+    o8 = native.gemm(dq, wq, b_mn=True, row_scale=ds[0], scale_b=ws[:1])
+    native.check_status()
+    assert _rel(o8, (dq.float() * ds[0][:, None]) @ (wq.float() * ws[0])) < 6e-3
