@@ -1,0 +1,117 @@
+"""Training-step bench of the parallel modes on one node, launched with torchrun (one process per GPU):
+data parallel, FSDP (full finetune, AdamW or the Muon hybrid, optional EMA) and the process-group pipeline
+(any schedule, optionally x data parallel). Device-timed with CUDA events, barrier + synchronize on both
+sides, max over ranks; rank 0 prints one JSON line. Synthetic data, random-init weights.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29600 \
+        scripts/bench/step/parallel.py --parallel fsdp --algo full --optimizer muon --ema 0.999
+    ... scripts/bench/step/parallel.py --parallel pipeline --stages 4 --schedule 1f1b --microbatches 8
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[3]))
+from kohakumosstrainer_b200.data import SyntheticConfig, SyntheticDataset  # noqa: E402
+from kohakumosstrainer_b200.ops import native  # noqa: E402
+from kohakumosstrainer_b200.training.trainer import Trainer, TrainerConfig  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--parallel", default="ddp", choices=("ddp", "fsdp", "pipeline"))
+    ap.add_argument("--algo", default="lora")
+    ap.add_argument("--optimizer", default="adamw")
+    ap.add_argument("--base", default="fp8_compute", help="base precision of adapter runs; full finetunes use bf16 / --full-base")
+    ap.add_argument("--full-base", default="auto")
+    ap.add_argument("--ema", type=float, default=0.0)
+    ap.add_argument("--fused-step", action="store_true", help="FSDP: AdamW inside the reduce-scatter kernel")
+    ap.add_argument("--tokens", type=int, default=20480)
+    ap.add_argument("--depth", type=int, default=0)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--stages", type=int, default=0)
+    ap.add_argument("--schedule", default="1f1b")
+    ap.add_argument("--microbatches", type=int, default=4)
+    ap.add_argument("--virtual", type=int, default=2)
+    ap.add_argument("--checkpoint", default="none")
+    args = ap.parse_args()
+    rank, local, world = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("LOCAL_RANK", "0"), ("WORLD_SIZE", "1")))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=device)
+    full = args.algo == "full"
+    cfg = TrainerConfig(variant="base", arch_overrides={"depth": args.depth} if args.depth else {}, algo=args.algo, dim=8, alpha=8.0,
+                        base_precision=args.full_base if full else args.base, optimizer=args.optimizer, ema=args.ema,
+                        schedule={"mode": "constant"}, steps=10_000, parallel=args.parallel if args.parallel != "pipeline" else "none",
+                        fused_step=args.fused_step, checkpoint=args.checkpoint, lr=5e-5 if full else 1e-4)
+    data = SyntheticDataset(SyntheticConfig(max_tokens=args.tokens, seed=1234))
+    n = args.steps + args.warmup
+    if args.parallel == "pipeline":
+        from kohakumosstrainer_b200 import adapters as adapters_pkg
+        from kohakumosstrainer_b200.models import build_backbone
+        from kohakumosstrainer_b200.models.build import resolve_arch
+        from kohakumosstrainer_b200.training.pipeline_driver import PipelineTrainer
+
+        model = build_backbone(resolve_arch(cfg.variant, cfg.arch_overrides), device=device, dtype=torch.bfloat16, seed=0)
+        named = None
+        if full:
+            for p in model.parameters():
+                p.requires_grad_(True)
+        else:
+            aset = adapters_pkg.apply(model, adapters_pkg.AdapterConfig(algo=args.algo, preset="attn-mlp", dim=8, alpha=8.0, dtype=torch.bfloat16))
+            named = list(aset.named_parameters())
+        stages = args.stages or world
+        tr = PipelineTrainer(model, cfg, device, stages, args.microbatches, args.schedule, "flops", named, args.virtual)
+        micro = args.microbatches
+        groups = [[data.materialize(s * micro + i, tr.replica, tr.replicas) for i in range(micro)] for s in range(n)]
+        step = lambda s: (tr.train_step(groups[s]), sum(h.image_tokens for h in groups[s]) / stages)[1]  # noqa: E731
+        label = f"pp{stages}x dp{world // stages} {args.schedule} mb{micro}"
+    else:
+        tr = Trainer(cfg, device=device, rank=rank, world=world)
+        host = [data.materialize(i, rank, world) for i in range(n)]
+        step = lambda s: (tr.train_step(host[s], next_batch=host[s + 1] if s + 1 < n else None), host[s].image_tokens)[1]  # noqa: E731
+        label = f"{args.parallel}{world}"
+
+    def sync():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for s in range(args.warmup):
+        step(s)
+    sync()
+    torch.cuda.reset_peak_memory_stats()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    tokens = 0.0
+    start.record()
+    for s in range(args.warmup, n):
+        tokens += step(s)
+    end.record()
+    sync()
+    native.check_status()
+    ms = torch.tensor([start.elapsed_time(end)], device=device)
+    tok = torch.tensor([tokens], device=device)
+    mem = torch.tensor([torch.cuda.max_memory_allocated() / 2**30], device=device)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    dist.all_reduce(tok, op=dist.ReduceOp.SUM)
+    dist.all_reduce(mem, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        per = ms.item() / args.steps
+        print(json.dumps({"metric": "dit_train_latent_tokens_per_s", "value": round(tok.item() / args.steps / per * 1e3, 1), "n_gpus": world,
+                          "ms_per_step": round(per, 2), "parallelism": label, "algo": args.algo, "optimizer": args.optimizer,
+                          "ema": args.ema, "fused_step": args.fused_step, "tokens_per_rank_step": args.tokens, "depth": args.depth or 42,
+                          "max_mem_gib": round(mem.item(), 2), "data": "synthetic"}), flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
