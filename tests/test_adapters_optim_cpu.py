@@ -479,3 +479,18 @@ def test_w4a8_codes_pack_decode_and_load_as_int8_weights():
     layers = comfy.scan_layers(sd)
     assert layers["layers.0.proj.q"].fmt == "w4a8" and layers["layers.0.proj.q"].group == 32
     assert comfy.base_of(layers["layers.0.proj.q"], sd).q.dtype == torch.int8
+
+
+def test_quant_embedding_reproduces_the_table_rows():
+    from kohakumosstrainer_b200.quant.embedding import QuantEmbedding
+
+    torch.manual_seed(0)
+    emb = torch.nn.Embedding(500, 256)
+    ids = torch.tensor([[0, 7, 499], [7, 7, 123]])
+    for rotation in (0, 64):
+        qe = QuantEmbedding.from_embedding(emb, rotation, torch.float32)
+        got, want = qe(ids), emb(ids)
+        assert got.shape == want.shape and qe.q.dtype == torch.int8
+        assert float((got - want).norm() / want.norm()) < 0.02
+        torch.testing.assert_close(qe.lookup(ids, "cpu"), got)
+        assert set(qe.state("embed_tokens.")) >= {"embed_tokens.weight", "embed_tokens.weight_scale"}
