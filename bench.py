@@ -228,7 +228,8 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_dev, 2),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": round(joint / BASELINE_JOINT_TOK_S, 3),
             "vs_baseline_note": "joint (image+text) tokens/s over the reference's published 26,830 joint tok/s on 1x B300 (LoKr f8)",
-            "dtype": "bf16 activations, fp8 base GEMMs (e4m3 per-tensor weights, per-row activation scales; e5m2 gradients), bf16 LoRA", "data": "synthetic",
+            "dtype": "bf16 activations, fp8 base GEMMs (e4m3 per-tensor weights, per-row activation scales; e5m2 gradients), bf16 LoRA",
+            "data": "synthetic" if world == 1 else "synthetic (each step's samples dealt to the ranks by cost: the data layer's rank balance)",
             "impl": "ours",
             "config": {
                 "model": MODEL if args.variant in ("base", "sft") and not args.depth else f"{args.variant} (debug, invalid as a headline)",

@@ -37,6 +37,8 @@ class SyntheticConfig:
     samples: int | None = None                   # exact sample count (with fixed_size)
     dtype: torch.dtype = torch.bfloat16
     seed: int = 0
+    balance: bool = True             # several ranks: deal a step's samples to the ranks by cost, not in drawing order
+    attention_scale: float = 6000.0  # cost of a sample of n joint tokens = n + n^2 / attention_scale (linear work + attention)
 
 
 class SyntheticDataset:
@@ -54,8 +56,41 @@ class SyntheticDataset:
         w = max(c.size_step, int(round(math.sqrt(area * aspect) / c.size_step)) * c.size_step)
         return h, w
 
-    def plan(self, index: int, rank: int = 0) -> tuple[list[tuple[int, int]], list[int]]:
-        """Latent grids and text lengths of batch `index` on `rank` (no tensors yet)."""
+    def plan(self, index: int, rank: int = 0, world: int = 1) -> tuple[list[tuple[int, int]], list[int]]:
+        """Latent grids and text lengths of batch `index` on `rank` (no tensors yet).
+
+        With several ranks and `balance`, the samples of the step's `world` batches are pooled and dealt
+        longest-cost-first to the rank with the least cost so far that still has token room (the rank
+        balance of the data layer, `src/kohakumoss_data/resolution/batching.py` there): a step lasts as
+        long as its slowest rank, so equal cost per rank is what weak scaling needs. The pooled samples are
+        the ones the unbalanced plan would have drawn; a sample that fits nowhere is left out."""
+        c = self.cfg
+        if world > 1 and c.balance and c.samples is None:
+            return self._balanced(index, rank, world)
+        return self._draw(index, rank)
+
+    def _balanced(self, index: int, rank: int, world: int):
+        c = self.cfg
+        pool = []
+        for r in range(world):
+            grids, texts = self._draw(index, r)
+            pool += list(zip(grids, texts))
+        cost = lambda s: (lambda n: n + n * n / c.attention_scale)(s[0][0] * s[0][1] + s[1])  # noqa: E731
+        pool.sort(key=lambda s: (-cost(s), s))
+        bins = [([], [], 0, 0.0) for _ in range(world)]
+        for s in pool:
+            n = s[0][0] * s[0][1] + s[1]
+            fits = [i for i, b in enumerate(bins) if b[2] + n <= c.max_tokens]
+            if not fits:
+                continue
+            i = min(fits, key=lambda j: (bins[j][3], j))
+            g_, t_, tok, cst = bins[i]
+            bins[i] = (g_ + [s[0]], t_ + [s[1]], tok + n, cst + cost(s))
+        # ranks rotate through the bins so that no rank always gets the fullest one
+        grids, texts, _, _ = bins[(rank + index) % world]
+        return grids, texts
+
+    def _draw(self, index: int, rank: int = 0) -> tuple[list[tuple[int, int]], list[int]]:
         c = self.cfg
         g = torch.Generator().manual_seed(seed_of("synthetic-plan", c.seed, rank, index))
         grids, texts, total = [], [], 0
@@ -77,7 +112,7 @@ class SyntheticDataset:
 
     def materialize(self, index: int, rank: int = 0, world: int = 1, pin: bool = True) -> HostBatch:
         c = self.cfg
-        grids, texts = self.plan(index, rank)
+        grids, texts = self.plan(index, rank, world)
         g = torch.Generator().manual_seed(seed_of("synthetic-data", c.seed, rank, index))
         n_img = sum(h * w for h, w in grids)
         n_txt = sum(texts)
