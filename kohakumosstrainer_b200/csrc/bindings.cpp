@@ -276,6 +276,34 @@ void situ_bwd(const Tensor& da, const Tensor& up, const Tensor& gate, Tensor dup
                                 dgate.data_ptr(), dup.stride(0), (int)up.size(0), (int)up.size(1), cur_stream()));
 }
 
+// SiTU backward that also writes the per-row e5m2 copy of [d up | d gate] and its scales [2, rows]; false when the
+// shape is outside what the fused kernel covers (the caller then runs the two kernels).
+bool situ_bwd_quant(const Tensor& da, const Tensor& up, const Tensor& gate, Tensor dup, Tensor dgate, Tensor q, Tensor scales) {
+  c10::cuda::CUDAGuard guard(up.device());
+  const int f = (int)up.size(1);
+  TORCH_CHECK(up.stride(0) == gate.stride(0) && dup.stride(0) == dgate.stride(0), "situ_bwd_quant: strides");
+  if (!kmoss::situ_bwd_quant_supported(f) || q.scalar_type() != at::kFloat8_e5m2 || q.stride(1) != 1 || q.size(1) != 2 * f ||
+      scales.numel() != 2 * up.size(0) || !scales.is_contiguous())
+    return false;
+  KM_CHECK_CUDA(kmoss::situ_bwd_quant(da.data_ptr(), da.stride(0), up.data_ptr(), gate.data_ptr(), up.stride(0), dup.data_ptr(),
+                                      dgate.data_ptr(), dup.stride(0), q.data_ptr(), q.stride(0), scales.data_ptr<float>(),
+                                      (int)up.size(0), f, cur_stream()));
+  return true;
+}
+
+// y = x * vec[seg] with the per-row e5m2 copy of y and its scales [2, rows]; false when not covered.
+bool seg_scale_quant(const Tensor& x, const Tensor& vec, const Tensor& seg, Tensor out, Tensor q, Tensor scales) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && out.is_contiguous() && vec.stride(1) == 1, "seg_scale_quant: layout");
+  const int dim = (int)x.size(1);
+  if (!kmoss::seg_scale_quant_supported(dim) || (vec.stride(0) % 4) != 0 || (reinterpret_cast<uintptr_t>(vec.data_ptr()) & 15) != 0 ||
+      q.scalar_type() != at::kFloat8_e5m2 || !q.is_contiguous() || scales.numel() != 2 * x.size(0) || !scales.is_contiguous())
+    return false;
+  KM_CHECK_CUDA(kmoss::seg_scale_quant(x.data_ptr(), vec.data_ptr<float>(), vec.stride(0), seg.data_ptr<int>(), out.data_ptr(),
+                                       q.data_ptr(), scales.data_ptr<float>(), (int)x.size(0), dim, cur_stream()));
+  return true;
+}
+
 void gated_residual(const Tensor& x, const Tensor& o, const optional<Tensor>& gate, const optional<Tensor>& seg,
                     double r, Tensor out) {
   c10::cuda::CUDAGuard guard(x.device());
@@ -617,6 +645,9 @@ TORCH_LIBRARY(kmoss_b200, m) {
   m.def("situ_bwd(Tensor da, Tensor up, Tensor gate, Tensor(a!) dup, Tensor(b!) dgate) -> ()", &situ_bwd);
   m.def("gated_residual(Tensor x, Tensor o, Tensor? gate, Tensor? seg, float r, Tensor(a!) out) -> ()", &gated_residual);
   m.def("seg_scale(Tensor x, Tensor vec, Tensor seg, Tensor(a!) out) -> ()", &seg_scale);
+  m.def("situ_bwd_quant(Tensor da, Tensor up, Tensor gate, Tensor(a!) dup, Tensor(b!) dgate, Tensor(c!) q, Tensor(d!) scales) -> bool",
+        &situ_bwd_quant);
+  m.def("seg_scale_quant(Tensor x, Tensor vec, Tensor seg, Tensor(a!) out, Tensor(b!) q, Tensor(c!) scales) -> bool", &seg_scale_quant);
   m.def("token_mse_fwd(Tensor pred, Tensor target, Tensor seg, Tensor? weight, Tensor? mask) -> Tensor", &token_mse_fwd);
   m.def("token_mse_bwd(Tensor dloss, Tensor pred, Tensor target, Tensor seg, Tensor? weight, Tensor? mask) -> Tensor",
         &token_mse_bwd);

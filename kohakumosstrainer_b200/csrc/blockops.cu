@@ -400,6 +400,130 @@ __global__ void seg_scale_kernel(const __nv_bfloat16* x, const float* vec, long 
 }
 
 // ---------------------------------------------------------------------------------------
+// Gradient producers that also emit the fp8 (e5m2) copy the dgrad GEMM reads, scaled per row:
+// the row is in registers when its maximum is known, so the quantiser's own pass over the
+// gradient (a 2-byte read per element) disappears. Statistics are taken from the bf16-rounded values,
+// exactly what a separate quantiser would read back.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint2 pack_e5m2_8(const float (&v)[8], float s) {
+  __nv_fp8x4_e5m2 lo(make_float4(v[0] * s, v[1] * s, v[2] * s, v[3] * s));
+  __nv_fp8x4_e5m2 hi(make_float4(v[4] * s, v[5] * s, v[6] * s, v[7] * s));
+  uint2 o;
+  o.x = *reinterpret_cast<uint32_t*>(&lo);
+  o.y = *reinterpret_cast<uint32_t*>(&hi);
+  return o;
+}
+__device__ __forceinline__ void round_bf16_8(float (&v)[8], uint4& packed, float& amax) {
+  packed.x = pack_bf16(v[0], v[1]); packed.y = pack_bf16(v[2], v[3]);
+  packed.z = pack_bf16(v[4], v[5]); packed.w = pack_bf16(v[6], v[7]);
+  const float2 a = unpack_bf16(packed.x), b = unpack_bf16(packed.y), c = unpack_bf16(packed.z), d = unpack_bf16(packed.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+}
+
+// One CTA of 256 threads per row of d = [d up | d gate] (2 f columns, f <= 8192): SiTU backward + row quantiser.
+constexpr int SITU_Q_ITERS = 4;
+__global__ void __launch_bounds__(256)
+situ_bwd_quant_kernel(const __nv_bfloat16* da, long ld_da, const __nv_bfloat16* up, const __nv_bfloat16* gate, long ld_in,
+                      __nv_bfloat16* dup, __nv_bfloat16* dgate, long ld_out, uint8_t* q, long ldq, float* row_scale, int rows, int f) {
+  __shared__ float red[8];
+  const int r = blockIdx.x;
+  uint4 pu[SITU_Q_ITERS], pg[SITU_Q_ITERS];
+  float amax = 0.f;
+#pragma unroll
+  for (int k = 0; k < SITU_Q_ITERS; ++k) {
+    const int c = (threadIdx.x + k * 256) * 8;
+    if (c < f) {
+      float u[8], g[8], d[8], ou[8], og[8];
+      load8(up + (size_t)r * ld_in + c, u);
+      load8(gate + (size_t)r * ld_in + c, g);
+      load8(da + (size_t)r * ld_da + c, d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float tu = tanhf(0.04f * u[j]);
+        const float tg = tanhf(0.25f * g[j]);
+        const float sg = 1.f / (1.f + __expf(-g[j]));
+        const float G = 4.f * tg * sg;
+        const float U = 25.f * tu;
+        ou[j] = d[j] * G * (1.f - tu * tu);
+        og[j] = d[j] * U * ((1.f - tg * tg) * sg + G * (1.f - sg));
+      }
+      round_bf16_8(ou, pu[k], amax);
+      round_bf16_8(og, pg[k], amax);
+      *reinterpret_cast<uint4*>(dup + (size_t)r * ld_out + c) = pu[k];
+      *reinterpret_cast<uint4*>(dgate + (size_t)r * ld_out + c) = pg[k];
+    }
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  float m = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+  m = fmaxf(m, 1e-12f);
+  const float s = 57344.f / m;
+  if (threadIdx.x == 0) {
+    row_scale[r] = m / 57344.f;
+    row_scale[rows + r] = s;
+  }
+#pragma unroll
+  for (int k = 0; k < SITU_Q_ITERS; ++k) {
+    const int c = (threadIdx.x + k * 256) * 8;
+    if (c < f) {
+      float v[8];
+      const float2 a0 = unpack_bf16(pu[k].x), a1 = unpack_bf16(pu[k].y), a2 = unpack_bf16(pu[k].z), a3 = unpack_bf16(pu[k].w);
+      v[0] = a0.x; v[1] = a0.y; v[2] = a1.x; v[3] = a1.y; v[4] = a2.x; v[5] = a2.y; v[6] = a3.x; v[7] = a3.y;
+      *reinterpret_cast<uint2*>(q + (size_t)r * ldq + c) = pack_e5m2_8(v, s);
+      const float2 b0 = unpack_bf16(pg[k].x), b1 = unpack_bf16(pg[k].y), b2 = unpack_bf16(pg[k].z), b3 = unpack_bf16(pg[k].w);
+      v[0] = b0.x; v[1] = b0.y; v[2] = b1.x; v[3] = b1.y; v[4] = b2.x; v[5] = b2.y; v[6] = b3.x; v[7] = b3.y;
+      *reinterpret_cast<uint2*>(q + (size_t)r * ldq + f + c) = pack_e5m2_8(v, s);
+    }
+  }
+}
+
+// One warp per row (dim <= 4096): y = x * v[seg] + row quantiser.
+constexpr int SEG_Q_ITERS = 16;
+__global__ void __launch_bounds__(32 * ROWS_PER_BLOCK)
+seg_scale_quant_kernel(const __nv_bfloat16* x, const float* vec, long vec_stride, const int* seg, __nv_bfloat16* out,
+                       uint8_t* q, float* row_scale, int rows, int dim) {
+  const int row = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float* gp = vec + (size_t)seg[row] * vec_stride;
+  uint4 keep[SEG_Q_ITERS];
+  float amax = 0.f;
+#pragma unroll
+  for (int k = 0; k < SEG_Q_ITERS; ++k) {
+    const int c = (lane + k * 32) * 8;
+    if (c < dim) {
+      float a[8];
+      load8(x + (size_t)row * dim + c, a);
+      const float4 g0 = __ldg(reinterpret_cast<const float4*>(gp + c)), g1 = __ldg(reinterpret_cast<const float4*>(gp + c + 4));
+      a[0] *= g0.x; a[1] *= g0.y; a[2] *= g0.z; a[3] *= g0.w; a[4] *= g1.x; a[5] *= g1.y; a[6] *= g1.z; a[7] *= g1.w;
+      round_bf16_8(a, keep[k], amax);
+      *reinterpret_cast<uint4*>(out + (size_t)row * dim + c) = keep[k];
+    }
+  }
+  const float m = fmaxf(warp_max(amax), 1e-12f);
+  const float s = 57344.f / m;
+  if (lane == 0) {
+    row_scale[row] = m / 57344.f;
+    row_scale[rows + row] = s;
+  }
+#pragma unroll
+  for (int k = 0; k < SEG_Q_ITERS; ++k) {
+    const int c = (lane + k * 32) * 8;
+    if (c < dim) {
+      float v[8];
+      const float2 a0 = unpack_bf16(keep[k].x), a1 = unpack_bf16(keep[k].y), a2 = unpack_bf16(keep[k].z), a3 = unpack_bf16(keep[k].w);
+      v[0] = a0.x; v[1] = a0.y; v[2] = a1.x; v[3] = a1.y; v[4] = a2.x; v[5] = a2.y; v[6] = a3.x; v[7] = a3.y;
+      *reinterpret_cast<uint2*>(q + (size_t)row * dim + c) = pack_e5m2_8(v, s);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // Token MSE: loss = sum_r weight[seg[r]] * mask[r] * mean_c (pred - target)^2, fp32,
 // deterministic: per-block partials then a single-block ordered sum.
 // ---------------------------------------------------------------------------------------
@@ -628,6 +752,25 @@ cudaError_t seg_scale(const void* x, const float* vec, long vec_stride, const in
   if (dim % 8) return cudaErrorInvalidValue;
   seg_scale_kernel<<<grid_for((long)rows * (dim / 8), 256), 256, 0, s>>>(
       (const __nv_bfloat16*)x, vec, vec_stride, seg, (__nv_bfloat16*)out, rows, dim);
+  return cudaGetLastError();
+}
+bool situ_bwd_quant_supported(int f) { return f % 8 == 0 && f <= SITU_Q_ITERS * 256 * 8; }
+cudaError_t situ_bwd_quant(const void* da, long ld_da, const void* up, const void* gate, long ld_in, void* dup, void* dgate,
+                           long ld_out, void* q, long ldq, float* row_scale, int rows, int f, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if (!situ_bwd_quant_supported(f)) return cudaErrorInvalidValue;
+  situ_bwd_quant_kernel<<<rows, 256, 0, s>>>((const __nv_bfloat16*)da, ld_da, (const __nv_bfloat16*)up, (const __nv_bfloat16*)gate,
+                                            ld_in, (__nv_bfloat16*)dup, (__nv_bfloat16*)dgate, ld_out, (uint8_t*)q, ldq, row_scale,
+                                            rows, f);
+  return cudaGetLastError();
+}
+bool seg_scale_quant_supported(int dim) { return dim % 8 == 0 && dim <= SEG_Q_ITERS * 32 * 8; }
+cudaError_t seg_scale_quant(const void* x, const float* vec, long vec_stride, const int* seg, void* out, void* q, float* row_scale,
+                            int rows, int dim, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if (!seg_scale_quant_supported(dim)) return cudaErrorInvalidValue;
+  seg_scale_quant_kernel<<<(rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK, 32 * ROWS_PER_BLOCK, 0, s>>>(
+      (const __nv_bfloat16*)x, vec, vec_stride, seg, (__nv_bfloat16*)out, (uint8_t*)q, row_scale, rows, dim);
   return cudaGetLastError();
 }
 int token_mse_blocks(int rows) {

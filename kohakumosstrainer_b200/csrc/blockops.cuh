@@ -90,6 +90,13 @@ cudaError_t gated_residual(const void* x, const void* o, const float* gate, long
                            void* out, int rows, int dim, cudaStream_t s);
 cudaError_t seg_scale(const void* x, const float* vec, long vec_stride, const int* seg, void* out, int rows, int dim,
                       cudaStream_t s);
+// Producers of an output gradient that also write its per-row e5m2 copy and scales ([2, rows] = {dequant, quant}).
+bool situ_bwd_quant_supported(int f);
+cudaError_t situ_bwd_quant(const void* da, long ld_da, const void* up, const void* gate, long ld_in, void* dup, void* dgate,
+                           long ld_out, void* q, long ldq, float* row_scale, int rows, int f, cudaStream_t s);
+bool seg_scale_quant_supported(int dim);
+cudaError_t seg_scale_quant(const void* x, const float* vec, long vec_stride, const int* seg, void* out, void* q, float* row_scale,
+                            int rows, int dim, cudaStream_t s);
 int token_mse_blocks(int rows);
 cudaError_t token_mse_fwd(const TokenMseArgs& a, float* partial, float* loss, cudaStream_t s);
 cudaError_t token_mse_bwd(const TokenMseArgs& a, const float* dloss, void* dpred, cudaStream_t s);

@@ -593,7 +593,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
         };
         // (acc * s [* col] + bias) [* gate] [+ beta * res] on 32 columns starting at n0
-        auto linear32 = [&](const uint32_t (&r)[32], int n0, float (&v)[32]) {
+        // `rp`: this row's residual for the 32 columns, already in registers (4 x 16 bytes), or nullptr to load it here
+        auto linear32 = [&](const uint32_t (&r)[32], int n0, float (&v)[32], const uint4* rp = nullptr) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = (p.int8 ? (float)(int)r[j] : __uint_as_float(r[j])) * row_s;
           if (has_col) {
@@ -618,7 +619,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             }
           }
           if (has_res && row_ok) {
-            const uint4* r4 = reinterpret_cast<const uint4*>(p.res + (size_t)m * p.ldr + n0);
+            const uint4* r4 = rp != nullptr ? rp : reinterpret_cast<const uint4*>(p.res + (size_t)m * p.ldr + n0);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const uint4 w = r4[i];
@@ -629,10 +630,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
         };
         if (p.epilogue == EPI_LINEAR) {
+          // The residual is a global load of a row the thread owns (about a microsecond from L2 / DRAM). Slab s + 1's
+          // 128 bytes are requested before slab s is worked on, so the wait falls under tensor-memory loads and math.
+          uint4 res_cur[8], res_nxt[8];
+          auto request_res = [&](int n0, uint4 (&dst)[8]) {
+            if (has_res && row_ok) {
+#pragma unroll
+              for (int half = 0; half < 2; ++half)
+                if (n0 + half * 32 < p.N) {
+                  const uint4* r4 = reinterpret_cast<const uint4*>(p.res + (size_t)m * p.ldr + n0 + half * 32);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) dst[4 * half + i] = r4[i];
+                }
+            }
+          };
+          request_res(n_tile, res_nxt);
 #pragma unroll 1
           for (int sl = 0; sl < BN / 64; ++sl) {
             const int n0 = n_tile + sl * 64;
             if (n0 >= p.N) break;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) res_cur[i] = res_nxt[i];
+            if (sl + 1 < BN / 64 && n0 + 64 < p.N) request_res(n0 + 64, res_nxt);
             slab_acquire(true);
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
@@ -641,7 +660,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
               tmem_ld_wait();
               float v[32];
               if (n0 + half * 32 < p.N) {
-                linear32(r, n0 + half * 32, v);
+                linear32(r, n0 + half * 32, v, has_res ? res_cur + 4 * half : nullptr);
               } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = 0.f;
@@ -701,6 +720,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             if (n_head >= p.N) break;
             if (n_head < p.rope_cols) {
               const __nv_bfloat16* w = (n_head < p.rope_cols / 2) ? p.q_norm_w : p.k_norm_w;
+              if (row_ok) {  // this row's cos | sin (512 bytes) is wanted after the sum of squares: start fetching it now
+                const char* rope_row = reinterpret_cast<const char*>(p.rope + (size_t)m * 128);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) asm volatile("prefetch.global.L1 [%0];" ::"l"(rope_row + 128 * i));
+              }
               float ss = 0.f;
 #pragma unroll 1
               for (int c = 0; c < 4; ++c) {

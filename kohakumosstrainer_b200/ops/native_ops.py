@@ -15,6 +15,8 @@ base GEMM's accumulator. The reference composes these ops from Triton kernels pl
 
 from __future__ import annotations
 
+import os
+
 import torch
 from torch import Tensor
 
@@ -72,6 +74,9 @@ class LoraPack:
 # the codes (the row is re-read from cache), where a per-tensor scale needs a full pass for the maximum
 # before the cast; it is also the finer scale. False selects the per-tensor path.
 FP8_ACT_ROWS = True
+# KMOSS_PREQUANT=1: the gradient producers (SiTU backward, gate scaling) write the e5m2 copy themselves instead of a
+# separate pass of the row quantiser over their output
+PREQUANT = os.environ.get("KMOSS_PREQUANT", "0") == "1"
 
 
 def _rows(xs) -> bool:
@@ -114,13 +119,13 @@ class _LinearCore:
         return out, t, xs
 
     @staticmethod
-    def backward(d, x, wp: WeightPack, lp: LoraPack | None, t, xs, need_dx=True, need_bias=False):
-        """`d`: gradient w.r.t. the pre-epilogue linear output, bf16 [M, out].
+    def backward(d, x, wp: WeightPack, lp: LoraPack | None, t, xs, need_dx=True, need_bias=False, dq=None, ds=None):
+        """`d`: gradient w.r.t. the pre-epilogue linear output, bf16 [M, out]; `dq`, `ds`: its per-row e5m2
+        copy and scales when the kernel that produced `d` already wrote them.
         Returns (dx, d_down [R, in], d_up [out, R], dW, dbias)."""
         dx = d_down = d_up = dW = dbias = None
         fp8 = wp.kind == "fp8"
-        dq = ds = None
-        if fp8 and need_dx:
+        if fp8 and need_dx and dq is None:
             d_main = d if wp.per_tensor else (d.float() * wp.col_scale).to(BF16)  # row recipe: scale varies along K
             dq, ds = native.quantize_fp8_rows(d_main, E5M2, both=True) if FP8_ACT_ROWS else native.quantize_fp8(d_main, E5M2)
         if lp is not None:
@@ -546,18 +551,31 @@ class FusedLinearFn(torch.autograd.Function):
         ops = native.load()
         dout = dout.contiguous()
         dres = dgate = None
+        # the kernel that produces the linear's output gradient also writes its per-row e5m2 copy when dgrad will read one
+        prequant = FP8_ACT_ROWS and PREQUANT and wp.kind == "fp8" and wp.per_tensor and ctx.needs_input_grad[1]
+        dq = ds = None
         if mode == "gated":
             if ctx.needs_input_grad[2]:
                 dres = dout if cfg["r"] == 1.0 else dout * cfg["r"]
             if gate is not None:
                 d = torch.empty_like(dout)
-                ops.seg_scale(dout, gate, cfg["seg"], d)
+                if prequant and dout.is_contiguous():
+                    dq, ds = torch.empty(dout.shape, dtype=E5M2, device=dout.device), torch.empty(2, dout.shape[0], device=dout.device)
+                    if not ops.seg_scale_quant(dout, gate, cfg["seg"], d, dq, ds):
+                        dq = ds = None
+                if dq is None:
+                    ops.seg_scale(dout, gate, cfg["seg"], d)
             else:
                 d = dout
         elif mode == "situ":
             f = aux.shape[1] // 2
             d = torch.empty_like(aux)
-            ops.situ_bwd(dout, aux[:, :f], aux[:, f:], d[:, :f], d[:, f:])
+            if prequant:
+                dq, ds = torch.empty(aux.shape, dtype=E5M2, device=aux.device), torch.empty(2, aux.shape[0], device=aux.device)
+                if not ops.situ_bwd_quant(dout, aux[:, :f], aux[:, f:], d[:, :f], d[:, f:], dq, ds):
+                    dq = ds = None
+            if dq is None:
+                ops.situ_bwd(dout, aux[:, :f], aux[:, f:], d[:, :f], d[:, f:])
         elif mode == "qkrope":
             rc = cfg["rope_cols"]
             heads = rc // 256
@@ -574,7 +592,7 @@ class FusedLinearFn(torch.autograd.Function):
         else:
             d = dout
         dx, d_down, d_up, dW, dbias = _LinearCore.backward(
-            d, x, wp, lp, t, xs, need_dx=ctx.needs_input_grad[1], need_bias=ctx.needs_input_grad[4]
+            d, x, wp, lp, t, xs, need_dx=ctx.needs_input_grad[1], need_bias=ctx.needs_input_grad[4], dq=dq, ds=ds
         )
         if d_down is not None:
             d_down, d_up = d_down.to(lp.down.dtype), d_up.to(lp.up.dtype)

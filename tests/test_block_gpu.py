@@ -300,3 +300,42 @@ def test_fused_adamw_state_formats_match_the_cpu_reference(states, writeback):
             # with 8-bit states a code on the other side of a rounding boundary moves a single element by a few 1e-4
             torch.testing.assert_close(full_a, full_b, rtol=1e-3, atol=2e-3 if states == "8bit" else 2e-4)
 
+
+
+@pytest.mark.gpu
+def test_gradient_producers_emit_the_row_quantised_copy():
+    """SiTU backward and the gate scaling write bf16 d plus its per-row e5m2 copy in one pass: both equal the
+    unfused kernel followed by the row quantiser."""
+    from kohakumosstrainer_b200.ops import native
+
+    ops = native.load()
+    g = torch.Generator(device="cuda").manual_seed(21)
+    for M, F in ((300, 8192), (77, 512)):
+        aux = (torch.randn(M, 2 * F, device="cuda", generator=g) * 2).bfloat16()
+        da = torch.randn(M, F, device="cuda", generator=g).bfloat16()
+        d_ref = torch.empty_like(aux)
+        ops.situ_bwd(da, aux[:, :F], aux[:, F:], d_ref[:, :F], d_ref[:, F:])
+        q_ref, s_ref = native.quantize_fp8_rows(d_ref, torch.float8_e5m2, both=True)
+        d = torch.empty_like(aux)
+        q = torch.empty(M, 2 * F, dtype=torch.float8_e5m2, device="cuda")
+        s = torch.empty(2, M, device="cuda")
+        assert ops.situ_bwd_quant(da, aux[:, :F], aux[:, F:], d[:, :F], d[:, F:], q, s)
+        assert torch.equal(d, d_ref)
+        torch.testing.assert_close(s, s_ref, rtol=1e-6, atol=0)
+        assert (q.view(torch.uint8) != q_ref.view(torch.uint8)).float().mean() < 1e-3
+    for M, D in ((513, 3072), (40, 256)):
+        x = torch.randn(M, D, device="cuda", generator=g).bfloat16()
+        mod = torch.randn(3, 6, D, device="cuda", generator=g)
+        seg = torch.randint(0, 3, (M,), device="cuda", generator=g, dtype=torch.int32).sort().values
+        y_ref = torch.empty_like(x)
+        ops.seg_scale(x, mod[:, 2], seg, y_ref)
+        q_ref, s_ref = native.quantize_fp8_rows(y_ref, torch.float8_e5m2, both=True)
+        y, q, s = torch.empty_like(x), torch.empty(M, D, dtype=torch.float8_e5m2, device="cuda"), torch.empty(2, M, device="cuda")
+        assert ops.seg_scale_quant(x, mod[:, 2], seg, y, q, s)
+        assert torch.equal(y, y_ref)
+        torch.testing.assert_close(s, s_ref, rtol=1e-6, atol=0)
+        assert (q.view(torch.uint8) != q_ref.view(torch.uint8)).float().mean() < 1e-3
+    # a row wider than the fused kernel covers is declined, not mangled
+    wide = torch.zeros(8, 8192, device="cuda", dtype=torch.bfloat16)
+    assert not ops.seg_scale_quant(wide, torch.ones(1, 8192, device="cuda"), torch.zeros(8, dtype=torch.int32, device="cuda"), torch.empty_like(wide),
+                                   torch.empty(8, 8192, dtype=torch.float8_e5m2, device="cuda"), torch.empty(2, 8, device="cuda"))
