@@ -36,7 +36,8 @@ def _seed():
 def reference_src() -> Path | None:
     """Source tree of the upstream implementation when it is mounted (used as a CPU
     oracle only; tests that need it skip when it is absent)."""
-    for cand in (os.environ.get("KMOSS_REFERENCE_SRC"), "/root/reference/src"):
+    beside = Path(__file__).resolve().parents[2] / "reference" / "src"   # a checkout next to this repository
+    for cand in (os.environ.get("KMOSS_REFERENCE_SRC"), str(beside)):
         if cand and Path(cand, "kohakumoss").is_dir():
             return Path(cand)
     return None
