@@ -668,6 +668,60 @@ cast_fp8_rows_kernel(const __nv_bfloat16* x, long ldx, int rows, int dim, uint8_
   }
 }
 
+// One CTA of 256 threads per row for wide rows (4096 < dim <= 16384): the row stays in registers between the
+// maximum and the cast, so it is read once. Narrow rows keep the warp-per-row kernel.
+constexpr int WIDE_Q_ITERS = 8;
+template <bool E5M2>
+__global__ void __launch_bounds__(256)
+cast_fp8_wide_rows_kernel(const __nv_bfloat16* x, long ldx, int rows, int dim, uint8_t* q, long ldq, float* row_scale, int with_inverse) {
+  __shared__ float red[8];
+  const int row = blockIdx.x;
+  const __nv_bfloat16* xr = x + (size_t)row * ldx;
+  constexpr float FMAX = E5M2 ? 57344.f : 448.f;
+  uint4 keep[WIDE_Q_ITERS];
+  float m = 0.f;
+#pragma unroll
+  for (int k = 0; k < WIDE_Q_ITERS; ++k) {
+    const int c = (threadIdx.x + k * 256) * 8;
+    if (c < dim) {
+      keep[k] = *reinterpret_cast<const uint4*>(xr + c);
+      const float2 a = unpack_bf16(keep[k].x), b = unpack_bf16(keep[k].y), cc = unpack_bf16(keep[k].z), d = unpack_bf16(keep[k].w);
+      m = fmaxf(m, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))));
+      m = fmaxf(m, fmaxf(fmaxf(fabsf(cc.x), fabsf(cc.y)), fmaxf(fabsf(d.x), fabsf(d.y))));
+    }
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+  m = fmaxf(m, 1e-12f);
+  const float s = FMAX / m;
+  if (threadIdx.x == 0) {
+    row_scale[row] = m / FMAX;
+    if (with_inverse) row_scale[rows + row] = s;
+  }
+#pragma unroll
+  for (int k = 0; k < WIDE_Q_ITERS; ++k) {
+    const int c = (threadIdx.x + k * 256) * 8;
+    if (c < dim) {
+      const float2 a = unpack_bf16(keep[k].x), b = unpack_bf16(keep[k].y), cc = unpack_bf16(keep[k].z), d = unpack_bf16(keep[k].w);
+      uint2 o;
+      if constexpr (E5M2) {
+        __nv_fp8x4_e5m2 lo(make_float4(a.x * s, a.y * s, b.x * s, b.y * s));
+        __nv_fp8x4_e5m2 hi(make_float4(cc.x * s, cc.y * s, d.x * s, d.y * s));
+        o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+      } else {
+        __nv_fp8x4_e4m3 lo(make_float4(a.x * s, a.y * s, b.x * s, b.y * s));
+        __nv_fp8x4_e4m3 hi(make_float4(cc.x * s, cc.y * s, d.x * s, d.y * s));
+        o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+      }
+      *reinterpret_cast<uint2*>(q + (size_t)row * ldq + c) = o;
+    }
+  }
+}
+
 inline int grid_for(long work, int threads, int cap_mult = 8) {
   long b = (work + threads - 1) / threads;
   long cap = 148L * cap_mult;
@@ -809,6 +863,11 @@ cudaError_t fp8_cast_rows(const void* x, long ldx, int rows, int dim, void* q, l
                           bool with_inverse, cudaStream_t s) {
   if (rows <= 0) return cudaSuccess;
   if (dim % 8) return cudaErrorInvalidValue;
+  if (dim > 4096 && dim <= WIDE_Q_ITERS * 256 * 8 && (ldx % 8) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    if (e5m2) cast_fp8_wide_rows_kernel<true><<<rows, 256, 0, s>>>((const __nv_bfloat16*)x, ldx, rows, dim, (uint8_t*)q, ldq, row_scale, with_inverse);
+    else cast_fp8_wide_rows_kernel<false><<<rows, 256, 0, s>>>((const __nv_bfloat16*)x, ldx, rows, dim, (uint8_t*)q, ldq, row_scale, with_inverse);
+    return cudaGetLastError();
+  }
   const int grid = (rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
   if (e5m2) cast_fp8_rows_kernel<true><<<grid, 32 * ROWS_PER_BLOCK, 0, s>>>((const __nv_bfloat16*)x, ldx, rows, dim, (uint8_t*)q, ldq,
                                                                             row_scale, with_inverse);

@@ -74,9 +74,9 @@ class LoraPack:
 # the codes (the row is re-read from cache), where a per-tensor scale needs a full pass for the maximum
 # before the cast; it is also the finer scale. False selects the per-tensor path.
 FP8_ACT_ROWS = True
-# KMOSS_PREQUANT=1: the gradient producers (SiTU backward, gate scaling) write the e5m2 copy themselves instead of a
-# separate pass of the row quantiser over their output
-PREQUANT = os.environ.get("KMOSS_PREQUANT", "0") == "1"
+# the gradient producers (SiTU backward, gate scaling) write the e5m2 copy themselves instead of a separate pass of the
+# row quantiser over their output (451 -> 443 ms per step); KMOSS_PREQUANT=0 runs the separate pass
+PREQUANT = os.environ.get("KMOSS_PREQUANT", "1") != "0"
 
 
 def _rows(xs) -> bool:

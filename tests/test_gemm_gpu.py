@@ -74,6 +74,14 @@ def test_quantize_matches_torch_cast():
     torch.testing.assert_close(rs5[1], 57344.0 / ramax)
     ref5 = (x.float() * (57344.0 / ramax)[:, None]).to(torch.float8_e5m2)
     assert (q5.view(torch.uint8) != ref5.view(torch.uint8)).float().mean() < 1e-3
+    for dim in (4104, 9216, 16384):       # rows wide enough for the one-CTA-per-row kernel
+        xw = (torch.randn(37, dim, device="cuda") * 3).bfloat16()
+        for dt, fmax in ((torch.float8_e4m3fn, 448.0), (torch.float8_e5m2, 57344.0)):
+            qw, sw = native.quantize_fp8_rows(xw, dt, both=True)
+            am = xw.float().abs().amax(1)
+            torch.testing.assert_close(sw[0], am / fmax)
+            refw = (xw.float() * (fmax / am)[:, None]).to(dt)
+            assert (qw.view(torch.uint8) != refw.view(torch.uint8)).float().mean() < 1e-3
 
 
 def test_linear_epilogue_scales_bias_gate_residual():
