@@ -103,16 +103,27 @@ class StageModule:
     def __init__(self, model, lo: int, hi: int, first: bool, last: bool):
         self.model, self.lo, self.hi, self.first, self.last = model, lo, hi, first, last
 
+    @staticmethod
+    def _all_parameters(module):
+        """Parameters of `module` and of the adapters attached to its linears (an adapter hangs off its
+        linear outside the module tree, so `module.parameters()` does not list it)."""
+        out = list(module.parameters())
+        for sub in module.modules():
+            adapter = sub.__dict__.get("adapter")
+            if adapter is not None:
+                out += list(adapter.parameters())
+        return out
+
     def parameters(self):
         m = self.model
         params = []
         for i in range(self.lo, self.hi):
-            params += list(m.layers[i].parameters())
+            params += self._all_parameters(m.layers[i])
         if self.first:
             for mod in (m.video_embedder, m.text_embedder, m.time_embedding, m.shared_block_modulation, m.video_head_modulation):
-                params += list(mod.parameters())
+                params += self._all_parameters(mod)
         if self.last:
-            params += list(m.final_norm_video.parameters()) + list(m.final_linear_video.parameters())
+            params += self._all_parameters(m.final_norm_video) + self._all_parameters(m.final_linear_video)
         return [p for p in params if p.requires_grad]
 
     def release_others(self) -> None:

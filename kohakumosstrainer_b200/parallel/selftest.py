@@ -218,7 +218,7 @@ def fsdp_worker(rank, world, device, out_dir, fused_step=False, optimizer="adamw
     _write(out_dir, rank, result)
 
 
-def pipeline_worker(rank, world, device, out_dir, n_stages=2, schedule="1f1b", micro=4):
+def pipeline_worker(rank, world, device, out_dir, n_stages=2, schedule="1f1b", micro=4, algo="full"):
     """Pipeline (x data parallel when world > n_stages) against single-process gradient
     accumulation over the same micro-batches: equal loss and equal gradients per stage."""
     from ..data import SyntheticConfig, SyntheticDataset
@@ -233,17 +233,31 @@ def pipeline_worker(rank, world, device, out_dir, n_stages=2, schedule="1f1b", m
     dtype = torch.bfloat16 if cuda else torch.float32
     if not cuda:
         torch.set_num_threads(2)
-    cfg = TrainerConfig(algo="full", optimizer="adamw", lr=1e-3, weight_decay=0.0, schedule={"mode": "constant"}, grad_clip=0.0,
+    cfg = TrainerConfig(algo=algo, optimizer="adamw", lr=1e-3, weight_decay=0.0, schedule={"mode": "constant"}, grad_clip=0.0,
                         timestep="logit_normal", seed=5, ddp_backend="kohakumoss" if cuda else "torch")
     data = SyntheticDataset(SyntheticConfig(max_tokens=260, min_area=96 * 96, max_area=128 * 128, size_step=32, text_dim=64, max_text=12, min_text=3,
                                             seed=2, dtype=torch.float32))
     model = build_backbone(arch, device=device, dtype=dtype, seed=1)
-    for p in model.parameters():
-        p.requires_grad_(True)
     ref = build_backbone(arch, device=device, dtype=dtype, seed=1)
-    for p in ref.parameters():
-        p.requires_grad_(True)
-    tr = PipelineTrainer(model, cfg, device, n_stages, micro, schedule, "even")
+    named = None
+    if algo == "full":
+        for p in list(model.parameters()) + list(ref.parameters()):
+            p.requires_grad_(True)
+        named_model, named_ref = (lambda: model.named_parameters()), (lambda: ref.named_parameters())
+    else:  # adapters hang off the linears, outside the module tree: the adapter set names them
+        from .. import adapters as adapters_pkg
+
+        acfg = adapters_pkg.AdapterConfig(algo=algo, preset="attn-mlp", dim=4, alpha=4.0, seed=3, dtype=dtype)
+        aset, aset_ref = adapters_pkg.apply(model, acfg), adapters_pkg.apply(ref, acfg)
+        gen = torch.Generator().manual_seed(17)
+        with torch.no_grad():  # zero-initialised factors would leave half of the gradients at zero
+            for pa, pb in zip(aset.parameters(), aset_ref.parameters()):
+                v = (torch.randn(pa.shape, generator=gen) * 0.05).to(pa)
+                pa.copy_(v)
+                pb.copy_(v)
+        named = list(aset.named_parameters())
+        named_model, named_ref = (lambda: aset.named_parameters()), (lambda: aset_ref.named_parameters())
+    tr = PipelineTrainer(model, cfg, device, n_stages, micro, schedule, "even", named)
     replicas = world // n_stages
     mine = [data.materialize(i, tr.replica, replicas, pin=cuda) for i in range(micro)]
     # reference: every replica's micro-batches through the whole model on this rank
@@ -266,15 +280,15 @@ def pipeline_worker(rank, world, device, out_dir, n_stages=2, schedule="1f1b", m
             loss = token_loss(ref.ops, v, target, b.seq.seg_img, torch.ones(b.seq.batch, device=device)) / total_tokens
             loss.backward()
             ref_loss += loss.item()
-    grads_ref = {n: p.grad.detach().float().clone() for n, p in ref.named_parameters() if p.grad is not None}
-    before = {n: p.detach().float().clone() for n, p in model.named_parameters() if p.numel() > 0}
+    grads_ref = {n: p.grad.detach().float().clone() for n, p in named_ref() if p.grad is not None}
+    before = {n: p.detach().float().clone() for n, p in named_model() if p.numel() > 0}
     # capture this stage's gradients before the optimiser consumes them
     captured = {}
     own = {id(p) for p in tr.params}
     orig_step = tr.bundle.optimizer.step
 
     def spy(*a, **k):
-        for n, p in model.named_parameters():
+        for n, p in named_model():
             if id(p) in own and p.grad is not None:
                 captured[n] = p.grad.detach().float().clone()
         return orig_step(*a, **k)

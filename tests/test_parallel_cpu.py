@@ -130,3 +130,14 @@ def test_shared_host_masters_step_like_one_host_optimiser(tmp_path):
         assert r["worst"] < 1e-6
         assert r["d2h"] == r["owned"][0] * 4 * 4             # a rank fetches only its own slice of the gradients, each of 4 steps
 
+
+def test_pipeline_trains_adapters_of_its_own_stage(tmp_path):
+    """LoRA under the pipeline: every stage steps the adapters of its own blocks, and their gradients equal
+    one process accumulating the same micro-batches."""
+    res = selftest.spawn_results(selftest.pipeline_worker, 2, str(tmp_path), (2, "1f1b", 3, "lora"), timeout_s=180)
+    assert {r["stage"] for r in res} == {0, 1}
+    for r in res:
+        assert r["n_grads"] > 5
+        assert abs(r["loss"] - r["ref_loss"]) / abs(r["ref_loss"]) < 1e-4
+        assert r["worst_grad_err"] < 1e-4, (r["worst"], r["worst_grad_err"])
+
