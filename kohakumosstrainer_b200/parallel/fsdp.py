@@ -85,8 +85,10 @@ class ShardedWeight:
         # the trainable parameter IS the fp32 master shard; `shard_sym` is its bf16 compute copy
         self.param = nn.Parameter(mine.float().contiguous().clone(), requires_grad=True)
         self.master = self.param.data
-        self.exp_avg = torch.zeros_like(self.master)
-        self.exp_avg_sq = torch.zeros_like(self.master)
+        # the moments live here only when AdamW runs inside the reduce-scatter kernel; otherwise the bundle's optimiser
+        # owns them and the kernel (reduce-only) never touches these arguments
+        self.exp_avg = torch.zeros_like(self.master) if engine.fused_step else self.master
+        self.exp_avg_sq = torch.zeros_like(self.master) if engine.fused_step else self.master
         self.ema: Tensor | None = None
         self.flags = symm.SymmetricBuffer(8, torch.int32, engine.device, engine.group, zero=True)
         self.ready = torch.zeros(8, dtype=torch.int32, device=engine.device)

@@ -43,6 +43,7 @@ def main():
     ap.add_argument("--microbatches", type=int, default=4)
     ap.add_argument("--virtual", type=int, default=2)
     ap.add_argument("--checkpoint", default="none")
+    ap.add_argument("--profile", action="store_true", help="rank 0 prints the kernel table of one extra step")
     args = ap.parse_args()
     rank, local, world = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("LOCAL_RANK", "0"), ("WORLD_SIZE", "1")))
     torch.cuda.set_device(local)
@@ -104,6 +105,18 @@ def main():
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     dist.all_reduce(tok, op=dist.ReduceOp.SUM)
     dist.all_reduce(mem, op=dist.ReduceOp.MAX)
+    if args.profile:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step(n - 1)
+            torch.cuda.synchronize()
+        if rank == 0:
+            rows = sorted(((e.device_time_total, e.count, e.key) for e in prof.key_averages() if e.device_time_total > 0), reverse=True)
+            total = sum(r[0] for r in rows)
+            print(f"kernel time {total / 1e3:.1f} ms", file=sys.stderr)
+            for t, c, k in rows[:30]:
+                print(f"{t / 1e3:9.2f} ms {100 * t / total:5.1f}% n={c:5d} {k[:110]}", file=sys.stderr)
     if rank == 0:
         per = ms.item() / args.steps
         print(json.dumps({"metric": "dit_train_latent_tokens_per_s", "value": round(tok.item() / args.steps / per * 1e3, 1), "n_gpus": world,
