@@ -221,6 +221,9 @@ Tensor seg_sum(const Tensor& a_, const optional<Tensor>& b_, const optional<Tens
   a.batch = (int)cu.numel() - 1; a.dim = (int)a_.size(1); a.mode = (int)mode;
   Tensor out = at::empty({a.batch, a.dim}, a_.options().dtype(at::kFloat));
   a.out = out.data_ptr<float>(); a.ldo = a.dim;
+  a.split = kmoss::SEG_SUM_SPLIT;
+  Tensor partial = at::empty({a.split, a.batch, a.dim}, a_.options().dtype(at::kFloat));
+  a.partial = partial.data_ptr<float>();
   KM_CHECK_CUDA(kmoss::seg_sum(a, cur_stream()));
   return out;
 }

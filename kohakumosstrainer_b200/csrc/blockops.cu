@@ -191,11 +191,16 @@ __global__ void norm_weight_grad_kernel(NormModBwdArgs a, float* partial, int ro
 // out[b, col] = sum over rows r of segment b (rows are segment-sorted: cu[b] .. cu[b+1])
 // of f(r, col); mode 0: dy ; mode 1: dy * xhat * w   (d shift / d scale of the norm);
 // mode 2: a[r, col] * b[r, col] (d gate of the gated residual).
+// Two launches: every (column tile, segment, row slice) block sums its slice, then the slices of a segment are added
+// in a fixed order. One block per segment would walk thousands of rows one after the other (1.5 ms per call at
+// 4096-token segments; 58 ms of a 204 ms full-finetune step of six blocks).
 __global__ void seg_sum_kernel(SegSumArgs a) {
   const int col = blockIdx.x * blockDim.x + threadIdx.x;
   const int b = blockIdx.y;
   if (col >= a.dim) return;
-  const int r0 = a.cu[b], r1 = a.cu[b + 1];
+  const int s0 = a.cu[b], s1 = a.cu[b + 1];
+  const int per = (s1 - s0 + a.split - 1) / a.split;
+  const int r0 = min(s1, s0 + (int)blockIdx.z * per), r1 = min(s1, r0 + per);
   float acc = 0.f;
   for (int r = r0; r < r1; ++r) {
     float v = __bfloat162float(a.a[(size_t)r * a.lda + col]);
@@ -209,6 +214,14 @@ __global__ void seg_sum_kernel(SegSumArgs a) {
     }
     acc += v;
   }
+  a.partial[((size_t)blockIdx.z * a.batch + b) * a.dim + col] = acc;
+}
+__global__ void seg_sum_finish_kernel(SegSumArgs a) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  if (col >= a.dim) return;
+  float acc = 0.f;
+  for (int z = 0; z < a.split; ++z) acc += a.partial[((size_t)z * a.batch + b) * a.dim + col];
   a.out[(size_t)b * a.ldo + col] = acc;
 }
 
@@ -754,8 +767,11 @@ cudaError_t norm_weight_grad(const NormModBwdArgs& a, float* partial, int chunks
 }
 cudaError_t seg_sum(const SegSumArgs& a, cudaStream_t s) {
   if (a.batch <= 0) return cudaSuccess;
-  dim3 grid((a.dim + 127) / 128, a.batch);
+  if (a.partial == nullptr || a.split < 1) return cudaErrorInvalidValue;
+  dim3 grid((a.dim + 127) / 128, a.batch, a.split);
   seg_sum_kernel<<<grid, 128, 0, s>>>(a);
+  dim3 grid2((a.dim + 127) / 128, a.batch);
+  seg_sum_finish_kernel<<<grid2, 128, 0, s>>>(a);
   return cudaGetLastError();
 }
 cudaError_t rope_table(const float* pos, const float* bands, float* table, int rows, int axes, int n_bands, cudaStream_t s) {

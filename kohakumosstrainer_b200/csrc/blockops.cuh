@@ -44,7 +44,10 @@ struct SegSumArgs {
   const int* cu;       // [batch + 1] row offsets of the (sorted) segments
   float* out; long ldo;
   int batch, dim, mode;
+  float* partial;      // [split, batch, dim] scratch: a segment's rows are summed in `split` slices, then the slices in order
+  int split;
 };
+constexpr int SEG_SUM_SPLIT = 32;
 
 struct QkRopeArgs {
   const __nv_bfloat16* x; long ldx;   // [rows, heads * 128]

@@ -319,6 +319,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const uint4* src = reinterpret_cast<const uint4*>(p.gather_src[s]);
       uint4* dst = reinterpret_cast<uint4*>(p.gather_dst + (size_t)s * p.gather_slab_bytes);
       size_t v = (size_t)g * NUM_THREADS + threadIdx.x;
+      // sixteen 16-byte loads in flight per thread: the few gather CTAs must cover a peer round trip of microseconds
+      for (; v + 15 * stride < n_vec; v += 16 * stride) {
+        uint4 r[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[i] = src[v + i * stride];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dst[v + i * stride] = r[i];
+      }
       for (; v + 3 * stride < n_vec; v += 4 * stride) {
         const uint4 a = src[v], b = src[v + stride], c = src[v + 2 * stride], d = src[v + 3 * stride];
         dst[v] = a; dst[v + stride] = b; dst[v + 2 * stride] = c; dst[v + 3 * stride] = d;

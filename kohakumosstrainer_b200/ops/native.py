@@ -47,7 +47,7 @@ def load(build_if_missing: bool = True):
 
 # Kernel launches behind each op (own kernels only), for the launch counter benchmarks report.
 _LAUNCHES_PER_OP = {
-    "gemm": 1, "rms_norm_mod_fwd": 1, "rms_norm_mod_bwd": 1, "norm_weight_grad": 1, "seg_sum": 1, "rope_table": 1,
+    "gemm": 1, "rms_norm_mod_fwd": 1, "rms_norm_mod_bwd": 1, "norm_weight_grad": 1, "seg_sum": 2, "rope_table": 1,
     "qk_norm_rope_fwd": 1, "qk_norm_rope_bwd": 1, "situ_fwd": 1, "situ_bwd": 1, "gated_residual": 1, "seg_scale": 1,
     "situ_bwd_quant": 1, "seg_scale_quant": 1,
     "token_mse_fwd": 2, "token_mse_bwd": 1, "quantize_fp8_tensor": 3, "cast_fp8": 1, "quantize_fp8_rows": 1,

@@ -136,6 +136,39 @@ def rank_order(schedule: str, P: int, V: int, n: int, rank: int) -> list[Op]:
     raise ValueError(f"schedule {schedule!r}: the multi-chunk engine runs {SCHEDULES_VIRTUAL}")
 
 
+def op_times(schedule: str, P: int, V: int, n: int) -> list[list[tuple[float, float]]]:
+    """(start, finish) of every operation of every rank's order on a model clock (forward 1, backward 2, transfers
+    free): ranks run their orders as early as their inputs allow. Used to decide WHEN a receive is posted."""
+    S = P * V
+    orders = [rank_order(schedule, P, V, n, r) for r in range(P)]
+    times: list[list[tuple[float, float]]] = [[] for _ in range(P)]
+    fin_f: dict[tuple[int, int], float] = {}
+    fin_b: dict[tuple[int, int], float] = {}
+    free = [0.0] * P
+    while any(len(times[r]) < len(orders[r]) for r in range(P)):
+        moved = False
+        for r in range(P):
+            if len(times[r]) == len(orders[r]):
+                continue
+            kind, i, c = orders[r][len(times[r])]
+            s = stage_of(schedule, P, r, c)
+            if kind == "F":
+                deps = [] if s == 0 else [fin_f.get((i, s - 1))]
+            else:
+                deps = [fin_f.get((i, s))] + ([] if s == S - 1 else [fin_b.get((i, s + 1))])
+            if any(d is None for d in deps):
+                continue
+            start = max([free[r]] + deps)
+            finish = start + (1.0 if kind == "F" else 2.0)
+            (fin_f if kind == "F" else fin_b)[(i, s)] = finish
+            free[r] = finish
+            times[r].append((start, finish))
+            moved = True
+        if not moved:
+            raise RuntimeError(f"{schedule}: the orders of P={P}, n={n} wait on one another")
+    return times
+
+
 def make_links(ranks_of_replicas: list[list[int]], backend: str | None = None) -> dict:
     """Two-rank groups for every directed neighbour link and kind of every replica's ring.
     Collective: every rank of the world calls it with the same argument. -> {(src, dst, kind): group}."""
@@ -148,6 +181,15 @@ def make_links(ranks_of_replicas: list[list[int]], backend: str | None = None) -
         for src, dst in pairs:
             for kind in ("F", "B"):
                 links[(src, dst, kind)] = dist.new_group(sorted((src, dst)), backend=backend)
+    # A communicator is built at its first use, and that build blocks the host until the peer arrives. Schedules make
+    # the ranks reach their links in different orders, so build all of them here, in one order every rank agrees on.
+    me = dist.get_rank()
+    for key in sorted(links):
+        if me in key[:2]:
+            group = links[key]
+            on_gpu = dist.get_backend(group) == "nccl"
+            probe = torch.zeros(1, device=torch.device("cuda", torch.cuda.current_device()) if on_gpu else "cpu")
+            dist.all_reduce(probe, group=group)
     return links
 
 
@@ -204,16 +246,16 @@ class VirtualPipelineEngine:
                        torch.empty((seq.batch, 6, d), dtype=torch.float32, device=self.device),
                        torch.empty((seq.batch, 2, d), dtype=torch.float32, device=self.device))
 
-    def _incoming(self, kind: str, n: int) -> dict[int, list[tuple[int, int]]]:
-        """Per source rank (index in the pipe): the (micro-batch, my chunk) keys of the messages
-        of `kind` it sends me, in its sending order."""
-        out: dict[int, list[tuple[int, int]]] = {}
+    def _incoming(self, kind: str, n: int, times=None) -> dict[int, list[tuple]]:
+        """Per source rank (index in the pipe): the (micro-batch, my chunk, time the message exists on the model
+        clock) of the messages of `kind` it sends me, in its sending order."""
+        out: dict[int, list[tuple]] = {}
         me = self.rank_in_pipe
         for src in range(self.P):
             if src == me:
                 continue
             keys = []
-            for k, i, c in rank_order(self.schedule, self.P, self.V, n, src):
+            for pos, (k, i, c) in enumerate(rank_order(self.schedule, self.P, self.V, n, src)):
                 if k != kind:
                     continue
                 s = stage_of(self.schedule, self.P, src, c)
@@ -222,7 +264,7 @@ class VirtualPipelineEngine:
                     continue
                 r, cc = place_of(self.schedule, self.P, t)
                 if r == me:
-                    keys.append((i, cc))
+                    keys.append((i, cc, times[src][pos][1] if times is not None else 0.0))
             if keys:
                 out[src] = keys
         return out
@@ -231,9 +273,10 @@ class VirtualPipelineEngine:
         n = len(micro_batches)
         me = self.rank_in_pipe
         order = rank_order(self.schedule, self.P, self.V, n, me)
-        incoming = {"F": self._incoming("F", n), "B": self._incoming("B", n)}
+        times = op_times(self.schedule, self.P, self.V, n)
+        incoming = {"F": self._incoming("F", n, times), "B": self._incoming("B", n, times)}
         cursor = {(kind, src): 0 for kind in incoming for src in incoming[kind]}
-        source = {(kind, key): src for kind in incoming for src, keys in incoming[kind].items() for key in keys}
+        source = {(kind, key[:2]): src for kind in incoming for src, keys in incoming[kind].items() for key in keys}
         stash: dict[tuple, tuple] = {}
         local: dict[tuple, list[Tensor]] = {}
         saved: dict[tuple[int, int], tuple] = {}
@@ -245,7 +288,7 @@ class VirtualPipelineEngine:
             pos = cursor[(kind, src)]
             if pos >= len(keys):
                 return
-            i, c = keys[pos]
+            i, c, _ = keys[pos]
             cursor[(kind, src)] = pos + 1
             io = self._alloc_io(micro_batches[i]["seq"])
             g_src = self.ranks[src]
@@ -260,7 +303,6 @@ class VirtualPipelineEngine:
             while (kind, i, c) not in stash:
                 post(kind, src)
             io, works = stash.pop((kind, i, c))
-            post(kind, src)  # the next message of this link transfers while this one is consumed
             for w in works or []:
                 w.wait()
             return io.tensors()
@@ -274,7 +316,17 @@ class VirtualPipelineEngine:
             group = self.links[(self.ranks[me], dst, kind)]
             sends.append(dist.batch_isend_irecv([dist.P2POp(dist.isend, t.detach().contiguous(), dst, group) for t in tensors]))
 
-        for kind, i, c in order:
+        def post_due(now: float) -> None:
+            """Post the receives of every message that exists by `now` on the model clock. A receive is a kernel that
+            waits on the device: posted too early (for a message that needs this rank's later work) it can hold the
+            SMs that later work needs; posted when its message is due, everything it waits for was enqueued before."""
+            for (k, src), pos in list(cursor.items()):
+                keys = incoming[k][src]
+                while cursor[(k, src)] < len(keys) and keys[cursor[(k, src)]][2] <= now:
+                    post(k, src)
+
+        for (kind, i, c), (t_start, _) in zip(order, times[me]):
+            post_due(t_start)
             mb, mod = micro_batches[i], self.mods[c]
             s = stage_of(self.schedule, self.P, me, c)
             if kind == "F":
