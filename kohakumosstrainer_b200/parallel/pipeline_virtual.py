@@ -34,10 +34,13 @@ from torch import Tensor
 from .pipeline import StageIO, StageModule
 
 SCHEDULES_VIRTUAL = ("looped-bfs", "interleaved-1f1b", "zbv")
+SCHEDULES_ONE_CHUNK = ("gpipe", "1f1b")   # one chunk per rank: the same engine with V = 1
 Op = tuple[str, int, int]  # (kind "F" | "B", micro-batch, chunk)
 
 
 def chunks_per_rank(schedule: str, virtual: int = 2) -> int:
+    if schedule in SCHEDULES_ONE_CHUNK:
+        return 1
     return 2 if schedule == "zbv" else max(1, int(virtual))
 
 
@@ -115,6 +118,14 @@ def _simulated(schedule: str, P: int, V: int, n: int) -> list[list[Op]]:
 
 
 def rank_order(schedule: str, P: int, V: int, n: int, rank: int) -> list[Op]:
+    if schedule == "gpipe":
+        return [("F", i, 0) for i in range(n)] + [("B", i, 0) for i in range(n)]
+    if schedule == "1f1b":
+        warm = min(n, P - rank - 1)
+        order: list[Op] = [("F", i, 0) for i in range(warm)]
+        for k in range(n - warm):
+            order += [("F", warm + k, 0), ("B", k, 0)]
+        return order + [("B", i, 0) for i in range(n - warm, n)]
     if schedule == "looped-bfs":
         return [("F", i, c) for c in range(V) for i in range(n)] + [("B", i, c) for c in reversed(range(V)) for i in range(n)]
     if schedule == "interleaved-1f1b":
@@ -223,8 +234,8 @@ class VirtualPipelineEngine:
 
     def __init__(self, model, stage: int, n_stages: int, bounds, device, ranks: list[int], links: dict, schedule: str = "interleaved-1f1b",
                  virtual: int = 2, compute_dtype=torch.bfloat16):
-        if schedule not in SCHEDULES_VIRTUAL:
-            raise ValueError(f"PIPELINE_SCHEDULE {schedule!r}: the multi-chunk engine runs {SCHEDULES_VIRTUAL}")
+        if schedule not in SCHEDULES_VIRTUAL + SCHEDULES_ONE_CHUNK:
+            raise ValueError(f"PIPELINE_SCHEDULE {schedule!r}: this engine runs {SCHEDULES_ONE_CHUNK + SCHEDULES_VIRTUAL}")
         self.P, self.V, self.rank_in_pipe, self.schedule = n_stages, chunks_per_rank(schedule, virtual), stage, schedule
         self.S = self.P * self.V
         if len(bounds) != self.S:

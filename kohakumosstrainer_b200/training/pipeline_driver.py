@@ -17,7 +17,7 @@ import torch.distributed as dist
 from ..diffusion import TIMESTEPS, TokenNormalizer, noise_latents, token_loss
 from ..optim import Bundle, build_optimizer
 from ..parallel.pipeline import PipelineEngine, pp_dp_groups, stage_bounds
-from ..parallel.pipeline_virtual import SCHEDULES_VIRTUAL, VirtualPipelineEngine, chunks_per_rank, make_links
+from ..parallel.pipeline_virtual import SCHEDULES_ONE_CHUNK, SCHEDULES_VIRTUAL, VirtualPipelineEngine, chunks_per_rank, make_links
 from ..utils.seeds import seed_of
 
 
@@ -30,7 +30,10 @@ class PipelineTrainer:
         self.n_stages, self.micro = n_stages, micro_batches
         self.replicas = self.world // n_stages
         base = self.replica * n_stages
-        if schedule in SCHEDULES_VIRTUAL:  # several chunks per rank
+        if schedule in SCHEDULES_VIRTUAL or (schedule in SCHEDULES_ONE_CHUNK and n_stages > 1):
+            # one engine for every schedule (gpipe / 1f1b are its one-chunk case): per-link communicators and receives
+            # posted when due; on two B200s 1f1b took 1133 ms per step on the shared-communicator engine, the
+            # multi-chunk schedules 500 to 570 ms on this one
             chunks = chunks_per_rank(schedule, virtual)
             bounds = stage_bounds(model.cfg, n_stages * chunks, split)
             rings = [[r * n_stages + s for s in range(n_stages)] for r in range(self.replicas)]
