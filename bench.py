@@ -158,6 +158,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    verbose = os.environ.get("KMOSS_BENCH_VERBOSE", "0") == "1"
+
     def timed(run_step, offset):
         """W warm-up + K timed steps; returns (ms per step max over ranks, image tokens this rank)."""
         for i in range(args.warmup):
@@ -166,11 +168,22 @@ def main():
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         tokens = 0
         launches0 = native.LAUNCHES["count"]
+        marks = []
         start.record()
         for i in range(args.steps):
             tokens += run_step(offset + args.warmup + i)
+            if verbose:  # per-step device times on stderr (KMOSS_BENCH_VERBOSE=1): an extra event record per step
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append(ev)
         end.record()
         sync()
+        if verbose and rank == 0:
+            prev, per = start, []
+            for ev in marks:
+                per.append(round(prev.elapsed_time(ev), 1))
+                prev = ev
+            print(f"per-step ms: {per} image tokens: {[host[offset + args.warmup + i].image_tokens for i in range(args.steps)]}", file=sys.stderr)
         ms = torch.tensor([start.elapsed_time(end)], device=device)
         tok = torch.tensor([float(tokens)], device=device)
         if world > 1:
