@@ -433,7 +433,7 @@ int64_t opt_record_bytes() { return (int64_t)sizeof(kmoss::OptTensor); }
 int64_t opt_chunk_elems() { return kmoss::opt_chunk_elems(); }
 
 void adamw_multi(const Tensor& table, const Tensor& chunks, double lr, double beta1, double beta2, double eps,
-                 int64_t step, double ema_decay, const optional<Tensor>& grad_scale, const optional<Tensor>& skip) {
+                 int64_t step, double ema_decay, const optional<Tensor>& grad_scale, const optional<Tensor>& skip, bool plain) {
   c10::cuda::CUDAGuard guard(table.device());
   kmoss::AdamWHyper h{};
   h.lr = (float)lr; h.beta1 = (float)beta1; h.beta2 = (float)beta2; h.eps = (float)eps;
@@ -444,7 +444,7 @@ void adamw_multi(const Tensor& table, const Tensor& chunks, double lr, double be
   h.grad_scale = cptr<float>(grad_scale);
   h.skip = cptr<int>(skip);
   KM_CHECK_CUDA(kmoss::adamw_multi(reinterpret_cast<const kmoss::OptTensor*>(table.data_ptr()),
-                                   reinterpret_cast<const int2*>(chunks.data_ptr()), (int)chunks.size(0), h, cur_stream()));
+                                   reinterpret_cast<const int2*>(chunks.data_ptr()), (int)chunks.size(0), h, plain, cur_stream()));
 }
 
 // returns fp32 [3] = {norm, clip coefficient, sum of squares}
@@ -614,7 +614,7 @@ TORCH_LIBRARY(kmoss_b200, m) {
   m.def("opt_record_bytes() -> int", &opt_record_bytes);
   m.def("opt_chunk_elems() -> int", &opt_chunk_elems);
   m.def("adamw_multi(Tensor table, Tensor chunks, float lr, float beta1, float beta2, float eps, int step, "
-        "float ema_decay, Tensor? grad_scale, Tensor? skip) -> ()", &adamw_multi);
+        "float ema_decay, Tensor? grad_scale, Tensor? skip, bool plain=False) -> ()", &adamw_multi);
   m.def("grad_norm_multi(Tensor table, Tensor chunks, float max_norm, Tensor(a!)? nonfinite) -> Tensor", &grad_norm_multi);
   m.def("ema_multi(Tensor table, Tensor chunks, float decay, Tensor? skip) -> ()", &ema_multi);
   m.def("kernel_status() -> Tensor", &kernel_status);

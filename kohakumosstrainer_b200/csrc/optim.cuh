@@ -41,7 +41,8 @@ struct AdamWHyper {
 };
 
 int opt_chunk_elems();
-cudaError_t adamw_multi(const OptTensor* tensors, const int2* chunks, int n_chunks, const AdamWHyper& h, cudaStream_t s);
+// plain: every tensor of the table has fp32 states and nearest writeback (no 8-bit codes, no compensation buffer)
+cudaError_t adamw_multi(const OptTensor* tensors, const int2* chunks, int n_chunks, const AdamWHyper& h, bool plain, cudaStream_t s);
 // partial: [n_chunks] fp32 scratch; out[0] = norm, out[1] = clip coefficient, out[2] = sum of squares
 cudaError_t grad_norm_multi(const OptTensor* tensors, const int2* chunks, int n_chunks, float* partial, int* nonfinite,
                             float max_norm, float* out, cudaStream_t s);

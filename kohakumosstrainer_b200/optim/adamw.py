@@ -95,6 +95,8 @@ class ParamTable:
         self.table = torch.frombuffer(bytes(rec) or b"\0", dtype=torch.uint8).clone().to(device)
         self.chunks = torch.tensor(chunks or [(0, 0)], dtype=torch.int32).reshape(-1, 2)[: len(chunks)].to(device)
         self.keys = tuple((e["param"].data_ptr(), e["grad"].data_ptr()) for e in entries)
+        # fp32 states and nearest writeback everywhere: the step may run the kernel without the other formats' code
+        self.plain = all(not e.get("mode") and e.get("comp") is None and e.get("mq") is None and e.get("m") is not None for e in entries)
 
 
 class FusedAdamW(torch.optim.Optimizer):
@@ -165,7 +167,7 @@ class FusedAdamW(torch.optim.Optimizer):
                     table = ParamTable(entries, entries[0]["param"].device)
                     self._tables[gi] = table
                 native.load().adamw_multi(table.table, table.chunks, group["lr"], b1, b2, group["eps"], self._steps,
-                                          self.ema_decay, grad_scale, skip)
+                                          self.ema_decay, grad_scale, skip, table.plain)
             else:
                 self._reference_step(entries, group, grad_scale, skip)
 
